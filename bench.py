@@ -1,0 +1,330 @@
+#!/usr/bin/env python
+"""Benchmark of the hot path: RWKV7 generalized delta rule forward + backward, tokens/s.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload cfg1|cfg2]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+One "step" is one forward + backward of ``generalized_delta_rule`` on one batch of synthetic
+input (benchmark configuration 1: bf16, B=8, T=4096, H=32, K=V=64, no initial state, upstream
+gradients for the output and the final state).  With N > 1 every rank runs the same per-GPU
+workload on its own batch (batch x head units are independent: no collective on the data path),
+so scaling is weak and ``value`` is the sum over ranks.
+
+Prints ONE JSON line (rank 0).  ``value``: inputs resident in HBM, device-timed with CUDA events,
+max over ranks.  ``e2e``: the same metric through the public API with HOST buffers, host->device
+and device->host copies of every input and output inside the timed region.  ``roofline``: the
+dominant kernel's achieved algorithmic bytes/s, timed with CUDA events around its launches inside
+the timed region.  ``cpu_baseline``: the CPU oracle (a port of the reference's native operator)
+timed on this host on a bounded sample.
+
+``--impl reference`` times the reference's own CPU implementation of the path (the oracle port of
+``rwkv_ops/rwkv7_kernel/native_keras_op.py``; the reference checkout itself does not travel to the
+GPU box) with all host threads, each step a bounded sample of the workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # name: B, T, H, with initial state
+    "cfg1": dict(B=8, T=4096, H=32, state=False, desc="rwkv7_fwd_bwd_bf16_B8_T4096_H32_K64"),
+    "cfg2": dict(B=16, T=8192, H=64, state=True, desc="rwkv7_fwd_bwd_bf16_B16_T8192_H64_K64_h0_padded"),
+}
+# algorithmic work per token*head (K = V = 64, bf16 token tensors): forward reads 6 and writes 1
+# vector of 128 B, backward reads 7 and writes 6
+BYTES_PER_TOKEN_HEAD = 2560
+FLOP_PER_TOKEN_HEAD = 434176
+CPU_SAMPLE_T = 256     # tokens per sequence of the cpu_baseline sample
+REF_STEP_T = 128       # tokens per sequence of one --impl reference step
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return dict(hbm_gbs=d["hbm_gbs"], bf16_tflops=d["bf16_tflops"], source="measured")
+    return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML (read-only) while the timed region runs."""
+
+    def __init__(self, index):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._th = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _run(self):
+        nv = self.nv
+        names = {
+            "hw_slowdown": getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8),
+            "hw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40),
+            "sw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20),
+            "sw_power_cap": getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4),
+        }
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                try:
+                    mask = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                except Exception:
+                    mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for n, bit in names.items():
+                    if mask & bit:
+                        self.reasons.add(n)
+            except Exception:
+                pass
+            self._stop.wait(0.05)
+
+    def __enter__(self):
+        if self.nv is not None:
+            self._th = threading.Thread(target=self._run, daemon=True)
+            self._th.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        if self._th is not None:
+            self._th.join()
+
+    def summary(self):
+        return {"sm_mhz": statistics.median(self.samples) if self.samples else None,
+                "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons)}
+
+
+def cpu_reference_step(B, T, H, with_state, seed):
+    """One forward + backward of the CPU oracle (port of the reference's native operator)."""
+    from oracle import generalized_delta_rule as oracle_gdr
+    from rwkv_ops_b200.workloads import rwkv7_inputs
+    d = rwkv7_inputs(B, T, H, dtype=torch.bfloat16, seed=seed, with_state=with_state, with_grads=True)
+    g = {n: d[n].requires_grad_(True) for n in "rwkvab"}
+    t0 = time.perf_counter()
+    o, s = oracle_gdr(*[g[n] for n in "rwkvab"], initial_state=d.get("initial_state"))
+    ((o.float() * d["d_out"].float()).sum() + (s * d["d_state"]).sum()).backward()
+    return time.perf_counter() - t0
+
+
+def run_reference(args, wl):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    B, H, T = wl["B"], wl["H"], REF_STEP_T
+    for i in range(args.warmup):
+        cpu_reference_step(B, T, H, wl["state"], 10 + i)
+    total = 0.0
+    for i in range(args.steps):
+        total += cpu_reference_step(B, T, H, wl["state"], 100 + i)
+    ms = 1e3 * total / args.steps
+    val = B * T / (ms / 1e3)
+    sample = f"B={B} H={H} first {T} of {wl['T']} tokens per sequence, fwd+bwd, float32 CPU"
+    line = {
+        "impl": "reference", "metric": "rwkv7_fwd_bwd_tokens_per_s", "value": val, "unit": "tokens/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": wl["desc"], "sample": sample},
+        "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def run_ours(args, wl):
+    import torch.distributed as dist
+    import rwkv_ops_b200 as ro
+    from rwkv_ops_b200 import _lib
+    from rwkv_ops_b200.workloads import rwkv7_inputs, rwkv7_pad_lengths, apply_w_padding
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback)")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    _lib.load()
+
+    B, T, H = wl["B"], wl["T"], wl["H"]
+    d = rwkv7_inputs(B, T, H, dtype=torch.bfloat16, seed=1001 + rank, device=dev, with_state=wl["state"],
+                     with_grads=True)
+    if wl["state"]:   # configuration 2 pads the trailing 0..512 tokens of every sequence through w
+        d["w"] = apply_w_padding(d["w"], rwkv7_pad_lengths(B, T, seed=1002 + rank))
+    names = "rwkvab"
+    leaves = {n: d[n].requires_grad_(True) for n in names}
+    h0 = d.get("initial_state")
+    if h0 is not None:
+        h0.requires_grad_(True)
+    d_out, d_state = d["d_out"], d["d_state"]
+
+    def step():
+        o, s = ro.generalized_delta_rule(*[leaves[n] for n in names], initial_state=h0)
+        torch.autograd.backward([o, s], [d_out, d_state])
+        for n in names:
+            leaves[n].grad = None
+        if h0 is not None:
+            h0.grad = None
+        return o
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(ms):
+        if world > 1:
+            t = torch.tensor([ms], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            return float(t.item())
+        return ms
+
+    # ---- device-resident throughput
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    _lib.profile(True)
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local) as clocks:
+        barrier()
+        ev0.record()
+        for _ in range(args.steps):
+            step()
+        ev1.record()
+        barrier()
+    ms_total = max_over_ranks(ev0.elapsed_time(ev1))
+    prof = _lib.profile_results()
+    _lib.profile(False)
+    ms_step = ms_total / args.steps
+    value = world * B * T / (ms_step / 1e3)
+    launches = sum(n for _, n in prof.values())
+
+    # ---- roofline of the dominant kernel (by summed event time inside the timed region)
+    pk = peaks()
+    roof = None
+    if prof:
+        top = max(prof, key=lambda k_: prof[k_][0])
+        top_ms, top_n = prof[top]
+        per_launch_s = top_ms / top_n / 1e3
+        units = B * T * H
+        # bytes the kernel must move per launch: the backward kernels read 7 and write 6 token
+        # vectors per token*head, the forward kernels read 6 and write 1
+        bytes_per_unit = 1664 if "bwd" in top else 896
+        achieved = units * bytes_per_unit / per_launch_s / 1e9
+        roof = {"kernel": top, "bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
+                "frac": achieved / pk["hbm_gbs"], "traffic": None, "peak_source": pk["source"],
+                "launch_ms": top_ms / top_n,
+                "tensor_tflops_whole_step": units * FLOP_PER_TOKEN_HEAD / (ms_step / 1e3) / 1e12,
+                "kernels": {k_: {"ms_per_step": v[0] / args.steps, "launches_per_step": v[1] / args.steps}
+                            for k_, v in prof.items()}}
+
+    # ---- end to end: host buffers in, host buffers out, through the public API
+    host_in = {n: d[n].detach().to("cpu").pin_memory() for n in names}
+    host_in["d_out"] = d_out.to("cpu").pin_memory()
+    host_in["d_state"] = d_state.to("cpu").pin_memory()
+    if h0 is not None:
+        host_in["h0"] = h0.detach().to("cpu").pin_memory()
+    host_out = {n: torch.empty_like(host_in[n]).pin_memory() for n in names}
+    host_out["o"] = torch.empty_like(host_in["r"]).pin_memory()
+    host_out["ht"] = torch.empty(B, H, 64, 64).pin_memory()
+    if h0 is not None:
+        host_out["dh0"] = torch.empty_like(host_in["h0"]).pin_memory()
+    h2d = sum(t.numel() * t.element_size() for t in host_in.values())
+    d2h = sum(t.numel() * t.element_size() for t in host_out.values())
+
+    def e2e_step():
+        dv = {n: host_in[n].to(dev, non_blocking=True) for n in host_in}
+        lv = {n: dv[n].requires_grad_(True) for n in names}
+        s0 = dv.get("h0")
+        if s0 is not None:
+            s0.requires_grad_(True)
+        o, s = ro.generalized_delta_rule(*[lv[n] for n in names], initial_state=s0)
+        torch.autograd.backward([o, s], [dv["d_out"], dv["d_state"]])
+        host_out["o"].copy_(o.detach(), non_blocking=True)
+        host_out["ht"].copy_(s.detach(), non_blocking=True)
+        for n in names:
+            host_out[n].copy_(lv[n].grad, non_blocking=True)
+        if s0 is not None:
+            host_out["dh0"].copy_(s0.grad, non_blocking=True)
+        torch.cuda.current_stream().synchronize()   # results are on the host when the step ends
+
+    e2e_steps = max(2, min(args.steps, 5))
+    for _ in range(2):
+        e2e_step()
+    barrier()
+    t0 = time.perf_counter()
+    ev0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    ev1.record()
+    barrier()
+    e2e_ms = max_over_ranks(max(ev0.elapsed_time(ev1), 1e3 * (time.perf_counter() - t0))) / e2e_steps
+    e2e_val = world * B * T / (e2e_ms / 1e3)
+
+    if rank == 0:
+        line = {
+            "metric": "rwkv7_fwd_bwd_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": wl["desc"], "per_gpu_batch": B, "seq_len": T, "heads": H,
+                       "sharding": f"batch x head units replicated per GPU, {world} rank(s), no collective",
+                       "l2": "inputs (0.94 GB per step) exceed the 126 MB L2",
+                       "algo": os.environ.get("RWKV_OPS_B200_RWKV7_ALGO", "auto")},
+            "clocks": clocks.summary(),
+            "e2e": {"value": e2e_val, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "ms_per_step": e2e_ms, "steps": e2e_steps},
+            "gpu_launches": launches,
+            "roofline": roof,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            cores = os.cpu_count() or 1
+            torch.set_num_threads(cores)
+            cpu_reference_step(B, 16, H, wl["state"], 5)   # warm the allocator and thread pool
+            sec = cpu_reference_step(B, CPU_SAMPLE_T, H, wl["state"], 6)
+            line["cpu_baseline"] = {
+                "value": B * CPU_SAMPLE_T / sec, "unit": "tokens/s", "cores": cores, "kind": "port",
+                "sample": f"B={B} H={H} first {CPU_SAMPLE_T} of {T} tokens per sequence, fwd+bwd, float32 CPU, "
+                          f"{sec:.1f} s"}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="cfg1", choices=sorted(WORKLOADS))
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    wl = WORKLOADS[args.workload]
+    if args.impl == "reference":
+        run_reference(args, wl)
+    else:
+        run_ours(args, wl)
+
+
+if __name__ == "__main__":
+    main()

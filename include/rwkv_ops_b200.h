@@ -1,0 +1,158 @@
+/*
+ * rwkv_ops_b200 -- C ABI of the sm_100a CUDA library behind the RWKV7
+ * generalized delta rule and the RWKV6 wkv operator.
+ *
+ * Every entry point takes plain device pointers and sizes; the caller owns all
+ * memory (inputs, outputs, workspace) and the stream.  Nothing here allocates,
+ * frees or keeps a pointer after it returns, and all work is enqueued on the
+ * given stream without synchronising it.  Return value: 0 on success, a negative
+ * RWKVB200_E_* code otherwise (rwkvb200_strerror names it).  Nothing traps or
+ * asserts on the device.
+ *
+ * Conventions shared by all entry points
+ *   dtype        RWKVB200_F32 / RWKVB200_BF16 / RWKVB200_F16: element type of the
+ *                token tensors (inputs, outputs and their gradients).  Arithmetic
+ *                and all states are float32.
+ *   head size    64 (key and value); other sizes return RWKVB200_E_UNSUPPORTED.
+ *   decay        every operator applies exp(-exp(w)) to its w input, as the
+ *                reference does (rwkv_ops/rwkv7_kernel/native_keras_op.py:58,
+ *                rwkv_ops/rwkv6_kernel/ops_rwkv_kernel.py:63).
+ *   alignment    token tensors 16-byte aligned, states 16-byte aligned.
+ */
+#ifndef RWKV_OPS_B200_H
+#define RWKV_OPS_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define RWKVB200_ABI_VERSION 1
+
+enum {
+  RWKVB200_F32 = 0,
+  RWKVB200_BF16 = 1,
+  RWKVB200_F16 = 2
+};
+
+enum {
+  RWKVB200_OK = 0,
+  RWKVB200_E_SHAPE = -1,        /* a size is <= 0 or inconsistent */
+  RWKVB200_E_DTYPE = -2,        /* unknown dtype code */
+  RWKVB200_E_ALIGN = -3,        /* a pointer is not 16-byte aligned */
+  RWKVB200_E_NULL = -4,         /* a required pointer is NULL */
+  RWKVB200_E_WORKSPACE = -5,    /* workspace smaller than *_workspace_bytes() */
+  RWKVB200_E_UNSUPPORTED = -6,  /* head size / mode not built */
+  RWKVB200_E_CUDA = -7,         /* the CUDA runtime reported an error at launch */
+  RWKVB200_E_STATE_MAP = -8,    /* a state_map entry is outside [0, n_state) */
+  RWKVB200_E_TOO_LARGE = -9     /* size beyond a fixed-capacity entry point's limit */
+};
+
+/* algo argument of the RWKV7 entry points */
+enum {
+  RWKVB200_ALGO_AUTO = 0,       /* chunked tensor-core path for bf16/f16 tokens, recurrent for f32 */
+  RWKVB200_ALGO_RECURRENT = 1,  /* token-by-token float32 recurrence (float32-exact) */
+  RWKVB200_ALGO_CHUNKED = 2     /* chunked tcgen05 path */
+};
+
+int rwkvb200_abi_version(void);
+const char* rwkvb200_strerror(int code);
+
+/* ------------------------------------------------------------------------------------------
+ * RWKV7 generalized delta rule.
+ * Replaces generalized_delta_rule of the reference
+ * (native: rwkv_ops/rwkv7_kernel/native_keras_op.py:23-95; GPU: rwkv_ops/rwkv7_kernel/torch_op.py:458-490)
+ * and the kernel sequence it launches (chunk_dplr_fwd, torch_op.py:46-120; chunk_dplr_bwd, :123-265).
+ *
+ * Token tensors r,w,k,v,a,b,o (and gradients) hold B*T*H*64 elements, laid out [B,T,H,64] when
+ * head_first == 0 and [B,H,T,64] when head_first != 0.  States are float32 [n,H,64,64] with the
+ * VALUE index before the KEY index (the native operator's layout, native_keras_op.py:85-88).
+ *   h0 / n_state   initial state: n_state = 0 (h0 ignored, zero state), 1 (one state broadcast over
+ *                  the batch, native_keras_op.py:62-63) or B.
+ *   ht             final state [B,H,64,64], may be NULL.
+ * ---------------------------------------------------------------------------------------- */
+
+/* One decode step (T == 1): token tensors are [B,H,64]; state_out may alias state_in when
+ * n_state == B.  Maths of native_keras_op.py:80-91 for a single t. */
+int rwkvb200_rwkv7_step(const void* r, const void* w, const void* k, const void* v,
+                        const void* a, const void* b,
+                        const float* state_in, int n_state, float* state_out, void* o,
+                        int B, int H, int head_size, int dtype, void* stream);
+
+size_t rwkvb200_rwkv7_fwd_workspace_bytes(int B, int T, int H, int head_size, int dtype, int algo);
+
+int rwkvb200_rwkv7_fwd(const void* r, const void* w, const void* k, const void* v,
+                       const void* a, const void* b,
+                       const float* h0, int n_state, void* o, float* ht,
+                       void* workspace, size_t workspace_bytes,
+                       int B, int T, int H, int head_size, int dtype, int head_first, int algo,
+                       void* stream);
+
+size_t rwkvb200_rwkv7_bwd_workspace_bytes(int B, int T, int H, int head_size, int dtype, int algo);
+
+/* Backward.  Recomputes the forward from the inputs (the reference's autograd node also saves
+ * only the inputs, torch_op.py:298).  d_o is the gradient of o; d_ht (may be NULL) the gradient of
+ * the final state.  Writes dr,dw,dk,dv,da,db (token layout, dtype) and, when d_h0 is not NULL,
+ * the float32 gradient of the per-batch-row initial state [B,H,64,64] (a caller that broadcast one
+ * state sums it over the batch).  dw is the gradient of the w INPUT (chain rule through
+ * exp(-exp(w)) included; the reference leaves that step to autograd, torch_op.py:434). */
+int rwkvb200_rwkv7_bwd(const void* r, const void* w, const void* k, const void* v,
+                       const void* a, const void* b,
+                       const float* h0, int n_state,
+                       const void* d_o, const float* d_ht,
+                       void* dr, void* dw, void* dk, void* dv, void* da, void* db, float* d_h0,
+                       void* workspace, size_t workspace_bytes,
+                       int B, int T, int H, int head_size, int dtype, int head_first, int algo,
+                       void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * RWKV6 wkv.
+ * Replaces RWKVKernelOperator.__call__ of the reference
+ * (native: rwkv_ops/rwkv6_kernel/ops_rwkv_kernel.py:10-86; GPU: rwkv_ops/rwkv6_kernel/torch_rwkv_kernel.py:214-304
+ * with kernels rwkv_ops/rwkv6_kernel/torch_kernel/wkv6_cuda.cu:13-357).
+ *
+ * r,k,v,w,y are [B,T,C], C = H*64; u is float32 [H,64].  States are float32 [n,H,64,64] with the KEY
+ * index before the VALUE index (ops_rwkv_kernel.py:71-77).
+ *   s0 / n_state / state_map   initial-state table [n_state,H,64,64] (n_state = 0: zero state) and a
+ *                  DEVICE int32 array [B] choosing one table row per batch row; NULL means row b for
+ *                  batch row b (then n_state must be B) or row 0 when n_state == 1.  The range of
+ *                  state_map is the caller's to check on the host (the Python layer does, before the
+ *                  launch); out-of-range entries are clamped on the device instead of trapping.
+ *   sT             final state [B,H,64,64], may be NULL.
+ * ---------------------------------------------------------------------------------------- */
+int rwkvb200_wkv6_fwd(const void* r, const void* k, const void* v, const void* w, const float* u,
+                      const float* s0, int n_state, const int32_t* state_map,
+                      void* y, float* sT,
+                      int B, int T, int H, int head_size, int dtype, void* stream);
+
+size_t rwkvb200_wkv6_bwd_workspace_bytes(int B, int T, int H, int head_size, int dtype);
+
+/* Backward of wkv6, including the gradient paths the reference's GPU operator lacks (initial state,
+ * final-state gradient; wkv6_cuda.cu:291,316 hard-zero them).  d_y: gradient of y; d_sT (may be NULL):
+ * gradient of the final state.  Writes dr,dk,dv,dw [B,T,C] (dtype; dw is the gradient of the w input),
+ * du float32 [H,64] summed over batch and time, and, when d_s0 is not NULL, the float32 gradient of the
+ * per-batch-row initial state [B,H,64,64] (the caller scatters rows through state_map). */
+int rwkvb200_wkv6_bwd(const void* r, const void* k, const void* v, const void* w, const float* u,
+                      const float* s0, int n_state, const int32_t* state_map,
+                      const void* d_y, const float* d_sT,
+                      void* dr, void* dk, void* dv, void* dw, float* du, float* d_s0,
+                      void* workspace, size_t workspace_bytes,
+                      int B, int T, int H, int head_size, int dtype, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Per-kernel timing for benchmarks (no counterpart in the reference, which ships no timing code).
+ * When enabled, each kernel launch of the library is bracketed by CUDA events on its stream.
+ * rwkvb200_profile_get synchronises on the recorded events and returns, for kernel name index i in
+ * [0, rwkvb200_profile_count()), the name, the summed duration in milliseconds and the launch count.
+ * ---------------------------------------------------------------------------------------- */
+void rwkvb200_profile_enable(int on);
+void rwkvb200_profile_reset(void);
+int rwkvb200_profile_count(void);
+int rwkvb200_profile_get(int i, char* name, int name_len, float* total_ms, int* launches);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* RWKV_OPS_B200_H */

@@ -1,0 +1,131 @@
+"""ctypes binding of librwkv_ops_b200.so (the C ABI declared in include/rwkv_ops_b200.h).
+
+There is no fallback: if the shared library is missing or an entry point returns an
+error code, the caller gets an exception.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from ctypes import c_int, c_size_t, c_void_p, c_char_p
+
+import torch
+
+_PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG, "librwkv_ops_b200.so")
+
+F32, BF16, F16 = 0, 1, 2
+ALGO_AUTO, ALGO_RECURRENT, ALGO_CHUNKED = 0, 1, 2
+_DTYPE_CODE = {torch.float32: F32, torch.bfloat16: BF16, torch.float16: F16}
+
+# name -> (restype, argtypes); mirrors include/rwkv_ops_b200.h one to one
+_P, _I, _Z = c_void_p, c_int, c_size_t
+SIGNATURES = {
+    "rwkvb200_abi_version": (c_int, []),
+    "rwkvb200_strerror": (c_char_p, [_I]),
+    "rwkvb200_rwkv7_step": (c_int, [_P] * 6 + [_P, _I, _P, _P, _I, _I, _I, _I, _P]),
+    "rwkvb200_rwkv7_fwd_workspace_bytes": (c_size_t, [_I] * 6),
+    "rwkvb200_rwkv7_fwd": (c_int, [_P] * 6 + [_P, _I, _P, _P, _P, _Z] + [_I] * 7 + [_P]),
+    "rwkvb200_rwkv7_bwd_workspace_bytes": (c_size_t, [_I] * 6),
+    "rwkvb200_rwkv7_bwd": (c_int, [_P] * 6 + [_P, _I, _P, _P] + [_P] * 7 + [_P, _Z] + [_I] * 7 + [_P]),
+    "rwkvb200_wkv6_fwd": (c_int, [_P] * 5 + [_P, _I, _P, _P, _P] + [_I] * 5 + [_P]),
+    "rwkvb200_wkv6_bwd_workspace_bytes": (c_size_t, [_I] * 5),
+    "rwkvb200_wkv6_bwd": (c_int, [_P] * 5 + [_P, _I, _P, _P, _P] + [_P] * 6 + [_P, _Z] + [_I] * 5 + [_P]),
+    "rwkvb200_profile_enable": (None, [_I]),
+    "rwkvb200_profile_reset": (None, []),
+    "rwkvb200_profile_count": (c_int, []),
+    "rwkvb200_profile_get": (c_int, [_I, c_char_p, _I, ctypes.POINTER(ctypes.c_float), ctypes.POINTER(c_int)]),
+}
+
+_lib = None
+
+
+class RwkvB200Error(RuntimeError):
+    pass
+
+
+def load() -> ctypes.CDLL:
+    """Load the shared library once; raise if it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise RwkvB200Error(
+            f"{LIB_PATH} not found. Build it with `python -m rwkv_ops_b200.build` (needs nvcc); "
+            "rwkv_ops_b200 has no CPU or eager fallback."
+        )
+    lib = ctypes.CDLL(LIB_PATH)
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(lib, name)  # AttributeError if the library does not export a declared symbol
+        fn.restype = res
+        fn.argtypes = args
+    got = lib.rwkvb200_abi_version()
+    if got != 1:
+        raise RwkvB200Error(f"ABI version mismatch: library {got}, binding 1")
+    _lib = lib
+    return lib
+
+
+def strerror(code: int) -> str:
+    return load().rwkvb200_strerror(code).decode()
+
+
+def check(code: int, what: str) -> None:
+    if code == 0:
+        return
+    msg = f"{what}: {strerror(code)} (code {code})"
+    if code in (-1, -2, -3, -4, -6, -8, -9):
+        raise ValueError(msg)
+    raise RwkvB200Error(msg)
+
+
+def dtype_code(dt: torch.dtype) -> int:
+    try:
+        return _DTYPE_CODE[dt]
+    except KeyError:
+        raise ValueError(f"unsupported token dtype {dt}; use float32, bfloat16 or float16") from None
+
+
+def ptr(t):
+    return None if t is None else t.data_ptr()
+
+
+def stream_ptr(device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def require_cuda(*tensors) -> torch.device:
+    dev = None
+    for t in tensors:
+        if t is None:
+            continue
+        if not t.is_cuda:
+            raise RwkvB200Error(
+                "rwkv_ops_b200 operators run on CUDA tensors only (got a tensor on "
+                f"{t.device}); there is no CPU fallback."
+            )
+        if dev is None:
+            dev = t.device
+        elif t.device != dev:
+            raise ValueError("all tensors must be on the same device")
+    return dev
+
+
+def profile(on: bool) -> None:
+    """Switch per-kernel event timing on (after clearing old records) or off."""
+    lib = load()
+    if on:
+        lib.rwkvb200_profile_reset()
+    lib.rwkvb200_profile_enable(int(on))
+
+
+def profile_results() -> dict:
+    """{kernel name: (total_ms, launches)} of everything launched since ``profile(True)``."""
+    lib = load()
+    out = {}
+    for i in range(lib.rwkvb200_profile_count()):
+        name = ctypes.create_string_buffer(96)
+        ms, n = ctypes.c_float(), c_int()
+        check(lib.rwkvb200_profile_get(i, name, 96, ctypes.byref(ms), ctypes.byref(n)), "profile_get")
+        out[name.value.decode()] = (ms.value, n.value)
+    return out

@@ -1,0 +1,186 @@
+// extern "C" entry points of librwkv_ops_b200.so: argument checks and dispatch.
+// The contract of every function is in include/rwkv_ops_b200.h.
+#include "common.cuh"
+
+using namespace rwkvb200;
+
+namespace {
+
+inline size_t align256(size_t x) { return (x + 255) & ~size_t(255); }
+
+inline int check_common(int B, int T, int H, int head_size, int dtype) {
+  if (B <= 0 || T <= 0 || H <= 0) return RWKVB200_E_SHAPE;
+  if (head_size != HS) return RWKVB200_E_UNSUPPORTED;
+  if (dtype != RWKVB200_F32 && dtype != RWKVB200_BF16 && dtype != RWKVB200_F16) return RWKVB200_E_DTYPE;
+  return RWKVB200_OK;
+}
+
+inline int resolve_r7_algo(int algo, int dtype) {
+  (void)dtype;
+  if (algo == RWKVB200_ALGO_AUTO) return RWKVB200_ALGO_RECURRENT;
+  return algo;
+}
+
+inline size_t r7_ckpt_bytes(int B, int T, int H) {
+  const size_t nc = (size_t)(T + R7_CKPT - 1) / R7_CKPT;
+  return align256((size_t)B * H * nc * HS * HS * sizeof(float));
+}
+
+inline size_t w6_ckpt_bytes(int B, int T, int H) {
+  const size_t nc = (size_t)(T + W6_CKPT - 1) / W6_CKPT;
+  return align256((size_t)B * H * nc * HS * HS * sizeof(float));
+}
+
+}  // namespace
+
+extern "C" {
+
+int rwkvb200_abi_version(void) { return RWKVB200_ABI_VERSION; }
+
+const char* rwkvb200_strerror(int code) {
+  switch (code) {
+    case RWKVB200_OK: return "ok";
+    case RWKVB200_E_SHAPE: return "bad shape: a size is <= 0 or inconsistent";
+    case RWKVB200_E_DTYPE: return "bad dtype code";
+    case RWKVB200_E_ALIGN: return "pointer not 16-byte aligned";
+    case RWKVB200_E_NULL: return "required pointer is NULL";
+    case RWKVB200_E_WORKSPACE: return "workspace too small";
+    case RWKVB200_E_UNSUPPORTED: return "unsupported head size or mode";
+    case RWKVB200_E_CUDA: return "CUDA runtime error at launch";
+    case RWKVB200_E_STATE_MAP: return "state_map entry out of range";
+    case RWKVB200_E_TOO_LARGE: return "size beyond this entry point's fixed capacity";
+    default: return "unknown error code";
+  }
+}
+
+int rwkvb200_rwkv7_step(const void* r, const void* w, const void* k, const void* v,
+                        const void* a, const void* b,
+                        const float* state_in, int n_state, float* state_out, void* o,
+                        int B, int H, int head_size, int dtype, void* stream) {
+  int e = check_common(B, 1, H, head_size, dtype);
+  if (e) return e;
+  if (!r || !w || !k || !v || !a || !b || !state_out || !o) return RWKVB200_E_NULL;
+  if (n_state != 0 && n_state != 1 && n_state != B) return RWKVB200_E_SHAPE;
+  if (n_state != 0 && !state_in) return RWKVB200_E_NULL;
+  const void* ps[] = {r, w, k, v, a, b, state_in, state_out, o};
+  for (const void* p : ps) if (p && !aligned16(p)) return RWKVB200_E_ALIGN;
+  return launch_rwkv7_step(r, w, k, v, a, b, n_state ? state_in : nullptr, n_state, state_out, o, B, H, dtype,
+                           (cudaStream_t)stream);
+}
+
+size_t rwkvb200_rwkv7_fwd_workspace_bytes(int B, int T, int H, int head_size, int dtype, int algo) {
+  if (check_common(B, T, H, head_size, dtype)) return 0;
+  (void)algo;
+  return 0;
+}
+
+int rwkvb200_rwkv7_fwd(const void* r, const void* w, const void* k, const void* v,
+                       const void* a, const void* b,
+                       const float* h0, int n_state, void* o, float* ht,
+                       void* workspace, size_t workspace_bytes,
+                       int B, int T, int H, int head_size, int dtype, int head_first, int algo,
+                       void* stream) {
+  int e = check_common(B, T, H, head_size, dtype);
+  if (e) return e;
+  if (!r || !w || !k || !v || !a || !b || !o) return RWKVB200_E_NULL;
+  if (n_state != 0 && n_state != 1 && n_state != B) return RWKVB200_E_SHAPE;
+  if (n_state != 0 && !h0) return RWKVB200_E_NULL;
+  const void* ps[] = {r, w, k, v, a, b, h0, o, ht, workspace};
+  for (const void* p : ps) if (p && !aligned16(p)) return RWKVB200_E_ALIGN;
+  if (workspace_bytes < rwkvb200_rwkv7_fwd_workspace_bytes(B, T, H, head_size, dtype, algo)) return RWKVB200_E_WORKSPACE;
+  switch (resolve_r7_algo(algo, dtype)) {
+    case RWKVB200_ALGO_RECURRENT:
+      return launch_rwkv7_rec_fwd(r, w, k, v, a, b, n_state ? h0 : nullptr, n_state, o, ht, nullptr, R7_CKPT,
+                                  B, T, H, dtype, head_first, (cudaStream_t)stream);
+    default:
+      return RWKVB200_E_UNSUPPORTED;
+  }
+}
+
+size_t rwkvb200_rwkv7_bwd_workspace_bytes(int B, int T, int H, int head_size, int dtype, int algo) {
+  if (check_common(B, T, H, head_size, dtype)) return 0;
+  switch (resolve_r7_algo(algo, dtype)) {
+    case RWKVB200_ALGO_RECURRENT: return r7_ckpt_bytes(B, T, H);
+    default: return 0;
+  }
+}
+
+int rwkvb200_rwkv7_bwd(const void* r, const void* w, const void* k, const void* v,
+                       const void* a, const void* b,
+                       const float* h0, int n_state,
+                       const void* d_o, const float* d_ht,
+                       void* dr, void* dw, void* dk, void* dv, void* da, void* db, float* d_h0,
+                       void* workspace, size_t workspace_bytes,
+                       int B, int T, int H, int head_size, int dtype, int head_first, int algo,
+                       void* stream) {
+  int e = check_common(B, T, H, head_size, dtype);
+  if (e) return e;
+  if (!r || !w || !k || !v || !a || !b || !d_o || !dr || !dw || !dk || !dv || !da || !db) return RWKVB200_E_NULL;
+  if (n_state != 0 && n_state != 1 && n_state != B) return RWKVB200_E_SHAPE;
+  if (n_state != 0 && !h0) return RWKVB200_E_NULL;
+  const void* ps[] = {r, w, k, v, a, b, h0, d_o, d_ht, dr, dw, dk, dv, da, db, d_h0, workspace};
+  for (const void* p : ps) if (p && !aligned16(p)) return RWKVB200_E_ALIGN;
+  const size_t need = rwkvb200_rwkv7_bwd_workspace_bytes(B, T, H, head_size, dtype, algo);
+  if (workspace_bytes < need || (need && !workspace)) return RWKVB200_E_WORKSPACE;
+  cudaStream_t st = (cudaStream_t)stream;
+  switch (resolve_r7_algo(algo, dtype)) {
+    case RWKVB200_ALGO_RECURRENT: {
+      float* ckpt = reinterpret_cast<float*>(workspace);
+      e = launch_rwkv7_rec_fwd(r, w, k, v, a, b, n_state ? h0 : nullptr, n_state, nullptr, nullptr, ckpt, R7_CKPT,
+                               B, T, H, dtype, head_first, st);
+      if (e) return e;
+      return launch_rwkv7_rec_bwd(r, w, k, v, a, b, d_o, d_ht, ckpt, dr, dw, dk, dv, da, db, d_h0,
+                                  B, T, H, dtype, head_first, st);
+    }
+    default:
+      return RWKVB200_E_UNSUPPORTED;
+  }
+}
+
+int rwkvb200_wkv6_fwd(const void* r, const void* k, const void* v, const void* w, const float* u,
+                      const float* s0, int n_state, const int32_t* state_map,
+                      void* y, float* sT,
+                      int B, int T, int H, int head_size, int dtype, void* stream) {
+  int e = check_common(B, T, H, head_size, dtype);
+  if (e) return e;
+  if (!r || !k || !v || !w || !u || !y) return RWKVB200_E_NULL;
+  if (n_state < 0) return RWKVB200_E_SHAPE;
+  if (n_state > 0 && !s0) return RWKVB200_E_NULL;
+  if (n_state > 1 && !state_map && n_state != B) return RWKVB200_E_STATE_MAP;
+  const void* ps[] = {r, k, v, w, u, s0, y, sT};
+  for (const void* p : ps) if (p && !aligned16(p)) return RWKVB200_E_ALIGN;
+  return launch_wkv6_fwd(r, k, v, w, u, n_state ? s0 : nullptr, n_state, state_map, y, sT, nullptr,
+                         B, T, H, dtype, (cudaStream_t)stream);
+}
+
+size_t rwkvb200_wkv6_bwd_workspace_bytes(int B, int T, int H, int head_size, int dtype) {
+  if (check_common(B, T, H, head_size, dtype)) return 0;
+  return w6_ckpt_bytes(B, T, H) + align256((size_t)B * H * 4 * HS * sizeof(float));
+}
+
+int rwkvb200_wkv6_bwd(const void* r, const void* k, const void* v, const void* w, const float* u,
+                      const float* s0, int n_state, const int32_t* state_map,
+                      const void* d_y, const float* d_sT,
+                      void* dr, void* dk, void* dv, void* dw, float* du, float* d_s0,
+                      void* workspace, size_t workspace_bytes,
+                      int B, int T, int H, int head_size, int dtype, void* stream) {
+  int e = check_common(B, T, H, head_size, dtype);
+  if (e) return e;
+  if (!r || !k || !v || !w || !u || !d_y || !dr || !dk || !dv || !dw || !du) return RWKVB200_E_NULL;
+  if (n_state < 0) return RWKVB200_E_SHAPE;
+  if (n_state > 0 && !s0) return RWKVB200_E_NULL;
+  if (n_state > 1 && !state_map && n_state != B) return RWKVB200_E_STATE_MAP;
+  const void* ps[] = {r, k, v, w, u, s0, d_y, d_sT, dr, dk, dv, dw, du, d_s0, workspace};
+  for (const void* p : ps) if (p && !aligned16(p)) return RWKVB200_E_ALIGN;
+  if (!workspace || workspace_bytes < rwkvb200_wkv6_bwd_workspace_bytes(B, T, H, head_size, dtype))
+    return RWKVB200_E_WORKSPACE;
+  cudaStream_t st = (cudaStream_t)stream;
+  float* ckpt = reinterpret_cast<float*>(workspace);
+  float* du_partial = reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + w6_ckpt_bytes(B, T, H));
+  e = launch_wkv6_fwd(r, k, v, w, u, n_state ? s0 : nullptr, n_state, state_map, nullptr, nullptr, ckpt,
+                      B, T, H, dtype, st);
+  if (e) return e;
+  return launch_wkv6_bwd(r, k, v, w, u, d_y, d_sT, ckpt, dr, dk, dv, dw, du_partial, du, d_s0, B, T, H, dtype, st);
+}
+
+}  // extern "C"

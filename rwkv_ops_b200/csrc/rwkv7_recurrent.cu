@@ -1,0 +1,364 @@
+// RWKV7 generalized delta rule, token-by-token in float32 (forward and backward).
+//
+// This is the float32-exact path: the same arithmetic as the reference's native operator
+// (rwkv_ops/rwkv7_kernel/native_keras_op.py:80-91), used for float32 token tensors and as the
+// on-device cross-check of the chunked tensor-core path.
+//
+//   d_t = exp(-exp(w_t));  sa_t = S_{t-1} a_t;  S_t = S_{t-1} diag(d_t) + sa_t b_t^T + v_t k_t^T;  o_t = S_t r_t
+//
+// with S[v][k].  Row v of S never mixes with another row, so the 64 value rows are split over
+// four CTAs (16 rows each): grid (B*H, 4), 64 threads.  In the "row role" thread (vl = tid>>2,
+// kq = tid&3) holds S[vl][16*kq .. 16*kq+15] in registers and reductions over k take two shuffles.
+//
+// Backward.  With dS the gradient of the state flowing from the future,
+//   dS += do_t r_t^T;  dr_t = S_t^T do_t;  dv_t = dS k_t;  dk_t = dS^T v_t;  dsa = dS b_t;  db_t = dS^T sa_t;
+//   dd_t[k] = sum_v dS[v,k] S_{t-1}[v,k];  da_t = S_{t-1}^T dsa;  dS <- dS diag(d_t) + dsa a_t^T;
+//   dw_t = dd_t * d_t * (-exp(w_t)).
+// It needs S_{t-1} and S_t for every token: a first forward sweep stores the state every R7_CKPT
+// tokens (the workspace), and the backward kernel walks the chunks in reverse, re-running each chunk
+// forward into shared memory before sweeping it backward.  Reductions over v (dr, dk, db, da, dd) need
+// all 64 rows: each thread also keeps a "column role" copy dS[0..15][k = tid] of the CTA's slab, the
+// four CTAs of a (batch, head) form a thread-block cluster, and after each chunk every CTA sums the
+// four partial results of a quarter of the chunk's tokens through distributed shared memory, in a
+// fixed order (deterministic, no atomics, no scratch beyond the checkpoints).
+#include <cooperative_groups.h>
+
+#include "common.cuh"
+
+namespace cg = cooperative_groups;
+
+namespace rwkvb200 {
+
+namespace {
+
+constexpr int VS = 16;        // value rows per CTA
+constexpr int NQ = HS / VS;   // CTAs per (batch, head)
+constexpr int TL = 16;        // tokens staged per tile in the forward kernel
+constexpr int CK = R7_CKPT;   // chunk of the backward = checkpoint interval
+constexpr int SROW = HS + 1;  // padded row of a state slab in shared memory
+
+// ---------------------------------------------------------------------------------------------
+// forward
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(64)
+rwkv7_rec_fwd_kernel(const T* __restrict__ r, const T* __restrict__ w, const T* __restrict__ k,
+                     const T* __restrict__ v, const T* __restrict__ a, const T* __restrict__ b,
+                     const float* __restrict__ h0, int n_state, T* __restrict__ o, float* __restrict__ ht,
+                     float* __restrict__ ckpt, int ckpt_every, int Tn, int H, TokLayout lay) {
+  __shared__ __align__(16) float tile[TL][5][HS];   // r, d, k, a, b
+  __shared__ __align__(16) float vt[TL][VS];
+  __shared__ __align__(16) float ot[TL][VS];
+
+  const int unit = blockIdx.x, y = blockIdx.y, tid = threadIdx.x;
+  const int bi = unit / H, hi = unit % H;
+  const int vl = tid >> 2, kq = tid & 3;
+  const long long base = bi * lay.sb + hi * lay.sh;
+  const int NC = ckpt ? (Tn + ckpt_every - 1) / ckpt_every : 0;
+
+  float S[16];
+  if (h0 && n_state > 0) {
+    const float* p = h0 + ((long long)(n_state == 1 ? hi : unit) * HS + (y * VS + vl)) * HS + 16 * kq;
+#pragma unroll
+    for (int j = 0; j < 16; j += 4) {
+      float4 f = *reinterpret_cast<const float4*>(p + j);
+      S[j] = f.x; S[j + 1] = f.y; S[j + 2] = f.z; S[j + 3] = f.w;
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 16; ++j) S[j] = 0.f;
+  }
+
+  for (int t0 = 0; t0 < Tn; t0 += TL) {
+    const int nt = min(TL, Tn - t0);
+    // stage the tile: 5 vectors x nt tokens, one float4 per thread per pass
+    for (int i = tid; i < nt * 5 * 16; i += 64) {
+      const int quad = i & 15, row = i >> 4, tl = row / 5, which = row % 5;
+      const T* src = which == 0 ? r : which == 1 ? w : which == 2 ? k : which == 3 ? a : b;
+      float4 f = load4(src + base + (long long)(t0 + tl) * lay.st + 4 * quad);
+      if (which == 1) f = make_float4(decay_of(f.x), decay_of(f.y), decay_of(f.z), decay_of(f.w));
+      *reinterpret_cast<float4*>(&tile[tl][which][4 * quad]) = f;
+    }
+    if (tid < nt * 4) {
+      const int tl = tid >> 2, quad = tid & 3;
+      *reinterpret_cast<float4*>(&vt[tl][4 * quad]) =
+          load4(v + base + (long long)(t0 + tl) * lay.st + y * VS + 4 * quad);
+    }
+    __syncthreads();
+
+    for (int tl = 0; tl < nt; ++tl) {
+      const int t = t0 + tl;
+      if (ckpt && (t % ckpt_every) == 0) {
+        float* p = ckpt + ((((long long)unit * NC + t / ckpt_every) * HS) + (y * VS + vl)) * HS + 16 * kq;
+#pragma unroll
+        for (int j = 0; j < 16; j += 4)
+          *reinterpret_cast<float4*>(p + j) = make_float4(S[j], S[j + 1], S[j + 2], S[j + 3]);
+      }
+      const float* tr = &tile[tl][0][16 * kq];
+      const float* td = &tile[tl][1][16 * kq];
+      const float* tk = &tile[tl][2][16 * kq];
+      const float* ta = &tile[tl][3][16 * kq];
+      const float* tb = &tile[tl][4][16 * kq];
+      float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+#pragma unroll
+      for (int j = 0; j < 16; j += 4) {
+        s0 += S[j] * ta[j]; s1 += S[j + 1] * ta[j + 1]; s2 += S[j + 2] * ta[j + 2]; s3 += S[j + 3] * ta[j + 3];
+      }
+      float sa = (s0 + s1) + (s2 + s3);
+      sa += __shfl_xor_sync(0xffffffffu, sa, 1);
+      sa += __shfl_xor_sync(0xffffffffu, sa, 2);
+      const float vv = vt[tl][vl];
+      float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
+#pragma unroll
+      for (int j = 0; j < 16; j += 4) {
+        S[j]     = S[j]     * td[j]     + sa * tb[j]     + vv * tk[j];
+        S[j + 1] = S[j + 1] * td[j + 1] + sa * tb[j + 1] + vv * tk[j + 1];
+        S[j + 2] = S[j + 2] * td[j + 2] + sa * tb[j + 2] + vv * tk[j + 2];
+        S[j + 3] = S[j + 3] * td[j + 3] + sa * tb[j + 3] + vv * tk[j + 3];
+        o0 += S[j] * tr[j]; o1 += S[j + 1] * tr[j + 1]; o2 += S[j + 2] * tr[j + 2]; o3 += S[j + 3] * tr[j + 3];
+      }
+      float oo = (o0 + o1) + (o2 + o3);
+      oo += __shfl_xor_sync(0xffffffffu, oo, 1);
+      oo += __shfl_xor_sync(0xffffffffu, oo, 2);
+      if (kq == 0) ot[tl][vl] = oo;
+    }
+    __syncthreads();
+    if (o && tid < nt * 4) {
+      const int tl = tid >> 2, quad = tid & 3;
+      store4(o + base + (long long)(t0 + tl) * lay.st + y * VS + 4 * quad,
+             *reinterpret_cast<const float4*>(&ot[tl][4 * quad]));
+    }
+    // the next tile's staging writes tile/vt only after every thread has passed the barrier
+    // above; ot is rewritten only after the next barrier pair
+  }
+  if (ht) {
+    float* p = ht + ((long long)unit * HS + (y * VS + vl)) * HS + 16 * kq;
+#pragma unroll
+    for (int j = 0; j < 16; j += 4)
+      *reinterpret_cast<float4*>(p + j) = make_float4(S[j], S[j + 1], S[j + 2], S[j + 3]);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// backward
+// ---------------------------------------------------------------------------------------------
+struct BwdSmem {
+  float tile[CK][6][HS];        // r, d, exp(w), k, a, b
+  float vt[CK][VS];
+  float dot[CK][VS];
+  float sa[CK][VS];
+  float dvt[CK][VS];
+  float dsa[2][VS];
+  float Sbuf[CK + 1][VS][SROW]; // state before token i of the chunk (i = nt: after the last)
+  float part[2][CK][5][HS];     // per-chunk partial dr, dk, db, da, dd of this CTA's 16 rows
+};
+
+template <typename T>
+__global__ void __cluster_dims__(1, NQ, 1) __launch_bounds__(64)
+rwkv7_rec_bwd_kernel(const T* __restrict__ r, const T* __restrict__ w, const T* __restrict__ k,
+                     const T* __restrict__ v, const T* __restrict__ a, const T* __restrict__ b,
+                     const T* __restrict__ d_o, const float* __restrict__ d_ht, const float* __restrict__ ckpt,
+                     T* __restrict__ dr, T* __restrict__ dw, T* __restrict__ dk, T* __restrict__ dv,
+                     T* __restrict__ da, T* __restrict__ db, float* __restrict__ d_h0,
+                     int Tn, int H, TokLayout lay) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  BwdSmem& sm = *reinterpret_cast<BwdSmem*>(smem_raw);
+  cg::cluster_group cluster = cg::this_cluster();
+
+  const int unit = blockIdx.x, y = blockIdx.y, tid = threadIdx.x;
+  const int bi = unit / H, hi = unit % H;
+  const int vl = tid >> 2, kq = tid & 3;   // row role
+  const int kc = tid;                      // column role
+  const long long base = bi * lay.sb + hi * lay.sh;
+  const int NC = (Tn + CK - 1) / CK;
+
+  float dSr[16], dSc[VS];
+  if (d_ht) {
+    const float* p = d_ht + ((long long)unit * HS + (y * VS + vl)) * HS + 16 * kq;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) dSr[j] = p[j];
+#pragma unroll
+    for (int i = 0; i < VS; ++i) dSc[i] = d_ht[((long long)unit * HS + (y * VS + i)) * HS + kc];
+  } else {
+#pragma unroll
+    for (int j = 0; j < 16; ++j) dSr[j] = 0.f;
+#pragma unroll
+    for (int i = 0; i < VS; ++i) dSc[i] = 0.f;
+  }
+
+  for (int c = NC - 1; c >= 0; --c) {
+    const int t0 = c * CK, nt = min(CK, Tn - t0), pb = c & 1;
+    // ---- stage the chunk's inputs
+    for (int i = tid; i < nt * 6 * 16; i += 64) {
+      const int quad = i & 15, row = i >> 4, tl = row / 6, which = row % 6;
+      const T* src = which == 0 ? r : (which == 1 || which == 2) ? w : which == 3 ? k : which == 4 ? a : b;
+      float4 f = load4(src + base + (long long)(t0 + tl) * lay.st + 4 * quad);
+      if (which == 1) f = make_float4(decay_of(f.x), decay_of(f.y), decay_of(f.z), decay_of(f.w));
+      if (which == 2) f = make_float4(expf(f.x), expf(f.y), expf(f.z), expf(f.w));
+      *reinterpret_cast<float4*>(&sm.tile[tl][which][4 * quad]) = f;
+    }
+    if (tid < nt * 4) {
+      const int tl = tid >> 2, quad = tid & 3;
+      const long long off = base + (long long)(t0 + tl) * lay.st + y * VS + 4 * quad;
+      *reinterpret_cast<float4*>(&sm.vt[tl][4 * quad]) = load4(v + off);
+      *reinterpret_cast<float4*>(&sm.dot[tl][4 * quad]) = load4(d_o + off);
+    }
+    // ---- re-run the chunk forward from its checkpoint (row role)
+    float S[16];
+    {
+      const float* p = ckpt + ((((long long)unit * NC + c) * HS) + (y * VS + vl)) * HS + 16 * kq;
+#pragma unroll
+      for (int j = 0; j < 16; j += 4) {
+        float4 f = *reinterpret_cast<const float4*>(p + j);
+        S[j] = f.x; S[j + 1] = f.y; S[j + 2] = f.z; S[j + 3] = f.w;
+      }
+    }
+    __syncthreads();
+    for (int tl = 0; tl < nt; ++tl) {
+      const float* td = &sm.tile[tl][1][16 * kq];
+      const float* tk = &sm.tile[tl][3][16 * kq];
+      const float* ta = &sm.tile[tl][4][16 * kq];
+      const float* tb = &sm.tile[tl][5][16 * kq];
+      float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+      for (int j = 0; j < 16; j += 2) {
+        sm.Sbuf[tl][vl][16 * kq + j] = S[j];
+        sm.Sbuf[tl][vl][16 * kq + j + 1] = S[j + 1];
+        s0 += S[j] * ta[j]; s1 += S[j + 1] * ta[j + 1];
+      }
+      float sa = s0 + s1;
+      sa += __shfl_xor_sync(0xffffffffu, sa, 1);
+      sa += __shfl_xor_sync(0xffffffffu, sa, 2);
+      if (kq == 0) sm.sa[tl][vl] = sa;
+      const float vv = sm.vt[tl][vl];
+#pragma unroll
+      for (int j = 0; j < 16; ++j) S[j] = S[j] * td[j] + sa * tb[j] + vv * tk[j];
+    }
+#pragma unroll
+    for (int j = 0; j < 16; ++j) sm.Sbuf[nt][vl][16 * kq + j] = S[j];
+    __syncthreads();
+
+    // ---- sweep the chunk backward
+    float St[VS], Sp[VS];
+#pragma unroll
+    for (int i = 0; i < VS; ++i) St[i] = sm.Sbuf[nt][i][kc];
+    for (int tl = nt - 1; tl >= 0; --tl) {
+      const int buf = tl & 1;
+      const float rk = sm.tile[tl][0][kc], dk_ = sm.tile[tl][1][kc], ak = sm.tile[tl][4][kc];
+      const float* tr = &sm.tile[tl][0][16 * kq];
+      const float* td = &sm.tile[tl][1][16 * kq];
+      const float* tk = &sm.tile[tl][3][16 * kq];
+      const float* ta = &sm.tile[tl][4][16 * kq];
+      const float* tb = &sm.tile[tl][5][16 * kq];
+      // row role: dS += do r^T ; dv = dS k ; dsa = dS b
+      const float dor = sm.dot[tl][vl];
+      float a0 = 0.f, a1 = 0.f, b0 = 0.f, b1 = 0.f;
+#pragma unroll
+      for (int j = 0; j < 16; j += 2) {
+        dSr[j] += dor * tr[j]; dSr[j + 1] += dor * tr[j + 1];
+        a0 += dSr[j] * tk[j]; a1 += dSr[j + 1] * tk[j + 1];
+        b0 += dSr[j] * tb[j]; b1 += dSr[j + 1] * tb[j + 1];
+      }
+      float dvv = a0 + a1, dsa = b0 + b1;
+      dvv += __shfl_xor_sync(0xffffffffu, dvv, 1);
+      dsa += __shfl_xor_sync(0xffffffffu, dsa, 1);
+      dvv += __shfl_xor_sync(0xffffffffu, dvv, 2);
+      dsa += __shfl_xor_sync(0xffffffffu, dsa, 2);
+      if (kq == 0) { sm.dvt[tl][vl] = dvv; sm.dsa[buf][vl] = dsa; }
+      // column role, part 1 (does not need dsa)
+      float p_dr = 0.f, p_dk = 0.f, p_db = 0.f, p_dd = 0.f;
+#pragma unroll
+      for (int i = 0; i < VS; ++i) {
+        Sp[i] = sm.Sbuf[tl][i][kc];
+        const float doi = sm.dot[tl][i];
+        dSc[i] += doi * rk;
+        p_dr += St[i] * doi;
+        p_dk += dSc[i] * sm.vt[tl][i];
+        p_db += dSc[i] * sm.sa[tl][i];
+        p_dd += dSc[i] * Sp[i];
+      }
+      __syncthreads();   // dsa of this token visible to every thread
+      float p_da = 0.f;
+#pragma unroll
+      for (int i = 0; i < VS; ++i) {
+        const float ds = sm.dsa[buf][i];
+        p_da += Sp[i] * ds;
+        dSc[i] = dSc[i] * dk_ + ds * ak;
+        St[i] = Sp[i];
+      }
+      const float dsr = sm.dsa[buf][vl];
+#pragma unroll
+      for (int j = 0; j < 16; ++j) dSr[j] = dSr[j] * td[j] + dsr * ta[j];
+      sm.part[pb][tl][0][kc] = p_dr;
+      sm.part[pb][tl][1][kc] = p_dk;
+      sm.part[pb][tl][2][kc] = p_db;
+      sm.part[pb][tl][3][kc] = p_da;
+      sm.part[pb][tl][4][kc] = p_dd;
+    }
+    // ---- dv rows of this CTA
+    __syncthreads();
+    for (int i = tid; i < nt * VS; i += 64) {
+      const int tl = i >> 4, vi = i & 15;
+      dv[base + (long long)(t0 + tl) * lay.st + y * VS + vi] = from_f32<T>(sm.dvt[tl][vi]);
+    }
+    // ---- sum the four CTAs' partial column results; this CTA finishes tokens tl = y, y+NQ, ...
+    cluster.sync();
+    for (int tl = y; tl < nt; tl += NQ) {
+      float acc[5] = {0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int rk_ = 0; rk_ < NQ; ++rk_) {
+        const float* rp = cluster.map_shared_rank(&sm.part[pb][tl][0][0], rk_);
+#pragma unroll
+        for (int qn = 0; qn < 5; ++qn) acc[qn] += rp[qn * HS + kc];
+      }
+      const long long off = base + (long long)(t0 + tl) * lay.st + kc;
+      dr[off] = from_f32<T>(acc[0]);
+      dk[off] = from_f32<T>(acc[1]);
+      db[off] = from_f32<T>(acc[2]);
+      da[off] = from_f32<T>(acc[3]);
+      dw[off] = from_f32<T>(acc[4] * sm.tile[tl][1][kc] * (-sm.tile[tl][2][kc]));
+    }
+    // part[pb] is rewritten two chunks later, after the next chunk's cluster.sync(); the tile is
+    // rewritten by the next chunk's staging, which only this CTA reads
+    __syncthreads();
+  }
+  if (d_h0) {
+    float* p = d_h0 + ((long long)unit * HS + (y * VS + vl)) * HS + 16 * kq;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) p[j] = dSr[j];
+  }
+  cluster.sync();   // no CTA leaves while a peer may still read its shared memory
+}
+
+}  // namespace
+
+int launch_rwkv7_rec_fwd(const void* r, const void* w, const void* k, const void* v, const void* a, const void* b,
+                         const float* h0, int n_state, void* o, float* ht, float* ckpt, int ckpt_every,
+                         int B, int Tn, int H, int dtype, int head_first, cudaStream_t st) {
+  TokLayout lay(Tn, H, head_first);
+  dim3 grid(B * H, NQ);
+  ProfScope prof("rwkv7_rec_fwd_kernel", st);
+  RWKVB200_DISPATCH_DTYPE(dtype,
+    rwkv7_rec_fwd_kernel<T><<<grid, 64, 0, st>>>((const T*)r, (const T*)w, (const T*)k, (const T*)v, (const T*)a,
+                                                 (const T*)b, h0, n_state, (T*)o, ht, ckpt, ckpt_every, Tn, H, lay));
+  return check_launch();
+}
+
+int launch_rwkv7_rec_bwd(const void* r, const void* w, const void* k, const void* v, const void* a, const void* b,
+                         const void* d_o, const float* d_ht, const float* ckpt,
+                         void* dr, void* dw, void* dk, void* dv, void* da, void* db, float* d_h0,
+                         int B, int Tn, int H, int dtype, int head_first, cudaStream_t st) {
+  TokLayout lay(Tn, H, head_first);
+  dim3 grid(B * H, NQ);
+  const int smem = (int)sizeof(BwdSmem);
+  ProfScope prof("rwkv7_rec_bwd_kernel", st);
+  RWKVB200_DISPATCH_DTYPE(dtype,
+    if (cudaFuncSetAttribute(rwkv7_rec_bwd_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+      return RWKVB200_E_CUDA;
+    rwkv7_rec_bwd_kernel<T><<<grid, 64, smem, st>>>((const T*)r, (const T*)w, (const T*)k, (const T*)v, (const T*)a,
+                                                    (const T*)b, (const T*)d_o, d_ht, ckpt, (T*)dr, (T*)dw, (T*)dk,
+                                                    (T*)dv, (T*)da, (T*)db, d_h0, Tn, H, lay));
+  return check_launch();
+}
+
+}  // namespace rwkvb200

@@ -1,0 +1,331 @@
+// RWKV6 wkv operator, float32 arithmetic, forward and backward.
+//
+// Maths of the reference's native operator (rwkv_ops/rwkv6_kernel/ops_rwkv_kernel.py:63-80):
+//   d_t = exp(-exp(w_t));  y_t[v] = sum_k r_t[k] (u[k] k_t[k] v_t[v] + S_{t-1}[k][v]);  S_t = diag(d_t) S_{t-1} + k_t v_t^T
+// with S[k][v] and S_0 = s0[state_map[b]] or zero.
+//
+// Column v of S never mixes with another column, so the 64 value columns are split over four CTAs
+// (16 columns each): grid (B*H, 4), 64 threads.  In the "value role" thread (vl = tid>>2, kq = tid&3)
+// holds S[16*kq .. 16*kq+15][vl] in registers; the reduction over k takes two shuffles.
+//
+// Backward, with G the gradient of the state flowing from the future and dyv = sum_v dy_t[v] v_t[v]:
+//   dr_t[k] = u[k] k_t[k] dyv + sum_v S_{t-1}[k][v] dy_t[v]      dk_t[k] = r_t[k] u[k] dyv + sum_v G[k][v] v_t[v]
+//   dv_t[v] = dy_t[v] sum_k r u k + sum_k G[k][v] k_t[k]         dd_t[k] = sum_v G[k][v] S_{t-1}[k][v]
+//   du[k]  += r_t[k] k_t[k] dyv                                  G <- diag(d_t) G + r_t dy_t^T
+//   dw_t = dd_t * d_t * (-exp(w_t))
+// S_{t-1} is needed per token: the forward sweep stores the state every W6_CKPT tokens (the workspace)
+// and the backward kernel re-runs each chunk forward into shared memory before sweeping it backward.
+// Sums over v need all four CTAs of a (batch, head): they form a thread-block cluster and exchange
+// per-chunk partial sums through distributed shared memory in a fixed order (deterministic).
+#include <cooperative_groups.h>
+
+#include "common.cuh"
+
+namespace cg = cooperative_groups;
+
+namespace rwkvb200 {
+
+namespace {
+
+constexpr int VS = 16;
+constexpr int NQ = HS / VS;
+constexpr int TL = 16;
+constexpr int CK = W6_CKPT;
+constexpr int SCOL = VS + 1;   // padded row (one key, 16 values) of a state slab in shared memory
+
+__device__ __forceinline__ long long state_row(const int32_t* smap, int n_state, int bi) {
+  if (n_state == 1) return 0;
+  if (!smap) return bi;
+  int m = smap[bi];
+  return m < 0 ? 0 : (m >= n_state ? n_state - 1 : m);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(64)
+wkv6_fwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __restrict__ v,
+                const T* __restrict__ w, const float* __restrict__ u,
+                const float* __restrict__ s0, int n_state, const int32_t* __restrict__ smap,
+                T* __restrict__ yout, float* __restrict__ sT, float* __restrict__ ckpt, int Tn, int H) {
+  __shared__ __align__(16) float tile[TL][4][HS];   // r, d, k, r*u*k
+  __shared__ __align__(16) float vt[TL][VS];
+  __shared__ __align__(16) float yt[TL][VS];
+
+  const int unit = blockIdx.x, y = blockIdx.y, tid = threadIdx.x;
+  const int bi = unit / H, hi = unit % H;
+  const int vl = tid >> 2, kq = tid & 3;
+  const long long base = ((long long)bi * Tn * H + hi) * HS;   // + t*H*HS
+  const long long tstride = (long long)H * HS;
+  const int NC = ckpt ? (Tn + CK - 1) / CK : 0;
+  const float4 u4 = *reinterpret_cast<const float4*>(u + hi * HS + 4 * (tid & 15));
+
+  float S[16];
+  if (s0 && n_state > 0) {
+    const float* p = s0 + ((state_row(smap, n_state, bi) * H + hi) * HS + 16 * kq) * HS + y * VS + vl;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) S[j] = p[j * HS];
+  } else {
+#pragma unroll
+    for (int j = 0; j < 16; ++j) S[j] = 0.f;
+  }
+
+  for (int t0 = 0; t0 < Tn; t0 += TL) {
+    const int nt = min(TL, Tn - t0);
+    for (int i = tid; i < nt * 16; i += 64) {
+      const int quad = i & 15, tl = i >> 4;   // quad == tid & 15
+      const long long off = base + (long long)(t0 + tl) * tstride + 4 * quad;
+      const float4 r4 = load4(r + off), k4 = load4(k + off), w4 = load4(w + off);
+      *reinterpret_cast<float4*>(&tile[tl][0][4 * quad]) = r4;
+      *reinterpret_cast<float4*>(&tile[tl][1][4 * quad]) =
+          make_float4(decay_of(w4.x), decay_of(w4.y), decay_of(w4.z), decay_of(w4.w));
+      *reinterpret_cast<float4*>(&tile[tl][2][4 * quad]) = k4;
+      *reinterpret_cast<float4*>(&tile[tl][3][4 * quad]) =
+          make_float4(r4.x * u4.x * k4.x, r4.y * u4.y * k4.y, r4.z * u4.z * k4.z, r4.w * u4.w * k4.w);
+    }
+    if (tid < nt * 4) {
+      const int tl = tid >> 2, quad = tid & 3;
+      *reinterpret_cast<float4*>(&vt[tl][4 * quad]) =
+          load4(v + base + (long long)(t0 + tl) * tstride + y * VS + 4 * quad);
+    }
+    __syncthreads();
+    for (int tl = 0; tl < nt; ++tl) {
+      const int t = t0 + tl;
+      if (ckpt && (t % CK) == 0) {
+        float* p = ckpt + ((((long long)unit * NC + t / CK) * HS) + 16 * kq) * HS + y * VS + vl;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) p[j * HS] = S[j];
+      }
+      const float* tr = &tile[tl][0][16 * kq];
+      const float* td = &tile[tl][1][16 * kq];
+      const float* tk = &tile[tl][2][16 * kq];
+      const float* tq = &tile[tl][3][16 * kq];
+      const float vv = vt[tl][vl];
+      float y0 = 0.f, y1 = 0.f, q0 = 0.f, q1 = 0.f;
+#pragma unroll
+      for (int j = 0; j < 16; j += 2) {
+        y0 += tr[j] * S[j]; y1 += tr[j + 1] * S[j + 1];
+        q0 += tq[j]; q1 += tq[j + 1];
+        S[j] = td[j] * S[j] + tk[j] * vv;
+        S[j + 1] = td[j + 1] * S[j + 1] + tk[j + 1] * vv;
+      }
+      float yy = (y0 + y1) + vv * (q0 + q1);
+      yy += __shfl_xor_sync(0xffffffffu, yy, 1);
+      yy += __shfl_xor_sync(0xffffffffu, yy, 2);
+      if (kq == 0) yt[tl][vl] = yy;
+    }
+    __syncthreads();
+    if (yout && tid < nt * 4) {
+      const int tl = tid >> 2, quad = tid & 3;
+      store4(yout + base + (long long)(t0 + tl) * tstride + y * VS + 4 * quad,
+             *reinterpret_cast<const float4*>(&yt[tl][4 * quad]));
+    }
+  }
+  if (sT) {
+    float* p = sT + (((long long)unit * HS) + 16 * kq) * HS + y * VS + vl;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) p[j * HS] = S[j];
+  }
+}
+
+struct BwdSmem {
+  float tile[CK][6][HS];          // r, d, exp(w), k, r*u, u*k
+  float ruk[CK];                  // sum_k r u k
+  float vt[CK][VS];
+  float dyt[CK][VS];
+  float dvt[CK][VS];
+  float Sbuf[CK][HS][SCOL];       // state before token i of the chunk
+  float part[2][CK][3][HS];       // partial dr, dk, dd over this CTA's 16 value columns
+  float pdyv[2][CK];              // partial sum_v dy v
+};
+
+template <typename T>
+__global__ void __cluster_dims__(1, NQ, 1) __launch_bounds__(64)
+wkv6_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __restrict__ v,
+                const T* __restrict__ w, const float* __restrict__ u,
+                const T* __restrict__ d_y, const float* __restrict__ d_sT, const float* __restrict__ ckpt,
+                T* __restrict__ dr, T* __restrict__ dk, T* __restrict__ dv, T* __restrict__ dw,
+                float* __restrict__ du_partial, float* __restrict__ d_s0, int Tn, int H) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  BwdSmem& sm = *reinterpret_cast<BwdSmem*>(smem_raw);
+  cg::cluster_group cluster = cg::this_cluster();
+
+  const int unit = blockIdx.x, y = blockIdx.y, tid = threadIdx.x;
+  const int bi = unit / H, hi = unit % H;
+  const int vl = tid >> 2, kq = tid & 3;   // value role
+  const int kc = tid;                      // key role
+  const long long base = ((long long)bi * Tn * H + hi) * HS;
+  const long long tstride = (long long)H * HS;
+  const int NC = (Tn + CK - 1) / CK;
+  const float4 u4 = *reinterpret_cast<const float4*>(u + hi * HS + 4 * (tid & 15));
+
+  float Gv[16], Gk[VS];   // value-role copy G[16kq+j][vl], key-role copy G[kc][i]
+  if (d_sT) {
+#pragma unroll
+    for (int j = 0; j < 16; ++j) Gv[j] = d_sT[(((long long)unit * HS) + 16 * kq + j) * HS + y * VS + vl];
+#pragma unroll
+    for (int i = 0; i < VS; ++i) Gk[i] = d_sT[(((long long)unit * HS) + kc) * HS + y * VS + i];
+  } else {
+#pragma unroll
+    for (int j = 0; j < 16; ++j) Gv[j] = 0.f;
+#pragma unroll
+    for (int i = 0; i < VS; ++i) Gk[i] = 0.f;
+  }
+  float du_acc = 0.f;
+
+  for (int c = NC - 1; c >= 0; --c) {
+    const int t0 = c * CK, nt = min(CK, Tn - t0), pb = c & 1;
+    for (int i = tid; i < nt * 16; i += 64) {
+      const int quad = i & 15, tl = i >> 4;
+      const long long off = base + (long long)(t0 + tl) * tstride + 4 * quad;
+      const float4 r4 = load4(r + off), k4 = load4(k + off), w4 = load4(w + off);
+      *reinterpret_cast<float4*>(&sm.tile[tl][0][4 * quad]) = r4;
+      *reinterpret_cast<float4*>(&sm.tile[tl][1][4 * quad]) =
+          make_float4(decay_of(w4.x), decay_of(w4.y), decay_of(w4.z), decay_of(w4.w));
+      *reinterpret_cast<float4*>(&sm.tile[tl][2][4 * quad]) = make_float4(expf(w4.x), expf(w4.y), expf(w4.z), expf(w4.w));
+      *reinterpret_cast<float4*>(&sm.tile[tl][3][4 * quad]) = k4;
+      *reinterpret_cast<float4*>(&sm.tile[tl][4][4 * quad]) = make_float4(r4.x * u4.x, r4.y * u4.y, r4.z * u4.z, r4.w * u4.w);
+      *reinterpret_cast<float4*>(&sm.tile[tl][5][4 * quad]) = make_float4(u4.x * k4.x, u4.y * k4.y, u4.z * k4.z, u4.w * k4.w);
+    }
+    if (tid < nt * 4) {
+      const int tl = tid >> 2, quad = tid & 3;
+      const long long off = base + (long long)(t0 + tl) * tstride + y * VS + 4 * quad;
+      *reinterpret_cast<float4*>(&sm.vt[tl][4 * quad]) = load4(v + off);
+      *reinterpret_cast<float4*>(&sm.dyt[tl][4 * quad]) = load4(d_y + off);
+    }
+    float S[16];
+    {
+      const float* p = ckpt + ((((long long)unit * NC + c) * HS) + 16 * kq) * HS + y * VS + vl;
+#pragma unroll
+      for (int j = 0; j < 16; ++j) S[j] = p[j * HS];
+    }
+    __syncthreads();
+    // sum_k r u k per token (threads 0..nt-1, one token each)
+    if (tid < nt) {
+      float s = 0.f;
+      for (int j = 0; j < HS; ++j) s += sm.tile[tid][4][j] * sm.tile[tid][3][j];
+      sm.ruk[tid] = s;
+    }
+    // re-run the chunk forward (value role), keeping the state before every token
+    for (int tl = 0; tl < nt; ++tl) {
+      const float* td = &sm.tile[tl][1][16 * kq];
+      const float* tk = &sm.tile[tl][3][16 * kq];
+      const float vv = sm.vt[tl][vl];
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        sm.Sbuf[tl][16 * kq + j][vl] = S[j];
+        S[j] = td[j] * S[j] + tk[j] * vv;
+      }
+    }
+    __syncthreads();
+
+    for (int tl = nt - 1; tl >= 0; --tl) {
+      // value role: dv = dy * sum(ruk) + sum_k G[k][v] k[k]
+      const float* tr = &sm.tile[tl][0][16 * kq];
+      const float* td = &sm.tile[tl][1][16 * kq];
+      const float* tk = &sm.tile[tl][3][16 * kq];
+      const float dyr = sm.dyt[tl][vl];
+      float a0 = 0.f, a1 = 0.f;
+#pragma unroll
+      for (int j = 0; j < 16; j += 2) {
+        a0 += Gv[j] * tk[j]; a1 += Gv[j + 1] * tk[j + 1];
+        Gv[j] = td[j] * Gv[j] + tr[j] * dyr;
+        Gv[j + 1] = td[j + 1] * Gv[j + 1] + tr[j + 1] * dyr;
+      }
+      float dvv = a0 + a1;
+      dvv += __shfl_xor_sync(0xffffffffu, dvv, 1);
+      dvv += __shfl_xor_sync(0xffffffffu, dvv, 2);
+      if (kq == 0) sm.dvt[tl][vl] = dvv + dyr * sm.ruk[tl];
+      // key role
+      const float rk = sm.tile[tl][0][kc], dk_ = sm.tile[tl][1][kc];
+      float p_dr = 0.f, p_dk = 0.f, p_dd = 0.f, p_dyv = 0.f;
+#pragma unroll
+      for (int i = 0; i < VS; ++i) {
+        const float sp = sm.Sbuf[tl][kc][i];
+        const float dyi = sm.dyt[tl][i], vi = sm.vt[tl][i];
+        p_dr += sp * dyi;
+        p_dk += Gk[i] * vi;
+        p_dd += Gk[i] * sp;
+        p_dyv += dyi * vi;
+        Gk[i] = dk_ * Gk[i] + rk * dyi;
+      }
+      sm.part[pb][tl][0][kc] = p_dr;
+      sm.part[pb][tl][1][kc] = p_dk;
+      sm.part[pb][tl][2][kc] = p_dd;
+      if (kc == 0) sm.pdyv[pb][tl] = p_dyv;
+    }
+    __syncthreads();
+    for (int i = tid; i < nt * VS; i += 64) {
+      const int tl = i >> 4, vi = i & 15;
+      dv[base + (long long)(t0 + tl) * tstride + y * VS + vi] = from_f32<T>(sm.dvt[tl][vi]);
+    }
+    cluster.sync();
+    for (int tl = y; tl < nt; tl += NQ) {
+      float acc[3] = {0.f, 0.f, 0.f}, dyv = 0.f;
+#pragma unroll
+      for (int rk_ = 0; rk_ < NQ; ++rk_) {
+        const float* rp = cluster.map_shared_rank(&sm.part[pb][tl][0][0], rk_);
+        const float* rd = cluster.map_shared_rank(&sm.pdyv[pb][0], rk_);
+#pragma unroll
+        for (int qn = 0; qn < 3; ++qn) acc[qn] += rp[qn * HS + kc];
+        dyv += rd[tl];
+      }
+      const long long off = base + (long long)(t0 + tl) * tstride + kc;
+      dr[off] = from_f32<T>(acc[0] + sm.tile[tl][5][kc] * dyv);
+      dk[off] = from_f32<T>(acc[1] + sm.tile[tl][4][kc] * dyv);
+      dw[off] = from_f32<T>(acc[2] * sm.tile[tl][1][kc] * (-sm.tile[tl][2][kc]));
+      du_acc += sm.tile[tl][0][kc] * sm.tile[tl][3][kc] * dyv;
+    }
+    __syncthreads();
+  }
+  du_partial[((long long)unit * NQ + y) * HS + kc] = du_acc;
+  if (d_s0) {
+#pragma unroll
+    for (int j = 0; j < 16; ++j) d_s0[(((long long)unit * HS) + 16 * kq + j) * HS + y * VS + vl] = Gv[j];
+  }
+  cluster.sync();
+}
+
+// du[h][k] = sum over batch rows and the four CTAs of a unit, in a fixed order.
+__global__ void __launch_bounds__(64)
+wkv6_du_reduce_kernel(const float* __restrict__ du_partial, float* __restrict__ du, int B, int H) {
+  const int hi = blockIdx.x, kc = threadIdx.x;
+  float s = 0.f;
+  for (int bi = 0; bi < B; ++bi)
+    for (int q = 0; q < NQ; ++q) s += du_partial[(((long long)bi * H + hi) * NQ + q) * HS + kc];
+  du[hi * HS + kc] = s;
+}
+
+}  // namespace
+
+int launch_wkv6_fwd(const void* r, const void* k, const void* v, const void* w, const float* u,
+                    const float* s0, int n_state, const int32_t* smap, void* y, float* sT,
+                    float* ckpt, int B, int Tn, int H, int dtype, cudaStream_t st) {
+  dim3 grid(B * H, NQ);
+  ProfScope prof("wkv6_fwd_kernel", st);
+  RWKVB200_DISPATCH_DTYPE(dtype,
+    wkv6_fwd_kernel<T><<<grid, 64, 0, st>>>((const T*)r, (const T*)k, (const T*)v, (const T*)w, u, s0, n_state, smap,
+                                            (T*)y, sT, ckpt, Tn, H));
+  return check_launch();
+}
+
+int launch_wkv6_bwd(const void* r, const void* k, const void* v, const void* w, const float* u,
+                    const void* d_y, const float* d_sT, const float* ckpt,
+                    void* dr, void* dk, void* dv, void* dw, float* du_partial, float* du, float* d_s0,
+                    int B, int Tn, int H, int dtype, cudaStream_t st) {
+  dim3 grid(B * H, NQ);
+  const int smem = (int)sizeof(BwdSmem);
+  {
+    ProfScope prof("wkv6_bwd_kernel", st);
+    RWKVB200_DISPATCH_DTYPE(dtype,
+      if (cudaFuncSetAttribute(wkv6_bwd_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+        return RWKVB200_E_CUDA;
+      wkv6_bwd_kernel<T><<<grid, 64, smem, st>>>((const T*)r, (const T*)k, (const T*)v, (const T*)w, u, (const T*)d_y,
+                                                 d_sT, ckpt, (T*)dr, (T*)dk, (T*)dv, (T*)dw, du_partial, d_s0, Tn, H));
+  }
+  int e = check_launch();
+  if (e) return e;
+  ProfScope prof("wkv6_du_reduce_kernel", st);
+  wkv6_du_reduce_kernel<<<H, 64, 0, st>>>(du_partial, du, B, H);
+  return check_launch();
+}
+
+}  // namespace rwkvb200

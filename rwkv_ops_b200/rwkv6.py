@@ -1,0 +1,175 @@
+"""RWKV6 wkv operator: the reference's ``RWKVKernelOperator`` interface over the CUDA library.
+
+Mirrors ``get_rwkv6_kernel`` / ``RWKVKernelOperator`` of the reference
+(``rwkv_ops/rwkv6_kernel/__init__.py:9-96``, ``rwkv_ops/rwkv6_kernel/ops_rwkv_kernel.py:5-86``,
+``rwkv_ops/rwkv6_kernel/torch_rwkv_kernel.py:50-304``): constructor ``(head_size,
+max_sequence_length, ops_loop=False)`` and call ``(r, k, v, w, u, with_state=False,
+init_state=None, state_map=None) -> (y, state | None)``.  Unlike the reference's GPU operator,
+gradients flow with ``with_state=True`` (to ``init_state`` as well), ``state_map`` works, and
+``max_sequence_length`` is not a compile-time constant (it is accepted and ignored).
+"""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib
+
+HEAD_SIZE = 64
+
+
+@torch.library.custom_op("rwkv_ops_b200::wkv6_fwd", mutates_args=())
+def _wkv6_fwd(r: torch.Tensor, k: torch.Tensor, v: torch.Tensor, w: torch.Tensor, u: torch.Tensor,
+              s0: Optional[torch.Tensor], state_map: Optional[torch.Tensor]) -> Tuple[torch.Tensor, torch.Tensor]:
+    lib = _lib.load()
+    dev = _lib.require_cuda(r, k, v, w, u, s0, state_map)
+    B, T, C = r.shape
+    H = C // HEAD_SIZE
+    code = _lib.dtype_code(r.dtype)
+    y = torch.empty_like(r)
+    sT = torch.empty(B, H, HEAD_SIZE, HEAD_SIZE, dtype=torch.float32, device=dev)
+    n_state = 0 if s0 is None else s0.shape[0]
+    with torch.cuda.device(dev):
+        rc = lib.rwkvb200_wkv6_fwd(r.data_ptr(), k.data_ptr(), v.data_ptr(), w.data_ptr(), u.data_ptr(),
+                                   _lib.ptr(s0), n_state, _lib.ptr(state_map), y.data_ptr(), sT.data_ptr(),
+                                   B, T, H, HEAD_SIZE, code, _lib.stream_ptr(dev))
+        _lib.check(rc, "wkv6_fwd")
+    return y, sT
+
+
+@_wkv6_fwd.register_fake
+def _(r, k, v, w, u, s0, state_map):
+    B, T, C = r.shape
+    return torch.empty_like(r), r.new_empty((B, C // HEAD_SIZE, HEAD_SIZE, HEAD_SIZE), dtype=torch.float32)
+
+
+@torch.library.custom_op("rwkv_ops_b200::wkv6_bwd", mutates_args=())
+def _wkv6_bwd(r: torch.Tensor, k: torch.Tensor, v: torch.Tensor, w: torch.Tensor, u: torch.Tensor,
+              s0: Optional[torch.Tensor], state_map: Optional[torch.Tensor],
+              d_y: torch.Tensor, d_sT: Optional[torch.Tensor]
+              ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
+    lib = _lib.load()
+    dev = _lib.require_cuda(r, k, v, w, u, s0, state_map, d_y, d_sT)
+    B, T, C = r.shape
+    H = C // HEAD_SIZE
+    code = _lib.dtype_code(r.dtype)
+    dr, dk, dv, dw = (torch.empty_like(r) for _ in range(4))
+    du = torch.empty(H, HEAD_SIZE, dtype=torch.float32, device=dev)
+    ds0 = torch.empty(B, H, HEAD_SIZE, HEAD_SIZE, dtype=torch.float32, device=dev)
+    n_state = 0 if s0 is None else s0.shape[0]
+    with torch.cuda.device(dev):
+        nws = lib.rwkvb200_wkv6_bwd_workspace_bytes(B, T, H, HEAD_SIZE, code)
+        ws = torch.empty(nws, dtype=torch.uint8, device=dev)
+        rc = lib.rwkvb200_wkv6_bwd(r.data_ptr(), k.data_ptr(), v.data_ptr(), w.data_ptr(), u.data_ptr(),
+                                   _lib.ptr(s0), n_state, _lib.ptr(state_map), d_y.data_ptr(), _lib.ptr(d_sT),
+                                   dr.data_ptr(), dk.data_ptr(), dv.data_ptr(), dw.data_ptr(), du.data_ptr(),
+                                   ds0.data_ptr(), ws.data_ptr(), nws, B, T, H, HEAD_SIZE, code,
+                                   _lib.stream_ptr(dev))
+        _lib.check(rc, "wkv6_bwd")
+    return dr, dk, dv, dw, du, ds0
+
+
+@_wkv6_bwd.register_fake
+def _(r, k, v, w, u, s0, state_map, d_y, d_sT):
+    B, T, C = r.shape
+    H = C // HEAD_SIZE
+    e = torch.empty_like
+    return (e(r), e(r), e(r), e(r), r.new_empty((H, HEAD_SIZE), dtype=torch.float32),
+            r.new_empty((B, H, HEAD_SIZE, HEAD_SIZE), dtype=torch.float32))
+
+
+def _setup_ctx(ctx, inputs, output):
+    r, k, v, w, u, s0, state_map = inputs
+    ctx.save_for_backward(r, k, v, w, u, s0, state_map)
+
+
+def _backward(ctx, d_y, d_sT):
+    r, k, v, w, u, s0, state_map = ctx.saved_tensors
+    if d_y is None:
+        d_y = torch.zeros_like(r)
+    d_y = d_y.to(r.dtype).contiguous()
+    if d_sT is not None:
+        d_sT = d_sT.to(torch.float32).contiguous()
+    dr, dk, dv, dw, du, ds0_rows = _wkv6_bwd(r, k, v, w, u, s0, state_map, d_y, d_sT)
+    ds0 = None
+    if s0 is not None and ctx.needs_input_grad[5]:
+        n_state, B = s0.shape[0], r.shape[0]
+        if state_map is not None:
+            idx = state_map.to(torch.int64)
+        elif n_state == 1:
+            idx = torch.zeros(B, dtype=torch.int64, device=r.device)
+        else:
+            idx = torch.arange(B, device=r.device)
+        # several batch rows may start from the same table row: their gradients add up
+        ds0 = torch.zeros_like(s0).index_add_(0, idx, ds0_rows)
+    return dr, dk, dv, dw, du, ds0, None
+
+
+torch.library.register_autograd("rwkv_ops_b200::wkv6_fwd", _backward, setup_context=_setup_ctx)
+
+
+class RWKVKernelOperator:
+    """Drop-in for the class returned by the reference's ``get_rwkv6_kernel``."""
+
+    def __init__(self, head_size, max_sequence_length, ops_loop=False):
+        if head_size != HEAD_SIZE:
+            raise ValueError("rwkv_ops_b200 is built for head size 64")
+        self.head_size = head_size
+        self.max_sequence_length = max_sequence_length   # kept for compatibility; no limit applies
+        self.ops_loop = ops_loop
+
+    def __call__(self, r, k, v, w, u, with_state=False, init_state=None, state_map=None):
+        dev = _lib.require_cuda(r, k, v, w, u, init_state)
+        if r.dim() != 3:
+            raise ValueError(f"expected [B, T, C] tensors, got {tuple(r.shape)}")
+        B, T, C = r.shape
+        N = self.head_size
+        assert C % N == 0, "hidden size must be a multiple of head_size"
+        H = C // N
+        for name, x in (("k", k), ("v", v), ("w", w)):
+            assert x.shape == r.shape, f"{name} has shape {tuple(x.shape)}, expected {tuple(r.shape)}"
+            assert x.dtype == r.dtype, "r, k, v, w must share one dtype"
+        assert u.numel() == C, f"u must have {C} elements"
+        dt = r.dtype
+        cdt = dt if dt in (torch.float32, torch.bfloat16, torch.float16) else torch.float32
+        state_dtype = torch.float32 if dt == torch.float16 else dt
+
+        s0 = None
+        smap = None
+        if init_state is not None:
+            assert init_state.dim() in (3, 4), "init_state must be [n_state, H, N, N] or [H, N, N]"
+            if init_state.dim() == 3:
+                assert tuple(init_state.shape) == (H, N, N), "init_state must be [H, N, N]"
+                init_state = init_state[None]
+            else:
+                assert tuple(init_state.shape[1:]) == (H, N, N), "init_state must be [n_state, H, N, N]"
+            n_state = init_state.shape[0]
+            if state_map is None:
+                if n_state not in (1, B):
+                    raise ValueError("state_map cannot be inferred from init_state; pass it explicitly")
+            else:
+                if isinstance(state_map, (list, tuple)):
+                    state_map = torch.tensor(state_map, dtype=torch.int32)
+                assert state_map.dtype in (torch.int32, torch.int64), "state_map must be int32 or int64"
+                assert state_map.numel() == B, "state_map must have one entry per batch row"
+                host = state_map.detach().cpu()
+                assert bool((host >= 0).all()) and bool((host < n_state).all()), (
+                    f"state_map values must lie in [0, {n_state})")
+                smap = state_map.to(device=dev, dtype=torch.int32).contiguous().view(B)
+            s0 = init_state.to(torch.float32).contiguous()
+        else:
+            assert state_map is None, "state_map needs init_state"
+
+        y, sT = _wkv6_fwd(r.to(cdt).contiguous(), k.to(cdt).contiguous(), v.to(cdt).contiguous(),
+                          w.to(cdt).contiguous(), u.reshape(H, N).to(torch.float32).contiguous(), s0, smap)
+        if y.dtype != dt:
+            y = y.to(dt)
+        if with_state:
+            return y, sT.to(state_dtype)
+        return y, None
+
+
+def get_rwkv6_kernel(KERNEL_TYPE: str = "cuda"):
+    """Reference signature (``rwkv_ops/rwkv6_kernel/__init__.py:9``); ``KERNEL_TYPE`` is ignored."""
+    return RWKVKernelOperator

@@ -1,0 +1,126 @@
+"""GPU parity of the RWKV6 wkv operator against the CPU oracle and the golden vectors recorded
+from the reference's native operator.  Tolerance: relative L2 1e-4 for float32, 2e-2 for bfloat16."""
+import glob
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import rwkv_ops_b200 as ro
+from oracle import RWKVKernelOperator as OracleOp, wkv6_manual_backward
+from rwkv_ops_b200.workloads import wkv6_inputs, rel_l2
+
+pytestmark = pytest.mark.gpu
+
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
+R6 = sorted(glob.glob(os.path.join(GOLDEN, "wkv6_*.npz")))
+
+
+@pytest.mark.parametrize("path", R6, ids=[os.path.basename(p)[:-4] for p in R6])
+def test_golden_forward_backward(path):
+    z = np.load(path)
+    ins = {n: torch.from_numpy(z[f"in_{n}"]).cuda().requires_grad_(True) for n in "rkvwu"}
+    s0 = torch.from_numpy(z["in_init_state"]).cuda().requires_grad_(True) if "in_init_state" in z else None
+    smap = torch.from_numpy(z["in_state_map"]).cuda() if "in_state_map" in z else None
+    with_state = "final_state" in z
+    T = ins["r"].shape[1]
+    y, s = ro.RWKV6_OP(64, T)(ins["r"], ins["k"], ins["v"], ins["w"], ins["u"], with_state=with_state,
+                              init_state=s0, state_map=smap)
+    assert rel_l2(y, torch.from_numpy(z["y"])) < 1e-4
+    loss = (y * torch.from_numpy(z["d_y"]).cuda()).sum()
+    if with_state:
+        assert rel_l2(s, torch.from_numpy(z["final_state"])) < 1e-4
+        loss = loss + (s * torch.from_numpy(z["d_state"]).cuda()).sum()
+    else:
+        assert s is None
+    loss.backward()
+    for n in "rkvwu":
+        assert ins[n].grad.shape == ins[n].shape
+        assert rel_l2(ins[n].grad, torch.from_numpy(z[f"grad_{n}"])) < 1e-4, n
+    if s0 is not None:
+        assert rel_l2(s0.grad, torch.from_numpy(z["grad_init_state"])) < 1e-4
+
+
+@pytest.mark.parametrize("T", [1, 2, 7, 8, 9, 31, 64, 100])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_ragged_lengths_vs_oracle(T, dtype):
+    B, H = 3, 2
+    d = wkv6_inputs(B, T, H, dtype=dtype, seed=600 + T, n_state=2, with_grads=True)
+    d["state_map"] = torch.tensor([1, 0, 1], dtype=torch.int32)   # a repeated table row
+    ref = {n: d[n].float().clone().requires_grad_(True) for n in "rkvwu"}
+    s0r = d["init_state"].float().clone().requires_grad_(True)
+    y_ref, s_ref = OracleOp(64, T)(ref["r"], ref["k"], ref["v"], ref["w"], ref["u"], with_state=True,
+                                   init_state=s0r, state_map=d["state_map"])
+    ((y_ref * d["d_y"].float()).sum() + (s_ref * d["d_state"].float()).sum()).backward()
+    g = {n: d[n].cuda().requires_grad_(True) for n in "rkvwu"}
+    s0 = d["init_state"].cuda().requires_grad_(True)
+    y, s = ro.RWKV6_OP(64, T)(g["r"], g["k"], g["v"], g["w"], g["u"], with_state=True, init_state=s0,
+                              state_map=d["state_map"].cuda())
+    assert y.dtype == dtype and s.dtype == dtype
+    ((y.float() * d["d_y"].cuda().float()).sum() + (s.float() * d["d_state"].cuda().float()).sum()).backward()
+    tol = 1e-4 if dtype == torch.float32 else 2e-2
+    assert rel_l2(y, y_ref) < tol and rel_l2(s, s_ref) < tol
+    for n in "rkvwu":
+        assert rel_l2(g[n].grad, ref[n].grad) < tol, n
+    assert rel_l2(s0.grad, s0r.grad) < tol
+
+
+def test_u_shapes_list_state_map_and_errors():
+    B, T, H = 2, 12, 2
+    d = wkv6_inputs(B, T, H, seed=61, n_state=3)
+    x = {n: d[n].cuda() for n in "rkvw"}
+    op = ro.RWKV6_OP(64, T)
+    y0, s0 = op(x["r"], x["k"], x["v"], x["w"], d["u"].cuda(), with_state=True, init_state=d["init_state"].cuda(),
+                state_map=[2, 0])
+    y1, s1 = op(x["r"], x["k"], x["v"], x["w"], d["u"].cuda().reshape(1, 1, -1), with_state=True,
+                init_state=d["init_state"].cuda(), state_map=torch.tensor([2, 0], dtype=torch.int64))
+    assert torch.equal(y0, y1) and torch.equal(s0, s1)
+    with pytest.raises(ValueError):
+        op(x["r"], x["k"], x["v"], x["w"], d["u"].cuda(), with_state=True, init_state=d["init_state"].cuda())
+    with pytest.raises(AssertionError):
+        op(x["r"], x["k"], x["v"], x["w"], d["u"].cuda(), with_state=True, init_state=d["init_state"].cuda(),
+           state_map=[0, 3])
+    with pytest.raises(AssertionError):
+        op(x["r"], x["k"], x["v"], x["w"], d["u"].cuda(), state_map=[0, 1])
+    # a single [H,N,N] state is shared by the batch
+    y2, _ = op(x["r"], x["k"], x["v"], x["w"], d["u"].cuda(), with_state=True, init_state=d["init_state"][1].cuda())
+    y3, _ = op(x["r"], x["k"], x["v"], x["w"], d["u"].cuda(), with_state=True, init_state=d["init_state"].cuda(),
+               state_map=[1, 1])
+    assert torch.equal(y2, y3)
+
+
+def test_split_sequence_equals_whole():
+    B, T, H = 2, 150, 3
+    d = wkv6_inputs(B, T, H, seed=62, n_state=B)
+    x = {n: d[n].cuda() for n in "rkvw"}
+    u = d["u"].cuda()
+    op = ro.RWKV6_OP(64, T)
+    y, s = op(x["r"], x["k"], x["v"], x["w"], u, with_state=True, init_state=d["init_state"].cuda())
+    y1, s1 = op(*[x[n][:, :61] for n in "rkvw"], u, with_state=True, init_state=d["init_state"].cuda())
+    y2, s2 = op(*[x[n][:, 61:] for n in "rkvw"], u, with_state=True, init_state=s1)
+    assert rel_l2(torch.cat([y1, y2], 1), y) < 1e-5 and rel_l2(s2, s) < 1e-5
+
+
+def test_full_size_sampled_units():
+    """Benchmark configuration 4 at full size (fp32, B16 T4096 C2048, 4 initial states): sampled
+    (batch, head) units against the oracle run on those units alone."""
+    B, T, H = 16, 4096, 32
+    d = wkv6_inputs(B, T, H, seed=1004, device="cuda", n_state=4, with_grads=True)
+    g = {n: d[n].requires_grad_(True) for n in "rkvwu"}
+    s0 = d["init_state"].requires_grad_(True)
+    y, s = ro.RWKV6_OP(64, T)(g["r"], g["k"], g["v"], g["w"], g["u"], with_state=True, init_state=s0,
+                              state_map=d["state_map"])
+    ((y * d["d_y"]).sum() + (s * d["d_state"]).sum()).backward()
+    units = [(0, 0), (5, 13), (15, 31)]
+    smap = d["state_map"].cpu()
+    for (b, h) in units:
+        sl = slice(h * 64, (h + 1) * 64)
+        sub = [g[n].detach()[b:b + 1, :, sl].cpu() for n in "rkvw"] + [g["u"].detach()[h:h + 1].cpu()]
+        s0b = s0.detach()[smap[b]:smap[b] + 1, h:h + 1].cpu()
+        y_ref, s_ref = OracleOp(64, T)(*sub, with_state=True, init_state=s0b)
+        assert rel_l2(y[b:b + 1, :, sl], y_ref) < 1e-4
+        assert rel_l2(s[b:b + 1, h:h + 1], s_ref) < 1e-4
+        gr = wkv6_manual_backward(*sub, s0b, d["d_y"][b:b + 1, :, sl].cpu(), d["d_state"][b:b + 1, h:h + 1].cpu(), 64)
+        for n, gn in zip("rkvw", gr[:4]):
+            assert rel_l2(g[n].grad[b:b + 1, :, sl], gn) < 1e-4, n
