@@ -107,6 +107,29 @@ int rwkvb200_rwkv7_bwd(const void* r, const void* w, const void* k, const void* 
                        int B, int T, int H, int head_size, int dtype, int head_first, int algo,
                        void* stream);
 
+/* Backward without a workspace argument, for callers that cannot allocate device memory.
+ * No counterpart in the reference.  It is the float32 recurrent backward (RWKVB200_ALGO_RECURRENT)
+ * with the same inputs, outputs and results as rwkvb200_rwkv7_bwd, but its state checkpoints live in
+ * a fixed array inside the library's device image instead of a caller workspace.  Meant for hosts
+ * that hand an operator only its input and output buffers and forbid cudaMalloc in the call
+ * (operator plugins of inference runtimes, servers that reserved all device memory at start-up).
+ *   - Every GPU that loads the library holds RWKVB200_STATIC_SCRATCH_BYTES for the life of the process.
+ *   - B*H*ceil(T/8)*16 KiB must fit in that array, else RWKVB200_E_TOO_LARGE.
+ *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress, with
+ *     that device current); make that first call before any stream capture begins.
+ *   - The array is shared by all calls and keeps the previous call's contents (nothing in it needs
+ *     to start at zero).  Calls that overlap on the GPU race on it: issue them on one stream.
+ *   - It calls no cudaMalloc / cudaFree and no allocating library routine. */
+#define RWKVB200_STATIC_SCRATCH_BYTES (32u << 20)
+size_t rwkvb200_rwkv7_bwd_static_capacity_bytes(void);
+int rwkvb200_rwkv7_bwd_static(const void* r, const void* w, const void* k, const void* v,
+                              const void* a, const void* b,
+                              const float* h0, int n_state,
+                              const void* d_o, const float* d_ht,
+                              void* dr, void* dw, void* dk, void* dv, void* da, void* db, float* d_h0,
+                              int B, int T, int H, int head_size, int dtype, int head_first,
+                              void* stream);
+
 /* ------------------------------------------------------------------------------------------
  * RWKV6 wkv.
  * Replaces RWKVKernelOperator.__call__ of the reference
