@@ -1,0 +1,134 @@
+"""Device-timed micro-benchmarks of the individual operators (CUDA events, inputs resident in HBM).
+
+    python -m rwkv_ops_b200.microbench step  [--B 256 --H 64 --steps 50 --dtype bf16]
+    python -m rwkv_ops_b200.microbench wkv6  [--B 16 --T 4096 --H 32 --steps 5]
+    python -m rwkv_ops_b200.microbench rwkv7 [--B 8 --T 4096 --H 32 --steps 5 --dtype bf16 --algo auto]
+
+Each prints one JSON line with the time per call and the achieved algorithmic bandwidth.  These
+are the commands the profiler captures in ``profiles/`` were taken from.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+
+import rwkv_ops_b200 as ro
+from rwkv_ops_b200 import _lib
+from rwkv_ops_b200.workloads import rwkv7_inputs, wkv6_inputs
+
+DT = {"bf16": torch.bfloat16, "f32": torch.float32, "f16": torch.float16}
+
+
+def _time(fn, steps, warmup=3):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    _lib.profile(True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    prof = _lib.profile_results()
+    _lib.profile(False)
+    return e0.elapsed_time(e1) / steps, {k: v[0] / max(v[1], 1) for k, v in prof.items()}
+
+
+def bench_step(a):
+    """Configuration 3: T=1 decode, fp32 state [B,H,64,64] fed back step after step."""
+    dt = DT[a.dtype]
+    n_in = 8   # distinct input sets so consecutive steps do not reuse L2-resident token vectors
+    ds = [rwkv7_inputs(a.B, 1, a.H, dtype=dt, seed=1003 + i, device="cuda") for i in range(n_in)]
+    state = 0.1 * torch.randn(a.B, a.H, 64, 64, device="cuda")
+    lib = _lib.load()
+    code = _lib.dtype_code(dt)
+    o = torch.empty(a.B, a.H, 64, dtype=dt, device="cuda")
+    bufs = [state, torch.empty_like(state)]
+    i = [0]
+
+    def fn():
+        d = ds[i[0] % n_in]
+        src, dst = bufs[i[0] & 1], bufs[(i[0] + 1) & 1]
+        rc = lib.rwkvb200_rwkv7_step(*[d[n].data_ptr() for n in "rwkvab"], src.data_ptr(), a.B, dst.data_ptr(),
+                                     o.data_ptr(), a.B, a.H, 64, code, torch.cuda.current_stream().cuda_stream)
+        assert rc == 0
+        i[0] += 1
+
+    ms, kern = _time(fn, a.steps)
+    es = torch.finfo(dt).bits // 8
+    nbytes = a.B * a.H * (2 * 64 * 64 * 4 + 7 * 64 * es)
+    return {"op": "rwkv7_step", "B": a.B, "H": a.H, "dtype": a.dtype, "us_per_step": 1e3 * ms,
+            "algorithmic_bytes": nbytes, "GBps": nbytes / (ms / 1e3) / 1e9,
+            "state_bytes_vs_l2": "state ping-pong buffers (2 x %.0f MB) exceed the 126 MB L2" % (a.B * a.H * 16384 / 1e6),
+            "kernel_ms": kern}
+
+
+def bench_wkv6(a):
+    """Configuration 4: wkv6 forward + backward, fp32, 4 initial states and a state_map."""
+    dt = DT[a.dtype]
+    d = wkv6_inputs(a.B, a.T, a.H, dtype=dt, seed=1004, device="cuda", n_state=4, with_grads=True)
+    g = {n: d[n].requires_grad_(True) for n in "rkvwu"}
+    s0 = d["init_state"].requires_grad_(True)
+    op = ro.RWKV6_OP(64, a.T)
+
+    def fn():
+        y, s = op(g["r"], g["k"], g["v"], g["w"], g["u"], with_state=True, init_state=s0, state_map=d["state_map"])
+        torch.autograd.backward([y, s], [d["d_y"], d["d_state"]])
+        for t in list(g.values()) + [s0]:
+            t.grad = None
+
+    ms, kern = _time(fn, a.steps)
+    es = torch.finfo(dt).bits // 8
+    nbytes = a.B * a.T * a.H * 64 * es * 14
+    return {"op": "wkv6_fwd_bwd", "B": a.B, "T": a.T, "H": a.H, "dtype": a.dtype, "ms_per_step": ms,
+            "tokens_per_s": a.B * a.T / (ms / 1e3), "algorithmic_bytes": nbytes,
+            "GBps": nbytes / (ms / 1e3) / 1e9, "kernel_ms": kern}
+
+
+def bench_rwkv7(a):
+    dt = DT[a.dtype]
+    os.environ["RWKV_OPS_B200_RWKV7_ALGO"] = a.algo
+    d = rwkv7_inputs(a.B, a.T, a.H, dtype=dt, seed=1001, device="cuda", with_grads=True)
+    g = {n: d[n].requires_grad_(True) for n in "rwkvab"}
+
+    def fn():
+        o, s = ro.generalized_delta_rule(*[g[n] for n in "rwkvab"])
+        if not a.fwd_only:
+            torch.autograd.backward([o, s], [d["d_out"], d["d_state"]])
+            for t in g.values():
+                t.grad = None
+
+    ms, kern = _time(fn, a.steps)
+    es = torch.finfo(dt).bits // 8
+    nbytes = a.B * a.T * a.H * 64 * es * (7 if a.fwd_only else 20)
+    return {"op": "rwkv7_fwd" if a.fwd_only else "rwkv7_fwd_bwd", "algo": a.algo, "B": a.B, "T": a.T, "H": a.H,
+            "dtype": a.dtype, "ms_per_step": ms, "tokens_per_s": a.B * a.T / (ms / 1e3),
+            "algorithmic_bytes": nbytes, "GBps": nbytes / (ms / 1e3) / 1e9, "kernel_ms": kern}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("op", choices=["step", "wkv6", "rwkv7"])
+    ap.add_argument("--B", type=int)
+    ap.add_argument("--T", type=int, default=4096)
+    ap.add_argument("--H", type=int)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--dtype", default=None)
+    ap.add_argument("--algo", default="auto")
+    ap.add_argument("--fwd-only", action="store_true")
+    a = ap.parse_args()
+    defaults = {"step": (256, 64, "bf16"), "wkv6": (16, 32, "f32"), "rwkv7": (8, 32, "bf16")}[a.op]
+    a.B = a.B or defaults[0]
+    a.H = a.H or defaults[1]
+    a.dtype = a.dtype or defaults[2]
+    torch.cuda.set_device(0)
+    res = {"step": bench_step, "wkv6": bench_wkv6, "rwkv7": bench_rwkv7}[a.op](a)
+    print(json.dumps(res), flush=True)
+
+
+if __name__ == "__main__":
+    main()
