@@ -1,6 +1,7 @@
 // extern "C" entry points of librwkv_ops_b200.so: argument checks and dispatch.
 // The contract of every function is in include/rwkv_ops_b200.h.
 #include "common.cuh"
+#include "rwkv7_chunked.cuh"
 
 using namespace rwkvb200;
 
@@ -70,7 +71,7 @@ int rwkvb200_rwkv7_step(const void* r, const void* w, const void* k, const void*
 
 size_t rwkvb200_rwkv7_fwd_workspace_bytes(int B, int T, int H, int head_size, int dtype, int algo) {
   if (check_common(B, T, H, head_size, dtype)) return 0;
-  (void)algo;
+  if (resolve_r7_algo(algo, dtype) == RWKVB200_ALGO_CHUNKED) return r7c::fwd_workspace_bytes(B, T, H, r7c::FWD_TILES);
   return 0;
 }
 
@@ -87,11 +88,16 @@ int rwkvb200_rwkv7_fwd(const void* r, const void* w, const void* k, const void* 
   if (n_state != 0 && !h0) return RWKVB200_E_NULL;
   const void* ps[] = {r, w, k, v, a, b, h0, o, ht, workspace};
   for (const void* p : ps) if (p && !aligned16(p)) return RWKVB200_E_ALIGN;
-  if (workspace_bytes < rwkvb200_rwkv7_fwd_workspace_bytes(B, T, H, head_size, dtype, algo)) return RWKVB200_E_WORKSPACE;
+  const size_t need = rwkvb200_rwkv7_fwd_workspace_bytes(B, T, H, head_size, dtype, algo);
+  if (workspace_bytes < need || (need && !workspace)) return RWKVB200_E_WORKSPACE;
   switch (resolve_r7_algo(algo, dtype)) {
     case RWKVB200_ALGO_RECURRENT:
       return launch_rwkv7_rec_fwd(r, w, k, v, a, b, n_state ? h0 : nullptr, n_state, o, ht, nullptr, R7_CKPT,
                                   B, T, H, dtype, head_first, (cudaStream_t)stream);
+    case RWKVB200_ALGO_CHUNKED:
+      if (dtype != RWKVB200_BF16) return RWKVB200_E_UNSUPPORTED;
+      return launch_rwkv7_chunked_fwd(r, w, k, v, a, b, n_state ? h0 : nullptr, n_state, o, ht, workspace,
+                                      B, T, H, head_first, false, (cudaStream_t)stream);
     default:
       return RWKVB200_E_UNSUPPORTED;
   }

@@ -1,0 +1,467 @@
+// Chunked RWKV7 forward on tcgen05 (bf16 token tensors, fp32 state).  Equations and the
+// two-kernel structure are described in rwkv7_chunked.cuh.
+#include "rwkv7_chunked.cuh"
+
+namespace rwkvb200 {
+namespace r7c {
+
+using namespace tc;
+typedef __nv_bfloat16 bf16;
+
+constexpr float EXP_CLAMP = 80.f;
+__device__ __forceinline__ float cexp(float x) { return __expf(fminf(fmaxf(x, -EXP_CLAMP), EXP_CLAMP)); }
+
+// ---------------------------------------------------------------------------------------------
+// intra-chunk kernel: grid = B*H*NT, 128 threads
+// ---------------------------------------------------------------------------------------------
+constexpr int NROW = 68;   // padded row of the fp32 copy of A_ab (keeps float4 alignment)
+
+struct IntraSmem {
+  unsigned char qt[TILE_BYTES], at[TILE_BYTES];     // [q~; a~]  (128-row A operand)
+  unsigned char kt[TILE_BYTES], bt[TILE_BYTES];     // [k~; b~]  (128-row B operand)
+  unsigned char aqk[TILE_BYTES], aak[TILE_BYTES];   // [A_qk; A_ak] (128-row A operand); aak later holds W
+  unsigned char o1[TILE_BYTES];                     // A_qk v
+  unsigned char aqb[TILE_BYTES];
+  unsigned char v[TILE_BYTES];                      // TMA; later U
+  unsigned char ainv[TILE_BYTES];
+  unsigned char y[TILE_BYTES];                      // A_ak v
+  float nmat[L * NROW];                             // stril(A_ab) in fp32
+  float tot[2][64];
+  uint64_t bar_v, bar_m1, bar_m2, bar_m3;
+  uint32_t tmem_base;
+};
+
+__global__ void __launch_bounds__(128)
+r7c_intra_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ w, const bf16* __restrict__ k,
+                     const bf16* __restrict__ a, const bf16* __restrict__ b,
+                     const __grid_constant__ CUtensorMap tmap_v, unsigned char* __restrict__ ws_tiles,
+                     float* __restrict__ ws_aux, int tiles_per_chunk, int keep_for_bwd,
+                     int Tn, int H, int NT, TokLayout lay, int* status) {
+  extern __shared__ unsigned char smem_raw[];
+  IntraSmem& sm = *reinterpret_cast<IntraSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int ch = blockIdx.x, unit = ch / NT, cidx = ch % NT;
+  const int bi = unit / H, hi = unit % H, t0 = cidx * L;
+  const long long base = bi * lay.sb + hi * lay.sh;
+  unsigned char* out_tiles = ws_tiles + (size_t)ch * tiles_per_chunk * TILE_BYTES;
+
+  if (tid == 0) {
+    mbar_init(&sm.bar_v, 1); mbar_init(&sm.bar_m1, 1); mbar_init(&sm.bar_m2, 1); mbar_init(&sm.bar_m3, 1);
+    fence_mbar_init();
+  }
+  if (warp == 0) tmem_alloc(&sm.tmem_base, 256);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tm = sm.tmem_base;
+  if (tid == 0) {
+    mbar_expect_tx(&sm.bar_v, TILE_BYTES);
+    tma_load_4d(sm.v, &tmap_v, &sm.bar_v, 0, t0, hi, bi);
+  }
+
+  // ---- phase A: decay prefix sums and the four scaled operands.  Thread = (channel, half of the chunk)
+  {
+    const int c = tid & 63, half = tid >> 6;
+    float gl[32];
+    float run = 0.f;
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      const int tok = t0 + 32 * half + j;
+      float g = 0.f;
+      if (tok < Tn) g = -expf(__bfloat162float(w[base + (long long)tok * lay.st + c]));
+      run += g;
+      gl[j] = run;
+    }
+    sm.tot[half][c] = run;
+    __syncthreads();
+    const float tot0 = sm.tot[0][c], tot1 = sm.tot[1][c];
+    if (half == 0) {
+      ws_aux[(size_t)ch * AUX_FLOATS + c] = __expf(fmaxf(tot0, -EXP_CLAMP));        // e^{gref}
+      ws_aux[(size_t)ch * AUX_FLOATS + 64 + c] = __expf(fmaxf(tot1, -EXP_CLAMP));   // e^{glast-gref}
+    }
+    const float shift = half ? 0.f : tot0;    // gi - gref = gl - shift
+#pragma unroll 8
+    for (int j = 0; j < 32; ++j) {
+      const int i = 32 * half + j, tok = t0 + i;
+      float qv = 0.f, kv = 0.f, av = 0.f, bv = 0.f;
+      if (tok < Tn) {
+        const long long off = base + (long long)tok * lay.st + c;
+        qv = __bfloat162float(q[off]); kv = __bfloat162float(k[off]);
+        av = __bfloat162float(a[off]); bv = __bfloat162float(b[off]);
+      }
+      const float d1 = gl[j] - shift;                       // gi - gref
+      const float gj = gl[j] - (j ? gl[j - 1] : 0.f);       // g of this token
+      const float eq = cexp(d1), ek = cexp(-d1), ea = cexp(d1 - gj);
+      const uint32_t off = tile_off(i, c);
+      *reinterpret_cast<bf16*>(sm.qt + off) = __float2bfloat16_rn(qv * eq);
+      *reinterpret_cast<bf16*>(sm.kt + off) = __float2bfloat16_rn(kv * ek);
+      *reinterpret_cast<bf16*>(sm.at + off) = __float2bfloat16_rn(av * ea);
+      *reinterpret_cast<bf16*>(sm.bt + off) = __float2bfloat16_rn(bv * ek);
+    }
+  }
+  fence_async_smem();
+  __syncthreads();
+
+  // ---- MMA 1: [q~; a~] [k~; b~]^T  ->  TMEM columns 0..127, row r on lane r
+  if (tid == 0) {
+    tc_fence_after();
+    umma_tile<128, 128, 0, 0>(tm, smem_u32(sm.qt), smem_u32(sm.kt), false);
+    umma_commit(&sm.bar_m1);
+  }
+  bool ok = mbar_wait(&sm.bar_m1, 0, status, 201);
+  tc_fence_after();
+  if (ok) {
+    const int i = tid & 63;
+    const bool lower = tid >= 64;       // rows of a~: strictly lower triangle; rows of q~: lower incl. diagonal
+#pragma unroll
+    for (int part = 0; part < 4; ++part) {
+      uint32_t r[32];
+      tmem_ld32(tmem_addr(tm, 32 * warp, 32 * part), r);
+      tmem_ld_wait();
+      float x[32];
+      const int j0 = 32 * (part & 1);
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        const bool keep = lower ? (j0 + j < i) : (j0 + j <= i);
+        x[j] = keep ? __uint_as_float(r[j]) : 0.f;
+      }
+      if (!lower) {
+        tile_store_row32(part < 2 ? sm.aqk : sm.aqb, i, j0, x);
+      } else if (part < 2) {
+        tile_store_row32(sm.aak, i, j0, x);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; j += 4)
+          *reinterpret_cast<float4*>(&sm.nmat[i * NROW + j0 + j]) = make_float4(x[j], x[j + 1], x[j + 2], x[j + 3]);
+      }
+    }
+  }
+  fence_async_smem();
+  tc_fence_before();
+  __syncthreads();
+
+  // ---- MMA 2: [A_qk; A_ak] v  ->  TMEM columns 128..191 (rows 0..63 = O1, 64..127 = Y)
+  if (tid == 0) {
+    ok = mbar_wait(&sm.bar_v, 0, status, 202);
+    tc_fence_after();
+    umma_tile<128, 64, 0, 1>(tmem_addr(tm, 0, 128), smem_u32(sm.aqk), smem_u32(sm.v), false);
+    umma_commit(&sm.bar_m2);
+    if (keep_for_bwd) {   // A_qk, A_ak, a~ are operands of the backward: copy them out before they are overwritten
+      bulk_store(out_tiles + S_AQK * TILE_BYTES, sm.aqk, TILE_BYTES);
+      bulk_store(out_tiles + S_AAK * TILE_BYTES, sm.aak, TILE_BYTES);
+      bulk_store(out_tiles + S_AT * TILE_BYTES, sm.at, TILE_BYTES);
+      bulk_commit();
+    }
+  }
+  if (tid < 64) {
+    // ---- Ainv = (I - stril(A_ab))^-1 by forward substitution, one column per thread, fp32
+    const int c = tid;
+    float X[64];
+#pragma unroll
+    for (int i = 0; i < 64; ++i) X[i] = 0.f;
+#pragma unroll
+    for (int i = 0; i < 64; ++i) {
+      float a0 = (i == c) ? 1.f : 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+#pragma unroll
+      for (int jj = 0; jj < (i + 3) / 4; ++jj) {
+        const float4 n = *reinterpret_cast<const float4*>(&sm.nmat[i * NROW + 4 * jj]);
+        a0 += n.x * X[4 * jj]; a1 += n.y * X[4 * jj + 1]; a2 += n.z * X[4 * jj + 2]; a3 += n.w * X[4 * jj + 3];
+      }
+      X[i] = (a0 + a1) + (a2 + a3);
+      *reinterpret_cast<bf16*>(sm.ainv + tile_off(i, c)) = __float2bfloat16_rn(X[i]);
+    }
+  }
+  {
+    // rows of MMA 2: threads 0..63 take O1 (after the inverse), threads 64..127 take Y
+    ok = mbar_wait(&sm.bar_m2, 0, status, 203) && ok;
+    tc_fence_after();
+    const int i = tid & 63;
+    unsigned char* dst = tid < 64 ? sm.o1 : sm.y;
+#pragma unroll
+    for (int part = 0; part < 2; ++part) {
+      uint32_t r[32];
+      tmem_ld32(tmem_addr(tm, 32 * warp, 128 + 32 * part), r);
+      tmem_ld_wait();
+      float x[32];
+#pragma unroll
+      for (int j = 0; j < 32; ++j) x[j] = __uint_as_float(r[j]);
+      tile_store_row32(dst, i, 32 * part, x);
+    }
+  }
+  fence_async_smem();
+  tc_fence_before();
+  __syncthreads();
+
+  // ---- MMA 3: W = Ainv a~ (lower lane halves), U = Ainv Y (upper lane halves) -> TMEM columns 0..63
+  if (tid == 0) {
+    tc_fence_after();
+    umma_tile<64, 64, 0, 1>(tmem_addr(tm, 0, 0), smem_u32(sm.ainv), smem_u32(sm.at), false);
+    umma_tile<64, 64, 0, 1>(tmem_addr(tm, 16, 0), smem_u32(sm.ainv), smem_u32(sm.y), false);
+    umma_commit(&sm.bar_m3);
+    bulk_store(out_tiles + S_QT * TILE_BYTES, sm.qt, TILE_BYTES);
+    bulk_store(out_tiles + S_KT * TILE_BYTES, sm.kt, TILE_BYTES);
+    bulk_store(out_tiles + S_BT * TILE_BYTES, sm.bt, TILE_BYTES);
+    bulk_store(out_tiles + S_AQB * TILE_BYTES, sm.aqb, TILE_BYTES);
+    bulk_store(out_tiles + S_O1 * TILE_BYTES, sm.o1, TILE_BYTES);
+    if (keep_for_bwd) bulk_store(out_tiles + S_AINV * TILE_BYTES, sm.ainv, TILE_BYTES);
+    bulk_commit();
+  }
+  ok = mbar_wait(&sm.bar_m3, 0, status, 204) && ok;
+  tc_fence_after();
+  if (tid == 0) bulk_wait_read();   // the A_ak tile is about to be overwritten by W
+  __syncthreads();
+  {
+    const int i = 16 * warp + (lane & 15);
+    unsigned char* dst = lane < 16 ? sm.aak : sm.v;     // W, U (both tiles are free: MMA 2 has completed)
+#pragma unroll
+    for (int part = 0; part < 2; ++part) {
+      uint32_t r[32];
+      tmem_ld32(tmem_addr(tm, 32 * warp, 32 * part), r);
+      tmem_ld_wait();
+      float x[32];
+#pragma unroll
+      for (int j = 0; j < 32; ++j) x[j] = __uint_as_float(r[j]);
+      tile_store_row32(dst, i, 32 * part, x);
+    }
+  }
+  fence_async_smem();
+  tc_fence_before();
+  __syncthreads();
+  if (tid == 0) {
+    bulk_store(out_tiles + S_W * TILE_BYTES, sm.aak, TILE_BYTES);
+    bulk_store(out_tiles + S_U * TILE_BYTES, sm.v, TILE_BYTES);
+    bulk_commit();
+    bulk_wait_all();
+  }
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tm, 256);
+}
+
+// ---------------------------------------------------------------------------------------------
+// scan kernel: grid = B*H, 128 threads, chunks in order, fp32 state in TMEM
+// ---------------------------------------------------------------------------------------------
+struct ScanStage {
+  unsigned char g[FWD_TILES][TILE_BYTES];   // q~, k~, b~, A_qb, O1, W, U (one bulk copy)
+  unsigned char v[TILE_BYTES];              // TMA
+};
+struct ScanSmem {
+  ScanStage st[2];
+  unsigned char ht[TILE_BYTES];             // h~0 as bf16, [k][v]
+  unsigned char sa[TILE_BYTES];             // sa as bf16, [token][v]
+  uint64_t bar_full[2], bar_a, bar_c;
+  uint32_t tmem_base;
+};
+
+__global__ void __launch_bounds__(128)
+r7c_scan_fwd_kernel(const __grid_constant__ CUtensorMap tmap_v, const unsigned char* __restrict__ ws_tiles,
+                    const float* __restrict__ ws_aux, int tiles_per_chunk, unsigned char* __restrict__ bwd_tiles,
+                    const float* __restrict__ h0, int n_state, bf16* __restrict__ o, float* __restrict__ ht,
+                    int Tn, int H, int NT, TokLayout lay, int* status) {
+  extern __shared__ unsigned char smem_raw[];
+  ScanSmem& sm = *reinterpret_cast<ScanSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int unit = blockIdx.x, bi = unit / H, hi = unit % H;
+  const long long base = bi * lay.sb + hi * lay.sh;
+  const size_t ch0 = (size_t)unit * NT;
+  const int row = 16 * warp + (lane & 15);   // state row k (lanes 0-15) or token row i (lanes 16-31)
+  const bool state_lane = lane < 16;
+
+  if (tid == 0) {
+    mbar_init(&sm.bar_full[0], 1); mbar_init(&sm.bar_full[1], 1);
+    mbar_init(&sm.bar_a, 1); mbar_init(&sm.bar_c, 1);
+    fence_mbar_init();
+  }
+  if (warp == 0) tmem_alloc(&sm.tmem_base, 128);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tm = sm.tmem_base;
+  const uint32_t tm_p1 = tmem_addr(tm, 32 * warp, 0), tm_p2 = tmem_addr(tm, 32 * warp, 64);
+
+  auto issue_loads = [&](int c) {
+    ScanStage& s = sm.st[c & 1];
+    mbar_expect_tx(&sm.bar_full[c & 1], (FWD_TILES + 1) * TILE_BYTES);
+    bulk_load(s.g, ws_tiles + (ch0 + c) * (size_t)tiles_per_chunk * TILE_BYTES, FWD_TILES * TILE_BYTES,
+              &sm.bar_full[c & 1]);
+    tma_load_4d(s.v, &tmap_v, &sm.bar_full[c & 1], 0, c * L, hi, bi);
+  };
+  if (tid == 0) {
+    issue_loads(0);
+    if (NT > 1) issue_loads(1);
+  }
+
+  // ---- initial state: h~0 = e^{gref(chunk 0)} h0, fp32 into TMEM (lower lane halves of P2), bf16 into ht
+  {
+    float x[64];
+    if (state_lane) {
+      const float e0 = ws_aux[ch0 * AUX_FLOATS + row];
+      if (n_state > 0) {
+        const float* S = h0 + (size_t)(n_state == 1 ? hi : unit) * 4096;   // S[v][k], h[k][v] = S[v][k]
+#pragma unroll
+        for (int vv = 0; vv < 64; ++vv) x[vv] = e0 * S[vv * 64 + row];
+      } else {
+#pragma unroll
+        for (int vv = 0; vv < 64; ++vv) x[vv] = 0.f;
+      }
+      tile_store_row32(sm.ht, row, 0, x);
+      tile_store_row32(sm.ht, row, 32, x + 32);
+    } else {
+#pragma unroll
+      for (int vv = 0; vv < 64; ++vv) x[vv] = 0.f;
+    }
+    uint32_t r[32];
+#pragma unroll
+    for (int part = 0; part < 2; ++part) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(x[32 * part + j]);
+      tmem_st32(tm_p2 + 32 * part, r);
+    }
+    tmem_st_wait();
+  }
+  fence_async_smem();
+  tc_fence_before();
+  __syncthreads();
+
+  bool ok = true;
+  for (int c = 0; c < NT && ok; ++c) {
+    ScanStage& s = sm.st[c & 1];
+    const int t0 = c * L;
+    // decay factors needed at the end of this chunk, fetched early
+    float scale = 1.f;
+    if (state_lane) {
+      scale = ws_aux[(ch0 + c) * AUX_FLOATS + 64 + row];                       // e^{glast-gref} of this chunk
+      if (c + 1 < NT) scale *= ws_aux[(ch0 + c + 1) * AUX_FLOATS + row];        // e^{gref} of the next chunk
+    }
+    ok = mbar_wait(&sm.bar_full[c & 1], (c >> 1) & 1, status, 211);
+    // (a) SA = W h~0, QH = q~ h~0 (P1);  H += k~^T v (P2 lower)
+    if (tid == 0 && ok) {
+      tc_fence_after();
+      umma_tile<64, 64, 0, 1>(tmem_addr(tm, 0, 0), smem_u32(s.g[S_W]), smem_u32(sm.ht), false);
+      umma_tile<64, 64, 0, 1>(tmem_addr(tm, 16, 0), smem_u32(s.g[S_QT]), smem_u32(sm.ht), false);
+      umma_tile<64, 64, 1, 1>(tmem_addr(tm, 0, 64), smem_u32(s.g[S_KT]), smem_u32(s.v), true);
+      umma_commit(&sm.bar_a);
+    }
+    ok = ok && mbar_wait(&sm.bar_a, c & 1, status, 212);
+    tc_fence_after();
+    float keep[64];     // token lanes: q~ h~0 + O1
+    if (ok) {
+#pragma unroll
+      for (int part = 0; part < 2; ++part) {
+        uint32_t r[32];
+        tmem_ld32(tm_p1 + 32 * part, r);
+        tmem_ld_wait();
+        float add[32];
+        tile_load_row32(state_lane ? s.g[S_U] : s.g[S_O1], row, 32 * part, add);
+#pragma unroll
+        for (int j = 0; j < 32; ++j) keep[32 * part + j] = __uint_as_float(r[j]) + add[j];
+        if (state_lane) tile_store_row32(sm.sa, row, 32 * part, keep + 32 * part);   // sa = W h~0 + U
+      }
+    }
+    fence_async_smem();
+    tc_fence_before();
+    ok = __syncthreads_and(ok);
+    if (bwd_tiles && tid == 0 && ok) {   // the backward needs sa and h~0 of every chunk
+      unsigned char* dst = bwd_tiles + (ch0 + c) * (size_t)tiles_per_chunk * TILE_BYTES;
+      bulk_store(dst + S_SA * TILE_BYTES, sm.sa, TILE_BYTES);
+      bulk_store(dst + S_H0 * TILE_BYTES, sm.ht, TILE_BYTES);
+      bulk_commit();
+    }
+    // (c) H += b~^T sa (P2 lower);  OQ = A_qb sa (P2 upper)
+    if (tid == 0 && ok) {
+      tc_fence_after();
+      umma_tile<64, 64, 1, 1>(tmem_addr(tm, 0, 64), smem_u32(s.g[S_BT]), smem_u32(sm.sa), true);
+      umma_tile<64, 64, 0, 1>(tmem_addr(tm, 16, 64), smem_u32(s.g[S_AQB]), smem_u32(sm.sa), false);
+      umma_commit(&sm.bar_c);
+    }
+    ok = ok && mbar_wait(&sm.bar_c, c & 1, status, 213);
+    tc_fence_after();
+    if (bwd_tiles) {                                  // ht / sa are rewritten below and in the next chunk
+      if (tid == 0) bulk_wait_read();
+      __syncthreads();
+    }
+    if (ok) {
+      const bool last = c + 1 == NT;
+      const int tok = t0 + row;
+#pragma unroll
+      for (int part = 0; part < 2; ++part) {
+        uint32_t r[32];
+        tmem_ld32(tm_p2 + 32 * part, r);
+        tmem_ld_wait();
+        float x[32];
+        if (state_lane) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) { x[j] = __uint_as_float(r[j]) * scale; r[j] = __float_as_uint(x[j]); }
+          if (!last) {
+            tile_store_row32(sm.ht, row, 32 * part, x);
+          } else if (ht) {
+            float* S = ht + (size_t)unit * 4096;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) S[(32 * part + j) * 64 + row] = x[j];
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) x[j] = __uint_as_float(r[j]) + keep[32 * part + j];
+          if (tok < Tn) {
+            bf16* dst = o + base + (long long)tok * lay.st + 32 * part;
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              uint4 u;
+              u.x = pack_bf16(x[j], x[j + 1]); u.y = pack_bf16(x[j + 2], x[j + 3]);
+              u.z = pack_bf16(x[j + 4], x[j + 5]); u.w = pack_bf16(x[j + 6], x[j + 7]);
+              *reinterpret_cast<uint4*>(dst + j) = u;
+            }
+          }
+        }
+        tmem_st32(tm_p2 + 32 * part, r);   // state lanes: rescaled state; token lanes: unchanged
+      }
+      tmem_st_wait();
+    }
+    fence_async_smem();
+    tc_fence_before();
+    ok = __syncthreads_and(ok);
+    if (tid == 0 && ok && c + 2 < NT) issue_loads(c + 2);
+  }
+  if (tid == 0) bulk_wait_all();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tm, 128);
+}
+
+}  // namespace r7c
+
+int launch_rwkv7_chunked_fwd(const void* r, const void* w, const void* k, const void* v, const void* a, const void* b,
+                             const float* h0, int n_state, void* o, float* ht, void* workspace,
+                             int B, int Tn, int H, int head_first, bool keep_for_bwd, cudaStream_t st) {
+  using namespace r7c;
+  typedef __nv_bfloat16 bf16;
+  int* status = device_status_ptr();
+  if (!status) return RWKVB200_E_CUDA;
+  CUtensorMap tmap_v;
+  int e = make_token_tensor_map(&tmap_v, v, B, Tn, H, head_first);
+  if (e) return e;
+  const int NT = num_chunks(Tn);
+  const int tpc = keep_for_bwd ? (int)ALL_TILES : (int)FWD_TILES;
+  Workspace ws = carve(workspace, B, Tn, H, tpc);
+  TokLayout lay(Tn, H, head_first);
+  {
+    const int smem = (int)sizeof(IntraSmem) + 1024;
+    if (cudaFuncSetAttribute(r7c_intra_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+      return RWKVB200_E_CUDA;
+    ProfScope prof("r7c_intra_fwd_kernel", st);
+    r7c_intra_fwd_kernel<<<B * H * NT, 128, smem, st>>>((const bf16*)r, (const bf16*)w, (const bf16*)k, (const bf16*)a,
+                                                         (const bf16*)b, tmap_v, ws.tiles, ws.aux, tpc,
+                                                         keep_for_bwd ? 1 : 0, Tn, H, NT, lay, status);
+  }
+  e = check_launch();
+  if (e) return e;
+  {
+    const int smem = (int)sizeof(ScanSmem) + 1024;
+    if (cudaFuncSetAttribute(r7c_scan_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+      return RWKVB200_E_CUDA;
+    ProfScope prof("r7c_scan_fwd_kernel", st);
+    r7c_scan_fwd_kernel<<<B * H, 128, smem, st>>>(tmap_v, ws.tiles, ws.aux, tpc, keep_for_bwd ? ws.tiles : nullptr,
+                                                  h0, n_state, (bf16*)o, ht, Tn, H, NT, lay, status);
+  }
+  return check_launch();
+}
+
+}  // namespace rwkvb200

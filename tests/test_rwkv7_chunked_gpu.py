@@ -1,0 +1,57 @@
+"""The chunked tcgen05 path of the RWKV7 delta rule (bf16 tokens) against the float32 CPU oracle.
+Tolerance: relative L2 <= 2e-2 per tensor (the bar for bf16 inputs), and no bounded wait may run out."""
+import pytest
+import torch
+
+import rwkv_ops_b200 as ro
+from oracle import generalized_delta_rule as oracle_gdr
+from rwkv_ops_b200 import _lib
+from rwkv_ops_b200.workloads import rwkv7_inputs, rel_l2
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(autouse=True)
+def _chunked(monkeypatch):
+    monkeypatch.setenv("RWKV_OPS_B200_RWKV7_ALGO", "chunked")
+    yield
+    torch.cuda.synchronize()
+    assert _lib.load().rwkvb200_device_status(1) == 0, "a bounded wait ran out inside a tensor-core kernel"
+
+
+@pytest.mark.parametrize("T", [64, 128, 17, 65, 130, 257])
+@pytest.mark.parametrize("state", [False, True])
+def test_forward_vs_oracle(T, state):
+    B, H = 2, 3
+    d = rwkv7_inputs(B, T, H, dtype=torch.bfloat16, seed=700 + T, with_state=state)
+    h0 = d.get("initial_state")
+    o_ref, s_ref = oracle_gdr(*[d[n] for n in "rwkvab"], initial_state=h0)
+    with torch.no_grad():
+        o, s = ro.generalized_delta_rule(*[d[n].cuda() for n in "rwkvab"],
+                                         initial_state=None if h0 is None else h0.cuda())
+    assert o.dtype == torch.bfloat16 and s.dtype == torch.float32
+    assert rel_l2(o, o_ref) < 2e-2, rel_l2(o, o_ref)
+    assert rel_l2(s, s_ref) < 2e-2, rel_l2(s, s_ref)
+
+
+def test_forward_head_first_and_broadcast_state():
+    B, T, H = 2, 100, 2
+    d = rwkv7_inputs(B, T, H, dtype=torch.bfloat16, seed=71, with_state=True, n_state=1)
+    o_ref, s_ref = oracle_gdr(*[d[n] for n in "rwkvab"], initial_state=d["initial_state"])
+    with torch.no_grad():
+        o, s = ro.generalized_delta_rule(*[d[n].cuda().permute(0, 2, 1, 3).contiguous() for n in "rwkvab"],
+                                         initial_state=d["initial_state"].cuda(), head_first=True)
+    assert rel_l2(o.permute(0, 2, 1, 3), o_ref) < 2e-2 and rel_l2(s, s_ref) < 2e-2
+
+
+def test_forward_full_size_sampled_units():
+    """Configuration 1 (bf16, B8 T4096 H32) at full size against the oracle on sampled units."""
+    B, T, H = 8, 4096, 32
+    d = rwkv7_inputs(B, T, H, dtype=torch.bfloat16, seed=1001, device="cuda")
+    with torch.no_grad():
+        o, s = ro.generalized_delta_rule(*[d[n] for n in "rwkvab"])
+    for (b, h) in [(0, 0), (3, 17), (7, 31)]:
+        sub = [d[n][b:b + 1, :, h:h + 1].cpu() for n in "rwkvab"]
+        o_ref, s_ref = oracle_gdr(*sub)
+        assert rel_l2(o[b:b + 1, :, h:h + 1], o_ref) < 2e-2
+        assert rel_l2(s[b:b + 1, h:h + 1], s_ref) < 2e-2
