@@ -178,6 +178,9 @@ int rwkvb200_wkv6_bwd(const void* r, const void* k, const void* v, const void* w
  *   second copy after a bulk load of the first.
  * ---------------------------------------------------------------------------------------- */
 int rwkvb200_device_status(int reset);
+/* Developer aid: while device_buffer (>= 64 int64, caller-owned) is installed, one CTA of each
+ * tensor-core kernel writes clock64() stamps at its phase boundaries into it; NULL switches it off. */
+void rwkvb200_debug_stamps(void* device_buffer);
 int rwkvb200_tc_selftest(int mode, const void* X, const void* Y, const void* Z, const void* W, float* out,
                          const void* tok, int B, int T, int H, int b, int t0, int h, void* img, void* stream);
 

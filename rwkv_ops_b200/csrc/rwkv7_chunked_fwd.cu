@@ -36,7 +36,8 @@ r7c_intra_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ w, con
                      const bf16* __restrict__ a, const bf16* __restrict__ b,
                      const __grid_constant__ CUtensorMap tmap_v, unsigned char* __restrict__ ws_tiles,
                      float* __restrict__ ws_aux, int tiles_per_chunk, int keep_for_bwd,
-                     int Tn, int H, int NT, TokLayout lay, int* status) {
+                     int Tn, int H, int NT, TokLayout lay, int* status, long long* dbg) {
+#define R7C_STAMP(n) do { if (dbg && tid == 0 && blockIdx.x == gridDim.x / 2) dbg[n] = clock64(); } while (0)
   extern __shared__ unsigned char smem_raw[];
   IntraSmem& sm = *reinterpret_cast<IntraSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -59,49 +60,102 @@ r7c_intra_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ w, con
     tma_load_4d(sm.v, &tmap_v, &sm.bar_v, 0, t0, hi, bi);
   }
 
-  // ---- phase A: decay prefix sums and the four scaled operands.  Thread = (channel, half of the chunk)
+  R7C_STAMP(0);
+  // ---- phase A: decay prefix sums and the four scaled operands.
+  // 16-byte loads (8 channels of one token), all in flight at once; the prefix sum over tokens goes
+  // through shared memory (the fp32 area that later holds A_ab).
   {
-    const int c = tid & 63, half = tid >> 6;
-    float gl[32];
-    float run = 0.f;
+    float* gs = sm.nmat;
+    uint4 rw[4], rq[4], rk[4], ra[4], rb[4];
+    const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
-    for (int j = 0; j < 32; ++j) {
-      const int tok = t0 + 32 * half + j;
-      float g = 0.f;
-      if (tok < Tn) g = -expf(__bfloat162float(w[base + (long long)tok * lay.st + c]));
-      run += g;
-      gl[j] = run;
+    for (int n = 0; n < 4; ++n) {
+      const int e = tid + 128 * n, row = e >> 3, cc = e & 7, tok = t0 + row;
+      const long long off = base + (long long)tok * lay.st + 8 * cc;
+      const bool valid = tok < Tn;
+      rw[n] = valid ? __ldg(reinterpret_cast<const uint4*>(w + off)) : zero4;
+      rq[n] = valid ? __ldg(reinterpret_cast<const uint4*>(q + off)) : zero4;
+      rk[n] = valid ? __ldg(reinterpret_cast<const uint4*>(k + off)) : zero4;
+      ra[n] = valid ? __ldg(reinterpret_cast<const uint4*>(a + off)) : zero4;
+      rb[n] = valid ? __ldg(reinterpret_cast<const uint4*>(b + off)) : zero4;
     }
-    sm.tot[half][c] = run;
-    __syncthreads();
-    const float tot0 = sm.tot[0][c], tot1 = sm.tot[1][c];
-    if (half == 0) {
-      ws_aux[(size_t)ch * AUX_FLOATS + c] = __expf(fmaxf(tot0, -EXP_CLAMP));        // e^{gref}
-      ws_aux[(size_t)ch * AUX_FLOATS + 64 + c] = __expf(fmaxf(tot1, -EXP_CLAMP));   // e^{glast-gref}
-    }
-    const float shift = half ? 0.f : tot0;    // gi - gref = gl - shift
-#pragma unroll 8
-    for (int j = 0; j < 32; ++j) {
-      const int i = 32 * half + j, tok = t0 + i;
-      float qv = 0.f, kv = 0.f, av = 0.f, bv = 0.f;
-      if (tok < Tn) {
-        const long long off = base + (long long)tok * lay.st + c;
-        qv = __bfloat162float(q[off]); kv = __bfloat162float(k[off]);
-        av = __bfloat162float(a[off]); bv = __bfloat162float(b[off]);
+#pragma unroll
+    for (int n = 0; n < 4; ++n) {
+      const int e = tid + 128 * n, row = e >> 3, cc = e & 7;
+      const bool valid = t0 + row < Tn;
+      const uint32_t u[4] = {rw[n].x, rw[n].y, rw[n].z, rw[n].w};
+      float g[8];
+#pragma unroll
+      for (int m = 0; m < 4; ++m) {
+        g[2 * m] = valid ? -expf(bf16_lo(u[m])) : 0.f;
+        g[2 * m + 1] = valid ? -expf(bf16_hi(u[m])) : 0.f;
       }
-      const float d1 = gl[j] - shift;                       // gi - gref
-      const float gj = gl[j] - (j ? gl[j - 1] : 0.f);       // g of this token
-      const float eq = cexp(d1), ek = cexp(-d1), ea = cexp(d1 - gj);
-      const uint32_t off = tile_off(i, c);
-      *reinterpret_cast<bf16*>(sm.qt + off) = __float2bfloat16_rn(qv * eq);
-      *reinterpret_cast<bf16*>(sm.kt + off) = __float2bfloat16_rn(kv * ek);
-      *reinterpret_cast<bf16*>(sm.at + off) = __float2bfloat16_rn(av * ea);
-      *reinterpret_cast<bf16*>(sm.bt + off) = __float2bfloat16_rn(bv * ek);
+      *reinterpret_cast<float4*>(&gs[row * NROW + 8 * cc]) = make_float4(g[0], g[1], g[2], g[3]);
+      *reinterpret_cast<float4*>(&gs[row * NROW + 8 * cc + 4]) = make_float4(g[4], g[5], g[6], g[7]);
+    }
+    __syncthreads();
+    R7C_STAMP(1);
+    {
+      const int c = tid & 63, half = tid >> 6;
+      float gv[32];
+#pragma unroll
+      for (int j = 0; j < 32; ++j) gv[j] = gs[(32 * half + j) * NROW + c];
+      float run = 0.f;
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        run += gv[j];
+        gs[(32 * half + j) * NROW + c] = run;   // inclusive prefix inside this half of the chunk
+      }
+      sm.tot[half][c] = run;
+    }
+    __syncthreads();
+    if (tid < 64) {
+      ws_aux[(size_t)ch * AUX_FLOATS + tid] = __expf(fmaxf(sm.tot[0][tid], -EXP_CLAMP));        // e^{gref}
+      ws_aux[(size_t)ch * AUX_FLOATS + 64 + tid] = __expf(fmaxf(sm.tot[1][tid], -EXP_CLAMP));   // e^{glast-gref}
+    }
+#pragma unroll
+    for (int n = 0; n < 4; ++n) {
+      const int e = tid + 128 * n, row = e >> 3, cc = e & 7;
+      const bool valid = t0 + row < Tn;
+      const bool first_half = row < 32;
+      float gl[8], sh[8];
+      *reinterpret_cast<float4*>(gl) = *reinterpret_cast<const float4*>(&gs[row * NROW + 8 * cc]);
+      *reinterpret_cast<float4*>(gl + 4) = *reinterpret_cast<const float4*>(&gs[row * NROW + 8 * cc + 4]);
+      *reinterpret_cast<float4*>(sh) = *reinterpret_cast<const float4*>(&sm.tot[0][8 * cc]);
+      *reinterpret_cast<float4*>(sh + 4) = *reinterpret_cast<const float4*>(&sm.tot[0][8 * cc + 4]);
+      const uint32_t uw[4] = {rw[n].x, rw[n].y, rw[n].z, rw[n].w};
+      const uint32_t uq[4] = {rq[n].x, rq[n].y, rq[n].z, rq[n].w};
+      const uint32_t uk[4] = {rk[n].x, rk[n].y, rk[n].z, rk[n].w};
+      const uint32_t ua[4] = {ra[n].x, ra[n].y, ra[n].z, ra[n].w};
+      const uint32_t ub[4] = {rb[n].x, rb[n].y, rb[n].z, rb[n].w};
+      uint32_t oq[4], ok_[4], oa[4], ob[4];
+#pragma unroll
+      for (int m = 0; m < 4; ++m) {
+        float eq[2], ek[2], ea[2];
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+          const int x = 2 * m + hh;
+          const float d1 = gl[x] - (first_half ? sh[x] : 0.f);          // gi - gref
+          const float wv = hh ? bf16_hi(uw[m]) : bf16_lo(uw[m]);
+          const float gj = valid ? -__expf(wv) : 0.f;                    // g of this token
+          eq[hh] = cexp(d1); ek[hh] = cexp(-d1); ea[hh] = cexp(d1 - gj);
+        }
+        oq[m] = pack_bf16(bf16_lo(uq[m]) * eq[0], bf16_hi(uq[m]) * eq[1]);
+        ok_[m] = pack_bf16(bf16_lo(uk[m]) * ek[0], bf16_hi(uk[m]) * ek[1]);
+        oa[m] = pack_bf16(bf16_lo(ua[m]) * ea[0], bf16_hi(ua[m]) * ea[1]);
+        ob[m] = pack_bf16(bf16_lo(ub[m]) * ek[0], bf16_hi(ub[m]) * ek[1]);
+      }
+      const uint32_t off = tile_chunk_off(row, cc);
+      *reinterpret_cast<uint4*>(sm.qt + off) = make_uint4(oq[0], oq[1], oq[2], oq[3]);
+      *reinterpret_cast<uint4*>(sm.kt + off) = make_uint4(ok_[0], ok_[1], ok_[2], ok_[3]);
+      *reinterpret_cast<uint4*>(sm.at + off) = make_uint4(oa[0], oa[1], oa[2], oa[3]);
+      *reinterpret_cast<uint4*>(sm.bt + off) = make_uint4(ob[0], ob[1], ob[2], ob[3]);
     }
   }
   fence_async_smem();
   __syncthreads();
 
+  R7C_STAMP(2);
   // ---- MMA 1: [q~; a~] [k~; b~]^T  ->  TMEM columns 0..127, row r on lane r
   if (tid == 0) {
     tc_fence_after();
@@ -110,6 +164,7 @@ r7c_intra_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ w, con
   }
   bool ok = mbar_wait(&sm.bar_m1, 0, status, 201);
   tc_fence_after();
+  R7C_STAMP(3);
   if (ok) {
     const int i = tid & 63;
     const bool lower = tid >= 64;       // rows of a~: strictly lower triangle; rows of q~: lower incl. diagonal
@@ -140,6 +195,7 @@ r7c_intra_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ w, con
   tc_fence_before();
   __syncthreads();
 
+  R7C_STAMP(4);
   // ---- MMA 2: [A_qk; A_ak] v  ->  TMEM columns 128..191 (rows 0..63 = O1, 64..127 = Y)
   if (tid == 0) {
     ok = mbar_wait(&sm.bar_v, 0, status, 202);
@@ -154,23 +210,42 @@ r7c_intra_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ w, con
     }
   }
   if (tid < 64) {
-    // ---- Ainv = (I - stril(A_ab))^-1 by forward substitution, one column per thread, fp32
+    // ---- Ainv = (I - stril(A_ab))^-1 by forward substitution, one column per thread, fp32.
+    // Rows are taken four at a time: the sums over earlier rows are independent chains (their loads
+    // and multiply-adds overlap), then a 4x4 triangular fix-up couples the four new entries.
     const int c = tid;
     float X[64];
 #pragma unroll
-    for (int i = 0; i < 64; ++i) X[i] = 0.f;
+    for (int ib = 0; ib < 16; ++ib) {
+      const int i0 = 4 * ib;
+      float acc[4][4];
 #pragma unroll
-    for (int i = 0; i < 64; ++i) {
-      float a0 = (i == c) ? 1.f : 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
-#pragma unroll
-      for (int jj = 0; jj < (i + 3) / 4; ++jj) {
-        const float4 n = *reinterpret_cast<const float4*>(&sm.nmat[i * NROW + 4 * jj]);
-        a0 += n.x * X[4 * jj]; a1 += n.y * X[4 * jj + 1]; a2 += n.z * X[4 * jj + 2]; a3 += n.w * X[4 * jj + 3];
+      for (int rr = 0; rr < 4; ++rr) {
+        acc[rr][0] = (i0 + rr == c) ? 1.f : 0.f;
+        acc[rr][1] = acc[rr][2] = acc[rr][3] = 0.f;
       }
-      X[i] = (a0 + a1) + (a2 + a3);
-      *reinterpret_cast<bf16*>(sm.ainv + tile_off(i, c)) = __float2bfloat16_rn(X[i]);
+#pragma unroll
+      for (int jj = 0; jj < ib; ++jj) {
+#pragma unroll
+        for (int rr = 0; rr < 4; ++rr) {
+          const float4 n = *reinterpret_cast<const float4*>(&sm.nmat[(i0 + rr) * NROW + 4 * jj]);
+          acc[rr][0] += n.x * X[4 * jj]; acc[rr][1] += n.y * X[4 * jj + 1];
+          acc[rr][2] += n.z * X[4 * jj + 2]; acc[rr][3] += n.w * X[4 * jj + 3];
+        }
+      }
+      const float4 n1 = *reinterpret_cast<const float4*>(&sm.nmat[(i0 + 1) * NROW + i0]);
+      const float4 n2 = *reinterpret_cast<const float4*>(&sm.nmat[(i0 + 2) * NROW + i0]);
+      const float4 n3 = *reinterpret_cast<const float4*>(&sm.nmat[(i0 + 3) * NROW + i0]);
+      X[i0] = (acc[0][0] + acc[0][1]) + (acc[0][2] + acc[0][3]);
+      X[i0 + 1] = (acc[1][0] + acc[1][1]) + (acc[1][2] + acc[1][3]) + n1.x * X[i0];
+      X[i0 + 2] = (acc[2][0] + acc[2][1]) + (acc[2][2] + acc[2][3]) + n2.x * X[i0] + n2.y * X[i0 + 1];
+      X[i0 + 3] = (acc[3][0] + acc[3][1]) + (acc[3][2] + acc[3][3]) + n3.x * X[i0] + n3.y * X[i0 + 1] + n3.z * X[i0 + 2];
+#pragma unroll
+      for (int rr = 0; rr < 4; ++rr)
+        *reinterpret_cast<bf16*>(sm.ainv + tile_off(i0 + rr, c)) = __float2bfloat16_rn(X[i0 + rr]);
     }
   }
+  R7C_STAMP(5);
   {
     // rows of MMA 2: threads 0..63 take O1 (after the inverse), threads 64..127 take Y
     ok = mbar_wait(&sm.bar_m2, 0, status, 203) && ok;
@@ -192,6 +267,7 @@ r7c_intra_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ w, con
   tc_fence_before();
   __syncthreads();
 
+  R7C_STAMP(6);
   // ---- MMA 3: W = Ainv a~ (lower lane halves), U = Ainv Y (upper lane halves) -> TMEM columns 0..63
   if (tid == 0) {
     tc_fence_after();
@@ -208,6 +284,7 @@ r7c_intra_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ w, con
   }
   ok = mbar_wait(&sm.bar_m3, 0, status, 204) && ok;
   tc_fence_after();
+  R7C_STAMP(7);
   if (tid == 0) bulk_wait_read();   // the A_ak tile is about to be overwritten by W
   __syncthreads();
   {
@@ -227,6 +304,7 @@ r7c_intra_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ w, con
   fence_async_smem();
   tc_fence_before();
   __syncthreads();
+  R7C_STAMP(8);
   if (tid == 0) {
     bulk_store(out_tiles + S_W * TILE_BYTES, sm.aak, TILE_BYTES);
     bulk_store(out_tiles + S_U * TILE_BYTES, sm.v, TILE_BYTES);
@@ -234,7 +312,9 @@ r7c_intra_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ w, con
     bulk_wait_all();
   }
   __syncthreads();
+  R7C_STAMP(9);
   if (warp == 0) tmem_dealloc(tm, 256);
+#undef R7C_STAMP
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -449,7 +529,8 @@ int launch_rwkv7_chunked_fwd(const void* r, const void* w, const void* k, const 
     ProfScope prof("r7c_intra_fwd_kernel", st);
     r7c_intra_fwd_kernel<<<B * H * NT, 128, smem, st>>>((const bf16*)r, (const bf16*)w, (const bf16*)k, (const bf16*)a,
                                                          (const bf16*)b, tmap_v, ws.tiles, ws.aux, tpc,
-                                                         keep_for_bwd ? 1 : 0, Tn, H, NT, lay, status);
+                                                         keep_for_bwd ? 1 : 0, Tn, H, NT, lay, status,
+                                                         debug_stamp_buffer());
   }
   e = check_launch();
   if (e) return e;

@@ -256,4 +256,8 @@ int make_token_tensor_map(CUtensorMap* out, const void* base, int B, int T, int 
 // ran out; nullptr if the lookup failed.  Read and cleared by rwkvb200_device_status().
 int* device_status_ptr();
 
+// Optional device buffer (>= 64 long long) that kernels fill with clock64() stamps at their phase
+// boundaries (one designated CTA); nullptr unless a developer installed one.
+long long* debug_stamp_buffer();
+
 }  // namespace rwkvb200

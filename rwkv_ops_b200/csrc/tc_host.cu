@@ -51,6 +51,9 @@ int make_token_tensor_map(CUtensorMap* out, const void* base, int B, int T, int 
   return r == CUDA_SUCCESS ? RWKVB200_OK : RWKVB200_E_CUDA;
 }
 
+static long long* g_stamp_buffer = nullptr;
+long long* debug_stamp_buffer() { return g_stamp_buffer; }
+
 int* device_status_ptr() {
   int dev = -1;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
@@ -171,6 +174,8 @@ tc_selftest_kernel(int mode, const __nv_bfloat16* X, const __nv_bfloat16* Y, con
 using namespace rwkvb200;
 
 extern "C" {
+
+void rwkvb200_debug_stamps(void* device_buffer) { g_stamp_buffer = reinterpret_cast<long long*>(device_buffer); }
 
 int rwkvb200_device_status(int reset) {
   int* p = device_status_ptr();
