@@ -59,6 +59,8 @@ enum {
 
 int rwkvb200_abi_version(void);
 const char* rwkvb200_strerror(int code);
+/* Text of the last CUDA runtime error behind a RWKVB200_E_CUDA return ("no error" if none). */
+const char* rwkvb200_last_cuda_error(void);
 
 /* ------------------------------------------------------------------------------------------
  * RWKV7 generalized delta rule.
@@ -175,7 +177,9 @@ int rwkvb200_wkv6_bwd(const void* r, const void* k, const void* v, const void* w
  *   mode 1: dumps the 128-lane x 64-column accumulator block holding X*Z (lower lane halves) and
  *   X^T*W (upper lane halves) to out[128][64]; mode 2: TMA-loads the 64-token tile (b,t0,h) of the
  *   [B,T,H,64] bf16 tensor tok, and writes its shared-memory image twice to img (2 x 4096 bf16), the
- *   second copy after a bulk load of the first.
+ *   second copy after a bulk load of the first; mode 3: out[128][64] = [X^T; Y^T] Z (128-wide
+ *   transposed A operand); mode 4: lanes' lower halves of out[128][64] = X^T Z + Y^T W (contraction
+ *   length 128 over two adjacent tiles).
  * ---------------------------------------------------------------------------------------- */
 int rwkvb200_device_status(int reset);
 /* Developer aid: while device_buffer (>= 64 int64, caller-owned) is installed, one CTA of each

@@ -23,6 +23,7 @@ _P, _I, _Z = c_void_p, c_int, c_size_t
 SIGNATURES = {
     "rwkvb200_abi_version": (c_int, []),
     "rwkvb200_strerror": (c_char_p, [_I]),
+    "rwkvb200_last_cuda_error": (c_char_p, []),
     "rwkvb200_rwkv7_step": (c_int, [_P] * 6 + [_P, _I, _P, _P, _I, _I, _I, _I, _P]),
     "rwkvb200_rwkv7_fwd_workspace_bytes": (c_size_t, [_I] * 6),
     "rwkvb200_rwkv7_fwd": (c_int, [_P] * 6 + [_P, _I, _P, _P, _P, _Z] + [_I] * 7 + [_P]),
@@ -79,6 +80,8 @@ def check(code: int, what: str) -> None:
     if code == 0:
         return
     msg = f"{what}: {strerror(code)} (code {code})"
+    if code == -7:
+        msg += f": {load().rwkvb200_last_cuda_error().decode()}"
     if code in (-1, -2, -3, -4, -6, -8, -9):
         raise ValueError(msg)
     raise RwkvB200Error(msg)

@@ -107,6 +107,7 @@ size_t rwkvb200_rwkv7_bwd_workspace_bytes(int B, int T, int H, int head_size, in
   if (check_common(B, T, H, head_size, dtype)) return 0;
   switch (resolve_r7_algo(algo, dtype)) {
     case RWKVB200_ALGO_RECURRENT: return r7_ckpt_bytes(B, T, H);
+    case RWKVB200_ALGO_CHUNKED: return r7c::fwd_workspace_bytes(B, T, H, r7c::ALL_TILES);
     default: return 0;
   }
 }
@@ -138,6 +139,10 @@ int rwkvb200_rwkv7_bwd(const void* r, const void* w, const void* k, const void* 
       return launch_rwkv7_rec_bwd(r, w, k, v, a, b, d_o, d_ht, ckpt, dr, dw, dk, dv, da, db, d_h0,
                                   B, T, H, dtype, head_first, st);
     }
+    case RWKVB200_ALGO_CHUNKED:
+      if (dtype != RWKVB200_BF16) return RWKVB200_E_UNSUPPORTED;
+      return launch_rwkv7_chunked_bwd(r, w, k, v, a, b, n_state ? h0 : nullptr, n_state, d_o, d_ht,
+                                      dr, dw, dk, dv, da, db, d_h0, workspace, B, T, H, head_first, st);
     default:
       return RWKVB200_E_UNSUPPORTED;
   }

@@ -79,10 +79,16 @@ struct TokLayout {
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
-inline int check_launch() {
-  cudaError_t e = cudaGetLastError();
-  return e == cudaSuccess ? RWKVB200_OK : RWKVB200_E_CUDA;
+// Last CUDA runtime error seen by this library (cudaSuccess if none); see rwkvb200_last_cuda_error().
+int& last_cuda_error_slot();
+
+inline int cuda_ok(cudaError_t e) {
+  if (e == cudaSuccess) return RWKVB200_OK;
+  last_cuda_error_slot() = (int)e;
+  return RWKVB200_E_CUDA;
 }
+
+inline int check_launch() { return cuda_ok(cudaGetLastError()); }
 
 // Brackets one kernel launch with timing events when profiling is on (see profile.cu).
 struct ProfScope {

@@ -2,6 +2,7 @@
 // bracketed by a pair of CUDA events recorded on the launch stream, and the totals per kernel name
 // can be read back after a synchronize.  Disabled by default (zero overhead beyond one branch).
 // Events are host-side driver objects; no device memory is allocated here.
+#include <stdio.h>
 #include <string.h>
 
 #include <mutex>
@@ -11,6 +12,11 @@
 #include "common.cuh"
 
 namespace rwkvb200 {
+
+int& last_cuda_error_slot() {
+  static int e = 0;
+  return e;
+}
 
 namespace {
 struct Rec { int name; cudaEvent_t a, b; };
@@ -54,6 +60,15 @@ ProfScope::~ProfScope() {
 using namespace rwkvb200;
 
 extern "C" {
+
+const char* rwkvb200_last_cuda_error(void) {
+  static char buf[96];
+  const int e = last_cuda_error_slot();
+  if (e < 99999) return cudaGetErrorString((cudaError_t)e);
+  if (e == 99999) return "device status word not available";
+  snprintf(buf, sizeof(buf), "cuTensorMapEncodeTiled failed with CUresult %d", e - 100000);
+  return buf;
+}
 
 void rwkvb200_profile_enable(int on) {
   std::lock_guard<std::mutex> lk(g_mu);

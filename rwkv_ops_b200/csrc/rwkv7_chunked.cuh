@@ -11,6 +11,19 @@
 //     sa  = W h~0 + U                       (rows a_i^T h_{i-1})
 //     o   = q~ h~0 + O1 + A_qb sa
 //     h_L = diag(e^{glast-gref}) (h~0 + k~^T v + b~^T sa)
+// Backward (do = grad of o, dh_L = grad of the state after the chunk, gref held constant: the result
+// does not depend on it):
+//     dh^  = diag(e^{glast-gref}) dh_L
+//     dz   = Ainv^T (A_qb^T do + b~ dh^)  = P2 + B2 dh^          (z = a~ h~0 + A_ak v,  sa = Ainv z)
+//     dh~0 = q~^T do + a~^T dz + dh^,   dh0 = diag(e^{gref}) dh~0
+//     dv   = A_qk^T do + A_ak^T dz + k~ dh^
+//     dA_qk = tril(do v^T)  dA_qb = tril(do sa^T)  dA_ak = stril(dz v^T)  dA_ab = stril(dz sa^T)
+//     dq~ = do h~0^T + dA_qk k~ + dA_qb b~        da~ = dz h~0^T + dA_ak k~ + dA_ab b~
+//     dk~ = dA_qk^T q~ + dA_ak^T a~ + v dh^^T     db~ = dA_qb^T q~ + dA_ab^T a~ + sa dh^^T
+//     dq = dq~ e^{gi-gref} ...;  dgi = dq~ q~ - dk~ k~ - db~ b~;  dge = da~ a~;  dglast = sum_v dh^ X
+//     dg_j = sum_{i>=j} (dgi_i + dge_i) - dge_j + dglast;   dw = dg g
+// (reference: chunk_o_bwd.py:111-113,246-277,364-381, chunk_h_bwd.py:141-157, wy_fast_bwd.py:99-193,
+// chunk_A_bwd.py:146-250,318-320 under rwkv_ops/rwkv7_kernel/triton_kernel/).
 // These are the chunk equations of the reference's kernels (rwkv_ops/rwkv7_kernel/triton_kernel/
 // chunk_A_fwd.py:111-165, wy_fast_fwd.py:57-62,273-321, chunk_h_fwd.py:140-150, chunk_o_fwd.py:82-136)
 // rewritten around one reference point per chunk so that all four A matrices come out of a single
@@ -31,7 +44,12 @@ namespace r7c {
 constexpr int L = 64;                 // chunk length
 // tiles of one chunk in the workspace, in this order (the first FWD_TILES feed the forward scan)
 enum Slot { S_QT = 0, S_KT, S_BT, S_AQB, S_O1, S_W, S_U, FWD_TILES,
-            S_AT = FWD_TILES, S_AQK, S_AAK, S_AINV, S_SA, S_H0, ALL_TILES };
+            // kept for the backward: a~, A_qk, A_ak, Ainv (intra kernel); sa, h~0 and
+            // X = h~0 + k~^T v + b~^T sa (forward scan)
+            S_AT = FWD_TILES, S_AQK, S_AAK, S_AINV, S_SA, S_H0, S_X,
+            // backward intermediates: B2 = Ainv^T b~, P2 = Ainv^T A_qb^T do (adjacent), then
+            // dz = Ainv^T dsa and dh^ = e^{glast-gref} dh_L written by the reverse scan
+            S_B2, S_P2, S_DZ, S_DHH, ALL_TILES };
 constexpr int AUX_FLOATS = 128;       // per chunk: e^{gref}[64], e^{glast-gref}[64]
 
 inline int num_chunks(int T) { return (T + L - 1) / L; }
@@ -60,6 +78,12 @@ inline Workspace carve(void* ws, int B, int T, int H, int tiles_per_chunk) {
 }
 
 }  // namespace r7c
+
+// Backward of the chunked path; `workspace` must hold fwd_workspace_bytes(B, T, H, ALL_TILES).
+int launch_rwkv7_chunked_bwd(const void* r, const void* w, const void* k, const void* v, const void* a, const void* b,
+                             const float* h0, int n_state, const void* d_o, const float* d_ht,
+                             void* dr, void* dw, void* dk, void* dv, void* da, void* db, float* d_h0,
+                             void* workspace, int B, int Tn, int H, int head_first, cudaStream_t st);
 
 int launch_rwkv7_chunked_fwd(const void* r, const void* w, const void* k, const void* v, const void* a, const void* b,
                              const float* h0, int n_state, void* o, float* ht, void* workspace,

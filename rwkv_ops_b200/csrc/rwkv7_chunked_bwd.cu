@@ -1,0 +1,557 @@
+// Chunked RWKV7 backward on tcgen05 (bf16 token tensors).  Equations in rwkv7_chunked.cuh.
+//
+// Launch sequence (all on the caller's stream, tiles exchanged through the workspace):
+//   1. forward intra kernel with keep_for_bwd (q~, k~, b~, a~, A_qk, A_ak, A_qb, Ainv, W, U, decay factors)
+//   2. forward scan without output, keeping sa, h~0 and X of every chunk
+//   3. r7c_bwd_pre_kernel    (parallel over chunks)   B2 = Ainv^T b~,  P2 = Ainv^T A_qb^T do
+//   4. r7c_bwd_scan_kernel   (one CTA per (b,h), chunks in reverse)  dz, dh^ per chunk, d initial state
+//   5. r7c_bwd_final_kernel  (parallel over chunks)   dq, dk, dv, da, db, dw
+#include "rwkv7_chunked.cuh"
+
+namespace rwkvb200 {
+namespace r7c {
+
+using namespace tc;
+typedef __nv_bfloat16 bf16;
+
+constexpr float EXP_CLAMP = 80.f;
+__device__ __forceinline__ float cexp(float x) { return __expf(fminf(fmaxf(x, -EXP_CLAMP), EXP_CLAMP)); }
+constexpr int NROW = 68;
+
+__device__ __forceinline__ void store_row32_global(bf16* dst, const float* x) {
+#pragma unroll
+  for (int j = 0; j < 32; j += 8) {
+    uint4 u;
+    u.x = pack_bf16(x[j], x[j + 1]); u.y = pack_bf16(x[j + 2], x[j + 3]);
+    u.z = pack_bf16(x[j + 4], x[j + 5]); u.w = pack_bf16(x[j + 6], x[j + 7]);
+    *reinterpret_cast<uint4*>(dst + j) = u;
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// 3. B2 = Ainv^T b~ and P2 = Ainv^T (A_qb^T do): grid = B*H*NT, 128 threads
+// ---------------------------------------------------------------------------------------------
+struct PreSmem {
+  unsigned char ainv[TILE_BYTES], bt[TILE_BYTES], aqb[TILE_BYTES], dout[TILE_BYTES];
+  unsigned char p1[TILE_BYTES], b2[TILE_BYTES], p2[TILE_BYTES];
+  uint64_t bar_ld, bar_m1, bar_m2;
+  uint32_t tmem_base;
+};
+
+__global__ void __launch_bounds__(128)
+r7c_bwd_pre_kernel(const __grid_constant__ CUtensorMap tmap_do, unsigned char* __restrict__ ws_tiles,
+                   int tiles_per_chunk, int H, int NT, int* status) {
+  extern __shared__ unsigned char smem_raw[];
+  PreSmem& sm = *reinterpret_cast<PreSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int ch = blockIdx.x, unit = ch / NT, cidx = ch % NT, bi = unit / H, hi = unit % H;
+  unsigned char* tiles = ws_tiles + (size_t)ch * tiles_per_chunk * TILE_BYTES;
+  const int row = 16 * warp + (lane & 15);
+  const bool lo = lane < 16;
+
+  if (tid == 0) {
+    mbar_init(&sm.bar_ld, 1); mbar_init(&sm.bar_m1, 1); mbar_init(&sm.bar_m2, 1);
+    fence_mbar_init();
+  }
+  if (warp == 0) tmem_alloc(&sm.tmem_base, 128);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tm = sm.tmem_base;
+  if (tid == 0) {
+    mbar_expect_tx(&sm.bar_ld, 4 * TILE_BYTES);
+    bulk_load(sm.ainv, tiles + S_AINV * TILE_BYTES, TILE_BYTES, &sm.bar_ld);
+    bulk_load(sm.bt, tiles + S_BT * TILE_BYTES, TILE_BYTES, &sm.bar_ld);
+    bulk_load(sm.aqb, tiles + S_AQB * TILE_BYTES, TILE_BYTES, &sm.bar_ld);
+    tma_load_4d(sm.dout, &tmap_do, &sm.bar_ld, 0, cidx * L, hi, bi);
+  }
+  bool ok = mbar_wait(&sm.bar_ld, 0, status, 301);
+  if (tid == 0 && ok) {
+    tc_fence_after();
+    umma_tile<64, 64, 1, 1>(tmem_addr(tm, 0, 0), smem_u32(sm.aqb), smem_u32(sm.dout), false);   // A_qb^T do
+    umma_tile<64, 64, 1, 1>(tmem_addr(tm, 16, 0), smem_u32(sm.ainv), smem_u32(sm.bt), false);   // Ainv^T b~
+    umma_commit(&sm.bar_m1);
+  }
+  ok = mbar_wait(&sm.bar_m1, 0, status, 302) && ok;
+  tc_fence_after();
+  if (ok) {
+#pragma unroll
+    for (int part = 0; part < 2; ++part) {
+      uint32_t r[32];
+      tmem_ld32(tmem_addr(tm, 32 * warp, 32 * part), r);
+      tmem_ld_wait();
+      float x[32];
+#pragma unroll
+      for (int j = 0; j < 32; ++j) x[j] = __uint_as_float(r[j]);
+      tile_store_row32(lo ? sm.p1 : sm.b2, row, 32 * part, x);
+    }
+  }
+  fence_async_smem();
+  tc_fence_before();
+  __syncthreads();
+  if (tid == 0 && ok) {
+    tc_fence_after();
+    umma_tile<64, 64, 1, 1>(tmem_addr(tm, 0, 64), smem_u32(sm.ainv), smem_u32(sm.p1), false);   // Ainv^T P1
+    umma_commit(&sm.bar_m2);
+    bulk_store(tiles + S_B2 * TILE_BYTES, sm.b2, TILE_BYTES);
+    bulk_commit();
+  }
+  ok = mbar_wait(&sm.bar_m2, 0, status, 303) && ok;
+  tc_fence_after();
+  if (ok) {
+#pragma unroll
+    for (int part = 0; part < 2; ++part) {
+      uint32_t r[32];
+      tmem_ld32(tmem_addr(tm, 32 * warp, 64 + 32 * part), r);
+      tmem_ld_wait();
+      if (lo) {
+        float x[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) x[j] = __uint_as_float(r[j]);
+        tile_store_row32(sm.p2, row, 32 * part, x);
+      }
+    }
+  }
+  fence_async_smem();
+  tc_fence_before();
+  __syncthreads();
+  if (tid == 0) {
+    if (ok) { bulk_store(tiles + S_P2 * TILE_BYTES, sm.p2, TILE_BYTES); bulk_commit(); }
+    bulk_wait_all();
+  }
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tm, 128);
+}
+
+// ---------------------------------------------------------------------------------------------
+// 4. reverse scan: grid = B*H, 128 threads
+// ---------------------------------------------------------------------------------------------
+struct BScanStage {
+  unsigned char b2[TILE_BYTES], p2[TILE_BYTES];   // adjacent workspace slots: one bulk copy
+  unsigned char at[TILE_BYTES], qt[TILE_BYTES], dout[TILE_BYTES];
+};
+struct BScanSmem {
+  BScanStage st[2];
+  unsigned char dhh[TILE_BYTES];    // dh^ as bf16, [k][v]
+  unsigned char dz[TILE_BYTES];     // dz as bf16, [token][v]
+  uint64_t bar_full[2], bar_m1, bar_m2;
+  uint32_t tmem_base;
+};
+
+__global__ void __launch_bounds__(128)
+r7c_bwd_scan_kernel(const __grid_constant__ CUtensorMap tmap_do, unsigned char* __restrict__ ws_tiles,
+                    const float* __restrict__ ws_aux, int tiles_per_chunk, const float* __restrict__ d_ht,
+                    float* __restrict__ d_h0, int H, int NT, int* status) {
+  extern __shared__ unsigned char smem_raw[];
+  BScanSmem& sm = *reinterpret_cast<BScanSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int unit = blockIdx.x, bi = unit / H, hi = unit % H;
+  const size_t ch0 = (size_t)unit * NT;
+  const int row = 16 * warp + (lane & 15);
+  const bool state_lane = lane < 16;
+
+  if (tid == 0) {
+    mbar_init(&sm.bar_full[0], 1); mbar_init(&sm.bar_full[1], 1);
+    mbar_init(&sm.bar_m1, 1); mbar_init(&sm.bar_m2, 1);
+    fence_mbar_init();
+  }
+  if (warp == 0) tmem_alloc(&sm.tmem_base, 64);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tm = sm.tmem_base;
+  const uint32_t tm_w = tmem_addr(tm, 32 * warp, 0);
+
+  auto issue_loads = [&](int n) {     // n-th chunk in reverse order
+    const int c = NT - 1 - n;
+    BScanStage& s = sm.st[n & 1];
+    unsigned char* tiles = ws_tiles + (ch0 + c) * (size_t)tiles_per_chunk * TILE_BYTES;
+    mbar_expect_tx(&sm.bar_full[n & 1], 5 * TILE_BYTES);
+    bulk_load(s.b2, tiles + S_B2 * TILE_BYTES, 2 * TILE_BYTES, &sm.bar_full[n & 1]);
+    bulk_load(s.at, tiles + S_AT * TILE_BYTES, TILE_BYTES, &sm.bar_full[n & 1]);
+    bulk_load(s.qt, tiles + S_QT * TILE_BYTES, TILE_BYTES, &sm.bar_full[n & 1]);
+    tma_load_4d(s.dout, &tmap_do, &sm.bar_full[n & 1], 0, c * L, hi, bi);
+  };
+  if (tid == 0) {
+    issue_loads(0);
+    if (NT > 1) issue_loads(1);
+  }
+
+  // gradient of the state after the current chunk, row k of dh[k][v] = d_ht[v][k]
+  float dh[64];
+  if (state_lane && d_ht) {
+    const float* S = d_ht + (size_t)unit * 4096;
+#pragma unroll
+    for (int vv = 0; vv < 64; ++vv) dh[vv] = S[vv * 64 + row];
+  } else {
+#pragma unroll
+    for (int vv = 0; vv < 64; ++vv) dh[vv] = 0.f;
+  }
+
+  bool ok = true;
+  for (int n = 0; n < NT && ok; ++n) {
+    const int c = NT - 1 - n;
+    BScanStage& s = sm.st[n & 1];
+    unsigned char* tiles = ws_tiles + (ch0 + c) * (size_t)tiles_per_chunk * TILE_BYTES;
+    float e0 = 1.f;
+    if (state_lane) {
+      const float dc = ws_aux[(ch0 + c) * AUX_FLOATS + 64 + row];
+      e0 = ws_aux[(ch0 + c) * AUX_FLOATS + row];
+#pragma unroll
+      for (int vv = 0; vv < 64; ++vv) dh[vv] *= dc;      // dh^ = e^{glast-gref} dh_L
+      tile_store_row32(sm.dhh, row, 0, dh);
+      tile_store_row32(sm.dhh, row, 32, dh + 32);
+    }
+    ok = mbar_wait(&sm.bar_full[n & 1], (n >> 1) & 1, status, 311);
+    fence_async_smem();
+    tc_fence_before();
+    ok = __syncthreads_and(ok);
+    if (tid == 0 && ok) {
+      tc_fence_after();
+      umma_tile<64, 64, 0, 1>(tmem_addr(tm, 16, 0), smem_u32(s.b2), smem_u32(sm.dhh), false);   // B2 dh^
+      umma_tile<64, 64, 1, 1>(tmem_addr(tm, 0, 0), smem_u32(s.qt), smem_u32(s.dout), false);    // q~^T do
+      umma_commit(&sm.bar_m1);
+      bulk_store(tiles + S_DHH * TILE_BYTES, sm.dhh, TILE_BYTES);
+      bulk_commit();
+    }
+    ok = ok && mbar_wait(&sm.bar_m1, n & 1, status, 312);
+    tc_fence_after();
+    if (ok) {
+#pragma unroll
+      for (int part = 0; part < 2; ++part) {
+        uint32_t r[32];
+        tmem_ld32(tm_w + 32 * part, r);
+        tmem_ld_wait();
+        if (!state_lane) {      // dz = P2 + B2 dh^
+          float x[32], p[32];
+          tile_load_row32(s.p2, row, 32 * part, p);
+#pragma unroll
+          for (int j = 0; j < 32; ++j) x[j] = __uint_as_float(r[j]) + p[j];
+          tile_store_row32(sm.dz, row, 32 * part, x);
+        }
+      }
+    }
+    fence_async_smem();
+    tc_fence_before();
+    ok = __syncthreads_and(ok);
+    if (tid == 0 && ok) {
+      tc_fence_after();
+      umma_tile<64, 64, 1, 1>(tmem_addr(tm, 0, 0), smem_u32(s.at), smem_u32(sm.dz), true);      // += a~^T dz
+      umma_commit(&sm.bar_m2);
+      bulk_store(tiles + S_DZ * TILE_BYTES, sm.dz, TILE_BYTES);
+      bulk_commit();
+    }
+    ok = ok && mbar_wait(&sm.bar_m2, n & 1, status, 313);
+    tc_fence_after();
+    if (ok) {
+#pragma unroll
+      for (int part = 0; part < 2; ++part) {
+        uint32_t r[32];
+        tmem_ld32(tm_w + 32 * part, r);
+        tmem_ld_wait();
+        if (state_lane) {       // dh0 = e^{gref} (q~^T do + a~^T dz + dh^)
+#pragma unroll
+          for (int j = 0; j < 32; ++j) dh[32 * part + j] = e0 * (__uint_as_float(r[j]) + dh[32 * part + j]);
+        }
+      }
+    }
+    if (tid == 0) bulk_wait_read();     // dhh and dz tiles are rewritten in the next iteration
+    tc_fence_before();
+    ok = __syncthreads_and(ok);
+    if (tid == 0 && ok && n + 2 < NT) issue_loads(n + 2);
+  }
+  if (state_lane && d_h0 && ok) {
+    float* S = d_h0 + (size_t)unit * 4096;
+#pragma unroll
+    for (int vv = 0; vv < 64; ++vv) S[vv * 64 + row] = dh[vv];
+  }
+  if (tid == 0) bulk_wait_all();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tm, 64);
+}
+
+// ---------------------------------------------------------------------------------------------
+// 5. all token gradients of one chunk: grid = B*H*NT, 128 threads
+// ---------------------------------------------------------------------------------------------
+struct FinalSmem {
+  unsigned char dout[TILE_BYTES], dz[TILE_BYTES];                 // [do; dz]
+  unsigned char v[TILE_BYTES], sa[TILE_BYTES];                    // [v; sa]
+  unsigned char daqk[TILE_BYTES], daak[TILE_BYTES], daqb[TILE_BYTES], daab[TILE_BYTES];
+  unsigned char aqk[TILE_BYTES], aak[TILE_BYTES];                 // adjacent workspace slots
+  unsigned char qt[TILE_BYTES], at[TILE_BYTES], kt[TILE_BYTES], bt[TILE_BYTES];
+  unsigned char h0[TILE_BYTES], dhh[TILE_BYTES];
+  float gs[L * NROW];       // inclusive prefix of g inside each half of the chunk
+  float gg[L * NROW];       // g
+  float tot[2][64];
+  float rtot[64];
+  float dgl[64];            // dglast
+  uint64_t bar_ld, bar_m1, bar_m2;
+  uint32_t tmem_base;
+};
+
+__global__ void __launch_bounds__(128)
+r7c_bwd_final_kernel(const bf16* __restrict__ w, const __grid_constant__ CUtensorMap tmap_do,
+                     const __grid_constant__ CUtensorMap tmap_v, const unsigned char* __restrict__ ws_tiles,
+                     int tiles_per_chunk, bf16* __restrict__ dq, bf16* __restrict__ dw, bf16* __restrict__ dk,
+                     bf16* __restrict__ dv, bf16* __restrict__ da, bf16* __restrict__ db,
+                     int Tn, int H, int NT, TokLayout lay, int* status) {
+  extern __shared__ unsigned char smem_raw[];
+  FinalSmem& sm = *reinterpret_cast<FinalSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int ch = blockIdx.x, unit = ch / NT, cidx = ch % NT, bi = unit / H, hi = unit % H, t0 = cidx * L;
+  const long long base = bi * lay.sb + hi * lay.sh;
+  const unsigned char* tiles = ws_tiles + (size_t)ch * tiles_per_chunk * TILE_BYTES;
+
+  if (tid == 0) {
+    mbar_init(&sm.bar_ld, 1); mbar_init(&sm.bar_m1, 1); mbar_init(&sm.bar_m2, 1);
+    fence_mbar_init();
+  }
+  if (warp == 0) tmem_alloc(&sm.tmem_base, 256);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tm = sm.tmem_base;
+  if (tid == 0) {
+    mbar_expect_tx(&sm.bar_ld, 12 * TILE_BYTES);
+    tma_load_4d(sm.dout, &tmap_do, &sm.bar_ld, 0, t0, hi, bi);
+    tma_load_4d(sm.v, &tmap_v, &sm.bar_ld, 0, t0, hi, bi);
+    bulk_load(sm.dz, tiles + S_DZ * TILE_BYTES, TILE_BYTES, &sm.bar_ld);
+    bulk_load(sm.sa, tiles + S_SA * TILE_BYTES, TILE_BYTES, &sm.bar_ld);
+    bulk_load(sm.aqk, tiles + S_AQK * TILE_BYTES, 2 * TILE_BYTES, &sm.bar_ld);
+    bulk_load(sm.qt, tiles + S_QT * TILE_BYTES, TILE_BYTES, &sm.bar_ld);
+    bulk_load(sm.at, tiles + S_AT * TILE_BYTES, TILE_BYTES, &sm.bar_ld);
+    bulk_load(sm.kt, tiles + S_KT * TILE_BYTES, TILE_BYTES, &sm.bar_ld);
+    bulk_load(sm.bt, tiles + S_BT * TILE_BYTES, TILE_BYTES, &sm.bar_ld);
+    bulk_load(sm.h0, tiles + S_H0 * TILE_BYTES, TILE_BYTES, &sm.bar_ld);
+    bulk_load(sm.dhh, tiles + S_DHH * TILE_BYTES, TILE_BYTES, &sm.bar_ld);
+  }
+
+  // ---- decay prefix sums (while the tiles arrive): gg = g, gs = inclusive prefix inside each half
+  {
+#pragma unroll
+    for (int n = 0; n < 4; ++n) {
+      const int e = tid + 128 * n, row = e >> 3, cc = e & 7, tok = t0 + row;
+      const bool valid = tok < Tn;
+      uint4 rw = make_uint4(0u, 0u, 0u, 0u);
+      if (valid) rw = __ldg(reinterpret_cast<const uint4*>(w + base + (long long)tok * lay.st + 8 * cc));
+      const uint32_t u[4] = {rw.x, rw.y, rw.z, rw.w};
+      float g[8];
+#pragma unroll
+      for (int m = 0; m < 4; ++m) {
+        g[2 * m] = valid ? -expf(bf16_lo(u[m])) : 0.f;
+        g[2 * m + 1] = valid ? -expf(bf16_hi(u[m])) : 0.f;
+      }
+      *reinterpret_cast<float4*>(&sm.gg[row * NROW + 8 * cc]) = make_float4(g[0], g[1], g[2], g[3]);
+      *reinterpret_cast<float4*>(&sm.gg[row * NROW + 8 * cc + 4]) = make_float4(g[4], g[5], g[6], g[7]);
+    }
+    __syncthreads();
+    const int c = tid & 63, half = tid >> 6;
+    float gv[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) gv[j] = sm.gg[(32 * half + j) * NROW + c];
+    float run = 0.f;
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      run += gv[j];
+      sm.gs[(32 * half + j) * NROW + c] = run;
+    }
+    sm.tot[half][c] = run;
+  }
+  bool ok = mbar_wait(&sm.bar_ld, 0, status, 321);
+  __syncthreads();
+
+  // ---- MMA group 1: all four dA products, and dv
+  if (tid == 0 && ok) {
+    tc_fence_after();
+    umma_tile<128, 128, 0, 0>(tmem_addr(tm, 0, 0), smem_u32(sm.dout), smem_u32(sm.v), false);        // [do;dz] [v;sa]^T
+    umma_tile<64, 64, 1, 1, 8>(tmem_addr(tm, 0, 128), smem_u32(sm.aqk), smem_u32(sm.dout), false);   // A_qk^T do + A_ak^T dz
+    umma_tile<64, 64, 0, 1>(tmem_addr(tm, 0, 128), smem_u32(sm.kt), smem_u32(sm.dhh), true);         // + k~ dh^
+    umma_commit(&sm.bar_m1);
+  }
+  // dglast[c] = sum_v dh^[c][v] X[c][v]  (threads 0..63, X straight from the workspace)
+  if (tid < 64 && ok) {
+    float s = 0.f;
+    const uint4* xr = reinterpret_cast<const uint4*>(tiles + S_X * TILE_BYTES);
+#pragma unroll
+    for (int cchunk = 0; cchunk < 8; ++cchunk) {
+      const uint4 xa = __ldg(xr + (tile_chunk_off(tid, cchunk) >> 4));
+      const uint4 da_ = *reinterpret_cast<const uint4*>(sm.dhh + tile_chunk_off(tid, cchunk));
+      s += bf16_lo(xa.x) * bf16_lo(da_.x) + bf16_hi(xa.x) * bf16_hi(da_.x);
+      s += bf16_lo(xa.y) * bf16_lo(da_.y) + bf16_hi(xa.y) * bf16_hi(da_.y);
+      s += bf16_lo(xa.z) * bf16_lo(da_.z) + bf16_hi(xa.z) * bf16_hi(da_.z);
+      s += bf16_lo(xa.w) * bf16_lo(da_.w) + bf16_hi(xa.w) * bf16_hi(da_.w);
+    }
+    sm.dgl[tid] = s;
+  }
+  ok = mbar_wait(&sm.bar_m1, 0, status, 322) && ok;
+  tc_fence_after();
+  if (ok) {
+    const int i = tid & 63;
+    const bool lower = tid >= 64;     // rows of dz: strictly lower; rows of do: lower incl. diagonal
+#pragma unroll
+    for (int part = 0; part < 4; ++part) {
+      uint32_t r[32];
+      tmem_ld32(tmem_addr(tm, 32 * warp, 32 * part), r);
+      tmem_ld_wait();
+      float x[32];
+      const int j0 = 32 * (part & 1);
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        const bool keep = lower ? (j0 + j < i) : (j0 + j <= i);
+        x[j] = keep ? __uint_as_float(r[j]) : 0.f;
+      }
+      unsigned char* dst = lower ? (part < 2 ? sm.daak : sm.daab) : (part < 2 ? sm.daqk : sm.daqb);
+      tile_store_row32(dst, i, j0, x);
+    }
+    // dv rows sit on the lower lane halves of columns 128..191
+    const int row = 16 * warp + (lane & 15), tok = t0 + row;
+#pragma unroll
+    for (int part = 0; part < 2; ++part) {
+      uint32_t r[32];
+      tmem_ld32(tmem_addr(tm, 32 * warp, 128 + 32 * part), r);
+      tmem_ld_wait();
+      if (lane < 16 && tok < Tn) {
+        float x[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) x[j] = __uint_as_float(r[j]);
+        store_row32_global(dv + base + (long long)tok * lay.st + 32 * part, x);
+      }
+    }
+  }
+  fence_async_smem();
+  tc_fence_before();
+  __syncthreads();
+
+  // ---- MMA group 2: [dq~; da~] (columns 0..63) and [dk~; db~] (columns 64..127)
+  if (tid == 0 && ok) {
+    tc_fence_after();
+    umma_tile<128, 64, 0, 0>(tmem_addr(tm, 0, 0), smem_u32(sm.dout), smem_u32(sm.h0), false);        // [do;dz] h~0^T
+    umma_tile<128, 64, 0, 1>(tmem_addr(tm, 0, 0), smem_u32(sm.daqk), smem_u32(sm.kt), true);         // + [dA_qk;dA_ak] k~
+    umma_tile<128, 64, 0, 1>(tmem_addr(tm, 0, 0), smem_u32(sm.daqb), smem_u32(sm.bt), true);         // + [dA_qb;dA_ab] b~
+    umma_tile<128, 64, 1, 1>(tmem_addr(tm, 0, 64), smem_u32(sm.daqk), smem_u32(sm.qt), false, 2 * TILE_BYTES);  // [dA_qk|dA_qb]^T q~
+    umma_tile<128, 64, 1, 1>(tmem_addr(tm, 0, 64), smem_u32(sm.daak), smem_u32(sm.at), true, 2 * TILE_BYTES);   // + [dA_ak|dA_ab]^T a~
+    umma_tile<128, 64, 0, 0>(tmem_addr(tm, 0, 64), smem_u32(sm.v), smem_u32(sm.dhh), true);          // + [v;sa] dh^^T
+    umma_commit(&sm.bar_m2);
+  }
+  ok = mbar_wait(&sm.bar_m2, 0, status, 323) && ok;
+  tc_fence_after();
+
+  // ---- epilogue.  Thread r < 64 holds dq~_i and dk~_i (token i = r), thread r >= 64 holds da~_i, db~_i.
+  // red[i][c] (fp32, in the dA tiles' space) collects dgi + dge; dge goes to the [do;dz] space.
+  float* red = reinterpret_cast<float*>(sm.daqk);
+  float* dge = reinterpret_cast<float*>(sm.dout);
+  const int i = tid & 63, tok = t0 + i;
+  const bool second = tid >= 64;
+  for (int phase = 0; phase < 2; ++phase) {
+    if (ok && (phase == 1) == second) {
+#pragma unroll
+      for (int part = 0; part < 2; ++part) {
+        uint32_t r1[32], r2[32];
+        tmem_ld32(tmem_addr(tm, 32 * warp, 32 * part), r1);          // dq~ / da~
+        tmem_ld32(tmem_addr(tm, 32 * warp, 64 + 32 * part), r2);     // dk~ / db~
+        tmem_ld_wait();
+        float t1[32], t2[32], o1[32], o2[32];
+        tile_load_row32(second ? sm.at : sm.qt, i, 32 * part, t1);
+        tile_load_row32(second ? sm.bt : sm.kt, i, 32 * part, t2);
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const int c = 32 * part + j;
+          const float d1 = sm.gs[i * NROW + c] - (i < 32 ? sm.tot[0][c] : 0.f);      // gi - gref
+          const float x1 = __uint_as_float(r1[j]), x2 = __uint_as_float(r2[j]);
+          const float ek = cexp(-d1);
+          if (!second) {
+            o1[j] = x1 * cexp(d1);                       // dq
+            o2[j] = x2 * ek;                             // dk
+            red[i * NROW + c] = x1 * t1[j] - x2 * t2[j]; // dq~ q~ - dk~ k~
+          } else {
+            o1[j] = x1 * cexp(d1 - sm.gg[i * NROW + c]); // da
+            o2[j] = x2 * ek;                             // db
+            const float ge_ = x1 * t1[j];                // da~ a~
+            dge[i * NROW + c] = ge_;
+            red[i * NROW + c] += ge_ - x2 * t2[j];
+          }
+        }
+        if (tok < Tn) {
+          const long long off = base + (long long)tok * lay.st + 32 * part;
+          store_row32_global((second ? da : dq) + off, o1);
+          store_row32_global((second ? db : dk) + off, o2);
+        }
+      }
+    }
+    __syncthreads();
+  }
+  // reverse inclusive prefix over tokens, per channel; thread = (channel, half)
+  {
+    const int c = tid & 63, half = tid >> 6;
+    float rv[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) rv[j] = red[(32 * half + j) * NROW + c];
+    float run = 0.f;
+#pragma unroll
+    for (int j = 31; j >= 0; --j) { run += rv[j]; rv[j] = run; }
+    if (half == 1) sm.rtot[c] = run;
+    __syncthreads();
+    const float add = (half == 0 ? sm.rtot[c] : 0.f) + sm.dgl[c];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      const int ii = 32 * half + j;
+      if (t0 + ii < Tn) {
+        const float dg = rv[j] + add - dge[ii * NROW + c];
+        dw[base + (long long)(t0 + ii) * lay.st + c] = __float2bfloat16_rn(dg * sm.gg[ii * NROW + c]);
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tm, 256);
+}
+
+}  // namespace r7c
+
+int launch_rwkv7_chunked_bwd(const void* r, const void* w, const void* k, const void* v, const void* a, const void* b,
+                             const float* h0, int n_state, const void* d_o, const float* d_ht,
+                             void* dr, void* dw, void* dk, void* dv, void* da, void* db, float* d_h0,
+                             void* workspace, int B, int Tn, int H, int head_first, cudaStream_t st) {
+  using namespace r7c;
+  typedef __nv_bfloat16 bf16;
+  int e = launch_rwkv7_chunked_fwd(r, w, k, v, a, b, h0, n_state, nullptr, nullptr, workspace, B, Tn, H, head_first,
+                                   true, st);
+  if (e) return e;
+  int* status = device_status_ptr();
+  if (!status) { last_cuda_error_slot() = 99999; return RWKVB200_E_CUDA; }
+  CUtensorMap tmap_do, tmap_v;
+  e = make_token_tensor_map(&tmap_do, d_o, B, Tn, H, head_first);
+  if (e) return e;
+  e = make_token_tensor_map(&tmap_v, v, B, Tn, H, head_first);
+  if (e) return e;
+  const int NT = num_chunks(Tn);
+  Workspace ws = carve(workspace, B, Tn, H, ALL_TILES);
+  TokLayout lay(Tn, H, head_first);
+  {
+    const int smem = (int)sizeof(PreSmem) + 1024;
+    if (cuda_ok(cudaFuncSetAttribute(r7c_bwd_pre_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem))) return RWKVB200_E_CUDA;
+    ProfScope prof("r7c_bwd_pre_kernel", st);
+    r7c_bwd_pre_kernel<<<B * H * NT, 128, smem, st>>>(tmap_do, ws.tiles, ALL_TILES, H, NT, status);
+  }
+  e = check_launch();
+  if (e) return e;
+  {
+    const int smem = (int)sizeof(BScanSmem) + 1024;
+    if (cuda_ok(cudaFuncSetAttribute(r7c_bwd_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem))) return RWKVB200_E_CUDA;
+    ProfScope prof("r7c_bwd_scan_kernel", st);
+    r7c_bwd_scan_kernel<<<B * H, 128, smem, st>>>(tmap_do, ws.tiles, ws.aux, ALL_TILES, d_ht, d_h0, H, NT, status);
+  }
+  e = check_launch();
+  if (e) return e;
+  {
+    const int smem = (int)sizeof(FinalSmem) + 1024;
+    if (cuda_ok(cudaFuncSetAttribute(r7c_bwd_final_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem))) return RWKVB200_E_CUDA;
+    ProfScope prof("r7c_bwd_final_kernel", st);
+    r7c_bwd_final_kernel<<<B * H * NT, 128, smem, st>>>((const bf16*)w, tmap_do, tmap_v, ws.tiles, ALL_TILES,
+                                                         (bf16*)dr, (bf16*)dw, (bf16*)dk, (bf16*)dv, (bf16*)da,
+                                                         (bf16*)db, Tn, H, NT, lay, status);
+  }
+  return check_launch();
+}
+
+}  // namespace rwkvb200

@@ -328,6 +328,7 @@ struct ScanSmem {
   ScanStage st[2];
   unsigned char ht[TILE_BYTES];             // h~0 as bf16, [k][v]
   unsigned char sa[TILE_BYTES];             // sa as bf16, [token][v]
+  unsigned char xt[TILE_BYTES];             // X = h~0 + k~^T v + b~^T sa as bf16 (kept for the backward)
   uint64_t bar_full[2], bar_a, bar_c;
   uint32_t tmem_base;
 };
@@ -469,6 +470,11 @@ r7c_scan_fwd_kernel(const __grid_constant__ CUtensorMap tmap_v, const unsigned c
         tmem_ld_wait();
         float x[32];
         if (state_lane) {
+          if (bwd_tiles) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) x[j] = __uint_as_float(r[j]);
+            tile_store_row32(sm.xt, row, 32 * part, x);
+          }
 #pragma unroll
           for (int j = 0; j < 32; ++j) { x[j] = __uint_as_float(r[j]) * scale; r[j] = __float_as_uint(x[j]); }
           if (!last) {
@@ -481,7 +487,7 @@ r7c_scan_fwd_kernel(const __grid_constant__ CUtensorMap tmap_v, const unsigned c
         } else {
 #pragma unroll
           for (int j = 0; j < 32; ++j) x[j] = __uint_as_float(r[j]) + keep[32 * part + j];
-          if (tok < Tn) {
+          if (o && tok < Tn) {
             bf16* dst = o + base + (long long)tok * lay.st + 32 * part;
 #pragma unroll
             for (int j = 0; j < 32; j += 8) {
@@ -499,6 +505,10 @@ r7c_scan_fwd_kernel(const __grid_constant__ CUtensorMap tmap_v, const unsigned c
     fence_async_smem();
     tc_fence_before();
     ok = __syncthreads_and(ok);
+    if (bwd_tiles && tid == 0 && ok) {
+      bulk_store(bwd_tiles + ((ch0 + c) * (size_t)tiles_per_chunk + S_X) * TILE_BYTES, sm.xt, TILE_BYTES);
+      bulk_commit();
+    }
     if (tid == 0 && ok && c + 2 < NT) issue_loads(c + 2);
   }
   if (tid == 0) bulk_wait_all();
@@ -514,7 +524,7 @@ int launch_rwkv7_chunked_fwd(const void* r, const void* w, const void* k, const 
   using namespace r7c;
   typedef __nv_bfloat16 bf16;
   int* status = device_status_ptr();
-  if (!status) return RWKVB200_E_CUDA;
+  if (!status) { last_cuda_error_slot() = 99999; return RWKVB200_E_CUDA; }
   CUtensorMap tmap_v;
   int e = make_token_tensor_map(&tmap_v, v, B, Tn, H, head_first);
   if (e) return e;
@@ -524,8 +534,7 @@ int launch_rwkv7_chunked_fwd(const void* r, const void* w, const void* k, const 
   TokLayout lay(Tn, H, head_first);
   {
     const int smem = (int)sizeof(IntraSmem) + 1024;
-    if (cudaFuncSetAttribute(r7c_intra_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
-      return RWKVB200_E_CUDA;
+    if (cuda_ok(cudaFuncSetAttribute(r7c_intra_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem))) return RWKVB200_E_CUDA;
     ProfScope prof("r7c_intra_fwd_kernel", st);
     r7c_intra_fwd_kernel<<<B * H * NT, 128, smem, st>>>((const bf16*)r, (const bf16*)w, (const bf16*)k, (const bf16*)a,
                                                          (const bf16*)b, tmap_v, ws.tiles, ws.aux, tpc,
@@ -536,8 +545,7 @@ int launch_rwkv7_chunked_fwd(const void* r, const void* w, const void* k, const 
   if (e) return e;
   {
     const int smem = (int)sizeof(ScanSmem) + 1024;
-    if (cudaFuncSetAttribute(r7c_scan_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
-      return RWKVB200_E_CUDA;
+    if (cuda_ok(cudaFuncSetAttribute(r7c_scan_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem))) return RWKVB200_E_CUDA;
     ProfScope prof("r7c_scan_fwd_kernel", st);
     r7c_scan_fwd_kernel<<<B * H, 128, smem, st>>>(tmap_v, ws.tiles, ws.aux, tpc, keep_for_bwd ? ws.tiles : nullptr,
                                                   h0, n_state, (bf16*)o, ht, Tn, H, NT, lay, status);

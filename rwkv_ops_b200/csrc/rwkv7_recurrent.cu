@@ -353,8 +353,7 @@ int launch_rwkv7_rec_bwd(const void* r, const void* w, const void* k, const void
   const int smem = (int)sizeof(BwdSmem);
   ProfScope prof("rwkv7_rec_bwd_kernel", st);
   RWKVB200_DISPATCH_DTYPE(dtype,
-    if (cudaFuncSetAttribute(rwkv7_rec_bwd_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
-      return RWKVB200_E_CUDA;
+    if (cuda_ok(cudaFuncSetAttribute(rwkv7_rec_bwd_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem))) return RWKVB200_E_CUDA;
     rwkv7_rec_bwd_kernel<T><<<grid, 64, smem, st>>>((const T*)r, (const T*)w, (const T*)k, (const T*)v, (const T*)a,
                                                     (const T*)b, (const T*)d_o, d_ht, ckpt, (T*)dr, (T*)dw, (T*)dk,
                                                     (T*)dv, (T*)da, (T*)db, d_h0, Tn, H, lay));

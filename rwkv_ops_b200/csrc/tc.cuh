@@ -66,11 +66,13 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 }
 // Bounded wait; returns false (and records `code`) if the phase never completed.
 // `status` is the library's device status word (0 = fine), see device_status_ptr().
+// The result is made uniform over the threads of the warp that wait together, so that the
+// warp-collective TMEM instructions that follow are never executed by part of a warp.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int code) {
-  for (uint32_t i = 0; i < WAIT_LIMIT; ++i)
-    if (mbar_try_wait(bar, parity)) return true;
-  atomicCAS(status, 0, code);
-  return false;
+  bool done = false;
+  for (uint32_t i = 0; i < WAIT_LIMIT && !done; ++i) done = mbar_try_wait(bar, parity);
+  if (!done) atomicCAS(status, 0, code);
+  return __all_sync(__activemask(), done) != 0;
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -138,8 +140,9 @@ __device__ __forceinline__ uint64_t umma_desc(uint32_t addr, uint32_t lbo_bytes,
 __device__ __forceinline__ uint64_t desc_kmajor(uint32_t tile_addr, int kstep) {
   return umma_desc(tile_addr + 32u * kstep, 16, 1024);
 }
-__device__ __forceinline__ uint64_t desc_mnmajor(uint32_t tile_addr, int kstep) {
-  return umma_desc(tile_addr + 2048u * kstep, TILE_BYTES, 1024);
+// `lbo` is the byte distance to the tile holding M/N elements 64..127 of a 128-wide MN-major operand.
+__device__ __forceinline__ uint64_t desc_mnmajor(uint32_t tile_addr, int kstep, uint32_t lbo = TILE_BYTES) {
+  return umma_desc(tile_addr + 2048u * kstep, lbo, 1024);
 }
 
 // Instruction descriptor, kind::f16 with bf16 inputs and fp32 accumulation.
@@ -165,14 +168,19 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar) {
                : "memory");
 }
 
-// A 64x64x64 (or 128-row) product as four K=16 steps.  a_mn / b_mn select the operand majors.
-template <int M, int N, int A_MN, int B_MN>
-__device__ __forceinline__ void umma_tile(uint32_t tmem_d, uint32_t a_addr, uint32_t b_addr, bool accumulate) {
+// A product with a contraction length of 16*KSTEPS as K=16 steps.  A_MN / B_MN select the operand
+// majors.  A 128-row K-major operand is two tiles adjacent in shared memory; a 128-wide MN-major operand
+// is two tiles `a_lbo` / `b_lbo` bytes apart; an MN-major operand with KSTEPS = 8 continues into the
+// tile that follows it (contraction rows 64..127).
+template <int M, int N, int A_MN, int B_MN, int KSTEPS = 4>
+__device__ __forceinline__ void umma_tile(uint32_t tmem_d, uint32_t a_addr, uint32_t b_addr, bool accumulate,
+                                          uint32_t a_lbo = TILE_BYTES, uint32_t b_lbo = TILE_BYTES) {
+  static_assert(KSTEPS == 4 || (A_MN && B_MN), "a K-major operand holds 64 contraction elements");
   constexpr uint32_t id = idesc_bf16(M, N, A_MN, B_MN);
 #pragma unroll
-  for (int ks = 0; ks < 4; ++ks) {
-    const uint64_t ad = A_MN ? desc_mnmajor(a_addr, ks) : desc_kmajor(a_addr, ks);
-    const uint64_t bd = B_MN ? desc_mnmajor(b_addr, ks) : desc_kmajor(b_addr, ks);
+  for (int ks = 0; ks < KSTEPS; ++ks) {
+    const uint64_t ad = A_MN ? desc_mnmajor(a_addr, ks, a_lbo) : desc_kmajor(a_addr, ks);
+    const uint64_t bd = B_MN ? desc_mnmajor(b_addr, ks, b_lbo) : desc_kmajor(b_addr, ks);
     umma(tmem_d, ad, bd, id, accumulate || ks > 0);
   }
 }

@@ -35,7 +35,7 @@ int* g_status_ptr[64] = {};
 
 int make_token_tensor_map(CUtensorMap* out, const void* base, int B, int T, int H, int head_first) {
   EncodeTiledFn fn = encode_fn();
-  if (!fn) return RWKVB200_E_CUDA;
+  if (!fn) { last_cuda_error_slot() = 100000; return RWKVB200_E_CUDA; }
   // dims, fastest first: (64 channels, T, H, B); strides in bytes of dims 1..3
   const cuuint64_t row = HS * 2;
   cuuint64_t dims[4] = {(cuuint64_t)HS, (cuuint64_t)T, (cuuint64_t)H, (cuuint64_t)B};
@@ -45,10 +45,16 @@ int make_token_tensor_map(CUtensorMap* out, const void* base, int B, int T, int 
   strides[2] = row * (cuuint64_t)T * H;
   cuuint32_t box[4] = {(cuuint32_t)HS, 64, 1, 1};
   cuuint32_t estr[4] = {1, 1, 1, 1};
+  // The driver entry point needs the device's primary context current on THIS host thread; a thread
+  // that has only been handed the device by its framework (e.g. an autograd worker) may not have it yet.
+  int dev = 0;
+  if (cuda_ok(cudaGetDevice(&dev)) || cuda_ok(cudaSetDevice(dev))) return RWKVB200_E_CUDA;
   CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? RWKVB200_OK : RWKVB200_E_CUDA;
+  if (r == CUDA_SUCCESS) return RWKVB200_OK;
+  last_cuda_error_slot() = 100000 + (int)r;   // driver-API result, reported by rwkvb200_last_cuda_error()
+  return RWKVB200_E_CUDA;
 }
 
 static long long* g_stamp_buffer = nullptr;
@@ -114,7 +120,7 @@ tc_selftest_kernel(int mode, const __nv_bfloat16* X, const __nv_bfloat16* Y, con
   const uint32_t tbase = sm.tmem_base;
   bool ok = true;
 
-  if (mode == 0 || mode == 1) {
+  if (mode == 0 || mode == 1 || mode == 3 || mode == 4) {
     load_tile_plain(sm.tiles[0], X, 64);
     load_tile_plain(sm.tiles[1], Y, 64);
     load_tile_plain(sm.tiles[2], Z, 64);
@@ -125,6 +131,12 @@ tc_selftest_kernel(int mode, const __nv_bfloat16* X, const __nv_bfloat16* Y, con
       tc_fence_after();
       if (mode == 0) {
         umma_tile<128, 128, 0, 0>(tbase, smem_u32(sm.tiles[0]), smem_u32(sm.tiles[2]), false);
+      } else if (mode == 3) {
+        // [X^T; Y^T] Z : 128-wide MN-major A (second half one tile further), MN-major B
+        umma_tile<128, 64, 1, 1>(tbase, smem_u32(sm.tiles[0]), smem_u32(sm.tiles[2]), false, TILE_BYTES);
+      } else if (mode == 4) {
+        // X^T Z + Y^T W as one product with a contraction length of 128 (both operands MN-major)
+        umma_tile<64, 64, 1, 1, 8>(tbase, smem_u32(sm.tiles[0]), smem_u32(sm.tiles[2]), false);
       } else {
         umma_tile<64, 64, 0, 1>(tmem_addr(tbase, 0, 0), smem_u32(sm.tiles[0]), smem_u32(sm.tiles[2]), false);
         umma_tile<64, 64, 1, 1>(tmem_addr(tbase, 16, 0), smem_u32(sm.tiles[0]), smem_u32(sm.tiles[3]), false);
@@ -134,7 +146,7 @@ tc_selftest_kernel(int mode, const __nv_bfloat16* X, const __nv_bfloat16* Y, con
     ok = mbar_wait(&sm.bar_mma, 0, status, 101);
     tc_fence_after();
     if (ok) {
-      const int ncol = mode == 0 ? 128 : 64;
+      const int ncol = mode == 0 ? 128 : 64;   // modes 1, 3, 4 dump 128 lanes x 64 columns
       for (int c0 = 0; c0 < ncol; c0 += 32) {
         uint32_t r[32];
         tmem_ld32(tmem_addr(tbase, 32 * warp, c0), r);
@@ -191,9 +203,9 @@ int rwkvb200_device_status(int reset) {
 
 int rwkvb200_tc_selftest(int mode, const void* X, const void* Y, const void* Z, const void* W, float* out,
                          const void* tok, int B, int T, int H, int b, int t0, int h, void* img, void* stream) {
-  if (mode < 0 || mode > 2) return RWKVB200_E_SHAPE;
+  if (mode < 0 || mode > 4) return RWKVB200_E_SHAPE;
   int* status = device_status_ptr();
-  if (!status) return RWKVB200_E_CUDA;
+  if (!status) { last_cuda_error_slot() = 99999; return RWKVB200_E_CUDA; }
   CUtensorMap tmap;
   memset(&tmap, 0, sizeof(tmap));
   if (mode == 2) {
@@ -204,8 +216,7 @@ int rwkvb200_tc_selftest(int mode, const void* X, const void* Y, const void* Z, 
     return RWKVB200_E_NULL;
   }
   const int smem = (int)sizeof(SelfTestSmem) + 1024;
-  if (cudaFuncSetAttribute(tc_selftest_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
-    return RWKVB200_E_CUDA;
+  if (cuda_ok(cudaFuncSetAttribute(tc_selftest_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem))) return RWKVB200_E_CUDA;
   tc_selftest_kernel<<<1, 128, smem, (cudaStream_t)stream>>>(
       mode, (const __nv_bfloat16*)X, (const __nv_bfloat16*)Y, (const __nv_bfloat16*)Z, (const __nv_bfloat16*)W, out,
       tmap, b, t0, h, (__nv_bfloat16*)img, status);

@@ -316,8 +316,7 @@ int launch_wkv6_bwd(const void* r, const void* k, const void* v, const void* w, 
   {
     ProfScope prof("wkv6_bwd_kernel", st);
     RWKVB200_DISPATCH_DTYPE(dtype,
-      if (cudaFuncSetAttribute(wkv6_bwd_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
-        return RWKVB200_E_CUDA;
+      if (cuda_ok(cudaFuncSetAttribute(wkv6_bwd_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem))) return RWKVB200_E_CUDA;
       wkv6_bwd_kernel<T><<<grid, 64, smem, st>>>((const T*)r, (const T*)k, (const T*)v, (const T*)w, u, (const T*)d_y,
                                                  d_sT, ckpt, (T*)dr, (T*)dk, (T*)dv, (T*)dw, du_partial, d_s0, Tn, H));
   }

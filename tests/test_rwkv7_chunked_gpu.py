@@ -55,3 +55,39 @@ def test_forward_full_size_sampled_units():
         o_ref, s_ref = oracle_gdr(*sub)
         assert rel_l2(o[b:b + 1, :, h:h + 1], o_ref) < 2e-2
         assert rel_l2(s[b:b + 1, h:h + 1], s_ref) < 2e-2
+
+
+@pytest.mark.parametrize("T", [64, 128, 17, 65, 130, 257])
+@pytest.mark.parametrize("state", [False, True])
+def test_backward_vs_oracle(T, state):
+    B, H = 2, 3
+    d = rwkv7_inputs(B, T, H, dtype=torch.bfloat16, seed=800 + T, with_state=state, with_grads=True)
+    ref = {n: d[n].float().clone().requires_grad_(True) for n in "rwkvab"}
+    h0r = d["initial_state"].clone().requires_grad_(True) if state else None
+    o_ref, s_ref = oracle_gdr(*[ref[n] for n in "rwkvab"], initial_state=h0r)
+    ((o_ref * d["d_out"].float()).sum() + (s_ref * d["d_state"]).sum()).backward()
+    g = {n: d[n].cuda().requires_grad_(True) for n in "rwkvab"}
+    h0 = d["initial_state"].cuda().requires_grad_(True) if state else None
+    o, s = ro.generalized_delta_rule(*[g[n] for n in "rwkvab"], initial_state=h0)
+    torch.autograd.backward([o, s], [d["d_out"].cuda(), d["d_state"].cuda()])
+    errs = {f"d{n}": rel_l2(g[n].grad, ref[n].grad) for n in "rwkvab"}
+    if state:
+        errs["dh0"] = rel_l2(h0.grad, h0r.grad)
+    assert all(e < 2e-2 for e in errs.values()), errs
+
+
+def test_backward_full_size_sampled_units():
+    """Configuration 1 at full size: all six gradients of sampled (batch, head) units against the
+    hand-derived float64 reverse recurrence of the oracle."""
+    from oracle import rwkv7_manual_backward
+    B, T, H = 8, 4096, 32
+    d = rwkv7_inputs(B, T, H, dtype=torch.bfloat16, seed=1001, device="cuda", with_grads=True)
+    g = {n: d[n].requires_grad_(True) for n in "rwkvab"}
+    o, s = ro.generalized_delta_rule(*[g[n] for n in "rwkvab"])
+    torch.autograd.backward([o, s], [d["d_out"], d["d_state"]])
+    for (b, h) in [(0, 0), (5, 9), (7, 31)]:
+        sub = [g[n].detach()[b:b + 1, :, h:h + 1].cpu() for n in "rwkvab"]
+        grads = rwkv7_manual_backward(*sub, None, d["d_out"][b:b + 1, :, h:h + 1].cpu(),
+                                      d["d_state"][b:b + 1, h:h + 1].cpu())
+        errs = {n: rel_l2(g[n].grad[b:b + 1, :, h:h + 1], gr) for n, gr in zip("rwkvab", grads[:6])}
+        assert all(e < 2e-2 for e in errs.values()), errs

@@ -50,6 +50,26 @@ def test_mma_64_pairs_with_transposed_operands():
     assert torch.allclose(hi, ref_hi, rtol=1e-4, atol=1e-3), (hi - ref_hi).abs().max()
 
 
+def test_mma_wide_and_long_transposed_operands():
+    lib = _lib.load()
+    X, Y, Z, W = _mats(4)
+    out = torch.zeros(128, 64, device="cuda")
+    args = (X.data_ptr(), Y.data_ptr(), Z.data_ptr(), W.data_ptr(), out.data_ptr(), None, 0, 0, 0, 0, 0, 0, None)
+    assert lib.rwkvb200_tc_selftest(3, *args, torch.cuda.current_stream().cuda_stream) == 0
+    torch.cuda.synchronize()
+    _status_clear(lib)
+    ref = torch.cat([X.float().T @ Z.float(), Y.float().T @ Z.float()])
+    assert torch.allclose(out, ref, rtol=1e-4, atol=1e-3), (out - ref).abs().max()
+    out.zero_()
+    assert lib.rwkvb200_tc_selftest(4, *args, torch.cuda.current_stream().cuda_stream) == 0
+    torch.cuda.synchronize()
+    _status_clear(lib)
+    r = torch.arange(64)
+    lo = out[((r % 16) + 32 * (r // 16)).cuda()]
+    ref = X.float().T @ Z.float() + Y.float().T @ W.float()
+    assert torch.allclose(lo, ref, rtol=1e-4, atol=2e-3), (lo - ref).abs().max()
+
+
 @pytest.mark.parametrize("t0,T", [(64, 192), (128, 150)])
 def test_tma_tile_load_and_bulk_copies(t0, T):
     lib = _lib.load()
