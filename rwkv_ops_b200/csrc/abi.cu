@@ -16,9 +16,11 @@ inline int check_common(int B, int T, int H, int head_size, int dtype) {
   return RWKVB200_OK;
 }
 
+// AUTO: bf16 token tensors take the chunked tensor-core path; float32 (whose parity bar of 1e-4 a
+// bf16-operand path cannot meet) and float16 (whose range the scaled operands exceed) take the
+// float32 recurrence.
 inline int resolve_r7_algo(int algo, int dtype) {
-  (void)dtype;
-  if (algo == RWKVB200_ALGO_AUTO) return RWKVB200_ALGO_RECURRENT;
+  if (algo == RWKVB200_ALGO_AUTO) return dtype == RWKVB200_BF16 ? RWKVB200_ALGO_CHUNKED : RWKVB200_ALGO_RECURRENT;
   return algo;
 }
 

@@ -17,7 +17,7 @@ pytestmark = pytest.mark.gpu
 GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
 R7 = sorted(glob.glob(os.path.join(GOLDEN, "rwkv7_*.npz")))
 TOL = {torch.float32: 1e-4, torch.bfloat16: 2e-2, torch.float16: 2e-2}
-ALGOS = ["recurrent"]
+ALGOS = ["recurrent", "auto"]
 
 
 @pytest.fixture(autouse=True)
@@ -147,8 +147,9 @@ def test_decode_steps_match_oracle_and_chain():
         outs.append(o_t)
     o = torch.cat(outs, dim=1)
     assert rel_l2(o, o_ref) < 2e-2 and rel_l2(s, s_ref) < 1e-4
+    # the same 24 tokens in one call (bf16 tokens: chunked tensor-core path, bf16 tolerance)
     o_all, s_all = ro.generalized_delta_rule(*[x[n] for n in "rwkvab"], initial_state=d["initial_state"].cuda())
-    assert rel_l2(s, s_all) < 1e-5 and rel_l2(o, o_all) < 1e-2
+    assert rel_l2(s, s_all) < 2e-2 and rel_l2(o, o_all) < 2e-2
 
 
 def test_step_kernel_in_place_through_c_abi():
