@@ -294,7 +294,8 @@ r7c_bwd_final_kernel(const bf16* __restrict__ w, const __grid_constant__ CUtenso
                      const __grid_constant__ CUtensorMap tmap_v, const unsigned char* __restrict__ ws_tiles,
                      int tiles_per_chunk, bf16* __restrict__ dq, bf16* __restrict__ dw, bf16* __restrict__ dk,
                      bf16* __restrict__ dv, bf16* __restrict__ da, bf16* __restrict__ db,
-                     int Tn, int H, int NT, TokLayout lay, int* status) {
+                     int Tn, int H, int NT, TokLayout lay, int* status, long long* dbg) {
+#define R7C_STAMP(n) do { if (dbg && tid == 0 && blockIdx.x == gridDim.x / 2) dbg[n] = clock64(); } while (0)
   extern __shared__ unsigned char smem_raw[];
   FinalSmem& sm = *reinterpret_cast<FinalSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -326,6 +327,7 @@ r7c_bwd_final_kernel(const bf16* __restrict__ w, const __grid_constant__ CUtenso
     bulk_load(sm.dhh, tiles + S_DHH * TILE_BYTES, TILE_BYTES, &sm.bar_ld);
   }
 
+  R7C_STAMP(16);
   // ---- decay prefix sums (while the tiles arrive): gg = g, gs = inclusive prefix inside each half
   {
 #pragma unroll
@@ -338,8 +340,8 @@ r7c_bwd_final_kernel(const bf16* __restrict__ w, const __grid_constant__ CUtenso
       float g[8];
 #pragma unroll
       for (int m = 0; m < 4; ++m) {
-        g[2 * m] = valid ? -expf(bf16_lo(u[m])) : 0.f;
-        g[2 * m + 1] = valid ? -expf(bf16_hi(u[m])) : 0.f;
+        g[2 * m] = valid ? -__expf(bf16_lo(u[m])) : 0.f;
+        g[2 * m + 1] = valid ? -__expf(bf16_hi(u[m])) : 0.f;
       }
       *reinterpret_cast<float4*>(&sm.gg[row * NROW + 8 * cc]) = make_float4(g[0], g[1], g[2], g[3]);
       *reinterpret_cast<float4*>(&sm.gg[row * NROW + 8 * cc + 4]) = make_float4(g[4], g[5], g[6], g[7]);
@@ -357,8 +359,10 @@ r7c_bwd_final_kernel(const bf16* __restrict__ w, const __grid_constant__ CUtenso
     }
     sm.tot[half][c] = run;
   }
+  R7C_STAMP(17);
   bool ok = mbar_wait(&sm.bar_ld, 0, status, 321);
   __syncthreads();
+  R7C_STAMP(18);
 
   // ---- MMA group 1: all four dA products, and dv
   if (tid == 0 && ok) {
@@ -385,6 +389,7 @@ r7c_bwd_final_kernel(const bf16* __restrict__ w, const __grid_constant__ CUtenso
   }
   ok = mbar_wait(&sm.bar_m1, 0, status, 322) && ok;
   tc_fence_after();
+  R7C_STAMP(19);
   if (ok) {
     const int i = tid & 63;
     const bool lower = tid >= 64;     // rows of dz: strictly lower; rows of do: lower incl. diagonal
@@ -422,6 +427,7 @@ r7c_bwd_final_kernel(const bf16* __restrict__ w, const __grid_constant__ CUtenso
   tc_fence_before();
   __syncthreads();
 
+  R7C_STAMP(20);
   // ---- MMA group 2: [dq~; da~] (columns 0..63) and [dk~; db~] (columns 64..127)
   if (tid == 0 && ok) {
     tc_fence_after();
@@ -435,57 +441,65 @@ r7c_bwd_final_kernel(const bf16* __restrict__ w, const __grid_constant__ CUtenso
   }
   ok = mbar_wait(&sm.bar_m2, 0, status, 323) && ok;
   tc_fence_after();
+  R7C_STAMP(21);
 
   // ---- epilogue.  Thread r < 64 holds dq~_i and dk~_i (token i = r), thread r >= 64 holds da~_i, db~_i.
-  // red[i][c] (fp32, in the dA tiles' space) collects dgi + dge; dge goes to the [do;dz] space.
-  float* red = reinterpret_cast<float*>(sm.daqk);
+  // Row-owner threads read and write the fp32 scratch arrays as float4 (conflict-free with the padded
+  // rows).  red1 = dq~ q~ - dk~ k~ and red2 = da~ a~ - db~ b~ live in the dA tiles' space, dge = da~ a~
+  // in the [do; dz; v; sa] space: all those tiles are dead once MMA group 2 has completed.
+  float* red1 = reinterpret_cast<float*>(sm.daqk);
+  float* red2 = red1 + L * NROW;
   float* dge = reinterpret_cast<float*>(sm.dout);
-  const int i = tid & 63, tok = t0 + i;
-  const bool second = tid >= 64;
-  for (int phase = 0; phase < 2; ++phase) {
-    if (ok && (phase == 1) == second) {
+  if (ok) {
+    const int i = tid & 63, tok = t0 + i;
+    const bool second = tid >= 64;
+    float* red = second ? red2 : red1;
 #pragma unroll
-      for (int part = 0; part < 2; ++part) {
-        uint32_t r1[32], r2[32];
-        tmem_ld32(tmem_addr(tm, 32 * warp, 32 * part), r1);          // dq~ / da~
-        tmem_ld32(tmem_addr(tm, 32 * warp, 64 + 32 * part), r2);     // dk~ / db~
-        tmem_ld_wait();
-        float t1[32], t2[32], o1[32], o2[32];
-        tile_load_row32(second ? sm.at : sm.qt, i, 32 * part, t1);
-        tile_load_row32(second ? sm.bt : sm.kt, i, 32 * part, t2);
+    for (int part = 0; part < 2; ++part) {
+      uint32_t r1[32], r2[32];
+      tmem_ld32(tmem_addr(tm, 32 * warp, 32 * part), r1);          // dq~ / da~
+      tmem_ld32(tmem_addr(tm, 32 * warp, 64 + 32 * part), r2);     // dk~ / db~
+      tmem_ld_wait();
+      float t1[32], t2[32], o1[32], o2[32];
+      tile_load_row32(second ? sm.at : sm.qt, i, 32 * part, t1);
+      tile_load_row32(second ? sm.bt : sm.kt, i, 32 * part, t2);
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const int c = 32 * part + j;
-          const float d1 = sm.gs[i * NROW + c] - (i < 32 ? sm.tot[0][c] : 0.f);      // gi - gref
+      for (int j4 = 0; j4 < 32; j4 += 4) {
+        const int c = 32 * part + j4;
+        const float4 gs4 = *reinterpret_cast<const float4*>(&sm.gs[i * NROW + c]);
+        const float4 gg4 = *reinterpret_cast<const float4*>(&sm.gg[i * NROW + c]);
+        const float4 tt4 = *reinterpret_cast<const float4*>(&sm.tot[0][c]);
+        const float gsv[4] = {gs4.x, gs4.y, gs4.z, gs4.w}, ggv[4] = {gg4.x, gg4.y, gg4.z, gg4.w};
+        const float ttv[4] = {tt4.x, tt4.y, tt4.z, tt4.w};
+        float rd[4], ge[4];
+#pragma unroll
+        for (int m = 0; m < 4; ++m) {
+          const int j = j4 + m;
+          const float d1 = gsv[m] - (i < 32 ? ttv[m] : 0.f);            // gi - gref
           const float x1 = __uint_as_float(r1[j]), x2 = __uint_as_float(r2[j]);
-          const float ek = cexp(-d1);
-          if (!second) {
-            o1[j] = x1 * cexp(d1);                       // dq
-            o2[j] = x2 * ek;                             // dk
-            red[i * NROW + c] = x1 * t1[j] - x2 * t2[j]; // dq~ q~ - dk~ k~
-          } else {
-            o1[j] = x1 * cexp(d1 - sm.gg[i * NROW + c]); // da
-            o2[j] = x2 * ek;                             // db
-            const float ge_ = x1 * t1[j];                // da~ a~
-            dge[i * NROW + c] = ge_;
-            red[i * NROW + c] += ge_ - x2 * t2[j];
-          }
+          o2[j] = x2 * cexp(-d1);                                        // dk / db
+          o1[j] = x1 * (second ? cexp(d1 - ggv[m]) : cexp(d1));          // da / dq
+          ge[m] = x1 * t1[j];
+          rd[m] = ge[m] - x2 * t2[j];
         }
-        if (tok < Tn) {
-          const long long off = base + (long long)tok * lay.st + 32 * part;
-          store_row32_global((second ? da : dq) + off, o1);
-          store_row32_global((second ? db : dk) + off, o2);
-        }
+        *reinterpret_cast<float4*>(&red[i * NROW + c]) = make_float4(rd[0], rd[1], rd[2], rd[3]);
+        if (second) *reinterpret_cast<float4*>(&dge[i * NROW + c]) = make_float4(ge[0], ge[1], ge[2], ge[3]);
+      }
+      if (tok < Tn) {
+        const long long off = base + (long long)tok * lay.st + 32 * part;
+        store_row32_global((second ? da : dq) + off, o1);
+        store_row32_global((second ? db : dk) + off, o2);
       }
     }
-    __syncthreads();
   }
+  __syncthreads();
+  R7C_STAMP(22);
   // reverse inclusive prefix over tokens, per channel; thread = (channel, half)
   {
     const int c = tid & 63, half = tid >> 6;
     float rv[32];
 #pragma unroll
-    for (int j = 0; j < 32; ++j) rv[j] = red[(32 * half + j) * NROW + c];
+    for (int j = 0; j < 32; ++j) rv[j] = red1[(32 * half + j) * NROW + c] + red2[(32 * half + j) * NROW + c];
     float run = 0.f;
 #pragma unroll
     for (int j = 31; j >= 0; --j) { run += rv[j]; rv[j] = run; }
@@ -503,7 +517,9 @@ r7c_bwd_final_kernel(const bf16* __restrict__ w, const __grid_constant__ CUtenso
   }
   tc_fence_before();
   __syncthreads();
+  R7C_STAMP(23);
   if (warp == 0) tmem_dealloc(tm, 256);
+#undef R7C_STAMP
 }
 
 }  // namespace r7c
@@ -549,7 +565,7 @@ int launch_rwkv7_chunked_bwd(const void* r, const void* w, const void* k, const 
     ProfScope prof("r7c_bwd_final_kernel", st);
     r7c_bwd_final_kernel<<<B * H * NT, 128, smem, st>>>((const bf16*)w, tmap_do, tmap_v, ws.tiles, ALL_TILES,
                                                          (bf16*)dr, (bf16*)dw, (bf16*)dk, (bf16*)dv, (bf16*)da,
-                                                         (bf16*)db, Tn, H, NT, lay, status);
+                                                         (bf16*)db, Tn, H, NT, lay, status, debug_stamp_buffer());
   }
   return check_launch();
 }

@@ -87,8 +87,8 @@ r7c_intra_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ w, con
       float g[8];
 #pragma unroll
       for (int m = 0; m < 4; ++m) {
-        g[2 * m] = valid ? -expf(bf16_lo(u[m])) : 0.f;
-        g[2 * m + 1] = valid ? -expf(bf16_hi(u[m])) : 0.f;
+        g[2 * m] = valid ? -__expf(bf16_lo(u[m])) : 0.f;
+        g[2 * m + 1] = valid ? -__expf(bf16_hi(u[m])) : 0.f;
       }
       *reinterpret_cast<float4*>(&gs[row * NROW + 8 * cc]) = make_float4(g[0], g[1], g[2], g[3]);
       *reinterpret_cast<float4*>(&gs[row * NROW + 8 * cc + 4]) = make_float4(g[4], g[5], g[6], g[7]);
@@ -210,39 +210,54 @@ r7c_intra_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ w, con
     }
   }
   if (tid < 64) {
-    // ---- Ainv = (I - stril(A_ab))^-1 by forward substitution, one column per thread, fp32.
-    // Rows are taken four at a time: the sums over earlier rows are independent chains (their loads
-    // and multiply-adds overlap), then a 4x4 triangular fix-up couples the four new entries.
+    // ---- Ainv = (I - stril(A_ab))^-1 by blocked forward substitution in fp32, one column per thread.
+    // Rows go in four blocks of 16.  The block being solved lives in registers; finished blocks of
+    // the column are parked in shared memory (xs, in the space of the A_qk / A_ak tiles once MMA 2
+    // has read them) so that the block loops stay rolled and small enough for the instruction cache.
     const int c = tid;
-    float X[64];
+    float* xs = reinterpret_cast<float*>(sm.aqk);          // xs[row][column], 64 x 64 fp32
+    for (int I = 0; I < 4; ++I) {
+      R7C_STAMP(10 + I);
+      float xb[16];
 #pragma unroll
-    for (int ib = 0; ib < 16; ++ib) {
-      const int i0 = 4 * ib;
-      float acc[4][4];
+      for (int rr = 0; rr < 16; ++rr) xb[rr] = (16 * I + rr == c) ? 1.f : 0.f;
+      for (int J = 0; J < I; ++J) {
+        float xj[16];
 #pragma unroll
-      for (int rr = 0; rr < 4; ++rr) {
-        acc[rr][0] = (i0 + rr == c) ? 1.f : 0.f;
-        acc[rr][1] = acc[rr][2] = acc[rr][3] = 0.f;
-      }
+        for (int t = 0; t < 16; ++t) xj[t] = xs[(16 * J + t) * 64 + c];
 #pragma unroll
-      for (int jj = 0; jj < ib; ++jj) {
+        for (int rr = 0; rr < 16; ++rr) {
+          const float* nrow = &sm.nmat[(16 * I + rr) * NROW + 16 * J];
 #pragma unroll
-        for (int rr = 0; rr < 4; ++rr) {
-          const float4 n = *reinterpret_cast<const float4*>(&sm.nmat[(i0 + rr) * NROW + 4 * jj]);
-          acc[rr][0] += n.x * X[4 * jj]; acc[rr][1] += n.y * X[4 * jj + 1];
-          acc[rr][2] += n.z * X[4 * jj + 2]; acc[rr][3] += n.w * X[4 * jj + 3];
+          for (int jj = 0; jj < 4; ++jj) {
+            const float4 n = *reinterpret_cast<const float4*>(nrow + 4 * jj);
+            xb[rr] += n.x * xj[4 * jj] + n.y * xj[4 * jj + 1] + n.z * xj[4 * jj + 2] + n.w * xj[4 * jj + 3];
+          }
         }
       }
-      const float4 n1 = *reinterpret_cast<const float4*>(&sm.nmat[(i0 + 1) * NROW + i0]);
-      const float4 n2 = *reinterpret_cast<const float4*>(&sm.nmat[(i0 + 2) * NROW + i0]);
-      const float4 n3 = *reinterpret_cast<const float4*>(&sm.nmat[(i0 + 3) * NROW + i0]);
-      X[i0] = (acc[0][0] + acc[0][1]) + (acc[0][2] + acc[0][3]);
-      X[i0 + 1] = (acc[1][0] + acc[1][1]) + (acc[1][2] + acc[1][3]) + n1.x * X[i0];
-      X[i0 + 2] = (acc[2][0] + acc[2][1]) + (acc[2][2] + acc[2][3]) + n2.x * X[i0] + n2.y * X[i0 + 1];
-      X[i0 + 3] = (acc[3][0] + acc[3][1]) + (acc[3][2] + acc[3][3]) + n3.x * X[i0] + n3.y * X[i0 + 1] + n3.z * X[i0 + 2];
 #pragma unroll
-      for (int rr = 0; rr < 4; ++rr)
-        *reinterpret_cast<bf16*>(sm.ainv + tile_off(i0 + rr, c)) = __float2bfloat16_rn(X[i0 + rr]);
+      for (int rr = 1; rr < 16; ++rr) {
+        const float* nrow = &sm.nmat[(16 * I + rr) * NROW + 16 * I];
+#pragma unroll
+        for (int jj = 0; jj < (rr + 3) / 4; ++jj) {
+          const float4 n = *reinterpret_cast<const float4*>(nrow + 4 * jj);   // entries at or right of the diagonal are 0
+          xb[rr] += n.x * xb[4 * jj];
+          if (4 * jj + 1 < rr) xb[rr] += n.y * xb[4 * jj + 1];
+          if (4 * jj + 2 < rr) xb[rr] += n.z * xb[4 * jj + 2];
+          if (4 * jj + 3 < rr) xb[rr] += n.w * xb[4 * jj + 3];
+        }
+      }
+      if (I == 0) {
+        // first write to xs: MMA 2 (and the copies of A_qk / A_ak kept for the backward) must be done
+        ok = mbar_wait(&sm.bar_m2, 0, status, 205) && ok;
+        if (tid == 0 && keep_for_bwd) bulk_wait_read();
+        asm volatile("bar.sync 1, 64;" ::: "memory");
+      }
+#pragma unroll
+      for (int rr = 0; rr < 16; ++rr) {
+        if (I < 3) xs[(16 * I + rr) * 64 + c] = xb[rr];
+        *reinterpret_cast<bf16*>(sm.ainv + tile_off(16 * I + rr, c)) = __float2bfloat16_rn(xb[rr]);
+      }
     }
   }
   R7C_STAMP(5);
