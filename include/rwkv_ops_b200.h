@@ -54,7 +54,12 @@ enum {
 enum {
   RWKVB200_ALGO_AUTO = 0,       /* chunked tensor-core path for bf16/f16 tokens, recurrent for f32 */
   RWKVB200_ALGO_RECURRENT = 1,  /* token-by-token float32 recurrence (float32-exact) */
-  RWKVB200_ALGO_CHUNKED = 2     /* chunked tcgen05 path */
+  RWKVB200_ALGO_CHUNKED = 2,    /* chunked tcgen05 path */
+  /* Flag, OR-ed into algo (chunked path only).  Forward: also leave the per-chunk tiles the backward
+   * needs in the workspace (size it with the flag set).  Backward: the workspace still holds what that
+   * forward call left there, so skip the recomputation.  Without the flag the backward recomputes the
+   * forward from the inputs, as the reference does (rwkv_ops/rwkv7_kernel/torch_op.py:163-183). */
+  RWKVB200_ALGO_KEEP = 0x100
 };
 
 int rwkvb200_abi_version(void);

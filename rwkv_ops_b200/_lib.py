@@ -16,6 +16,7 @@ LIB_PATH = os.path.join(_PKG, "librwkv_ops_b200.so")
 
 F32, BF16, F16 = 0, 1, 2
 ALGO_AUTO, ALGO_RECURRENT, ALGO_CHUNKED = 0, 1, 2
+ALGO_KEEP = 0x100
 _DTYPE_CODE = {torch.float32: F32, torch.bfloat16: BF16, torch.float16: F16}
 
 # name -> (restype, argtypes); mirrors include/rwkv_ops_b200.h one to one

@@ -20,6 +20,7 @@ inline int check_common(int B, int T, int H, int head_size, int dtype) {
 // bf16-operand path cannot meet) and float16 (whose range the scaled operands exceed) take the
 // float32 recurrence.
 inline int resolve_r7_algo(int algo, int dtype) {
+  algo &= 0xff;
   if (algo == RWKVB200_ALGO_AUTO) return dtype == RWKVB200_BF16 ? RWKVB200_ALGO_CHUNKED : RWKVB200_ALGO_RECURRENT;
   return algo;
 }
@@ -73,7 +74,8 @@ int rwkvb200_rwkv7_step(const void* r, const void* w, const void* k, const void*
 
 size_t rwkvb200_rwkv7_fwd_workspace_bytes(int B, int T, int H, int head_size, int dtype, int algo) {
   if (check_common(B, T, H, head_size, dtype)) return 0;
-  if (resolve_r7_algo(algo, dtype) == RWKVB200_ALGO_CHUNKED) return r7c::fwd_workspace_bytes(B, T, H, r7c::FWD_TILES);
+  if (resolve_r7_algo(algo, dtype) == RWKVB200_ALGO_CHUNKED)
+    return r7c::fwd_workspace_bytes(B, T, H, (algo & RWKVB200_ALGO_KEEP) ? r7c::ALL_TILES : r7c::FWD_TILES);
   return 0;
 }
 
@@ -99,7 +101,7 @@ int rwkvb200_rwkv7_fwd(const void* r, const void* w, const void* k, const void* 
     case RWKVB200_ALGO_CHUNKED:
       if (dtype != RWKVB200_BF16) return RWKVB200_E_UNSUPPORTED;
       return launch_rwkv7_chunked_fwd(r, w, k, v, a, b, n_state ? h0 : nullptr, n_state, o, ht, workspace,
-                                      B, T, H, head_first, false, (cudaStream_t)stream);
+                                      B, T, H, head_first, (algo & RWKVB200_ALGO_KEEP) != 0, (cudaStream_t)stream);
     default:
       return RWKVB200_E_UNSUPPORTED;
   }
@@ -144,7 +146,8 @@ int rwkvb200_rwkv7_bwd(const void* r, const void* w, const void* k, const void* 
     case RWKVB200_ALGO_CHUNKED:
       if (dtype != RWKVB200_BF16) return RWKVB200_E_UNSUPPORTED;
       return launch_rwkv7_chunked_bwd(r, w, k, v, a, b, n_state ? h0 : nullptr, n_state, d_o, d_ht,
-                                      dr, dw, dk, dv, da, db, d_h0, workspace, B, T, H, head_first, st);
+                                      dr, dw, dk, dv, da, db, d_h0, workspace, B, T, H, head_first,
+                                      (algo & RWKVB200_ALGO_KEEP) != 0, st);
     default:
       return RWKVB200_E_UNSUPPORTED;
   }

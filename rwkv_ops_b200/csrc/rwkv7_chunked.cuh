@@ -83,7 +83,7 @@ inline Workspace carve(void* ws, int B, int T, int H, int tiles_per_chunk) {
 int launch_rwkv7_chunked_bwd(const void* r, const void* w, const void* k, const void* v, const void* a, const void* b,
                              const float* h0, int n_state, const void* d_o, const float* d_ht,
                              void* dr, void* dw, void* dk, void* dv, void* da, void* db, float* d_h0,
-                             void* workspace, int B, int Tn, int H, int head_first, cudaStream_t st);
+                             void* workspace, int B, int Tn, int H, int head_first, bool kept, cudaStream_t st);
 
 int launch_rwkv7_chunked_fwd(const void* r, const void* w, const void* k, const void* v, const void* a, const void* b,
                              const float* h0, int n_state, void* o, float* ht, void* workspace,

@@ -527,12 +527,15 @@ r7c_bwd_final_kernel(const bf16* __restrict__ w, const __grid_constant__ CUtenso
 int launch_rwkv7_chunked_bwd(const void* r, const void* w, const void* k, const void* v, const void* a, const void* b,
                              const float* h0, int n_state, const void* d_o, const float* d_ht,
                              void* dr, void* dw, void* dk, void* dv, void* da, void* db, float* d_h0,
-                             void* workspace, int B, int Tn, int H, int head_first, cudaStream_t st) {
+                             void* workspace, int B, int Tn, int H, int head_first, bool kept, cudaStream_t st) {
   using namespace r7c;
   typedef __nv_bfloat16 bf16;
-  int e = launch_rwkv7_chunked_fwd(r, w, k, v, a, b, h0, n_state, nullptr, nullptr, workspace, B, Tn, H, head_first,
-                                   true, st);
-  if (e) return e;
+  int e = RWKVB200_OK;
+  if (!kept) {   // the workspace does not hold a forward pass yet: recompute it from the inputs
+    e = launch_rwkv7_chunked_fwd(r, w, k, v, a, b, h0, n_state, nullptr, nullptr, workspace, B, Tn, H, head_first,
+                                 true, st);
+    if (e) return e;
+  }
   int* status = device_status_ptr();
   if (!status) { last_cuda_error_slot() = 99999; return RWKVB200_E_CUDA; }
   CUtensorMap tmap_do, tmap_v;

@@ -29,6 +29,12 @@ def _workspace(nbytes: int, device) -> Optional[torch.Tensor]:
     return torch.empty(nbytes, dtype=torch.uint8, device=device) if nbytes else None
 
 
+def _keep_limit_bytes() -> int:
+    """Largest per-call tile store (MiB, ``RWKV_OPS_B200_KEEP_LIMIT_MB``) that a training forward may
+    hand to its backward instead of having the backward recompute the forward."""
+    return int(os.environ.get("RWKV_OPS_B200_KEEP_LIMIT_MB", "16384")) << 20
+
+
 # --------------------------------------------------------------------------------------------
 # custom ops (tensors are contiguous token tensors of one dtype; states float32)
 # --------------------------------------------------------------------------------------------
@@ -70,6 +76,106 @@ def _(r, w, k, v, a, b, h0, head_first, algo):
     else:
         B, T, H, K = r.shape
     return torch.empty_like(r), r.new_empty((B, H, K, K), dtype=torch.float32)
+
+
+# Training forward of the chunked path: same results, and the per-chunk tiles the backward needs are
+# returned in `kept` (an opaque byte tensor) so that the backward does not recompute the forward.
+@torch.library.custom_op("rwkv_ops_b200::rwkv7_fwd_keep", mutates_args=())
+def _rwkv7_fwd_keep(r: torch.Tensor, w: torch.Tensor, k: torch.Tensor, v: torch.Tensor, a: torch.Tensor,
+                    b: torch.Tensor, h0: Optional[torch.Tensor], head_first: bool, algo: int
+                    ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    lib = _lib.load()
+    dev = _lib.require_cuda(r, w, k, v, a, b, h0)
+    if head_first:
+        B, H, T, K = r.shape
+    else:
+        B, T, H, K = r.shape
+    code = _lib.dtype_code(r.dtype)
+    o = torch.empty_like(r)
+    ht = torch.empty(B, H, K, K, dtype=torch.float32, device=dev)
+    n_state = 0 if h0 is None else h0.shape[0]
+    flags = algo | _lib.ALGO_KEEP
+    with torch.cuda.device(dev):
+        nws = lib.rwkvb200_rwkv7_fwd_workspace_bytes(B, T, H, K, code, flags)
+        kept = torch.empty(nws, dtype=torch.uint8, device=dev)
+        rc = lib.rwkvb200_rwkv7_fwd(r.data_ptr(), w.data_ptr(), k.data_ptr(), v.data_ptr(), a.data_ptr(),
+                                    b.data_ptr(), _lib.ptr(h0), n_state, o.data_ptr(), ht.data_ptr(),
+                                    kept.data_ptr(), nws, B, T, H, K, code, int(head_first), flags,
+                                    _lib.stream_ptr(dev))
+        _lib.check(rc, "rwkv7_fwd")
+    return o, ht, kept
+
+
+@_rwkv7_fwd_keep.register_fake
+def _(r, w, k, v, a, b, h0, head_first, algo):
+    if head_first:
+        B, H, T, K = r.shape
+    else:
+        B, T, H, K = r.shape
+    return (torch.empty_like(r), r.new_empty((B, H, K, K), dtype=torch.float32),
+            r.new_empty((1,), dtype=torch.uint8))
+
+
+# `kept` also serves as scratch for the backward kernels; the tiles the forward left in it are not changed.
+@torch.library.custom_op("rwkv_ops_b200::rwkv7_bwd_kept", mutates_args=())
+def _rwkv7_bwd_kept(r: torch.Tensor, w: torch.Tensor, k: torch.Tensor, v: torch.Tensor, a: torch.Tensor,
+                    b: torch.Tensor, h0: Optional[torch.Tensor], d_o: torch.Tensor, d_ht: Optional[torch.Tensor],
+                    kept: torch.Tensor, head_first: bool, algo: int
+                    ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor,
+                               torch.Tensor]:
+    lib = _lib.load()
+    dev = _lib.require_cuda(r, w, k, v, a, b, h0, d_o, d_ht, kept)
+    if head_first:
+        B, H, T, K = r.shape
+    else:
+        B, T, H, K = r.shape
+    code = _lib.dtype_code(r.dtype)
+    dr, dw, dk, dv, da, db = (torch.empty_like(r) for _ in range(6))
+    dh0 = torch.empty(B, H, K, K, dtype=torch.float32, device=dev)
+    n_state = 0 if h0 is None else h0.shape[0]
+    with torch.cuda.device(dev):
+        rc = lib.rwkvb200_rwkv7_bwd(r.data_ptr(), w.data_ptr(), k.data_ptr(), v.data_ptr(), a.data_ptr(),
+                                    b.data_ptr(), _lib.ptr(h0), n_state, d_o.data_ptr(), _lib.ptr(d_ht),
+                                    dr.data_ptr(), dw.data_ptr(), dk.data_ptr(), dv.data_ptr(), da.data_ptr(),
+                                    db.data_ptr(), dh0.data_ptr(), kept.data_ptr(), kept.numel(),
+                                    B, T, H, K, code, int(head_first), algo | _lib.ALGO_KEEP, _lib.stream_ptr(dev))
+        _lib.check(rc, "rwkv7_bwd")
+    return dr, dw, dk, dv, da, db, dh0
+
+
+@_rwkv7_bwd_kept.register_fake
+def _(r, w, k, v, a, b, h0, d_o, d_ht, kept, head_first, algo):
+    if head_first:
+        B, H, T, K = r.shape
+    else:
+        B, T, H, K = r.shape
+    e = torch.empty_like
+    return e(r), e(r), e(r), e(r), e(r), e(r), r.new_empty((B, H, K, K), dtype=torch.float32)
+
+
+def _setup_ctx_keep(ctx, inputs, output):
+    r, w, k, v, a, b, h0, head_first, algo = inputs
+    ctx.save_for_backward(r, w, k, v, a, b, h0, output[2])
+    ctx.head_first = head_first
+    ctx.algo = algo
+
+
+def _backward_keep(ctx, d_o, d_ht, d_kept):
+    r, w, k, v, a, b, h0, kept = ctx.saved_tensors
+    if d_o is None:
+        d_o = torch.zeros_like(r)
+    d_o = d_o.to(r.dtype).contiguous()
+    if d_ht is not None:
+        d_ht = d_ht.to(torch.float32).contiguous()
+    dr, dw, dk, dv, da, db, dh0 = _rwkv7_bwd_kept(r, w, k, v, a, b, h0, d_o, d_ht, kept, ctx.head_first, ctx.algo)
+    if h0 is None or not ctx.needs_input_grad[6]:
+        dh0 = None
+    elif h0.shape[0] == 1 and dh0.shape[0] != 1:
+        dh0 = dh0.sum(0, keepdim=True)
+    return dr, dw, dk, dv, da, db, dh0, None, None
+
+
+torch.library.register_autograd("rwkv_ops_b200::rwkv7_fwd_keep", _backward_keep, setup_context=_setup_ctx_keep)
 
 
 @torch.library.custom_op("rwkv_ops_b200::rwkv7_bwd", mutates_args=())
@@ -174,7 +280,18 @@ def generalized_delta_rule(
             raise ValueError(
                 f"initial_state must be [B or 1, {H}, {HEAD_SIZE}, {HEAD_SIZE}], got {tuple(initial_state.shape)}")
         h0 = initial_state.to(torch.float32).contiguous()
-    o, ht = _rwkv7_fwd(r_, w_, k_, v_, a_, b_, h0, bool(head_first), _default_algo())
+    algo = _default_algo()
+    T = r.shape[2] if head_first else r.shape[1]
+    needs_grad = torch.is_grad_enabled() and (
+        any(x.requires_grad for x in (r_, w_, k_, v_, a_, b_)) or (h0 is not None and h0.requires_grad))
+    keep = False
+    if needs_grad and T > 1 and cdt == torch.bfloat16 and algo in (_lib.ALGO_AUTO, _lib.ALGO_CHUNKED):
+        nws = _lib.load().rwkvb200_rwkv7_fwd_workspace_bytes(B, T, H, HEAD_SIZE, _lib.BF16, algo | _lib.ALGO_KEEP)
+        keep = nws <= _keep_limit_bytes()
+    if keep:
+        o, ht, _ = _rwkv7_fwd_keep(r_, w_, k_, v_, a_, b_, h0, bool(head_first), algo)
+    else:
+        o, ht = _rwkv7_fwd(r_, w_, k_, v_, a_, b_, h0, bool(head_first), algo)
     if o.dtype != out_dtype:
         o = o.to(out_dtype)
     if output_final_state:

@@ -91,3 +91,30 @@ def test_backward_full_size_sampled_units():
                                       d["d_state"][b:b + 1, h:h + 1].cpu())
         errs = {n: rel_l2(g[n].grad[b:b + 1, :, h:h + 1], gr) for n, gr in zip("rwkvab", grads[:6])}
         assert all(e < 2e-2 for e in errs.values()), errs
+
+
+def test_kept_tiles_and_recompute_agree(monkeypatch):
+    """A training forward hands its per-chunk tiles to the backward; with the limit at zero the backward
+    recomputes them from the inputs.  Both give the same gradients, and a second backward through the
+    same graph works."""
+    B, T, H = 2, 200, 2
+    d = rwkv7_inputs(B, T, H, dtype=torch.bfloat16, seed=91, with_state=True, with_grads=True)
+
+    def run():
+        g = {n: d[n].cuda().requires_grad_(True) for n in "rwkvab"}
+        h0 = d["initial_state"].cuda().requires_grad_(True)
+        o, s = ro.generalized_delta_rule(*[g[n] for n in "rwkvab"], initial_state=h0)
+        torch.autograd.backward([o, s], [d["d_out"].cuda(), d["d_state"].cuda()], retain_graph=True)
+        first = [g[n].grad.clone() for n in "rwkvab"] + [h0.grad.clone()]
+        for t in list(g.values()) + [h0]:
+            t.grad = None
+        torch.autograd.backward([o, s], [d["d_out"].cuda(), d["d_state"].cuda()])
+        second = [g[n].grad for n in "rwkvab"] + [h0.grad]
+        return o, s, first, second
+
+    o1, s1, kept_first, kept_second = run()
+    monkeypatch.setenv("RWKV_OPS_B200_KEEP_LIMIT_MB", "0")
+    o2, s2, rec_first, _ = run()
+    assert torch.equal(o1, o2) and torch.equal(s1, s2)
+    for a_, b_, c_ in zip(kept_first, kept_second, rec_first):
+        assert torch.equal(a_, b_) and torch.equal(a_, c_)
