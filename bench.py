@@ -238,44 +238,75 @@ def run_ours(args, wl):
                 "kernels": {k_: {"ms_per_step": v[0] / args.steps, "launches_per_step": v[1] / args.steps}
                             for k_, v in prof.items()}}
 
-    # ---- end to end: host buffers in, host buffers out, through the public API
+    # ---- end to end: host buffers in, host buffers out, through the public API.
+    # Every step copies all of its inputs from pinned host memory and all of its results back to
+    # pinned host memory.  Steps are independent, so they are software-pipelined over three streams:
+    # the upload of step i+1 and the download of step i-1 overlap the compute of step i (PCIe is
+    # full duplex); two sets of device and host buffers alternate.
     host_in = {n: d[n].detach().to("cpu").pin_memory() for n in names}
     host_in["d_out"] = d_out.to("cpu").pin_memory()
     host_in["d_state"] = d_state.to("cpu").pin_memory()
     if h0 is not None:
         host_in["h0"] = h0.detach().to("cpu").pin_memory()
-    host_out = {n: torch.empty_like(host_in[n]).pin_memory() for n in names}
-    host_out["o"] = torch.empty_like(host_in["r"]).pin_memory()
-    host_out["ht"] = torch.empty(B, H, 64, 64).pin_memory()
-    if h0 is not None:
-        host_out["dh0"] = torch.empty_like(host_in["h0"]).pin_memory()
+    out_names = list(names) + ["o", "ht"] + (["dh0"] if h0 is not None else [])
+
+    def host_out_set():
+        ho = {n: torch.empty_like(host_in[n]).pin_memory() for n in names}
+        ho["o"] = torch.empty_like(host_in["r"]).pin_memory()
+        ho["ht"] = torch.empty(B, H, 64, 64).pin_memory()
+        if h0 is not None:
+            ho["dh0"] = torch.empty_like(host_in["h0"]).pin_memory()
+        return ho
+
+    host_out = [host_out_set(), host_out_set()]
+    dev_in = [{n: torch.empty_like(t, device=dev) for n, t in host_in.items()} for _ in range(2)]
     h2d = sum(t.numel() * t.element_size() for t in host_in.values())
-    d2h = sum(t.numel() * t.element_size() for t in host_out.values())
+    d2h = sum(t.numel() * t.element_size() for t in host_out[0].values())
+    s_up, s_run, s_down = torch.cuda.Stream(dev), torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+    ev_up = [torch.cuda.Event() for _ in range(2)]
+    ev_run = [torch.cuda.Event() for _ in range(2)]
+    ev_down = [torch.cuda.Event() for _ in range(2)]
+    results = [None, None]
 
-    def e2e_step():
-        dv = {n: host_in[n].to(dev, non_blocking=True) for n in host_in}
-        lv = {n: dv[n].requires_grad_(True) for n in names}
-        s0 = dv.get("h0")
-        if s0 is not None:
-            s0.requires_grad_(True)
-        o, s = ro.generalized_delta_rule(*[lv[n] for n in names], initial_state=s0)
-        torch.autograd.backward([o, s], [dv["d_out"], dv["d_state"]])
-        host_out["o"].copy_(o.detach(), non_blocking=True)
-        host_out["ht"].copy_(s.detach(), non_blocking=True)
-        for n in names:
-            host_out[n].copy_(lv[n].grad, non_blocking=True)
-        if s0 is not None:
-            host_out["dh0"].copy_(s0.grad, non_blocking=True)
-        torch.cuda.current_stream().synchronize()   # results are on the host when the step ends
+    def e2e_run(nsteps):
+        for i in range(nsteps):
+            sl = i & 1
+            with torch.cuda.stream(s_up):
+                s_up.wait_event(ev_run[sl])          # the compute that last read this input set is done
+                for n, t in host_in.items():
+                    dev_in[sl][n].copy_(t, non_blocking=True)
+                ev_up[sl].record(s_up)
+            with torch.cuda.stream(s_run):
+                s_run.wait_event(ev_up[sl])
+                s_run.wait_event(ev_down[sl])        # the download that last read this result set is done
+                dv = dev_in[sl]
+                lv = {n: dv[n].detach().requires_grad_(True) for n in names}
+                s0 = dv.get("h0")
+                if s0 is not None:
+                    s0 = s0.detach().requires_grad_(True)
+                o, s = ro.generalized_delta_rule(*[lv[n] for n in names], initial_state=s0)
+                torch.autograd.backward([o, s], [dv["d_out"], dv["d_state"]])
+                res = {n: lv[n].grad for n in names}
+                res["o"], res["ht"] = o.detach(), s.detach()
+                if s0 is not None:
+                    res["dh0"] = s0.grad
+                results[sl] = res
+                ev_run[sl].record(s_run)
+            with torch.cuda.stream(s_down):
+                s_down.wait_event(ev_run[sl])
+                for n in out_names:
+                    host_out[sl][n].copy_(results[sl][n], non_blocking=True)
+                    results[sl][n].record_stream(s_down)
+                ev_down[sl].record(s_down)
+        for st_ in (s_up, s_run, s_down):
+            st_.synchronize()                        # every result is in host memory
 
-    e2e_steps = max(2, min(args.steps, 5))
-    for _ in range(2):
-        e2e_step()
+    e2e_steps = max(4, min(args.steps, 10))
+    e2e_run(3)
     barrier()
     t0 = time.perf_counter()
     ev0.record()
-    for _ in range(e2e_steps):
-        e2e_step()
+    e2e_run(e2e_steps)
     ev1.record()
     barrier()
     e2e_ms = max_over_ranks(max(ev0.elapsed_time(ev1), 1e3 * (time.perf_counter() - t0))) / e2e_steps
@@ -292,7 +323,8 @@ def run_ours(args, wl):
                        "algo": os.environ.get("RWKV_OPS_B200_RWKV7_ALGO", "auto")},
             "clocks": clocks.summary(),
             "e2e": {"value": e2e_val, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "ms_per_step": e2e_ms, "steps": e2e_steps},
+                    "ms_per_step": e2e_ms, "steps": e2e_steps,
+                    "pipeline": "upload / compute / download of consecutive steps overlap on three streams"},
             "gpu_launches": launches,
             "roofline": roof,
         }
