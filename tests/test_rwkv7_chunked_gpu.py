@@ -118,3 +118,31 @@ def test_kept_tiles_and_recompute_agree(monkeypatch):
     assert torch.equal(o1, o2) and torch.equal(s1, s2)
     for a_, b_, c_ in zip(kept_first, kept_second, rec_first):
         assert torch.equal(a_, b_) and torch.equal(a_, c_)
+
+
+def test_cfg2_full_size_padded_with_state():
+    """Configuration 2 at full size (bf16, B16 T8192 H64, per-sequence initial state, trailing 0..512
+    tokens of every sequence padded through w += -1e9): outputs, final state and gradients of sampled
+    (batch, head) units against the oracle run on those units alone."""
+    from oracle import rwkv7_manual_backward
+    from rwkv_ops_b200.workloads import rwkv7_pad_lengths, apply_w_padding
+    B, T, H = 16, 8192, 64
+    d = rwkv7_inputs(B, T, H, dtype=torch.bfloat16, seed=1002, device="cuda", with_state=True, with_grads=True)
+    lengths = rwkv7_pad_lengths(B, T, seed=1002)
+    d["w"] = apply_w_padding(d["w"], lengths)
+    g = {n: d[n].requires_grad_(True) for n in "rwkvab"}
+    h0 = d["initial_state"].requires_grad_(True)
+    o, s = ro.generalized_delta_rule(*[g[n] for n in "rwkvab"], initial_state=h0)
+    torch.autograd.backward([o, s], [d["d_out"], d["d_state"]])
+    assert torch.isfinite(o).all() and torch.isfinite(s).all()
+    for (b, h) in [(0, 0), (9, 33), (15, 63)]:
+        sub = [g[n].detach()[b:b + 1, :, h:h + 1].cpu() for n in "rwkvab"]
+        h0s = h0.detach()[b:b + 1, h:h + 1].cpu()
+        o_ref, s_ref = oracle_gdr(*sub, initial_state=h0s)
+        assert rel_l2(o[b:b + 1, :, h:h + 1], o_ref) < 2e-2
+        assert rel_l2(s[b:b + 1, h:h + 1], s_ref) < 2e-2
+        grads = rwkv7_manual_backward(*sub, h0s, d["d_out"][b:b + 1, :, h:h + 1].cpu(),
+                                      d["d_state"][b:b + 1, h:h + 1].cpu())
+        errs = {n: rel_l2(g[n].grad[b:b + 1, :, h:h + 1], gr) for n, gr in zip("rwkvab", grads[:6])}
+        errs["h0"] = rel_l2(h0.grad[b:b + 1, h:h + 1], grads[6])
+        assert all(e < 2e-2 for e in errs.values()), errs
