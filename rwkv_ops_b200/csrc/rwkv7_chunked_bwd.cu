@@ -280,16 +280,18 @@ struct FinalSmem {
   unsigned char aqk[TILE_BYTES], aak[TILE_BYTES];                 // adjacent workspace slots
   unsigned char qt[TILE_BYTES], at[TILE_BYTES], kt[TILE_BYTES], bt[TILE_BYTES];
   unsigned char h0[TILE_BYTES], dhh[TILE_BYTES];
-  float gs[L * NROW];       // inclusive prefix of g inside each half of the chunk
+  float gs[L * NROW];       // gi - (start of the half): inclusive prefix of g inside each half of the chunk
   float gg[L * NROW];       // g
-  float tot[2][64];
-  float rtot[64];
+  float qtot[4][64];        // sums of g over the four quarters of the chunk
+  float rqtot[4][64];       // sums of the decay-gradient terms over the four quarters
   float dgl[64];            // dglast
   uint64_t bar_ld, bar_m1, bar_m2;
   uint32_t tmem_base;
 };
 
-__global__ void __launch_bounds__(128)
+// 256 threads: warp w reads TMEM lanes 32*(w&3).. (its row), and the two warps that share a lane
+// window split the columns (hsel = w>>2), so every elementwise phase is spread over 8 warps.
+__global__ void __launch_bounds__(256)
 r7c_bwd_final_kernel(const bf16* __restrict__ w, const __grid_constant__ CUtensorMap tmap_do,
                      const __grid_constant__ CUtensorMap tmap_v, const unsigned char* __restrict__ ws_tiles,
                      int tiles_per_chunk, bf16* __restrict__ dq, bf16* __restrict__ dw, bf16* __restrict__ dk,
@@ -299,6 +301,7 @@ r7c_bwd_final_kernel(const bf16* __restrict__ w, const __grid_constant__ CUtenso
   extern __shared__ unsigned char smem_raw[];
   FinalSmem& sm = *reinterpret_cast<FinalSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int wq = warp & 3, hsel = warp >> 2;
   const int ch = blockIdx.x, unit = ch / NT, cidx = ch % NT, bi = unit / H, hi = unit % H, t0 = cidx * L;
   const long long base = bi * lay.sb + hi * lay.sh;
   const unsigned char* tiles = ws_tiles + (size_t)ch * tiles_per_chunk * TILE_BYTES;
@@ -326,38 +329,24 @@ r7c_bwd_final_kernel(const bf16* __restrict__ w, const __grid_constant__ CUtenso
     bulk_load(sm.h0, tiles + S_H0 * TILE_BYTES, TILE_BYTES, &sm.bar_ld);
     bulk_load(sm.dhh, tiles + S_DHH * TILE_BYTES, TILE_BYTES, &sm.bar_ld);
   }
-
   R7C_STAMP(16);
-  // ---- decay prefix sums (while the tiles arrive): gg = g, gs = inclusive prefix inside each half
-  {
+
+  // ---- g of every (token, channel) while the tiles arrive
 #pragma unroll
-    for (int n = 0; n < 4; ++n) {
-      const int e = tid + 128 * n, row = e >> 3, cc = e & 7, tok = t0 + row;
-      const bool valid = tok < Tn;
-      uint4 rw = make_uint4(0u, 0u, 0u, 0u);
-      if (valid) rw = __ldg(reinterpret_cast<const uint4*>(w + base + (long long)tok * lay.st + 8 * cc));
-      const uint32_t u[4] = {rw.x, rw.y, rw.z, rw.w};
-      float g[8];
+  for (int n = 0; n < 2; ++n) {
+    const int e = tid + 256 * n, row = e >> 3, cc = e & 7, tok = t0 + row;
+    const bool valid = tok < Tn;
+    uint4 rw = make_uint4(0u, 0u, 0u, 0u);
+    if (valid) rw = __ldg(reinterpret_cast<const uint4*>(w + base + (long long)tok * lay.st + 8 * cc));
+    const uint32_t u[4] = {rw.x, rw.y, rw.z, rw.w};
+    float g[8];
 #pragma unroll
-      for (int m = 0; m < 4; ++m) {
-        g[2 * m] = valid ? -__expf(bf16_lo(u[m])) : 0.f;
-        g[2 * m + 1] = valid ? -__expf(bf16_hi(u[m])) : 0.f;
-      }
-      *reinterpret_cast<float4*>(&sm.gg[row * NROW + 8 * cc]) = make_float4(g[0], g[1], g[2], g[3]);
-      *reinterpret_cast<float4*>(&sm.gg[row * NROW + 8 * cc + 4]) = make_float4(g[4], g[5], g[6], g[7]);
+    for (int m = 0; m < 4; ++m) {
+      g[2 * m] = valid ? -__expf(bf16_lo(u[m])) : 0.f;
+      g[2 * m + 1] = valid ? -__expf(bf16_hi(u[m])) : 0.f;
     }
-    __syncthreads();
-    const int c = tid & 63, half = tid >> 6;
-    float gv[32];
-#pragma unroll
-    for (int j = 0; j < 32; ++j) gv[j] = sm.gg[(32 * half + j) * NROW + c];
-    float run = 0.f;
-#pragma unroll
-    for (int j = 0; j < 32; ++j) {
-      run += gv[j];
-      sm.gs[(32 * half + j) * NROW + c] = run;
-    }
-    sm.tot[half][c] = run;
+    *reinterpret_cast<float4*>(&sm.gg[row * NROW + 8 * cc]) = make_float4(g[0], g[1], g[2], g[3]);
+    *reinterpret_cast<float4*>(&sm.gg[row * NROW + 8 * cc + 4]) = make_float4(g[4], g[5], g[6], g[7]);
   }
   R7C_STAMP(17);
   bool ok = mbar_wait(&sm.bar_ld, 0, status, 321);
@@ -372,62 +361,76 @@ r7c_bwd_final_kernel(const bf16* __restrict__ w, const __grid_constant__ CUtenso
     umma_tile<64, 64, 0, 1>(tmem_addr(tm, 0, 128), smem_u32(sm.kt), smem_u32(sm.dhh), true);         // + k~ dh^
     umma_commit(&sm.bar_m1);
   }
-  // dglast[c] = sum_v dh^[c][v] X[c][v]  (threads 0..63, X straight from the workspace)
-  if (tid < 64 && ok) {
+  // ---- meanwhile: prefix sums of g over tokens, thread = (channel, quarter of the chunk)
+  {
+    const int c = tid & 63, quarter = tid >> 6;
+    float gv[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) gv[j] = sm.gg[(16 * quarter + j) * NROW + c];
+    float run = 0.f;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) { run += gv[j]; gv[j] = run; }
+    sm.qtot[quarter][c] = run;
+    __syncthreads();
+    const float add = (quarter & 1) ? sm.qtot[quarter - 1][c] : 0.f;    // start of the half
+#pragma unroll
+    for (int j = 0; j < 16; ++j) sm.gs[(16 * quarter + j) * NROW + c] = gv[j] + add;
+  }
+  // dglast[c] = sum_v dh^[c][v] X[c][v]  (X straight from the workspace)
+  if (tid >= 128 && tid < 192 && ok) {
+    const int c = tid - 128;
     float s = 0.f;
     const uint4* xr = reinterpret_cast<const uint4*>(tiles + S_X * TILE_BYTES);
 #pragma unroll
     for (int cchunk = 0; cchunk < 8; ++cchunk) {
-      const uint4 xa = __ldg(xr + (tile_chunk_off(tid, cchunk) >> 4));
-      const uint4 da_ = *reinterpret_cast<const uint4*>(sm.dhh + tile_chunk_off(tid, cchunk));
+      const uint4 xa = __ldg(xr + (tile_chunk_off(c, cchunk) >> 4));
+      const uint4 da_ = *reinterpret_cast<const uint4*>(sm.dhh + tile_chunk_off(c, cchunk));
       s += bf16_lo(xa.x) * bf16_lo(da_.x) + bf16_hi(xa.x) * bf16_hi(da_.x);
       s += bf16_lo(xa.y) * bf16_lo(da_.y) + bf16_hi(xa.y) * bf16_hi(da_.y);
       s += bf16_lo(xa.z) * bf16_lo(da_.z) + bf16_hi(xa.z) * bf16_hi(da_.z);
       s += bf16_lo(xa.w) * bf16_lo(da_.w) + bf16_hi(xa.w) * bf16_hi(da_.w);
     }
-    sm.dgl[tid] = s;
+    sm.dgl[c] = s;
   }
   ok = mbar_wait(&sm.bar_m1, 0, status, 322) && ok;
   tc_fence_after();
   R7C_STAMP(19);
   if (ok) {
-    const int i = tid & 63;
-    const bool lower = tid >= 64;     // rows of dz: strictly lower; rows of do: lower incl. diagonal
+    const int r = 32 * wq + lane, i = r & 63;
+    const bool lower = r >= 64;       // rows of dz: strictly lower; rows of do: lower incl. diagonal
 #pragma unroll
-    for (int part = 0; part < 4; ++part) {
-      uint32_t r[32];
-      tmem_ld32(tmem_addr(tm, 32 * warp, 32 * part), r);
+    for (int pp = 0; pp < 2; ++pp) {
+      const int part = 2 * hsel + pp;   // hsel 0: products with v (dA_qk / dA_ak); hsel 1: with sa (dA_qb / dA_ab)
+      uint32_t rr[32];
+      tmem_ld32(tmem_addr(tm, 32 * wq, 32 * part), rr);
       tmem_ld_wait();
       float x[32];
-      const int j0 = 32 * (part & 1);
+      const int j0 = 32 * pp;
 #pragma unroll
       for (int j = 0; j < 32; ++j) {
         const bool keep = lower ? (j0 + j < i) : (j0 + j <= i);
-        x[j] = keep ? __uint_as_float(r[j]) : 0.f;
+        x[j] = keep ? __uint_as_float(rr[j]) : 0.f;
       }
-      unsigned char* dst = lower ? (part < 2 ? sm.daak : sm.daab) : (part < 2 ? sm.daqk : sm.daqb);
+      unsigned char* dst = lower ? (hsel ? sm.daab : sm.daak) : (hsel ? sm.daqb : sm.daqk);
       tile_store_row32(dst, i, j0, x);
     }
-    // dv rows sit on the lower lane halves of columns 128..191
-    const int row = 16 * warp + (lane & 15), tok = t0 + row;
+    // dv rows sit on the lower lane halves of columns 128..191; each warp of a pair takes 32 columns
+    const int row = 16 * wq + (lane & 15), tok = t0 + row;
+    uint32_t rr[32];
+    tmem_ld32(tmem_addr(tm, 32 * wq, 128 + 32 * hsel), rr);
+    tmem_ld_wait();
+    if (lane < 16 && tok < Tn) {
+      float x[32];
 #pragma unroll
-    for (int part = 0; part < 2; ++part) {
-      uint32_t r[32];
-      tmem_ld32(tmem_addr(tm, 32 * warp, 128 + 32 * part), r);
-      tmem_ld_wait();
-      if (lane < 16 && tok < Tn) {
-        float x[32];
-#pragma unroll
-        for (int j = 0; j < 32; ++j) x[j] = __uint_as_float(r[j]);
-        store_row32_global(dv + base + (long long)tok * lay.st + 32 * part, x);
-      }
+      for (int j = 0; j < 32; ++j) x[j] = __uint_as_float(rr[j]);
+      store_row32_global(dv + base + (long long)tok * lay.st + 32 * hsel, x);
     }
   }
   fence_async_smem();
   tc_fence_before();
   __syncthreads();
-
   R7C_STAMP(20);
+
   // ---- MMA group 2: [dq~; da~] (columns 0..63) and [dk~; db~] (columns 64..127)
   if (tid == 0 && ok) {
     tc_fence_after();
@@ -443,72 +446,73 @@ r7c_bwd_final_kernel(const bf16* __restrict__ w, const __grid_constant__ CUtenso
   tc_fence_after();
   R7C_STAMP(21);
 
-  // ---- epilogue.  Thread r < 64 holds dq~_i and dk~_i (token i = r), thread r >= 64 holds da~_i, db~_i.
-  // Row-owner threads read and write the fp32 scratch arrays as float4 (conflict-free with the padded
-  // rows).  red1 = dq~ q~ - dk~ k~ and red2 = da~ a~ - db~ b~ live in the dA tiles' space, dge = da~ a~
-  // in the [do; dz; v; sa] space: all those tiles are dead once MMA group 2 has completed.
+  // ---- epilogue.  Row r < 64 holds dq~_i and dk~_i (token i = r), row r >= 64 holds da~_i, db~_i; the
+  // two warps of a lane window take 32 channels each.  Row owners read and write the fp32 scratch
+  // arrays as float4 (conflict-free with the padded rows).  red1 = dq~ q~ - dk~ k~ and
+  // red2 = da~ a~ - db~ b~ live in the dA tiles' space, dge = da~ a~ in the [do; dz; v; sa] space: all
+  // those tiles are dead once MMA group 2 has completed.
   float* red1 = reinterpret_cast<float*>(sm.daqk);
   float* red2 = red1 + L * NROW;
   float* dge = reinterpret_cast<float*>(sm.dout);
   if (ok) {
-    const int i = tid & 63, tok = t0 + i;
-    const bool second = tid >= 64;
+    const int r = 32 * wq + lane, i = r & 63, tok = t0 + i;
+    const bool second = r >= 64;
     float* red = second ? red2 : red1;
+    const int c0 = 32 * hsel;
+    uint32_t r1[32], r2[32];
+    tmem_ld32(tmem_addr(tm, 32 * wq, c0), r1);          // dq~ / da~
+    tmem_ld32(tmem_addr(tm, 32 * wq, 64 + c0), r2);     // dk~ / db~
+    tmem_ld_wait();
+    float t1[32], t2[32], o1[32], o2[32];
+    tile_load_row32(second ? sm.at : sm.qt, i, c0, t1);
+    tile_load_row32(second ? sm.bt : sm.kt, i, c0, t2);
 #pragma unroll
-    for (int part = 0; part < 2; ++part) {
-      uint32_t r1[32], r2[32];
-      tmem_ld32(tmem_addr(tm, 32 * warp, 32 * part), r1);          // dq~ / da~
-      tmem_ld32(tmem_addr(tm, 32 * warp, 64 + 32 * part), r2);     // dk~ / db~
-      tmem_ld_wait();
-      float t1[32], t2[32], o1[32], o2[32];
-      tile_load_row32(second ? sm.at : sm.qt, i, 32 * part, t1);
-      tile_load_row32(second ? sm.bt : sm.kt, i, 32 * part, t2);
+    for (int j4 = 0; j4 < 32; j4 += 4) {
+      const int c = c0 + j4;
+      const float4 gs4 = *reinterpret_cast<const float4*>(&sm.gs[i * NROW + c]);
+      const float4 gg4 = *reinterpret_cast<const float4*>(&sm.gg[i * NROW + c]);
+      const float4 ta4 = *reinterpret_cast<const float4*>(&sm.qtot[0][c]);
+      const float4 tb4 = *reinterpret_cast<const float4*>(&sm.qtot[1][c]);
+      const float gsv[4] = {gs4.x, gs4.y, gs4.z, gs4.w}, ggv[4] = {gg4.x, gg4.y, gg4.z, gg4.w};
+      const float ttv[4] = {ta4.x + tb4.x, ta4.y + tb4.y, ta4.z + tb4.z, ta4.w + tb4.w};   // gref - (start of chunk)
+      float rd[4], ge[4];
 #pragma unroll
-      for (int j4 = 0; j4 < 32; j4 += 4) {
-        const int c = 32 * part + j4;
-        const float4 gs4 = *reinterpret_cast<const float4*>(&sm.gs[i * NROW + c]);
-        const float4 gg4 = *reinterpret_cast<const float4*>(&sm.gg[i * NROW + c]);
-        const float4 tt4 = *reinterpret_cast<const float4*>(&sm.tot[0][c]);
-        const float gsv[4] = {gs4.x, gs4.y, gs4.z, gs4.w}, ggv[4] = {gg4.x, gg4.y, gg4.z, gg4.w};
-        const float ttv[4] = {tt4.x, tt4.y, tt4.z, tt4.w};
-        float rd[4], ge[4];
-#pragma unroll
-        for (int m = 0; m < 4; ++m) {
-          const int j = j4 + m;
-          const float d1 = gsv[m] - (i < 32 ? ttv[m] : 0.f);            // gi - gref
-          const float x1 = __uint_as_float(r1[j]), x2 = __uint_as_float(r2[j]);
-          o2[j] = x2 * cexp(-d1);                                        // dk / db
-          o1[j] = x1 * (second ? cexp(d1 - ggv[m]) : cexp(d1));          // da / dq
-          ge[m] = x1 * t1[j];
-          rd[m] = ge[m] - x2 * t2[j];
-        }
-        *reinterpret_cast<float4*>(&red[i * NROW + c]) = make_float4(rd[0], rd[1], rd[2], rd[3]);
-        if (second) *reinterpret_cast<float4*>(&dge[i * NROW + c]) = make_float4(ge[0], ge[1], ge[2], ge[3]);
+      for (int m = 0; m < 4; ++m) {
+        const int j = j4 + m;
+        const float d1 = gsv[m] - (i < 32 ? ttv[m] : 0.f);            // gi - gref
+        const float x1 = __uint_as_float(r1[j]), x2 = __uint_as_float(r2[j]);
+        o2[j] = x2 * cexp(-d1);                                        // dk / db
+        o1[j] = x1 * (second ? cexp(d1 - ggv[m]) : cexp(d1));          // da / dq
+        ge[m] = x1 * t1[j];
+        rd[m] = ge[m] - x2 * t2[j];
       }
-      if (tok < Tn) {
-        const long long off = base + (long long)tok * lay.st + 32 * part;
-        store_row32_global((second ? da : dq) + off, o1);
-        store_row32_global((second ? db : dk) + off, o2);
-      }
+      *reinterpret_cast<float4*>(&red[i * NROW + c]) = make_float4(rd[0], rd[1], rd[2], rd[3]);
+      if (second) *reinterpret_cast<float4*>(&dge[i * NROW + c]) = make_float4(ge[0], ge[1], ge[2], ge[3]);
+    }
+    if (tok < Tn) {
+      const long long off = base + (long long)tok * lay.st + c0;
+      store_row32_global((second ? da : dq) + off, o1);
+      store_row32_global((second ? db : dk) + off, o2);
     }
   }
   __syncthreads();
   R7C_STAMP(22);
-  // reverse inclusive prefix over tokens, per channel; thread = (channel, half)
+  // reverse inclusive prefix over tokens, per channel; thread = (channel, quarter)
   {
-    const int c = tid & 63, half = tid >> 6;
-    float rv[32];
+    const int c = tid & 63, quarter = tid >> 6;
+    float rv[16];
 #pragma unroll
-    for (int j = 0; j < 32; ++j) rv[j] = red1[(32 * half + j) * NROW + c] + red2[(32 * half + j) * NROW + c];
+    for (int j = 0; j < 16; ++j) rv[j] = red1[(16 * quarter + j) * NROW + c] + red2[(16 * quarter + j) * NROW + c];
     float run = 0.f;
 #pragma unroll
-    for (int j = 31; j >= 0; --j) { run += rv[j]; rv[j] = run; }
-    if (half == 1) sm.rtot[c] = run;
+    for (int j = 15; j >= 0; --j) { run += rv[j]; rv[j] = run; }
+    sm.rqtot[quarter][c] = run;
     __syncthreads();
-    const float add = (half == 0 ? sm.rtot[c] : 0.f) + sm.dgl[c];
+    float add = sm.dgl[c];
+    for (int q2 = quarter + 1; q2 < 4; ++q2) add += sm.rqtot[q2][c];
 #pragma unroll
-    for (int j = 0; j < 32; ++j) {
-      const int ii = 32 * half + j;
+    for (int j = 0; j < 16; ++j) {
+      const int ii = 16 * quarter + j;
       if (t0 + ii < Tn) {
         const float dg = rv[j] + add - dge[ii * NROW + c];
         dw[base + (long long)(t0 + ii) * lay.st + c] = __float2bfloat16_rn(dg * sm.gg[ii * NROW + c]);
@@ -566,7 +570,7 @@ int launch_rwkv7_chunked_bwd(const void* r, const void* w, const void* k, const 
     const int smem = (int)sizeof(FinalSmem) + 1024;
     if (cuda_ok(cudaFuncSetAttribute(r7c_bwd_final_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem))) return RWKVB200_E_CUDA;
     ProfScope prof("r7c_bwd_final_kernel", st);
-    r7c_bwd_final_kernel<<<B * H * NT, 128, smem, st>>>((const bf16*)w, tmap_do, tmap_v, ws.tiles, ALL_TILES,
+    r7c_bwd_final_kernel<<<B * H * NT, 256, smem, st>>>((const bf16*)w, tmap_do, tmap_v, ws.tiles, ALL_TILES,
                                                          (bf16*)dr, (bf16*)dw, (bf16*)dk, (bf16*)dv, (bf16*)da,
                                                          (bf16*)db, Tn, H, NT, lay, status, debug_stamp_buffer());
   }

@@ -82,6 +82,7 @@ def _(r, k, v, w, u, s0, state_map, d_y, d_sT):
 def _setup_ctx(ctx, inputs, output):
     r, k, v, w, u, s0, state_map = inputs
     ctx.save_for_backward(r, k, v, w, u, s0, state_map)
+    ctx.set_materialize_grads(False)
 
 
 def _backward(ctx, d_y, d_sT):

@@ -156,6 +156,7 @@ def _(r, w, k, v, a, b, h0, d_o, d_ht, kept, head_first, algo):
 def _setup_ctx_keep(ctx, inputs, output):
     r, w, k, v, a, b, h0, head_first, algo = inputs
     ctx.save_for_backward(r, w, k, v, a, b, h0, output[2])
+    ctx.set_materialize_grads(False)   # no zero tensor for the (never differentiated) tile store
     ctx.head_first = head_first
     ctx.algo = algo
 
@@ -219,6 +220,7 @@ def _(r, w, k, v, a, b, h0, d_o, d_ht, head_first, algo):
 def _setup_ctx(ctx, inputs, output):
     r, w, k, v, a, b, h0, head_first, algo = inputs
     ctx.save_for_backward(r, w, k, v, a, b, h0)
+    ctx.set_materialize_grads(False)
     ctx.head_first = head_first
     ctx.algo = algo
 
