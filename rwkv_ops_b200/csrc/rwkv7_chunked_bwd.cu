@@ -277,6 +277,7 @@ struct FinalSmem {
   unsigned char dout[TILE_BYTES], dz[TILE_BYTES];                 // [do; dz]
   unsigned char v[TILE_BYTES], sa[TILE_BYTES];                    // [v; sa]
   unsigned char daqk[TILE_BYTES], daak[TILE_BYTES], daqb[TILE_BYTES], daab[TILE_BYTES];
+  unsigned char red_pad[2048];    // the two fp32 scratch arrays that later overlay the dA tiles need 34 KB
   unsigned char aqk[TILE_BYTES], aak[TILE_BYTES];                 // adjacent workspace slots
   unsigned char qt[TILE_BYTES], at[TILE_BYTES], kt[TILE_BYTES], bt[TILE_BYTES];
   unsigned char h0[TILE_BYTES], dhh[TILE_BYTES];
@@ -294,8 +295,10 @@ struct FinalSmem {
 __global__ void __launch_bounds__(256)
 r7c_bwd_final_kernel(const bf16* __restrict__ w, const __grid_constant__ CUtensorMap tmap_do,
                      const __grid_constant__ CUtensorMap tmap_v, const unsigned char* __restrict__ ws_tiles,
-                     int tiles_per_chunk, bf16* __restrict__ dq, bf16* __restrict__ dw, bf16* __restrict__ dk,
-                     bf16* __restrict__ dv, bf16* __restrict__ da, bf16* __restrict__ db,
+                     int tiles_per_chunk, const __grid_constant__ CUtensorMap tmap_dq,
+                     const __grid_constant__ CUtensorMap tmap_dw, const __grid_constant__ CUtensorMap tmap_dk,
+                     const __grid_constant__ CUtensorMap tmap_dv, const __grid_constant__ CUtensorMap tmap_da,
+                     const __grid_constant__ CUtensorMap tmap_db,
                      int Tn, int H, int NT, TokLayout lay, int* status, long long* dbg) {
 #define R7C_STAMP(n) do { if (dbg && tid == 0 && blockIdx.x == gridDim.x / 2) dbg[n] = clock64(); } while (0)
   extern __shared__ unsigned char smem_raw[];
@@ -415,21 +418,25 @@ r7c_bwd_final_kernel(const bf16* __restrict__ w, const __grid_constant__ CUtenso
       tile_store_row32(dst, i, j0, x);
     }
     // dv rows sit on the lower lane halves of columns 128..191; each warp of a pair takes 32 columns
-    const int row = 16 * wq + (lane & 15), tok = t0 + row;
+    const int row = 16 * wq + (lane & 15);
     uint32_t rr[32];
     tmem_ld32(tmem_addr(tm, 32 * wq, 128 + 32 * hsel), rr);
     tmem_ld_wait();
-    if (lane < 16 && tok < Tn) {
+    if (lane < 16) {     // staged in the A_qk tile (dead: MMA group 1 has completed), stored by TMA below
       float x[32];
 #pragma unroll
       for (int j = 0; j < 32; ++j) x[j] = __uint_as_float(rr[j]);
-      store_row32_global(dv + base + (long long)tok * lay.st + 32 * hsel, x);
+      tile_store_row32(sm.aqk, row, 32 * hsel, x);
     }
   }
   fence_async_smem();
   tc_fence_before();
   __syncthreads();
   R7C_STAMP(20);
+  if (tid == 32 && ok) {
+    tma_store_4d(&tmap_dv, sm.aqk, 0, t0, hi, bi);
+    bulk_commit();
+  }
 
   // ---- MMA group 2: [dq~; da~] (columns 0..63) and [dk~; db~] (columns 64..127)
   if (tid == 0 && ok) {
@@ -455,7 +462,7 @@ r7c_bwd_final_kernel(const bf16* __restrict__ w, const __grid_constant__ CUtenso
   float* red2 = red1 + L * NROW;
   float* dge = reinterpret_cast<float*>(sm.dout);
   if (ok) {
-    const int r = 32 * wq + lane, i = r & 63, tok = t0 + i;
+    const int r = 32 * wq + lane, i = r & 63;
     const bool second = r >= 64;
     float* red = second ? red2 : red1;
     const int c0 = 32 * hsel;
@@ -489,14 +496,20 @@ r7c_bwd_final_kernel(const bf16* __restrict__ w, const __grid_constant__ CUtenso
       *reinterpret_cast<float4*>(&red[i * NROW + c]) = make_float4(rd[0], rd[1], rd[2], rd[3]);
       if (second) *reinterpret_cast<float4*>(&dge[i * NROW + c]) = make_float4(ge[0], ge[1], ge[2], ge[3]);
     }
-    if (tok < Tn) {
-      const long long off = base + (long long)tok * lay.st + c0;
-      store_row32_global((second ? da : dq) + off, o1);
-      store_row32_global((second ? db : dk) + off, o2);
-    }
+    // staged as bf16 tiles in dead operand tiles (dq -> h0, dk -> dhh, da -> aak, db -> sa), stored by TMA
+    tile_store_row32(second ? sm.aak : sm.h0, i, c0, o1);
+    tile_store_row32(second ? sm.sa : sm.dhh, i, c0, o2);
   }
+  fence_async_smem();
   __syncthreads();
   R7C_STAMP(22);
+  if (tid == 32 && ok) {
+    tma_store_4d(&tmap_dq, sm.h0, 0, t0, hi, bi);
+    tma_store_4d(&tmap_dk, sm.dhh, 0, t0, hi, bi);
+    tma_store_4d(&tmap_da, sm.aak, 0, t0, hi, bi);
+    tma_store_4d(&tmap_db, sm.sa, 0, t0, hi, bi);
+    bulk_commit();
+  }
   // reverse inclusive prefix over tokens, per channel; thread = (channel, quarter)
   {
     const int c = tid & 63, quarter = tid >> 6;
@@ -511,15 +524,19 @@ r7c_bwd_final_kernel(const bf16* __restrict__ w, const __grid_constant__ CUtenso
     float add = sm.dgl[c];
     for (int q2 = quarter + 1; q2 < 4; ++q2) add += sm.rqtot[q2][c];
 #pragma unroll
-    for (int j = 0; j < 16; ++j) {
+    for (int j = 0; j < 16; ++j) {      // dw staged in the q~ tile (its last reader was the epilogue above)
       const int ii = 16 * quarter + j;
-      if (t0 + ii < Tn) {
-        const float dg = rv[j] + add - dge[ii * NROW + c];
-        dw[base + (long long)(t0 + ii) * lay.st + c] = __float2bfloat16_rn(dg * sm.gg[ii * NROW + c]);
-      }
+      const float dg = rv[j] + add - dge[ii * NROW + c];
+      *reinterpret_cast<bf16*>(sm.qt + tile_off(ii, c)) = __float2bfloat16_rn(dg * sm.gg[ii * NROW + c]);
     }
   }
+  fence_async_smem();
   tc_fence_before();
+  __syncthreads();
+  if (tid == 32) {
+    if (ok) { tma_store_4d(&tmap_dw, sm.qt, 0, t0, hi, bi); bulk_commit(); }
+    bulk_wait_all();
+  }
   __syncthreads();
   R7C_STAMP(23);
   if (warp == 0) tmem_dealloc(tm, 256);
@@ -542,11 +559,16 @@ int launch_rwkv7_chunked_bwd(const void* r, const void* w, const void* k, const 
   }
   int* status = device_status_ptr();
   if (!status) { last_cuda_error_slot() = 99999; return RWKVB200_E_CUDA; }
-  CUtensorMap tmap_do, tmap_v;
+  CUtensorMap tmap_do, tmap_v, tmap_out[6];
   e = make_token_tensor_map(&tmap_do, d_o, B, Tn, H, head_first);
   if (e) return e;
   e = make_token_tensor_map(&tmap_v, v, B, Tn, H, head_first);
   if (e) return e;
+  void* outs[6] = {dr, dw, dk, dv, da, db};
+  for (int i = 0; i < 6; ++i) {
+    e = make_token_tensor_map(&tmap_out[i], outs[i], B, Tn, H, head_first);
+    if (e) return e;
+  }
   const int NT = num_chunks(Tn);
   Workspace ws = carve(workspace, B, Tn, H, ALL_TILES);
   TokLayout lay(Tn, H, head_first);
@@ -571,8 +593,9 @@ int launch_rwkv7_chunked_bwd(const void* r, const void* w, const void* k, const 
     if (cuda_ok(cudaFuncSetAttribute(r7c_bwd_final_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem))) return RWKVB200_E_CUDA;
     ProfScope prof("r7c_bwd_final_kernel", st);
     r7c_bwd_final_kernel<<<B * H * NT, 256, smem, st>>>((const bf16*)w, tmap_do, tmap_v, ws.tiles, ALL_TILES,
-                                                         (bf16*)dr, (bf16*)dw, (bf16*)dk, (bf16*)dv, (bf16*)da,
-                                                         (bf16*)db, Tn, H, NT, lay, status, debug_stamp_buffer());
+                                                         tmap_out[0], tmap_out[1], tmap_out[2], tmap_out[3],
+                                                         tmap_out[4], tmap_out[5], Tn, H, NT, lay, status,
+                                                         debug_stamp_buffer());
   }
   return check_launch();
 }

@@ -344,6 +344,7 @@ struct ScanSmem {
   unsigned char ht[TILE_BYTES];             // h~0 as bf16, [k][v]
   unsigned char sa[TILE_BYTES];             // sa as bf16, [token][v]
   unsigned char xt[TILE_BYTES];             // X = h~0 + k~^T v + b~^T sa as bf16 (kept for the backward)
+  unsigned char ot[2][TILE_BYTES];          // output rows of a chunk, staged for a TMA store
   uint64_t bar_full[2], bar_a, bar_c;
   uint32_t tmem_base;
 };
@@ -351,13 +352,12 @@ struct ScanSmem {
 __global__ void __launch_bounds__(128)
 r7c_scan_fwd_kernel(const __grid_constant__ CUtensorMap tmap_v, const unsigned char* __restrict__ ws_tiles,
                     const float* __restrict__ ws_aux, int tiles_per_chunk, unsigned char* __restrict__ bwd_tiles,
-                    const float* __restrict__ h0, int n_state, bf16* __restrict__ o, float* __restrict__ ht,
-                    int Tn, int H, int NT, TokLayout lay, int* status) {
+                    const float* __restrict__ h0, int n_state, const __grid_constant__ CUtensorMap tmap_o,
+                    int write_o, float* __restrict__ ht, int Tn, int H, int NT, int* status) {
   extern __shared__ unsigned char smem_raw[];
   ScanSmem& sm = *reinterpret_cast<ScanSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int unit = blockIdx.x, bi = unit / H, hi = unit % H;
-  const long long base = bi * lay.sb + hi * lay.sh;
   const size_t ch0 = (size_t)unit * NT;
   const int row = 16 * warp + (lane & 15);   // state row k (lanes 0-15) or token row i (lanes 16-31)
   const bool state_lane = lane < 16;
@@ -477,7 +477,6 @@ r7c_scan_fwd_kernel(const __grid_constant__ CUtensorMap tmap_v, const unsigned c
     }
     if (ok) {
       const bool last = c + 1 == NT;
-      const int tok = t0 + row;
 #pragma unroll
       for (int part = 0; part < 2; ++part) {
         uint32_t r[32];
@@ -502,16 +501,7 @@ r7c_scan_fwd_kernel(const __grid_constant__ CUtensorMap tmap_v, const unsigned c
         } else {
 #pragma unroll
           for (int j = 0; j < 32; ++j) x[j] = __uint_as_float(r[j]) + keep[32 * part + j];
-          if (o && tok < Tn) {
-            bf16* dst = o + base + (long long)tok * lay.st + 32 * part;
-#pragma unroll
-            for (int j = 0; j < 32; j += 8) {
-              uint4 u;
-              u.x = pack_bf16(x[j], x[j + 1]); u.y = pack_bf16(x[j + 2], x[j + 3]);
-              u.z = pack_bf16(x[j + 4], x[j + 5]); u.w = pack_bf16(x[j + 6], x[j + 7]);
-              *reinterpret_cast<uint4*>(dst + j) = u;
-            }
-          }
+          if (write_o) tile_store_row32(sm.ot[c & 1], row, 32 * part, x);
         }
         tmem_st32(tm_p2 + 32 * part, r);   // state lanes: rescaled state; token lanes: unchanged
       }
@@ -523,6 +513,11 @@ r7c_scan_fwd_kernel(const __grid_constant__ CUtensorMap tmap_v, const unsigned c
     if (bwd_tiles && tid == 0 && ok) {
       bulk_store(bwd_tiles + ((ch0 + c) * (size_t)tiles_per_chunk + S_X) * TILE_BYTES, sm.xt, TILE_BYTES);
       bulk_commit();
+    }
+    if (write_o && tid == 0 && ok) {     // rows past the end of the sequence are clipped by the TMA store
+      tma_store_4d(&tmap_o, sm.ot[c & 1], 0, t0, hi, bi);
+      bulk_commit();
+      bulk_wait_read_1();                // the buffer of the previous chunk is free again
     }
     if (tid == 0 && ok && c + 2 < NT) issue_loads(c + 2);
   }
@@ -540,8 +535,10 @@ int launch_rwkv7_chunked_fwd(const void* r, const void* w, const void* k, const 
   typedef __nv_bfloat16 bf16;
   int* status = device_status_ptr();
   if (!status) { last_cuda_error_slot() = 99999; return RWKVB200_E_CUDA; }
-  CUtensorMap tmap_v;
+  CUtensorMap tmap_v, tmap_o;
   int e = make_token_tensor_map(&tmap_v, v, B, Tn, H, head_first);
+  if (e) return e;
+  e = make_token_tensor_map(&tmap_o, o ? o : v, B, Tn, H, head_first);   // unused when o is NULL
   if (e) return e;
   const int NT = num_chunks(Tn);
   const int tpc = keep_for_bwd ? (int)ALL_TILES : (int)FWD_TILES;
@@ -563,7 +560,7 @@ int launch_rwkv7_chunked_fwd(const void* r, const void* w, const void* k, const 
     if (cuda_ok(cudaFuncSetAttribute(r7c_scan_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem))) return RWKVB200_E_CUDA;
     ProfScope prof("r7c_scan_fwd_kernel", st);
     r7c_scan_fwd_kernel<<<B * H, 128, smem, st>>>(tmap_v, ws.tiles, ws.aux, tpc, keep_for_bwd ? ws.tiles : nullptr,
-                                                  h0, n_state, (bf16*)o, ht, Tn, H, NT, lay, status);
+                                                  h0, n_state, tmap_o, o ? 1 : 0, ht, Tn, H, NT, status);
   }
   return check_launch();
 }
