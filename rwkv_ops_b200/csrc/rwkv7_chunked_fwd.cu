@@ -26,12 +26,14 @@ struct IntraSmem {
   unsigned char ainv[TILE_BYTES];
   unsigned char y[TILE_BYTES];                      // A_ak v
   float nmat[L * NROW];                             // stril(A_ab) in fp32
-  float tot[2][64];
+  float qtot[4][64];                                // sums of g over the four quarters of the chunk
   uint64_t bar_v, bar_m1, bar_m2, bar_m3;
   uint32_t tmem_base;
 };
 
-__global__ void __launch_bounds__(128)
+// 256 threads: warp w reads TMEM lanes 32*(w&3).. and the two warps that share a lane window split
+// the columns (hsel = w>>2); the triangular solve runs on warps 0-1 while the other warps drain MMA 2.
+__global__ void __launch_bounds__(256)
 r7c_intra_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ w, const bf16* __restrict__ k,
                      const bf16* __restrict__ a, const bf16* __restrict__ b,
                      const __grid_constant__ CUtensorMap tmap_v, unsigned char* __restrict__ ws_tiles,
@@ -41,6 +43,7 @@ r7c_intra_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ w, con
   extern __shared__ unsigned char smem_raw[];
   IntraSmem& sm = *reinterpret_cast<IntraSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int wq = warp & 3, hsel = warp >> 2;
   const int ch = blockIdx.x, unit = ch / NT, cidx = ch % NT;
   const int bi = unit / H, hi = unit % H, t0 = cidx * L;
   const long long base = bi * lay.sb + hi * lay.sh;
@@ -66,11 +69,11 @@ r7c_intra_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ w, con
   // through shared memory (the fp32 area that later holds A_ab).
   {
     float* gs = sm.nmat;
-    uint4 rw[4], rq[4], rk[4], ra[4], rb[4];
+    uint4 rw[2], rq[2], rk[2], ra[2], rb[2];
     const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
-    for (int n = 0; n < 4; ++n) {
-      const int e = tid + 128 * n, row = e >> 3, cc = e & 7, tok = t0 + row;
+    for (int n = 0; n < 2; ++n) {
+      const int e = tid + 256 * n, row = e >> 3, cc = e & 7, tok = t0 + row;
       const long long off = base + (long long)tok * lay.st + 8 * cc;
       const bool valid = tok < Tn;
       rw[n] = valid ? __ldg(reinterpret_cast<const uint4*>(w + off)) : zero4;
@@ -79,51 +82,53 @@ r7c_intra_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ w, con
       ra[n] = valid ? __ldg(reinterpret_cast<const uint4*>(a + off)) : zero4;
       rb[n] = valid ? __ldg(reinterpret_cast<const uint4*>(b + off)) : zero4;
     }
+    float gown[2][8];     // g of this thread's 2 x 8 (token, channel) entries
 #pragma unroll
-    for (int n = 0; n < 4; ++n) {
-      const int e = tid + 128 * n, row = e >> 3, cc = e & 7;
+    for (int n = 0; n < 2; ++n) {
+      const int e = tid + 256 * n, row = e >> 3, cc = e & 7;
       const bool valid = t0 + row < Tn;
       const uint32_t u[4] = {rw[n].x, rw[n].y, rw[n].z, rw[n].w};
-      float g[8];
 #pragma unroll
       for (int m = 0; m < 4; ++m) {
-        g[2 * m] = valid ? -__expf(bf16_lo(u[m])) : 0.f;
-        g[2 * m + 1] = valid ? -__expf(bf16_hi(u[m])) : 0.f;
+        gown[n][2 * m] = valid ? -__expf(bf16_lo(u[m])) : 0.f;
+        gown[n][2 * m + 1] = valid ? -__expf(bf16_hi(u[m])) : 0.f;
       }
-      *reinterpret_cast<float4*>(&gs[row * NROW + 8 * cc]) = make_float4(g[0], g[1], g[2], g[3]);
-      *reinterpret_cast<float4*>(&gs[row * NROW + 8 * cc + 4]) = make_float4(g[4], g[5], g[6], g[7]);
+      *reinterpret_cast<float4*>(&gs[row * NROW + 8 * cc]) = make_float4(gown[n][0], gown[n][1], gown[n][2], gown[n][3]);
+      *reinterpret_cast<float4*>(&gs[row * NROW + 8 * cc + 4]) = make_float4(gown[n][4], gown[n][5], gown[n][6], gown[n][7]);
     }
     __syncthreads();
     R7C_STAMP(1);
     {
-      const int c = tid & 63, half = tid >> 6;
-      float gv[32];
+      const int c = tid & 63, quarter = tid >> 6;
+      float gv[16];
 #pragma unroll
-      for (int j = 0; j < 32; ++j) gv[j] = gs[(32 * half + j) * NROW + c];
+      for (int j = 0; j < 16; ++j) gv[j] = gs[(16 * quarter + j) * NROW + c];
       float run = 0.f;
 #pragma unroll
-      for (int j = 0; j < 32; ++j) {
-        run += gv[j];
-        gs[(32 * half + j) * NROW + c] = run;   // inclusive prefix inside this half of the chunk
-      }
-      sm.tot[half][c] = run;
+      for (int j = 0; j < 16; ++j) { run += gv[j]; gv[j] = run; }
+      sm.qtot[quarter][c] = run;
+      __syncthreads();
+      const float add = (quarter & 1) ? sm.qtot[quarter - 1][c] : 0.f;
+#pragma unroll
+      for (int j = 0; j < 16; ++j) gs[(16 * quarter + j) * NROW + c] = gv[j] + add;   // prefix inside each half
     }
     __syncthreads();
     if (tid < 64) {
-      ws_aux[(size_t)ch * AUX_FLOATS + tid] = __expf(fmaxf(sm.tot[0][tid], -EXP_CLAMP));        // e^{gref}
-      ws_aux[(size_t)ch * AUX_FLOATS + 64 + tid] = __expf(fmaxf(sm.tot[1][tid], -EXP_CLAMP));   // e^{glast-gref}
+      const float tot0 = sm.qtot[0][tid] + sm.qtot[1][tid], tot1 = sm.qtot[2][tid] + sm.qtot[3][tid];
+      ws_aux[(size_t)ch * AUX_FLOATS + tid] = __expf(fmaxf(tot0, -EXP_CLAMP));        // e^{gref}
+      ws_aux[(size_t)ch * AUX_FLOATS + 64 + tid] = __expf(fmaxf(tot1, -EXP_CLAMP));   // e^{glast-gref}
     }
 #pragma unroll
-    for (int n = 0; n < 4; ++n) {
-      const int e = tid + 128 * n, row = e >> 3, cc = e & 7;
-      const bool valid = t0 + row < Tn;
+    for (int n = 0; n < 2; ++n) {
+      const int e = tid + 256 * n, row = e >> 3, cc = e & 7;
       const bool first_half = row < 32;
-      float gl[8], sh[8];
+      float gl[8], sh[8], sh2[8];
       *reinterpret_cast<float4*>(gl) = *reinterpret_cast<const float4*>(&gs[row * NROW + 8 * cc]);
       *reinterpret_cast<float4*>(gl + 4) = *reinterpret_cast<const float4*>(&gs[row * NROW + 8 * cc + 4]);
-      *reinterpret_cast<float4*>(sh) = *reinterpret_cast<const float4*>(&sm.tot[0][8 * cc]);
-      *reinterpret_cast<float4*>(sh + 4) = *reinterpret_cast<const float4*>(&sm.tot[0][8 * cc + 4]);
-      const uint32_t uw[4] = {rw[n].x, rw[n].y, rw[n].z, rw[n].w};
+      *reinterpret_cast<float4*>(sh) = *reinterpret_cast<const float4*>(&sm.qtot[0][8 * cc]);
+      *reinterpret_cast<float4*>(sh + 4) = *reinterpret_cast<const float4*>(&sm.qtot[0][8 * cc + 4]);
+      *reinterpret_cast<float4*>(sh2) = *reinterpret_cast<const float4*>(&sm.qtot[1][8 * cc]);
+      *reinterpret_cast<float4*>(sh2 + 4) = *reinterpret_cast<const float4*>(&sm.qtot[1][8 * cc + 4]);
       const uint32_t uq[4] = {rq[n].x, rq[n].y, rq[n].z, rq[n].w};
       const uint32_t uk[4] = {rk[n].x, rk[n].y, rk[n].z, rk[n].w};
       const uint32_t ua[4] = {ra[n].x, ra[n].y, ra[n].z, ra[n].w};
@@ -135,10 +140,8 @@ r7c_intra_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ w, con
 #pragma unroll
         for (int hh = 0; hh < 2; ++hh) {
           const int x = 2 * m + hh;
-          const float d1 = gl[x] - (first_half ? sh[x] : 0.f);          // gi - gref
-          const float wv = hh ? bf16_hi(uw[m]) : bf16_lo(uw[m]);
-          const float gj = valid ? -__expf(wv) : 0.f;                    // g of this token
-          eq[hh] = cexp(d1); ek[hh] = cexp(-d1); ea[hh] = cexp(d1 - gj);
+          const float d1 = gl[x] - (first_half ? sh[x] + sh2[x] : 0.f);   // gi - gref
+          eq[hh] = cexp(d1); ek[hh] = cexp(-d1); ea[hh] = cexp(d1 - gown[n][x]);
         }
         oq[m] = pack_bf16(bf16_lo(uq[m]) * eq[0], bf16_hi(uq[m]) * eq[1]);
         ok_[m] = pack_bf16(bf16_lo(uk[m]) * ek[0], bf16_hi(uk[m]) * ek[1]);
@@ -166,23 +169,23 @@ r7c_intra_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ w, con
   tc_fence_after();
   R7C_STAMP(3);
   if (ok) {
-    const int i = tid & 63;
-    const bool lower = tid >= 64;       // rows of a~: strictly lower triangle; rows of q~: lower incl. diagonal
+    const int r = 32 * wq + lane, i = r & 63;
+    const bool lower = r >= 64;       // rows of a~: strictly lower triangle; rows of q~: lower incl. diagonal
 #pragma unroll
-    for (int part = 0; part < 4; ++part) {
-      uint32_t r[32];
-      tmem_ld32(tmem_addr(tm, 32 * warp, 32 * part), r);
+    for (int pp = 0; pp < 2; ++pp) {
+      uint32_t rr[32];
+      tmem_ld32(tmem_addr(tm, 32 * wq, 64 * hsel + 32 * pp), rr);   // hsel 0: products with k~, 1: with b~
       tmem_ld_wait();
       float x[32];
-      const int j0 = 32 * (part & 1);
+      const int j0 = 32 * pp;
 #pragma unroll
       for (int j = 0; j < 32; ++j) {
         const bool keep = lower ? (j0 + j < i) : (j0 + j <= i);
-        x[j] = keep ? __uint_as_float(r[j]) : 0.f;
+        x[j] = keep ? __uint_as_float(rr[j]) : 0.f;
       }
       if (!lower) {
-        tile_store_row32(part < 2 ? sm.aqk : sm.aqb, i, j0, x);
-      } else if (part < 2) {
+        tile_store_row32(hsel ? sm.aqb : sm.aqk, i, j0, x);
+      } else if (!hsel) {
         tile_store_row32(sm.aak, i, j0, x);
       } else {
 #pragma unroll
@@ -238,14 +241,16 @@ r7c_intra_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ w, con
 #pragma unroll
       for (int rr = 1; rr < 16; ++rr) {
         const float* nrow = &sm.nmat[(16 * I + rr) * NROW + 16 * I];
+        float p0 = 0.f, p1 = 0.f, p2 = 0.f, p3 = 0.f;   // entries at or right of the diagonal are 0
 #pragma unroll
         for (int jj = 0; jj < (rr + 3) / 4; ++jj) {
-          const float4 n = *reinterpret_cast<const float4*>(nrow + 4 * jj);   // entries at or right of the diagonal are 0
-          xb[rr] += n.x * xb[4 * jj];
-          if (4 * jj + 1 < rr) xb[rr] += n.y * xb[4 * jj + 1];
-          if (4 * jj + 2 < rr) xb[rr] += n.z * xb[4 * jj + 2];
-          if (4 * jj + 3 < rr) xb[rr] += n.w * xb[4 * jj + 3];
+          const float4 n = *reinterpret_cast<const float4*>(nrow + 4 * jj);
+          p0 += n.x * xb[4 * jj];
+          if (4 * jj + 1 < rr) p1 += n.y * xb[4 * jj + 1];
+          if (4 * jj + 2 < rr) p2 += n.z * xb[4 * jj + 2];
+          if (4 * jj + 3 < rr) p3 += n.w * xb[4 * jj + 3];
         }
+        xb[rr] += (p0 + p1) + (p2 + p3);
       }
       if (I == 0) {
         // first write to xs: MMA 2 (and the copies of A_qk / A_ak kept for the backward) must be done
@@ -259,25 +264,34 @@ r7c_intra_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ w, con
         *reinterpret_cast<bf16*>(sm.ainv + tile_off(16 * I + rr, c)) = __float2bfloat16_rn(xb[rr]);
       }
     }
-  }
-  R7C_STAMP(5);
-  {
-    // rows of MMA 2: threads 0..63 take O1 (after the inverse), threads 64..127 take Y
+  } else {
+    // rows of MMA 2 for the other six warps: warps 4-5 take O1 (both column halves), warps 2-3 and
+    // 6-7 take Y (one column half each)
     ok = mbar_wait(&sm.bar_m2, 0, status, 203) && ok;
     tc_fence_after();
-    const int i = tid & 63;
-    unsigned char* dst = tid < 64 ? sm.o1 : sm.y;
+    const int i = (32 * wq + lane) & 63;
+    if (wq < 2) {        // warps 4, 5
 #pragma unroll
-    for (int part = 0; part < 2; ++part) {
-      uint32_t r[32];
-      tmem_ld32(tmem_addr(tm, 32 * warp, 128 + 32 * part), r);
+      for (int part = 0; part < 2; ++part) {
+        uint32_t rr[32];
+        tmem_ld32(tmem_addr(tm, 32 * wq, 128 + 32 * part), rr);
+        tmem_ld_wait();
+        float x[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) x[j] = __uint_as_float(rr[j]);
+        tile_store_row32(sm.o1, i, 32 * part, x);
+      }
+    } else {             // warps 2, 3, 6, 7
+      uint32_t rr[32];
+      tmem_ld32(tmem_addr(tm, 32 * wq, 128 + 32 * hsel), rr);
       tmem_ld_wait();
       float x[32];
 #pragma unroll
-      for (int j = 0; j < 32; ++j) x[j] = __uint_as_float(r[j]);
-      tile_store_row32(dst, i, 32 * part, x);
+      for (int j = 0; j < 32; ++j) x[j] = __uint_as_float(rr[j]);
+      tile_store_row32(sm.y, i, 32 * hsel, x);
     }
   }
+  R7C_STAMP(5);
   fence_async_smem();
   tc_fence_before();
   __syncthreads();
@@ -300,21 +314,16 @@ r7c_intra_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ w, con
   ok = mbar_wait(&sm.bar_m3, 0, status, 204) && ok;
   tc_fence_after();
   R7C_STAMP(7);
-  if (tid == 0) bulk_wait_read();   // the A_ak tile is about to be overwritten by W
-  __syncthreads();
   {
-    const int i = 16 * warp + (lane & 15);
+    const int i = 16 * wq + (lane & 15);
     unsigned char* dst = lane < 16 ? sm.aak : sm.v;     // W, U (both tiles are free: MMA 2 has completed)
+    uint32_t rr[32];
+    tmem_ld32(tmem_addr(tm, 32 * wq, 32 * hsel), rr);
+    tmem_ld_wait();
+    float x[32];
 #pragma unroll
-    for (int part = 0; part < 2; ++part) {
-      uint32_t r[32];
-      tmem_ld32(tmem_addr(tm, 32 * warp, 32 * part), r);
-      tmem_ld_wait();
-      float x[32];
-#pragma unroll
-      for (int j = 0; j < 32; ++j) x[j] = __uint_as_float(r[j]);
-      tile_store_row32(dst, i, 32 * part, x);
-    }
+    for (int j = 0; j < 32; ++j) x[j] = __uint_as_float(rr[j]);
+    tile_store_row32(dst, i, 32 * hsel, x);
   }
   fence_async_smem();
   tc_fence_before();
@@ -548,7 +557,7 @@ int launch_rwkv7_chunked_fwd(const void* r, const void* w, const void* k, const 
     const int smem = (int)sizeof(IntraSmem) + 1024;
     if (cuda_ok(cudaFuncSetAttribute(r7c_intra_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem))) return RWKVB200_E_CUDA;
     ProfScope prof("r7c_intra_fwd_kernel", st);
-    r7c_intra_fwd_kernel<<<B * H * NT, 128, smem, st>>>((const bf16*)r, (const bf16*)w, (const bf16*)k, (const bf16*)a,
+    r7c_intra_fwd_kernel<<<B * H * NT, 256, smem, st>>>((const bf16*)r, (const bf16*)w, (const bf16*)k, (const bf16*)a,
                                                          (const bf16*)b, tmap_v, ws.tiles, ws.aux, tpc,
                                                          keep_for_bwd ? 1 : 0, Tn, H, NT, lay, status,
                                                          debug_stamp_buffer());
