@@ -274,22 +274,30 @@ r7c_bwd_scan_kernel(const __grid_constant__ CUtensorMap tmap_do, unsigned char* 
 // 5. all token gradients of one chunk: grid = B*H*NT, 128 threads
 // ---------------------------------------------------------------------------------------------
 struct FinalSmem {
+  // loaded per chunk, group A (free again once MMA group 2 has completed)
   unsigned char dout[TILE_BYTES], dz[TILE_BYTES];                 // [do; dz]
   unsigned char v[TILE_BYTES], sa[TILE_BYTES];                    // [v; sa]
+  unsigned char aqk[TILE_BYTES], aak[TILE_BYTES];                 // adjacent workspace slots; aqk later stages dv
+  unsigned char h0[TILE_BYTES], dhh[TILE_BYTES];
+  // loaded per chunk, group B (read by the last epilogue, free after it)
+  unsigned char qt[TILE_BYTES], at[TILE_BYTES], kt[TILE_BYTES], bt[TILE_BYTES];
+  // computed
   unsigned char daqk[TILE_BYTES], daak[TILE_BYTES], daqb[TILE_BYTES], daab[TILE_BYTES];
   unsigned char red_pad[2048];    // the two fp32 scratch arrays that later overlay the dA tiles need 34 KB
-  unsigned char aqk[TILE_BYTES], aak[TILE_BYTES];                 // adjacent workspace slots
-  unsigned char qt[TILE_BYTES], at[TILE_BYTES], kt[TILE_BYTES], bt[TILE_BYTES];
-  unsigned char h0[TILE_BYTES], dhh[TILE_BYTES];
+  unsigned char dge[TILE_BYTES];  // da~ a~ as bf16
+  unsigned char stage[5][TILE_BYTES];   // dq, dk, da, db, dw rows staged for TMA stores
   float gs[L * NROW];       // gi - (start of the half): inclusive prefix of g inside each half of the chunk
   float gg[L * NROW];       // g
   float qtot[4][64];        // sums of g over the four quarters of the chunk
   float rqtot[4][64];       // sums of the decay-gradient terms over the four quarters
   float dgl[64];            // dglast
-  uint64_t bar_ld, bar_m1, bar_m2;
+  uint64_t bar_lda, bar_ldb, bar_m1, bar_m2;
   uint32_t tmem_base;
 };
 
+// Persistent: one CTA per SM walks over chunk-heads ch = blockIdx.x, blockIdx.x + gridDim.x, ...; the
+// tiles of the next chunk-head are requested as soon as the current one no longer needs them, and its w
+// rows wait in registers, so only the first chunk-head of a CTA pays the load latency.
 // 256 threads: warp w reads TMEM lanes 32*(w&3).. (its row), and the two warps that share a lane
 // window split the columns (hsel = w>>2), so every elementwise phase is spread over 8 warps.
 __global__ void __launch_bounds__(256)
@@ -299,18 +307,15 @@ r7c_bwd_final_kernel(const bf16* __restrict__ w, const __grid_constant__ CUtenso
                      const __grid_constant__ CUtensorMap tmap_dw, const __grid_constant__ CUtensorMap tmap_dk,
                      const __grid_constant__ CUtensorMap tmap_dv, const __grid_constant__ CUtensorMap tmap_da,
                      const __grid_constant__ CUtensorMap tmap_db,
-                     int Tn, int H, int NT, TokLayout lay, int* status, long long* dbg) {
-#define R7C_STAMP(n) do { if (dbg && tid == 0 && blockIdx.x == gridDim.x / 2) dbg[n] = clock64(); } while (0)
+                     int Tn, int H, int NT, int n_ch, TokLayout lay, int* status, long long* dbg) {
+#define R7C_STAMP(n) do { if (dbg && tid == 0 && blockIdx.x == gridDim.x / 2 && it == 1) dbg[n] = clock64(); } while (0)
   extern __shared__ unsigned char smem_raw[];
   FinalSmem& sm = *reinterpret_cast<FinalSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int wq = warp & 3, hsel = warp >> 2;
-  const int ch = blockIdx.x, unit = ch / NT, cidx = ch % NT, bi = unit / H, hi = unit % H, t0 = cidx * L;
-  const long long base = bi * lay.sb + hi * lay.sh;
-  const unsigned char* tiles = ws_tiles + (size_t)ch * tiles_per_chunk * TILE_BYTES;
 
   if (tid == 0) {
-    mbar_init(&sm.bar_ld, 1); mbar_init(&sm.bar_m1, 1); mbar_init(&sm.bar_m2, 1);
+    mbar_init(&sm.bar_lda, 1); mbar_init(&sm.bar_ldb, 1); mbar_init(&sm.bar_m1, 1); mbar_init(&sm.bar_m2, 1);
     fence_mbar_init();
   }
   if (warp == 0) tmem_alloc(&sm.tmem_base, 256);
@@ -318,227 +323,265 @@ r7c_bwd_final_kernel(const bf16* __restrict__ w, const __grid_constant__ CUtenso
   __syncthreads();
   tc_fence_after();
   const uint32_t tm = sm.tmem_base;
-  if (tid == 0) {
-    mbar_expect_tx(&sm.bar_ld, 12 * TILE_BYTES);
-    tma_load_4d(sm.dout, &tmap_do, &sm.bar_ld, 0, t0, hi, bi);
-    tma_load_4d(sm.v, &tmap_v, &sm.bar_ld, 0, t0, hi, bi);
-    bulk_load(sm.dz, tiles + S_DZ * TILE_BYTES, TILE_BYTES, &sm.bar_ld);
-    bulk_load(sm.sa, tiles + S_SA * TILE_BYTES, TILE_BYTES, &sm.bar_ld);
-    bulk_load(sm.aqk, tiles + S_AQK * TILE_BYTES, 2 * TILE_BYTES, &sm.bar_ld);
-    bulk_load(sm.qt, tiles + S_QT * TILE_BYTES, TILE_BYTES, &sm.bar_ld);
-    bulk_load(sm.at, tiles + S_AT * TILE_BYTES, TILE_BYTES, &sm.bar_ld);
-    bulk_load(sm.kt, tiles + S_KT * TILE_BYTES, TILE_BYTES, &sm.bar_ld);
-    bulk_load(sm.bt, tiles + S_BT * TILE_BYTES, TILE_BYTES, &sm.bar_ld);
-    bulk_load(sm.h0, tiles + S_H0 * TILE_BYTES, TILE_BYTES, &sm.bar_ld);
-    bulk_load(sm.dhh, tiles + S_DHH * TILE_BYTES, TILE_BYTES, &sm.bar_ld);
-  }
-  R7C_STAMP(16);
 
-  // ---- g of every (token, channel) while the tiles arrive
+  auto coords = [&](int ch, int& bi, int& hi, int& t0) {
+    const int unit = ch / NT;
+    bi = unit / H; hi = unit % H; t0 = (ch % NT) * L;
+  };
+  auto load_group_a = [&](int ch) {     // tid 0
+    int bi, hi, t0; coords(ch, bi, hi, t0);
+    const unsigned char* tiles = ws_tiles + (size_t)ch * tiles_per_chunk * TILE_BYTES;
+    mbar_expect_tx(&sm.bar_lda, 8 * TILE_BYTES);
+    tma_load_4d(sm.dout, &tmap_do, &sm.bar_lda, 0, t0, hi, bi);
+    tma_load_4d(sm.v, &tmap_v, &sm.bar_lda, 0, t0, hi, bi);
+    bulk_load(sm.dz, tiles + S_DZ * TILE_BYTES, TILE_BYTES, &sm.bar_lda);
+    bulk_load(sm.sa, tiles + S_SA * TILE_BYTES, TILE_BYTES, &sm.bar_lda);
+    bulk_load(sm.aqk, tiles + S_AQK * TILE_BYTES, 2 * TILE_BYTES, &sm.bar_lda);
+    bulk_load(sm.h0, tiles + S_H0 * TILE_BYTES, TILE_BYTES, &sm.bar_lda);
+    bulk_load(sm.dhh, tiles + S_DHH * TILE_BYTES, TILE_BYTES, &sm.bar_lda);
+  };
+  auto load_group_b = [&](int ch) {     // tid 0
+    const unsigned char* tiles = ws_tiles + (size_t)ch * tiles_per_chunk * TILE_BYTES;
+    mbar_expect_tx(&sm.bar_ldb, 4 * TILE_BYTES);
+    bulk_load(sm.qt, tiles + S_QT * TILE_BYTES, TILE_BYTES, &sm.bar_ldb);
+    bulk_load(sm.at, tiles + S_AT * TILE_BYTES, TILE_BYTES, &sm.bar_ldb);
+    bulk_load(sm.kt, tiles + S_KT * TILE_BYTES, TILE_BYTES, &sm.bar_ldb);
+    bulk_load(sm.bt, tiles + S_BT * TILE_BYTES, TILE_BYTES, &sm.bar_ldb);
+  };
+  auto load_w = [&](int ch, uint4 (&rw)[2]) {   // all threads: 2 x 8 channels of the chunk's w rows
+    int bi, hi, t0; coords(ch, bi, hi, t0);
+    const long long base = bi * lay.sb + hi * lay.sh;
 #pragma unroll
-  for (int n = 0; n < 2; ++n) {
-    const int e = tid + 256 * n, row = e >> 3, cc = e & 7, tok = t0 + row;
-    const bool valid = tok < Tn;
-    uint4 rw = make_uint4(0u, 0u, 0u, 0u);
-    if (valid) rw = __ldg(reinterpret_cast<const uint4*>(w + base + (long long)tok * lay.st + 8 * cc));
-    const uint32_t u[4] = {rw.x, rw.y, rw.z, rw.w};
-    float g[8];
-#pragma unroll
-    for (int m = 0; m < 4; ++m) {
-      g[2 * m] = valid ? -__expf(bf16_lo(u[m])) : 0.f;
-      g[2 * m + 1] = valid ? -__expf(bf16_hi(u[m])) : 0.f;
+    for (int n = 0; n < 2; ++n) {
+      const int e = tid + 256 * n, row = e >> 3, cc = e & 7, tok = t0 + row;
+      rw[n] = make_uint4(0u, 0u, 0u, 0u);
+      if (tok < Tn) rw[n] = __ldg(reinterpret_cast<const uint4*>(w + base + (long long)tok * lay.st + 8 * cc));
     }
-    *reinterpret_cast<float4*>(&sm.gg[row * NROW + 8 * cc]) = make_float4(g[0], g[1], g[2], g[3]);
-    *reinterpret_cast<float4*>(&sm.gg[row * NROW + 8 * cc + 4]) = make_float4(g[4], g[5], g[6], g[7]);
-  }
-  R7C_STAMP(17);
-  bool ok = mbar_wait(&sm.bar_ld, 0, status, 321);
-  __syncthreads();
-  R7C_STAMP(18);
+  };
 
-  // ---- MMA group 1: all four dA products, and dv
-  if (tid == 0 && ok) {
-    tc_fence_after();
-    umma_tile<128, 128, 0, 0>(tmem_addr(tm, 0, 0), smem_u32(sm.dout), smem_u32(sm.v), false);        // [do;dz] [v;sa]^T
-    umma_tile<64, 64, 1, 1, 8>(tmem_addr(tm, 0, 128), smem_u32(sm.aqk), smem_u32(sm.dout), false);   // A_qk^T do + A_ak^T dz
-    umma_tile<64, 64, 0, 1>(tmem_addr(tm, 0, 128), smem_u32(sm.kt), smem_u32(sm.dhh), true);         // + k~ dh^
-    umma_commit(&sm.bar_m1);
-  }
-  // ---- meanwhile: prefix sums of g over tokens, thread = (channel, quarter of the chunk)
-  {
-    const int c = tid & 63, quarter = tid >> 6;
-    float gv[16];
-#pragma unroll
-    for (int j = 0; j < 16; ++j) gv[j] = sm.gg[(16 * quarter + j) * NROW + c];
-    float run = 0.f;
-#pragma unroll
-    for (int j = 0; j < 16; ++j) { run += gv[j]; gv[j] = run; }
-    sm.qtot[quarter][c] = run;
-    __syncthreads();
-    const float add = (quarter & 1) ? sm.qtot[quarter - 1][c] : 0.f;    // start of the half
-#pragma unroll
-    for (int j = 0; j < 16; ++j) sm.gs[(16 * quarter + j) * NROW + c] = gv[j] + add;
-  }
-  // dglast[c] = sum_v dh^[c][v] X[c][v]  (X straight from the workspace)
-  if (tid >= 128 && tid < 192 && ok) {
-    const int c = tid - 128;
-    float s = 0.f;
-    const uint4* xr = reinterpret_cast<const uint4*>(tiles + S_X * TILE_BYTES);
-#pragma unroll
-    for (int cchunk = 0; cchunk < 8; ++cchunk) {
-      const uint4 xa = __ldg(xr + (tile_chunk_off(c, cchunk) >> 4));
-      const uint4 da_ = *reinterpret_cast<const uint4*>(sm.dhh + tile_chunk_off(c, cchunk));
-      s += bf16_lo(xa.x) * bf16_lo(da_.x) + bf16_hi(xa.x) * bf16_hi(da_.x);
-      s += bf16_lo(xa.y) * bf16_lo(da_.y) + bf16_hi(xa.y) * bf16_hi(da_.y);
-      s += bf16_lo(xa.z) * bf16_lo(da_.z) + bf16_hi(xa.z) * bf16_hi(da_.z);
-      s += bf16_lo(xa.w) * bf16_lo(da_.w) + bf16_hi(xa.w) * bf16_hi(da_.w);
-    }
-    sm.dgl[c] = s;
-  }
-  ok = mbar_wait(&sm.bar_m1, 0, status, 322) && ok;
-  tc_fence_after();
-  R7C_STAMP(19);
-  if (ok) {
-    const int r = 32 * wq + lane, i = r & 63;
-    const bool lower = r >= 64;       // rows of dz: strictly lower; rows of do: lower incl. diagonal
-#pragma unroll
-    for (int pp = 0; pp < 2; ++pp) {
-      const int part = 2 * hsel + pp;   // hsel 0: products with v (dA_qk / dA_ak); hsel 1: with sa (dA_qb / dA_ab)
-      uint32_t rr[32];
-      tmem_ld32(tmem_addr(tm, 32 * wq, 32 * part), rr);
-      tmem_ld_wait();
-      float x[32];
-      const int j0 = 32 * pp;
-#pragma unroll
-      for (int j = 0; j < 32; ++j) {
-        const bool keep = lower ? (j0 + j < i) : (j0 + j <= i);
-        x[j] = keep ? __uint_as_float(rr[j]) : 0.f;
-      }
-      unsigned char* dst = lower ? (hsel ? sm.daab : sm.daak) : (hsel ? sm.daqb : sm.daqk);
-      tile_store_row32(dst, i, j0, x);
-    }
-    // dv rows sit on the lower lane halves of columns 128..191; each warp of a pair takes 32 columns
-    const int row = 16 * wq + (lane & 15);
-    uint32_t rr[32];
-    tmem_ld32(tmem_addr(tm, 32 * wq, 128 + 32 * hsel), rr);
-    tmem_ld_wait();
-    if (lane < 16) {     // staged in the A_qk tile (dead: MMA group 1 has completed), stored by TMA below
-      float x[32];
-#pragma unroll
-      for (int j = 0; j < 32; ++j) x[j] = __uint_as_float(rr[j]);
-      tile_store_row32(sm.aqk, row, 32 * hsel, x);
-    }
-  }
-  fence_async_smem();
-  tc_fence_before();
-  __syncthreads();
-  R7C_STAMP(20);
-  if (tid == 32 && ok) {
-    tma_store_4d(&tmap_dv, sm.aqk, 0, t0, hi, bi);
-    bulk_commit();
+  uint4 rw[2];
+  if (blockIdx.x < n_ch) {
+    if (tid == 0) { load_group_a(blockIdx.x); load_group_b(blockIdx.x); }
+    load_w(blockIdx.x, rw);
   }
 
-  // ---- MMA group 2: [dq~; da~] (columns 0..63) and [dk~; db~] (columns 64..127)
-  if (tid == 0 && ok) {
-    tc_fence_after();
-    umma_tile<128, 64, 0, 0>(tmem_addr(tm, 0, 0), smem_u32(sm.dout), smem_u32(sm.h0), false);        // [do;dz] h~0^T
-    umma_tile<128, 64, 0, 1>(tmem_addr(tm, 0, 0), smem_u32(sm.daqk), smem_u32(sm.kt), true);         // + [dA_qk;dA_ak] k~
-    umma_tile<128, 64, 0, 1>(tmem_addr(tm, 0, 0), smem_u32(sm.daqb), smem_u32(sm.bt), true);         // + [dA_qb;dA_ab] b~
-    umma_tile<128, 64, 1, 1>(tmem_addr(tm, 0, 64), smem_u32(sm.daqk), smem_u32(sm.qt), false, 2 * TILE_BYTES);  // [dA_qk|dA_qb]^T q~
-    umma_tile<128, 64, 1, 1>(tmem_addr(tm, 0, 64), smem_u32(sm.daak), smem_u32(sm.at), true, 2 * TILE_BYTES);   // + [dA_ak|dA_ab]^T a~
-    umma_tile<128, 64, 0, 0>(tmem_addr(tm, 0, 64), smem_u32(sm.v), smem_u32(sm.dhh), true);          // + [v;sa] dh^^T
-    umma_commit(&sm.bar_m2);
-  }
-  ok = mbar_wait(&sm.bar_m2, 0, status, 323) && ok;
-  tc_fence_after();
-  R7C_STAMP(21);
+  bool ok = true;
+  int it = 0;
+  for (int ch = blockIdx.x; ch < n_ch && ok; ch += gridDim.x, ++it) {
+    int bi, hi, t0; coords(ch, bi, hi, t0);
+    const unsigned char* tiles = ws_tiles + (size_t)ch * tiles_per_chunk * TILE_BYTES;
+    const uint32_t par = it & 1;
+    const int next = ch + gridDim.x;
+    R7C_STAMP(16);
 
-  // ---- epilogue.  Row r < 64 holds dq~_i and dk~_i (token i = r), row r >= 64 holds da~_i, db~_i; the
-  // two warps of a lane window take 32 channels each.  Row owners read and write the fp32 scratch
-  // arrays as float4 (conflict-free with the padded rows).  red1 = dq~ q~ - dk~ k~ and
-  // red2 = da~ a~ - db~ b~ live in the dA tiles' space, dge = da~ a~ in the [do; dz; v; sa] space: all
-  // those tiles are dead once MMA group 2 has completed.
-  float* red1 = reinterpret_cast<float*>(sm.daqk);
-  float* red2 = red1 + L * NROW;
-  float* dge = reinterpret_cast<float*>(sm.dout);
-  if (ok) {
-    const int r = 32 * wq + lane, i = r & 63;
-    const bool second = r >= 64;
-    float* red = second ? red2 : red1;
-    const int c0 = 32 * hsel;
-    uint32_t r1[32], r2[32];
-    tmem_ld32(tmem_addr(tm, 32 * wq, c0), r1);          // dq~ / da~
-    tmem_ld32(tmem_addr(tm, 32 * wq, 64 + c0), r2);     // dk~ / db~
-    tmem_ld_wait();
-    float t1[32], t2[32], o1[32], o2[32];
-    tile_load_row32(second ? sm.at : sm.qt, i, c0, t1);
-    tile_load_row32(second ? sm.bt : sm.kt, i, c0, t2);
+    // ---- g of every (token, channel), from the w rows already in registers
 #pragma unroll
-    for (int j4 = 0; j4 < 32; j4 += 4) {
-      const int c = c0 + j4;
-      const float4 gs4 = *reinterpret_cast<const float4*>(&sm.gs[i * NROW + c]);
-      const float4 gg4 = *reinterpret_cast<const float4*>(&sm.gg[i * NROW + c]);
-      const float4 ta4 = *reinterpret_cast<const float4*>(&sm.qtot[0][c]);
-      const float4 tb4 = *reinterpret_cast<const float4*>(&sm.qtot[1][c]);
-      const float gsv[4] = {gs4.x, gs4.y, gs4.z, gs4.w}, ggv[4] = {gg4.x, gg4.y, gg4.z, gg4.w};
-      const float ttv[4] = {ta4.x + tb4.x, ta4.y + tb4.y, ta4.z + tb4.z, ta4.w + tb4.w};   // gref - (start of chunk)
-      float rd[4], ge[4];
+    for (int n = 0; n < 2; ++n) {
+      const int e = tid + 256 * n, row = e >> 3, cc = e & 7;
+      const bool valid = t0 + row < Tn;
+      const uint32_t u[4] = {rw[n].x, rw[n].y, rw[n].z, rw[n].w};
+      float g[8];
 #pragma unroll
       for (int m = 0; m < 4; ++m) {
-        const int j = j4 + m;
-        const float d1 = gsv[m] - (i < 32 ? ttv[m] : 0.f);            // gi - gref
-        const float x1 = __uint_as_float(r1[j]), x2 = __uint_as_float(r2[j]);
-        o2[j] = x2 * cexp(-d1);                                        // dk / db
-        o1[j] = x1 * (second ? cexp(d1 - ggv[m]) : cexp(d1));          // da / dq
-        ge[m] = x1 * t1[j];
-        rd[m] = ge[m] - x2 * t2[j];
+        g[2 * m] = valid ? -__expf(bf16_lo(u[m])) : 0.f;
+        g[2 * m + 1] = valid ? -__expf(bf16_hi(u[m])) : 0.f;
       }
-      *reinterpret_cast<float4*>(&red[i * NROW + c]) = make_float4(rd[0], rd[1], rd[2], rd[3]);
-      if (second) *reinterpret_cast<float4*>(&dge[i * NROW + c]) = make_float4(ge[0], ge[1], ge[2], ge[3]);
+      *reinterpret_cast<float4*>(&sm.gg[row * NROW + 8 * cc]) = make_float4(g[0], g[1], g[2], g[3]);
+      *reinterpret_cast<float4*>(&sm.gg[row * NROW + 8 * cc + 4]) = make_float4(g[4], g[5], g[6], g[7]);
     }
-    // staged as bf16 tiles in dead operand tiles (dq -> h0, dk -> dhh, da -> aak, db -> sa), stored by TMA
-    tile_store_row32(second ? sm.aak : sm.h0, i, c0, o1);
-    tile_store_row32(second ? sm.sa : sm.dhh, i, c0, o2);
-  }
-  fence_async_smem();
-  __syncthreads();
-  R7C_STAMP(22);
-  if (tid == 32 && ok) {
-    tma_store_4d(&tmap_dq, sm.h0, 0, t0, hi, bi);
-    tma_store_4d(&tmap_dk, sm.dhh, 0, t0, hi, bi);
-    tma_store_4d(&tmap_da, sm.aak, 0, t0, hi, bi);
-    tma_store_4d(&tmap_db, sm.sa, 0, t0, hi, bi);
-    bulk_commit();
-  }
-  // reverse inclusive prefix over tokens, per channel; thread = (channel, quarter)
-  {
-    const int c = tid & 63, quarter = tid >> 6;
-    float rv[16];
-#pragma unroll
-    for (int j = 0; j < 16; ++j) rv[j] = red1[(16 * quarter + j) * NROW + c] + red2[(16 * quarter + j) * NROW + c];
-    float run = 0.f;
-#pragma unroll
-    for (int j = 15; j >= 0; --j) { run += rv[j]; rv[j] = run; }
-    sm.rqtot[quarter][c] = run;
-    __syncthreads();
-    float add = sm.dgl[c];
-    for (int q2 = quarter + 1; q2 < 4; ++q2) add += sm.rqtot[q2][c];
-#pragma unroll
-    for (int j = 0; j < 16; ++j) {      // dw staged in the q~ tile (its last reader was the epilogue above)
-      const int ii = 16 * quarter + j;
-      const float dg = rv[j] + add - dge[ii * NROW + c];
-      *reinterpret_cast<bf16*>(sm.qt + tile_off(ii, c)) = __float2bfloat16_rn(dg * sm.gg[ii * NROW + c]);
+    if (tid == 0) bulk_wait_read();    // the TMA stores of the previous chunk-head have left the staging tiles
+    R7C_STAMP(17);
+    ok = mbar_wait(&sm.bar_lda, par, status, 321) && ok;
+    ok = mbar_wait(&sm.bar_ldb, par, status, 324) && ok;
+    ok = __syncthreads_and(ok);
+    R7C_STAMP(18);
+
+    // ---- MMA group 1: all four dA products, and dv
+    if (tid == 0 && ok) {
+      tc_fence_after();
+      umma_tile<128, 128, 0, 0>(tmem_addr(tm, 0, 0), smem_u32(sm.dout), smem_u32(sm.v), false);        // [do;dz] [v;sa]^T
+      umma_tile<64, 64, 1, 1, 8>(tmem_addr(tm, 0, 128), smem_u32(sm.aqk), smem_u32(sm.dout), false);   // A_qk^T do + A_ak^T dz
+      umma_tile<64, 64, 0, 1>(tmem_addr(tm, 0, 128), smem_u32(sm.kt), smem_u32(sm.dhh), true);         // + k~ dh^
+      umma_commit(&sm.bar_m1);
     }
+    // ---- meanwhile: prefix sums of g over tokens, thread = (channel, quarter of the chunk)
+    {
+      const int c = tid & 63, quarter = tid >> 6;
+      float gv[16];
+#pragma unroll
+      for (int j = 0; j < 16; ++j) gv[j] = sm.gg[(16 * quarter + j) * NROW + c];
+      float run = 0.f;
+#pragma unroll
+      for (int j = 0; j < 16; ++j) { run += gv[j]; gv[j] = run; }
+      sm.qtot[quarter][c] = run;
+      __syncthreads();
+      const float add = (quarter & 1) ? sm.qtot[quarter - 1][c] : 0.f;    // start of the half
+#pragma unroll
+      for (int j = 0; j < 16; ++j) sm.gs[(16 * quarter + j) * NROW + c] = gv[j] + add;
+    }
+    // dglast[c] = sum_v dh^[c][v] X[c][v]  (X straight from the workspace)
+    if (tid >= 128 && tid < 192 && ok) {
+      const int c = tid - 128;
+      float s_ = 0.f;
+      const uint4* xr = reinterpret_cast<const uint4*>(tiles + S_X * TILE_BYTES);
+#pragma unroll
+      for (int cchunk = 0; cchunk < 8; ++cchunk) {
+        const uint4 xa = __ldg(xr + (tile_chunk_off(c, cchunk) >> 4));
+        const uint4 da_ = *reinterpret_cast<const uint4*>(sm.dhh + tile_chunk_off(c, cchunk));
+        s_ += bf16_lo(xa.x) * bf16_lo(da_.x) + bf16_hi(xa.x) * bf16_hi(da_.x);
+        s_ += bf16_lo(xa.y) * bf16_lo(da_.y) + bf16_hi(xa.y) * bf16_hi(da_.y);
+        s_ += bf16_lo(xa.z) * bf16_lo(da_.z) + bf16_hi(xa.z) * bf16_hi(da_.z);
+        s_ += bf16_lo(xa.w) * bf16_lo(da_.w) + bf16_hi(xa.w) * bf16_hi(da_.w);
+      }
+      sm.dgl[c] = s_;
+    }
+    ok = mbar_wait(&sm.bar_m1, par, status, 322) && ok;
+    tc_fence_after();
+    R7C_STAMP(19);
+    if (ok) {
+      const int r = 32 * wq + lane, i = r & 63;
+      const bool lower = r >= 64;       // rows of dz: strictly lower; rows of do: lower incl. diagonal
+#pragma unroll
+      for (int pp = 0; pp < 2; ++pp) {
+        const int part = 2 * hsel + pp;   // hsel 0: products with v (dA_qk / dA_ak); hsel 1: with sa (dA_qb / dA_ab)
+        uint32_t rr[32];
+        tmem_ld32(tmem_addr(tm, 32 * wq, 32 * part), rr);
+        tmem_ld_wait();
+        float x[32];
+        const int j0 = 32 * pp;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const bool keep = lower ? (j0 + j < i) : (j0 + j <= i);
+          x[j] = keep ? __uint_as_float(rr[j]) : 0.f;
+        }
+        unsigned char* dst = lower ? (hsel ? sm.daab : sm.daak) : (hsel ? sm.daqb : sm.daqk);
+        tile_store_row32(dst, i, j0, x);
+      }
+      // dv rows sit on the lower lane halves of columns 128..191; each warp of a pair takes 32 columns.
+      // Staged in the A_qk tile (dead: MMA group 1 has completed), stored by TMA below.
+      const int row = 16 * wq + (lane & 15);
+      uint32_t rr[32];
+      tmem_ld32(tmem_addr(tm, 32 * wq, 128 + 32 * hsel), rr);
+      tmem_ld_wait();
+      if (lane < 16) {
+        float x[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) x[j] = __uint_as_float(rr[j]);
+        tile_store_row32(sm.aqk, row, 32 * hsel, x);
+      }
+    }
+    fence_async_smem();
+    tc_fence_before();
+    ok = __syncthreads_and(ok);
+    R7C_STAMP(20);
+
+    // ---- MMA group 2: [dq~; da~] (columns 0..63) and [dk~; db~] (columns 64..127)
+    if (tid == 0 && ok) {
+      tc_fence_after();
+      umma_tile<128, 64, 0, 0>(tmem_addr(tm, 0, 0), smem_u32(sm.dout), smem_u32(sm.h0), false);        // [do;dz] h~0^T
+      umma_tile<128, 64, 0, 1>(tmem_addr(tm, 0, 0), smem_u32(sm.daqk), smem_u32(sm.kt), true);         // + [dA_qk;dA_ak] k~
+      umma_tile<128, 64, 0, 1>(tmem_addr(tm, 0, 0), smem_u32(sm.daqb), smem_u32(sm.bt), true);         // + [dA_qb;dA_ab] b~
+      umma_tile<128, 64, 1, 1>(tmem_addr(tm, 0, 64), smem_u32(sm.daqk), smem_u32(sm.qt), false, 2 * TILE_BYTES);  // [dA_qk|dA_qb]^T q~
+      umma_tile<128, 64, 1, 1>(tmem_addr(tm, 0, 64), smem_u32(sm.daak), smem_u32(sm.at), true, 2 * TILE_BYTES);   // + [dA_ak|dA_ab]^T a~
+      umma_tile<128, 64, 0, 0>(tmem_addr(tm, 0, 64), smem_u32(sm.v), smem_u32(sm.dhh), true);          // + [v;sa] dh^^T
+      umma_commit(&sm.bar_m2);
+      tma_store_4d(&tmap_dv, sm.aqk, 0, t0, hi, bi);
+      bulk_commit();
+    }
+    ok = mbar_wait(&sm.bar_m2, par, status, 323) && ok;
+    tc_fence_after();
+    R7C_STAMP(21);
+    // group A tiles are free: request the next chunk-head's, and fetch its w rows
+    if (next < n_ch) {
+      if (tid == 0 && ok) { bulk_wait_read(); load_group_a(next); }
+      load_w(next, rw);
+    }
+
+    // ---- epilogue.  Row r < 64 holds dq~_i and dk~_i (token i = r), row r >= 64 holds da~_i, db~_i; the
+    // two warps of a lane window take 32 channels each.  Row owners read and write the fp32 scratch
+    // arrays as float4 (conflict-free with the padded rows).  red1 = dq~ q~ - dk~ k~ and
+    // red2 = da~ a~ - db~ b~ overlay the dA tiles (dead once MMA group 2 has completed).
+    float* red1 = reinterpret_cast<float*>(sm.daqk);
+    float* red2 = red1 + L * NROW;
+    if (ok) {
+      const int r = 32 * wq + lane, i = r & 63;
+      const bool second = r >= 64;
+      float* red = second ? red2 : red1;
+      const int c0 = 32 * hsel;
+      uint32_t r1[32], r2[32];
+      tmem_ld32(tmem_addr(tm, 32 * wq, c0), r1);          // dq~ / da~
+      tmem_ld32(tmem_addr(tm, 32 * wq, 64 + c0), r2);     // dk~ / db~
+      tmem_ld_wait();
+      float t1[32], t2[32], o1[32], o2[32], ge[32];
+      tile_load_row32(second ? sm.at : sm.qt, i, c0, t1);
+      tile_load_row32(second ? sm.bt : sm.kt, i, c0, t2);
+#pragma unroll
+      for (int j4 = 0; j4 < 32; j4 += 4) {
+        const int c = c0 + j4;
+        const float4 gs4 = *reinterpret_cast<const float4*>(&sm.gs[i * NROW + c]);
+        const float4 gg4 = *reinterpret_cast<const float4*>(&sm.gg[i * NROW + c]);
+        const float4 ta4 = *reinterpret_cast<const float4*>(&sm.qtot[0][c]);
+        const float4 tb4 = *reinterpret_cast<const float4*>(&sm.qtot[1][c]);
+        const float gsv[4] = {gs4.x, gs4.y, gs4.z, gs4.w}, ggv[4] = {gg4.x, gg4.y, gg4.z, gg4.w};
+        const float ttv[4] = {ta4.x + tb4.x, ta4.y + tb4.y, ta4.z + tb4.z, ta4.w + tb4.w};   // gref - (start of chunk)
+        float rd[4];
+#pragma unroll
+        for (int m = 0; m < 4; ++m) {
+          const int j = j4 + m;
+          const float d1 = gsv[m] - (i < 32 ? ttv[m] : 0.f);            // gi - gref
+          const float x1 = __uint_as_float(r1[j]), x2 = __uint_as_float(r2[j]);
+          o2[j] = x2 * cexp(-d1);                                        // dk / db
+          o1[j] = x1 * (second ? cexp(d1 - ggv[m]) : cexp(d1));          // da / dq
+          ge[j] = x1 * t1[j];
+          rd[m] = ge[j] - x2 * t2[j];
+        }
+        *reinterpret_cast<float4*>(&red[i * NROW + c]) = make_float4(rd[0], rd[1], rd[2], rd[3]);
+      }
+      if (second) tile_store_row32(sm.dge, i, c0, ge);
+      tile_store_row32(sm.stage[second ? 2 : 0], i, c0, o1);    // da / dq
+      tile_store_row32(sm.stage[second ? 3 : 1], i, c0, o2);    // db / dk
+    }
+    fence_async_smem();
+    ok = __syncthreads_and(ok);
+    R7C_STAMP(22);
+    if (tid == 0 && ok) {
+      tma_store_4d(&tmap_dq, sm.stage[0], 0, t0, hi, bi);
+      tma_store_4d(&tmap_dk, sm.stage[1], 0, t0, hi, bi);
+      tma_store_4d(&tmap_da, sm.stage[2], 0, t0, hi, bi);
+      tma_store_4d(&tmap_db, sm.stage[3], 0, t0, hi, bi);
+      bulk_commit();
+      if (next < n_ch) load_group_b(next);      // q~, a~, k~, b~ were last read by the epilogue above
+    }
+    // reverse inclusive prefix over tokens, per channel; thread = (channel, quarter)
+    {
+      const int c = tid & 63, quarter = tid >> 6;
+      float rv[16];
+#pragma unroll
+      for (int j = 0; j < 16; ++j) rv[j] = red1[(16 * quarter + j) * NROW + c] + red2[(16 * quarter + j) * NROW + c];
+      float run = 0.f;
+#pragma unroll
+      for (int j = 15; j >= 0; --j) { run += rv[j]; rv[j] = run; }
+      sm.rqtot[quarter][c] = run;
+      __syncthreads();
+      float add = sm.dgl[c];
+      for (int q2 = quarter + 1; q2 < 4; ++q2) add += sm.rqtot[q2][c];
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        const int ii = 16 * quarter + j;
+        const float e_ = __bfloat162float(*reinterpret_cast<const bf16*>(sm.dge + tile_off(ii, c)));
+        const float dg = rv[j] + add - e_;
+        *reinterpret_cast<bf16*>(sm.stage[4] + tile_off(ii, c)) = __float2bfloat16_rn(dg * sm.gg[ii * NROW + c]);
+      }
+    }
+    fence_async_smem();
+    tc_fence_before();
+    ok = __syncthreads_and(ok);
+    if (tid == 0 && ok) { tma_store_4d(&tmap_dw, sm.stage[4], 0, t0, hi, bi); bulk_commit(); }
+    R7C_STAMP(23);
   }
-  fence_async_smem();
+  if (tid == 0) bulk_wait_all();
   tc_fence_before();
   __syncthreads();
-  if (tid == 32) {
-    if (ok) { tma_store_4d(&tmap_dw, sm.qt, 0, t0, hi, bi); bulk_commit(); }
-    bulk_wait_all();
-  }
-  __syncthreads();
-  R7C_STAMP(23);
   if (warp == 0) tmem_dealloc(tm, 256);
 #undef R7C_STAMP
 }
@@ -592,10 +635,15 @@ int launch_rwkv7_chunked_bwd(const void* r, const void* w, const void* k, const 
     const int smem = (int)sizeof(FinalSmem) + 1024;
     if (cuda_ok(cudaFuncSetAttribute(r7c_bwd_final_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem))) return RWKVB200_E_CUDA;
     ProfScope prof("r7c_bwd_final_kernel", st);
-    r7c_bwd_final_kernel<<<B * H * NT, 256, smem, st>>>((const bf16*)w, tmap_do, tmap_v, ws.tiles, ALL_TILES,
-                                                         tmap_out[0], tmap_out[1], tmap_out[2], tmap_out[3],
-                                                         tmap_out[4], tmap_out[5], Tn, H, NT, lay, status,
-                                                         debug_stamp_buffer());
+    const int n_ch = B * H * NT;
+    int dev = 0, sms = 0;
+    if (cuda_ok(cudaGetDevice(&dev)) || cuda_ok(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)))
+      return RWKVB200_E_CUDA;
+    const int grid = n_ch < sms ? n_ch : sms;     // persistent: one CTA per SM
+    r7c_bwd_final_kernel<<<grid, 256, smem, st>>>((const bf16*)w, tmap_do, tmap_v, ws.tiles, ALL_TILES,
+                                                   tmap_out[0], tmap_out[1], tmap_out[2], tmap_out[3],
+                                                   tmap_out[4], tmap_out[5], Tn, H, NT, n_ch, lay, status,
+                                                   debug_stamp_buffer());
   }
   return check_launch();
 }
