@@ -31,23 +31,22 @@ struct IntraSmem {
   uint32_t tmem_base;
 };
 
+// Persistent: CTAs (two per SM) walk over chunk-heads ch = blockIdx.x, blockIdx.x + gridDim.x, ...; the
+// token rows of the next chunk-head are fetched into registers while the current one is in its MMA
+// phases, and its v tile is requested as soon as MMA 2 has read the current one.
 // 256 threads: warp w reads TMEM lanes 32*(w&3).. and the two warps that share a lane window split
 // the columns (hsel = w>>2); the triangular solve runs on warps 0-1 while the other warps drain MMA 2.
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 2)
 r7c_intra_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ w, const bf16* __restrict__ k,
                      const bf16* __restrict__ a, const bf16* __restrict__ b,
                      const __grid_constant__ CUtensorMap tmap_v, unsigned char* __restrict__ ws_tiles,
                      float* __restrict__ ws_aux, int tiles_per_chunk, int keep_for_bwd,
-                     int Tn, int H, int NT, TokLayout lay, int* status, long long* dbg) {
-#define R7C_STAMP(n) do { if (dbg && tid == 0 && blockIdx.x == gridDim.x / 2) dbg[n] = clock64(); } while (0)
+                     int Tn, int H, int NT, int n_ch, TokLayout lay, int* status, long long* dbg) {
+#define R7C_STAMP(n) do { if (dbg && tid == 0 && blockIdx.x == gridDim.x / 2 && it == 1) dbg[n] = clock64(); } while (0)
   extern __shared__ unsigned char smem_raw[];
   IntraSmem& sm = *reinterpret_cast<IntraSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int wq = warp & 3, hsel = warp >> 2;
-  const int ch = blockIdx.x, unit = ch / NT, cidx = ch % NT;
-  const int bi = unit / H, hi = unit % H, t0 = cidx * L;
-  const long long base = bi * lay.sb + hi * lay.sh;
-  unsigned char* out_tiles = ws_tiles + (size_t)ch * tiles_per_chunk * TILE_BYTES;
 
   if (tid == 0) {
     mbar_init(&sm.bar_v, 1); mbar_init(&sm.bar_m1, 1); mbar_init(&sm.bar_m2, 1); mbar_init(&sm.bar_m3, 1);
@@ -58,18 +57,16 @@ r7c_intra_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ w, con
   __syncthreads();
   tc_fence_after();
   const uint32_t tm = sm.tmem_base;
-  if (tid == 0) {
-    mbar_expect_tx(&sm.bar_v, TILE_BYTES);
-    tma_load_4d(sm.v, &tmap_v, &sm.bar_v, 0, t0, hi, bi);
-  }
 
-  R7C_STAMP(0);
-  // ---- phase A: decay prefix sums and the four scaled operands.
-  // 16-byte loads (8 channels of one token), all in flight at once; the prefix sum over tokens goes
-  // through shared memory (the fp32 area that later holds A_ab).
-  {
-    float* gs = sm.nmat;
-    uint4 rw[2], rq[2], rk[2], ra[2], rb[2];
+  auto coords = [&](int ch, int& bi, int& hi, int& t0) {
+    const int unit = ch / NT;
+    bi = unit / H; hi = unit % H; t0 = (ch % NT) * L;
+  };
+  // 16-byte loads (8 channels of one token) of the five token tensors, two per thread and tensor
+  uint4 rw[2], rq[2], rk[2], ra[2], rb[2];
+  auto load_rows = [&](int ch) {
+    int bi, hi, t0; coords(ch, bi, hi, t0);
+    const long long base = bi * lay.sb + hi * lay.sh;
     const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
     for (int n = 0; n < 2; ++n) {
@@ -82,261 +79,296 @@ r7c_intra_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ w, con
       ra[n] = valid ? __ldg(reinterpret_cast<const uint4*>(a + off)) : zero4;
       rb[n] = valid ? __ldg(reinterpret_cast<const uint4*>(b + off)) : zero4;
     }
-    float gown[2][8];     // g of this thread's 2 x 8 (token, channel) entries
-#pragma unroll
-    for (int n = 0; n < 2; ++n) {
-      const int e = tid + 256 * n, row = e >> 3, cc = e & 7;
-      const bool valid = t0 + row < Tn;
-      const uint32_t u[4] = {rw[n].x, rw[n].y, rw[n].z, rw[n].w};
-#pragma unroll
-      for (int m = 0; m < 4; ++m) {
-        gown[n][2 * m] = valid ? -__expf(bf16_lo(u[m])) : 0.f;
-        gown[n][2 * m + 1] = valid ? -__expf(bf16_hi(u[m])) : 0.f;
-      }
-      *reinterpret_cast<float4*>(&gs[row * NROW + 8 * cc]) = make_float4(gown[n][0], gown[n][1], gown[n][2], gown[n][3]);
-      *reinterpret_cast<float4*>(&gs[row * NROW + 8 * cc + 4]) = make_float4(gown[n][4], gown[n][5], gown[n][6], gown[n][7]);
-    }
-    __syncthreads();
-    R7C_STAMP(1);
+  };
+  auto load_v = [&](int ch) {   // tid 0
+    int bi, hi, t0; coords(ch, bi, hi, t0);
+    mbar_expect_tx(&sm.bar_v, TILE_BYTES);
+    tma_load_4d(sm.v, &tmap_v, &sm.bar_v, 0, t0, hi, bi);
+  };
+  if (blockIdx.x < n_ch) {
+    if (tid == 0) load_v(blockIdx.x);
+    load_rows(blockIdx.x);
+  }
+
+  bool ok = true;
+  int it = 0;
+  for (int ch = blockIdx.x; ch < n_ch && ok; ch += gridDim.x, ++it) {
+    int bi, hi, t0; coords(ch, bi, hi, t0);
+    unsigned char* out_tiles = ws_tiles + (size_t)ch * tiles_per_chunk * TILE_BYTES;
+    const uint32_t par = it & 1;
+    const int next = ch + gridDim.x;
+
+    R7C_STAMP(0);
+    // the copies of the previous chunk-head's q~, k~, b~, A_qb, O1, Ainv tiles have left shared memory
+    // (its W, U copies, committed last, may still be reading: those tiles are rewritten only after MMA 1)
+    if (tid == 0) bulk_wait_read_1();
+    // ---- phase A: decay prefix sums and the four scaled operands; the prefix sum over tokens goes
+    // through shared memory (the fp32 area that later holds A_ab).
     {
-      const int c = tid & 63, quarter = tid >> 6;
-      float gv[16];
+      float* gs = sm.nmat;
+      float gown[2][8];     // g of this thread's 2 x 8 (token, channel) entries
 #pragma unroll
-      for (int j = 0; j < 16; ++j) gv[j] = gs[(16 * quarter + j) * NROW + c];
-      float run = 0.f;
+      for (int n = 0; n < 2; ++n) {
+        const int e = tid + 256 * n, row = e >> 3, cc = e & 7;
+        const bool valid = t0 + row < Tn;
+        const uint32_t u[4] = {rw[n].x, rw[n].y, rw[n].z, rw[n].w};
 #pragma unroll
-      for (int j = 0; j < 16; ++j) { run += gv[j]; gv[j] = run; }
-      sm.qtot[quarter][c] = run;
-      __syncthreads();
-      const float add = (quarter & 1) ? sm.qtot[quarter - 1][c] : 0.f;
-#pragma unroll
-      for (int j = 0; j < 16; ++j) gs[(16 * quarter + j) * NROW + c] = gv[j] + add;   // prefix inside each half
-    }
-    __syncthreads();
-    if (tid < 64) {
-      const float tot0 = sm.qtot[0][tid] + sm.qtot[1][tid], tot1 = sm.qtot[2][tid] + sm.qtot[3][tid];
-      ws_aux[(size_t)ch * AUX_FLOATS + tid] = __expf(fmaxf(tot0, -EXP_CLAMP));        // e^{gref}
-      ws_aux[(size_t)ch * AUX_FLOATS + 64 + tid] = __expf(fmaxf(tot1, -EXP_CLAMP));   // e^{glast-gref}
-    }
-#pragma unroll
-    for (int n = 0; n < 2; ++n) {
-      const int e = tid + 256 * n, row = e >> 3, cc = e & 7;
-      const bool first_half = row < 32;
-      float gl[8], sh[8], sh2[8];
-      *reinterpret_cast<float4*>(gl) = *reinterpret_cast<const float4*>(&gs[row * NROW + 8 * cc]);
-      *reinterpret_cast<float4*>(gl + 4) = *reinterpret_cast<const float4*>(&gs[row * NROW + 8 * cc + 4]);
-      *reinterpret_cast<float4*>(sh) = *reinterpret_cast<const float4*>(&sm.qtot[0][8 * cc]);
-      *reinterpret_cast<float4*>(sh + 4) = *reinterpret_cast<const float4*>(&sm.qtot[0][8 * cc + 4]);
-      *reinterpret_cast<float4*>(sh2) = *reinterpret_cast<const float4*>(&sm.qtot[1][8 * cc]);
-      *reinterpret_cast<float4*>(sh2 + 4) = *reinterpret_cast<const float4*>(&sm.qtot[1][8 * cc + 4]);
-      const uint32_t uq[4] = {rq[n].x, rq[n].y, rq[n].z, rq[n].w};
-      const uint32_t uk[4] = {rk[n].x, rk[n].y, rk[n].z, rk[n].w};
-      const uint32_t ua[4] = {ra[n].x, ra[n].y, ra[n].z, ra[n].w};
-      const uint32_t ub[4] = {rb[n].x, rb[n].y, rb[n].z, rb[n].w};
-      uint32_t oq[4], ok_[4], oa[4], ob[4];
-#pragma unroll
-      for (int m = 0; m < 4; ++m) {
-        float eq[2], ek[2], ea[2];
-#pragma unroll
-        for (int hh = 0; hh < 2; ++hh) {
-          const int x = 2 * m + hh;
-          const float d1 = gl[x] - (first_half ? sh[x] + sh2[x] : 0.f);   // gi - gref
-          eq[hh] = cexp(d1); ek[hh] = cexp(-d1); ea[hh] = cexp(d1 - gown[n][x]);
+        for (int m = 0; m < 4; ++m) {
+          gown[n][2 * m] = valid ? -__expf(bf16_lo(u[m])) : 0.f;
+          gown[n][2 * m + 1] = valid ? -__expf(bf16_hi(u[m])) : 0.f;
         }
-        oq[m] = pack_bf16(bf16_lo(uq[m]) * eq[0], bf16_hi(uq[m]) * eq[1]);
-        ok_[m] = pack_bf16(bf16_lo(uk[m]) * ek[0], bf16_hi(uk[m]) * ek[1]);
-        oa[m] = pack_bf16(bf16_lo(ua[m]) * ea[0], bf16_hi(ua[m]) * ea[1]);
-        ob[m] = pack_bf16(bf16_lo(ub[m]) * ek[0], bf16_hi(ub[m]) * ek[1]);
+        *reinterpret_cast<float4*>(&gs[row * NROW + 8 * cc]) = make_float4(gown[n][0], gown[n][1], gown[n][2], gown[n][3]);
+        *reinterpret_cast<float4*>(&gs[row * NROW + 8 * cc + 4]) = make_float4(gown[n][4], gown[n][5], gown[n][6], gown[n][7]);
       }
-      const uint32_t off = tile_chunk_off(row, cc);
-      *reinterpret_cast<uint4*>(sm.qt + off) = make_uint4(oq[0], oq[1], oq[2], oq[3]);
-      *reinterpret_cast<uint4*>(sm.kt + off) = make_uint4(ok_[0], ok_[1], ok_[2], ok_[3]);
-      *reinterpret_cast<uint4*>(sm.at + off) = make_uint4(oa[0], oa[1], oa[2], oa[3]);
-      *reinterpret_cast<uint4*>(sm.bt + off) = make_uint4(ob[0], ob[1], ob[2], ob[3]);
+      __syncthreads();
+      R7C_STAMP(1);
+      {
+        const int c = tid & 63, quarter = tid >> 6;
+        float gv[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) gv[j] = gs[(16 * quarter + j) * NROW + c];
+        float run = 0.f;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) { run += gv[j]; gv[j] = run; }
+        sm.qtot[quarter][c] = run;
+        __syncthreads();
+        const float add = (quarter & 1) ? sm.qtot[quarter - 1][c] : 0.f;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) gs[(16 * quarter + j) * NROW + c] = gv[j] + add;   // prefix inside each half
+      }
+      __syncthreads();
+      if (tid < 64) {
+        const float tot0 = sm.qtot[0][tid] + sm.qtot[1][tid], tot1 = sm.qtot[2][tid] + sm.qtot[3][tid];
+        ws_aux[(size_t)ch * AUX_FLOATS + tid] = __expf(fmaxf(tot0, -EXP_CLAMP));        // e^{gref}
+        ws_aux[(size_t)ch * AUX_FLOATS + 64 + tid] = __expf(fmaxf(tot1, -EXP_CLAMP));   // e^{glast-gref}
+      }
+#pragma unroll
+      for (int n = 0; n < 2; ++n) {
+        const int e = tid + 256 * n, row = e >> 3, cc = e & 7;
+        const bool first_half = row < 32;
+        float gl[8], sh[8], sh2[8];
+        *reinterpret_cast<float4*>(gl) = *reinterpret_cast<const float4*>(&gs[row * NROW + 8 * cc]);
+        *reinterpret_cast<float4*>(gl + 4) = *reinterpret_cast<const float4*>(&gs[row * NROW + 8 * cc + 4]);
+        *reinterpret_cast<float4*>(sh) = *reinterpret_cast<const float4*>(&sm.qtot[0][8 * cc]);
+        *reinterpret_cast<float4*>(sh + 4) = *reinterpret_cast<const float4*>(&sm.qtot[0][8 * cc + 4]);
+        *reinterpret_cast<float4*>(sh2) = *reinterpret_cast<const float4*>(&sm.qtot[1][8 * cc]);
+        *reinterpret_cast<float4*>(sh2 + 4) = *reinterpret_cast<const float4*>(&sm.qtot[1][8 * cc + 4]);
+        const uint32_t uq[4] = {rq[n].x, rq[n].y, rq[n].z, rq[n].w};
+        const uint32_t uk[4] = {rk[n].x, rk[n].y, rk[n].z, rk[n].w};
+        const uint32_t ua[4] = {ra[n].x, ra[n].y, ra[n].z, ra[n].w};
+        const uint32_t ub[4] = {rb[n].x, rb[n].y, rb[n].z, rb[n].w};
+        uint32_t oq[4], ok_[4], oa[4], ob[4];
+#pragma unroll
+        for (int m = 0; m < 4; ++m) {
+          float eq[2], ek[2], ea[2];
+#pragma unroll
+          for (int hh = 0; hh < 2; ++hh) {
+            const int x = 2 * m + hh;
+            const float d1 = gl[x] - (first_half ? sh[x] + sh2[x] : 0.f);   // gi - gref
+            eq[hh] = cexp(d1); ek[hh] = cexp(-d1); ea[hh] = cexp(d1 - gown[n][x]);
+          }
+          oq[m] = pack_bf16(bf16_lo(uq[m]) * eq[0], bf16_hi(uq[m]) * eq[1]);
+          ok_[m] = pack_bf16(bf16_lo(uk[m]) * ek[0], bf16_hi(uk[m]) * ek[1]);
+          oa[m] = pack_bf16(bf16_lo(ua[m]) * ea[0], bf16_hi(ua[m]) * ea[1]);
+          ob[m] = pack_bf16(bf16_lo(ub[m]) * ek[0], bf16_hi(ub[m]) * ek[1]);
+        }
+        const uint32_t off = tile_chunk_off(row, cc);
+        *reinterpret_cast<uint4*>(sm.qt + off) = make_uint4(oq[0], oq[1], oq[2], oq[3]);
+        *reinterpret_cast<uint4*>(sm.kt + off) = make_uint4(ok_[0], ok_[1], ok_[2], ok_[3]);
+        *reinterpret_cast<uint4*>(sm.at + off) = make_uint4(oa[0], oa[1], oa[2], oa[3]);
+        *reinterpret_cast<uint4*>(sm.bt + off) = make_uint4(ob[0], ob[1], ob[2], ob[3]);
+      }
     }
-  }
-  fence_async_smem();
-  __syncthreads();
+    fence_async_smem();
+    __syncthreads();
 
-  R7C_STAMP(2);
-  // ---- MMA 1: [q~; a~] [k~; b~]^T  ->  TMEM columns 0..127, row r on lane r
-  if (tid == 0) {
+    R7C_STAMP(2);
+    // ---- MMA 1: [q~; a~] [k~; b~]^T  ->  TMEM columns 0..127, row r on lane r
+    if (tid == 0) {
+      bulk_wait_read();      // the previous W, U copies are done: the epilogue below rewrites their tiles
+      tc_fence_after();
+      umma_tile<128, 128, 0, 0>(tm, smem_u32(sm.qt), smem_u32(sm.kt), false);
+      umma_commit(&sm.bar_m1);
+    }
+    ok = mbar_wait(&sm.bar_m1, par, status, 201) && ok;
     tc_fence_after();
-    umma_tile<128, 128, 0, 0>(tm, smem_u32(sm.qt), smem_u32(sm.kt), false);
-    umma_commit(&sm.bar_m1);
-  }
-  bool ok = mbar_wait(&sm.bar_m1, 0, status, 201);
-  tc_fence_after();
-  R7C_STAMP(3);
-  if (ok) {
-    const int r = 32 * wq + lane, i = r & 63;
-    const bool lower = r >= 64;       // rows of a~: strictly lower triangle; rows of q~: lower incl. diagonal
+    R7C_STAMP(3);
+    if (ok) {
+      const int r = 32 * wq + lane, i = r & 63;
+      const bool lower = r >= 64;       // rows of a~: strictly lower triangle; rows of q~: lower incl. diagonal
 #pragma unroll
-    for (int pp = 0; pp < 2; ++pp) {
-      uint32_t rr[32];
-      tmem_ld32(tmem_addr(tm, 32 * wq, 64 * hsel + 32 * pp), rr);   // hsel 0: products with k~, 1: with b~
-      tmem_ld_wait();
-      float x[32];
-      const int j0 = 32 * pp;
+      for (int pp = 0; pp < 2; ++pp) {
+        uint32_t rr[32];
+        tmem_ld32(tmem_addr(tm, 32 * wq, 64 * hsel + 32 * pp), rr);   // hsel 0: products with k~, 1: with b~
+        tmem_ld_wait();
+        float x[32];
+        const int j0 = 32 * pp;
 #pragma unroll
-      for (int j = 0; j < 32; ++j) {
-        const bool keep = lower ? (j0 + j < i) : (j0 + j <= i);
-        x[j] = keep ? __uint_as_float(rr[j]) : 0.f;
-      }
-      if (!lower) {
-        tile_store_row32(hsel ? sm.aqb : sm.aqk, i, j0, x);
-      } else if (!hsel) {
-        tile_store_row32(sm.aak, i, j0, x);
-      } else {
+        for (int j = 0; j < 32; ++j) {
+          const bool keep = lower ? (j0 + j < i) : (j0 + j <= i);
+          x[j] = keep ? __uint_as_float(rr[j]) : 0.f;
+        }
+        if (!lower) {
+          tile_store_row32(hsel ? sm.aqb : sm.aqk, i, j0, x);
+        } else if (!hsel) {
+          tile_store_row32(sm.aak, i, j0, x);
+        } else {
 #pragma unroll
-        for (int j = 0; j < 32; j += 4)
-          *reinterpret_cast<float4*>(&sm.nmat[i * NROW + j0 + j]) = make_float4(x[j], x[j + 1], x[j + 2], x[j + 3]);
+          for (int j = 0; j < 32; j += 4)
+            *reinterpret_cast<float4*>(&sm.nmat[i * NROW + j0 + j]) = make_float4(x[j], x[j + 1], x[j + 2], x[j + 3]);
+        }
       }
     }
-  }
-  fence_async_smem();
-  tc_fence_before();
-  __syncthreads();
+    fence_async_smem();
+    tc_fence_before();
+    ok = __syncthreads_and(ok);
 
-  R7C_STAMP(4);
-  // ---- MMA 2: [A_qk; A_ak] v  ->  TMEM columns 128..191 (rows 0..63 = O1, 64..127 = Y)
-  if (tid == 0) {
-    ok = mbar_wait(&sm.bar_v, 0, status, 202);
-    tc_fence_after();
-    umma_tile<128, 64, 0, 1>(tmem_addr(tm, 0, 128), smem_u32(sm.aqk), smem_u32(sm.v), false);
-    umma_commit(&sm.bar_m2);
-    if (keep_for_bwd) {   // A_qk, A_ak, a~ are operands of the backward: copy them out before they are overwritten
-      bulk_store(out_tiles + S_AQK * TILE_BYTES, sm.aqk, TILE_BYTES);
-      bulk_store(out_tiles + S_AAK * TILE_BYTES, sm.aak, TILE_BYTES);
-      bulk_store(out_tiles + S_AT * TILE_BYTES, sm.at, TILE_BYTES);
-      bulk_commit();
+    R7C_STAMP(4);
+    // ---- MMA 2: [A_qk; A_ak] v  ->  TMEM columns 128..191 (rows 0..63 = O1, 64..127 = Y)
+    if (tid == 0) {
+      ok = mbar_wait(&sm.bar_v, par, status, 202) && ok;
+      tc_fence_after();
+      umma_tile<128, 64, 0, 1>(tmem_addr(tm, 0, 128), smem_u32(sm.aqk), smem_u32(sm.v), false);
+      umma_commit(&sm.bar_m2);
+      if (keep_for_bwd) {   // A_qk, A_ak, a~ are operands of the backward: copy them out before they are overwritten
+        bulk_store(out_tiles + S_AQK * TILE_BYTES, sm.aqk, TILE_BYTES);
+        bulk_store(out_tiles + S_AAK * TILE_BYTES, sm.aak, TILE_BYTES);
+        bulk_store(out_tiles + S_AT * TILE_BYTES, sm.at, TILE_BYTES);
+        bulk_commit();
+      }
     }
-  }
-  if (tid < 64) {
-    // ---- Ainv = (I - stril(A_ab))^-1 by blocked forward substitution in fp32, one column per thread.
-    // Rows go in four blocks of 16.  The block being solved lives in registers; finished blocks of
-    // the column are parked in shared memory (xs, in the space of the A_qk / A_ak tiles once MMA 2
-    // has read them) so that the block loops stay rolled and small enough for the instruction cache.
-    const int c = tid;
-    float* xs = reinterpret_cast<float*>(sm.aqk);          // xs[row][column], 64 x 64 fp32
-    for (int I = 0; I < 4; ++I) {
-      R7C_STAMP(10 + I);
-      float xb[16];
+    if (tid < 64) {
+      // ---- Ainv = (I - stril(A_ab))^-1 by blocked forward substitution in fp32, one column per thread.
+      // Rows go in four blocks of 16.  The block being solved lives in registers; finished blocks of
+      // the column are parked in shared memory (xs, in the space of the A_qk / A_ak tiles once MMA 2
+      // has read them) so that the block loops stay rolled and small enough for the instruction cache.
+      const int c = tid;
+      float* xs = reinterpret_cast<float*>(sm.aqk);          // xs[row][column], 64 x 64 fp32
+      for (int I = 0; I < 4; ++I) {
+        R7C_STAMP(10 + I);
+        float xb[16];
 #pragma unroll
-      for (int rr = 0; rr < 16; ++rr) xb[rr] = (16 * I + rr == c) ? 1.f : 0.f;
-      for (int J = 0; J < I; ++J) {
-        float xj[16];
+        for (int rr = 0; rr < 16; ++rr) xb[rr] = (16 * I + rr == c) ? 1.f : 0.f;
+        for (int J = 0; J < I; ++J) {
+          float xj[16];
 #pragma unroll
-        for (int t = 0; t < 16; ++t) xj[t] = xs[(16 * J + t) * 64 + c];
+          for (int t = 0; t < 16; ++t) xj[t] = xs[(16 * J + t) * 64 + c];
 #pragma unroll
-        for (int rr = 0; rr < 16; ++rr) {
-          const float* nrow = &sm.nmat[(16 * I + rr) * NROW + 16 * J];
+          for (int rr = 0; rr < 16; ++rr) {
+            const float* nrow = &sm.nmat[(16 * I + rr) * NROW + 16 * J];
 #pragma unroll
-          for (int jj = 0; jj < 4; ++jj) {
-            const float4 n = *reinterpret_cast<const float4*>(nrow + 4 * jj);
-            xb[rr] += n.x * xj[4 * jj] + n.y * xj[4 * jj + 1] + n.z * xj[4 * jj + 2] + n.w * xj[4 * jj + 3];
+            for (int jj = 0; jj < 4; ++jj) {
+              const float4 n = *reinterpret_cast<const float4*>(nrow + 4 * jj);
+              xb[rr] += n.x * xj[4 * jj] + n.y * xj[4 * jj + 1] + n.z * xj[4 * jj + 2] + n.w * xj[4 * jj + 3];
+            }
           }
         }
-      }
 #pragma unroll
-      for (int rr = 1; rr < 16; ++rr) {
-        const float* nrow = &sm.nmat[(16 * I + rr) * NROW + 16 * I];
-        float p0 = 0.f, p1 = 0.f, p2 = 0.f, p3 = 0.f;   // entries at or right of the diagonal are 0
+        for (int rr = 1; rr < 16; ++rr) {
+          const float* nrow = &sm.nmat[(16 * I + rr) * NROW + 16 * I];
+          float p0 = 0.f, p1 = 0.f, p2 = 0.f, p3 = 0.f;   // entries at or right of the diagonal are 0
 #pragma unroll
-        for (int jj = 0; jj < (rr + 3) / 4; ++jj) {
-          const float4 n = *reinterpret_cast<const float4*>(nrow + 4 * jj);
-          p0 += n.x * xb[4 * jj];
-          if (4 * jj + 1 < rr) p1 += n.y * xb[4 * jj + 1];
-          if (4 * jj + 2 < rr) p2 += n.z * xb[4 * jj + 2];
-          if (4 * jj + 3 < rr) p3 += n.w * xb[4 * jj + 3];
+          for (int jj = 0; jj < (rr + 3) / 4; ++jj) {
+            const float4 n = *reinterpret_cast<const float4*>(nrow + 4 * jj);
+            p0 += n.x * xb[4 * jj];
+            if (4 * jj + 1 < rr) p1 += n.y * xb[4 * jj + 1];
+            if (4 * jj + 2 < rr) p2 += n.z * xb[4 * jj + 2];
+            if (4 * jj + 3 < rr) p3 += n.w * xb[4 * jj + 3];
+          }
+          xb[rr] += (p0 + p1) + (p2 + p3);
         }
-        xb[rr] += (p0 + p1) + (p2 + p3);
-      }
-      if (I == 0) {
-        // first write to xs: MMA 2 (and the copies of A_qk / A_ak kept for the backward) must be done
-        ok = mbar_wait(&sm.bar_m2, 0, status, 205) && ok;
-        if (tid == 0 && keep_for_bwd) bulk_wait_read();
-        asm volatile("bar.sync 1, 64;" ::: "memory");
-      }
+        if (I == 0) {
+          // first write to xs: MMA 2 (and the copies of A_qk / A_ak kept for the backward) must be done
+          ok = mbar_wait(&sm.bar_m2, par, status, 205) && ok;
+          if (tid == 0) {
+            if (keep_for_bwd) bulk_wait_read();
+            if (next < n_ch) load_v(next);      // MMA 2 has read the v tile: request the next one
+          }
+          asm volatile("bar.sync 1, 64;" ::: "memory");
+        }
 #pragma unroll
-      for (int rr = 0; rr < 16; ++rr) {
-        if (I < 3) xs[(16 * I + rr) * 64 + c] = xb[rr];
-        *reinterpret_cast<bf16*>(sm.ainv + tile_off(16 * I + rr, c)) = __float2bfloat16_rn(xb[rr]);
+        for (int rr = 0; rr < 16; ++rr) {
+          if (I < 3) xs[(16 * I + rr) * 64 + c] = xb[rr];
+          *reinterpret_cast<bf16*>(sm.ainv + tile_off(16 * I + rr, c)) = __float2bfloat16_rn(xb[rr]);
+        }
       }
-    }
-  } else {
-    // rows of MMA 2 for the other six warps: warps 4-5 take O1 (both column halves), warps 2-3 and
-    // 6-7 take Y (one column half each)
-    ok = mbar_wait(&sm.bar_m2, 0, status, 203) && ok;
-    tc_fence_after();
-    const int i = (32 * wq + lane) & 63;
-    if (wq < 2) {        // warps 4, 5
+    } else {
+      // rows of MMA 2 for the other six warps: warps 4-5 take O1 (both column halves), warps 2-3 and
+      // 6-7 take Y (one column half each)
+      ok = mbar_wait(&sm.bar_m2, par, status, 203) && ok;
+      tc_fence_after();
+      const int i = (32 * wq + lane) & 63;
+      if (wq < 2) {        // warps 4, 5
 #pragma unroll
-      for (int part = 0; part < 2; ++part) {
+        for (int part = 0; part < 2; ++part) {
+          uint32_t rr[32];
+          tmem_ld32(tmem_addr(tm, 32 * wq, 128 + 32 * part), rr);
+          tmem_ld_wait();
+          float x[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) x[j] = __uint_as_float(rr[j]);
+          tile_store_row32(sm.o1, i, 32 * part, x);
+        }
+      } else {             // warps 2, 3, 6, 7
         uint32_t rr[32];
-        tmem_ld32(tmem_addr(tm, 32 * wq, 128 + 32 * part), rr);
+        tmem_ld32(tmem_addr(tm, 32 * wq, 128 + 32 * hsel), rr);
         tmem_ld_wait();
         float x[32];
 #pragma unroll
         for (int j = 0; j < 32; ++j) x[j] = __uint_as_float(rr[j]);
-        tile_store_row32(sm.o1, i, 32 * part, x);
+        tile_store_row32(sm.y, i, 32 * hsel, x);
       }
-    } else {             // warps 2, 3, 6, 7
+    }
+    R7C_STAMP(5);
+    fence_async_smem();
+    tc_fence_before();
+    ok = __syncthreads_and(ok);
+
+    R7C_STAMP(6);
+    // ---- MMA 3: W = Ainv a~ (lower lane halves), U = Ainv Y (upper lane halves) -> TMEM columns 0..63
+    if (tid == 0) {
+      tc_fence_after();
+      umma_tile<64, 64, 0, 1>(tmem_addr(tm, 0, 0), smem_u32(sm.ainv), smem_u32(sm.at), false);
+      umma_tile<64, 64, 0, 1>(tmem_addr(tm, 16, 0), smem_u32(sm.ainv), smem_u32(sm.y), false);
+      umma_commit(&sm.bar_m3);
+      bulk_store(out_tiles + S_QT * TILE_BYTES, sm.qt, TILE_BYTES);
+      bulk_store(out_tiles + S_KT * TILE_BYTES, sm.kt, TILE_BYTES);
+      bulk_store(out_tiles + S_BT * TILE_BYTES, sm.bt, TILE_BYTES);
+      bulk_store(out_tiles + S_AQB * TILE_BYTES, sm.aqb, TILE_BYTES);
+      bulk_store(out_tiles + S_O1 * TILE_BYTES, sm.o1, TILE_BYTES);
+      if (keep_for_bwd) bulk_store(out_tiles + S_AINV * TILE_BYTES, sm.ainv, TILE_BYTES);
+      bulk_commit();
+    }
+    if (next < n_ch) load_rows(next);     // in flight while MMA 3 runs and its result is read out
+    ok = mbar_wait(&sm.bar_m3, par, status, 204) && ok;
+    tc_fence_after();
+    R7C_STAMP(7);
+    {
+      // W -> the A_ak tile (free since MMA 2), U -> the Y tile (free: MMA 3 has completed)
+      const int i = 16 * wq + (lane & 15);
+      unsigned char* dst = lane < 16 ? sm.aak : sm.y;
       uint32_t rr[32];
-      tmem_ld32(tmem_addr(tm, 32 * wq, 128 + 32 * hsel), rr);
+      tmem_ld32(tmem_addr(tm, 32 * wq, 32 * hsel), rr);
       tmem_ld_wait();
       float x[32];
 #pragma unroll
       for (int j = 0; j < 32; ++j) x[j] = __uint_as_float(rr[j]);
-      tile_store_row32(sm.y, i, 32 * hsel, x);
+      tile_store_row32(dst, i, 32 * hsel, x);
     }
+    fence_async_smem();
+    tc_fence_before();
+    ok = __syncthreads_and(ok);
+    R7C_STAMP(8);
+    if (tid == 0 && ok) {
+      bulk_store(out_tiles + S_W * TILE_BYTES, sm.aak, TILE_BYTES);
+      bulk_store(out_tiles + S_U * TILE_BYTES, sm.y, TILE_BYTES);
+      bulk_commit();
+    }
+    R7C_STAMP(9);
   }
-  R7C_STAMP(5);
-  fence_async_smem();
+  if (tid == 0) bulk_wait_all();
   tc_fence_before();
   __syncthreads();
-
-  R7C_STAMP(6);
-  // ---- MMA 3: W = Ainv a~ (lower lane halves), U = Ainv Y (upper lane halves) -> TMEM columns 0..63
-  if (tid == 0) {
-    tc_fence_after();
-    umma_tile<64, 64, 0, 1>(tmem_addr(tm, 0, 0), smem_u32(sm.ainv), smem_u32(sm.at), false);
-    umma_tile<64, 64, 0, 1>(tmem_addr(tm, 16, 0), smem_u32(sm.ainv), smem_u32(sm.y), false);
-    umma_commit(&sm.bar_m3);
-    bulk_store(out_tiles + S_QT * TILE_BYTES, sm.qt, TILE_BYTES);
-    bulk_store(out_tiles + S_KT * TILE_BYTES, sm.kt, TILE_BYTES);
-    bulk_store(out_tiles + S_BT * TILE_BYTES, sm.bt, TILE_BYTES);
-    bulk_store(out_tiles + S_AQB * TILE_BYTES, sm.aqb, TILE_BYTES);
-    bulk_store(out_tiles + S_O1 * TILE_BYTES, sm.o1, TILE_BYTES);
-    if (keep_for_bwd) bulk_store(out_tiles + S_AINV * TILE_BYTES, sm.ainv, TILE_BYTES);
-    bulk_commit();
-  }
-  ok = mbar_wait(&sm.bar_m3, 0, status, 204) && ok;
-  tc_fence_after();
-  R7C_STAMP(7);
-  {
-    const int i = 16 * wq + (lane & 15);
-    unsigned char* dst = lane < 16 ? sm.aak : sm.v;     // W, U (both tiles are free: MMA 2 has completed)
-    uint32_t rr[32];
-    tmem_ld32(tmem_addr(tm, 32 * wq, 32 * hsel), rr);
-    tmem_ld_wait();
-    float x[32];
-#pragma unroll
-    for (int j = 0; j < 32; ++j) x[j] = __uint_as_float(rr[j]);
-    tile_store_row32(dst, i, 32 * hsel, x);
-  }
-  fence_async_smem();
-  tc_fence_before();
-  __syncthreads();
-  R7C_STAMP(8);
-  if (tid == 0) {
-    bulk_store(out_tiles + S_W * TILE_BYTES, sm.aak, TILE_BYTES);
-    bulk_store(out_tiles + S_U * TILE_BYTES, sm.v, TILE_BYTES);
-    bulk_commit();
-    bulk_wait_all();
-  }
-  __syncthreads();
-  R7C_STAMP(9);
   if (warp == 0) tmem_dealloc(tm, 256);
 #undef R7C_STAMP
 }
@@ -557,10 +589,15 @@ int launch_rwkv7_chunked_fwd(const void* r, const void* w, const void* k, const 
     const int smem = (int)sizeof(IntraSmem) + 1024;
     if (cuda_ok(cudaFuncSetAttribute(r7c_intra_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem))) return RWKVB200_E_CUDA;
     ProfScope prof("r7c_intra_fwd_kernel", st);
-    r7c_intra_fwd_kernel<<<B * H * NT, 256, smem, st>>>((const bf16*)r, (const bf16*)w, (const bf16*)k, (const bf16*)a,
-                                                         (const bf16*)b, tmap_v, ws.tiles, ws.aux, tpc,
-                                                         keep_for_bwd ? 1 : 0, Tn, H, NT, lay, status,
-                                                         debug_stamp_buffer());
+    const int n_ch = B * H * NT;
+    int dev = 0, sms = 0;
+    if (cuda_ok(cudaGetDevice(&dev)) || cuda_ok(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)))
+      return RWKVB200_E_CUDA;
+    const int grid = n_ch < 2 * sms ? n_ch : 2 * sms;     // persistent: two CTAs per SM
+    r7c_intra_fwd_kernel<<<grid, 256, smem, st>>>((const bf16*)r, (const bf16*)w, (const bf16*)k, (const bf16*)a,
+                                                   (const bf16*)b, tmap_v, ws.tiles, ws.aux, tpc,
+                                                   keep_for_bwd ? 1 : 0, Tn, H, NT, n_ch, lay, status,
+                                                   debug_stamp_buffer());
   }
   e = check_launch();
   if (e) return e;
