@@ -72,12 +72,32 @@ r7c_intra_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ w, con
     for (int n = 0; n < 2; ++n) {
       const int e = tid + 256 * n, row = e >> 3, cc = e & 7, tok = t0 + row;
       const long long off = base + (long long)tok * lay.st + 8 * cc;
-      const bool valid = tok < Tn;
-      rw[n] = valid ? __ldg(reinterpret_cast<const uint4*>(w + off)) : zero4;
-      rq[n] = valid ? __ldg(reinterpret_cast<const uint4*>(q + off)) : zero4;
-      rk[n] = valid ? __ldg(reinterpret_cast<const uint4*>(k + off)) : zero4;
-      ra[n] = valid ? __ldg(reinterpret_cast<const uint4*>(a + off)) : zero4;
-      rb[n] = valid ? __ldg(reinterpret_cast<const uint4*>(b + off)) : zero4;
+      rw[n] = zero4; rq[n] = zero4; rk[n] = zero4; ra[n] = zero4; rb[n] = zero4;
+      if (tok < Tn) {      // predicated loads straight into the registers: nothing waits on them here
+        rw[n] = __ldg(reinterpret_cast<const uint4*>(w + off));
+        rq[n] = __ldg(reinterpret_cast<const uint4*>(q + off));
+        rk[n] = __ldg(reinterpret_cast<const uint4*>(k + off));
+        ra[n] = __ldg(reinterpret_cast<const uint4*>(a + off));
+        rb[n] = __ldg(reinterpret_cast<const uint4*>(b + off));
+      }
+    }
+  };
+  // Ask for the next chunk-head's token rows to be brought into L2 (no registers are tied up); the
+  // loads at the top of the next iteration then hit L2.
+  auto prefetch_rows = [&](int ch) {
+    int bi, hi, t0; coords(ch, bi, hi, t0);
+    const long long base = bi * lay.sb + hi * lay.sh;
+#pragma unroll
+    for (int n = 0; n < 2; ++n) {
+      const int e = tid + 256 * n, row = e >> 3, cc = e & 7, tok = t0 + row;
+      if (tok < Tn && cc == 0) {      // one 128-byte row per request
+        const long long off = base + (long long)tok * lay.st;
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(w + off));
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(q + off));
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(k + off));
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(a + off));
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(b + off));
+      }
     }
   };
   auto load_v = [&](int ch) {   // tid 0
@@ -85,10 +105,11 @@ r7c_intra_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ w, con
     mbar_expect_tx(&sm.bar_v, TILE_BYTES);
     tma_load_4d(sm.v, &tmap_v, &sm.bar_v, 0, t0, hi, bi);
   };
-  if (blockIdx.x < n_ch) {
-    if (tid == 0) load_v(blockIdx.x);
-    load_rows(blockIdx.x);
-  }
+  if (blockIdx.x < n_ch && tid == 0) load_v(blockIdx.x);
+  // The two CTAs that share an SM would otherwise run their phases in lockstep and compete for the
+  // same unit (shared-memory pipe during the triangular solve); start every other CTA half a
+  // chunk-head late.
+  if (blockIdx.x & 1) __nanosleep(6000);
 
   bool ok = true;
   int it = 0;
@@ -99,6 +120,8 @@ r7c_intra_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ w, con
     const int next = ch + gridDim.x;
 
     R7C_STAMP(0);
+    load_rows(ch);
+    if (next < n_ch) prefetch_rows(next);
     // the copies of the previous chunk-head's q~, k~, b~, A_qb, O1, Ainv tiles have left shared memory
     // (its W, U copies, committed last, may still be reading: those tiles are rewritten only after MMA 1)
     if (tid == 0) bulk_wait_read_1();
@@ -237,86 +260,96 @@ r7c_intra_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ w, con
         bulk_commit();
       }
     }
-    if (tid < 64) {
-      // ---- Ainv = (I - stril(A_ab))^-1 by blocked forward substitution in fp32, one column per thread.
-      // Rows go in four blocks of 16.  The block being solved lives in registers; finished blocks of
-      // the column are parked in shared memory (xs, in the space of the A_qk / A_ak tiles once MMA 2
-      // has read them) so that the block loops stay rolled and small enough for the instruction cache.
-      const int c = tid;
+    // ---- rows of MMA 2 (warps 2-7), then Ainv = (I - stril(A_ab))^-1 in fp32 on all eight warps.
+    // Thread (column c = tid & 63, row block I = tid >> 6) owns the 16 entries X[16I .. 16I+15][c] of
+    // the inverse.  Blocked forward substitution, right-looking: in step J the threads of block J finish
+    // their block with a 16-row substitution against the diagonal block and publish it to shared memory
+    // (xs, in the space of the A_qk / A_ak tiles once MMA 2 has read them); after a barrier every later
+    // block subtracts its coupling with block J.  The four steps are the only serial chain.
+    {
+      const int c = tid & 63, I = tid >> 6;
       float* xs = reinterpret_cast<float*>(sm.aqk);          // xs[row][column], 64 x 64 fp32
-      for (int I = 0; I < 4; ++I) {
-        R7C_STAMP(10 + I);
-        float xb[16];
+      if (warp >= 2) {
+        // warps 4-5 take O1 (both column halves), warps 2-3 and 6-7 take Y (one column half each)
+        ok = mbar_wait(&sm.bar_m2, par, status, 203) && ok;
+        tc_fence_after();
+        const int i = (32 * wq + lane) & 63;
+        if (wq < 2) {        // warps 4, 5
 #pragma unroll
-        for (int rr = 0; rr < 16; ++rr) xb[rr] = (16 * I + rr == c) ? 1.f : 0.f;
-        for (int J = 0; J < I; ++J) {
-          float xj[16];
+          for (int part = 0; part < 2; ++part) {
+            uint32_t rr[32];
+            tmem_ld32(tmem_addr(tm, 32 * wq, 128 + 32 * part), rr);
+            tmem_ld_wait();
+            float x[32];
 #pragma unroll
-          for (int t = 0; t < 16; ++t) xj[t] = xs[(16 * J + t) * 64 + c];
-#pragma unroll
-          for (int rr = 0; rr < 16; ++rr) {
-            const float* nrow = &sm.nmat[(16 * I + rr) * NROW + 16 * J];
-#pragma unroll
-            for (int jj = 0; jj < 4; ++jj) {
-              const float4 n = *reinterpret_cast<const float4*>(nrow + 4 * jj);
-              xb[rr] += n.x * xj[4 * jj] + n.y * xj[4 * jj + 1] + n.z * xj[4 * jj + 2] + n.w * xj[4 * jj + 3];
-            }
+            for (int j = 0; j < 32; ++j) x[j] = __uint_as_float(rr[j]);
+            tile_store_row32(sm.o1, i, 32 * part, x);
           }
-        }
-#pragma unroll
-        for (int rr = 1; rr < 16; ++rr) {
-          const float* nrow = &sm.nmat[(16 * I + rr) * NROW + 16 * I];
-          float p0 = 0.f, p1 = 0.f, p2 = 0.f, p3 = 0.f;   // entries at or right of the diagonal are 0
-#pragma unroll
-          for (int jj = 0; jj < (rr + 3) / 4; ++jj) {
-            const float4 n = *reinterpret_cast<const float4*>(nrow + 4 * jj);
-            p0 += n.x * xb[4 * jj];
-            if (4 * jj + 1 < rr) p1 += n.y * xb[4 * jj + 1];
-            if (4 * jj + 2 < rr) p2 += n.z * xb[4 * jj + 2];
-            if (4 * jj + 3 < rr) p3 += n.w * xb[4 * jj + 3];
-          }
-          xb[rr] += (p0 + p1) + (p2 + p3);
-        }
-        if (I == 0) {
-          // first write to xs: MMA 2 (and the copies of A_qk / A_ak kept for the backward) must be done
-          ok = mbar_wait(&sm.bar_m2, par, status, 205) && ok;
-          if (tid == 0) {
-            if (keep_for_bwd) bulk_wait_read();
-            if (next < n_ch) load_v(next);      // MMA 2 has read the v tile: request the next one
-          }
-          asm volatile("bar.sync 1, 64;" ::: "memory");
-        }
-#pragma unroll
-        for (int rr = 0; rr < 16; ++rr) {
-          if (I < 3) xs[(16 * I + rr) * 64 + c] = xb[rr];
-          *reinterpret_cast<bf16*>(sm.ainv + tile_off(16 * I + rr, c)) = __float2bfloat16_rn(xb[rr]);
-        }
-      }
-    } else {
-      // rows of MMA 2 for the other six warps: warps 4-5 take O1 (both column halves), warps 2-3 and
-      // 6-7 take Y (one column half each)
-      ok = mbar_wait(&sm.bar_m2, par, status, 203) && ok;
-      tc_fence_after();
-      const int i = (32 * wq + lane) & 63;
-      if (wq < 2) {        // warps 4, 5
-#pragma unroll
-        for (int part = 0; part < 2; ++part) {
+        } else {             // warps 2, 3, 6, 7
           uint32_t rr[32];
-          tmem_ld32(tmem_addr(tm, 32 * wq, 128 + 32 * part), rr);
+          tmem_ld32(tmem_addr(tm, 32 * wq, 128 + 32 * hsel), rr);
           tmem_ld_wait();
           float x[32];
 #pragma unroll
           for (int j = 0; j < 32; ++j) x[j] = __uint_as_float(rr[j]);
-          tile_store_row32(sm.o1, i, 32 * part, x);
+          tile_store_row32(sm.y, i, 32 * hsel, x);
         }
-      } else {             // warps 2, 3, 6, 7
-        uint32_t rr[32];
-        tmem_ld32(tmem_addr(tm, 32 * wq, 128 + 32 * hsel), rr);
-        tmem_ld_wait();
-        float x[32];
+      }
+      float xb[16];
 #pragma unroll
-        for (int j = 0; j < 32; ++j) x[j] = __uint_as_float(rr[j]);
-        tile_store_row32(sm.y, i, 32 * hsel, x);
+      for (int rr = 0; rr < 16; ++rr) xb[rr] = (16 * I + rr == c) ? 1.f : 0.f;
+      const bool live = 16 * I + 15 >= c;        // rows above the diagonal of column c stay zero
+      for (int J = 0; J < 4; ++J) {
+        R7C_STAMP(10 + J);
+        if (I == J) {
+          if (live) {
+#pragma unroll
+            for (int rr = 1; rr < 16; ++rr) {
+              const float* nrow = &sm.nmat[(16 * I + rr) * NROW + 16 * I];
+              float p0 = 0.f, p1 = 0.f, p2 = 0.f, p3 = 0.f;   // entries at or right of the diagonal are 0
+#pragma unroll
+              for (int jj = 0; jj < (rr + 3) / 4; ++jj) {
+                const float4 n = *reinterpret_cast<const float4*>(nrow + 4 * jj);
+                p0 += n.x * xb[4 * jj];
+                if (4 * jj + 1 < rr) p1 += n.y * xb[4 * jj + 1];
+                if (4 * jj + 2 < rr) p2 += n.z * xb[4 * jj + 2];
+                if (4 * jj + 3 < rr) p3 += n.w * xb[4 * jj + 3];
+              }
+              xb[rr] += (p0 + p1) + (p2 + p3);
+            }
+          }
+          if (J == 0) {
+            // first write to xs: MMA 2 (and the copies of A_qk / A_ak kept for the backward) must be done
+            ok = mbar_wait(&sm.bar_m2, par, status, 205) && ok;
+            if (tid == 0) {
+              if (keep_for_bwd) bulk_wait_read();
+              if (next < n_ch) load_v(next);      // MMA 2 has read the v tile: request the next one
+            }
+            asm volatile("bar.sync 1, 64;" ::: "memory");
+          }
+#pragma unroll
+          for (int rr = 0; rr < 16; ++rr) {
+            if (J < 3) xs[(16 * I + rr) * 64 + c] = xb[rr];
+            *reinterpret_cast<bf16*>(sm.ainv + tile_off(16 * I + rr, c)) = __float2bfloat16_rn(xb[rr]);
+          }
+        }
+        if (J < 3) {
+          __syncthreads();
+          if (I > J && 16 * J + 15 >= c) {        // block J of column c is not all zero
+            float xj[16];
+#pragma unroll
+            for (int t = 0; t < 16; ++t) xj[t] = xs[(16 * J + t) * 64 + c];
+#pragma unroll
+            for (int rr = 0; rr < 16; ++rr) {
+              const float* nrow = &sm.nmat[(16 * I + rr) * NROW + 16 * J];
+#pragma unroll
+              for (int jj = 0; jj < 4; ++jj) {
+                const float4 n = *reinterpret_cast<const float4*>(nrow + 4 * jj);
+                xb[rr] += n.x * xj[4 * jj] + n.y * xj[4 * jj + 1] + n.z * xj[4 * jj + 2] + n.w * xj[4 * jj + 3];
+              }
+            }
+          }
+        }
       }
     }
     R7C_STAMP(5);
@@ -339,7 +372,6 @@ r7c_intra_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ w, con
       if (keep_for_bwd) bulk_store(out_tiles + S_AINV * TILE_BYTES, sm.ainv, TILE_BYTES);
       bulk_commit();
     }
-    if (next < n_ch) load_rows(next);     // in flight while MMA 3 runs and its result is read out
     ok = mbar_wait(&sm.bar_m3, par, status, 204) && ok;
     tc_fence_after();
     R7C_STAMP(7);
