@@ -45,6 +45,12 @@ WORKLOADS = {
 # vector of 128 B, backward reads 7 and writes 6
 BYTES_PER_TOKEN_HEAD = 2560
 FLOP_PER_TOKEN_HEAD = 434176
+# DRAM traffic (dram__bytes_read + dram__bytes_write, ncu) per chunk-head (64 tokens of one head) of each
+# chunked kernel, captured on a small case (profiles/r7c_chunked_kernels_B2_T4096_H16.md); traffic grows
+# in proportion to the number of chunk-heads, so a full launch is this figure times B*H*ceil(T/64).
+TRAFFIC_PER_CHUNK_HEAD = {"r7c_intra_fwd_kernel": 114.0e3, "r7c_scan_fwd_kernel": 85.4e3,
+                          "r7c_bwd_pre_kernel": 36.0e3, "r7c_bwd_scan_kernel": 47.7e3,
+                          "r7c_bwd_final_kernel": 149.5e3}
 CPU_SAMPLE_T = 256     # tokens per sequence of the cpu_baseline sample
 REF_STEP_T = 128       # tokens per sequence of one --impl reference step
 
@@ -232,7 +238,10 @@ def run_ours(args, wl):
         bytes_per_unit = 1664 if "bwd" in top else 896
         achieved = units * bytes_per_unit / per_launch_s / 1e9
         roof = {"kernel": top, "bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
-                "frac": achieved / pk["hbm_gbs"], "traffic": None, "peak_source": pk["source"],
+                "frac": achieved / pk["hbm_gbs"],
+                "traffic": (TRAFFIC_PER_CHUNK_HEAD[top] * B * H * ((T + 63) // 64)
+                            if top in TRAFFIC_PER_CHUNK_HEAD else None),
+                "algorithmic_bytes": units * bytes_per_unit, "peak_source": pk["source"],
                 "launch_ms": top_ms / top_n,
                 "tensor_tflops_whole_step": units * FLOP_PER_TOKEN_HEAD / (ms_step / 1e3) / 1e12,
                 "kernels": {k_: {"ms_per_step": v[0] / args.steps, "launches_per_step": v[1] / args.steps}
