@@ -151,13 +151,15 @@ int rwkvb200_rwkv7_bwd_static(const void* r, const void* w, const void* k, const
  *                  state_map is the caller's to check on the host (the Python layer does, before the
  *                  launch); out-of-range entries are clamped on the device instead of trapping.
  *   sT             final state [B,H,64,64], may be NULL.
+ *   algo           RWKVB200_ALGO_AUTO / _RECURRENT (token-by-token float32) / _CHUNKED (tcgen05 with
+ *                  split-precision bf16 operands, float32-grade accuracy for every dtype); AUTO = chunked.
  * ---------------------------------------------------------------------------------------- */
 int rwkvb200_wkv6_fwd(const void* r, const void* k, const void* v, const void* w, const float* u,
                       const float* s0, int n_state, const int32_t* state_map,
                       void* y, float* sT,
-                      int B, int T, int H, int head_size, int dtype, void* stream);
+                      int B, int T, int H, int head_size, int dtype, int algo, void* stream);
 
-size_t rwkvb200_wkv6_bwd_workspace_bytes(int B, int T, int H, int head_size, int dtype);
+size_t rwkvb200_wkv6_bwd_workspace_bytes(int B, int T, int H, int head_size, int dtype, int algo);
 
 /* Backward of wkv6, including the gradient paths the reference's GPU operator lacks (initial state,
  * final-state gradient; wkv6_cuda.cu:291,316 hard-zero them).  d_y: gradient of y; d_sT (may be NULL):
@@ -169,7 +171,7 @@ int rwkvb200_wkv6_bwd(const void* r, const void* k, const void* v, const void* w
                       const void* d_y, const float* d_sT,
                       void* dr, void* dk, void* dv, void* dw, float* du, float* d_s0,
                       void* workspace, size_t workspace_bytes,
-                      int B, int T, int H, int head_size, int dtype, void* stream);
+                      int B, int T, int H, int head_size, int dtype, int algo, void* stream);
 
 /* ------------------------------------------------------------------------------------------
  * Diagnostics of the tensor-core path (no counterpart in the reference).

@@ -25,6 +25,12 @@ inline int resolve_r7_algo(int algo, int dtype) {
   return algo;
 }
 
+// wkv6: AUTO = chunked tensor-core path (its split-precision operands keep float32-grade accuracy).
+inline int resolve_w6_algo(int algo) {
+  algo &= 0xff;
+  return algo == RWKVB200_ALGO_RECURRENT ? RWKVB200_ALGO_RECURRENT : RWKVB200_ALGO_CHUNKED;
+}
+
 inline size_t r7_ckpt_bytes(int B, int T, int H) {
   const size_t nc = (size_t)(T + R7_CKPT - 1) / R7_CKPT;
   return align256((size_t)B * H * nc * HS * HS * sizeof(float));
@@ -156,7 +162,7 @@ int rwkvb200_rwkv7_bwd(const void* r, const void* w, const void* k, const void* 
 int rwkvb200_wkv6_fwd(const void* r, const void* k, const void* v, const void* w, const float* u,
                       const float* s0, int n_state, const int32_t* state_map,
                       void* y, float* sT,
-                      int B, int T, int H, int head_size, int dtype, void* stream) {
+                      int B, int T, int H, int head_size, int dtype, int algo, void* stream) {
   int e = check_common(B, T, H, head_size, dtype);
   if (e) return e;
   if (!r || !k || !v || !w || !u || !y) return RWKVB200_E_NULL;
@@ -165,12 +171,16 @@ int rwkvb200_wkv6_fwd(const void* r, const void* k, const void* v, const void* w
   if (n_state > 1 && !state_map && n_state != B) return RWKVB200_E_STATE_MAP;
   const void* ps[] = {r, k, v, w, u, s0, y, sT};
   for (const void* p : ps) if (p && !aligned16(p)) return RWKVB200_E_ALIGN;
+  if (resolve_w6_algo(algo) == RWKVB200_ALGO_CHUNKED)
+    return launch_wkv6_chunked_fwd(r, k, v, w, u, n_state ? s0 : nullptr, n_state, state_map, y, sT, nullptr,
+                                   B, T, H, dtype, (cudaStream_t)stream);
   return launch_wkv6_fwd(r, k, v, w, u, n_state ? s0 : nullptr, n_state, state_map, y, sT, nullptr,
                          B, T, H, dtype, (cudaStream_t)stream);
 }
 
-size_t rwkvb200_wkv6_bwd_workspace_bytes(int B, int T, int H, int head_size, int dtype) {
+size_t rwkvb200_wkv6_bwd_workspace_bytes(int B, int T, int H, int head_size, int dtype, int algo) {
   if (check_common(B, T, H, head_size, dtype)) return 0;
+  (void)algo;
   return w6_ckpt_bytes(B, T, H) + align256((size_t)B * H * 4 * HS * sizeof(float));
 }
 
@@ -179,7 +189,7 @@ int rwkvb200_wkv6_bwd(const void* r, const void* k, const void* v, const void* w
                       const void* d_y, const float* d_sT,
                       void* dr, void* dk, void* dv, void* dw, float* du, float* d_s0,
                       void* workspace, size_t workspace_bytes,
-                      int B, int T, int H, int head_size, int dtype, void* stream) {
+                      int B, int T, int H, int head_size, int dtype, int algo, void* stream) {
   int e = check_common(B, T, H, head_size, dtype);
   if (e) return e;
   if (!r || !k || !v || !w || !u || !d_y || !dr || !dk || !dv || !dw || !du) return RWKVB200_E_NULL;
@@ -188,7 +198,7 @@ int rwkvb200_wkv6_bwd(const void* r, const void* k, const void* v, const void* w
   if (n_state > 1 && !state_map && n_state != B) return RWKVB200_E_STATE_MAP;
   const void* ps[] = {r, k, v, w, u, s0, d_y, d_sT, dr, dk, dv, dw, du, d_s0, workspace};
   for (const void* p : ps) if (p && !aligned16(p)) return RWKVB200_E_ALIGN;
-  if (!workspace || workspace_bytes < rwkvb200_wkv6_bwd_workspace_bytes(B, T, H, head_size, dtype))
+  if (!workspace || workspace_bytes < rwkvb200_wkv6_bwd_workspace_bytes(B, T, H, head_size, dtype, algo))
     return RWKVB200_E_WORKSPACE;
   cudaStream_t st = (cudaStream_t)stream;
   float* ckpt = reinterpret_cast<float*>(workspace);

@@ -132,4 +132,10 @@ int launch_wkv6_bwd(const void* r, const void* k, const void* v, const void* w, 
                     int B, int Tn, int H, int dtype, cudaStream_t st);
 constexpr int W6_CKPT = 8;
 
+// Chunked tcgen05 wkv6 (wkv6_chunked.cu).  `states` (may be NULL) receives the fp32 state at every chunk
+// boundary, [B*H][ceil(T/64)+1][64][64].
+int launch_wkv6_chunked_fwd(const void* r, const void* k, const void* v, const void* w, const float* u,
+                            const float* s0, int n_state, const int32_t* smap, void* y, float* sT,
+                            float* states, int B, int Tn, int H, int dtype, cudaStream_t st);
+
 }  // namespace rwkvb200

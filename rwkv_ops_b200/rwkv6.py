@@ -10,6 +10,7 @@ gradients flow with ``with_state=True`` (to ``init_state`` as well), ``state_map
 """
 from __future__ import annotations
 
+import os
 from typing import Optional, Tuple
 
 import torch
@@ -17,11 +18,17 @@ import torch
 from . import _lib
 
 HEAD_SIZE = 64
+_ALGO_NAMES = {"auto": _lib.ALGO_AUTO, "recurrent": _lib.ALGO_RECURRENT, "chunked": _lib.ALGO_CHUNKED}
+
+
+def _default_algo() -> int:
+    return _ALGO_NAMES[os.environ.get("RWKV_OPS_B200_WKV6_ALGO", "auto").lower()]
 
 
 @torch.library.custom_op("rwkv_ops_b200::wkv6_fwd", mutates_args=())
 def _wkv6_fwd(r: torch.Tensor, k: torch.Tensor, v: torch.Tensor, w: torch.Tensor, u: torch.Tensor,
-              s0: Optional[torch.Tensor], state_map: Optional[torch.Tensor]) -> Tuple[torch.Tensor, torch.Tensor]:
+              s0: Optional[torch.Tensor], state_map: Optional[torch.Tensor], algo: int
+              ) -> Tuple[torch.Tensor, torch.Tensor]:
     lib = _lib.load()
     dev = _lib.require_cuda(r, k, v, w, u, s0, state_map)
     B, T, C = r.shape
@@ -33,13 +40,13 @@ def _wkv6_fwd(r: torch.Tensor, k: torch.Tensor, v: torch.Tensor, w: torch.Tensor
     with torch.cuda.device(dev):
         rc = lib.rwkvb200_wkv6_fwd(r.data_ptr(), k.data_ptr(), v.data_ptr(), w.data_ptr(), u.data_ptr(),
                                    _lib.ptr(s0), n_state, _lib.ptr(state_map), y.data_ptr(), sT.data_ptr(),
-                                   B, T, H, HEAD_SIZE, code, _lib.stream_ptr(dev))
+                                   B, T, H, HEAD_SIZE, code, algo, _lib.stream_ptr(dev))
         _lib.check(rc, "wkv6_fwd")
     return y, sT
 
 
 @_wkv6_fwd.register_fake
-def _(r, k, v, w, u, s0, state_map):
+def _(r, k, v, w, u, s0, state_map, algo):
     B, T, C = r.shape
     return torch.empty_like(r), r.new_empty((B, C // HEAD_SIZE, HEAD_SIZE, HEAD_SIZE), dtype=torch.float32)
 
@@ -47,7 +54,7 @@ def _(r, k, v, w, u, s0, state_map):
 @torch.library.custom_op("rwkv_ops_b200::wkv6_bwd", mutates_args=())
 def _wkv6_bwd(r: torch.Tensor, k: torch.Tensor, v: torch.Tensor, w: torch.Tensor, u: torch.Tensor,
               s0: Optional[torch.Tensor], state_map: Optional[torch.Tensor],
-              d_y: torch.Tensor, d_sT: Optional[torch.Tensor]
+              d_y: torch.Tensor, d_sT: Optional[torch.Tensor], algo: int
               ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
     lib = _lib.load()
     dev = _lib.require_cuda(r, k, v, w, u, s0, state_map, d_y, d_sT)
@@ -59,19 +66,19 @@ def _wkv6_bwd(r: torch.Tensor, k: torch.Tensor, v: torch.Tensor, w: torch.Tensor
     ds0 = torch.empty(B, H, HEAD_SIZE, HEAD_SIZE, dtype=torch.float32, device=dev)
     n_state = 0 if s0 is None else s0.shape[0]
     with torch.cuda.device(dev):
-        nws = lib.rwkvb200_wkv6_bwd_workspace_bytes(B, T, H, HEAD_SIZE, code)
+        nws = lib.rwkvb200_wkv6_bwd_workspace_bytes(B, T, H, HEAD_SIZE, code, algo)
         ws = torch.empty(nws, dtype=torch.uint8, device=dev)
         rc = lib.rwkvb200_wkv6_bwd(r.data_ptr(), k.data_ptr(), v.data_ptr(), w.data_ptr(), u.data_ptr(),
                                    _lib.ptr(s0), n_state, _lib.ptr(state_map), d_y.data_ptr(), _lib.ptr(d_sT),
                                    dr.data_ptr(), dk.data_ptr(), dv.data_ptr(), dw.data_ptr(), du.data_ptr(),
-                                   ds0.data_ptr(), ws.data_ptr(), nws, B, T, H, HEAD_SIZE, code,
+                                   ds0.data_ptr(), ws.data_ptr(), nws, B, T, H, HEAD_SIZE, code, algo,
                                    _lib.stream_ptr(dev))
         _lib.check(rc, "wkv6_bwd")
     return dr, dk, dv, dw, du, ds0
 
 
 @_wkv6_bwd.register_fake
-def _(r, k, v, w, u, s0, state_map, d_y, d_sT):
+def _(r, k, v, w, u, s0, state_map, d_y, d_sT, algo):
     B, T, C = r.shape
     H = C // HEAD_SIZE
     e = torch.empty_like
@@ -80,9 +87,10 @@ def _(r, k, v, w, u, s0, state_map, d_y, d_sT):
 
 
 def _setup_ctx(ctx, inputs, output):
-    r, k, v, w, u, s0, state_map = inputs
+    r, k, v, w, u, s0, state_map, algo = inputs
     ctx.save_for_backward(r, k, v, w, u, s0, state_map)
     ctx.set_materialize_grads(False)
+    ctx.algo = algo
 
 
 def _backward(ctx, d_y, d_sT):
@@ -92,7 +100,7 @@ def _backward(ctx, d_y, d_sT):
     d_y = d_y.to(r.dtype).contiguous()
     if d_sT is not None:
         d_sT = d_sT.to(torch.float32).contiguous()
-    dr, dk, dv, dw, du, ds0_rows = _wkv6_bwd(r, k, v, w, u, s0, state_map, d_y, d_sT)
+    dr, dk, dv, dw, du, ds0_rows = _wkv6_bwd(r, k, v, w, u, s0, state_map, d_y, d_sT, ctx.algo)
     ds0 = None
     if s0 is not None and ctx.needs_input_grad[5]:
         n_state, B = s0.shape[0], r.shape[0]
@@ -104,7 +112,7 @@ def _backward(ctx, d_y, d_sT):
             idx = torch.arange(B, device=r.device)
         # several batch rows may start from the same table row: their gradients add up
         ds0 = torch.zeros_like(s0).index_add_(0, idx, ds0_rows)
-    return dr, dk, dv, dw, du, ds0, None
+    return dr, dk, dv, dw, du, ds0, None, None
 
 
 torch.library.register_autograd("rwkv_ops_b200::wkv6_fwd", _backward, setup_context=_setup_ctx)
@@ -163,7 +171,8 @@ class RWKVKernelOperator:
             assert state_map is None, "state_map needs init_state"
 
         y, sT = _wkv6_fwd(r.to(cdt).contiguous(), k.to(cdt).contiguous(), v.to(cdt).contiguous(),
-                          w.to(cdt).contiguous(), u.reshape(H, N).to(torch.float32).contiguous(), s0, smap)
+                          w.to(cdt).contiguous(), u.reshape(H, N).to(torch.float32).contiguous(), s0, smap,
+                          _default_algo())
         if y.dtype != dt:
             y = y.to(dt)
         if with_state:
