@@ -180,7 +180,7 @@ int rwkvb200_wkv6_fwd(const void* r, const void* k, const void* v, const void* w
 
 size_t rwkvb200_wkv6_bwd_workspace_bytes(int B, int T, int H, int head_size, int dtype, int algo) {
   if (check_common(B, T, H, head_size, dtype)) return 0;
-  (void)algo;
+  if (resolve_w6_algo(algo) == RWKVB200_ALGO_CHUNKED) return wkv6_chunked_bwd_workspace_bytes(B, T, H);
   return w6_ckpt_bytes(B, T, H) + align256((size_t)B * H * 4 * HS * sizeof(float));
 }
 
@@ -201,6 +201,9 @@ int rwkvb200_wkv6_bwd(const void* r, const void* k, const void* v, const void* w
   if (!workspace || workspace_bytes < rwkvb200_wkv6_bwd_workspace_bytes(B, T, H, head_size, dtype, algo))
     return RWKVB200_E_WORKSPACE;
   cudaStream_t st = (cudaStream_t)stream;
+  if (resolve_w6_algo(algo) == RWKVB200_ALGO_CHUNKED)
+    return launch_wkv6_chunked_bwd(r, k, v, w, u, n_state ? s0 : nullptr, n_state, state_map, d_y, d_sT,
+                                   dr, dk, dv, dw, du, d_s0, workspace, B, T, H, dtype, st);
   float* ckpt = reinterpret_cast<float*>(workspace);
   float* du_partial = reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + w6_ckpt_bytes(B, T, H));
   e = launch_wkv6_fwd(r, k, v, w, u, n_state ? s0 : nullptr, n_state, state_map, nullptr, nullptr, ckpt,

@@ -89,7 +89,7 @@ struct FwdSmem {
 
 // S0 of every chunk (and the final state) goes to `states` [B*H][NT+1][64][64] when it is not NULL.
 template <typename T>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 2)
 wkv6c_fwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __restrict__ v, const T* __restrict__ w,
                  const float* __restrict__ u, const float* __restrict__ s0, int n_state,
                  const int32_t* __restrict__ smap, T* __restrict__ y, float* __restrict__ sT,
@@ -345,6 +345,376 @@ wkv6c_fwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
   if (warp == 0) tmem_dealloc(tm, 128);
 }
 
+// ---------------------------------------------------------------------------------------------
+// backward: one CTA per (batch, head), chunks in reverse; `states` holds the forward state at every
+// chunk boundary (written by the forward kernel)
+// ---------------------------------------------------------------------------------------------
+struct BwdSmem {
+  unsigned char rt[2][TILE_BYTES];    // r~            [token][k]
+  unsigned char kt[2][TILE_BYTES];    // k~            [token][k]
+  // the twelve tiles below are dead once MMA batch 2 has completed; the fp32 staging arrays overlay them
+  unsigned char vt[2][TILE_BYTES];    // v             [token][v]
+  unsigned char dyt[2][TILE_BYTES];   // dy            [token][v]
+  unsigned char at[2][TILE_BYTES];    // A             [i][j]
+  unsigned char dat[2][TILE_BYTES];   // stril(dA)     [i][j]
+  unsigned char st[2][TILE_BYTES];    // S~0           [k][v]
+  unsigned char dst[2][TILE_BYTES];   // dS^           [k][v]
+  float gs[L * NROW];                 // prefix of g inside each half
+  float gg[L * NROW];                 // g
+  float red_e[L * NROW];              // dr~ r~
+  float qtot[4][64];
+  float rqtot[4][64];
+  float dgs[64];                      // sum_k r u k per token
+  float dds[64];                      // dy_i . v_i per token
+  float dgl[2][64];                   // dglast, one partial per column half
+  float du_s[64];
+  uint64_t bar_1, bar_2;
+  uint32_t tmem_base;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+wkv6c_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __restrict__ v, const T* __restrict__ w,
+                 const float* __restrict__ u, const T* __restrict__ d_y, const float* __restrict__ d_sT,
+                 const float* __restrict__ states, T* __restrict__ dr, T* __restrict__ dk, T* __restrict__ dv,
+                 T* __restrict__ dw, float* __restrict__ du_partial, float* __restrict__ d_s0,
+                 int Tn, int H, int* status) {
+  extern __shared__ unsigned char smem_raw[];
+  BwdSmem& sm = *reinterpret_cast<BwdSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int wq = warp & 3, hsel = warp >> 2;
+  const int unit = blockIdx.x, bi = unit / H, hi = unit % H;
+  const long long tstride = (long long)H * HS;
+  const long long base = ((long long)bi * Tn * H + hi) * HS;
+  const int NT = (Tn + L - 1) / L;
+  const int srow = 16 * wq + (lane & 15);
+  const bool lower = lane < 16;
+  const int c4 = tid & 15;
+  const float4 u4 = *reinterpret_cast<const float4*>(u + hi * HS + 4 * c4);
+  // fp32 arrays that overlay the dead tiles after MMA batch 2
+  float* stage_dr = reinterpret_cast<float*>(sm.vt[0]);
+  float* stage_dk = stage_dr + L * NROW;
+  float* stage_dv = stage_dk + L * NROW;
+  float* stage_dw = stage_dv + L * NROW;
+  float* red_i = stage_dw + L * NROW;          // 5 x 17408 B = 87040 B <= 12 tiles
+
+  if (tid == 0) {
+    mbar_init(&sm.bar_1, 1); mbar_init(&sm.bar_2, 1);
+    fence_mbar_init();
+  }
+  if (tid < 64) sm.du_s[tid] = 0.f;
+  if (warp == 0) tmem_alloc(&sm.tmem_base, 256);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tm = sm.tmem_base;
+  const uint32_t tm_c0 = tmem_addr(tm, 32 * wq, 32 * hsel);          // A (lower), dA (upper)
+  const uint32_t tm_c1 = tmem_addr(tm, 32 * wq, 64 + 32 * hsel);     // dv (lower), dr~ (upper)
+  const uint32_t tm_c2 = tmem_addr(tm, 32 * wq, 128 + 32 * hsel);    // dk~ (lower), dS~0 (upper)
+
+  // gradient of the state after the current chunk: row k = srow (upper lane halves), 32 columns
+  float dsreg[32];
+#pragma unroll
+  for (int j = 0; j < 32; ++j) dsreg[j] = 0.f;
+  if (!lower && d_sT) {
+    const float* S = d_sT + (((size_t)unit * HS) + srow) * HS + 32 * hsel;
+#pragma unroll
+    for (int j = 0; j < 32; j += 4) {
+      const float4 f = *reinterpret_cast<const float4*>(S + j);
+      dsreg[j] = f.x; dsreg[j + 1] = f.y; dsreg[j + 2] = f.z; dsreg[j + 3] = f.w;
+    }
+  }
+  float4 du_acc = make_float4(0.f, 0.f, 0.f, 0.f);
+
+  bool ok = true;
+  for (int c = NT - 1; c >= 0 && ok; --c) {
+    const int t0 = c * L;
+    const uint32_t par = (NT - 1 - c) & 1;
+    // ---- pass W: g and its prefix sums
+    float4 gw[4];
+#pragma unroll
+    for (int n = 0; n < 4; ++n) {
+      const int e = tid + 256 * n, row = e >> 4, tok = t0 + row;
+      float4 f = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (tok < Tn) {
+        f = load4(w + base + (long long)tok * tstride + 4 * c4);
+        f = make_float4(-__expf(f.x), -__expf(f.y), -__expf(f.z), -__expf(f.w));
+      }
+      gw[n] = f;
+      *reinterpret_cast<float4*>(&sm.gg[row * NROW + 4 * c4]) = f;
+    }
+    __syncthreads();
+    {
+      const int ch = tid & 63, quarter = tid >> 6;
+      float gv[16];
+#pragma unroll
+      for (int j = 0; j < 16; ++j) gv[j] = sm.gg[(16 * quarter + j) * NROW + ch];
+      float run = 0.f;
+#pragma unroll
+      for (int j = 0; j < 16; ++j) { run += gv[j]; gv[j] = run; }
+      sm.qtot[quarter][ch] = run;
+      __syncthreads();
+      const float add = (quarter & 1) ? sm.qtot[quarter - 1][ch] : 0.f;
+#pragma unroll
+      for (int j = 0; j < 16; ++j) sm.gs[(16 * quarter + j) * NROW + ch] = gv[j] + add;
+    }
+    __syncthreads();
+    float e0 = 1.f, dlast = 1.f;
+    if (!lower) {
+      e0 = __expf(fmaxf(sm.qtot[0][srow] + sm.qtot[1][srow], -EXP_CLAMP));
+      dlast = __expf(fmaxf(sm.qtot[2][srow] + sm.qtot[3][srow], -EXP_CLAMP));
+    }
+    // ---- state rows (upper lane halves): dglast, dS^ = e^{glast-gref} dS_L, S~0 = e^{gref} S0
+    if (!lower) {
+      const float* SL = states + (((size_t)unit * (NT + 1) + c + 1) * HS + srow) * HS + 32 * hsel;
+      const float* S0 = states + (((size_t)unit * (NT + 1) + c) * HS + srow) * HS + 32 * hsel;
+      float acc = 0.f, x[32];
+#pragma unroll
+      for (int j = 0; j < 32; j += 4) {
+        const float4 f = *reinterpret_cast<const float4*>(SL + j);
+        acc += dsreg[j] * f.x + dsreg[j + 1] * f.y + dsreg[j + 2] * f.z + dsreg[j + 3] * f.w;
+      }
+      sm.dgl[hsel][srow] = acc;
+#pragma unroll
+      for (int j = 0; j < 32; ++j) { dsreg[j] *= dlast; x[j] = dsreg[j]; }     // dsreg now holds dS^
+      store_split_row32(sm.dst[0], sm.dst[1], srow, 32 * hsel, x);
+#pragma unroll
+      for (int j = 0; j < 32; j += 4) {
+        const float4 f = *reinterpret_cast<const float4*>(S0 + j);
+        x[j] = f.x * e0; x[j + 1] = f.y * e0; x[j + 2] = f.z * e0; x[j + 3] = f.w * e0;
+      }
+      store_split_row32(sm.st[0], sm.st[1], srow, 32 * hsel, x);
+    }
+    // ---- pass RK: scaled r, k (split) and the diagonal term
+#pragma unroll
+    for (int n = 0; n < 4; ++n) {
+      const int e = tid + 256 * n, row = e >> 4, tok = t0 + row;
+      float4 r4 = make_float4(0.f, 0.f, 0.f, 0.f), k4 = r4;
+      if (tok < Tn) {
+        const long long off = base + (long long)tok * tstride + 4 * c4;
+        r4 = load4(r + off); k4 = load4(k + off);
+      }
+      const float4 gp = *reinterpret_cast<const float4*>(&sm.gs[row * NROW + 4 * c4]);
+      const float4 ta = *reinterpret_cast<const float4*>(&sm.qtot[0][4 * c4]);
+      const float4 tb = *reinterpret_cast<const float4*>(&sm.qtot[1][4 * c4]);
+      const bool fh = row < 32;
+      const float d1x = gp.x - (fh ? ta.x + tb.x : 0.f), d1y = gp.y - (fh ? ta.y + tb.y : 0.f);
+      const float d1z = gp.z - (fh ? ta.z + tb.z : 0.f), d1w = gp.w - (fh ? ta.w + tb.w : 0.f);
+      const float4 rs = make_float4(r4.x * cexp(d1x - gw[n].x), r4.y * cexp(d1y - gw[n].y),
+                                    r4.z * cexp(d1z - gw[n].z), r4.w * cexp(d1w - gw[n].w));
+      const float4 ks = make_float4(k4.x * cexp(-d1x), k4.y * cexp(-d1y), k4.z * cexp(-d1z), k4.w * cexp(-d1w));
+      store_split4(sm.rt[0], sm.rt[1], row, 4 * c4, rs);
+      store_split4(sm.kt[0], sm.kt[1], row, 4 * c4, ks);
+      float dg = r4.x * u4.x * k4.x + r4.y * u4.y * k4.y + r4.z * u4.z * k4.z + r4.w * u4.w * k4.w;
+#pragma unroll
+      for (int m = 8; m >= 1; m >>= 1) dg += __shfl_xor_sync(0xffffffffu, dg, m);
+      if (c4 == 0) sm.dgs[row] = dg;
+    }
+    // ---- pass V / DY: split tiles and dd_i = dy_i . v_i
+#pragma unroll
+    for (int n = 0; n < 4; ++n) {
+      const int e = tid + 256 * n, row = e >> 4, tok = t0 + row;
+      float4 v4 = make_float4(0.f, 0.f, 0.f, 0.f), y4 = v4;
+      if (tok < Tn) {
+        const long long off = base + (long long)tok * tstride + 4 * c4;
+        v4 = load4(v + off); y4 = load4(d_y + off);
+      }
+      store_split4(sm.vt[0], sm.vt[1], row, 4 * c4, v4);
+      store_split4(sm.dyt[0], sm.dyt[1], row, 4 * c4, y4);
+      float dd = v4.x * y4.x + v4.y * y4.y + v4.z * y4.z + v4.w * y4.w;
+#pragma unroll
+      for (int m = 8; m >= 1; m >>= 1) dd += __shfl_xor_sync(0xffffffffu, dd, m);
+      if (c4 == 0) sm.dds[row] = dd;
+    }
+    if (c > 0 && c4 == 0) {   // bring the previous chunk's rows into L2 while this chunk is in its MMA phases
+#pragma unroll
+      for (int n = 0; n < 4; ++n) {
+        const int tok = t0 - L + ((tid + 256 * n) >> 4);
+        const long long off = base + (long long)tok * tstride;
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(w + off));
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(r + off));
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(k + off));
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(v + off));
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(d_y + off));
+        if (sizeof(T) == 4) {
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(w + off + 32));
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(r + off + 32));
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(k + off + 32));
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(v + off + 32));
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(d_y + off + 32));
+        }
+      }
+    }
+    fence_async_smem();
+    tc_fence_before();
+    __syncthreads();
+
+    // ---- batch 1: r~ k~^T (lower halves) and dy v^T (upper halves), columns 0..63
+    if (tid == 0) {
+      tc_fence_after();
+      umma_split<64, 64, 0, 0>(tmem_addr(tm, 0, 0), smem_u32(sm.rt[0]), smem_u32(sm.kt[0]), false);
+      umma_split<64, 64, 0, 0>(tmem_addr(tm, 16, 0), smem_u32(sm.dyt[0]), smem_u32(sm.vt[0]), false);
+      umma_commit(&sm.bar_1);
+    }
+    ok = mbar_wait(&sm.bar_1, par, status, 411) && ok;
+    tc_fence_after();
+    if (ok) {
+      uint32_t rr[32];
+      tmem_ld32(tm_c0, rr);
+      tmem_ld_wait();
+      float x[32];
+      const float dgi = lower ? sm.dgs[srow] : 0.f;     // the diagonal of A carries the u term; dA's does not
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        const int jj = 32 * hsel + j;
+        x[j] = jj < srow ? __uint_as_float(rr[j]) : (jj == srow ? dgi : 0.f);
+      }
+      if (lower) store_split_row32(sm.at[0], sm.at[1], srow, 32 * hsel, x);
+      else       store_split_row32(sm.dat[0], sm.dat[1], srow, 32 * hsel, x);
+    }
+    fence_async_smem();
+    tc_fence_before();
+    ok = __syncthreads_and(ok);
+
+    // ---- batch 2
+    if (tid == 0 && ok) {
+      tc_fence_after();
+      // dv = A^T dy + k~ dS^                        (lower halves, columns 64..127)
+      umma_split<64, 64, 1, 1>(tmem_addr(tm, 0, 64), smem_u32(sm.at[0]), smem_u32(sm.dyt[0]), false);
+      umma_split<64, 64, 0, 1>(tmem_addr(tm, 0, 64), smem_u32(sm.kt[0]), smem_u32(sm.dst[0]), true);
+      // dr~ = dy S~0^T + stril(dA) k~               (upper halves, columns 64..127)
+      umma_split<64, 64, 0, 0>(tmem_addr(tm, 16, 64), smem_u32(sm.dyt[0]), smem_u32(sm.st[0]), false);
+      umma_split<64, 64, 0, 1>(tmem_addr(tm, 16, 64), smem_u32(sm.dat[0]), smem_u32(sm.kt[0]), true);
+      // dk~ = stril(dA)^T r~ + v dS^^T              (lower halves, columns 128..191)
+      umma_split<64, 64, 1, 1>(tmem_addr(tm, 0, 128), smem_u32(sm.dat[0]), smem_u32(sm.rt[0]), false);
+      umma_split<64, 64, 0, 0>(tmem_addr(tm, 0, 128), smem_u32(sm.vt[0]), smem_u32(sm.dst[0]), true);
+      // dS~0 = r~^T dy                              (upper halves, columns 128..191)
+      umma_split<64, 64, 1, 1>(tmem_addr(tm, 16, 128), smem_u32(sm.rt[0]), smem_u32(sm.dyt[0]), false);
+      umma_commit(&sm.bar_2);
+    }
+    ok = mbar_wait(&sm.bar_2, par, status, 412) && ok;
+    tc_fence_after();
+    if (ok) {
+      uint32_t r1[32], r2[32];
+      tmem_ld32(tm_c1, r1);
+      tmem_ld32(tm_c2, r2);
+      tmem_ld_wait();
+      const int c0 = 32 * hsel;
+      float th[32], tl[32];
+      // lower halves: dv row and dk~ row of token srow; upper halves: dr~ row of token srow and dS~0 row k = srow
+      tile_load_row32(lower ? sm.kt[0] : sm.rt[0], srow, c0, th);
+      tile_load_row32(lower ? sm.kt[1] : sm.rt[1], srow, c0, tl);
+      if (!lower) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) dsreg[j] = e0 * (__uint_as_float(r2[j]) + dsreg[j]);   // dS0 = e^{gref}(r~^T dy + dS^)
+      }
+#pragma unroll
+      for (int j4 = 0; j4 < 32; j4 += 4) {
+        const int cc = c0 + j4;
+        const float4 gs4 = *reinterpret_cast<const float4*>(&sm.gs[srow * NROW + cc]);
+        const float4 gg4 = *reinterpret_cast<const float4*>(&sm.gg[srow * NROW + cc]);
+        const float4 ta4 = *reinterpret_cast<const float4*>(&sm.qtot[0][cc]);
+        const float4 tb4 = *reinterpret_cast<const float4*>(&sm.qtot[1][cc]);
+        const float gsv[4] = {gs4.x, gs4.y, gs4.z, gs4.w}, ggv[4] = {gg4.x, gg4.y, gg4.z, gg4.w};
+        const float ttv[4] = {ta4.x + tb4.x, ta4.y + tb4.y, ta4.z + tb4.z, ta4.w + tb4.w};
+        float o[4], rd[4], dvv[4];
+#pragma unroll
+        for (int m = 0; m < 4; ++m) {
+          const int j = j4 + m;
+          const float d1 = gsv[m] - (srow < 32 ? ttv[m] : 0.f);     // gi - gref
+          const float tt = th[j] + tl[j];                            // k~ (lower) / r~ (upper)
+          if (lower) {
+            const float x2 = __uint_as_float(r2[j]);                 // dk~
+            o[m] = x2 * cexp(-d1);
+            rd[m] = -x2 * tt;
+            dvv[m] = __uint_as_float(r1[j]);
+          } else {
+            const float x1 = __uint_as_float(r1[j]);                 // dr~
+            o[m] = x1 * cexp(d1 - ggv[m]);
+            rd[m] = x1 * tt;
+          }
+        }
+        if (lower) {
+          *reinterpret_cast<float4*>(&stage_dk[srow * NROW + cc]) = make_float4(o[0], o[1], o[2], o[3]);
+          *reinterpret_cast<float4*>(&red_i[srow * NROW + cc]) = make_float4(rd[0], rd[1], rd[2], rd[3]);
+          *reinterpret_cast<float4*>(&stage_dv[srow * NROW + cc]) = make_float4(dvv[0], dvv[1], dvv[2], dvv[3]);
+        } else {
+          *reinterpret_cast<float4*>(&stage_dr[srow * NROW + cc]) = make_float4(o[0], o[1], o[2], o[3]);
+          *reinterpret_cast<float4*>(&sm.red_e[srow * NROW + cc]) = make_float4(rd[0], rd[1], rd[2], rd[3]);
+        }
+      }
+    }
+    tc_fence_before();
+    ok = __syncthreads_and(ok);
+    // ---- decay gradient: dg_j = sum_{i>=j} (dgi_i + dge_i) - dge_j + dglast;  dw = dg g
+    {
+      const int ch = tid & 63, quarter = tid >> 6;
+      float rv[16];
+#pragma unroll
+      for (int j = 0; j < 16; ++j)
+        rv[j] = red_i[(16 * quarter + j) * NROW + ch] + sm.red_e[(16 * quarter + j) * NROW + ch];
+      float run = 0.f;
+#pragma unroll
+      for (int j = 15; j >= 0; --j) { run += rv[j]; rv[j] = run; }
+      sm.rqtot[quarter][ch] = run;
+      __syncthreads();
+      float add = sm.dgl[0][ch] + sm.dgl[1][ch];
+      for (int q2 = quarter + 1; q2 < 4; ++q2) add += sm.rqtot[q2][ch];
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        const int ii = 16 * quarter + j;
+        const float dg = rv[j] + add - sm.red_e[ii * NROW + ch];
+        stage_dw[ii * NROW + ch] = dg * sm.gg[ii * NROW + ch];
+      }
+    }
+    __syncthreads();
+    // ---- outputs, coalesced, plus the u-term parts of dr, dk and du
+#pragma unroll
+    for (int n = 0; n < 4; ++n) {
+      const int e = tid + 256 * n, row = e >> 4, tok = t0 + row;
+      if (tok < Tn) {
+        const long long off = base + (long long)tok * tstride + 4 * c4;
+        const float4 r4 = load4(r + off), k4 = load4(k + off);
+        const float dd = sm.dds[row];
+        float4 a = *reinterpret_cast<const float4*>(&stage_dr[row * NROW + 4 * c4]);
+        a.x += dd * u4.x * k4.x; a.y += dd * u4.y * k4.y; a.z += dd * u4.z * k4.z; a.w += dd * u4.w * k4.w;
+        store4(dr + off, a);
+        float4 b = *reinterpret_cast<const float4*>(&stage_dk[row * NROW + 4 * c4]);
+        b.x += dd * r4.x * u4.x; b.y += dd * r4.y * u4.y; b.z += dd * r4.z * u4.z; b.w += dd * r4.w * u4.w;
+        store4(dk + off, b);
+        store4(dv + off, *reinterpret_cast<const float4*>(&stage_dv[row * NROW + 4 * c4]));
+        store4(dw + off, *reinterpret_cast<const float4*>(&stage_dw[row * NROW + 4 * c4]));
+        du_acc.x += dd * r4.x * k4.x; du_acc.y += dd * r4.y * k4.y;
+        du_acc.z += dd * r4.z * k4.z; du_acc.w += dd * r4.w * k4.w;
+      }
+    }
+    __syncthreads();
+  }
+  // ---- du of this (batch, head) and the gradient of its initial state
+  atomicAdd(&sm.du_s[4 * c4], du_acc.x); atomicAdd(&sm.du_s[4 * c4 + 1], du_acc.y);
+  atomicAdd(&sm.du_s[4 * c4 + 2], du_acc.z); atomicAdd(&sm.du_s[4 * c4 + 3], du_acc.w);
+  __syncthreads();
+  if (tid < 64) du_partial[(size_t)unit * HS + tid] = sm.du_s[tid];
+  if (!lower && d_s0 && ok) {
+    float* dst = d_s0 + (((size_t)unit * HS) + srow) * HS + 32 * hsel;
+#pragma unroll
+    for (int j = 0; j < 32; j += 4)
+      *reinterpret_cast<float4*>(dst + j) = make_float4(dsreg[j], dsreg[j + 1], dsreg[j + 2], dsreg[j + 3]);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tm, 256);
+}
+
+// du[h][k] = sum over batch rows, fixed order
+__global__ void __launch_bounds__(64)
+wkv6c_du_reduce_kernel(const float* __restrict__ du_partial, float* __restrict__ du, int B, int H) {
+  const int hi = blockIdx.x, kc = threadIdx.x;
+  float s = 0.f;
+  for (int bi = 0; bi < B; ++bi) s += du_partial[((size_t)bi * H + hi) * HS + kc];
+  du[hi * HS + kc] = s;
+}
+
 }  // namespace w6c
 
 int launch_wkv6_chunked_fwd(const void* r, const void* k, const void* v, const void* w, const float* u,
@@ -360,6 +730,46 @@ int launch_wkv6_chunked_fwd(const void* r, const void* k, const void* v, const v
       return RWKVB200_E_CUDA;
     wkv6c_fwd_kernel<T><<<B * H, 256, smem, st>>>((const T*)r, (const T*)k, (const T*)v, (const T*)w, u, s0, n_state,
                                                    smap, (T*)y, sT, states, Tn, H, status));
+  return check_launch();
+}
+
+}  // namespace rwkvb200
+
+namespace rwkvb200 {
+
+size_t wkv6_chunked_bwd_workspace_bytes(int B, int Tn, int H) {
+  const size_t nt = (size_t)(Tn + w6c::L - 1) / w6c::L;
+  return (((size_t)B * H * (nt + 1) * HS * HS * sizeof(float) + 255) & ~size_t(255)) +
+         (((size_t)B * H * HS * sizeof(float) + 255) & ~size_t(255));
+}
+
+int launch_wkv6_chunked_bwd(const void* r, const void* k, const void* v, const void* w, const float* u,
+                            const float* s0, int n_state, const int32_t* smap, const void* d_y, const float* d_sT,
+                            void* dr, void* dk, void* dv, void* dw, float* du, float* d_s0, void* workspace,
+                            int B, int Tn, int H, int dtype, cudaStream_t st) {
+  using namespace w6c;
+  const size_t nt = (size_t)(Tn + L - 1) / L;
+  float* states = reinterpret_cast<float*>(workspace);
+  float* du_partial = reinterpret_cast<float*>(
+      reinterpret_cast<char*>(workspace) + (((size_t)B * H * (nt + 1) * HS * HS * sizeof(float) + 255) & ~size_t(255)));
+  int e = launch_wkv6_chunked_fwd(r, k, v, w, u, s0, n_state, smap, nullptr, nullptr, states, B, Tn, H, dtype, st);
+  if (e) return e;
+  int* status = device_status_ptr();
+  if (!status) { last_cuda_error_slot() = 99999; return RWKVB200_E_CUDA; }
+  const int smem = (int)sizeof(BwdSmem) + 1024;
+  {
+    ProfScope prof("wkv6c_bwd_kernel", st);
+    RWKVB200_DISPATCH_DTYPE(dtype,
+      if (cuda_ok(cudaFuncSetAttribute(wkv6c_bwd_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)))
+        return RWKVB200_E_CUDA;
+      wkv6c_bwd_kernel<T><<<B * H, 256, smem, st>>>((const T*)r, (const T*)k, (const T*)v, (const T*)w, u,
+                                                     (const T*)d_y, d_sT, states, (T*)dr, (T*)dk, (T*)dv, (T*)dw,
+                                                     du_partial, d_s0, Tn, H, status));
+  }
+  e = check_launch();
+  if (e) return e;
+  ProfScope prof("wkv6c_du_reduce_kernel", st);
+  wkv6c_du_reduce_kernel<<<H, 64, 0, st>>>(du_partial, du, B, H);
   return check_launch();
 }
 

@@ -13,6 +13,16 @@ from rwkv_ops_b200.workloads import wkv6_inputs, rel_l2
 
 pytestmark = pytest.mark.gpu
 
+
+@pytest.fixture(autouse=True, params=["auto", "recurrent"])
+def _algo(request, monkeypatch):
+    """Every test runs on the chunked tensor-core path (auto) and on the float32 recurrence."""
+    monkeypatch.setenv("RWKV_OPS_B200_WKV6_ALGO", request.param)
+    yield request.param
+    torch.cuda.synchronize()
+    from rwkv_ops_b200 import _lib
+    assert _lib.load().rwkvb200_device_status(1) == 0, "a bounded wait ran out inside a tensor-core kernel"
+
 GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
 R6 = sorted(glob.glob(os.path.join(GOLDEN, "wkv6_*.npz")))
 
