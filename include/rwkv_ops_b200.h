@@ -153,10 +153,14 @@ int rwkvb200_rwkv7_bwd_static(const void* r, const void* w, const void* k, const
  *   sT             final state [B,H,64,64], may be NULL.
  *   algo           RWKVB200_ALGO_AUTO / _RECURRENT (token-by-token float32) / _CHUNKED (tcgen05 with
  *                  split-precision bf16 operands, float32-grade accuracy for every dtype); AUTO = chunked.
+ *                  With RWKVB200_ALGO_KEEP (chunked only) the forward also writes the state at every chunk
+ *                  boundary into `workspace` (rwkvb200_wkv6_bwd_workspace_bytes of it), and a backward
+ *                  called with the same flag and workspace skips its recomputation of the forward;
+ *                  without the flag the forward needs no workspace (NULL, 0).
  * ---------------------------------------------------------------------------------------- */
 int rwkvb200_wkv6_fwd(const void* r, const void* k, const void* v, const void* w, const float* u,
                       const float* s0, int n_state, const int32_t* state_map,
-                      void* y, float* sT,
+                      void* y, float* sT, void* workspace, size_t workspace_bytes,
                       int B, int T, int H, int head_size, int dtype, int algo, void* stream);
 
 size_t rwkvb200_wkv6_bwd_workspace_bytes(int B, int T, int H, int head_size, int dtype, int algo);

@@ -161,7 +161,7 @@ int rwkvb200_rwkv7_bwd(const void* r, const void* w, const void* k, const void* 
 
 int rwkvb200_wkv6_fwd(const void* r, const void* k, const void* v, const void* w, const float* u,
                       const float* s0, int n_state, const int32_t* state_map,
-                      void* y, float* sT,
+                      void* y, float* sT, void* workspace, size_t workspace_bytes,
                       int B, int T, int H, int head_size, int dtype, int algo, void* stream) {
   int e = check_common(B, T, H, head_size, dtype);
   if (e) return e;
@@ -171,9 +171,16 @@ int rwkvb200_wkv6_fwd(const void* r, const void* k, const void* v, const void* w
   if (n_state > 1 && !state_map && n_state != B) return RWKVB200_E_STATE_MAP;
   const void* ps[] = {r, k, v, w, u, s0, y, sT};
   for (const void* p : ps) if (p && !aligned16(p)) return RWKVB200_E_ALIGN;
-  if (resolve_w6_algo(algo) == RWKVB200_ALGO_CHUNKED)
-    return launch_wkv6_chunked_fwd(r, k, v, w, u, n_state ? s0 : nullptr, n_state, state_map, y, sT, nullptr,
+  if (resolve_w6_algo(algo) == RWKVB200_ALGO_CHUNKED) {
+    float* states = nullptr;
+    if (algo & RWKVB200_ALGO_KEEP) {
+      if (!workspace || !aligned16(workspace) || workspace_bytes < wkv6_chunked_bwd_workspace_bytes(B, T, H))
+        return RWKVB200_E_WORKSPACE;
+      states = reinterpret_cast<float*>(workspace);
+    }
+    return launch_wkv6_chunked_fwd(r, k, v, w, u, n_state ? s0 : nullptr, n_state, state_map, y, sT, states,
                                    B, T, H, dtype, (cudaStream_t)stream);
+  }
   return launch_wkv6_fwd(r, k, v, w, u, n_state ? s0 : nullptr, n_state, state_map, y, sT, nullptr,
                          B, T, H, dtype, (cudaStream_t)stream);
 }
@@ -203,7 +210,8 @@ int rwkvb200_wkv6_bwd(const void* r, const void* k, const void* v, const void* w
   cudaStream_t st = (cudaStream_t)stream;
   if (resolve_w6_algo(algo) == RWKVB200_ALGO_CHUNKED)
     return launch_wkv6_chunked_bwd(r, k, v, w, u, n_state ? s0 : nullptr, n_state, state_map, d_y, d_sT,
-                                   dr, dk, dv, dw, du, d_s0, workspace, B, T, H, dtype, st);
+                                   dr, dk, dv, dw, du, d_s0, workspace, B, T, H, dtype,
+                                   (algo & RWKVB200_ALGO_KEEP) != 0, st);
   float* ckpt = reinterpret_cast<float*>(workspace);
   float* du_partial = reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + w6_ckpt_bytes(B, T, H));
   e = launch_wkv6_fwd(r, k, v, w, u, n_state ? s0 : nullptr, n_state, state_map, nullptr, nullptr, ckpt,

@@ -141,6 +141,6 @@ size_t wkv6_chunked_bwd_workspace_bytes(int B, int Tn, int H);
 int launch_wkv6_chunked_bwd(const void* r, const void* k, const void* v, const void* w, const float* u,
                             const float* s0, int n_state, const int32_t* smap, const void* d_y, const float* d_sT,
                             void* dr, void* dk, void* dv, void* dw, float* du, float* d_s0, void* workspace,
-                            int B, int Tn, int H, int dtype, cudaStream_t st);
+                            int B, int Tn, int H, int dtype, bool kept, cudaStream_t st);
 
 }  // namespace rwkvb200

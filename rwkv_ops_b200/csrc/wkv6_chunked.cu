@@ -746,14 +746,17 @@ size_t wkv6_chunked_bwd_workspace_bytes(int B, int Tn, int H) {
 int launch_wkv6_chunked_bwd(const void* r, const void* k, const void* v, const void* w, const float* u,
                             const float* s0, int n_state, const int32_t* smap, const void* d_y, const float* d_sT,
                             void* dr, void* dk, void* dv, void* dw, float* du, float* d_s0, void* workspace,
-                            int B, int Tn, int H, int dtype, cudaStream_t st) {
+                            int B, int Tn, int H, int dtype, bool kept, cudaStream_t st) {
   using namespace w6c;
   const size_t nt = (size_t)(Tn + L - 1) / L;
   float* states = reinterpret_cast<float*>(workspace);
   float* du_partial = reinterpret_cast<float*>(
       reinterpret_cast<char*>(workspace) + (((size_t)B * H * (nt + 1) * HS * HS * sizeof(float) + 255) & ~size_t(255)));
-  int e = launch_wkv6_chunked_fwd(r, k, v, w, u, s0, n_state, smap, nullptr, nullptr, states, B, Tn, H, dtype, st);
-  if (e) return e;
+  int e = RWKVB200_OK;
+  if (!kept) {   // the workspace does not hold the chunk-boundary states yet: run the forward for them
+    e = launch_wkv6_chunked_fwd(r, k, v, w, u, s0, n_state, smap, nullptr, nullptr, states, B, Tn, H, dtype, st);
+    if (e) return e;
+  }
   int* status = device_status_ptr();
   if (!status) { last_cuda_error_slot() = 99999; return RWKVB200_E_CUDA; }
   const int smem = (int)sizeof(BwdSmem) + 1024;

@@ -27,8 +27,8 @@ def _default_algo() -> int:
 
 @torch.library.custom_op("rwkv_ops_b200::wkv6_fwd", mutates_args=())
 def _wkv6_fwd(r: torch.Tensor, k: torch.Tensor, v: torch.Tensor, w: torch.Tensor, u: torch.Tensor,
-              s0: Optional[torch.Tensor], state_map: Optional[torch.Tensor], algo: int
-              ) -> Tuple[torch.Tensor, torch.Tensor]:
+              s0: Optional[torch.Tensor], state_map: Optional[torch.Tensor], algo: int, keep: bool
+              ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
     lib = _lib.load()
     dev = _lib.require_cuda(r, k, v, w, u, s0, state_map)
     B, T, C = r.shape
@@ -38,23 +38,29 @@ def _wkv6_fwd(r: torch.Tensor, k: torch.Tensor, v: torch.Tensor, w: torch.Tensor
     sT = torch.empty(B, H, HEAD_SIZE, HEAD_SIZE, dtype=torch.float32, device=dev)
     n_state = 0 if s0 is None else s0.shape[0]
     with torch.cuda.device(dev):
+        # a training forward of the chunked path leaves the chunk-boundary states for the backward
+        flags = algo | (_lib.ALGO_KEEP if keep else 0)
+        nws = lib.rwkvb200_wkv6_bwd_workspace_bytes(B, T, H, HEAD_SIZE, code, algo) if keep else 0
+        kept = torch.empty(nws, dtype=torch.uint8, device=dev)
         rc = lib.rwkvb200_wkv6_fwd(r.data_ptr(), k.data_ptr(), v.data_ptr(), w.data_ptr(), u.data_ptr(),
                                    _lib.ptr(s0), n_state, _lib.ptr(state_map), y.data_ptr(), sT.data_ptr(),
-                                   B, T, H, HEAD_SIZE, code, algo, _lib.stream_ptr(dev))
+                                   kept.data_ptr() if keep else None, nws,
+                                   B, T, H, HEAD_SIZE, code, flags, _lib.stream_ptr(dev))
         _lib.check(rc, "wkv6_fwd")
-    return y, sT
+    return y, sT, kept
 
 
 @_wkv6_fwd.register_fake
-def _(r, k, v, w, u, s0, state_map, algo):
+def _(r, k, v, w, u, s0, state_map, algo, keep):
     B, T, C = r.shape
-    return torch.empty_like(r), r.new_empty((B, C // HEAD_SIZE, HEAD_SIZE, HEAD_SIZE), dtype=torch.float32)
+    return (torch.empty_like(r), r.new_empty((B, C // HEAD_SIZE, HEAD_SIZE, HEAD_SIZE), dtype=torch.float32),
+            r.new_empty((0,), dtype=torch.uint8))
 
 
 @torch.library.custom_op("rwkv_ops_b200::wkv6_bwd", mutates_args=())
 def _wkv6_bwd(r: torch.Tensor, k: torch.Tensor, v: torch.Tensor, w: torch.Tensor, u: torch.Tensor,
               s0: Optional[torch.Tensor], state_map: Optional[torch.Tensor],
-              d_y: torch.Tensor, d_sT: Optional[torch.Tensor], algo: int
+              d_y: torch.Tensor, d_sT: Optional[torch.Tensor], kept: torch.Tensor, algo: int
               ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
     lib = _lib.load()
     dev = _lib.require_cuda(r, k, v, w, u, s0, state_map, d_y, d_sT)
@@ -67,7 +73,9 @@ def _wkv6_bwd(r: torch.Tensor, k: torch.Tensor, v: torch.Tensor, w: torch.Tensor
     n_state = 0 if s0 is None else s0.shape[0]
     with torch.cuda.device(dev):
         nws = lib.rwkvb200_wkv6_bwd_workspace_bytes(B, T, H, HEAD_SIZE, code, algo)
-        ws = torch.empty(nws, dtype=torch.uint8, device=dev)
+        have = kept.numel() >= nws and kept.numel() > 0      # the forward left its chunk-boundary states
+        ws = kept if have else torch.empty(nws, dtype=torch.uint8, device=dev)
+        algo = algo | (_lib.ALGO_KEEP if have else 0)
         rc = lib.rwkvb200_wkv6_bwd(r.data_ptr(), k.data_ptr(), v.data_ptr(), w.data_ptr(), u.data_ptr(),
                                    _lib.ptr(s0), n_state, _lib.ptr(state_map), d_y.data_ptr(), _lib.ptr(d_sT),
                                    dr.data_ptr(), dk.data_ptr(), dv.data_ptr(), dw.data_ptr(), du.data_ptr(),
@@ -78,7 +86,7 @@ def _wkv6_bwd(r: torch.Tensor, k: torch.Tensor, v: torch.Tensor, w: torch.Tensor
 
 
 @_wkv6_bwd.register_fake
-def _(r, k, v, w, u, s0, state_map, d_y, d_sT, algo):
+def _(r, k, v, w, u, s0, state_map, d_y, d_sT, kept, algo):
     B, T, C = r.shape
     H = C // HEAD_SIZE
     e = torch.empty_like
@@ -87,20 +95,20 @@ def _(r, k, v, w, u, s0, state_map, d_y, d_sT, algo):
 
 
 def _setup_ctx(ctx, inputs, output):
-    r, k, v, w, u, s0, state_map, algo = inputs
-    ctx.save_for_backward(r, k, v, w, u, s0, state_map)
+    r, k, v, w, u, s0, state_map, algo, keep = inputs
+    ctx.save_for_backward(r, k, v, w, u, s0, state_map, output[2])
     ctx.set_materialize_grads(False)
     ctx.algo = algo
 
 
-def _backward(ctx, d_y, d_sT):
-    r, k, v, w, u, s0, state_map = ctx.saved_tensors
+def _backward(ctx, d_y, d_sT, d_kept):
+    r, k, v, w, u, s0, state_map, kept = ctx.saved_tensors
     if d_y is None:
         d_y = torch.zeros_like(r)
     d_y = d_y.to(r.dtype).contiguous()
     if d_sT is not None:
         d_sT = d_sT.to(torch.float32).contiguous()
-    dr, dk, dv, dw, du, ds0_rows = _wkv6_bwd(r, k, v, w, u, s0, state_map, d_y, d_sT, ctx.algo)
+    dr, dk, dv, dw, du, ds0_rows = _wkv6_bwd(r, k, v, w, u, s0, state_map, d_y, d_sT, kept, ctx.algo)
     ds0 = None
     if s0 is not None and ctx.needs_input_grad[5]:
         n_state, B = s0.shape[0], r.shape[0]
@@ -112,7 +120,7 @@ def _backward(ctx, d_y, d_sT):
             idx = torch.arange(B, device=r.device)
         # several batch rows may start from the same table row: their gradients add up
         ds0 = torch.zeros_like(s0).index_add_(0, idx, ds0_rows)
-    return dr, dk, dv, dw, du, ds0, None, None
+    return dr, dk, dv, dw, du, ds0, None, None, None
 
 
 torch.library.register_autograd("rwkv_ops_b200::wkv6_fwd", _backward, setup_context=_setup_ctx)
@@ -170,9 +178,13 @@ class RWKVKernelOperator:
         else:
             assert state_map is None, "state_map needs init_state"
 
-        y, sT = _wkv6_fwd(r.to(cdt).contiguous(), k.to(cdt).contiguous(), v.to(cdt).contiguous(),
-                          w.to(cdt).contiguous(), u.reshape(H, N).to(torch.float32).contiguous(), s0, smap,
-                          _default_algo())
+        algo = _default_algo()
+        needs_grad = torch.is_grad_enabled() and (
+            any(x.requires_grad for x in (r, k, v, w, u)) or (init_state is not None and init_state.requires_grad))
+        keep = needs_grad and algo != _lib.ALGO_RECURRENT and T > 1
+        y, sT, _ = _wkv6_fwd(r.to(cdt).contiguous(), k.to(cdt).contiguous(), v.to(cdt).contiguous(),
+                             w.to(cdt).contiguous(), u.reshape(H, N).to(torch.float32).contiguous(), s0, smap,
+                             algo, keep)
         if y.dtype != dt:
             y = y.to(dt)
         if with_state:

@@ -63,7 +63,7 @@ def test_argument_validation_without_launch(lib):
     assert lib.rwkvb200_rwkv7_bwd(*six, None, 0, A, None, *([A] * 6), None, A, need - 1,
                                   2, 8, 4, 64, 0, 0, 1, None) == -5
     # wkv6: several initial states and no state_map, n_state != B
-    assert lib.rwkvb200_wkv6_fwd(*([A] * 5), A, 3, None, A, None, 2, 8, 4, 64, 0, 0, None) == -8
+    assert lib.rwkvb200_wkv6_fwd(*([A] * 5), A, 3, None, A, None, None, 0, 2, 8, 4, 64, 0, 0, None) == -8
     assert lib.rwkvb200_wkv6_bwd_workspace_bytes(2, 8, 4, 64, 0, 1) > 0
     assert lib.rwkvb200_wkv6_bwd_workspace_bytes(2, 8, 4, 32, 0, 1) == 0
 
