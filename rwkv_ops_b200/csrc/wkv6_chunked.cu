@@ -147,18 +147,28 @@ wkv6c_fwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
   for (int c = 0; c < NT && ok; ++c) {
     const int t0 = c * L;
     const uint32_t par = c & 1;
-    // ---- pass W: g and its prefix sums
-    float4 gw[4];
+    // ---- the w and v rows of the chunk are requested together (r and k follow after the prefix sums:
+    // holding them across the barriers would spill at two CTAs per SM)
+    float4 gw[4], vv4[4];
+#pragma unroll
+    for (int n = 0; n < 4; ++n) {
+      const int e = tid + 256 * n, row = e >> 4, tok = t0 + row;
+      gw[n] = make_float4(0.f, 0.f, 0.f, 0.f);
+      vv4[n] = gw[n];
+      if (tok < Tn) {
+        const long long off = base + (long long)tok * tstride + 4 * c4;
+        gw[n] = load4(w + off); vv4[n] = load4(v + off);
+      }
+    }
+    // ---- pass W: g and its prefix sums; pass V
 #pragma unroll
     for (int n = 0; n < 4; ++n) {
       const int e = tid + 256 * n, row = e >> 4, tok = t0 + row;
       float4 f = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (tok < Tn) {
-        f = load4(w + base + (long long)tok * tstride + 4 * c4);
-        f = make_float4(-__expf(f.x), -__expf(f.y), -__expf(f.z), -__expf(f.w));
-      }
+      if (tok < Tn) f = make_float4(-__expf(gw[n].x), -__expf(gw[n].y), -__expf(gw[n].z), -__expf(gw[n].w));
       gw[n] = f;
       *reinterpret_cast<float4*>(&sm.gs[row * NROW + 4 * c4]) = f;
+      store_split4(sm.vt[0], sm.vt[1], row, 4 * c4, vv4[n]);
     }
     __syncthreads();
     {
@@ -199,14 +209,21 @@ wkv6c_fwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
       tmem_st_wait();
     }
     // ---- pass RK: scaled r, k (split hi/lo) and the diagonal term
+    float4 rr4[4], kk4[4];
 #pragma unroll
     for (int n = 0; n < 4; ++n) {
-      const int e = tid + 256 * n, row = e >> 4, tok = t0 + row;
-      float4 r4 = make_float4(0.f, 0.f, 0.f, 0.f), k4 = r4;
+      const int tok = t0 + ((tid + 256 * n) >> 4);
+      rr4[n] = make_float4(0.f, 0.f, 0.f, 0.f);
+      kk4[n] = rr4[n];
       if (tok < Tn) {
         const long long off = base + (long long)tok * tstride + 4 * c4;
-        r4 = load4(r + off); k4 = load4(k + off);
+        rr4[n] = load4(r + off); kk4[n] = load4(k + off);
       }
+    }
+#pragma unroll
+    for (int n = 0; n < 4; ++n) {
+      const int e = tid + 256 * n, row = e >> 4;
+      const float4 r4 = rr4[n], k4 = kk4[n];
       const float4 gp = *reinterpret_cast<const float4*>(&sm.gs[row * NROW + 4 * c4]);
       const float4 ta = *reinterpret_cast<const float4*>(&sm.qtot[0][4 * c4]);
       const float4 tb = *reinterpret_cast<const float4*>(&sm.qtot[1][4 * c4]);
@@ -222,14 +239,6 @@ wkv6c_fwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
 #pragma unroll
       for (int m = 8; m >= 1; m >>= 1) dg += __shfl_xor_sync(0xffffffffu, dg, m);
       if (c4 == 0) sm.dgs[row] = dg;
-    }
-    // ---- pass V
-#pragma unroll
-    for (int n = 0; n < 4; ++n) {
-      const int e = tid + 256 * n, row = e >> 4, tok = t0 + row;
-      float4 v4 = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (tok < Tn) v4 = load4(v + base + (long long)tok * tstride + 4 * c4);
-      store_split4(sm.vt[0], sm.vt[1], row, 4 * c4, v4);
     }
     // ask for the next chunk's rows to be brought into L2 while this chunk is in its MMA phases
     if (t0 + L < Tn && c4 == 0) {
@@ -430,18 +439,37 @@ wkv6c_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
   for (int c = NT - 1; c >= 0 && ok; --c) {
     const int t0 = c * L;
     const uint32_t par = (NT - 1 - c) & 1;
-    // ---- pass W: g and its prefix sums
-    float4 gw[4];
+    // ---- all global loads of the chunk are issued together (one exposed latency per chunk); r and k
+    // stay in registers until the u-term gradients at the end of the chunk
+    float4 gw[4], rr4[4], kk4[4];
+    {
+      float4 vv4[4], yy4[4];
 #pragma unroll
-    for (int n = 0; n < 4; ++n) {
-      const int e = tid + 256 * n, row = e >> 4, tok = t0 + row;
-      float4 f = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (tok < Tn) {
-        f = load4(w + base + (long long)tok * tstride + 4 * c4);
-        f = make_float4(-__expf(f.x), -__expf(f.y), -__expf(f.z), -__expf(f.w));
+      for (int n = 0; n < 4; ++n) {
+        const int e = tid + 256 * n, row = e >> 4, tok = t0 + row;
+        gw[n] = make_float4(0.f, 0.f, 0.f, 0.f);
+        rr4[n] = gw[n]; kk4[n] = gw[n]; vv4[n] = gw[n]; yy4[n] = gw[n];
+        if (tok < Tn) {
+          const long long off = base + (long long)tok * tstride + 4 * c4;
+          gw[n] = load4(w + off); vv4[n] = load4(v + off); yy4[n] = load4(d_y + off);
+          rr4[n] = load4(r + off); kk4[n] = load4(k + off);
+        }
       }
-      gw[n] = f;
-      *reinterpret_cast<float4*>(&sm.gg[row * NROW + 4 * c4]) = f;
+      // ---- pass W: g; pass V / DY: split tiles and dd_i = dy_i . v_i
+#pragma unroll
+      for (int n = 0; n < 4; ++n) {
+        const int e = tid + 256 * n, row = e >> 4, tok = t0 + row;
+        float4 f = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (tok < Tn) f = make_float4(-__expf(gw[n].x), -__expf(gw[n].y), -__expf(gw[n].z), -__expf(gw[n].w));
+        gw[n] = f;
+        *reinterpret_cast<float4*>(&sm.gg[row * NROW + 4 * c4]) = f;
+        store_split4(sm.vt[0], sm.vt[1], row, 4 * c4, vv4[n]);
+        store_split4(sm.dyt[0], sm.dyt[1], row, 4 * c4, yy4[n]);
+        float dd = vv4[n].x * yy4[n].x + vv4[n].y * yy4[n].y + vv4[n].z * yy4[n].z + vv4[n].w * yy4[n].w;
+#pragma unroll
+        for (int m = 8; m >= 1; m >>= 1) dd += __shfl_xor_sync(0xffffffffu, dd, m);
+        if (c4 == 0) sm.dds[row] = dd;
+      }
     }
     __syncthreads();
     {
@@ -488,12 +516,8 @@ wkv6c_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
     // ---- pass RK: scaled r, k (split) and the diagonal term
 #pragma unroll
     for (int n = 0; n < 4; ++n) {
-      const int e = tid + 256 * n, row = e >> 4, tok = t0 + row;
-      float4 r4 = make_float4(0.f, 0.f, 0.f, 0.f), k4 = r4;
-      if (tok < Tn) {
-        const long long off = base + (long long)tok * tstride + 4 * c4;
-        r4 = load4(r + off); k4 = load4(k + off);
-      }
+      const int e = tid + 256 * n, row = e >> 4;
+      const float4 r4 = rr4[n], k4 = kk4[n];
       const float4 gp = *reinterpret_cast<const float4*>(&sm.gs[row * NROW + 4 * c4]);
       const float4 ta = *reinterpret_cast<const float4*>(&sm.qtot[0][4 * c4]);
       const float4 tb = *reinterpret_cast<const float4*>(&sm.qtot[1][4 * c4]);
@@ -510,22 +534,6 @@ wkv6c_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
       for (int m = 8; m >= 1; m >>= 1) dg += __shfl_xor_sync(0xffffffffu, dg, m);
       if (c4 == 0) sm.dgs[row] = dg;
     }
-    // ---- pass V / DY: split tiles and dd_i = dy_i . v_i
-#pragma unroll
-    for (int n = 0; n < 4; ++n) {
-      const int e = tid + 256 * n, row = e >> 4, tok = t0 + row;
-      float4 v4 = make_float4(0.f, 0.f, 0.f, 0.f), y4 = v4;
-      if (tok < Tn) {
-        const long long off = base + (long long)tok * tstride + 4 * c4;
-        v4 = load4(v + off); y4 = load4(d_y + off);
-      }
-      store_split4(sm.vt[0], sm.vt[1], row, 4 * c4, v4);
-      store_split4(sm.dyt[0], sm.dyt[1], row, 4 * c4, y4);
-      float dd = v4.x * y4.x + v4.y * y4.y + v4.z * y4.z + v4.w * y4.w;
-#pragma unroll
-      for (int m = 8; m >= 1; m >>= 1) dd += __shfl_xor_sync(0xffffffffu, dd, m);
-      if (c4 == 0) sm.dds[row] = dd;
-    }
     if (c > 0 && c4 == 0) {   // bring the previous chunk's rows into L2 while this chunk is in its MMA phases
 #pragma unroll
       for (int n = 0; n < 4; ++n) {
@@ -536,6 +544,12 @@ wkv6c_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
         asm volatile("prefetch.global.L2 [%0];" ::"l"(k + off));
         asm volatile("prefetch.global.L2 [%0];" ::"l"(v + off));
         asm volatile("prefetch.global.L2 [%0];" ::"l"(d_y + off));
+        {   // the chunk-boundary state the previous chunk starts from, one 256-byte row per request pair
+          const int row = (tid + 256 * n) >> 4;
+          const float* S0p = states + (((size_t)unit * (NT + 1) + c - 1) * HS + row) * HS;
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(S0p));
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(S0p + 32));
+        }
         if (sizeof(T) == 4) {
           asm volatile("prefetch.global.L2 [%0];" ::"l"(w + off + 32));
           asm volatile("prefetch.global.L2 [%0];" ::"l"(r + off + 32));
@@ -674,7 +688,7 @@ wkv6c_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
       const int e = tid + 256 * n, row = e >> 4, tok = t0 + row;
       if (tok < Tn) {
         const long long off = base + (long long)tok * tstride + 4 * c4;
-        const float4 r4 = load4(r + off), k4 = load4(k + off);
+        const float4 r4 = rr4[n], k4 = kk4[n];
         const float dd = sm.dds[row];
         float4 a = *reinterpret_cast<const float4*>(&stage_dr[row * NROW + 4 * c4]);
         a.x += dd * u4.x * k4.x; a.y += dd * u4.y * k4.y; a.z += dd * u4.z * k4.z; a.w += dd * u4.w * k4.w;
