@@ -408,21 +408,23 @@ r7c_intra_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ w, con
 // ---------------------------------------------------------------------------------------------
 // scan kernel: grid = B*H, 128 threads, chunks in order, fp32 state in TMEM
 // ---------------------------------------------------------------------------------------------
-struct ScanStage {
-  unsigned char g[FWD_TILES][TILE_BYTES];   // q~, k~, b~, A_qb, O1, W, U (one bulk copy)
-  unsigned char v[TILE_BYTES];              // TMA
-};
+// Operand tiles are single-buffered: each group is requested for the next chunk the moment the MMAs
+// that read it have completed, which leaves it at least half a chunk step to arrive.  U and O1 are only
+// added row by row, so they never enter shared memory: every thread fetches its row into registers.
+// 11 tiles = 88 KB, so two CTAs (two sequences) share an SM.
 struct ScanSmem {
-  ScanStage st[2];
+  unsigned char qt[TILE_BYTES], kt[TILE_BYTES];   // group 1 (read by step a): q~, k~ (adjacent slots)
+  unsigned char w[TILE_BYTES], v[TILE_BYTES];     //                            W, v (TMA)
+  unsigned char bt[TILE_BYTES], aqb[TILE_BYTES];  // group 2 (read by step c): b~, A_qb (adjacent slots)
   unsigned char ht[TILE_BYTES];             // h~0 as bf16, [k][v]
   unsigned char sa[TILE_BYTES];             // sa as bf16, [token][v]
   unsigned char xt[TILE_BYTES];             // X = h~0 + k~^T v + b~^T sa as bf16 (kept for the backward)
   unsigned char ot[2][TILE_BYTES];          // output rows of a chunk, staged for a TMA store
-  uint64_t bar_full[2], bar_a, bar_c;
+  uint64_t bar_g1, bar_g2, bar_a, bar_c;
   uint32_t tmem_base;
 };
 
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(128, 2)
 r7c_scan_fwd_kernel(const __grid_constant__ CUtensorMap tmap_v, const unsigned char* __restrict__ ws_tiles,
                     const float* __restrict__ ws_aux, int tiles_per_chunk, unsigned char* __restrict__ bwd_tiles,
                     const float* __restrict__ h0, int n_state, const __grid_constant__ CUtensorMap tmap_o,
@@ -436,7 +438,7 @@ r7c_scan_fwd_kernel(const __grid_constant__ CUtensorMap tmap_v, const unsigned c
   const bool state_lane = lane < 16;
 
   if (tid == 0) {
-    mbar_init(&sm.bar_full[0], 1); mbar_init(&sm.bar_full[1], 1);
+    mbar_init(&sm.bar_g1, 1); mbar_init(&sm.bar_g2, 1);
     mbar_init(&sm.bar_a, 1); mbar_init(&sm.bar_c, 1);
     fence_mbar_init();
   }
@@ -447,16 +449,21 @@ r7c_scan_fwd_kernel(const __grid_constant__ CUtensorMap tmap_v, const unsigned c
   const uint32_t tm = sm.tmem_base;
   const uint32_t tm_p1 = tmem_addr(tm, 32 * warp, 0), tm_p2 = tmem_addr(tm, 32 * warp, 64);
 
-  auto issue_loads = [&](int c) {
-    ScanStage& s = sm.st[c & 1];
-    mbar_expect_tx(&sm.bar_full[c & 1], (FWD_TILES + 1) * TILE_BYTES);
-    bulk_load(s.g, ws_tiles + (ch0 + c) * (size_t)tiles_per_chunk * TILE_BYTES, FWD_TILES * TILE_BYTES,
-              &sm.bar_full[c & 1]);
-    tma_load_4d(s.v, &tmap_v, &sm.bar_full[c & 1], 0, c * L, hi, bi);
+  auto issue_g1 = [&](int c) {      // tid 0
+    const unsigned char* tiles = ws_tiles + (ch0 + c) * (size_t)tiles_per_chunk * TILE_BYTES;
+    mbar_expect_tx(&sm.bar_g1, 4 * TILE_BYTES);
+    bulk_load(sm.qt, tiles + S_QT * TILE_BYTES, 2 * TILE_BYTES, &sm.bar_g1);
+    bulk_load(sm.w, tiles + S_W * TILE_BYTES, TILE_BYTES, &sm.bar_g1);
+    tma_load_4d(sm.v, &tmap_v, &sm.bar_g1, 0, c * L, hi, bi);
+  };
+  auto issue_g2 = [&](int c) {      // tid 0
+    const unsigned char* tiles = ws_tiles + (ch0 + c) * (size_t)tiles_per_chunk * TILE_BYTES;
+    mbar_expect_tx(&sm.bar_g2, 2 * TILE_BYTES);
+    bulk_load(sm.bt, tiles + S_BT * TILE_BYTES, 2 * TILE_BYTES, &sm.bar_g2);
   };
   if (tid == 0) {
-    issue_loads(0);
-    if (NT > 1) issue_loads(1);
+    issue_g1(0);
+    issue_g2(0);
   }
 
   // ---- initial state: h~0 = e^{gref(chunk 0)} h0, fp32 into TMEM (lower lane halves of P2), bf16 into ht
@@ -493,25 +500,35 @@ r7c_scan_fwd_kernel(const __grid_constant__ CUtensorMap tmap_v, const unsigned c
 
   bool ok = true;
   for (int c = 0; c < NT && ok; ++c) {
-    ScanStage& s = sm.st[c & 1];
     const int t0 = c * L;
+    // this thread's row of U (state lanes) or O1 (token lanes), straight from the workspace
+    uint4 addrow[8];
+    {
+      const unsigned char* tile = ws_tiles + ((ch0 + c) * (size_t)tiles_per_chunk + (state_lane ? S_U : S_O1)) * TILE_BYTES;
+#pragma unroll
+      for (int q = 0; q < 8; ++q) addrow[q] = __ldg(reinterpret_cast<const uint4*>(tile + tile_chunk_off(row, q)));
+      if (c + 1 < NT) asm volatile("prefetch.global.L2 [%0];" ::"l"(tile + (size_t)tiles_per_chunk * TILE_BYTES + row * 128));
+    }
     // decay factors needed at the end of this chunk, fetched early
     float scale = 1.f;
     if (state_lane) {
       scale = ws_aux[(ch0 + c) * AUX_FLOATS + 64 + row];                       // e^{glast-gref} of this chunk
       if (c + 1 < NT) scale *= ws_aux[(ch0 + c + 1) * AUX_FLOATS + row];        // e^{gref} of the next chunk
     }
-    ok = mbar_wait(&sm.bar_full[c & 1], (c >> 1) & 1, status, 211);
     // (a) SA = W h~0, QH = q~ h~0 (P1);  H += k~^T v (P2 lower)
-    if (tid == 0 && ok) {
-      tc_fence_after();
-      umma_tile<64, 64, 0, 1>(tmem_addr(tm, 0, 0), smem_u32(s.g[S_W]), smem_u32(sm.ht), false);
-      umma_tile<64, 64, 0, 1>(tmem_addr(tm, 16, 0), smem_u32(s.g[S_QT]), smem_u32(sm.ht), false);
-      umma_tile<64, 64, 1, 1>(tmem_addr(tm, 0, 64), smem_u32(s.g[S_KT]), smem_u32(s.v), true);
-      umma_commit(&sm.bar_a);
+    if (tid == 0) {
+      ok = mbar_wait(&sm.bar_g1, c & 1, status, 211);
+      if (ok) {
+        tc_fence_after();
+        umma_tile<64, 64, 0, 1>(tmem_addr(tm, 0, 0), smem_u32(sm.w), smem_u32(sm.ht), false);
+        umma_tile<64, 64, 0, 1>(tmem_addr(tm, 16, 0), smem_u32(sm.qt), smem_u32(sm.ht), false);
+        umma_tile<64, 64, 1, 1>(tmem_addr(tm, 0, 64), smem_u32(sm.kt), smem_u32(sm.v), true);
+        umma_commit(&sm.bar_a);
+      }
     }
     ok = ok && mbar_wait(&sm.bar_a, c & 1, status, 212);
     tc_fence_after();
+    if (tid == 0 && ok && c + 1 < NT) issue_g1(c + 1);     // group 1 has been read: request the next chunk's
     float keep[64];     // token lanes: q~ h~0 + O1
     if (ok) {
 #pragma unroll
@@ -520,7 +537,14 @@ r7c_scan_fwd_kernel(const __grid_constant__ CUtensorMap tmap_v, const unsigned c
         tmem_ld32(tm_p1 + 32 * part, r);
         tmem_ld_wait();
         float add[32];
-        tile_load_row32(state_lane ? s.g[S_U] : s.g[S_O1], row, 32 * part, add);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const uint4 u = addrow[4 * part + q];
+          add[8 * q + 0] = bf16_lo(u.x); add[8 * q + 1] = bf16_hi(u.x);
+          add[8 * q + 2] = bf16_lo(u.y); add[8 * q + 3] = bf16_hi(u.y);
+          add[8 * q + 4] = bf16_lo(u.z); add[8 * q + 5] = bf16_hi(u.z);
+          add[8 * q + 6] = bf16_lo(u.w); add[8 * q + 7] = bf16_hi(u.w);
+        }
 #pragma unroll
         for (int j = 0; j < 32; ++j) keep[32 * part + j] = __uint_as_float(r[j]) + add[j];
         if (state_lane) tile_store_row32(sm.sa, row, 32 * part, keep + 32 * part);   // sa = W h~0 + U
@@ -537,13 +561,17 @@ r7c_scan_fwd_kernel(const __grid_constant__ CUtensorMap tmap_v, const unsigned c
     }
     // (c) H += b~^T sa (P2 lower);  OQ = A_qb sa (P2 upper)
     if (tid == 0 && ok) {
-      tc_fence_after();
-      umma_tile<64, 64, 1, 1>(tmem_addr(tm, 0, 64), smem_u32(s.g[S_BT]), smem_u32(sm.sa), true);
-      umma_tile<64, 64, 0, 1>(tmem_addr(tm, 16, 64), smem_u32(s.g[S_AQB]), smem_u32(sm.sa), false);
-      umma_commit(&sm.bar_c);
+      ok = mbar_wait(&sm.bar_g2, c & 1, status, 214);
+      if (ok) {
+        tc_fence_after();
+        umma_tile<64, 64, 1, 1>(tmem_addr(tm, 0, 64), smem_u32(sm.bt), smem_u32(sm.sa), true);
+        umma_tile<64, 64, 0, 1>(tmem_addr(tm, 16, 64), smem_u32(sm.aqb), smem_u32(sm.sa), false);
+        umma_commit(&sm.bar_c);
+      }
     }
     ok = ok && mbar_wait(&sm.bar_c, c & 1, status, 213);
     tc_fence_after();
+    if (tid == 0 && ok && c + 1 < NT) issue_g2(c + 1);     // group 2 has been read
     if (bwd_tiles) {                                  // ht / sa are rewritten below and in the next chunk
       if (tid == 0) bulk_wait_read();
       __syncthreads();
@@ -592,7 +620,6 @@ r7c_scan_fwd_kernel(const __grid_constant__ CUtensorMap tmap_v, const unsigned c
       bulk_commit();
       bulk_wait_read_1();                // the buffer of the previous chunk is free again
     }
-    if (tid == 0 && ok && c + 2 < NT) issue_loads(c + 2);
   }
   if (tid == 0) bulk_wait_all();
   __syncthreads();
