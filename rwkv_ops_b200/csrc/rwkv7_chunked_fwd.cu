@@ -260,15 +260,39 @@ r7c_intra_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ w, con
         bulk_commit();
       }
     }
-    // ---- rows of MMA 2 (warps 2-7), then Ainv = (I - stril(A_ab))^-1 in fp32 on all eight warps.
-    // Thread (column c = tid & 63, row block I = tid >> 6) owns the 16 entries X[16I .. 16I+15][c] of
-    // the inverse.  Blocked forward substitution, right-looking: in step J the threads of block J finish
-    // their block with a 16-row substitution against the diagonal block and publish it to shared memory
-    // (xs, in the space of the A_qk / A_ak tiles once MMA 2 has read them); after a barrier every later
-    // block subtracts its coupling with block J.  The four steps are the only serial chain.
+    // ---- rows of MMA 2 (warps 2-7), then Ainv = X = (I - N)^-1, N = stril(A_ab), in fp32 on all eight warps,
+    // by two levels of block inversion (everything below happens in place in nmat):
+    //   D. the four 16 x 16 diagonal blocks D_I = (I - N_II)^-1, one column per thread, row by row -- the
+    //      only substitutions, all four side by side;
+    //   1. the two 32 x 32 diagonal blocks: X_10 = D_1 (N_10 D_0) and X_32 = D_3 (N_32 D_2), 64 threads each;
+    //   2. T = N_BA X_A (A = rows 0..31, B = rows 32..63), four entries per thread on all 256 threads;
+    //   3. X_BA = X_B T, likewise.
+    // P = N_IJ D_J and T pass through the A_qk / A_ak tiles, free once MMA 2 has read them.
     {
       const int c = tid & 63, I = tid >> 6;
-      float* xs = reinterpret_cast<float*>(sm.aqk);          // xs[row][column], 64 x 64 fp32
+      float* scratch = reinterpret_cast<float*>(sm.aqk);
+      if ((c >> 4) == I) {       // step D (while MMA 2 runs)
+        float xb[16];
+#pragma unroll
+        for (int rr = 0; rr < 16; ++rr) xb[rr] = (rr == (c & 15)) ? 1.f : 0.f;
+#pragma unroll
+        for (int rr = 1; rr < 16; ++rr) {
+          const float* nrow = &sm.nmat[(16 * I + rr) * NROW + 16 * I];
+          float p0 = 0.f, p1 = 0.f, p2 = 0.f, p3 = 0.f;   // entries at or right of the diagonal are 0
+#pragma unroll
+          for (int jj = 0; jj < (rr + 3) / 4; ++jj) {
+            const float4 n = *reinterpret_cast<const float4*>(nrow + 4 * jj);
+            p0 += n.x * xb[4 * jj];
+            if (4 * jj + 1 < rr) p1 += n.y * xb[4 * jj + 1];
+            if (4 * jj + 2 < rr) p2 += n.z * xb[4 * jj + 2];
+            if (4 * jj + 3 < rr) p3 += n.w * xb[4 * jj + 3];
+          }
+          xb[rr] += (p0 + p1) + (p2 + p3);
+        }
+        __syncwarp((c & 16) ? 0xffff0000u : 0x0000ffffu);   // the 16 columns of a block share a half-warp
+#pragma unroll
+        for (int rr = 0; rr < 16; ++rr) sm.nmat[(16 * I + rr) * NROW + c] = xb[rr];
+      }
       if (warp >= 2) {
         // warps 4-5 take O1 (both column halves), warps 2-3 and 6-7 take Y (one column half each)
         ok = mbar_wait(&sm.bar_m2, par, status, 203) && ok;
@@ -295,62 +319,104 @@ r7c_intra_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ w, con
           tile_store_row32(sm.y, i, 32 * hsel, x);
         }
       }
-      float xb[16];
+      // the scratch area: MMA 2 (and the copies of A_qk / A_ak kept for the backward) must be done with it
+      ok = mbar_wait(&sm.bar_m2, par, status, 205) && ok;
+      if (tid == 0) {
+        if (keep_for_bwd) bulk_wait_read();
+        if (next < n_ch) load_v(next);      // MMA 2 has read the v tile: request the next one
+      }
+      __syncthreads();
+      R7C_STAMP(10);
+      if (I & 1) {               // step 1: row block I, column block I - 1
+        const int cl = tid & 15, r0 = ((tid & 63) >> 4) * 4;
+        const int rb = 16 * I, cbk = 16 * (I - 1);
+        float* P = scratch + (I >> 1) * 256;
+        float col[16], acc[4];
 #pragma unroll
-      for (int rr = 0; rr < 16; ++rr) xb[rr] = (16 * I + rr == c) ? 1.f : 0.f;
-      const bool live = 16 * I + 15 >= c;        // rows above the diagonal of column c stay zero
-      for (int J = 0; J < 4; ++J) {
-        R7C_STAMP(10 + J);
-        if (I == J) {
-          if (live) {
+        for (int kk = 0; kk < 16; ++kk) col[kk] = sm.nmat[(cbk + kk) * NROW + cbk + cl];     // D_J[:, cl]
 #pragma unroll
-            for (int rr = 1; rr < 16; ++rr) {
-              const float* nrow = &sm.nmat[(16 * I + rr) * NROW + 16 * I];
-              float p0 = 0.f, p1 = 0.f, p2 = 0.f, p3 = 0.f;   // entries at or right of the diagonal are 0
+        for (int q = 0; q < 4; ++q) {
+          const float* nrow = &sm.nmat[(rb + r0 + q) * NROW + cbk];
+          float s_ = 0.f;
 #pragma unroll
-              for (int jj = 0; jj < (rr + 3) / 4; ++jj) {
-                const float4 n = *reinterpret_cast<const float4*>(nrow + 4 * jj);
-                p0 += n.x * xb[4 * jj];
-                if (4 * jj + 1 < rr) p1 += n.y * xb[4 * jj + 1];
-                if (4 * jj + 2 < rr) p2 += n.z * xb[4 * jj + 2];
-                if (4 * jj + 3 < rr) p3 += n.w * xb[4 * jj + 3];
-              }
-              xb[rr] += (p0 + p1) + (p2 + p3);
-            }
+          for (int jj = 0; jj < 4; ++jj) {
+            const float4 n = *reinterpret_cast<const float4*>(nrow + 4 * jj);
+            s_ += n.x * col[4 * jj] + n.y * col[4 * jj + 1] + n.z * col[4 * jj + 2] + n.w * col[4 * jj + 3];
           }
-          if (J == 0) {
-            // first write to xs: MMA 2 (and the copies of A_qk / A_ak kept for the backward) must be done
-            ok = mbar_wait(&sm.bar_m2, par, status, 205) && ok;
-            if (tid == 0) {
-              if (keep_for_bwd) bulk_wait_read();
-              if (next < n_ch) load_v(next);      // MMA 2 has read the v tile: request the next one
-            }
-            asm volatile("bar.sync 1, 64;" ::: "memory");
-          }
-#pragma unroll
-          for (int rr = 0; rr < 16; ++rr) {
-            if (J < 3) xs[(16 * I + rr) * 64 + c] = xb[rr];
-            *reinterpret_cast<bf16*>(sm.ainv + tile_off(16 * I + rr, c)) = __float2bfloat16_rn(xb[rr]);
-          }
+          acc[q] = s_;
         }
-        if (J < 3) {
-          __syncthreads();
-          if (I > J && 16 * J + 15 >= c) {        // block J of column c is not all zero
-            float xj[16];
 #pragma unroll
-            for (int t = 0; t < 16; ++t) xj[t] = xs[(16 * J + t) * 64 + c];
+        for (int q = 0; q < 4; ++q) P[(r0 + q) * 16 + cl] = acc[q];
+        if (I == 1) asm volatile("bar.sync 1, 64;" ::: "memory");
+        else        asm volatile("bar.sync 2, 64;" ::: "memory");
 #pragma unroll
-            for (int rr = 0; rr < 16; ++rr) {
-              const float* nrow = &sm.nmat[(16 * I + rr) * NROW + 16 * J];
+        for (int kk = 0; kk < 16; ++kk) col[kk] = P[kk * 16 + cl];
 #pragma unroll
-              for (int jj = 0; jj < 4; ++jj) {
-                const float4 n = *reinterpret_cast<const float4*>(nrow + 4 * jj);
-                xb[rr] += n.x * xj[4 * jj] + n.y * xj[4 * jj + 1] + n.z * xj[4 * jj + 2] + n.w * xj[4 * jj + 3];
-              }
-            }
+        for (int q = 0; q < 4; ++q) {
+          const float* drow = &sm.nmat[(rb + r0 + q) * NROW + rb];       // D_I is stored in full (zeros above)
+          float s_ = 0.f;
+#pragma unroll
+          for (int jj = 0; jj < 4; ++jj) {
+            const float4 n = *reinterpret_cast<const float4*>(drow + 4 * jj);
+            s_ += n.x * col[4 * jj] + n.y * col[4 * jj + 1] + n.z * col[4 * jj + 2] + n.w * col[4 * jj + 3];
+          }
+          acc[q] = s_;
+        }
+#pragma unroll
+        for (int q = 0; q < 4; ++q) sm.nmat[(rb + r0 + q) * NROW + cbk + cl] = acc[q];
+      }
+      __syncthreads();
+      R7C_STAMP(11);
+      float* Tm = scratch;       // T[32][33]
+      {                          // step 2, and the three finished quadrants of Ainv as bf16
+        const int r0 = 4 * warp;
+        float col[32], acc[4];
+#pragma unroll
+        for (int kk = 0; kk < 32; ++kk) col[kk] = sm.nmat[kk * NROW + lane];                 // X_A[:, lane]
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const float* nrow = &sm.nmat[(32 + r0 + q) * NROW];
+          float s_ = 0.f;
+#pragma unroll
+          for (int jj = 0; jj < 8; ++jj) {
+            const float4 n = *reinterpret_cast<const float4*>(nrow + 4 * jj);
+            s_ += n.x * col[4 * jj] + n.y * col[4 * jj + 1] + n.z * col[4 * jj + 2] + n.w * col[4 * jj + 3];
+          }
+          acc[q] = s_;
+        }
+#pragma unroll
+        for (int q = 0; q < 4; ++q) Tm[(r0 + q) * 33 + lane] = acc[q];
+#pragma unroll
+        for (int n = 0; n < 2; ++n) {
+          const int e = tid + 256 * n, row = e >> 3, cc = e & 7;
+          if (row < 32 || cc >= 4) {
+            const float4 f0 = *reinterpret_cast<const float4*>(&sm.nmat[row * NROW + 8 * cc]);
+            const float4 f1 = *reinterpret_cast<const float4*>(&sm.nmat[row * NROW + 8 * cc + 4]);
+            *reinterpret_cast<uint4*>(sm.ainv + tile_chunk_off(row, cc)) =
+                make_uint4(pack_bf16(f0.x, f0.y), pack_bf16(f0.z, f0.w), pack_bf16(f1.x, f1.y), pack_bf16(f1.z, f1.w));
           }
         }
       }
+      __syncthreads();
+      R7C_STAMP(12);
+      {                          // step 3
+        const int r0 = 4 * warp;
+        float col[32];
+#pragma unroll
+        for (int kk = 0; kk < 32; ++kk) col[kk] = Tm[kk * 33 + lane];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const float* xrow = &sm.nmat[(32 + r0 + q) * NROW + 32];        // X_B row (zeros above the diagonal)
+          float s_ = 0.f;
+#pragma unroll
+          for (int jj = 0; jj < 8; ++jj) {
+            const float4 n = *reinterpret_cast<const float4*>(xrow + 4 * jj);
+            s_ += n.x * col[4 * jj] + n.y * col[4 * jj + 1] + n.z * col[4 * jj + 2] + n.w * col[4 * jj + 3];
+          }
+          *reinterpret_cast<bf16*>(sm.ainv + tile_off(32 + r0 + q, lane)) = __float2bfloat16_rn(s_);
+        }
+      }
+      R7C_STAMP(13);
     }
     R7C_STAMP(5);
     fence_async_smem();

@@ -387,7 +387,8 @@ wkv6c_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
                  const float* __restrict__ u, const T* __restrict__ d_y, const float* __restrict__ d_sT,
                  const float* __restrict__ states, T* __restrict__ dr, T* __restrict__ dk, T* __restrict__ dv,
                  T* __restrict__ dw, float* __restrict__ du_partial, float* __restrict__ d_s0,
-                 int Tn, int H, int* status) {
+                 int Tn, int H, int* status, long long* dbg) {
+#define W6C_STAMP(n) do { if (dbg && tid == 0 && blockIdx.x == gridDim.x / 2 && c == NT - 2) dbg[n] = clock64(); } while (0)
   extern __shared__ unsigned char smem_raw[];
   BwdSmem& sm = *reinterpret_cast<BwdSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -439,6 +440,7 @@ wkv6c_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
   for (int c = NT - 1; c >= 0 && ok; --c) {
     const int t0 = c * L;
     const uint32_t par = (NT - 1 - c) & 1;
+    W6C_STAMP(32);
     // ---- all global loads of the chunk are issued together (one exposed latency per chunk); r and k
     // stay in registers until the u-term gradients at the end of the chunk
     float4 gw[4], rr4[4], kk4[4];
@@ -472,6 +474,7 @@ wkv6c_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
       }
     }
     __syncthreads();
+    W6C_STAMP(33);
     {
       const int ch = tid & 63, quarter = tid >> 6;
       float gv[16];
@@ -487,6 +490,7 @@ wkv6c_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
       for (int j = 0; j < 16; ++j) sm.gs[(16 * quarter + j) * NROW + ch] = gv[j] + add;
     }
     __syncthreads();
+    W6C_STAMP(34);
     float e0 = 1.f, dlast = 1.f;
     if (!lower) {
       e0 = __expf(fmaxf(sm.qtot[0][srow] + sm.qtot[1][srow], -EXP_CLAMP));
@@ -513,6 +517,7 @@ wkv6c_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
       }
       store_split_row32(sm.st[0], sm.st[1], srow, 32 * hsel, x);
     }
+    W6C_STAMP(35);
     // ---- pass RK: scaled r, k (split) and the diagonal term
 #pragma unroll
     for (int n = 0; n < 4; ++n) {
@@ -563,6 +568,7 @@ wkv6c_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
     tc_fence_before();
     __syncthreads();
 
+    W6C_STAMP(36);
     // ---- batch 1: r~ k~^T (lower halves) and dy v^T (upper halves), columns 0..63
     if (tid == 0) {
       tc_fence_after();
@@ -572,6 +578,7 @@ wkv6c_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
     }
     ok = mbar_wait(&sm.bar_1, par, status, 411) && ok;
     tc_fence_after();
+    W6C_STAMP(37);
     if (ok) {
       uint32_t rr[32];
       tmem_ld32(tm_c0, rr);
@@ -590,6 +597,7 @@ wkv6c_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
     tc_fence_before();
     ok = __syncthreads_and(ok);
 
+    W6C_STAMP(38);
     // ---- batch 2
     if (tid == 0 && ok) {
       tc_fence_after();
@@ -608,6 +616,7 @@ wkv6c_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
     }
     ok = mbar_wait(&sm.bar_2, par, status, 412) && ok;
     tc_fence_after();
+    W6C_STAMP(39);
     if (ok) {
       uint32_t r1[32], r2[32];
       tmem_ld32(tm_c1, r1);
@@ -660,6 +669,7 @@ wkv6c_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
     }
     tc_fence_before();
     ok = __syncthreads_and(ok);
+    W6C_STAMP(40);
     // ---- decay gradient: dg_j = sum_{i>=j} (dgi_i + dge_i) - dge_j + dglast;  dw = dg g
     {
       const int ch = tid & 63, quarter = tid >> 6;
@@ -682,6 +692,7 @@ wkv6c_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
       }
     }
     __syncthreads();
+    W6C_STAMP(41);
     // ---- outputs, coalesced, plus the u-term parts of dr, dk and du
 #pragma unroll
     for (int n = 0; n < 4; ++n) {
@@ -703,7 +714,9 @@ wkv6c_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
       }
     }
     __syncthreads();
+    W6C_STAMP(42);
   }
+#undef W6C_STAMP
   // ---- du of this (batch, head) and the gradient of its initial state
   atomicAdd(&sm.du_s[4 * c4], du_acc.x); atomicAdd(&sm.du_s[4 * c4 + 1], du_acc.y);
   atomicAdd(&sm.du_s[4 * c4 + 2], du_acc.z); atomicAdd(&sm.du_s[4 * c4 + 3], du_acc.w);
@@ -781,7 +794,7 @@ int launch_wkv6_chunked_bwd(const void* r, const void* k, const void* v, const v
         return RWKVB200_E_CUDA;
       wkv6c_bwd_kernel<T><<<B * H, 256, smem, st>>>((const T*)r, (const T*)k, (const T*)v, (const T*)w, u,
                                                      (const T*)d_y, d_sT, states, (T*)dr, (T*)dk, (T*)dv, (T*)dw,
-                                                     du_partial, d_s0, Tn, H, status));
+                                                     du_partial, d_s0, Tn, H, status, debug_stamp_buffer()));
   }
   e = check_launch();
   if (e) return e;
