@@ -124,7 +124,7 @@ r7c_bwd_pre_kernel(const __grid_constant__ CUtensorMap tmap_do, unsigned char* _
 }
 
 // ---------------------------------------------------------------------------------------------
-// 4. reverse scan: grid = B*H, 128 threads
+// 4. reverse scan: grid = B*H, 256 threads (the two warps of a TMEM lane window take 32 columns each)
 // ---------------------------------------------------------------------------------------------
 struct BScanStage {
   unsigned char b2[TILE_BYTES], p2[TILE_BYTES];   // adjacent workspace slots: one bulk copy
@@ -138,7 +138,7 @@ struct BScanSmem {
   uint32_t tmem_base;
 };
 
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(256, 2)
 r7c_bwd_scan_kernel(const __grid_constant__ CUtensorMap tmap_do, unsigned char* __restrict__ ws_tiles,
                     const float* __restrict__ ws_aux, int tiles_per_chunk, const float* __restrict__ d_ht,
                     float* __restrict__ d_h0, int H, int NT, int* status) {
@@ -147,7 +147,8 @@ r7c_bwd_scan_kernel(const __grid_constant__ CUtensorMap tmap_do, unsigned char* 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int unit = blockIdx.x, bi = unit / H, hi = unit % H;
   const size_t ch0 = (size_t)unit * NT;
-  const int row = 16 * warp + (lane & 15);
+  const int wq = warp & 3, hsel = warp >> 2, c0 = 32 * hsel;
+  const int row = 16 * wq + (lane & 15);
   const bool state_lane = lane < 16;
 
   if (tid == 0) {
@@ -160,7 +161,7 @@ r7c_bwd_scan_kernel(const __grid_constant__ CUtensorMap tmap_do, unsigned char* 
   __syncthreads();
   tc_fence_after();
   const uint32_t tm = sm.tmem_base;
-  const uint32_t tm_w = tmem_addr(tm, 32 * warp, 0);
+  const uint32_t tm_w = tmem_addr(tm, 32 * wq, c0);
 
   auto issue_loads = [&](int n) {     // n-th chunk in reverse order
     const int c = NT - 1 - n;
@@ -178,14 +179,14 @@ r7c_bwd_scan_kernel(const __grid_constant__ CUtensorMap tmap_do, unsigned char* 
   }
 
   // gradient of the state after the current chunk, row k of dh[k][v] = d_ht[v][k]
-  float dh[64];
+  float dh[32];        // columns c0 .. c0 + 31
   if (state_lane && d_ht) {
     const float* S = d_ht + (size_t)unit * 4096;
 #pragma unroll
-    for (int vv = 0; vv < 64; ++vv) dh[vv] = S[vv * 64 + row];
+    for (int vv = 0; vv < 32; ++vv) dh[vv] = S[(c0 + vv) * 64 + row];
   } else {
 #pragma unroll
-    for (int vv = 0; vv < 64; ++vv) dh[vv] = 0.f;
+    for (int vv = 0; vv < 32; ++vv) dh[vv] = 0.f;
   }
 
   bool ok = true;
@@ -198,9 +199,8 @@ r7c_bwd_scan_kernel(const __grid_constant__ CUtensorMap tmap_do, unsigned char* 
       const float dc = ws_aux[(ch0 + c) * AUX_FLOATS + 64 + row];
       e0 = ws_aux[(ch0 + c) * AUX_FLOATS + row];
 #pragma unroll
-      for (int vv = 0; vv < 64; ++vv) dh[vv] *= dc;      // dh^ = e^{glast-gref} dh_L
-      tile_store_row32(sm.dhh, row, 0, dh);
-      tile_store_row32(sm.dhh, row, 32, dh + 32);
+      for (int vv = 0; vv < 32; ++vv) dh[vv] *= dc;      // dh^ = e^{glast-gref} dh_L
+      tile_store_row32(sm.dhh, row, c0, dh);
     }
     ok = mbar_wait(&sm.bar_full[n & 1], (n >> 1) & 1, status, 311);
     fence_async_smem();
@@ -217,18 +217,15 @@ r7c_bwd_scan_kernel(const __grid_constant__ CUtensorMap tmap_do, unsigned char* 
     ok = ok && mbar_wait(&sm.bar_m1, n & 1, status, 312);
     tc_fence_after();
     if (ok) {
+      uint32_t r[32];
+      tmem_ld32(tm_w, r);
+      tmem_ld_wait();
+      if (!state_lane) {      // dz = P2 + B2 dh^
+        float x[32], p[32];
+        tile_load_row32(s.p2, row, c0, p);
 #pragma unroll
-      for (int part = 0; part < 2; ++part) {
-        uint32_t r[32];
-        tmem_ld32(tm_w + 32 * part, r);
-        tmem_ld_wait();
-        if (!state_lane) {      // dz = P2 + B2 dh^
-          float x[32], p[32];
-          tile_load_row32(s.p2, row, 32 * part, p);
-#pragma unroll
-          for (int j = 0; j < 32; ++j) x[j] = __uint_as_float(r[j]) + p[j];
-          tile_store_row32(sm.dz, row, 32 * part, x);
-        }
+        for (int j = 0; j < 32; ++j) x[j] = __uint_as_float(r[j]) + p[j];
+        tile_store_row32(sm.dz, row, c0, x);
       }
     }
     fence_async_smem();
@@ -244,15 +241,12 @@ r7c_bwd_scan_kernel(const __grid_constant__ CUtensorMap tmap_do, unsigned char* 
     ok = ok && mbar_wait(&sm.bar_m2, n & 1, status, 313);
     tc_fence_after();
     if (ok) {
+      uint32_t r[32];
+      tmem_ld32(tm_w, r);
+      tmem_ld_wait();
+      if (state_lane) {       // dh0 = e^{gref} (q~^T do + a~^T dz + dh^)
 #pragma unroll
-      for (int part = 0; part < 2; ++part) {
-        uint32_t r[32];
-        tmem_ld32(tm_w + 32 * part, r);
-        tmem_ld_wait();
-        if (state_lane) {       // dh0 = e^{gref} (q~^T do + a~^T dz + dh^)
-#pragma unroll
-          for (int j = 0; j < 32; ++j) dh[32 * part + j] = e0 * (__uint_as_float(r[j]) + dh[32 * part + j]);
-        }
+        for (int j = 0; j < 32; ++j) dh[j] = e0 * (__uint_as_float(r[j]) + dh[j]);
       }
     }
     if (tid == 0) bulk_wait_read();     // dhh and dz tiles are rewritten in the next iteration
@@ -263,7 +257,7 @@ r7c_bwd_scan_kernel(const __grid_constant__ CUtensorMap tmap_do, unsigned char* 
   if (state_lane && d_h0 && ok) {
     float* S = d_h0 + (size_t)unit * 4096;
 #pragma unroll
-    for (int vv = 0; vv < 64; ++vv) S[vv * 64 + row] = dh[vv];
+    for (int vv = 0; vv < 32; ++vv) S[(c0 + vv) * 64 + row] = dh[vv];
   }
   if (tid == 0) bulk_wait_all();
   __syncthreads();
@@ -348,6 +342,26 @@ r7c_bwd_final_kernel(const bf16* __restrict__ w, const __grid_constant__ CUtenso
     bulk_load(sm.kt, tiles + S_KT * TILE_BYTES, TILE_BYTES, &sm.bar_ldb);
     bulk_load(sm.bt, tiles + S_BT * TILE_BYTES, TILE_BYTES, &sm.bar_ldb);
   };
+  // Ask for everything a chunk-head will load to be brought into L2 (issued one chunk-head ahead of the
+  // loads themselves, which then take an L2 round trip instead of a DRAM one).
+  auto prefetch_l2 = [&](int ch) {      // one warp
+    int bi, hi, t0; coords(ch, bi, hi, t0);
+    const unsigned char* tiles = ws_tiles + (size_t)ch * tiles_per_chunk * TILE_BYTES;
+    if (lane == 0) {
+      tma_prefetch_4d(&tmap_do, 0, t0, hi, bi);
+      tma_prefetch_4d(&tmap_v, 0, t0, hi, bi);
+      bulk_prefetch_l2(tiles + S_QT * TILE_BYTES, 3 * TILE_BYTES);     // q~, k~, b~
+      bulk_prefetch_l2(tiles + S_AT * TILE_BYTES, 3 * TILE_BYTES);     // a~, A_qk, A_ak
+      bulk_prefetch_l2(tiles + S_SA * TILE_BYTES, 3 * TILE_BYTES);     // sa, h~0, X
+      bulk_prefetch_l2(tiles + S_DZ * TILE_BYTES, 2 * TILE_BYTES);     // dz, dh^
+    }
+    const long long base = bi * lay.sb + hi * lay.sh;
+#pragma unroll
+    for (int n = 0; n < 2; ++n) {
+      const int tok = t0 + lane + 32 * n;
+      if (tok < Tn) asm volatile("prefetch.global.L2 [%0];" ::"l"(w + base + (long long)tok * lay.st));
+    }
+  };
   auto load_w = [&](int ch, uint4 (&rw)[2]) {   // all threads: 2 x 8 channels of the chunk's w rows
     int bi, hi, t0; coords(ch, bi, hi, t0);
     const long long base = bi * lay.sb + hi * lay.sh;
@@ -363,6 +377,7 @@ r7c_bwd_final_kernel(const bf16* __restrict__ w, const __grid_constant__ CUtenso
   if (blockIdx.x < n_ch) {
     if (tid == 0) { load_group_a(blockIdx.x); load_group_b(blockIdx.x); }
     load_w(blockIdx.x, rw);
+    if (warp == 1 && blockIdx.x + gridDim.x < n_ch) prefetch_l2(blockIdx.x + gridDim.x);
   }
 
   bool ok = true;
@@ -495,6 +510,7 @@ r7c_bwd_final_kernel(const bf16* __restrict__ w, const __grid_constant__ CUtenso
     if (next < n_ch) {
       if (tid == 0 && ok) { bulk_wait_read(); load_group_a(next); }
       load_w(next, rw);
+      if (warp == 1 && next + (int)gridDim.x < n_ch) prefetch_l2(next + gridDim.x);
     }
 
     // ---- epilogue.  Row r < 64 holds dq~_i and dk~_i (token i = r), row r >= 64 holds da~_i, db~_i; the
@@ -627,7 +643,7 @@ int launch_rwkv7_chunked_bwd(const void* r, const void* w, const void* k, const 
     const int smem = (int)sizeof(BScanSmem) + 1024;
     if (cuda_ok(cudaFuncSetAttribute(r7c_bwd_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem))) return RWKVB200_E_CUDA;
     ProfScope prof("r7c_bwd_scan_kernel", st);
-    r7c_bwd_scan_kernel<<<B * H, 128, smem, st>>>(tmap_do, ws.tiles, ws.aux, ALL_TILES, d_ht, d_h0, H, NT, status);
+    r7c_bwd_scan_kernel<<<B * H, 256, smem, st>>>(tmap_do, ws.tiles, ws.aux, ALL_TILES, d_ht, d_h0, H, NT, status);
   }
   e = check_launch();
   if (e) return e;

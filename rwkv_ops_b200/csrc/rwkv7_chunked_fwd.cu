@@ -472,7 +472,8 @@ r7c_intra_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ w, con
 }
 
 // ---------------------------------------------------------------------------------------------
-// scan kernel: grid = B*H, 128 threads, chunks in order, fp32 state in TMEM
+// scan kernel: grid = B*H, 256 threads, chunks in order, fp32 state in TMEM.  Warp w reads TMEM lanes
+// 32*(w&3)..; the two warps that share a lane window take 32 of the 64 columns each (hsel = w>>2).
 // ---------------------------------------------------------------------------------------------
 // Operand tiles are single-buffered: each group is requested for the next chunk the moment the MMAs
 // that read it have completed, which leaves it at least half a chunk step to arrive.  U and O1 are only
@@ -490,17 +491,19 @@ struct ScanSmem {
   uint32_t tmem_base;
 };
 
-__global__ void __launch_bounds__(128, 2)
+__global__ void __launch_bounds__(256, 2)
 r7c_scan_fwd_kernel(const __grid_constant__ CUtensorMap tmap_v, const unsigned char* __restrict__ ws_tiles,
                     const float* __restrict__ ws_aux, int tiles_per_chunk, unsigned char* __restrict__ bwd_tiles,
                     const float* __restrict__ h0, int n_state, const __grid_constant__ CUtensorMap tmap_o,
-                    int write_o, float* __restrict__ ht, int Tn, int H, int NT, int* status) {
+                    int write_o, float* __restrict__ ht, int Tn, int H, int NT, int* status, long long* dbg) {
+#define R7C_STAMP(n) do { if (dbg && tid == 0 && blockIdx.x == gridDim.x / 2 && c == 2) dbg[n] = clock64(); } while (0)
   extern __shared__ unsigned char smem_raw[];
   ScanSmem& sm = *reinterpret_cast<ScanSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int wq = warp & 3, hsel = warp >> 2, c0 = 32 * hsel;
   const int unit = blockIdx.x, bi = unit / H, hi = unit % H;
   const size_t ch0 = (size_t)unit * NT;
-  const int row = 16 * warp + (lane & 15);   // state row k (lanes 0-15) or token row i (lanes 16-31)
+  const int row = 16 * wq + (lane & 15);     // state row k (lanes 0-15) or token row i (lanes 16-31)
   const bool state_lane = lane < 16;
 
   if (tid == 0) {
@@ -513,7 +516,7 @@ r7c_scan_fwd_kernel(const __grid_constant__ CUtensorMap tmap_v, const unsigned c
   __syncthreads();
   tc_fence_after();
   const uint32_t tm = sm.tmem_base;
-  const uint32_t tm_p1 = tmem_addr(tm, 32 * warp, 0), tm_p2 = tmem_addr(tm, 32 * warp, 64);
+  const uint32_t tm_p1 = tmem_addr(tm, 32 * wq, c0), tm_p2 = tmem_addr(tm, 32 * wq, 64 + c0);
 
   auto issue_g1 = [&](int c) {      // tid 0
     const unsigned char* tiles = ws_tiles + (ch0 + c) * (size_t)tiles_per_chunk * TILE_BYTES;
@@ -534,30 +537,22 @@ r7c_scan_fwd_kernel(const __grid_constant__ CUtensorMap tmap_v, const unsigned c
 
   // ---- initial state: h~0 = e^{gref(chunk 0)} h0, fp32 into TMEM (lower lane halves of P2), bf16 into ht
   {
-    float x[64];
+    float x[32];
+#pragma unroll
+    for (int vv = 0; vv < 32; ++vv) x[vv] = 0.f;
     if (state_lane) {
       const float e0 = ws_aux[ch0 * AUX_FLOATS + row];
       if (n_state > 0) {
         const float* S = h0 + (size_t)(n_state == 1 ? hi : unit) * 4096;   // S[v][k], h[k][v] = S[v][k]
 #pragma unroll
-        for (int vv = 0; vv < 64; ++vv) x[vv] = e0 * S[vv * 64 + row];
-      } else {
-#pragma unroll
-        for (int vv = 0; vv < 64; ++vv) x[vv] = 0.f;
+        for (int vv = 0; vv < 32; ++vv) x[vv] = e0 * S[(c0 + vv) * 64 + row];
       }
-      tile_store_row32(sm.ht, row, 0, x);
-      tile_store_row32(sm.ht, row, 32, x + 32);
-    } else {
-#pragma unroll
-      for (int vv = 0; vv < 64; ++vv) x[vv] = 0.f;
+      tile_store_row32(sm.ht, row, c0, x);
     }
     uint32_t r[32];
 #pragma unroll
-    for (int part = 0; part < 2; ++part) {
-#pragma unroll
-      for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(x[32 * part + j]);
-      tmem_st32(tm_p2 + 32 * part, r);
-    }
+    for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(x[j]);
+    tmem_st32(tm_p2, r);
     tmem_st_wait();
   }
   fence_async_smem();
@@ -567,13 +562,14 @@ r7c_scan_fwd_kernel(const __grid_constant__ CUtensorMap tmap_v, const unsigned c
   bool ok = true;
   for (int c = 0; c < NT && ok; ++c) {
     const int t0 = c * L;
+    R7C_STAMP(48);
     // this thread's row of U (state lanes) or O1 (token lanes), straight from the workspace
-    uint4 addrow[8];
+    uint4 addrow[4];
     {
       const unsigned char* tile = ws_tiles + ((ch0 + c) * (size_t)tiles_per_chunk + (state_lane ? S_U : S_O1)) * TILE_BYTES;
 #pragma unroll
-      for (int q = 0; q < 8; ++q) addrow[q] = __ldg(reinterpret_cast<const uint4*>(tile + tile_chunk_off(row, q)));
-      if (c + 1 < NT) asm volatile("prefetch.global.L2 [%0];" ::"l"(tile + (size_t)tiles_per_chunk * TILE_BYTES + row * 128));
+      for (int q = 0; q < 4; ++q) addrow[q] = __ldg(reinterpret_cast<const uint4*>(tile + tile_chunk_off(row, 4 * hsel + q)));
+      if (c + 1 < NT && hsel == 0) asm volatile("prefetch.global.L2 [%0];" ::"l"(tile + (size_t)tiles_per_chunk * TILE_BYTES + row * 128));
     }
     // decay factors needed at the end of this chunk, fetched early
     float scale = 1.f;
@@ -584,6 +580,7 @@ r7c_scan_fwd_kernel(const __grid_constant__ CUtensorMap tmap_v, const unsigned c
     // (a) SA = W h~0, QH = q~ h~0 (P1);  H += k~^T v (P2 lower)
     if (tid == 0) {
       ok = mbar_wait(&sm.bar_g1, c & 1, status, 211);
+      R7C_STAMP(49);
       if (ok) {
         tc_fence_after();
         umma_tile<64, 64, 0, 1>(tmem_addr(tm, 0, 0), smem_u32(sm.w), smem_u32(sm.ht), false);
@@ -594,27 +591,25 @@ r7c_scan_fwd_kernel(const __grid_constant__ CUtensorMap tmap_v, const unsigned c
     }
     ok = ok && mbar_wait(&sm.bar_a, c & 1, status, 212);
     tc_fence_after();
+    R7C_STAMP(50);
     if (tid == 0 && ok && c + 1 < NT) issue_g1(c + 1);     // group 1 has been read: request the next chunk's
-    float keep[64];     // token lanes: q~ h~0 + O1
+    float keep[32];     // token lanes: q~ h~0 + O1
     if (ok) {
+      uint32_t r[32];
+      tmem_ld32(tm_p1, r);
+      tmem_ld_wait();
+      float add[32];
 #pragma unroll
-      for (int part = 0; part < 2; ++part) {
-        uint32_t r[32];
-        tmem_ld32(tm_p1 + 32 * part, r);
-        tmem_ld_wait();
-        float add[32];
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const uint4 u = addrow[4 * part + q];
-          add[8 * q + 0] = bf16_lo(u.x); add[8 * q + 1] = bf16_hi(u.x);
-          add[8 * q + 2] = bf16_lo(u.y); add[8 * q + 3] = bf16_hi(u.y);
-          add[8 * q + 4] = bf16_lo(u.z); add[8 * q + 5] = bf16_hi(u.z);
-          add[8 * q + 6] = bf16_lo(u.w); add[8 * q + 7] = bf16_hi(u.w);
-        }
-#pragma unroll
-        for (int j = 0; j < 32; ++j) keep[32 * part + j] = __uint_as_float(r[j]) + add[j];
-        if (state_lane) tile_store_row32(sm.sa, row, 32 * part, keep + 32 * part);   // sa = W h~0 + U
+      for (int q = 0; q < 4; ++q) {
+        const uint4 u = addrow[q];
+        add[8 * q + 0] = bf16_lo(u.x); add[8 * q + 1] = bf16_hi(u.x);
+        add[8 * q + 2] = bf16_lo(u.y); add[8 * q + 3] = bf16_hi(u.y);
+        add[8 * q + 4] = bf16_lo(u.z); add[8 * q + 5] = bf16_hi(u.z);
+        add[8 * q + 6] = bf16_lo(u.w); add[8 * q + 7] = bf16_hi(u.w);
       }
+#pragma unroll
+      for (int j = 0; j < 32; ++j) keep[j] = __uint_as_float(r[j]) + add[j];
+      if (state_lane) tile_store_row32(sm.sa, row, c0, keep);   // sa = W h~0 + U
     }
     fence_async_smem();
     tc_fence_before();
@@ -626,8 +621,10 @@ r7c_scan_fwd_kernel(const __grid_constant__ CUtensorMap tmap_v, const unsigned c
       bulk_commit();
     }
     // (c) H += b~^T sa (P2 lower);  OQ = A_qb sa (P2 upper)
+    R7C_STAMP(51);
     if (tid == 0 && ok) {
       ok = mbar_wait(&sm.bar_g2, c & 1, status, 214);
+      R7C_STAMP(52);
       if (ok) {
         tc_fence_after();
         umma_tile<64, 64, 1, 1>(tmem_addr(tm, 0, 64), smem_u32(sm.bt), smem_u32(sm.sa), true);
@@ -637,46 +634,46 @@ r7c_scan_fwd_kernel(const __grid_constant__ CUtensorMap tmap_v, const unsigned c
     }
     ok = ok && mbar_wait(&sm.bar_c, c & 1, status, 213);
     tc_fence_after();
+    R7C_STAMP(53);
     if (tid == 0 && ok && c + 1 < NT) issue_g2(c + 1);     // group 2 has been read
     if (bwd_tiles) {                                  // ht / sa are rewritten below and in the next chunk
       if (tid == 0) bulk_wait_read();
       __syncthreads();
     }
+    R7C_STAMP(54);
     if (ok) {
       const bool last = c + 1 == NT;
+      uint32_t r[32];
+      tmem_ld32(tm_p2, r);
+      tmem_ld_wait();
+      float x[32];
+      if (state_lane) {
+        if (bwd_tiles) {
 #pragma unroll
-      for (int part = 0; part < 2; ++part) {
-        uint32_t r[32];
-        tmem_ld32(tm_p2 + 32 * part, r);
-        tmem_ld_wait();
-        float x[32];
-        if (state_lane) {
-          if (bwd_tiles) {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) x[j] = __uint_as_float(r[j]);
-            tile_store_row32(sm.xt, row, 32 * part, x);
-          }
-#pragma unroll
-          for (int j = 0; j < 32; ++j) { x[j] = __uint_as_float(r[j]) * scale; r[j] = __float_as_uint(x[j]); }
-          if (!last) {
-            tile_store_row32(sm.ht, row, 32 * part, x);
-          } else if (ht) {
-            float* S = ht + (size_t)unit * 4096;
-#pragma unroll
-            for (int j = 0; j < 32; ++j) S[(32 * part + j) * 64 + row] = x[j];
-          }
-        } else {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) x[j] = __uint_as_float(r[j]) + keep[32 * part + j];
-          if (write_o) tile_store_row32(sm.ot[c & 1], row, 32 * part, x);
+          for (int j = 0; j < 32; ++j) x[j] = __uint_as_float(r[j]);
+          tile_store_row32(sm.xt, row, c0, x);
         }
-        tmem_st32(tm_p2 + 32 * part, r);   // state lanes: rescaled state; token lanes: unchanged
+#pragma unroll
+        for (int j = 0; j < 32; ++j) { x[j] = __uint_as_float(r[j]) * scale; r[j] = __float_as_uint(x[j]); }
+        if (!last) {
+          tile_store_row32(sm.ht, row, c0, x);
+        } else if (ht) {
+          float* S = ht + (size_t)unit * 4096;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) S[(c0 + j) * 64 + row] = x[j];
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) x[j] = __uint_as_float(r[j]) + keep[j];
+        if (write_o) tile_store_row32(sm.ot[c & 1], row, c0, x);
       }
+      tmem_st32(tm_p2, r);   // state lanes: rescaled state; token lanes: unchanged
       tmem_st_wait();
     }
     fence_async_smem();
     tc_fence_before();
     ok = __syncthreads_and(ok);
+    R7C_STAMP(55);
     if (bwd_tiles && tid == 0 && ok) {
       bulk_store(bwd_tiles + ((ch0 + c) * (size_t)tiles_per_chunk + S_X) * TILE_BYTES, sm.xt, TILE_BYTES);
       bulk_commit();
@@ -686,7 +683,9 @@ r7c_scan_fwd_kernel(const __grid_constant__ CUtensorMap tmap_v, const unsigned c
       bulk_commit();
       bulk_wait_read_1();                // the buffer of the previous chunk is free again
     }
+    R7C_STAMP(56);
   }
+#undef R7C_STAMP
   if (tid == 0) bulk_wait_all();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tm, 128);
@@ -730,8 +729,9 @@ int launch_rwkv7_chunked_fwd(const void* r, const void* w, const void* k, const 
     const int smem = (int)sizeof(ScanSmem) + 1024;
     if (cuda_ok(cudaFuncSetAttribute(r7c_scan_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem))) return RWKVB200_E_CUDA;
     ProfScope prof("r7c_scan_fwd_kernel", st);
-    r7c_scan_fwd_kernel<<<B * H, 128, smem, st>>>(tmap_v, ws.tiles, ws.aux, tpc, keep_for_bwd ? ws.tiles : nullptr,
-                                                  h0, n_state, tmap_o, o ? 1 : 0, ht, Tn, H, NT, status);
+    r7c_scan_fwd_kernel<<<B * H, 256, smem, st>>>(tmap_v, ws.tiles, ws.aux, tpc, keep_for_bwd ? ws.tiles : nullptr,
+                                                  h0, n_state, tmap_o, o ? 1 : 0, ht, Tn, H, NT, status,
+                                                  debug_stamp_buffer());
   }
   return check_launch();
 }

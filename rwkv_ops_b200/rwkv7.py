@@ -29,10 +29,14 @@ def _workspace(nbytes: int, device) -> Optional[torch.Tensor]:
     return torch.empty(nbytes, dtype=torch.uint8, device=device) if nbytes else None
 
 
-def _keep_limit_bytes() -> int:
-    """Largest per-call tile store (MiB, ``RWKV_OPS_B200_KEEP_LIMIT_MB``) that a training forward may
-    hand to its backward instead of having the backward recompute the forward."""
-    return int(os.environ.get("RWKV_OPS_B200_KEEP_LIMIT_MB", "16384")) << 20
+def _keep_limit_bytes(device) -> int:
+    """Largest per-call tile store that a training forward may hand to its backward instead of having
+    the backward recompute the forward: ``RWKV_OPS_B200_KEEP_LIMIT_MB`` (MiB) when set, else a quarter
+    of the device's memory (about 45 GiB on a B200)."""
+    env = os.environ.get("RWKV_OPS_B200_KEEP_LIMIT_MB")
+    if env is not None:
+        return int(env) << 20
+    return torch.cuda.get_device_properties(device).total_memory // 4
 
 
 # --------------------------------------------------------------------------------------------
@@ -289,7 +293,7 @@ def generalized_delta_rule(
     keep = False
     if needs_grad and T > 1 and cdt == torch.bfloat16 and algo in (_lib.ALGO_AUTO, _lib.ALGO_CHUNKED):
         nws = _lib.load().rwkvb200_rwkv7_fwd_workspace_bytes(B, T, H, HEAD_SIZE, _lib.BF16, algo | _lib.ALGO_KEEP)
-        keep = nws <= _keep_limit_bytes()
+        keep = nws <= _keep_limit_bytes(r_.device)
     if keep:
         o, ht, _ = _rwkv7_fwd_keep(r_, w_, k_, v_, a_, b_, h0, bool(head_first), algo)
     else:
