@@ -88,6 +88,16 @@ int rwkvb200_rwkv7_step(const void* r, const void* w, const void* k, const void*
                         const float* state_in, int n_state, float* state_out, void* o,
                         int B, int H, int head_size, int dtype, void* stream);
 
+/* One decode step in place on a state the caller keeps on the device across steps:
+ * state [B,H,64,64] (value index before key index, like the reference's final_state), element type
+ * state_dtype = RWKVB200_F32 (the reference's state type; same arithmetic as rwkvb200_rwkv7_step) or
+ * RWKVB200_BF16 (half the state traffic; the state is rounded to bfloat16 after every token, which the
+ * reference does not do).  Token tensors [B,H,64] of `dtype`.  No counterpart in the reference, whose
+ * T == 1 call allocates a new state every step (native_keras_op.py:60-95). */
+int rwkvb200_rwkv7_decode_step(const void* r, const void* w, const void* k, const void* v,
+                               const void* a, const void* b, void* state, int state_dtype, void* o,
+                               int B, int H, int head_size, int dtype, void* stream);
+
 size_t rwkvb200_rwkv7_fwd_workspace_bytes(int B, int T, int H, int head_size, int dtype, int algo);
 
 int rwkvb200_rwkv7_fwd(const void* r, const void* w, const void* k, const void* v,

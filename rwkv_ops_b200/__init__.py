@@ -4,10 +4,12 @@ Exports the same names as the reference package (``rwkv_ops/__init__.py:22-29``)
 ``generalized_delta_rule``, ``rwkv7_op``, ``RWKV7_USE_KERNEL``, ``get_generalized_delta_rule``,
 ``RWKV6_OP`` and ``get_rwkv6_kernel``.  The ``KERNEL_TYPE`` / ``KERAS_BACKEND`` environment
 variables of the reference are not consulted: there is one implementation, hand-written CUDA
-behind a C ABI, and it raises if its shared library is missing.
+behind a C ABI, and it raises if its shared library is missing.  ``Rwkv7DecodeState`` (in-place
+single-token decoding) has no counterpart in the reference.
 """
 from .rwkv7 import generalized_delta_rule, get_generalized_delta_rule
 from .rwkv6 import RWKVKernelOperator, get_rwkv6_kernel
+from .decode import Rwkv7DecodeState
 
 __version__ = "0.1"
 
@@ -23,4 +25,5 @@ __all__ = [
     "RWKV6_OP",
     "get_rwkv6_kernel",
     "RWKVKernelOperator",
+    "Rwkv7DecodeState",
 ]

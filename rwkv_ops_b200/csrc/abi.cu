@@ -78,6 +78,18 @@ int rwkvb200_rwkv7_step(const void* r, const void* w, const void* k, const void*
                            (cudaStream_t)stream);
 }
 
+int rwkvb200_rwkv7_decode_step(const void* r, const void* w, const void* k, const void* v,
+                               const void* a, const void* b, void* state, int state_dtype, void* o,
+                               int B, int H, int head_size, int dtype, void* stream) {
+  int e = check_common(B, 1, H, head_size, dtype);
+  if (e) return e;
+  if (state_dtype != RWKVB200_F32 && state_dtype != RWKVB200_BF16) return RWKVB200_E_DTYPE;
+  if (!r || !w || !k || !v || !a || !b || !state || !o) return RWKVB200_E_NULL;
+  const void* ps[] = {r, w, k, v, a, b, state, o};
+  for (const void* p : ps) if (!aligned16(p)) return RWKVB200_E_ALIGN;
+  return launch_rwkv7_decode_step(r, w, k, v, a, b, state, state_dtype, o, B, H, dtype, (cudaStream_t)stream);
+}
+
 size_t rwkvb200_rwkv7_fwd_workspace_bytes(int B, int T, int H, int head_size, int dtype, int algo) {
   if (check_common(B, T, H, head_size, dtype)) return 0;
   if (resolve_r7_algo(algo, dtype) == RWKVB200_ALGO_CHUNKED)

@@ -108,6 +108,8 @@ struct ProfScope {
   }
 
 // Kernel launchers implemented in the .cu files (internal linkage across the library only).
+int launch_rwkv7_decode_step(const void* r, const void* w, const void* k, const void* v, const void* a, const void* b,
+                             void* state, int state_dtype, void* o, int B, int H, int dtype, cudaStream_t st);
 int launch_rwkv7_step(const void* r, const void* w, const void* k, const void* v, const void* a, const void* b,
                       const float* s_in, int n_state, float* s_out, void* o, int B, int H, int dtype,
                       cudaStream_t st);

@@ -93,7 +93,8 @@ __global__ void __launch_bounds__(256, 2)
 wkv6c_fwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __restrict__ v, const T* __restrict__ w,
                  const float* __restrict__ u, const float* __restrict__ s0, int n_state,
                  const int32_t* __restrict__ smap, T* __restrict__ y, float* __restrict__ sT,
-                 float* __restrict__ states, int Tn, int H, int* status) {
+                 float* __restrict__ states, int Tn, int H, int* status, long long* dbg) {
+#define W6C_STAMP(n) do { if (dbg && tid == 0 && blockIdx.x == gridDim.x / 2 && c == 2) dbg[n] = clock64(); } while (0)
   extern __shared__ unsigned char smem_raw[];
   FwdSmem& sm = *reinterpret_cast<FwdSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -147,6 +148,7 @@ wkv6c_fwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
   for (int c = 0; c < NT && ok; ++c) {
     const int t0 = c * L;
     const uint32_t par = c & 1;
+    W6C_STAMP(0);
     // ---- the w and v rows of the chunk are requested together (r and k follow after the prefix sums:
     // holding them across the barriers would spill at two CTAs per SM)
     float4 gw[4], vv4[4];
@@ -171,6 +173,7 @@ wkv6c_fwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
       store_split4(sm.vt[0], sm.vt[1], row, 4 * c4, vv4[n]);
     }
     __syncthreads();
+    W6C_STAMP(1);
     {
       const int ch = tid & 63, quarter = tid >> 6;
       float gv[16];
@@ -186,29 +189,8 @@ wkv6c_fwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
       for (int j = 0; j < 16; ++j) sm.gs[(16 * quarter + j) * NROW + ch] = gv[j] + add;   // prefix inside each half
     }
     __syncthreads();
-    // decay factors of the state rows: e^{gref} of this chunk scales the incoming state, e^{glast-gref} the outgoing
-    float e0 = 1.f, dlast = 1.f;
-    if (!tok_lane) {
-      e0 = __expf(fmaxf(sm.qtot[0][srow] + sm.qtot[1][srow], -EXP_CLAMP));
-      dlast = __expf(fmaxf(sm.qtot[2][srow] + sm.qtot[3][srow], -EXP_CLAMP));
-    }
-    // ---- S~0 = e^{gref} S0: fp32 into TMEM (upper lane halves), hi/lo bf16 tiles for the r~ S~0 product
-    {
-      if (!tok_lane && states) {
-        float* dst = states + (((size_t)unit * (NT + 1) + c) * HS + srow) * HS + 32 * hsel;
-#pragma unroll
-        for (int j = 0; j < 32; j += 4)
-          *reinterpret_cast<float4*>(dst + j) = make_float4(sreg[j], sreg[j + 1], sreg[j + 2], sreg[j + 3]);
-      }
-      uint32_t rr[32];
-      float x[32];
-#pragma unroll
-      for (int j = 0; j < 32; ++j) { x[j] = sreg[j] * e0; rr[j] = __float_as_uint(x[j]); }
-      if (!tok_lane) store_split_row32(sm.st[0], sm.st[1], srow, 32 * hsel, x);
-      tmem_st32(tm_ys, rr);            // lower halves (y) get zeros: overwritten by the first product
-      tmem_st_wait();
-    }
-    // ---- pass RK: scaled r, k (split hi/lo) and the diagonal term
+    W6C_STAMP(2);
+    // the r and k rows are requested here so that their latency passes under the state phase
     float4 rr4[4], kk4[4];
 #pragma unroll
     for (int n = 0; n < 4; ++n) {
@@ -220,6 +202,26 @@ wkv6c_fwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
         rr4[n] = load4(r + off); kk4[n] = load4(k + off);
       }
     }
+    // decay factors of the state rows: e^{gref} of this chunk scales the incoming state, e^{glast-gref} the outgoing
+    float e0 = 1.f, dlast = 1.f;
+    if (!tok_lane) {
+      e0 = __expf(fmaxf(sm.qtot[0][srow] + sm.qtot[1][srow], -EXP_CLAMP));
+      dlast = __expf(fmaxf(sm.qtot[2][srow] + sm.qtot[3][srow], -EXP_CLAMP));
+    }
+    // ---- S~0 = e^{gref} S0 stays in registers (fp32); hi/lo bf16 tiles for the r~ S~0 product
+    if (!tok_lane) {
+      if (states) {
+        float* dst = states + (((size_t)unit * (NT + 1) + c) * HS + srow) * HS + 32 * hsel;
+#pragma unroll
+        for (int j = 0; j < 32; j += 4)
+          *reinterpret_cast<float4*>(dst + j) = make_float4(sreg[j], sreg[j + 1], sreg[j + 2], sreg[j + 3]);
+      }
+#pragma unroll
+      for (int j = 0; j < 32; ++j) sreg[j] *= e0;
+      store_split_row32(sm.st[0], sm.st[1], srow, 32 * hsel, sreg);
+    }
+    W6C_STAMP(3);
+    // ---- pass RK: scaled r, k (split hi/lo) and the diagonal term
 #pragma unroll
     for (int n = 0; n < 4; ++n) {
       const int e = tid + 256 * n, row = e >> 4;
@@ -264,16 +266,18 @@ wkv6c_fwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
     tc_fence_before();
     __syncthreads();
 
-    // ---- batch 1: r~ k~^T (columns 0..63), y = r~ S~0 (columns 64.., lower), state += k~^T v (upper)
+    W6C_STAMP(4);
+    // ---- batch 1: r~ k~^T (columns 0..63), y = r~ S~0 (columns 64.., lower), k~^T v (upper)
     if (tid == 0) {
       tc_fence_after();
       umma_split<64, 64, 0, 0>(tmem_addr(tm, 0, 0), smem_u32(sm.rt[0]), smem_u32(sm.kt[0]), false);
       umma_split<64, 64, 0, 1>(tmem_addr(tm, 0, 64), smem_u32(sm.rt[0]), smem_u32(sm.st[0]), false);
-      umma_split<64, 64, 1, 1>(tmem_addr(tm, 16, 64), smem_u32(sm.kt[0]), smem_u32(sm.vt[0]), true);
+      umma_split<64, 64, 1, 1>(tmem_addr(tm, 16, 64), smem_u32(sm.kt[0]), smem_u32(sm.vt[0]), false);
       umma_commit(&sm.bar_1);
     }
     ok = mbar_wait(&sm.bar_1, par, status, 401) && ok;
     tc_fence_after();
+    W6C_STAMP(5);
     if (ok) {
       // A rows (lower halves of columns 0..63): strictly lower part plus the diagonal term, split hi/lo
       uint32_t rr[32];
@@ -289,18 +293,19 @@ wkv6c_fwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
         }
         store_split_row32(sm.at[0], sm.at[1], srow, 32 * hsel, x);
       }
-      // state rows (upper halves of columns 64..127): S_L = e^{glast-gref} (S~0 + k~^T v)
+      // state rows (k~^T v on the upper halves of columns 64..127): S_L = e^{glast-gref} (S~0 + k~^T v)
       tmem_ld32(tm_ys, rr);
       tmem_ld_wait();
       if (!tok_lane) {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) sreg[j] = __uint_as_float(rr[j]) * dlast;
+        for (int j = 0; j < 32; ++j) sreg[j] = (sreg[j] + __uint_as_float(rr[j])) * dlast;
       }
     }
     fence_async_smem();
     tc_fence_before();
     ok = __syncthreads_and(ok);
 
+    W6C_STAMP(6);
     // ---- batch 2: y += A v
     if (tid == 0 && ok) {
       tc_fence_after();
@@ -309,6 +314,7 @@ wkv6c_fwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
     }
     ok = mbar_wait(&sm.bar_2, par, status, 402) && ok;
     tc_fence_after();
+    W6C_STAMP(7);
     if (ok) {
       uint32_t rr[32];
       tmem_ld32(tm_ys, rr);
@@ -323,6 +329,7 @@ wkv6c_fwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
     }
     tc_fence_before();
     ok = __syncthreads_and(ok);
+    W6C_STAMP(8);
     if (y && ok) {
 #pragma unroll
       for (int n = 0; n < 4; ++n) {
@@ -333,7 +340,9 @@ wkv6c_fwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
       }
     }
     __syncthreads();
+    W6C_STAMP(9);
   }
+#undef W6C_STAMP
   // ---- final state
   if (!tok_lane && ok) {
     if (sT) {
@@ -756,7 +765,7 @@ int launch_wkv6_chunked_fwd(const void* r, const void* k, const void* v, const v
     if (cuda_ok(cudaFuncSetAttribute(wkv6c_fwd_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)))
       return RWKVB200_E_CUDA;
     wkv6c_fwd_kernel<T><<<B * H, 256, smem, st>>>((const T*)r, (const T*)k, (const T*)v, (const T*)w, u, s0, n_state,
-                                                   smap, (T*)y, sT, states, Tn, H, status));
+                                                   smap, (T*)y, sT, states, Tn, H, status, debug_stamp_buffer()));
   return check_launch();
 }
 

@@ -1,6 +1,7 @@
 """Device-timed micro-benchmarks of the individual operators (CUDA events, inputs resident in HBM).
 
     python -m rwkv_ops_b200.microbench step  [--B 256 --H 64 --steps 50 --dtype bf16]
+    python -m rwkv_ops_b200.microbench step  --state-dtype bf16      (in place, bfloat16 state)
     python -m rwkv_ops_b200.microbench wkv6  [--B 16 --T 4096 --H 32 --steps 5]
     python -m rwkv_ops_b200.microbench rwkv7 [--B 8 --T 4096 --H 32 --steps 5 --dtype bf16 --algo auto]
 
@@ -58,8 +59,28 @@ def bench_step(a):
         assert rc == 0
         i[0] += 1
 
-    ms, kern = _time(fn, a.steps)
     es = torch.finfo(dt).bits // 8
+    if a.state_dtype:      # in place on one state buffer (float32 or bfloat16)
+        sdt = DT[a.state_dtype]
+        inplace = state.to(sdt)
+        scode = _lib.dtype_code(sdt)
+        ss = torch.finfo(sdt).bits // 8
+
+        def fn():   # noqa: F811
+            d = ds[i[0] % n_in]
+            rc = lib.rwkvb200_rwkv7_decode_step(*[d[n].data_ptr() for n in "rwkvab"], inplace.data_ptr(), scode,
+                                                o.data_ptr(), a.B, a.H, 64, code,
+                                                torch.cuda.current_stream().cuda_stream)
+            assert rc == 0
+            i[0] += 1
+
+        ms, kern = _time(fn, a.steps)
+        nbytes = a.B * a.H * (2 * 64 * 64 * ss + 7 * 64 * es)
+        return {"op": "rwkv7_decode_step", "B": a.B, "H": a.H, "dtype": a.dtype, "state_dtype": a.state_dtype,
+                "us_per_step": 1e3 * ms, "algorithmic_bytes": nbytes, "GBps": nbytes / (ms / 1e3) / 1e9,
+                "state_bytes_vs_l2": "state updated in place, %.0f MB against the 126 MB L2" % (a.B * a.H * 4096 * ss / 1e6),
+                "kernel_ms": kern}
+    ms, kern = _time(fn, a.steps)
     nbytes = a.B * a.H * (2 * 64 * 64 * 4 + 7 * 64 * es)
     return {"op": "rwkv7_step", "B": a.B, "H": a.H, "dtype": a.dtype, "us_per_step": 1e3 * ms,
             "algorithmic_bytes": nbytes, "GBps": nbytes / (ms / 1e3) / 1e9,
@@ -119,6 +140,8 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--dtype", default=None)
     ap.add_argument("--algo", default="auto")
+    ap.add_argument("--state-dtype", default=None, choices=["f32", "bf16"],
+                    help="step: decode in place on one state buffer of this type (rwkvb200_rwkv7_decode_step)")
     ap.add_argument("--fwd-only", action="store_true")
     a = ap.parse_args()
     defaults = {"step": (256, 64, "bf16"), "wkv6": (16, 32, "f32"), "rwkv7": (8, 32, "bf16")}[a.op]
