@@ -475,30 +475,46 @@ r7c_intra_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ w, con
 // scan kernel: grid = B*H, 256 threads, chunks in order, fp32 state in TMEM.  Warp w reads TMEM lanes
 // 32*(w&3)..; the two warps that share a lane window take 32 of the 64 columns each (hsel = w>>2).
 // ---------------------------------------------------------------------------------------------
-// Operand tiles are single-buffered: each group is requested for the next chunk the moment the MMAs
-// that read it have completed, which leaves it at least half a chunk step to arrive.  U and O1 are only
-// added row by row, so they never enter shared memory: every thread fetches its row into registers.
-// 11 tiles = 88 KB, so two CTAs (two sequences) share an SM.
+// Operand tiles come in two groups, each requested again the moment the MMAs that read it have completed.
+// STAGES = 1 (single-buffered, 11 tiles = 88 KB): two CTAs (two sequences) share an SM, the choice when
+// there are more sequences than SMs; U and O1, which are only added row by row, do not enter shared
+// memory: every thread fetches its row into registers at the top of a chunk.  STAGES = 2 (21 tiles): one
+// CTA per SM with the groups of chunk c + 2 requested during chunk c and U, O1 staged with group 1, for
+// the case of few sequences, where nothing else on the SM covers a load latency.
+template <int STAGES> struct ScanGroup1 {
+  unsigned char qt[TILE_BYTES], kt[TILE_BYTES];   // read by step a: q~, k~ (adjacent slots)
+  unsigned char w[TILE_BYTES], v[TILE_BYTES];     //                 W, v (TMA)
+};
+template <> struct ScanGroup1<2> {
+  unsigned char qt[TILE_BYTES], kt[TILE_BYTES];
+  unsigned char o1[TILE_BYTES], w[TILE_BYTES], u[TILE_BYTES];   // adjacent slots O1, W, U: one copy
+  unsigned char v[TILE_BYTES];
+};
+struct ScanGroup2 {
+  unsigned char bt[TILE_BYTES], aqb[TILE_BYTES];  // read by step c: b~, A_qb (adjacent slots)
+};
+template <int STAGES>
 struct ScanSmem {
-  unsigned char qt[TILE_BYTES], kt[TILE_BYTES];   // group 1 (read by step a): q~, k~ (adjacent slots)
-  unsigned char w[TILE_BYTES], v[TILE_BYTES];     //                            W, v (TMA)
-  unsigned char bt[TILE_BYTES], aqb[TILE_BYTES];  // group 2 (read by step c): b~, A_qb (adjacent slots)
+  ScanGroup1<STAGES> g1[STAGES];
+  ScanGroup2 g2[STAGES];
   unsigned char ht[TILE_BYTES];             // h~0 as bf16, [k][v]
   unsigned char sa[TILE_BYTES];             // sa as bf16, [token][v]
   unsigned char xt[TILE_BYTES];             // X = h~0 + k~^T v + b~^T sa as bf16 (kept for the backward)
   unsigned char ot[2][TILE_BYTES];          // output rows of a chunk, staged for a TMA store
-  uint64_t bar_g1, bar_g2, bar_a, bar_c;
+  uint64_t bar_g1[STAGES], bar_g2[STAGES], bar_a, bar_c;
   uint32_t tmem_base;
 };
 
-__global__ void __launch_bounds__(256, 2)
+template <int STAGES>
+__global__ void __launch_bounds__(256, 3 - STAGES)
 r7c_scan_fwd_kernel(const __grid_constant__ CUtensorMap tmap_v, const unsigned char* __restrict__ ws_tiles,
                     const float* __restrict__ ws_aux, int tiles_per_chunk, unsigned char* __restrict__ bwd_tiles,
                     const float* __restrict__ h0, int n_state, const __grid_constant__ CUtensorMap tmap_o,
                     int write_o, float* __restrict__ ht, int Tn, int H, int NT, int* status, long long* dbg) {
 #define R7C_STAMP(n) do { if (dbg && tid == 0 && blockIdx.x == gridDim.x / 2 && c == 2) dbg[n] = clock64(); } while (0)
   extern __shared__ unsigned char smem_raw[];
-  ScanSmem& sm = *reinterpret_cast<ScanSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  ScanSmem<STAGES>& sm =
+      *reinterpret_cast<ScanSmem<STAGES>*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int wq = warp & 3, hsel = warp >> 2, c0 = 32 * hsel;
   const int unit = blockIdx.x, bi = unit / H, hi = unit % H;
@@ -507,7 +523,7 @@ r7c_scan_fwd_kernel(const __grid_constant__ CUtensorMap tmap_v, const unsigned c
   const bool state_lane = lane < 16;
 
   if (tid == 0) {
-    mbar_init(&sm.bar_g1, 1); mbar_init(&sm.bar_g2, 1);
+    for (int i = 0; i < STAGES; ++i) { mbar_init(&sm.bar_g1[i], 1); mbar_init(&sm.bar_g2[i], 1); }
     mbar_init(&sm.bar_a, 1); mbar_init(&sm.bar_c, 1);
     fence_mbar_init();
   }
@@ -520,19 +536,22 @@ r7c_scan_fwd_kernel(const __grid_constant__ CUtensorMap tmap_v, const unsigned c
 
   auto issue_g1 = [&](int c) {      // tid 0
     const unsigned char* tiles = ws_tiles + (ch0 + c) * (size_t)tiles_per_chunk * TILE_BYTES;
-    mbar_expect_tx(&sm.bar_g1, 4 * TILE_BYTES);
-    bulk_load(sm.qt, tiles + S_QT * TILE_BYTES, 2 * TILE_BYTES, &sm.bar_g1);
-    bulk_load(sm.w, tiles + S_W * TILE_BYTES, TILE_BYTES, &sm.bar_g1);
-    tma_load_4d(sm.v, &tmap_v, &sm.bar_g1, 0, c * L, hi, bi);
+    ScanGroup1<STAGES>& g = sm.g1[c % STAGES];
+    uint64_t* bar = &sm.bar_g1[c % STAGES];
+    mbar_expect_tx(bar, (STAGES == 2 ? 6 : 4) * TILE_BYTES);
+    bulk_load(g.qt, tiles + S_QT * TILE_BYTES, 2 * TILE_BYTES, bar);
+    if constexpr (STAGES == 2) bulk_load(g.o1, tiles + S_O1 * TILE_BYTES, 3 * TILE_BYTES, bar);
+    else                       bulk_load(g.w, tiles + S_W * TILE_BYTES, TILE_BYTES, bar);
+    tma_load_4d(g.v, &tmap_v, bar, 0, c * L, hi, bi);
   };
   auto issue_g2 = [&](int c) {      // tid 0
     const unsigned char* tiles = ws_tiles + (ch0 + c) * (size_t)tiles_per_chunk * TILE_BYTES;
-    mbar_expect_tx(&sm.bar_g2, 2 * TILE_BYTES);
-    bulk_load(sm.bt, tiles + S_BT * TILE_BYTES, 2 * TILE_BYTES, &sm.bar_g2);
+    uint64_t* bar = &sm.bar_g2[c % STAGES];
+    mbar_expect_tx(bar, 2 * TILE_BYTES);
+    bulk_load(sm.g2[c % STAGES].bt, tiles + S_BT * TILE_BYTES, 2 * TILE_BYTES, bar);
   };
   if (tid == 0) {
-    issue_g1(0);
-    issue_g2(0);
+    for (int c = 0; c < STAGES && c < NT; ++c) { issue_g1(c); issue_g2(c); }
   }
 
   // ---- initial state: h~0 = e^{gref(chunk 0)} h0, fp32 into TMEM (lower lane halves of P2), bf16 into ht
@@ -565,7 +584,7 @@ r7c_scan_fwd_kernel(const __grid_constant__ CUtensorMap tmap_v, const unsigned c
     R7C_STAMP(48);
     // this thread's row of U (state lanes) or O1 (token lanes), straight from the workspace
     uint4 addrow[4];
-    {
+    if constexpr (STAGES == 1) {
       const unsigned char* tile = ws_tiles + ((ch0 + c) * (size_t)tiles_per_chunk + (state_lane ? S_U : S_O1)) * TILE_BYTES;
 #pragma unroll
       for (int q = 0; q < 4; ++q) addrow[q] = __ldg(reinterpret_cast<const uint4*>(tile + tile_chunk_off(row, 4 * hsel + q)));
@@ -579,21 +598,29 @@ r7c_scan_fwd_kernel(const __grid_constant__ CUtensorMap tmap_v, const unsigned c
     }
     // (a) SA = W h~0, QH = q~ h~0 (P1);  H += k~^T v (P2 lower)
     if (tid == 0) {
-      ok = mbar_wait(&sm.bar_g1, c & 1, status, 211);
+      ScanGroup1<STAGES>& g = sm.g1[c % STAGES];
+      ok = mbar_wait(&sm.bar_g1[c % STAGES], (c / STAGES) & 1, status, 211);
       R7C_STAMP(49);
       if (ok) {
         tc_fence_after();
-        umma_tile<64, 64, 0, 1>(tmem_addr(tm, 0, 0), smem_u32(sm.w), smem_u32(sm.ht), false);
-        umma_tile<64, 64, 0, 1>(tmem_addr(tm, 16, 0), smem_u32(sm.qt), smem_u32(sm.ht), false);
-        umma_tile<64, 64, 1, 1>(tmem_addr(tm, 0, 64), smem_u32(sm.kt), smem_u32(sm.v), true);
+        umma_tile<64, 64, 0, 1>(tmem_addr(tm, 0, 0), smem_u32(g.w), smem_u32(sm.ht), false);
+        umma_tile<64, 64, 0, 1>(tmem_addr(tm, 16, 0), smem_u32(g.qt), smem_u32(sm.ht), false);
+        umma_tile<64, 64, 1, 1>(tmem_addr(tm, 0, 64), smem_u32(g.kt), smem_u32(g.v), true);
         umma_commit(&sm.bar_a);
       }
     }
     ok = ok && mbar_wait(&sm.bar_a, c & 1, status, 212);
     tc_fence_after();
     R7C_STAMP(50);
-    if (tid == 0 && ok && c + 1 < NT) issue_g1(c + 1);     // group 1 has been read: request the next chunk's
+    // group 1 has been read by the MMAs: request the next (the staged O1 / U rows are still to be read)
+    if (STAGES == 1 && tid == 0 && ok && c + STAGES < NT) issue_g1(c + STAGES);
     float keep[32];     // token lanes: q~ h~0 + O1
+    if constexpr (STAGES == 2) {      // the staged O1 / U rows: observe the arrival of group 1 before reading them
+      ok = ok && mbar_wait(&sm.bar_g1[c % STAGES], (c / STAGES) & 1, status, 215);
+      const unsigned char* tile = state_lane ? sm.g1[c % STAGES].u : sm.g1[c % STAGES].o1;
+#pragma unroll
+      for (int q = 0; q < 4; ++q) addrow[q] = *reinterpret_cast<const uint4*>(tile + tile_chunk_off(row, 4 * hsel + q));
+    }
     if (ok) {
       uint32_t r[32];
       tmem_ld32(tm_p1, r);
@@ -614,6 +641,7 @@ r7c_scan_fwd_kernel(const __grid_constant__ CUtensorMap tmap_v, const unsigned c
     fence_async_smem();
     tc_fence_before();
     ok = __syncthreads_and(ok);
+    if (STAGES == 2 && tid == 0 && ok && c + STAGES < NT) issue_g1(c + STAGES);
     if (bwd_tiles && tid == 0 && ok) {   // the backward needs sa and h~0 of every chunk
       unsigned char* dst = bwd_tiles + (ch0 + c) * (size_t)tiles_per_chunk * TILE_BYTES;
       bulk_store(dst + S_SA * TILE_BYTES, sm.sa, TILE_BYTES);
@@ -623,19 +651,20 @@ r7c_scan_fwd_kernel(const __grid_constant__ CUtensorMap tmap_v, const unsigned c
     // (c) H += b~^T sa (P2 lower);  OQ = A_qb sa (P2 upper)
     R7C_STAMP(51);
     if (tid == 0 && ok) {
-      ok = mbar_wait(&sm.bar_g2, c & 1, status, 214);
+      ScanGroup2& g = sm.g2[c % STAGES];
+      ok = mbar_wait(&sm.bar_g2[c % STAGES], (c / STAGES) & 1, status, 214);
       R7C_STAMP(52);
       if (ok) {
         tc_fence_after();
-        umma_tile<64, 64, 1, 1>(tmem_addr(tm, 0, 64), smem_u32(sm.bt), smem_u32(sm.sa), true);
-        umma_tile<64, 64, 0, 1>(tmem_addr(tm, 16, 64), smem_u32(sm.aqb), smem_u32(sm.sa), false);
+        umma_tile<64, 64, 1, 1>(tmem_addr(tm, 0, 64), smem_u32(g.bt), smem_u32(sm.sa), true);
+        umma_tile<64, 64, 0, 1>(tmem_addr(tm, 16, 64), smem_u32(g.aqb), smem_u32(sm.sa), false);
         umma_commit(&sm.bar_c);
       }
     }
     ok = ok && mbar_wait(&sm.bar_c, c & 1, status, 213);
     tc_fence_after();
     R7C_STAMP(53);
-    if (tid == 0 && ok && c + 1 < NT) issue_g2(c + 1);     // group 2 has been read
+    if (tid == 0 && ok && c + STAGES < NT) issue_g2(c + STAGES);     // group 2 has been read
     if (bwd_tiles) {                                  // ht / sa are rewritten below and in the next chunk
       if (tid == 0) bulk_wait_read();
       __syncthreads();
@@ -726,12 +755,23 @@ int launch_rwkv7_chunked_fwd(const void* r, const void* w, const void* k, const 
   e = check_launch();
   if (e) return e;
   {
-    const int smem = (int)sizeof(ScanSmem) + 1024;
-    if (cuda_ok(cudaFuncSetAttribute(r7c_scan_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem))) return RWKVB200_E_CUDA;
+    int dev = 0, sms = 0;
+    if (cuda_ok(cudaGetDevice(&dev)) || cuda_ok(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)))
+      return RWKVB200_E_CUDA;
     ProfScope prof("r7c_scan_fwd_kernel", st);
-    r7c_scan_fwd_kernel<<<B * H, 256, smem, st>>>(tmap_v, ws.tiles, ws.aux, tpc, keep_for_bwd ? ws.tiles : nullptr,
-                                                  h0, n_state, tmap_o, o ? 1 : 0, ht, Tn, H, NT, status,
-                                                  debug_stamp_buffer());
+    if (B * H > sms) {      // more sequences than SMs: two single-buffered CTAs per SM
+      const int smem = (int)sizeof(ScanSmem<1>) + 1024;
+      if (cuda_ok(cudaFuncSetAttribute(r7c_scan_fwd_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem))) return RWKVB200_E_CUDA;
+      r7c_scan_fwd_kernel<1><<<B * H, 256, smem, st>>>(tmap_v, ws.tiles, ws.aux, tpc, keep_for_bwd ? ws.tiles : nullptr,
+                                                       h0, n_state, tmap_o, o ? 1 : 0, ht, Tn, H, NT, status,
+                                                       debug_stamp_buffer());
+    } else {                // one double-buffered CTA per SM
+      const int smem = (int)sizeof(ScanSmem<2>) + 1024;
+      if (cuda_ok(cudaFuncSetAttribute(r7c_scan_fwd_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem))) return RWKVB200_E_CUDA;
+      r7c_scan_fwd_kernel<2><<<B * H, 256, smem, st>>>(tmap_v, ws.tiles, ws.aux, tpc, keep_for_bwd ? ws.tiles : nullptr,
+                                                       h0, n_state, tmap_o, o ? 1 : 0, ht, Tn, H, NT, status,
+                                                       debug_stamp_buffer());
+    }
   }
   return check_launch();
 }
