@@ -347,7 +347,7 @@ def run_ours(args, wl):
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": wl["desc"], "per_gpu_batch": B, "seq_len": T, "heads": H,
                        "sharding": f"batch x head units replicated per GPU, {world} rank(s), no collective",
-                       "l2": "inputs (0.94 GB per step) exceed the 126 MB L2",
+                       "l2": f"inputs ({7 * B * T * H * 64 * 2 / 1e9:.2f} GB per step) exceed the 126 MB L2",
                        "algo": os.environ.get("RWKV_OPS_B200_RWKV7_ALGO", "auto")},
             "clocks": clocks.summary(),
             "e2e": {"value": e2e_val, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
