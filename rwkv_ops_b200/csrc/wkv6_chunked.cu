@@ -453,6 +453,13 @@ wkv6c_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
     // ---- all global loads of the chunk are issued together (one exposed latency per chunk); r and k
     // stay in registers until the u-term gradients at the end of the chunk
     float4 gw[4], rr4[4], kk4[4];
+    // the state row of this lane (upper lane: S_L for dglast, lower lane: S0) is requested with them
+    float4 srow4[8];
+    {
+      const float* Srow = states + (((size_t)unit * (NT + 1) + c + (lower ? 0 : 1)) * HS + srow) * HS + 32 * hsel;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) srow4[j] = *reinterpret_cast<const float4*>(Srow + 4 * j);
+    }
     {
       float4 vv4[4], yy4[4];
 #pragma unroll
@@ -500,28 +507,27 @@ wkv6c_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
     }
     __syncthreads();
     W6C_STAMP(34);
-    float e0 = 1.f, dlast = 1.f;
+    // decay factors of state row k = srow (both lanes of a pair work on that row below)
+    const float e0 = __expf(fmaxf(sm.qtot[0][srow] + sm.qtot[1][srow], -EXP_CLAMP));
+    const float dlast = __expf(fmaxf(sm.qtot[2][srow] + sm.qtot[3][srow], -EXP_CLAMP));
+    // ---- state rows: the upper lane of a pair holds dS and takes dglast and dS^ = e^{glast-gref} dS_L,
+    // the lower lane takes S~0 = e^{gref} S0
     if (!lower) {
-      e0 = __expf(fmaxf(sm.qtot[0][srow] + sm.qtot[1][srow], -EXP_CLAMP));
-      dlast = __expf(fmaxf(sm.qtot[2][srow] + sm.qtot[3][srow], -EXP_CLAMP));
-    }
-    // ---- state rows (upper lane halves): dglast, dS^ = e^{glast-gref} dS_L, S~0 = e^{gref} S0
-    if (!lower) {
-      const float* SL = states + (((size_t)unit * (NT + 1) + c + 1) * HS + srow) * HS + 32 * hsel;
-      const float* S0 = states + (((size_t)unit * (NT + 1) + c) * HS + srow) * HS + 32 * hsel;
-      float acc = 0.f, x[32];
+      float acc = 0.f;
 #pragma unroll
       for (int j = 0; j < 32; j += 4) {
-        const float4 f = *reinterpret_cast<const float4*>(SL + j);
+        const float4 f = srow4[j >> 2];
         acc += dsreg[j] * f.x + dsreg[j + 1] * f.y + dsreg[j + 2] * f.z + dsreg[j + 3] * f.w;
       }
       sm.dgl[hsel][srow] = acc;
 #pragma unroll
-      for (int j = 0; j < 32; ++j) { dsreg[j] *= dlast; x[j] = dsreg[j]; }     // dsreg now holds dS^
-      store_split_row32(sm.dst[0], sm.dst[1], srow, 32 * hsel, x);
+      for (int j = 0; j < 32; ++j) dsreg[j] *= dlast;     // dsreg now holds dS^
+      store_split_row32(sm.dst[0], sm.dst[1], srow, 32 * hsel, dsreg);
+    } else {
+      float x[32];
 #pragma unroll
       for (int j = 0; j < 32; j += 4) {
-        const float4 f = *reinterpret_cast<const float4*>(S0 + j);
+        const float4 f = srow4[j >> 2];
         x[j] = f.x * e0; x[j + 1] = f.y * e0; x[j + 2] = f.z * e0; x[j + 3] = f.w * e0;
       }
       store_split_row32(sm.st[0], sm.st[1], srow, 32 * hsel, x);
