@@ -265,7 +265,7 @@ r7c_bwd_scan_kernel(const __grid_constant__ CUtensorMap tmap_do, unsigned char* 
 }
 
 // ---------------------------------------------------------------------------------------------
-// 5. all token gradients of one chunk: grid = B*H*NT, 128 threads
+// 5. all token gradients of one chunk: persistent CTAs of 256 threads over the B*H*NT chunk-heads
 // ---------------------------------------------------------------------------------------------
 struct FinalSmem {
   // loaded per chunk, group A (free again once MMA group 2 has completed)

@@ -12,7 +12,7 @@ constexpr float EXP_CLAMP = 80.f;
 __device__ __forceinline__ float cexp(float x) { return __expf(fminf(fmaxf(x, -EXP_CLAMP), EXP_CLAMP)); }
 
 // ---------------------------------------------------------------------------------------------
-// intra-chunk kernel: grid = B*H*NT, 128 threads
+// intra-chunk kernel: persistent CTAs of 256 threads over the B*H*NT chunk-heads
 // ---------------------------------------------------------------------------------------------
 constexpr int NROW = 68;   // padded row of the fp32 copy of A_ab (keeps float4 alignment)
 
