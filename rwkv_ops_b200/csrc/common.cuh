@@ -44,6 +44,24 @@ template <> __device__ __forceinline__ float4 load4<__half>(const __half* p) {
   return make_float4(a.x, a.y, b.x, b.y);
 }
 
+// The same from shared memory (load4 reads through the read-only global path and must not be given a
+// shared-memory address).
+template <typename T> __device__ __forceinline__ float4 load4_shared(const T* p);
+template <> __device__ __forceinline__ float4 load4_shared<float>(const float* p) {
+  return *reinterpret_cast<const float4*>(p);
+}
+template <> __device__ __forceinline__ float4 load4_shared<__nv_bfloat16>(const __nv_bfloat16* p) {
+  const uint2 u = *reinterpret_cast<const uint2*>(p);
+  return make_float4(__uint_as_float(u.x << 16), __uint_as_float(u.x & 0xffff0000u),
+                     __uint_as_float(u.y << 16), __uint_as_float(u.y & 0xffff0000u));
+}
+template <> __device__ __forceinline__ float4 load4_shared<__half>(const __half* p) {
+  const uint2 u = *reinterpret_cast<const uint2*>(p);
+  const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&u.x));
+  const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&u.y));
+  return make_float4(a.x, a.y, b.x, b.y);
+}
+
 // Store four consecutive elements from a float4 (same alignment rule as load4).
 template <typename T> __device__ __forceinline__ void store4(T* p, float4 f);
 template <> __device__ __forceinline__ void store4<float>(float* p, float4 f) {

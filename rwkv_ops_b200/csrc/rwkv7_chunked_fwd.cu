@@ -27,18 +27,22 @@ struct IntraSmem {
   unsigned char y[TILE_BYTES];                      // A_ak v
   float nmat[L * NROW];                             // stril(A_ab) in fp32
   float qtot[4][64];                                // sums of g over the four quarters of the chunk
-  uint64_t bar_v, bar_m1, bar_m2, bar_m3;
+  uint64_t bar_v, bar_in, bar_m1, bar_m2, bar_m3;
   uint32_t tmem_base;
 };
 
-// Persistent: CTAs (two per SM) walk over chunk-heads ch = blockIdx.x, blockIdx.x + gridDim.x, ...; the
-// token rows of the next chunk-head are fetched into registers while the current one is in its MMA
-// phases, and its v tile is requested as soon as MMA 2 has read the current one.
+// Persistent: CTAs (two per SM) walk over chunk-heads ch = blockIdx.x, blockIdx.x + gridDim.x, ...  The
+// raw q, k, a, b, w tiles of the next chunk-head are requested by TMA as soon as the tiles they land in
+// (q~, k~, a~, b~, which are then scaled in place, and O1) have been copied out, its v tile as soon as
+// MMA 2 has read the current one, and the rows of the one after that are asked into L2.
 // 256 threads: warp w reads TMEM lanes 32*(w&3).. and the two warps that share a lane window split
 // the columns (hsel = w>>2); the triangular solve runs on warps 0-1 while the other warps drain MMA 2.
 __global__ void __launch_bounds__(256, 2)
 r7c_intra_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ w, const bf16* __restrict__ k,
                      const bf16* __restrict__ a, const bf16* __restrict__ b,
+                     const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_w,
+                     const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_a,
+                     const __grid_constant__ CUtensorMap tmap_b,
                      const __grid_constant__ CUtensorMap tmap_v, unsigned char* __restrict__ ws_tiles,
                      float* __restrict__ ws_aux, int tiles_per_chunk, int keep_for_bwd,
                      int Tn, int H, int NT, int n_ch, TokLayout lay, int* status, long long* dbg) {
@@ -49,7 +53,7 @@ r7c_intra_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ w, con
   const int wq = warp & 3, hsel = warp >> 2;
 
   if (tid == 0) {
-    mbar_init(&sm.bar_v, 1); mbar_init(&sm.bar_m1, 1); mbar_init(&sm.bar_m2, 1); mbar_init(&sm.bar_m3, 1);
+    mbar_init(&sm.bar_v, 1); mbar_init(&sm.bar_in, 1); mbar_init(&sm.bar_m1, 1); mbar_init(&sm.bar_m2, 1); mbar_init(&sm.bar_m3, 1);
     fence_mbar_init();
   }
   if (warp == 0) tmem_alloc(&sm.tmem_base, 256);
@@ -62,28 +66,18 @@ r7c_intra_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ w, con
     const int unit = ch / NT;
     bi = unit / H; hi = unit % H; t0 = (ch % NT) * L;
   };
-  // 16-byte loads (8 channels of one token) of the five token tensors, two per thread and tensor
-  uint4 rw[2], rq[2], rk[2], ra[2], rb[2];
-  auto load_rows = [&](int ch) {
+  // the raw tiles of a chunk-head: q, k, a, b into the tiles that will hold their scaled versions, w into
+  // the O1 tile (written again only after MMA 2); rows past the end of the sequence arrive as zeros
+  auto load_in = [&](int ch) {      // tid 0
     int bi, hi, t0; coords(ch, bi, hi, t0);
-    const long long base = bi * lay.sb + hi * lay.sh;
-    const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
-#pragma unroll
-    for (int n = 0; n < 2; ++n) {
-      const int e = tid + 256 * n, row = e >> 3, cc = e & 7, tok = t0 + row;
-      const long long off = base + (long long)tok * lay.st + 8 * cc;
-      rw[n] = zero4; rq[n] = zero4; rk[n] = zero4; ra[n] = zero4; rb[n] = zero4;
-      if (tok < Tn) {      // predicated loads straight into the registers: nothing waits on them here
-        rw[n] = __ldg(reinterpret_cast<const uint4*>(w + off));
-        rq[n] = __ldg(reinterpret_cast<const uint4*>(q + off));
-        rk[n] = __ldg(reinterpret_cast<const uint4*>(k + off));
-        ra[n] = __ldg(reinterpret_cast<const uint4*>(a + off));
-        rb[n] = __ldg(reinterpret_cast<const uint4*>(b + off));
-      }
-    }
+    mbar_expect_tx(&sm.bar_in, 5 * TILE_BYTES);
+    tma_load_4d(sm.o1, &tmap_w, &sm.bar_in, 0, t0, hi, bi);
+    tma_load_4d(sm.qt, &tmap_q, &sm.bar_in, 0, t0, hi, bi);
+    tma_load_4d(sm.kt, &tmap_k, &sm.bar_in, 0, t0, hi, bi);
+    tma_load_4d(sm.at, &tmap_a, &sm.bar_in, 0, t0, hi, bi);
+    tma_load_4d(sm.bt, &tmap_b, &sm.bar_in, 0, t0, hi, bi);
   };
-  // Ask for the next chunk-head's token rows to be brought into L2 (no registers are tied up); the
-  // loads at the top of the next iteration then hit L2.
+  // Ask for a chunk-head's token rows to be brought into L2, ahead of the TMA loads above.
   auto prefetch_rows = [&](int ch) {
     int bi, hi, t0; coords(ch, bi, hi, t0);
     const long long base = bi * lay.sb + hi * lay.sh;
@@ -105,7 +99,7 @@ r7c_intra_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ w, con
     mbar_expect_tx(&sm.bar_v, TILE_BYTES);
     tma_load_4d(sm.v, &tmap_v, &sm.bar_v, 0, t0, hi, bi);
   };
-  if (blockIdx.x < n_ch && tid == 0) load_v(blockIdx.x);
+  if (blockIdx.x < n_ch && tid == 0) { load_in(blockIdx.x); load_v(blockIdx.x); }
   // The two CTAs that share an SM would otherwise run their phases in lockstep and compete for the
   // same unit (shared-memory pipe during the triangular solve); start every other CTA half a
   // chunk-head late.
@@ -120,11 +114,22 @@ r7c_intra_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ w, con
     const int next = ch + gridDim.x;
 
     R7C_STAMP(0);
-    load_rows(ch);
     if (next < n_ch) prefetch_rows(next);
-    // the copies of the previous chunk-head's q~, k~, b~, A_qb, O1, Ainv tiles have left shared memory
-    // (its W, U copies, committed last, may still be reading: those tiles are rewritten only after MMA 1)
-    if (tid == 0) bulk_wait_read_1();
+    // this thread's 2 x 16 bytes (8 channels of one token) of each raw tile; the scaled values go back to
+    // the same places (the previous chunk-head's W, U copies, committed last, may still be reading their
+    // tiles: those are rewritten only after MMA 1)
+    uint4 rw[2], rq[2], rk[2], ra[2], rb[2];
+    ok = mbar_wait(&sm.bar_in, par, status, 206) && ok;
+#pragma unroll
+    for (int n = 0; n < 2; ++n) {
+      const int e = tid + 256 * n;
+      const uint32_t off = tile_chunk_off(e >> 3, e & 7);
+      rw[n] = *reinterpret_cast<const uint4*>(sm.o1 + off);
+      rq[n] = *reinterpret_cast<const uint4*>(sm.qt + off);
+      rk[n] = *reinterpret_cast<const uint4*>(sm.kt + off);
+      ra[n] = *reinterpret_cast<const uint4*>(sm.at + off);
+      rb[n] = *reinterpret_cast<const uint4*>(sm.bt + off);
+    }
     // ---- phase A: decay prefix sums and the four scaled operands; the prefix sum over tokens goes
     // through shared memory (the fp32 area that later holds A_ab).
     {
@@ -441,6 +446,8 @@ r7c_intra_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ w, con
     ok = mbar_wait(&sm.bar_m3, par, status, 204) && ok;
     tc_fence_after();
     R7C_STAMP(7);
+    // MMA 3 has read a~; once the copies issued with it have left q~, k~, b~, O1, the next raw tiles may land
+    if (tid == 0 && ok && next < n_ch) { bulk_wait_read(); load_in(next); }
     {
       // W -> the A_ak tile (free since MMA 2), U -> the Y tile (free: MMA 3 has completed)
       const int i = 16 * wq + (lane & 15);
@@ -734,6 +741,12 @@ int launch_rwkv7_chunked_fwd(const void* r, const void* w, const void* k, const 
   if (e) return e;
   e = make_token_tensor_map(&tmap_o, o ? o : v, B, Tn, H, head_first);   // unused when o is NULL
   if (e) return e;
+  CUtensorMap tmap_in[5];
+  const void* ins[5] = {r, w, k, a, b};
+  for (int i = 0; i < 5; ++i) {
+    e = make_token_tensor_map(&tmap_in[i], ins[i], B, Tn, H, head_first);
+    if (e) return e;
+  }
   const int NT = num_chunks(Tn);
   const int tpc = keep_for_bwd ? (int)ALL_TILES : (int)FWD_TILES;
   Workspace ws = carve(workspace, B, Tn, H, tpc);
@@ -748,7 +761,8 @@ int launch_rwkv7_chunked_fwd(const void* r, const void* w, const void* k, const 
       return RWKVB200_E_CUDA;
     const int grid = n_ch < 2 * sms ? n_ch : 2 * sms;     // persistent: two CTAs per SM
     r7c_intra_fwd_kernel<<<grid, 256, smem, st>>>((const bf16*)r, (const bf16*)w, (const bf16*)k, (const bf16*)a,
-                                                   (const bf16*)b, tmap_v, ws.tiles, ws.aux, tpc,
+                                                   (const bf16*)b, tmap_in[0], tmap_in[1], tmap_in[2], tmap_in[3],
+                                                   tmap_in[4], tmap_v, ws.tiles, ws.aux, tpc,
                                                    keep_for_bwd ? 1 : 0, Tn, H, NT, n_ch, lay, status,
                                                    debug_stamp_buffer());
   }

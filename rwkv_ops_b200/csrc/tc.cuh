@@ -283,6 +283,7 @@ int* device_status_ptr();
 
 // Optional device buffer (>= 64 long long) that kernels fill with clock64() stamps at their phase
 // boundaries (one designated CTA); nullptr unless a developer installed one.
+int make_row_tensor_map(CUtensorMap* out, const void* base, int B, int T, int H, int elem_bytes);
 long long* debug_stamp_buffer();
 
 }  // namespace rwkvb200

@@ -57,6 +57,26 @@ int make_token_tensor_map(CUtensorMap* out, const void* base, int B, int T, int 
   return RWKVB200_E_CUDA;
 }
 
+// [B][T][H][64] rows of 2- or 4-byte elements, box = 64 rows x 64 elements of one (batch, head), no swizzle:
+// the box lands in shared memory as 64 consecutive rows of 64 * elem_bytes bytes
+int make_row_tensor_map(CUtensorMap* out, const void* base, int B, int T, int H, int elem_bytes) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) { last_cuda_error_slot() = 100000; return RWKVB200_E_CUDA; }
+  const cuuint64_t row = (cuuint64_t)HS * elem_bytes;
+  cuuint64_t dims[4] = {(cuuint64_t)HS, (cuuint64_t)T, (cuuint64_t)H, (cuuint64_t)B};
+  cuuint64_t strides[3] = {row * H, row, row * (cuuint64_t)T * H};
+  cuuint32_t box[4] = {(cuuint32_t)HS, 64, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  int dev = 0;
+  if (cuda_ok(cudaGetDevice(&dev)) || cuda_ok(cudaSetDevice(dev))) return RWKVB200_E_CUDA;
+  CUresult r = fn(out, elem_bytes == 4 ? CU_TENSOR_MAP_DATA_TYPE_UINT32 : CU_TENSOR_MAP_DATA_TYPE_UINT16, 4,
+                  const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r == CUDA_SUCCESS) return RWKVB200_OK;
+  last_cuda_error_slot() = 100000 + (int)r;
+  return RWKVB200_E_CUDA;
+}
+
 static long long* g_stamp_buffer = nullptr;
 long long* debug_stamp_buffer() { return g_stamp_buffer; }
 

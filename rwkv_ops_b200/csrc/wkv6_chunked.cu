@@ -83,17 +83,23 @@ struct FwdSmem {
   float gs[L * NROW];                 // prefix of g inside each half; later the staged y rows
   float qtot[4][64];
   float dgs[64];                      // sum_k r u k per token
-  uint64_t bar_1, bar_2;
+  uint64_t bar_1, bar_2, bar_in;
   uint32_t tmem_base;
 };
 
+// The raw r, k, v, w rows of a chunk (64 rows of 64 elements each) arrive by TMA in the space of the tile
+// pairs they are turned into (r -> rt, k -> kt, v -> vt, w -> at), requested for the next chunk as soon as
+// the last MMA of the current one has read those tiles; a thread reads its elements, all threads meet at a
+// barrier, and then the split tiles are written over the raw rows.
 // S0 of every chunk (and the final state) goes to `states` [B*H][NT+1][64][64] when it is not NULL.
 template <typename T>
 __global__ void __launch_bounds__(256, 2)
 wkv6c_fwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __restrict__ v, const T* __restrict__ w,
                  const float* __restrict__ u, const float* __restrict__ s0, int n_state,
                  const int32_t* __restrict__ smap, T* __restrict__ y, float* __restrict__ sT,
-                 float* __restrict__ states, int Tn, int H, int* status, long long* dbg) {
+                 float* __restrict__ states, const __grid_constant__ CUtensorMap tmap_r,
+                 const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
+                 const __grid_constant__ CUtensorMap tmap_w, int Tn, int H, int* status, long long* dbg) {
 #define W6C_STAMP(n) do { if (dbg && tid == 0 && blockIdx.x == gridDim.x / 2 && c == 2) dbg[n] = clock64(); } while (0)
   extern __shared__ unsigned char smem_raw[];
   FwdSmem& sm = *reinterpret_cast<FwdSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -107,7 +113,7 @@ wkv6c_fwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
   const bool tok_lane = lane < 16;            // lower lane halves hold token rows, upper halves state rows
 
   if (tid == 0) {
-    mbar_init(&sm.bar_1, 1); mbar_init(&sm.bar_2, 1);
+    mbar_init(&sm.bar_1, 1); mbar_init(&sm.bar_2, 1); mbar_init(&sm.bar_in, 1);
     fence_mbar_init();
   }
   if (warp == 0) tmem_alloc(&sm.tmem_base, 128);
@@ -144,24 +150,34 @@ wkv6c_fwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
     }
   }
 
+  const T* raw_r = reinterpret_cast<const T*>(sm.rt[0]);
+  const T* raw_k = reinterpret_cast<const T*>(sm.kt[0]);
+  const T* raw_v = reinterpret_cast<const T*>(sm.vt[0]);
+  const T* raw_w = reinterpret_cast<const T*>(sm.at[0]);
+  auto load_in = [&](int c) {      // tid 0; rows past the end of the sequence arrive as zeros
+    mbar_expect_tx(&sm.bar_in, 4 * 64 * 64 * (uint32_t)sizeof(T));
+    tma_load_4d(sm.at[0], &tmap_w, &sm.bar_in, 0, c * L, hi, bi);
+    tma_load_4d(sm.vt[0], &tmap_v, &sm.bar_in, 0, c * L, hi, bi);
+    tma_load_4d(sm.rt[0], &tmap_r, &sm.bar_in, 0, c * L, hi, bi);
+    tma_load_4d(sm.kt[0], &tmap_k, &sm.bar_in, 0, c * L, hi, bi);
+  };
+  if (tid == 0 && NT > 0) load_in(0);
+
   bool ok = true;
   for (int c = 0; c < NT && ok; ++c) {
     const int t0 = c * L;
     const uint32_t par = c & 1;
     W6C_STAMP(0);
-    // ---- the w and v rows of the chunk are requested together (r and k follow after the prefix sums:
-    // holding them across the barriers would spill at two CTAs per SM)
+    // ---- the raw rows of the chunk have landed: this thread's w and v elements
+    ok = mbar_wait(&sm.bar_in, par, status, 403) && ok;
     float4 gw[4], vv4[4];
 #pragma unroll
     for (int n = 0; n < 4; ++n) {
-      const int e = tid + 256 * n, row = e >> 4, tok = t0 + row;
-      gw[n] = make_float4(0.f, 0.f, 0.f, 0.f);
-      vv4[n] = gw[n];
-      if (tok < Tn) {
-        const long long off = base + (long long)tok * tstride + 4 * c4;
-        gw[n] = load4(w + off); vv4[n] = load4(v + off);
-      }
+      const int e = tid + 256 * n, row = e >> 4;
+      gw[n] = load4_shared(raw_w + row * 64 + 4 * c4);
+      vv4[n] = load4_shared(raw_v + row * 64 + 4 * c4);
     }
+    __syncthreads();      // every raw v element is in registers: the split v tiles may overwrite the rows
     // ---- pass W: g and its prefix sums; pass V
 #pragma unroll
     for (int n = 0; n < 4; ++n) {
@@ -190,18 +206,6 @@ wkv6c_fwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
     }
     __syncthreads();
     W6C_STAMP(2);
-    // the r and k rows are requested here so that their latency passes under the state phase
-    float4 rr4[4], kk4[4];
-#pragma unroll
-    for (int n = 0; n < 4; ++n) {
-      const int tok = t0 + ((tid + 256 * n) >> 4);
-      rr4[n] = make_float4(0.f, 0.f, 0.f, 0.f);
-      kk4[n] = rr4[n];
-      if (tok < Tn) {
-        const long long off = base + (long long)tok * tstride + 4 * c4;
-        rr4[n] = load4(r + off); kk4[n] = load4(k + off);
-      }
-    }
     // decay factors of the state rows: e^{gref} of this chunk scales the incoming state, e^{glast-gref} the outgoing
     float e0 = 1.f, dlast = 1.f;
     if (!tok_lane) {
@@ -222,6 +226,14 @@ wkv6c_fwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
     }
     W6C_STAMP(3);
     // ---- pass RK: scaled r, k (split hi/lo) and the diagonal term
+    float4 rr4[4], kk4[4];
+#pragma unroll
+    for (int n = 0; n < 4; ++n) {
+      const int row = (tid + 256 * n) >> 4;
+      rr4[n] = load4_shared(raw_r + row * 64 + 4 * c4);
+      kk4[n] = load4_shared(raw_k + row * 64 + 4 * c4);
+    }
+    __syncthreads();      // every raw r, k element is in registers
 #pragma unroll
     for (int n = 0; n < 4; ++n) {
       const int e = tid + 256 * n, row = e >> 4;
@@ -315,6 +327,7 @@ wkv6c_fwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
     ok = mbar_wait(&sm.bar_2, par, status, 402) && ok;
     tc_fence_after();
     W6C_STAMP(7);
+    if (tid == 0 && ok && c + 1 < NT) load_in(c + 1);      // the tiles of this chunk have been read for the last time
     if (ok) {
       uint32_t rr[32];
       tmem_ld32(tm_ys, rr);
@@ -766,12 +779,20 @@ int launch_wkv6_chunked_fwd(const void* r, const void* k, const void* v, const v
   int* status = device_status_ptr();
   if (!status) { last_cuda_error_slot() = 99999; return RWKVB200_E_CUDA; }
   const int smem = (int)sizeof(FwdSmem) + 1024;
+  const int esz = dtype == RWKVB200_F32 ? 4 : 2;
+  CUtensorMap tm_r, tm_k, tm_v, tm_w;
+  int e = make_row_tensor_map(&tm_r, r, B, Tn, H, esz);
+  if (!e) e = make_row_tensor_map(&tm_k, k, B, Tn, H, esz);
+  if (!e) e = make_row_tensor_map(&tm_v, v, B, Tn, H, esz);
+  if (!e) e = make_row_tensor_map(&tm_w, w, B, Tn, H, esz);
+  if (e) return e;
   ProfScope prof("wkv6c_fwd_kernel", st);
   RWKVB200_DISPATCH_DTYPE(dtype,
     if (cuda_ok(cudaFuncSetAttribute(wkv6c_fwd_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)))
       return RWKVB200_E_CUDA;
     wkv6c_fwd_kernel<T><<<B * H, 256, smem, st>>>((const T*)r, (const T*)k, (const T*)v, (const T*)w, u, s0, n_state,
-                                                   smap, (T*)y, sT, states, Tn, H, status, debug_stamp_buffer()));
+                                                   smap, (T*)y, sT, states, tm_r, tm_k, tm_v, tm_w, Tn, H, status,
+                                                   debug_stamp_buffer()));
   return check_launch();
 }
 
