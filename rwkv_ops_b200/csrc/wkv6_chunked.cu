@@ -399,9 +399,14 @@ struct BwdSmem {
   float dds[64];                      // dy_i . v_i per token
   float dgl[2][64];                   // dglast, one partial per column half
   float du_s[64];
-  uint64_t bar_1, bar_2;
+  // raw rows of the next chunk, requested by TMA a chunk ahead: w and dy (needed first) here; r and k land
+  // in the space of rt / kt once the last epilogue has read those, v in red_e once the decay gradient has
+  alignas(128) unsigned char raw_w[L * 64 * 4];
+  alignas(128) unsigned char raw_dy[L * 64 * 4];
+  uint64_t bar_1, bar_2, bar_in_a, bar_in_b, bar_in_c;
   uint32_t tmem_base;
 };
+static_assert(sizeof(BwdSmem) + 1024 <= 227 * 1024, "backward shared memory");
 
 template <typename T>
 __global__ void __launch_bounds__(256)
@@ -409,7 +414,9 @@ wkv6c_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
                  const float* __restrict__ u, const T* __restrict__ d_y, const float* __restrict__ d_sT,
                  const float* __restrict__ states, T* __restrict__ dr, T* __restrict__ dk, T* __restrict__ dv,
                  T* __restrict__ dw, float* __restrict__ du_partial, float* __restrict__ d_s0,
-                 int Tn, int H, int* status, long long* dbg) {
+                 const __grid_constant__ CUtensorMap tmap_r, const __grid_constant__ CUtensorMap tmap_k,
+                 const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_w,
+                 const __grid_constant__ CUtensorMap tmap_dy, int Tn, int H, int* status, long long* dbg) {
 #define W6C_STAMP(n) do { if (dbg && tid == 0 && blockIdx.x == gridDim.x / 2 && c == NT - 2) dbg[n] = clock64(); } while (0)
   extern __shared__ unsigned char smem_raw[];
   BwdSmem& sm = *reinterpret_cast<BwdSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -432,6 +439,7 @@ wkv6c_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
 
   if (tid == 0) {
     mbar_init(&sm.bar_1, 1); mbar_init(&sm.bar_2, 1);
+    mbar_init(&sm.bar_in_a, 1); mbar_init(&sm.bar_in_b, 1); mbar_init(&sm.bar_in_c, 1);
     fence_mbar_init();
   }
   if (tid < 64) sm.du_s[tid] = 0.f;
@@ -458,52 +466,52 @@ wkv6c_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
   }
   float4 du_acc = make_float4(0.f, 0.f, 0.f, 0.f);
 
+  constexpr uint32_t RAW_BYTES = 64 * 64 * (uint32_t)sizeof(T);
+  const T* raw_w = reinterpret_cast<const T*>(sm.raw_w);
+  const T* raw_dy = reinterpret_cast<const T*>(sm.raw_dy);
+  const T* raw_v = reinterpret_cast<const T*>(sm.red_e);
+  const T* raw_r = reinterpret_cast<const T*>(sm.rt[0]);
+  const T* raw_k = reinterpret_cast<const T*>(sm.kt[0]);
+  auto load_in_a = [&](int c) {      // tid 0; rows past the end of the sequence arrive as zeros
+    mbar_expect_tx(&sm.bar_in_a, 2 * RAW_BYTES);
+    tma_load_4d(sm.raw_w, &tmap_w, &sm.bar_in_a, 0, c * L, hi, bi);
+    tma_load_4d(sm.raw_dy, &tmap_dy, &sm.bar_in_a, 0, c * L, hi, bi);
+  };
+  auto load_in_b = [&](int c) {
+    mbar_expect_tx(&sm.bar_in_b, 2 * RAW_BYTES);
+    tma_load_4d(sm.rt[0], &tmap_r, &sm.bar_in_b, 0, c * L, hi, bi);
+    tma_load_4d(sm.kt[0], &tmap_k, &sm.bar_in_b, 0, c * L, hi, bi);
+  };
+  auto load_in_c = [&](int c) {
+    mbar_expect_tx(&sm.bar_in_c, RAW_BYTES);
+    tma_load_4d(sm.red_e, &tmap_v, &sm.bar_in_c, 0, c * L, hi, bi);
+  };
+  if (tid == 0 && NT > 0) { load_in_a(NT - 1); load_in_c(NT - 1); load_in_b(NT - 1); }
+
   bool ok = true;
   for (int c = NT - 1; c >= 0 && ok; --c) {
     const int t0 = c * L;
     const uint32_t par = (NT - 1 - c) & 1;
     W6C_STAMP(32);
-    // ---- all global loads of the chunk are issued together (one exposed latency per chunk); r and k
-    // stay in registers until the u-term gradients at the end of the chunk
+    // ---- r and k are read at pass RK and stay in registers until the u-term gradients at the end of the chunk
     float4 gw[4], rr4[4], kk4[4];
-    // the state row of this lane (upper lane: S_L for dglast, lower lane: S0) is requested with them
-    float4 srow4[8];
     {
-      const float* Srow = states + (((size_t)unit * (NT + 1) + c + (lower ? 0 : 1)) * HS + srow) * HS + 32 * hsel;
-#pragma unroll
-      for (int j = 0; j < 8; ++j) srow4[j] = *reinterpret_cast<const float4*>(Srow + 4 * j);
-    }
-    {
-      float4 vv4[4], yy4[4];
+      ok = mbar_wait(&sm.bar_in_a, par, status, 413) && ok;
+      // ---- pass W: g; pass DY: split tiles
 #pragma unroll
       for (int n = 0; n < 4; ++n) {
         const int e = tid + 256 * n, row = e >> 4, tok = t0 + row;
-        gw[n] = make_float4(0.f, 0.f, 0.f, 0.f);
-        rr4[n] = gw[n]; kk4[n] = gw[n]; vv4[n] = gw[n]; yy4[n] = gw[n];
-        if (tok < Tn) {
-          const long long off = base + (long long)tok * tstride + 4 * c4;
-          gw[n] = load4(w + off); vv4[n] = load4(v + off); yy4[n] = load4(d_y + off);
-          rr4[n] = load4(r + off); kk4[n] = load4(k + off);
-        }
-      }
-      // ---- pass W: g; pass V / DY: split tiles and dd_i = dy_i . v_i
-#pragma unroll
-      for (int n = 0; n < 4; ++n) {
-        const int e = tid + 256 * n, row = e >> 4, tok = t0 + row;
+        const float4 w4 = load4_shared(raw_w + row * 64 + 4 * c4);
         float4 f = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (tok < Tn) f = make_float4(-__expf(gw[n].x), -__expf(gw[n].y), -__expf(gw[n].z), -__expf(gw[n].w));
+        if (tok < Tn) f = make_float4(-__expf(w4.x), -__expf(w4.y), -__expf(w4.z), -__expf(w4.w));
         gw[n] = f;
         *reinterpret_cast<float4*>(&sm.gg[row * NROW + 4 * c4]) = f;
-        store_split4(sm.vt[0], sm.vt[1], row, 4 * c4, vv4[n]);
-        store_split4(sm.dyt[0], sm.dyt[1], row, 4 * c4, yy4[n]);
-        float dd = vv4[n].x * yy4[n].x + vv4[n].y * yy4[n].y + vv4[n].z * yy4[n].z + vv4[n].w * yy4[n].w;
-#pragma unroll
-        for (int m = 8; m >= 1; m >>= 1) dd += __shfl_xor_sync(0xffffffffu, dd, m);
-        if (c4 == 0) sm.dds[row] = dd;
+        store_split4(sm.dyt[0], sm.dyt[1], row, 4 * c4, load4_shared(raw_dy + row * 64 + 4 * c4));
       }
     }
     __syncthreads();
     W6C_STAMP(33);
+
     {
       const int ch = tid & 63, quarter = tid >> 6;
       float gv[16];
@@ -520,33 +528,26 @@ wkv6c_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
     }
     __syncthreads();
     W6C_STAMP(34);
-    // decay factors of state row k = srow (both lanes of a pair work on that row below)
-    const float e0 = __expf(fmaxf(sm.qtot[0][srow] + sm.qtot[1][srow], -EXP_CLAMP));
-    const float dlast = __expf(fmaxf(sm.qtot[2][srow] + sm.qtot[3][srow], -EXP_CLAMP));
-    // ---- state rows: the upper lane of a pair holds dS and takes dglast and dS^ = e^{glast-gref} dS_L,
-    // the lower lane takes S~0 = e^{gref} S0
-    if (!lower) {
-      float acc = 0.f;
-#pragma unroll
-      for (int j = 0; j < 32; j += 4) {
-        const float4 f = srow4[j >> 2];
-        acc += dsreg[j] * f.x + dsreg[j + 1] * f.y + dsreg[j + 2] * f.z + dsreg[j + 3] * f.w;
-      }
-      sm.dgl[hsel][srow] = acc;
-#pragma unroll
-      for (int j = 0; j < 32; ++j) dsreg[j] *= dlast;     // dsreg now holds dS^
-      store_split_row32(sm.dst[0], sm.dst[1], srow, 32 * hsel, dsreg);
-    } else {
-      float x[32];
-#pragma unroll
-      for (int j = 0; j < 32; j += 4) {
-        const float4 f = srow4[j >> 2];
-        x[j] = f.x * e0; x[j + 1] = f.y * e0; x[j + 2] = f.z * e0; x[j + 3] = f.w * e0;
-      }
-      store_split_row32(sm.st[0], sm.st[1], srow, 32 * hsel, x);
-    }
     W6C_STAMP(35);
-    // ---- pass RK: scaled r, k (split) and the diagonal term
+    // ---- pass RK: scaled r, k (split, written over the raw rows once every thread has its elements) and
+    // the diagonal term
+    ok = mbar_wait(&sm.bar_in_b, par, status, 415) && ok;
+    ok = mbar_wait(&sm.bar_in_c, par, status, 414) && ok;
+#pragma unroll
+    for (int n = 0; n < 4; ++n) {
+      const int row = (tid + 256 * n) >> 4;
+      rr4[n] = load4_shared(raw_r + row * 64 + 4 * c4);
+      kk4[n] = load4_shared(raw_k + row * 64 + 4 * c4);
+      // pass V: split tiles and dd_i = dy_i . v_i
+      const float4 v4 = load4_shared(raw_v + row * 64 + 4 * c4), y4 = load4_shared(raw_dy + row * 64 + 4 * c4);
+      store_split4(sm.vt[0], sm.vt[1], row, 4 * c4, v4);
+      float dd = v4.x * y4.x + v4.y * y4.y + v4.z * y4.z + v4.w * y4.w;
+#pragma unroll
+      for (int m = 8; m >= 1; m >>= 1) dd += __shfl_xor_sync(0xffffffffu, dd, m);
+      if (c4 == 0) sm.dds[row] = dd;
+    }
+    __syncthreads();
+    if (tid == 0 && ok && c > 0) load_in_a(c - 1);      // every thread has taken its w and dy elements
 #pragma unroll
     for (int n = 0; n < 4; ++n) {
       const int e = tid + 256 * n, row = e >> 4;
@@ -566,6 +567,14 @@ wkv6c_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
 #pragma unroll
       for (int m = 8; m >= 1; m >>= 1) dg += __shfl_xor_sync(0xffffffffu, dg, m);
       if (c4 == 0) sm.dgs[row] = dg;
+    }
+    // the state row of this lane (upper lane: S_L for dglast, lower lane: S0) is requested here and used
+    // after the first epilogue: MMA batch 1 and that epilogue cover its latency
+    float4 srow4[8];
+    {
+      const float* Srow = states + (((size_t)unit * (NT + 1) + c + (lower ? 0 : 1)) * HS + srow) * HS + 32 * hsel;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) srow4[j] = *reinterpret_cast<const float4*>(Srow + 4 * j);
     }
     if (c > 0 && c4 == 0) {   // bring the previous chunk's rows into L2 while this chunk is in its MMA phases
 #pragma unroll
@@ -620,6 +629,31 @@ wkv6c_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
       }
       if (lower) store_split_row32(sm.at[0], sm.at[1], srow, 32 * hsel, x);
       else       store_split_row32(sm.dat[0], sm.dat[1], srow, 32 * hsel, x);
+    }
+    // decay factors of state row k = srow (both lanes of a pair work on that row below)
+    const float e0 = __expf(fmaxf(sm.qtot[0][srow] + sm.qtot[1][srow], -EXP_CLAMP));
+    const float dlast = __expf(fmaxf(sm.qtot[2][srow] + sm.qtot[3][srow], -EXP_CLAMP));
+    // ---- state rows: the upper lane of a pair holds dS and takes dglast and dS^ = e^{glast-gref} dS_L,
+    // the lower lane takes S~0 = e^{gref} S0
+    if (!lower) {
+      float acc = 0.f;
+#pragma unroll
+      for (int j = 0; j < 32; j += 4) {
+        const float4 f = srow4[j >> 2];
+        acc += dsreg[j] * f.x + dsreg[j + 1] * f.y + dsreg[j + 2] * f.z + dsreg[j + 3] * f.w;
+      }
+      sm.dgl[hsel][srow] = acc;
+#pragma unroll
+      for (int j = 0; j < 32; ++j) dsreg[j] *= dlast;     // dsreg now holds dS^
+      store_split_row32(sm.dst[0], sm.dst[1], srow, 32 * hsel, dsreg);
+    } else {
+      float x[32];
+#pragma unroll
+      for (int j = 0; j < 32; j += 4) {
+        const float4 f = srow4[j >> 2];
+        x[j] = f.x * e0; x[j + 1] = f.y * e0; x[j + 2] = f.z * e0; x[j + 3] = f.w * e0;
+      }
+      store_split_row32(sm.st[0], sm.st[1], srow, 32 * hsel, x);
     }
     fence_async_smem();
     tc_fence_before();
@@ -697,6 +731,7 @@ wkv6c_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
     }
     tc_fence_before();
     ok = __syncthreads_and(ok);
+    if (tid == 0 && ok && c > 0) load_in_b(c - 1);      // the epilogue above was the last reader of rt / kt
     W6C_STAMP(40);
     // ---- decay gradient: dg_j = sum_{i>=j} (dgi_i + dge_i) - dge_j + dglast;  dw = dg g
     {
@@ -720,6 +755,7 @@ wkv6c_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
       }
     }
     __syncthreads();
+    if (tid == 0 && ok && c > 0) load_in_c(c - 1);      // red_e has been read for the last time
     W6C_STAMP(41);
     // ---- outputs, coalesced, plus the u-term parts of dr, dk and du
 #pragma unroll
@@ -824,13 +860,22 @@ int launch_wkv6_chunked_bwd(const void* r, const void* k, const void* v, const v
   if (!status) { last_cuda_error_slot() = 99999; return RWKVB200_E_CUDA; }
   const int smem = (int)sizeof(BwdSmem) + 1024;
   {
+    const int esz = dtype == RWKVB200_F32 ? 4 : 2;
+    CUtensorMap tm_r, tm_k, tm_v, tm_w, tm_dy;
+    e = make_row_tensor_map(&tm_r, r, B, Tn, H, esz);
+    if (!e) e = make_row_tensor_map(&tm_k, k, B, Tn, H, esz);
+    if (!e) e = make_row_tensor_map(&tm_v, v, B, Tn, H, esz);
+    if (!e) e = make_row_tensor_map(&tm_w, w, B, Tn, H, esz);
+    if (!e) e = make_row_tensor_map(&tm_dy, d_y, B, Tn, H, esz);
+    if (e) return e;
     ProfScope prof("wkv6c_bwd_kernel", st);
     RWKVB200_DISPATCH_DTYPE(dtype,
       if (cuda_ok(cudaFuncSetAttribute(wkv6c_bwd_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)))
         return RWKVB200_E_CUDA;
       wkv6c_bwd_kernel<T><<<B * H, 256, smem, st>>>((const T*)r, (const T*)k, (const T*)v, (const T*)w, u,
                                                      (const T*)d_y, d_sT, states, (T*)dr, (T*)dk, (T*)dv, (T*)dw,
-                                                     du_partial, d_s0, Tn, H, status, debug_stamp_buffer()));
+                                                     du_partial, d_s0, tm_r, tm_k, tm_v, tm_w, tm_dy, Tn, H, status,
+                                                     debug_stamp_buffer()));
   }
   e = check_launch();
   if (e) return e;
