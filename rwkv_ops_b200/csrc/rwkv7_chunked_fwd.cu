@@ -27,7 +27,7 @@ struct IntraSmem {
   unsigned char y[TILE_BYTES];                      // A_ak v
   float nmat[L * NROW];                             // stril(A_ab) in fp32
   float qtot[4][64];                                // sums of g over the four quarters of the chunk
-  uint64_t bar_v, bar_in, bar_m1, bar_m2, bar_m3;
+  uint64_t bar_v, bar_w, bar_in, bar_m1, bar_m2, bar_m3;
   uint32_t tmem_base;
 };
 
@@ -53,7 +53,7 @@ r7c_intra_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ w, con
   const int wq = warp & 3, hsel = warp >> 2;
 
   if (tid == 0) {
-    mbar_init(&sm.bar_v, 1); mbar_init(&sm.bar_in, 1); mbar_init(&sm.bar_m1, 1); mbar_init(&sm.bar_m2, 1); mbar_init(&sm.bar_m3, 1);
+    mbar_init(&sm.bar_v, 1); mbar_init(&sm.bar_w, 1); mbar_init(&sm.bar_in, 1); mbar_init(&sm.bar_m1, 1); mbar_init(&sm.bar_m2, 1); mbar_init(&sm.bar_m3, 1);
     fence_mbar_init();
   }
   if (warp == 0) tmem_alloc(&sm.tmem_base, 256);
@@ -66,12 +66,18 @@ r7c_intra_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ w, con
     const int unit = ch / NT;
     bi = unit / H; hi = unit % H; t0 = (ch % NT) * L;
   };
-  // the raw tiles of a chunk-head: q, k, a, b into the tiles that will hold their scaled versions, w into
-  // the O1 tile (written again only after MMA 2); rows past the end of the sequence arrive as zeros
+  // The raw tiles of a chunk-head (rows past the end of the sequence arrive as zeros).  w, needed first,
+  // lands in the A_qk tile, free from the end of the triangular inverse to the first epilogue of the next
+  // chunk-head; q, k, a, b, needed only after the prefix sums, land in the tiles that will hold their
+  // scaled versions once those have been copied out.
+  auto load_w = [&](int ch) {       // tid 0
+    int bi, hi, t0; coords(ch, bi, hi, t0);
+    mbar_expect_tx(&sm.bar_w, TILE_BYTES);
+    tma_load_4d(sm.aqk, &tmap_w, &sm.bar_w, 0, t0, hi, bi);
+  };
   auto load_in = [&](int ch) {      // tid 0
     int bi, hi, t0; coords(ch, bi, hi, t0);
-    mbar_expect_tx(&sm.bar_in, 5 * TILE_BYTES);
-    tma_load_4d(sm.o1, &tmap_w, &sm.bar_in, 0, t0, hi, bi);
+    mbar_expect_tx(&sm.bar_in, 4 * TILE_BYTES);
     tma_load_4d(sm.qt, &tmap_q, &sm.bar_in, 0, t0, hi, bi);
     tma_load_4d(sm.kt, &tmap_k, &sm.bar_in, 0, t0, hi, bi);
     tma_load_4d(sm.at, &tmap_a, &sm.bar_in, 0, t0, hi, bi);
@@ -99,7 +105,7 @@ r7c_intra_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ w, con
     mbar_expect_tx(&sm.bar_v, TILE_BYTES);
     tma_load_4d(sm.v, &tmap_v, &sm.bar_v, 0, t0, hi, bi);
   };
-  if (blockIdx.x < n_ch && tid == 0) { load_in(blockIdx.x); load_v(blockIdx.x); }
+  if (blockIdx.x < n_ch && tid == 0) { load_w(blockIdx.x); load_in(blockIdx.x); load_v(blockIdx.x); }
   // The two CTAs that share an SM would otherwise run their phases in lockstep and compete for the
   // same unit (shared-memory pipe during the triangular solve); start every other CTA half a
   // chunk-head late.
@@ -115,20 +121,13 @@ r7c_intra_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ w, con
 
     R7C_STAMP(0);
     if (next < n_ch) prefetch_rows(next);
-    // this thread's 2 x 16 bytes (8 channels of one token) of each raw tile; the scaled values go back to
-    // the same places (the previous chunk-head's W, U copies, committed last, may still be reading their
-    // tiles: those are rewritten only after MMA 1)
-    uint4 rw[2], rq[2], rk[2], ra[2], rb[2];
-    ok = mbar_wait(&sm.bar_in, par, status, 206) && ok;
+    // this thread's 2 x 16 bytes (8 channels of one token) of the raw w tile
+    uint4 rw[2];
+    ok = mbar_wait(&sm.bar_w, par, status, 206) && ok;
 #pragma unroll
     for (int n = 0; n < 2; ++n) {
       const int e = tid + 256 * n;
-      const uint32_t off = tile_chunk_off(e >> 3, e & 7);
-      rw[n] = *reinterpret_cast<const uint4*>(sm.o1 + off);
-      rq[n] = *reinterpret_cast<const uint4*>(sm.qt + off);
-      rk[n] = *reinterpret_cast<const uint4*>(sm.kt + off);
-      ra[n] = *reinterpret_cast<const uint4*>(sm.at + off);
-      rb[n] = *reinterpret_cast<const uint4*>(sm.bt + off);
+      rw[n] = *reinterpret_cast<const uint4*>(sm.aqk + tile_chunk_off(e >> 3, e & 7));
     }
     // ---- phase A: decay prefix sums and the four scaled operands; the prefix sum over tokens goes
     // through shared memory (the fp32 area that later holds A_ab).
@@ -169,6 +168,19 @@ r7c_intra_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ w, con
         const float tot0 = sm.qtot[0][tid] + sm.qtot[1][tid], tot1 = sm.qtot[2][tid] + sm.qtot[3][tid];
         ws_aux[(size_t)ch * AUX_FLOATS + tid] = __expf(fmaxf(tot0, -EXP_CLAMP));        // e^{gref}
         ws_aux[(size_t)ch * AUX_FLOATS + 64 + tid] = __expf(fmaxf(tot1, -EXP_CLAMP));   // e^{glast-gref}
+      }
+      // the raw q, k, a, b: each thread scales its own 2 x 16 bytes in place (the previous chunk-head's W, U
+      // copies, committed last, may still be reading their tiles: those are rewritten only after MMA 1)
+      uint4 rq[2], rk[2], ra[2], rb[2];
+      ok = mbar_wait(&sm.bar_in, par, status, 207) && ok;
+#pragma unroll
+      for (int n = 0; n < 2; ++n) {
+        const int e = tid + 256 * n;
+        const uint32_t off = tile_chunk_off(e >> 3, e & 7);
+        rq[n] = *reinterpret_cast<const uint4*>(sm.qt + off);
+        rk[n] = *reinterpret_cast<const uint4*>(sm.kt + off);
+        ra[n] = *reinterpret_cast<const uint4*>(sm.at + off);
+        rb[n] = *reinterpret_cast<const uint4*>(sm.bt + off);
       }
 #pragma unroll
       for (int n = 0; n < 2; ++n) {
@@ -431,6 +443,7 @@ r7c_intra_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ w, con
     R7C_STAMP(6);
     // ---- MMA 3: W = Ainv a~ (lower lane halves), U = Ainv Y (upper lane halves) -> TMEM columns 0..63
     if (tid == 0) {
+      if (ok && next < n_ch) load_w(next);      // the scratch area in the A_qk tile is free again
       tc_fence_after();
       umma_tile<64, 64, 0, 1>(tmem_addr(tm, 0, 0), smem_u32(sm.ainv), smem_u32(sm.at), false);
       umma_tile<64, 64, 0, 1>(tmem_addr(tm, 16, 0), smem_u32(sm.ainv), smem_u32(sm.y), false);
@@ -446,8 +459,7 @@ r7c_intra_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ w, con
     ok = mbar_wait(&sm.bar_m3, par, status, 204) && ok;
     tc_fence_after();
     R7C_STAMP(7);
-    // MMA 3 has read a~; once the copies issued with it have left q~, k~, b~, O1, the next raw tiles may land
-    if (tid == 0 && ok && next < n_ch) { bulk_wait_read(); load_in(next); }
+
     {
       // W -> the A_ak tile (free since MMA 2), U -> the Y tile (free: MMA 3 has completed)
       const int i = 16 * wq + (lane & 15);
@@ -468,6 +480,9 @@ r7c_intra_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ w, con
       bulk_store(out_tiles + S_W * TILE_BYTES, sm.aak, TILE_BYTES);
       bulk_store(out_tiles + S_U * TILE_BYTES, sm.y, TILE_BYTES);
       bulk_commit();
+      // every copy but the two just committed has left shared memory (q~, k~, a~, b~ among them), and MMA 3
+      // has read a~: the next raw tiles may land
+      if (next < n_ch) { bulk_wait_read_1(); load_in(next); }
     }
     R7C_STAMP(9);
   }
