@@ -88,6 +88,31 @@ int rwkvb200_rwkv7_step(const void* r, const void* w, const void* k, const void*
                         const float* state_in, int n_state, float* state_out, void* o,
                         int B, int H, int head_size, int dtype, void* stream);
 
+/* Packed variable-length batches (bfloat16 token tensors only).  The n_seq sequences lie end to end in
+ * token tensors of shape [1, total_len, H, 64]; sequence i is tokens seq_start[i] .. seq_start[i] +
+ * seq_len[i] - 1 (device arrays of n_seq int32, every length >= 1, no overlap) and max_len is the longest
+ * length.  States are per sequence: h0 [n_state, H, 64, 64] with n_state 0, 1 or n_seq, ht and d_h0
+ * [n_seq, H, 64, 64].  keep / kept as RWKVB200_ALGO_KEEP in the dense entry points; the workspace is
+ * sized by rwkvb200_rwkv7_varlen_workspace_bytes (every sequence owns ceil(max_len / 64) chunk slots).
+ * The reference carries cu_seqlens plumbing for this but has it disabled (torch_op.py:283,299;
+ * triton_kernel/chunk_A_fwd.py:47-56); the result equals running each sequence on its own. */
+size_t rwkvb200_rwkv7_varlen_workspace_bytes(int n_seq, int max_len, int H, int head_size, int keep);
+
+int rwkvb200_rwkv7_fwd_varlen(const void* r, const void* w, const void* k, const void* v,
+                              const void* a, const void* b,
+                              const int32_t* seq_start, const int32_t* seq_len, int n_seq, int max_len, int total_len,
+                              const float* h0, int n_state, void* o, float* ht,
+                              void* workspace, size_t workspace_bytes,
+                              int H, int head_size, int dtype, int keep, void* stream);
+
+int rwkvb200_rwkv7_bwd_varlen(const void* r, const void* w, const void* k, const void* v,
+                              const void* a, const void* b,
+                              const int32_t* seq_start, const int32_t* seq_len, int n_seq, int max_len, int total_len,
+                              const float* h0, int n_state, const void* d_o, const float* d_ht,
+                              void* dr, void* dw, void* dk, void* dv, void* da, void* db, float* d_h0,
+                              void* workspace, size_t workspace_bytes,
+                              int H, int head_size, int dtype, int kept, void* stream);
+
 /* One decode step in place on a state the caller keeps on the device across steps:
  * state [B,H,64,64] (value index before key index, like the reference's final_state), element type
  * state_dtype = RWKVB200_F32 (the reference's state type; same arithmetic as rwkvb200_rwkv7_step) or

@@ -171,6 +171,57 @@ int rwkvb200_rwkv7_bwd(const void* r, const void* w, const void* k, const void* 
   }
 }
 
+// ---- packed variable-length batches (chunked bf16 path only)
+size_t rwkvb200_rwkv7_varlen_workspace_bytes(int n_seq, int max_len, int H, int head_size, int keep) {
+  if (check_common(n_seq, max_len, H, head_size, RWKVB200_BF16)) return 0;
+  return r7c::fwd_workspace_bytes(n_seq, max_len, H, keep ? r7c::ALL_TILES : r7c::FWD_TILES);
+}
+
+int rwkvb200_rwkv7_fwd_varlen(const void* r, const void* w, const void* k, const void* v,
+                              const void* a, const void* b,
+                              const int32_t* seq_start, const int32_t* seq_len, int n_seq, int max_len, int total_len,
+                              const float* h0, int n_state, void* o, float* ht,
+                              void* workspace, size_t workspace_bytes,
+                              int H, int head_size, int dtype, int keep, void* stream) {
+  int e = check_common(n_seq, max_len, H, head_size, dtype);
+  if (e) return e;
+  if (dtype != RWKVB200_BF16) return RWKVB200_E_UNSUPPORTED;
+  if (total_len < max_len) return RWKVB200_E_SHAPE;
+  if (!r || !w || !k || !v || !a || !b || !o || !seq_start || !seq_len) return RWKVB200_E_NULL;
+  if (n_state != 0 && n_state != 1 && n_state != n_seq) return RWKVB200_E_SHAPE;
+  if (n_state != 0 && !h0) return RWKVB200_E_NULL;
+  const void* ps[] = {r, w, k, v, a, b, h0, o, ht, workspace};
+  for (const void* p : ps) if (p && !aligned16(p)) return RWKVB200_E_ALIGN;
+  const size_t need = rwkvb200_rwkv7_varlen_workspace_bytes(n_seq, max_len, H, head_size, keep);
+  if (workspace_bytes < need || !workspace) return RWKVB200_E_WORKSPACE;
+  return launch_rwkv7_chunked_fwd(r, w, k, v, a, b, n_state ? h0 : nullptr, n_state, o, ht, workspace,
+                                  n_seq, max_len, H, 0, keep != 0, (cudaStream_t)stream, seq_start, seq_len, total_len);
+}
+
+int rwkvb200_rwkv7_bwd_varlen(const void* r, const void* w, const void* k, const void* v,
+                              const void* a, const void* b,
+                              const int32_t* seq_start, const int32_t* seq_len, int n_seq, int max_len, int total_len,
+                              const float* h0, int n_state, const void* d_o, const float* d_ht,
+                              void* dr, void* dw, void* dk, void* dv, void* da, void* db, float* d_h0,
+                              void* workspace, size_t workspace_bytes,
+                              int H, int head_size, int dtype, int kept, void* stream) {
+  int e = check_common(n_seq, max_len, H, head_size, dtype);
+  if (e) return e;
+  if (dtype != RWKVB200_BF16) return RWKVB200_E_UNSUPPORTED;
+  if (total_len < max_len) return RWKVB200_E_SHAPE;
+  if (!r || !w || !k || !v || !a || !b || !d_o || !dr || !dw || !dk || !dv || !da || !db || !seq_start || !seq_len)
+    return RWKVB200_E_NULL;
+  if (n_state != 0 && n_state != 1 && n_state != n_seq) return RWKVB200_E_SHAPE;
+  if (n_state != 0 && !h0) return RWKVB200_E_NULL;
+  const void* ps[] = {r, w, k, v, a, b, h0, d_o, d_ht, dr, dw, dk, dv, da, db, d_h0, workspace};
+  for (const void* p : ps) if (p && !aligned16(p)) return RWKVB200_E_ALIGN;
+  const size_t need = rwkvb200_rwkv7_varlen_workspace_bytes(n_seq, max_len, H, head_size, 1);
+  if (workspace_bytes < need || !workspace) return RWKVB200_E_WORKSPACE;
+  return launch_rwkv7_chunked_bwd(r, w, k, v, a, b, n_state ? h0 : nullptr, n_state, d_o, d_ht,
+                                  dr, dw, dk, dv, da, db, d_h0, workspace, n_seq, max_len, H, 0, kept != 0,
+                                  (cudaStream_t)stream, seq_start, seq_len, total_len);
+}
+
 int rwkvb200_wkv6_fwd(const void* r, const void* k, const void* v, const void* w, const float* u,
                       const float* s0, int n_state, const int32_t* state_map,
                       void* y, float* sT, void* workspace, size_t workspace_bytes,

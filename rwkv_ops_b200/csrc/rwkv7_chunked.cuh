@@ -54,6 +54,40 @@ constexpr int AUX_FLOATS = 128;       // per chunk: e^{gref}[64], e^{glast-gref}
 
 inline int num_chunks(int T) { return (T + L - 1) / L; }
 
+// Which tokens a sequence occupies.  A dense batch has B sequences of Tn tokens, sequence bi in batch row
+// bi of the token tensors.  A packed variable-length batch (start != nullptr) has its sequences laid end
+// to end in ONE batch row; sequence bi is tokens start[bi] .. start[bi] + len[bi] - 1 of that row and Tn is
+// the longest length: every sequence owns ceil(Tn / 64) chunk slots of the workspace and uses the first
+// ceil(len / 64) of them.
+// The kernels are compiled for both cases (template parameter PACKED), so that the dense case pays nothing.
+struct SeqView {
+  const int* start;   // device pointers, one entry per sequence, or nullptr
+  const int* len;
+  int Tn;
+  template <bool PACKED> __device__ __forceinline__ int first(int bi) const {
+    if constexpr (PACKED) return __ldg(start + bi); else return 0;
+  }
+  template <bool PACKED> __device__ __forceinline__ int length(int bi) const {
+    if constexpr (PACKED) return __ldg(len + bi); else return Tn;
+  }
+  template <bool PACKED> __device__ __forceinline__ int row(int bi) const {
+    if constexpr (PACKED) return 0; else return bi;
+  }
+};
+
+// Rows 0 .. n_rows-1 of a swizzled bf16 tile to token rows `dst`, `dst + st`, ... (st in elements), by all
+// NTHREADS threads of the CTA: the store of a chunk whose last rows belong to the next packed sequence,
+// which a TMA store of the whole box would overwrite.
+template <int NTHREADS>
+__device__ __forceinline__ void store_tile_rows(__nv_bfloat16* dst, long long st, const unsigned char* tile,
+                                                int n_rows, int tid) {
+  for (int e = tid; e < 512; e += NTHREADS) {
+    const int row = e >> 3, cc = e & 7;
+    if (row < n_rows)
+      *reinterpret_cast<uint4*>(dst + row * st + 8 * cc) = *reinterpret_cast<const uint4*>(tile + tc::tile_chunk_off(row, cc));
+  }
+}
+
 struct Workspace {
   unsigned char* tiles;   // [n_chunks_total][tiles_per_chunk][8192]
   float* aux;             // [n_chunks_total][128]
@@ -80,13 +114,17 @@ inline Workspace carve(void* ws, int B, int T, int H, int tiles_per_chunk) {
 }  // namespace r7c
 
 // Backward of the chunked path; `workspace` must hold fwd_workspace_bytes(B, T, H, ALL_TILES).
+// Packed variable-length batches: seq_start / seq_len are device arrays of B entries, Tn the longest length
+// and T_total the number of tokens in the one batch row; dense batches pass nullptr, nullptr, 0.
 int launch_rwkv7_chunked_bwd(const void* r, const void* w, const void* k, const void* v, const void* a, const void* b,
                              const float* h0, int n_state, const void* d_o, const float* d_ht,
                              void* dr, void* dw, void* dk, void* dv, void* da, void* db, float* d_h0,
-                             void* workspace, int B, int Tn, int H, int head_first, bool kept, cudaStream_t st);
+                             void* workspace, int B, int Tn, int H, int head_first, bool kept, cudaStream_t st,
+                             const int* seq_start = nullptr, const int* seq_len = nullptr, int T_total = 0);
 
 int launch_rwkv7_chunked_fwd(const void* r, const void* w, const void* k, const void* v, const void* a, const void* b,
                              const float* h0, int n_state, void* o, float* ht, void* workspace,
-                             int B, int Tn, int H, int head_first, bool keep_for_bwd, cudaStream_t st);
+                             int B, int Tn, int H, int head_first, bool keep_for_bwd, cudaStream_t st,
+                             const int* seq_start = nullptr, const int* seq_len = nullptr, int T_total = 0);
 
 }  // namespace rwkvb200

@@ -38,13 +38,15 @@ struct PreSmem {
   uint32_t tmem_base;
 };
 
+template <bool PACKED>
 __global__ void __launch_bounds__(128)
 r7c_bwd_pre_kernel(const __grid_constant__ CUtensorMap tmap_do, unsigned char* __restrict__ ws_tiles,
-                   int tiles_per_chunk, int H, int NT, int* status) {
+                   int tiles_per_chunk, SeqView sv, int H, int NT, int* status) {
   extern __shared__ unsigned char smem_raw[];
   PreSmem& sm = *reinterpret_cast<PreSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int ch = blockIdx.x, unit = ch / NT, cidx = ch % NT, bi = unit / H, hi = unit % H;
+  if (cidx * L >= sv.length<PACKED>(bi)) return;      // a chunk slot past the end of a packed sequence
   unsigned char* tiles = ws_tiles + (size_t)ch * tiles_per_chunk * TILE_BYTES;
   const int row = 16 * warp + (lane & 15);
   const bool lo = lane < 16;
@@ -63,7 +65,7 @@ r7c_bwd_pre_kernel(const __grid_constant__ CUtensorMap tmap_do, unsigned char* _
     bulk_load(sm.ainv, tiles + S_AINV * TILE_BYTES, TILE_BYTES, &sm.bar_ld);
     bulk_load(sm.bt, tiles + S_BT * TILE_BYTES, TILE_BYTES, &sm.bar_ld);
     bulk_load(sm.aqb, tiles + S_AQB * TILE_BYTES, TILE_BYTES, &sm.bar_ld);
-    tma_load_4d(sm.dout, &tmap_do, &sm.bar_ld, 0, cidx * L, hi, bi);
+    tma_load_4d(sm.dout, &tmap_do, &sm.bar_ld, 0, sv.first<PACKED>(bi) + cidx * L, hi, sv.row<PACKED>(bi));
   }
   bool ok = mbar_wait(&sm.bar_ld, 0, status, 301);
   if (tid == 0 && ok) {
@@ -138,15 +140,18 @@ struct BScanSmem {
   uint32_t tmem_base;
 };
 
+template <bool PACKED>
 __global__ void __launch_bounds__(256, 2)
 r7c_bwd_scan_kernel(const __grid_constant__ CUtensorMap tmap_do, unsigned char* __restrict__ ws_tiles,
                     const float* __restrict__ ws_aux, int tiles_per_chunk, const float* __restrict__ d_ht,
-                    float* __restrict__ d_h0, int H, int NT, int* status) {
+                    float* __restrict__ d_h0, SeqView sv, int H, int NT_slots, int* status) {
   extern __shared__ unsigned char smem_raw[];
   BScanSmem& sm = *reinterpret_cast<BScanSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int unit = blockIdx.x, bi = unit / H, hi = unit % H;
-  const size_t ch0 = (size_t)unit * NT;
+  const size_t ch0 = (size_t)unit * NT_slots;
+  const int NT = (sv.length<PACKED>(bi) + L - 1) / L;      // chunks of this sequence
+  const int tb = sv.first<PACKED>(bi), brow = sv.row<PACKED>(bi);
   const int wq = warp & 3, hsel = warp >> 2, c0 = 32 * hsel;
   const int row = 16 * wq + (lane & 15);
   const bool state_lane = lane < 16;
@@ -171,7 +176,7 @@ r7c_bwd_scan_kernel(const __grid_constant__ CUtensorMap tmap_do, unsigned char* 
     bulk_load(s.b2, tiles + S_B2 * TILE_BYTES, 2 * TILE_BYTES, &sm.bar_full[n & 1]);
     bulk_load(s.at, tiles + S_AT * TILE_BYTES, TILE_BYTES, &sm.bar_full[n & 1]);
     bulk_load(s.qt, tiles + S_QT * TILE_BYTES, TILE_BYTES, &sm.bar_full[n & 1]);
-    tma_load_4d(s.dout, &tmap_do, &sm.bar_full[n & 1], 0, c * L, hi, bi);
+    tma_load_4d(s.dout, &tmap_do, &sm.bar_full[n & 1], 0, tb + c * L, hi, brow);
   };
   if (tid == 0) {
     issue_loads(0);
@@ -294,6 +299,7 @@ struct FinalSmem {
 // rows wait in registers, so only the first chunk-head of a CTA pays the load latency.
 // 256 threads: warp w reads TMEM lanes 32*(w&3).. (its row), and the two warps that share a lane
 // window split the columns (hsel = w>>2), so every elementwise phase is spread over 8 warps.
+template <bool PACKED>
 __global__ void __launch_bounds__(256)
 r7c_bwd_final_kernel(const bf16* __restrict__ w, const __grid_constant__ CUtensorMap tmap_do,
                      const __grid_constant__ CUtensorMap tmap_v, const unsigned char* __restrict__ ws_tiles,
@@ -301,7 +307,9 @@ r7c_bwd_final_kernel(const bf16* __restrict__ w, const __grid_constant__ CUtenso
                      const __grid_constant__ CUtensorMap tmap_dw, const __grid_constant__ CUtensorMap tmap_dk,
                      const __grid_constant__ CUtensorMap tmap_dv, const __grid_constant__ CUtensorMap tmap_da,
                      const __grid_constant__ CUtensorMap tmap_db,
-                     int Tn, int H, int NT, int n_ch, TokLayout lay, int* status, long long* dbg) {
+                     bf16* __restrict__ dq_rows, bf16* __restrict__ dw_rows, bf16* __restrict__ dk_rows,
+                     bf16* __restrict__ dv_rows, bf16* __restrict__ da_rows, bf16* __restrict__ db_rows,
+                     SeqView sv, int H, int NT, int n_ch, TokLayout lay, int* status, long long* dbg) {
 #define R7C_STAMP(n) do { if (dbg && tid == 0 && blockIdx.x == gridDim.x / 2 && it == 1) dbg[n] = clock64(); } while (0)
   extern __shared__ unsigned char smem_raw[];
   FinalSmem& sm = *reinterpret_cast<FinalSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -326,8 +334,8 @@ r7c_bwd_final_kernel(const bf16* __restrict__ w, const __grid_constant__ CUtenso
     int bi, hi, t0; coords(ch, bi, hi, t0);
     const unsigned char* tiles = ws_tiles + (size_t)ch * tiles_per_chunk * TILE_BYTES;
     mbar_expect_tx(&sm.bar_lda, 8 * TILE_BYTES);
-    tma_load_4d(sm.dout, &tmap_do, &sm.bar_lda, 0, t0, hi, bi);
-    tma_load_4d(sm.v, &tmap_v, &sm.bar_lda, 0, t0, hi, bi);
+    tma_load_4d(sm.dout, &tmap_do, &sm.bar_lda, 0, sv.first<PACKED>(bi) + t0, hi, sv.row<PACKED>(bi));
+    tma_load_4d(sm.v, &tmap_v, &sm.bar_lda, 0, sv.first<PACKED>(bi) + t0, hi, sv.row<PACKED>(bi));
     bulk_load(sm.dz, tiles + S_DZ * TILE_BYTES, TILE_BYTES, &sm.bar_lda);
     bulk_load(sm.sa, tiles + S_SA * TILE_BYTES, TILE_BYTES, &sm.bar_lda);
     bulk_load(sm.aqk, tiles + S_AQK * TILE_BYTES, 2 * TILE_BYTES, &sm.bar_lda);
@@ -348,14 +356,15 @@ r7c_bwd_final_kernel(const bf16* __restrict__ w, const __grid_constant__ CUtenso
     int bi, hi, t0; coords(ch, bi, hi, t0);
     const unsigned char* tiles = ws_tiles + (size_t)ch * tiles_per_chunk * TILE_BYTES;
     if (lane == 0) {
-      tma_prefetch_4d(&tmap_do, 0, t0, hi, bi);
-      tma_prefetch_4d(&tmap_v, 0, t0, hi, bi);
+      tma_prefetch_4d(&tmap_do, 0, sv.first<PACKED>(bi) + t0, hi, sv.row<PACKED>(bi));
+      tma_prefetch_4d(&tmap_v, 0, sv.first<PACKED>(bi) + t0, hi, sv.row<PACKED>(bi));
       bulk_prefetch_l2(tiles + S_QT * TILE_BYTES, 3 * TILE_BYTES);     // q~, k~, b~
       bulk_prefetch_l2(tiles + S_AT * TILE_BYTES, 3 * TILE_BYTES);     // a~, A_qk, A_ak
       bulk_prefetch_l2(tiles + S_SA * TILE_BYTES, 3 * TILE_BYTES);     // sa, h~0, X
       bulk_prefetch_l2(tiles + S_DZ * TILE_BYTES, 2 * TILE_BYTES);     // dz, dh^
     }
-    const long long base = bi * lay.sb + hi * lay.sh;
+    const int Tn = sv.length<PACKED>(bi);
+    const long long base = sv.row<PACKED>(bi) * lay.sb + hi * lay.sh + sv.first<PACKED>(bi) * lay.st;
 #pragma unroll
     for (int n = 0; n < 2; ++n) {
       const int tok = t0 + lane + 32 * n;
@@ -364,7 +373,8 @@ r7c_bwd_final_kernel(const bf16* __restrict__ w, const __grid_constant__ CUtenso
   };
   auto load_w = [&](int ch, uint4 (&rw)[2]) {   // all threads: 2 x 8 channels of the chunk's w rows
     int bi, hi, t0; coords(ch, bi, hi, t0);
-    const long long base = bi * lay.sb + hi * lay.sh;
+    const int Tn = sv.length<PACKED>(bi);
+    const long long base = sv.row<PACKED>(bi) * lay.sb + hi * lay.sh + sv.first<PACKED>(bi) * lay.st;
 #pragma unroll
     for (int n = 0; n < 2; ++n) {
       const int e = tid + 256 * n, row = e >> 3, cc = e & 7, tok = t0 + row;
@@ -373,20 +383,39 @@ r7c_bwd_final_kernel(const bf16* __restrict__ w, const __grid_constant__ CUtenso
     }
   };
 
+  // chunk slots past the end of a (packed) sequence are skipped
+  auto empty = [&](int ch) {
+    if constexpr (!PACKED) return false;      // a dense batch has no empty slots
+    int bi, hi, t0; coords(ch, bi, hi, t0);
+    return t0 >= sv.length<PACKED>(bi);
+  };
+  auto advance = [&](int ch) {
+    do { ch += gridDim.x; } while (ch < n_ch && empty(ch));
+    return ch;
+  };
+  int ch_first = blockIdx.x;
+  if (ch_first < n_ch && empty(ch_first)) ch_first = advance(ch_first);
+
   uint4 rw[2];
-  if (blockIdx.x < n_ch) {
-    if (tid == 0) { load_group_a(blockIdx.x); load_group_b(blockIdx.x); }
-    load_w(blockIdx.x, rw);
-    if (warp == 1 && blockIdx.x + gridDim.x < n_ch) prefetch_l2(blockIdx.x + gridDim.x);
+  if (ch_first < n_ch) {
+    if (tid == 0) { load_group_a(ch_first); load_group_b(ch_first); }
+    load_w(ch_first, rw);
+    const int second = advance(ch_first);
+    if (warp == 1 && second < n_ch) prefetch_l2(second);
   }
 
   bool ok = true;
   int it = 0;
-  for (int ch = blockIdx.x; ch < n_ch && ok; ch += gridDim.x, ++it) {
+  for (int ch = ch_first, next; ch < n_ch && ok; ch = next, ++it) {
     int bi, hi, t0; coords(ch, bi, hi, t0);
+    const int Tn = sv.length<PACKED>(bi);
+    // in a packed batch the last rows of a sequence's last chunk belong to the next sequence: such a chunk
+    // is stored row by row instead of by TMA boxes
+    const bool row_stores = PACKED && t0 + L > Tn;
+    const long long out_base = sv.row<PACKED>(bi) * lay.sb + hi * lay.sh + (long long)(sv.first<PACKED>(bi) + t0) * lay.st;
     const unsigned char* tiles = ws_tiles + (size_t)ch * tiles_per_chunk * TILE_BYTES;
     const uint32_t par = it & 1;
-    const int next = ch + gridDim.x;
+    next = advance(ch);
     R7C_STAMP(16);
 
     // ---- g of every (token, channel), from the w rows already in registers
@@ -500,8 +529,14 @@ r7c_bwd_final_kernel(const bf16* __restrict__ w, const __grid_constant__ CUtenso
       umma_tile<128, 64, 1, 1>(tmem_addr(tm, 0, 64), smem_u32(sm.daak), smem_u32(sm.at), true, 2 * TILE_BYTES);   // + [dA_ak|dA_ab]^T a~
       umma_tile<128, 64, 0, 0>(tmem_addr(tm, 0, 64), smem_u32(sm.v), smem_u32(sm.dhh), true);          // + [v;sa] dh^^T
       umma_commit(&sm.bar_m2);
-      tma_store_4d(&tmap_dv, sm.aqk, 0, t0, hi, bi);
-      bulk_commit();
+      if (!row_stores) {
+        tma_store_4d(&tmap_dv, sm.aqk, 0, sv.first<PACKED>(bi) + t0, hi, sv.row<PACKED>(bi));
+        bulk_commit();
+      }
+    }
+    if (row_stores && ok) {
+      store_tile_rows<256>(dv_rows + out_base, lay.st, sm.aqk, Tn - t0, tid);
+      __syncthreads();      // the A_qk tile is loaded again below
     }
     ok = mbar_wait(&sm.bar_m2, par, status, 323) && ok;
     tc_fence_after();
@@ -510,7 +545,8 @@ r7c_bwd_final_kernel(const bf16* __restrict__ w, const __grid_constant__ CUtenso
     if (next < n_ch) {
       if (tid == 0 && ok) { bulk_wait_read(); load_group_a(next); }
       load_w(next, rw);
-      if (warp == 1 && next + (int)gridDim.x < n_ch) prefetch_l2(next + gridDim.x);
+      const int after = advance(next);
+      if (warp == 1 && after < n_ch) prefetch_l2(after);
     }
 
     // ---- epilogue.  Row r < 64 holds dq~_i and dk~_i (token i = r), row r >= 64 holds da~_i, db~_i; the
@@ -560,12 +596,21 @@ r7c_bwd_final_kernel(const bf16* __restrict__ w, const __grid_constant__ CUtenso
     fence_async_smem();
     ok = __syncthreads_and(ok);
     R7C_STAMP(22);
+    if (row_stores && ok) {
+      store_tile_rows<256>(dq_rows + out_base, lay.st, sm.stage[0], Tn - t0, tid);
+      store_tile_rows<256>(dk_rows + out_base, lay.st, sm.stage[1], Tn - t0, tid);
+      store_tile_rows<256>(da_rows + out_base, lay.st, sm.stage[2], Tn - t0, tid);
+      store_tile_rows<256>(db_rows + out_base, lay.st, sm.stage[3], Tn - t0, tid);
+    }
     if (tid == 0 && ok) {
-      tma_store_4d(&tmap_dq, sm.stage[0], 0, t0, hi, bi);
-      tma_store_4d(&tmap_dk, sm.stage[1], 0, t0, hi, bi);
-      tma_store_4d(&tmap_da, sm.stage[2], 0, t0, hi, bi);
-      tma_store_4d(&tmap_db, sm.stage[3], 0, t0, hi, bi);
-      bulk_commit();
+      if (!row_stores) {
+        const int tt = sv.first<PACKED>(bi) + t0, br = sv.row<PACKED>(bi);
+        tma_store_4d(&tmap_dq, sm.stage[0], 0, tt, hi, br);
+        tma_store_4d(&tmap_dk, sm.stage[1], 0, tt, hi, br);
+        tma_store_4d(&tmap_da, sm.stage[2], 0, tt, hi, br);
+        tma_store_4d(&tmap_db, sm.stage[3], 0, tt, hi, br);
+        bulk_commit();
+      }
       if (next < n_ch) load_group_b(next);      // q~, a~, k~, b~ were last read by the epilogue above
     }
     // reverse inclusive prefix over tokens, per channel; thread = (channel, quarter)
@@ -592,7 +637,12 @@ r7c_bwd_final_kernel(const bf16* __restrict__ w, const __grid_constant__ CUtenso
     fence_async_smem();
     tc_fence_before();
     ok = __syncthreads_and(ok);
-    if (tid == 0 && ok) { tma_store_4d(&tmap_dw, sm.stage[4], 0, t0, hi, bi); bulk_commit(); }
+    if (row_stores) {
+      if (ok) store_tile_rows<256>(dw_rows + out_base, lay.st, sm.stage[4], Tn - t0, tid);
+    } else if (tid == 0 && ok) {
+      tma_store_4d(&tmap_dw, sm.stage[4], 0, sv.first<PACKED>(bi) + t0, hi, sv.row<PACKED>(bi));
+      bulk_commit();
+    }
     R7C_STAMP(23);
   }
   if (tid == 0) bulk_wait_all();
@@ -607,60 +657,74 @@ r7c_bwd_final_kernel(const bf16* __restrict__ w, const __grid_constant__ CUtenso
 int launch_rwkv7_chunked_bwd(const void* r, const void* w, const void* k, const void* v, const void* a, const void* b,
                              const float* h0, int n_state, const void* d_o, const float* d_ht,
                              void* dr, void* dw, void* dk, void* dv, void* da, void* db, float* d_h0,
-                             void* workspace, int B, int Tn, int H, int head_first, bool kept, cudaStream_t st) {
+                             void* workspace, int B, int Tn, int H, int head_first, bool kept, cudaStream_t st,
+                             const int* seq_start, const int* seq_len, int T_total) {
   using namespace r7c;
   typedef __nv_bfloat16 bf16;
   int e = RWKVB200_OK;
   if (!kept) {   // the workspace does not hold a forward pass yet: recompute it from the inputs
     e = launch_rwkv7_chunked_fwd(r, w, k, v, a, b, h0, n_state, nullptr, nullptr, workspace, B, Tn, H, head_first,
-                                 true, st);
+                                 true, st, seq_start, seq_len, T_total);
     if (e) return e;
   }
   int* status = device_status_ptr();
   if (!status) { last_cuda_error_slot() = 99999; return RWKVB200_E_CUDA; }
   CUtensorMap tmap_do, tmap_v, tmap_out[6];
-  e = make_token_tensor_map(&tmap_do, d_o, B, Tn, H, head_first);
+  const SeqView sv{seq_start, seq_len, Tn};
+  const int mapB = seq_start ? 1 : B, mapT = seq_start ? T_total : Tn;   // shape of the token tensors
+  e = make_token_tensor_map(&tmap_do, d_o, mapB, mapT, H, head_first);
   if (e) return e;
-  e = make_token_tensor_map(&tmap_v, v, B, Tn, H, head_first);
+  e = make_token_tensor_map(&tmap_v, v, mapB, mapT, H, head_first);
   if (e) return e;
   void* outs[6] = {dr, dw, dk, dv, da, db};
   for (int i = 0; i < 6; ++i) {
-    e = make_token_tensor_map(&tmap_out[i], outs[i], B, Tn, H, head_first);
+    e = make_token_tensor_map(&tmap_out[i], outs[i], mapB, mapT, H, head_first);
     if (e) return e;
   }
   const int NT = num_chunks(Tn);
   Workspace ws = carve(workspace, B, Tn, H, ALL_TILES);
-  TokLayout lay(Tn, H, head_first);
+  TokLayout lay(mapT, H, head_first);
+  // every kernel exists for dense batches and for packed variable-length ones
+#define R7C_DISPATCH_PACKED(...) do { if (seq_start) { constexpr bool P = true; __VA_ARGS__; } else { constexpr bool P = false; __VA_ARGS__; } } while (0)
   {
     const int smem = (int)sizeof(PreSmem) + 1024;
-    if (cuda_ok(cudaFuncSetAttribute(r7c_bwd_pre_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem))) return RWKVB200_E_CUDA;
     ProfScope prof("r7c_bwd_pre_kernel", st);
-    r7c_bwd_pre_kernel<<<B * H * NT, 128, smem, st>>>(tmap_do, ws.tiles, ALL_TILES, H, NT, status);
+    R7C_DISPATCH_PACKED(
+      if (cuda_ok(cudaFuncSetAttribute(r7c_bwd_pre_kernel<P>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)))
+        return RWKVB200_E_CUDA;
+      r7c_bwd_pre_kernel<P><<<B * H * NT, 128, smem, st>>>(tmap_do, ws.tiles, ALL_TILES, sv, H, NT, status));
   }
   e = check_launch();
   if (e) return e;
   {
     const int smem = (int)sizeof(BScanSmem) + 1024;
-    if (cuda_ok(cudaFuncSetAttribute(r7c_bwd_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem))) return RWKVB200_E_CUDA;
     ProfScope prof("r7c_bwd_scan_kernel", st);
-    r7c_bwd_scan_kernel<<<B * H, 256, smem, st>>>(tmap_do, ws.tiles, ws.aux, ALL_TILES, d_ht, d_h0, H, NT, status);
+    R7C_DISPATCH_PACKED(
+      if (cuda_ok(cudaFuncSetAttribute(r7c_bwd_scan_kernel<P>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)))
+        return RWKVB200_E_CUDA;
+      r7c_bwd_scan_kernel<P><<<B * H, 256, smem, st>>>(tmap_do, ws.tiles, ws.aux, ALL_TILES, d_ht, d_h0, sv, H, NT,
+                                                       status));
   }
   e = check_launch();
   if (e) return e;
   {
     const int smem = (int)sizeof(FinalSmem) + 1024;
-    if (cuda_ok(cudaFuncSetAttribute(r7c_bwd_final_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem))) return RWKVB200_E_CUDA;
     ProfScope prof("r7c_bwd_final_kernel", st);
     const int n_ch = B * H * NT;
     int dev = 0, sms = 0;
     if (cuda_ok(cudaGetDevice(&dev)) || cuda_ok(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)))
       return RWKVB200_E_CUDA;
     const int grid = n_ch < sms ? n_ch : sms;     // persistent: one CTA per SM
-    r7c_bwd_final_kernel<<<grid, 256, smem, st>>>((const bf16*)w, tmap_do, tmap_v, ws.tiles, ALL_TILES,
-                                                   tmap_out[0], tmap_out[1], tmap_out[2], tmap_out[3],
-                                                   tmap_out[4], tmap_out[5], Tn, H, NT, n_ch, lay, status,
-                                                   debug_stamp_buffer());
+    R7C_DISPATCH_PACKED(
+      if (cuda_ok(cudaFuncSetAttribute(r7c_bwd_final_kernel<P>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)))
+        return RWKVB200_E_CUDA;
+      r7c_bwd_final_kernel<P><<<grid, 256, smem, st>>>((const bf16*)w, tmap_do, tmap_v, ws.tiles, ALL_TILES,
+                                                       tmap_out[0], tmap_out[1], tmap_out[2], tmap_out[3],
+                                                       tmap_out[4], tmap_out[5], (bf16*)dr, (bf16*)dw, (bf16*)dk,
+                                                       (bf16*)dv, (bf16*)da, (bf16*)db, sv, H, NT, n_ch, lay, status,
+                                                       debug_stamp_buffer()));
   }
+#undef R7C_DISPATCH_PACKED
   return check_launch();
 }
 

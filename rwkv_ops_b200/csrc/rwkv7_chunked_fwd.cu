@@ -37,6 +37,7 @@ struct IntraSmem {
 // MMA 2 has read the current one, and the rows of the one after that are asked into L2.
 // 256 threads: warp w reads TMEM lanes 32*(w&3).. and the two warps that share a lane window split
 // the columns (hsel = w>>2); the triangular solve runs on warps 0-1 while the other warps drain MMA 2.
+template <bool PACKED>
 __global__ void __launch_bounds__(256, 2)
 r7c_intra_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ w, const bf16* __restrict__ k,
                      const bf16* __restrict__ a, const bf16* __restrict__ b,
@@ -45,7 +46,7 @@ r7c_intra_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ w, con
                      const __grid_constant__ CUtensorMap tmap_b,
                      const __grid_constant__ CUtensorMap tmap_v, unsigned char* __restrict__ ws_tiles,
                      float* __restrict__ ws_aux, int tiles_per_chunk, int keep_for_bwd,
-                     int Tn, int H, int NT, int n_ch, TokLayout lay, int* status, long long* dbg) {
+                     SeqView sv, int H, int NT, int n_ch, TokLayout lay, int* status, long long* dbg) {
 #define R7C_STAMP(n) do { if (dbg && tid == 0 && blockIdx.x == gridDim.x / 2 && it == 1) dbg[n] = clock64(); } while (0)
   extern __shared__ unsigned char smem_raw[];
   IntraSmem& sm = *reinterpret_cast<IntraSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -73,20 +74,32 @@ r7c_intra_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ w, con
   auto load_w = [&](int ch) {       // tid 0
     int bi, hi, t0; coords(ch, bi, hi, t0);
     mbar_expect_tx(&sm.bar_w, TILE_BYTES);
-    tma_load_4d(sm.aqk, &tmap_w, &sm.bar_w, 0, t0, hi, bi);
+    tma_load_4d(sm.aqk, &tmap_w, &sm.bar_w, 0, sv.first<PACKED>(bi) + t0, hi, sv.row<PACKED>(bi));
   };
   auto load_in = [&](int ch) {      // tid 0
     int bi, hi, t0; coords(ch, bi, hi, t0);
+    const int tt = sv.first<PACKED>(bi) + t0, br = sv.row<PACKED>(bi);
     mbar_expect_tx(&sm.bar_in, 4 * TILE_BYTES);
-    tma_load_4d(sm.qt, &tmap_q, &sm.bar_in, 0, t0, hi, bi);
-    tma_load_4d(sm.kt, &tmap_k, &sm.bar_in, 0, t0, hi, bi);
-    tma_load_4d(sm.at, &tmap_a, &sm.bar_in, 0, t0, hi, bi);
-    tma_load_4d(sm.bt, &tmap_b, &sm.bar_in, 0, t0, hi, bi);
+    tma_load_4d(sm.qt, &tmap_q, &sm.bar_in, 0, tt, hi, br);
+    tma_load_4d(sm.kt, &tmap_k, &sm.bar_in, 0, tt, hi, br);
+    tma_load_4d(sm.at, &tmap_a, &sm.bar_in, 0, tt, hi, br);
+    tma_load_4d(sm.bt, &tmap_b, &sm.bar_in, 0, tt, hi, br);
+  };
+  // chunk slots past the end of a (packed) sequence are skipped
+  auto empty = [&](int ch) {
+    if constexpr (!PACKED) return false;      // a dense batch has no empty slots
+    int bi, hi, t0; coords(ch, bi, hi, t0);
+    return t0 >= sv.length<PACKED>(bi);
+  };
+  auto advance = [&](int ch) {
+    do { ch += gridDim.x; } while (ch < n_ch && empty(ch));
+    return ch;
   };
   // Ask for a chunk-head's token rows to be brought into L2, ahead of the TMA loads above.
   auto prefetch_rows = [&](int ch) {
     int bi, hi, t0; coords(ch, bi, hi, t0);
-    const long long base = bi * lay.sb + hi * lay.sh;
+    const int Tn = sv.length<PACKED>(bi);
+    const long long base = sv.row<PACKED>(bi) * lay.sb + hi * lay.sh + sv.first<PACKED>(bi) * lay.st;
 #pragma unroll
     for (int n = 0; n < 2; ++n) {
       const int e = tid + 256 * n, row = e >> 3, cc = e & 7, tok = t0 + row;
@@ -103,9 +116,11 @@ r7c_intra_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ w, con
   auto load_v = [&](int ch) {   // tid 0
     int bi, hi, t0; coords(ch, bi, hi, t0);
     mbar_expect_tx(&sm.bar_v, TILE_BYTES);
-    tma_load_4d(sm.v, &tmap_v, &sm.bar_v, 0, t0, hi, bi);
+    tma_load_4d(sm.v, &tmap_v, &sm.bar_v, 0, sv.first<PACKED>(bi) + t0, hi, sv.row<PACKED>(bi));
   };
-  if (blockIdx.x < n_ch && tid == 0) { load_w(blockIdx.x); load_in(blockIdx.x); load_v(blockIdx.x); }
+  int ch_first = blockIdx.x;
+  if (ch_first < n_ch && empty(ch_first)) ch_first = advance(ch_first);
+  if (ch_first < n_ch && tid == 0) { load_w(ch_first); load_in(ch_first); load_v(ch_first); }
   // The two CTAs that share an SM would otherwise run their phases in lockstep and compete for the
   // same unit (shared-memory pipe during the triangular solve); start every other CTA half a
   // chunk-head late.
@@ -113,11 +128,12 @@ r7c_intra_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ w, con
 
   bool ok = true;
   int it = 0;
-  for (int ch = blockIdx.x; ch < n_ch && ok; ch += gridDim.x, ++it) {
+  for (int ch = ch_first, next; ch < n_ch && ok; ch = next, ++it) {
     int bi, hi, t0; coords(ch, bi, hi, t0);
+    const int Tn = sv.length<PACKED>(bi);
     unsigned char* out_tiles = ws_tiles + (size_t)ch * tiles_per_chunk * TILE_BYTES;
     const uint32_t par = it & 1;
-    const int next = ch + gridDim.x;
+    next = advance(ch);
 
     R7C_STAMP(0);
     if (next < n_ch) prefetch_rows(next);
@@ -181,6 +197,9 @@ r7c_intra_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ w, con
         rk[n] = *reinterpret_cast<const uint4*>(sm.kt + off);
         ra[n] = *reinterpret_cast<const uint4*>(sm.at + off);
         rb[n] = *reinterpret_cast<const uint4*>(sm.bt + off);
+        if (PACKED && t0 + (e >> 3) >= Tn) {      // in a packed batch these rows belong to the next sequence
+          rq[n] = make_uint4(0u, 0u, 0u, 0u); rk[n] = rq[n]; ra[n] = rq[n]; rb[n] = rq[n];
+        }
       }
 #pragma unroll
       for (int n = 0; n < 2; ++n) {
@@ -527,12 +546,13 @@ struct ScanSmem {
   uint32_t tmem_base;
 };
 
-template <int STAGES>
+template <int STAGES, bool PACKED>
 __global__ void __launch_bounds__(256, 3 - STAGES)
 r7c_scan_fwd_kernel(const __grid_constant__ CUtensorMap tmap_v, const unsigned char* __restrict__ ws_tiles,
                     const float* __restrict__ ws_aux, int tiles_per_chunk, unsigned char* __restrict__ bwd_tiles,
                     const float* __restrict__ h0, int n_state, const __grid_constant__ CUtensorMap tmap_o,
-                    int write_o, float* __restrict__ ht, int Tn, int H, int NT, int* status, long long* dbg) {
+                    int write_o, float* __restrict__ ht, bf16* __restrict__ o_rows, SeqView sv, int H, int NT_slots,
+                    TokLayout lay, int* status, long long* dbg) {
 #define R7C_STAMP(n) do { if (dbg && tid == 0 && blockIdx.x == gridDim.x / 2 && c == 2) dbg[n] = clock64(); } while (0)
   extern __shared__ unsigned char smem_raw[];
   ScanSmem<STAGES>& sm =
@@ -540,7 +560,9 @@ r7c_scan_fwd_kernel(const __grid_constant__ CUtensorMap tmap_v, const unsigned c
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int wq = warp & 3, hsel = warp >> 2, c0 = 32 * hsel;
   const int unit = blockIdx.x, bi = unit / H, hi = unit % H;
-  const size_t ch0 = (size_t)unit * NT;
+  const size_t ch0 = (size_t)unit * NT_slots;
+  const int Tn = sv.length<PACKED>(bi), tb = sv.first<PACKED>(bi), brow = sv.row<PACKED>(bi);
+  const int NT = (Tn + L - 1) / L;           // chunks of this sequence (at least one)
   const int row = 16 * wq + (lane & 15);     // state row k (lanes 0-15) or token row i (lanes 16-31)
   const bool state_lane = lane < 16;
 
@@ -564,7 +586,7 @@ r7c_scan_fwd_kernel(const __grid_constant__ CUtensorMap tmap_v, const unsigned c
     bulk_load(g.qt, tiles + S_QT * TILE_BYTES, 2 * TILE_BYTES, bar);
     if constexpr (STAGES == 2) bulk_load(g.o1, tiles + S_O1 * TILE_BYTES, 3 * TILE_BYTES, bar);
     else                       bulk_load(g.w, tiles + S_W * TILE_BYTES, TILE_BYTES, bar);
-    tma_load_4d(g.v, &tmap_v, bar, 0, c * L, hi, bi);
+    tma_load_4d(g.v, &tmap_v, bar, 0, tb + c * L, hi, brow);
   };
   auto issue_g2 = [&](int c) {      // tid 0
     const unsigned char* tiles = ws_tiles + (ch0 + c) * (size_t)tiles_per_chunk * TILE_BYTES;
@@ -729,10 +751,15 @@ r7c_scan_fwd_kernel(const __grid_constant__ CUtensorMap tmap_v, const unsigned c
       bulk_store(bwd_tiles + ((ch0 + c) * (size_t)tiles_per_chunk + S_X) * TILE_BYTES, sm.xt, TILE_BYTES);
       bulk_commit();
     }
-    if (write_o && tid == 0 && ok) {     // rows past the end of the sequence are clipped by the TMA store
-      tma_store_4d(&tmap_o, sm.ot[c & 1], 0, t0, hi, bi);
-      bulk_commit();
-      bulk_wait_read_1();                // the buffer of the previous chunk is free again
+    if (write_o && ok) {
+      if (PACKED && t0 + L > Tn) {  // the last rows of the box belong to the next sequence: row by row
+        store_tile_rows<256>(o_rows + brow * lay.sb + hi * lay.sh + (long long)(tb + t0) * lay.st, lay.st,
+                             sm.ot[c & 1], Tn - t0, tid);
+      } else if (tid == 0) {             // rows past the end of the tensor are clipped by the TMA store
+        tma_store_4d(&tmap_o, sm.ot[c & 1], 0, tb + t0, hi, brow);
+        bulk_commit();
+        bulk_wait_read_1();              // the buffer of the previous chunk is free again
+      }
     }
     R7C_STAMP(56);
   }
@@ -746,40 +773,47 @@ r7c_scan_fwd_kernel(const __grid_constant__ CUtensorMap tmap_v, const unsigned c
 
 int launch_rwkv7_chunked_fwd(const void* r, const void* w, const void* k, const void* v, const void* a, const void* b,
                              const float* h0, int n_state, void* o, float* ht, void* workspace,
-                             int B, int Tn, int H, int head_first, bool keep_for_bwd, cudaStream_t st) {
+                             int B, int Tn, int H, int head_first, bool keep_for_bwd, cudaStream_t st,
+                             const int* seq_start, const int* seq_len, int T_total) {
   using namespace r7c;
   typedef __nv_bfloat16 bf16;
+  const SeqView sv{seq_start, seq_len, Tn};
+  const int mapB = seq_start ? 1 : B, mapT = seq_start ? T_total : Tn;   // shape of the token tensors
   int* status = device_status_ptr();
   if (!status) { last_cuda_error_slot() = 99999; return RWKVB200_E_CUDA; }
   CUtensorMap tmap_v, tmap_o;
-  int e = make_token_tensor_map(&tmap_v, v, B, Tn, H, head_first);
+  int e = make_token_tensor_map(&tmap_v, v, mapB, mapT, H, head_first);
   if (e) return e;
-  e = make_token_tensor_map(&tmap_o, o ? o : v, B, Tn, H, head_first);   // unused when o is NULL
+  e = make_token_tensor_map(&tmap_o, o ? o : v, mapB, mapT, H, head_first);   // unused when o is NULL
   if (e) return e;
   CUtensorMap tmap_in[5];
   const void* ins[5] = {r, w, k, a, b};
   for (int i = 0; i < 5; ++i) {
-    e = make_token_tensor_map(&tmap_in[i], ins[i], B, Tn, H, head_first);
+    e = make_token_tensor_map(&tmap_in[i], ins[i], mapB, mapT, H, head_first);
     if (e) return e;
   }
   const int NT = num_chunks(Tn);
   const int tpc = keep_for_bwd ? (int)ALL_TILES : (int)FWD_TILES;
   Workspace ws = carve(workspace, B, Tn, H, tpc);
-  TokLayout lay(Tn, H, head_first);
+  TokLayout lay(mapT, H, head_first);
   {
     const int smem = (int)sizeof(IntraSmem) + 1024;
-    if (cuda_ok(cudaFuncSetAttribute(r7c_intra_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem))) return RWKVB200_E_CUDA;
     ProfScope prof("r7c_intra_fwd_kernel", st);
     const int n_ch = B * H * NT;
     int dev = 0, sms = 0;
     if (cuda_ok(cudaGetDevice(&dev)) || cuda_ok(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)))
       return RWKVB200_E_CUDA;
     const int grid = n_ch < 2 * sms ? n_ch : 2 * sms;     // persistent: two CTAs per SM
-    r7c_intra_fwd_kernel<<<grid, 256, smem, st>>>((const bf16*)r, (const bf16*)w, (const bf16*)k, (const bf16*)a,
-                                                   (const bf16*)b, tmap_in[0], tmap_in[1], tmap_in[2], tmap_in[3],
-                                                   tmap_in[4], tmap_v, ws.tiles, ws.aux, tpc,
-                                                   keep_for_bwd ? 1 : 0, Tn, H, NT, n_ch, lay, status,
-                                                   debug_stamp_buffer());
+#define R7C_LAUNCH_INTRA(P)                                                                                        \
+    do {                                                                                                           \
+      if (cuda_ok(cudaFuncSetAttribute(r7c_intra_fwd_kernel<P>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem))) \
+        return RWKVB200_E_CUDA;                                                                                    \
+      r7c_intra_fwd_kernel<P><<<grid, 256, smem, st>>>((const bf16*)r, (const bf16*)w, (const bf16*)k,            \
+          (const bf16*)a, (const bf16*)b, tmap_in[0], tmap_in[1], tmap_in[2], tmap_in[3], tmap_in[4], tmap_v,      \
+          ws.tiles, ws.aux, tpc, keep_for_bwd ? 1 : 0, sv, H, NT, n_ch, lay, status, debug_stamp_buffer());        \
+    } while (0)
+    if (seq_start) R7C_LAUNCH_INTRA(true); else R7C_LAUNCH_INTRA(false);
+#undef R7C_LAUNCH_INTRA
   }
   e = check_launch();
   if (e) return e;
@@ -788,19 +822,19 @@ int launch_rwkv7_chunked_fwd(const void* r, const void* w, const void* k, const 
     if (cuda_ok(cudaGetDevice(&dev)) || cuda_ok(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)))
       return RWKVB200_E_CUDA;
     ProfScope prof("r7c_scan_fwd_kernel", st);
-    if (B * H > sms) {      // more sequences than SMs: two single-buffered CTAs per SM
-      const int smem = (int)sizeof(ScanSmem<1>) + 1024;
-      if (cuda_ok(cudaFuncSetAttribute(r7c_scan_fwd_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem))) return RWKVB200_E_CUDA;
-      r7c_scan_fwd_kernel<1><<<B * H, 256, smem, st>>>(tmap_v, ws.tiles, ws.aux, tpc, keep_for_bwd ? ws.tiles : nullptr,
-                                                       h0, n_state, tmap_o, o ? 1 : 0, ht, Tn, H, NT, status,
-                                                       debug_stamp_buffer());
-    } else {                // one double-buffered CTA per SM
-      const int smem = (int)sizeof(ScanSmem<2>) + 1024;
-      if (cuda_ok(cudaFuncSetAttribute(r7c_scan_fwd_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem))) return RWKVB200_E_CUDA;
-      r7c_scan_fwd_kernel<2><<<B * H, 256, smem, st>>>(tmap_v, ws.tiles, ws.aux, tpc, keep_for_bwd ? ws.tiles : nullptr,
-                                                       h0, n_state, tmap_o, o ? 1 : 0, ht, Tn, H, NT, status,
-                                                       debug_stamp_buffer());
-    }
+    // more sequences than SMs: two single-buffered CTAs per SM; else one double-buffered CTA per SM
+#define R7C_LAUNCH_SCAN(S, P)                                                                                      \
+    do {                                                                                                           \
+      const int smem = (int)sizeof(ScanSmem<S>) + 1024;                                                            \
+      if (cuda_ok(cudaFuncSetAttribute(r7c_scan_fwd_kernel<S, P>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem))) \
+        return RWKVB200_E_CUDA;                                                                                    \
+      r7c_scan_fwd_kernel<S, P><<<B * H, 256, smem, st>>>(tmap_v, ws.tiles, ws.aux, tpc,                           \
+          keep_for_bwd ? ws.tiles : nullptr, h0, n_state, tmap_o, o ? 1 : 0, ht, (bf16*)o, sv, H, NT, lay, status, \
+          debug_stamp_buffer());                                                                                   \
+    } while (0)
+    if (B * H > sms) { if (seq_start) R7C_LAUNCH_SCAN(1, true); else R7C_LAUNCH_SCAN(1, false); }
+    else             { if (seq_start) R7C_LAUNCH_SCAN(2, true); else R7C_LAUNCH_SCAN(2, false); }
+#undef R7C_LAUNCH_SCAN
   }
   return check_launch();
 }

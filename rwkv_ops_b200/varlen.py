@@ -1,0 +1,165 @@
+"""RWKV7 generalized delta rule on packed variable-length batches.
+
+The reference carries ``cu_seqlens`` plumbing for this in its Triton path but has it disabled
+(``rwkv_ops/rwkv7_kernel/torch_op.py:283,299``, the ``if False:`` blocks of e.g.
+``triton_kernel/chunk_A_fwd.py:47-56``); its users pad every sequence to the longest one and push the
+padding's decay input to ``-1e9`` (``README.md:92-98``).  ``generalized_delta_rule_varlen`` takes the
+sequences laid end to end instead -- token tensors ``[1, total_len, H, 64]`` plus ``cu_seqlens``
+``[n_seq + 1]`` (``cu_seqlens[i]`` is the first token of sequence ``i``) -- and returns what running the
+operator on every sequence alone would: ``o`` ``[1, total_len, H, 64]`` and one final state per
+sequence ``[n_seq, H, 64, 64]``.  No padded token is ever loaded or stored.
+
+bfloat16 token tensors run on the chunked tensor-core kernels (chunk slots past the end of a sequence
+are skipped, a partial last chunk is stored row by row so that the next sequence's rows stay intact);
+other dtypes run the dense operator once per sequence.
+"""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib
+from .rwkv7 import HEAD_SIZE, generalized_delta_rule
+
+
+def _seq_arrays(cu_seqlens, total_len: int, device):
+    cu = torch.as_tensor(cu_seqlens).detach().to("cpu", torch.int64).flatten()
+    if cu.numel() < 2 or int(cu[0]) != 0 or int(cu[-1]) != total_len:
+        raise ValueError(f"cu_seqlens must run from 0 to the number of tokens ({total_len}), got {cu.tolist()}")
+    lens = cu[1:] - cu[:-1]
+    if int(lens.min()) < 1:
+        raise ValueError("every sequence must hold at least one token")
+    start = cu[:-1].to(device=device, dtype=torch.int32)
+    return cu, start, lens.to(device=device, dtype=torch.int32), int(lens.max())
+
+
+@torch.library.custom_op("rwkv_ops_b200::rwkv7_fwd_varlen", mutates_args=())
+def _fwd_varlen(r: torch.Tensor, w: torch.Tensor, k: torch.Tensor, v: torch.Tensor, a: torch.Tensor,
+                b: torch.Tensor, seq_start: torch.Tensor, seq_len: torch.Tensor, max_len: int,
+                h0: Optional[torch.Tensor], keep: bool) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    lib = _lib.load()
+    dev = _lib.require_cuda(r, w, k, v, a, b, seq_start, seq_len, h0)
+    _, T, H, K = r.shape
+    n_seq = seq_start.numel()
+    o = torch.empty_like(r)
+    ht = torch.empty(n_seq, H, K, K, dtype=torch.float32, device=dev)
+    n_state = 0 if h0 is None else h0.shape[0]
+    with torch.cuda.device(dev):
+        nws = lib.rwkvb200_rwkv7_varlen_workspace_bytes(n_seq, max_len, H, K, int(keep))
+        ws = torch.empty(nws, dtype=torch.uint8, device=dev)
+        rc = lib.rwkvb200_rwkv7_fwd_varlen(r.data_ptr(), w.data_ptr(), k.data_ptr(), v.data_ptr(), a.data_ptr(),
+                                           b.data_ptr(), seq_start.data_ptr(), seq_len.data_ptr(), n_seq, max_len,
+                                           T, _lib.ptr(h0), n_state, o.data_ptr(), ht.data_ptr(), ws.data_ptr(),
+                                           nws, H, K, _lib.dtype_code(r.dtype), int(keep), _lib.stream_ptr(dev))
+        _lib.check(rc, "rwkv7_fwd_varlen")
+    return o, ht, (ws if keep else ws.new_empty((1,)))
+
+
+@_fwd_varlen.register_fake
+def _(r, w, k, v, a, b, seq_start, seq_len, max_len, h0, keep):
+    _, T, H, K = r.shape
+    return (torch.empty_like(r), r.new_empty((seq_start.numel(), H, K, K), dtype=torch.float32),
+            r.new_empty((1,), dtype=torch.uint8))
+
+
+# `kept` also serves as scratch for the backward kernels; the tiles the forward left in it are not changed.
+@torch.library.custom_op("rwkv_ops_b200::rwkv7_bwd_varlen", mutates_args=())
+def _bwd_varlen(r: torch.Tensor, w: torch.Tensor, k: torch.Tensor, v: torch.Tensor, a: torch.Tensor,
+                b: torch.Tensor, seq_start: torch.Tensor, seq_len: torch.Tensor, max_len: int,
+                h0: Optional[torch.Tensor], d_o: torch.Tensor, d_ht: Optional[torch.Tensor], kept: torch.Tensor
+                ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor,
+                           torch.Tensor]:
+    lib = _lib.load()
+    dev = _lib.require_cuda(r, w, k, v, a, b, seq_start, seq_len, h0, d_o, d_ht, kept)
+    _, T, H, K = r.shape
+    n_seq = seq_start.numel()
+    dr, dw, dk, dv, da, db = (torch.empty_like(r) for _ in range(6))
+    dh0 = torch.empty(n_seq, H, K, K, dtype=torch.float32, device=dev)
+    n_state = 0 if h0 is None else h0.shape[0]
+    with torch.cuda.device(dev):
+        nws = lib.rwkvb200_rwkv7_varlen_workspace_bytes(n_seq, max_len, H, K, 1)
+        have = kept.numel() >= nws
+        ws = kept if have else torch.empty(nws, dtype=torch.uint8, device=dev)
+        rc = lib.rwkvb200_rwkv7_bwd_varlen(r.data_ptr(), w.data_ptr(), k.data_ptr(), v.data_ptr(), a.data_ptr(),
+                                           b.data_ptr(), seq_start.data_ptr(), seq_len.data_ptr(), n_seq, max_len,
+                                           T, _lib.ptr(h0), n_state, d_o.data_ptr(), _lib.ptr(d_ht),
+                                           dr.data_ptr(), dw.data_ptr(), dk.data_ptr(), dv.data_ptr(),
+                                           da.data_ptr(), db.data_ptr(), dh0.data_ptr(), ws.data_ptr(), nws,
+                                           H, K, _lib.dtype_code(r.dtype), int(have), _lib.stream_ptr(dev))
+        _lib.check(rc, "rwkv7_bwd_varlen")
+    return dr, dw, dk, dv, da, db, dh0
+
+
+@_bwd_varlen.register_fake
+def _(r, w, k, v, a, b, seq_start, seq_len, max_len, h0, d_o, d_ht, kept):
+    _, T, H, K = r.shape
+    e = torch.empty_like
+    return e(r), e(r), e(r), e(r), e(r), e(r), r.new_empty((seq_start.numel(), H, K, K), dtype=torch.float32)
+
+
+def _setup_ctx(ctx, inputs, output):
+    r, w, k, v, a, b, seq_start, seq_len, max_len, h0, keep = inputs
+    ctx.save_for_backward(r, w, k, v, a, b, seq_start, seq_len, h0, output[2])
+    ctx.set_materialize_grads(False)
+    ctx.max_len = max_len
+
+
+def _backward(ctx, d_o, d_ht, d_kept):
+    r, w, k, v, a, b, seq_start, seq_len, h0, kept = ctx.saved_tensors
+    if d_o is None:
+        d_o = torch.zeros_like(r)
+    d_o = d_o.to(r.dtype).contiguous()
+    if d_ht is not None:
+        d_ht = d_ht.to(torch.float32).contiguous()
+    dr, dw, dk, dv, da, db, dh0 = _bwd_varlen(r, w, k, v, a, b, seq_start, seq_len, ctx.max_len, h0, d_o, d_ht, kept)
+    if h0 is None or not ctx.needs_input_grad[9]:
+        dh0 = None
+    elif h0.shape[0] == 1 and dh0.shape[0] != 1:
+        dh0 = dh0.sum(0, keepdim=True)   # one state broadcast over the sequences
+    return dr, dw, dk, dv, da, db, None, None, None, dh0, None
+
+
+torch.library.register_autograd("rwkv_ops_b200::rwkv7_fwd_varlen", _backward, setup_context=_setup_ctx)
+
+
+def generalized_delta_rule_varlen(r, w, k, v, a, b, cu_seqlens, initial_state=None, output_final_state=True):
+    """``generalized_delta_rule`` over sequences packed end to end (see the module docstring).
+
+    ``r, w, k, v, a, b``: ``[1, total_len, H, 64]``; ``cu_seqlens``: ``n_seq + 1`` increasing integers from
+    0 to ``total_len`` (tensor or list); ``initial_state``: float32 ``[n_seq or 1, H, 64, 64]``.
+    Returns ``(o, final_state)`` with ``final_state`` ``[n_seq, H, 64, 64]``, or just ``o``.
+    """
+    dev = _lib.require_cuda(r, w, k, v, a, b, initial_state)
+    if r.dim() != 4 or r.shape[0] != 1 or r.shape[-1] != HEAD_SIZE:
+        raise ValueError(f"expected packed token tensors [1, total_len, H, {HEAD_SIZE}], got {tuple(r.shape)}")
+    for name, x in (("w", w), ("k", k), ("v", v), ("a", a), ("b", b)):
+        if x.shape != r.shape:
+            raise ValueError(f"{name} has shape {tuple(x.shape)}, expected {tuple(r.shape)}")
+    T, H = r.shape[1], r.shape[2]
+    cu, start, lens, max_len = _seq_arrays(cu_seqlens, T, dev)
+    n_seq = start.numel()
+    h0 = None
+    if initial_state is not None:
+        if initial_state.dim() != 4 or tuple(initial_state.shape[1:]) != (H, HEAD_SIZE, HEAD_SIZE) \
+                or initial_state.shape[0] not in (1, n_seq):
+            raise ValueError(f"initial_state must be [{n_seq} or 1, {H}, {HEAD_SIZE}, {HEAD_SIZE}], "
+                             f"got {tuple(initial_state.shape)}")
+        h0 = initial_state.to(torch.float32).contiguous()
+
+    if r.dtype != torch.bfloat16:
+        # one dense call per sequence (the float32 recurrence has no packed form)
+        outs, states = [], []
+        for i in range(n_seq):
+            s, e = int(cu[i]), int(cu[i + 1])
+            hi = None if h0 is None else h0[i:i + 1] if h0.shape[0] == n_seq else h0
+            oi, si = generalized_delta_rule(*(x[:, s:e] for x in (r, w, k, v, a, b)), initial_state=hi)
+            outs.append(oi)
+            states.append(si)
+        o, ht = torch.cat(outs, dim=1), torch.cat(states, dim=0)
+    else:
+        args = [x.contiguous() for x in (r, w, k, v, a, b)]
+        needs_grad = torch.is_grad_enabled() and (
+            any(x.requires_grad for x in args) or (h0 is not None and h0.requires_grad))
+        o, ht, _ = _fwd_varlen(*args, start, lens, max_len, h0, needs_grad)
+    return (o, ht) if output_final_state else o
