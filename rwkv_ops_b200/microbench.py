@@ -4,6 +4,7 @@
     python -m rwkv_ops_b200.microbench step  --state-dtype bf16      (in place, bfloat16 state)
     python -m rwkv_ops_b200.microbench wkv6  [--B 16 --T 4096 --H 32 --steps 5]
     python -m rwkv_ops_b200.microbench rwkv7 [--B 8 --T 4096 --H 32 --steps 5 --dtype bf16 --algo auto]
+    python -m rwkv_ops_b200.microbench varlen [--B 8 --T 4096 --H 32]     (packed sequences vs padded)
 
 Each prints one JSON line with the time per call and the achieved algorithmic bandwidth.  These
 are the commands the profiler captures in ``profiles/`` were taken from.
@@ -88,6 +89,46 @@ def bench_step(a):
             "kernel_ms": kern}
 
 
+def bench_varlen(a):
+    """Packed variable-length batch (lengths uniform in [T/16, T], seeded) against the same sequences padded
+    to T with the reference's recipe (w = -1e9 on the padding), forward + backward, bf16."""
+    from rwkv_ops_b200 import generalized_delta_rule_varlen
+    gen = torch.Generator().manual_seed(1001)
+    n_seq = a.B
+    lens = torch.randint(a.T // 16, a.T + 1, (n_seq,), generator=gen).tolist()
+    cu = [0]
+    for n in lens:
+        cu.append(cu[-1] + n)
+    total = cu[-1]
+    d = rwkv7_inputs(1, total, a.H, dtype=torch.bfloat16, seed=1001, device="cuda", with_grads=True)
+    g = {n: d[n].requires_grad_(True) for n in "rwkvab"}
+    cu_t = torch.tensor(cu)
+    d_state = 0.1 * torch.randn(n_seq, a.H, 64, 64, device="cuda")
+
+    def packed():
+        o, s = generalized_delta_rule_varlen(*[g[n] for n in "rwkvab"], cu_t)
+        torch.autograd.backward([o, s], [d["d_out"], d_state])
+
+    pad = {n: torch.zeros(n_seq, a.T, a.H, 64, dtype=torch.bfloat16, device="cuda") for n in "rwkvab"}
+    pad["w"].fill_(-1e9)
+    for i, n_tok in enumerate(lens):
+        for n in "rwkvab":
+            pad[n][i, :n_tok] = d[n][0, cu[i]:cu[i + 1]].detach()
+    gp = {n: pad[n].requires_grad_(True) for n in "rwkvab"}
+    d_out_pad = torch.randn(n_seq, a.T, a.H, 64, device="cuda").bfloat16()
+
+    def padded():
+        o, s = ro.generalized_delta_rule(*[gp[n] for n in "rwkvab"])
+        torch.autograd.backward([o, s], [d_out_pad, d_state])
+
+    ms_packed, kern = _time(packed, a.steps)
+    ms_padded, _ = _time(padded, a.steps)
+    return {"op": "rwkv7_fwd_bwd_varlen", "n_seq": n_seq, "max_len": a.T, "H": a.H, "tokens": total,
+            "padded_tokens": n_seq * a.T, "ms_packed": ms_packed, "ms_padded": ms_padded,
+            "tokens_per_s_packed": total / (ms_packed / 1e3), "tokens_per_s_padded": total / (ms_padded / 1e3),
+            "kernel_ms": kern}
+
+
 def bench_wkv6(a):
     """Configuration 4: wkv6 forward + backward, fp32, 4 initial states and a state_map."""
     dt = DT[a.dtype]
@@ -133,7 +174,7 @@ def bench_rwkv7(a):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("op", choices=["step", "wkv6", "rwkv7"])
+    ap.add_argument("op", choices=["step", "wkv6", "rwkv7", "varlen"])
     ap.add_argument("--B", type=int)
     ap.add_argument("--T", type=int, default=4096)
     ap.add_argument("--H", type=int)
@@ -144,12 +185,12 @@ def main():
                     help="step: decode in place on one state buffer of this type (rwkvb200_rwkv7_decode_step)")
     ap.add_argument("--fwd-only", action="store_true")
     a = ap.parse_args()
-    defaults = {"step": (256, 64, "bf16"), "wkv6": (16, 32, "f32"), "rwkv7": (8, 32, "bf16")}[a.op]
+    defaults = {"step": (256, 64, "bf16"), "wkv6": (16, 32, "f32"), "rwkv7": (8, 32, "bf16"), "varlen": (8, 32, "bf16")}[a.op]
     a.B = a.B or defaults[0]
     a.H = a.H or defaults[1]
     a.dtype = a.dtype or defaults[2]
     torch.cuda.set_device(0)
-    res = {"step": bench_step, "wkv6": bench_wkv6, "rwkv7": bench_rwkv7}[a.op](a)
+    res = {"step": bench_step, "wkv6": bench_wkv6, "rwkv7": bench_rwkv7, "varlen": bench_varlen}[a.op](a)
     print(json.dumps(res), flush=True)
 
 
