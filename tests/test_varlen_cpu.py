@@ -1,0 +1,33 @@
+"""Host-side logic of the packed variable-length entry: cu_seqlens handling (no GPU needed)."""
+import pytest
+import torch
+
+from rwkv_ops_b200.varlen import _seq_arrays, generalized_delta_rule_varlen
+from rwkv_ops_b200 import _lib
+
+
+def test_seq_arrays_from_list_and_tensor():
+    for cu_in in ([0, 3, 10, 11], torch.tensor([0, 3, 10, 11]), torch.tensor([0, 3, 10, 11], dtype=torch.int32)):
+        cu, start, lens, max_len = _seq_arrays(cu_in, 11, "cpu")
+        assert cu.tolist() == [0, 3, 10, 11]
+        assert start.tolist() == [0, 3, 10] and start.dtype == torch.int32
+        assert lens.tolist() == [3, 7, 1] and lens.dtype == torch.int32
+        assert max_len == 7
+
+
+@pytest.mark.parametrize("cu,total", [
+    ([0], 0),               # no sequence
+    ([1, 5], 5),            # does not start at 0
+    ([0, 4], 5),            # does not cover every token
+    ([0, 3, 3, 5], 5),      # an empty sequence
+    ([0, 4, 2, 5], 5),      # not increasing
+])
+def test_seq_arrays_rejects(cu, total):
+    with pytest.raises(ValueError):
+        _seq_arrays(cu, total, "cpu")
+
+
+def test_varlen_needs_cuda_tensors():
+    x = torch.zeros(1, 4, 2, 64, dtype=torch.bfloat16)
+    with pytest.raises(_lib.RwkvB200Error):
+        generalized_delta_rule_varlen(x, x, x, x, x, x, [0, 4])
