@@ -11,7 +11,7 @@ the reference's working surface.
 from .rwkv7 import generalized_delta_rule, get_generalized_delta_rule
 from .rwkv6 import RWKVKernelOperator, get_rwkv6_kernel
 from .decode import Rwkv7DecodeState
-from .varlen import generalized_delta_rule_varlen
+from .varlen import PackedSequences, generalized_delta_rule_varlen
 
 __version__ = "0.1"
 
@@ -29,4 +29,5 @@ __all__ = [
     "RWKVKernelOperator",
     "Rwkv7DecodeState",
     "generalized_delta_rule_varlen",
+    "PackedSequences",
 ]

@@ -102,7 +102,7 @@ def bench_varlen(a):
     total = cu[-1]
     d = rwkv7_inputs(1, total, a.H, dtype=torch.bfloat16, seed=1001, device="cuda", with_grads=True)
     g = {n: d[n].requires_grad_(True) for n in "rwkvab"}
-    cu_t = torch.tensor(cu)
+    cu_t = ro.PackedSequences(cu, "cuda")      # prepared once, as for all the layers of a step
     d_state = 0.1 * torch.randn(n_seq, a.H, 64, 64, device="cuda")
 
     def packed():

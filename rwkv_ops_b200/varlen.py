@@ -34,6 +34,17 @@ def _seq_arrays(cu_seqlens, total_len: int, device):
     return cu, start, lens.to(device=device, dtype=torch.int32), int(lens.max())
 
 
+class PackedSequences:
+    """``cu_seqlens`` prepared once (host copy, device arrays of first tokens and lengths, longest length)
+    for all the calls that share it, e.g. every layer of a step; pass it in place of ``cu_seqlens``."""
+
+    def __init__(self, cu_seqlens, device="cuda"):
+        cu = torch.as_tensor(cu_seqlens).detach().to("cpu", torch.int64).flatten()
+        self.total_len = int(cu[-1]) if cu.numel() else 0
+        self.device = torch.device(device)
+        self.cu, self.start, self.lens, self.max_len = _seq_arrays(cu, self.total_len, self.device)
+
+
 @torch.library.custom_op("rwkv_ops_b200::rwkv7_fwd_varlen", mutates_args=())
 def _fwd_varlen(r: torch.Tensor, w: torch.Tensor, k: torch.Tensor, v: torch.Tensor, a: torch.Tensor,
                 b: torch.Tensor, seq_start: torch.Tensor, seq_len: torch.Tensor, max_len: int,
@@ -127,7 +138,7 @@ def generalized_delta_rule_varlen(r, w, k, v, a, b, cu_seqlens, initial_state=No
     """``generalized_delta_rule`` over sequences packed end to end (see the module docstring).
 
     ``r, w, k, v, a, b``: ``[1, total_len, H, 64]``; ``cu_seqlens``: ``n_seq + 1`` increasing integers from
-    0 to ``total_len`` (tensor or list); ``initial_state``: float32 ``[n_seq or 1, H, 64, 64]``.
+    0 to ``total_len`` (tensor or list, or a ``PackedSequences`` made from them once); ``initial_state``: float32 ``[n_seq or 1, H, 64, 64]``.
     Returns ``(o, final_state)`` with ``final_state`` ``[n_seq, H, 64, 64]``, or just ``o``.
     """
     dev = _lib.require_cuda(r, w, k, v, a, b, initial_state)
@@ -137,7 +148,12 @@ def generalized_delta_rule_varlen(r, w, k, v, a, b, cu_seqlens, initial_state=No
         if x.shape != r.shape:
             raise ValueError(f"{name} has shape {tuple(x.shape)}, expected {tuple(r.shape)}")
     T, H = r.shape[1], r.shape[2]
-    cu, start, lens, max_len = _seq_arrays(cu_seqlens, T, dev)
+    if isinstance(cu_seqlens, PackedSequences):
+        if cu_seqlens.total_len != T or cu_seqlens.start.device != dev:
+            raise ValueError("the PackedSequences object was made for another token count or device")
+        cu, start, lens, max_len = cu_seqlens.cu, cu_seqlens.start, cu_seqlens.lens, cu_seqlens.max_len
+    else:
+        cu, start, lens, max_len = _seq_arrays(cu_seqlens, T, dev)
     n_seq = start.numel()
     h0 = None
     if initial_state is not None:

@@ -68,6 +68,9 @@ def test_varlen_equals_dense_calls_and_leaves_no_gaps():
     cu = [0, 100, 164, 165, 422]
     d = rwkv7_inputs(1, T, H, dtype=torch.bfloat16, seed=99, device="cuda")
     o, st = generalized_delta_rule_varlen(*[d[n] for n in NAMES], cu)
+    from rwkv_ops_b200 import PackedSequences
+    o2, st2 = generalized_delta_rule_varlen(*[d[n] for n in NAMES], PackedSequences(cu, "cuda"))
+    assert torch.equal(o, o2) and torch.equal(st, st2)
     for i in range(len(lens)):
         s, e = cu[i], cu[i + 1]
         oi, si = generalized_delta_rule(*[d[n][:, s:e].contiguous() for n in NAMES])
