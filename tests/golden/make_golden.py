@@ -103,7 +103,7 @@ def wkv6_case(ref6, name, B, T, H, *, seed, n_state=None, explicit_map=True, wit
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="path of a checkout of pass-lin/rwkv_ops")
     args = ap.parse_args()
     torch.manual_seed(0)
     torch.set_num_threads(os.cpu_count() or 1)
