@@ -5,6 +5,7 @@
     python -m rwkv_ops_b200.microbench wkv6  [--B 16 --T 4096 --H 32 --steps 5]
     python -m rwkv_ops_b200.microbench rwkv7 [--B 8 --T 4096 --H 32 --steps 5 --dtype bf16 --algo auto]
     python -m rwkv_ops_b200.microbench varlen [--B 8 --T 4096 --H 32]     (packed sequences vs padded)
+    python -m torch.distributed.run --nproc-per-node 2 --master-addr 127.0.0.1 -m rwkv_ops_b200.microbench sp
 
 Each prints one JSON line with the time per call and the achieved algorithmic bandwidth.  These
 are the commands the profiler captures in ``profiles/`` were taken from.
@@ -129,6 +130,40 @@ def bench_varlen(a):
             "kernel_ms": kern}
 
 
+def bench_sp(a):
+    """Sequence-parallel forward + backward: every rank holds T tokens of each of B sequences (the whole
+    sequence is world x T long); run under torchrun, one rank per GPU.  Time = max over ranks."""
+    import torch.distributed as dist
+    from rwkv_ops_b200.sequence_parallel import generalized_delta_rule_sp
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
+    dist.init_process_group("nccl")
+    d = rwkv7_inputs(a.B, a.T, a.H, dtype=torch.bfloat16, seed=1001 + rank, device="cuda", with_grads=True)
+    g = {n: d[n].requires_grad_(True) for n in "rwkvab"}
+
+    def step():
+        o, s = generalized_delta_rule_sp(*[g[n] for n in "rwkvab"], pipeline_groups=a.groups)
+        torch.autograd.backward([o, s], [d["d_out"], d["d_state"]])
+
+    for _ in range(3):
+        step()
+    torch.cuda.synchronize()
+    dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(a.steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = torch.tensor([e0.elapsed_time(e1) / a.steps], device="cuda")
+    dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    res = {"op": "rwkv7_fwd_bwd_sequence_parallel", "ranks": world, "B": a.B, "tokens_per_rank": a.T,
+           "sequence_length": world * a.T, "H": a.H, "pipeline_groups": a.groups, "ms_per_step": float(ms),
+           "tokens_per_s": a.B * a.T * world / (float(ms) / 1e3)}
+    dist.destroy_process_group()
+    return res if rank == 0 else None
+
+
 def bench_wkv6(a):
     """Configuration 4: wkv6 forward + backward, fp32, 4 initial states and a state_map."""
     dt = DT[a.dtype]
@@ -174,7 +209,8 @@ def bench_rwkv7(a):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("op", choices=["step", "wkv6", "rwkv7", "varlen"])
+    ap.add_argument("op", choices=["step", "wkv6", "rwkv7", "varlen", "sp"])
+    ap.add_argument("--groups", type=int, default=4, help="sp: batch groups pipelined along the chain of ranks")
     ap.add_argument("--B", type=int)
     ap.add_argument("--T", type=int, default=4096)
     ap.add_argument("--H", type=int)
@@ -185,13 +221,15 @@ def main():
                     help="step: decode in place on one state buffer of this type (rwkvb200_rwkv7_decode_step)")
     ap.add_argument("--fwd-only", action="store_true")
     a = ap.parse_args()
-    defaults = {"step": (256, 64, "bf16"), "wkv6": (16, 32, "f32"), "rwkv7": (8, 32, "bf16"), "varlen": (8, 32, "bf16")}[a.op]
+    defaults = {"step": (256, 64, "bf16"), "wkv6": (16, 32, "f32"), "rwkv7": (8, 32, "bf16"), "varlen": (8, 32, "bf16"), "sp": (8, 32, "bf16")}[a.op]
     a.B = a.B or defaults[0]
     a.H = a.H or defaults[1]
     a.dtype = a.dtype or defaults[2]
-    torch.cuda.set_device(0)
-    res = {"step": bench_step, "wkv6": bench_wkv6, "rwkv7": bench_rwkv7, "varlen": bench_varlen}[a.op](a)
-    print(json.dumps(res), flush=True)
+    if a.op != "sp":
+        torch.cuda.set_device(0)
+    res = {"step": bench_step, "wkv6": bench_wkv6, "rwkv7": bench_rwkv7, "varlen": bench_varlen, "sp": bench_sp}[a.op](a)
+    if res is not None:
+        print(json.dumps(res), flush=True)
 
 
 if __name__ == "__main__":
