@@ -34,26 +34,34 @@ constexpr int NROW = 68;
 constexpr float EXP_CLAMP = 80.f;
 __device__ __forceinline__ float cexp(float x) { return __expf(fminf(fmaxf(x, -EXP_CLAMP), EXP_CLAMP)); }
 
-__device__ __forceinline__ void split2(float x, float& hi, float& lo) {
-  hi = __bfloat162float(__float2bfloat16_rn(x));
-  lo = x - hi;
+// two values as packed bf16 pairs hi and lo with x = hi + lo (+ an error of about 2^-17 |x|)
+__device__ __forceinline__ void split_pair(float x0, float x1, uint32_t& hi, uint32_t& lo) {
+  hi = pack_bf16(x0, x1);
+  lo = pack_bf16(x0 - bf16_lo(hi), x1 - bf16_hi(hi));
 }
 // write 4 consecutive values (columns col .. col+3, col a multiple of 4) of `row` into a hi and a lo tile
 __device__ __forceinline__ void store_split4(unsigned char* hi_t, unsigned char* lo_t, int row, int col, float4 x) {
-  float h[4], l[4];
-  split2(x.x, h[0], l[0]); split2(x.y, h[1], l[1]); split2(x.z, h[2], l[2]); split2(x.w, h[3], l[3]);
+  uint2 h, l;
+  split_pair(x.x, x.y, h.x, l.x);
+  split_pair(x.z, x.w, h.y, l.y);
   const uint32_t off = tile_off(row, col);
-  *reinterpret_cast<uint2*>(hi_t + off) = make_uint2(pack_bf16(h[0], h[1]), pack_bf16(h[2], h[3]));
-  *reinterpret_cast<uint2*>(lo_t + off) = make_uint2(pack_bf16(l[0], l[1]), pack_bf16(l[2], l[3]));
+  *reinterpret_cast<uint2*>(hi_t + off) = h;
+  *reinterpret_cast<uint2*>(lo_t + off) = l;
 }
-// write 32 consecutive fp32 values of `row` into a hi and a lo tile
+// write 32 consecutive fp32 values of `row` (columns col0 .., col0 a multiple of 8) into a hi and a lo tile
 __device__ __forceinline__ void store_split_row32(unsigned char* hi_t, unsigned char* lo_t, int row, int col0,
                                                   const float* x) {
-  float h[32], l[32];
 #pragma unroll
-  for (int j = 0; j < 32; ++j) split2(x[j], h[j], l[j]);
-  tile_store_row32(hi_t, row, col0, h);
-  tile_store_row32(lo_t, row, col0, l);
+  for (int c = 0; c < 4; ++c) {
+    uint4 h, l;
+    split_pair(x[8 * c + 0], x[8 * c + 1], h.x, l.x);
+    split_pair(x[8 * c + 2], x[8 * c + 3], h.y, l.y);
+    split_pair(x[8 * c + 4], x[8 * c + 5], h.z, l.z);
+    split_pair(x[8 * c + 6], x[8 * c + 7], h.w, l.w);
+    const uint32_t off = tile_chunk_off(row, (col0 >> 3) + c);
+    *reinterpret_cast<uint4*>(hi_t + off) = h;
+    *reinterpret_cast<uint4*>(lo_t + off) = l;
+  }
 }
 
 // D (+)= X Y with X = xh + xl, Y = yh + yl (lo tile = hi tile + TILE_BYTES): hi*hi + hi*lo + lo*hi
