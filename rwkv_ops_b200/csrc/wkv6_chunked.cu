@@ -457,8 +457,8 @@ wkv6c_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
   tc_fence_after();
   const uint32_t tm = sm.tmem_base;
   const uint32_t tm_c0 = tmem_addr(tm, 32 * wq, 32 * hsel);          // A (lower), dA (upper)
-  const uint32_t tm_c1 = tmem_addr(tm, 32 * wq, 64 + 32 * hsel);     // dv (lower), dr~ (upper)
-  const uint32_t tm_c2 = tmem_addr(tm, 32 * wq, 128 + 32 * hsel);    // dk~ (lower), dS~0 (upper)
+  const uint32_t tm_c1 = tmem_addr(tm, 32 * wq, 64 + 32 * hsel);     // dk~ (lower), dr~ (upper)
+  const uint32_t tm_c2 = tmem_addr(tm, 32 * wq, 128 + 32 * hsel);    // dv (lower), dS~0 (upper)
 
   // gradient of the state after the current chunk: row k = srow (upper lane halves), 32 columns
   float dsreg[32];
@@ -635,33 +635,35 @@ wkv6c_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
         const int jj = 32 * hsel + j;
         x[j] = jj < srow ? __uint_as_float(rr[j]) : (jj == srow ? dgi : 0.f);
       }
-      if (lower) store_split_row32(sm.at[0], sm.at[1], srow, 32 * hsel, x);
-      else       store_split_row32(sm.dat[0], sm.dat[1], srow, 32 * hsel, x);
+      unsigned char* hi_t = lower ? sm.at[0] : sm.dat[0];      // one call: both lane halves run the same code
+      store_split_row32(hi_t, hi_t + TILE_BYTES, srow, 32 * hsel, x);
     }
     // decay factors of state row k = srow (both lanes of a pair work on that row below)
     const float e0 = __expf(fmaxf(sm.qtot[0][srow] + sm.qtot[1][srow], -EXP_CLAMP));
     const float dlast = __expf(fmaxf(sm.qtot[2][srow] + sm.qtot[3][srow], -EXP_CLAMP));
     // ---- state rows: the upper lane of a pair holds dS and takes dglast and dS^ = e^{glast-gref} dS_L,
-    // the lower lane takes S~0 = e^{gref} S0
-    if (!lower) {
-      float acc = 0.f;
-#pragma unroll
-      for (int j = 0; j < 32; j += 4) {
-        const float4 f = srow4[j >> 2];
-        acc += dsreg[j] * f.x + dsreg[j + 1] * f.y + dsreg[j + 2] * f.z + dsreg[j + 3] * f.w;
-      }
-      sm.dgl[hsel][srow] = acc;
-#pragma unroll
-      for (int j = 0; j < 32; ++j) dsreg[j] *= dlast;     // dsreg now holds dS^
-      store_split_row32(sm.dst[0], sm.dst[1], srow, 32 * hsel, dsreg);
-    } else {
+    // the lower lane takes S~0 = e^{gref} S0; one split-and-store call serves both
+    {
       float x[32];
+      if (!lower) {
+        float acc = 0.f;
 #pragma unroll
-      for (int j = 0; j < 32; j += 4) {
-        const float4 f = srow4[j >> 2];
-        x[j] = f.x * e0; x[j + 1] = f.y * e0; x[j + 2] = f.z * e0; x[j + 3] = f.w * e0;
+        for (int j = 0; j < 32; j += 4) {
+          const float4 f = srow4[j >> 2];
+          acc += dsreg[j] * f.x + dsreg[j + 1] * f.y + dsreg[j + 2] * f.z + dsreg[j + 3] * f.w;
+        }
+        sm.dgl[hsel][srow] = acc;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) { dsreg[j] *= dlast; x[j] = dsreg[j]; }     // dsreg now holds dS^
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; j += 4) {
+          const float4 f = srow4[j >> 2];
+          x[j] = f.x * e0; x[j + 1] = f.y * e0; x[j + 2] = f.z * e0; x[j + 3] = f.w * e0;
+        }
       }
-      store_split_row32(sm.st[0], sm.st[1], srow, 32 * hsel, x);
+      unsigned char* hi_t = lower ? sm.st[0] : sm.dst[0];
+      store_split_row32(hi_t, hi_t + TILE_BYTES, srow, 32 * hsel, x);
     }
     fence_async_smem();
     tc_fence_before();
@@ -671,15 +673,16 @@ wkv6c_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
     // ---- batch 2
     if (tid == 0 && ok) {
       tc_fence_after();
-      // dv = A^T dy + k~ dS^                        (lower halves, columns 64..127)
-      umma_split<64, 64, 1, 1>(tmem_addr(tm, 0, 64), smem_u32(sm.at[0]), smem_u32(sm.dyt[0]), false);
-      umma_split<64, 64, 0, 1>(tmem_addr(tm, 0, 64), smem_u32(sm.kt[0]), smem_u32(sm.dst[0]), true);
+      // dv = A^T dy + k~ dS^                        (lower halves, columns 128..191)
+      umma_split<64, 64, 1, 1>(tmem_addr(tm, 0, 128), smem_u32(sm.at[0]), smem_u32(sm.dyt[0]), false);
+      umma_split<64, 64, 0, 1>(tmem_addr(tm, 0, 128), smem_u32(sm.kt[0]), smem_u32(sm.dst[0]), true);
       // dr~ = dy S~0^T + stril(dA) k~               (upper halves, columns 64..127)
       umma_split<64, 64, 0, 0>(tmem_addr(tm, 16, 64), smem_u32(sm.dyt[0]), smem_u32(sm.st[0]), false);
       umma_split<64, 64, 0, 1>(tmem_addr(tm, 16, 64), smem_u32(sm.dat[0]), smem_u32(sm.kt[0]), true);
-      // dk~ = stril(dA)^T r~ + v dS^^T              (lower halves, columns 128..191)
-      umma_split<64, 64, 1, 1>(tmem_addr(tm, 0, 128), smem_u32(sm.dat[0]), smem_u32(sm.rt[0]), false);
-      umma_split<64, 64, 0, 0>(tmem_addr(tm, 0, 128), smem_u32(sm.vt[0]), smem_u32(sm.dst[0]), true);
+      // dk~ = stril(dA)^T r~ + v dS^^T              (lower halves, columns 64..127: beside dr~, so that one
+      // piece of code scales both in the epilogue)
+      umma_split<64, 64, 1, 1>(tmem_addr(tm, 0, 64), smem_u32(sm.dat[0]), smem_u32(sm.rt[0]), false);
+      umma_split<64, 64, 0, 0>(tmem_addr(tm, 0, 64), smem_u32(sm.vt[0]), smem_u32(sm.dst[0]), true);
       // dS~0 = r~^T dy                              (upper halves, columns 128..191)
       umma_split<64, 64, 1, 1>(tmem_addr(tm, 16, 128), smem_u32(sm.rt[0]), smem_u32(sm.dyt[0]), false);
       umma_commit(&sm.bar_2);
@@ -694,7 +697,8 @@ wkv6c_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
       tmem_ld_wait();
       const int c0 = 32 * hsel;
       float th[32], tl[32];
-      // lower halves: dv row and dk~ row of token srow; upper halves: dr~ row of token srow and dS~0 row k = srow
+      // r1: dk~ (lower halves) / dr~ (upper halves) row of token srow; r2: dv row of token srow (lower) /
+      // dS~0 row k = srow (upper)
       tile_load_row32(lower ? sm.kt[0] : sm.rt[0], srow, c0, th);
       tile_load_row32(lower ? sm.kt[1] : sm.rt[1], srow, c0, tl);
       if (!lower) {
@@ -710,27 +714,22 @@ wkv6c_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
         const float4 tb4 = *reinterpret_cast<const float4*>(&sm.qtot[1][cc]);
         const float gsv[4] = {gs4.x, gs4.y, gs4.z, gs4.w}, ggv[4] = {gg4.x, gg4.y, gg4.z, gg4.w};
         const float ttv[4] = {ta4.x + tb4.x, ta4.y + tb4.y, ta4.z + tb4.z, ta4.w + tb4.w};
-        float o[4], rd[4], dvv[4];
+        float o[4], rd[4];
 #pragma unroll
         for (int m = 0; m < 4; ++m) {
           const int j = j4 + m;
           const float d1 = gsv[m] - (srow < 32 ? ttv[m] : 0.f);     // gi - gref
           const float tt = th[j] + tl[j];                            // k~ (lower) / r~ (upper)
-          if (lower) {
-            const float x2 = __uint_as_float(r2[j]);                 // dk~
-            o[m] = x2 * cexp(-d1);
-            rd[m] = -x2 * tt;
-            dvv[m] = __uint_as_float(r1[j]);
-          } else {
-            const float x1 = __uint_as_float(r1[j]);                 // dr~
-            o[m] = x1 * cexp(d1 - ggv[m]);
-            rd[m] = x1 * tt;
-          }
+          const float x = __uint_as_float(r1[j]);                    // dk~ (lower) / dr~ (upper)
+          o[m] = x * cexp(lower ? -d1 : d1 - ggv[m]);                // dk = dk~ e^{gref-gi},  dr = dr~ e^{ge-gref}
+          rd[m] = lower ? -x * tt : x * tt;                          // dgi = -dk~ k~,  dge = dr~ r~
         }
         if (lower) {
           *reinterpret_cast<float4*>(&stage_dk[srow * NROW + cc]) = make_float4(o[0], o[1], o[2], o[3]);
           *reinterpret_cast<float4*>(&red_i[srow * NROW + cc]) = make_float4(rd[0], rd[1], rd[2], rd[3]);
-          *reinterpret_cast<float4*>(&stage_dv[srow * NROW + cc]) = make_float4(dvv[0], dvv[1], dvv[2], dvv[3]);
+          *reinterpret_cast<float4*>(&stage_dv[srow * NROW + cc]) =
+              make_float4(__uint_as_float(r2[j4]), __uint_as_float(r2[j4 + 1]), __uint_as_float(r2[j4 + 2]),
+                          __uint_as_float(r2[j4 + 3]));
         } else {
           *reinterpret_cast<float4*>(&stage_dr[srow * NROW + cc]) = make_float4(o[0], o[1], o[2], o[3]);
           *reinterpret_cast<float4*>(&sm.red_e[srow * NROW + cc]) = make_float4(rd[0], rd[1], rd[2], rd[3]);
