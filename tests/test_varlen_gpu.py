@@ -80,6 +80,38 @@ def test_varlen_equals_dense_calls_and_leaves_no_gaps():
     assert torch.isfinite(o.float()).all()
 
 
+def test_varlen_long_sequences_forward_backward_equal_dense_calls():
+    """Lengths in the thousands (more chunk slots than SMs, skipped slots, partial last chunks): outputs,
+    states and every gradient equal those of one dense call per sequence (itself checked against the oracle)."""
+    from rwkv_ops_b200 import generalized_delta_rule, generalized_delta_rule_varlen
+    gen = torch.Generator().manual_seed(31)
+    lens = torch.randint(50, 2500, (9,), generator=gen).tolist() + [4096, 1]
+    H, T = 4, sum(lens)
+    cu = [0]
+    for n in lens:
+        cu.append(cu[-1] + n)
+    d = rwkv7_inputs(1, T, H, dtype=torch.bfloat16, seed=123, device="cuda", with_grads=True)
+    h0 = (0.1 * torch.randn(len(lens), H, 64, 64, device="cuda")).requires_grad_(True)
+    d_state = 0.1 * torch.randn(len(lens), H, 64, 64, device="cuda")
+    g = {n: d[n].clone().requires_grad_(True) for n in NAMES}
+    o, st = generalized_delta_rule_varlen(*[g[n] for n in NAMES], cu, initial_state=h0)
+    torch.autograd.backward([o, st], [d["d_out"], d_state])
+    h0_ref = h0.detach().clone().requires_grad_(True)
+    ref = {n: d[n].clone().requires_grad_(True) for n in NAMES}
+    outs, states = [], []
+    for i in range(len(lens)):
+        s, e = cu[i], cu[i + 1]
+        oi, si = generalized_delta_rule(*[ref[n][:, s:e] for n in NAMES], initial_state=h0_ref[i:i + 1])
+        outs.append(oi)
+        states.append(si)
+    o_ref, s_ref = torch.cat(outs, 1), torch.cat(states, 0)
+    torch.autograd.backward([o_ref, s_ref], [d["d_out"], d_state])
+    assert rel_l2(o, o_ref) <= 5e-3 and rel_l2(st, s_ref) <= 5e-3
+    for n in NAMES:
+        assert rel_l2(g[n].grad, ref[n].grad) <= 1e-2, n
+    assert rel_l2(h0.grad, h0_ref.grad) <= 1e-2
+
+
 def test_varlen_float32_runs_per_sequence():
     from rwkv_ops_b200 import generalized_delta_rule_varlen
     lens = [9, 30]
