@@ -113,6 +113,28 @@ int rwkvb200_rwkv7_bwd_varlen(const void* r, const void* w, const void* k, const
                               void* workspace, size_t workspace_bytes,
                               int H, int head_size, int dtype, int kept, void* stream);
 
+/* The delta rule with its three elementwise producers fused in (bfloat16, dense [B,T,H,64] batches):
+ *   w = -exp(-1/2) * sigmoid(w_pre),  kk = kk_pre / max(|kk_pre|_2, 1e-12) over the 64 channels of a head,
+ *   a = -kk,  b = kk * sigmoid(a_pre),
+ * each rounded to bfloat16 as a materialised tensor would be, then rwkvb200_rwkv7_fwd / _bwd on
+ * (r, w, k, v, a, b): same results, without w, a, b (forward) or their gradients (backward) ever being
+ * written to or read from memory.  The backward returns the gradients of the pre-activations.  Workspace
+ * as rwkvb200_rwkv7_fwd_workspace_bytes / _bwd_workspace_bytes with the chunked algorithm (keep / kept as
+ * RWKVB200_ALGO_KEEP).  These producers are not part of the reference; they are what its callers compute
+ * right before the operator (the input distributions of its value test, test_script/test_rwkv7_value.py). */
+int rwkvb200_rwkv7_fused_fwd(const void* r, const void* w_pre, const void* k, const void* v,
+                             const void* kk_pre, const void* a_pre,
+                             const float* h0, int n_state, void* o, float* ht,
+                             void* workspace, size_t workspace_bytes,
+                             int B, int T, int H, int head_size, int dtype, int keep, void* stream);
+
+int rwkvb200_rwkv7_fused_bwd(const void* r, const void* w_pre, const void* k, const void* v,
+                             const void* kk_pre, const void* a_pre,
+                             const float* h0, int n_state, const void* d_o, const float* d_ht,
+                             void* dr, void* dw_pre, void* dk, void* dv, void* dkk_pre, void* da_pre, float* d_h0,
+                             void* workspace, size_t workspace_bytes,
+                             int B, int T, int H, int head_size, int dtype, int kept, void* stream);
+
 /* One decode step in place on a state the caller keeps on the device across steps:
  * state [B,H,64,64] (value index before key index, like the reference's final_state), element type
  * state_dtype = RWKVB200_F32 (the reference's state type; same arithmetic as rwkvb200_rwkv7_step) or

@@ -27,6 +27,9 @@ SIGNATURES = {
     "rwkvb200_last_cuda_error": (c_char_p, []),
     "rwkvb200_rwkv7_step": (c_int, [_P] * 6 + [_P, _I, _P, _P, _I, _I, _I, _I, _P]),
     "rwkvb200_rwkv7_decode_step": (c_int, [_P] * 6 + [_P, _I, _P, _I, _I, _I, _I, _P]),
+    "rwkvb200_rwkv7_fused_fwd": (c_int, [_P] * 6 + [_P, _I, _P, _P, _P, c_size_t, _I, _I, _I, _I, _I, _I, _P]),
+    "rwkvb200_rwkv7_fused_bwd": (c_int, [_P] * 6 + [_P, _I, _P, _P] + [_P] * 7 +
+                                 [_P, c_size_t, _I, _I, _I, _I, _I, _I, _P]),
     "rwkvb200_rwkv7_varlen_workspace_bytes": (c_size_t, [_I] * 5),
     "rwkvb200_rwkv7_fwd_varlen": (c_int, [_P] * 6 + [_P, _P, _I, _I, _I, _P, _I, _P, _P, _P, c_size_t,
                                                       _I, _I, _I, _I, _P]),

@@ -222,6 +222,48 @@ int rwkvb200_rwkv7_bwd_varlen(const void* r, const void* w, const void* k, const
                                   (cudaStream_t)stream, seq_start, seq_len, total_len);
 }
 
+// ---- fused producers (chunked bf16 path, dense [B,T,H,64] batches)
+int rwkvb200_rwkv7_fused_fwd(const void* r, const void* w_pre, const void* k, const void* v,
+                             const void* kk_pre, const void* a_pre,
+                             const float* h0, int n_state, void* o, float* ht,
+                             void* workspace, size_t workspace_bytes,
+                             int B, int T, int H, int head_size, int dtype, int keep, void* stream) {
+  int e = check_common(B, T, H, head_size, dtype);
+  if (e) return e;
+  if (dtype != RWKVB200_BF16) return RWKVB200_E_UNSUPPORTED;
+  if (!r || !w_pre || !k || !v || !kk_pre || !a_pre || !o) return RWKVB200_E_NULL;
+  if (n_state != 0 && n_state != 1 && n_state != B) return RWKVB200_E_SHAPE;
+  if (n_state != 0 && !h0) return RWKVB200_E_NULL;
+  const void* ps[] = {r, w_pre, k, v, kk_pre, a_pre, h0, o, ht, workspace};
+  for (const void* p : ps) if (p && !aligned16(p)) return RWKVB200_E_ALIGN;
+  const size_t need = r7c::fwd_workspace_bytes(B, T, H, keep ? r7c::ALL_TILES : r7c::FWD_TILES);
+  if (workspace_bytes < need || !workspace) return RWKVB200_E_WORKSPACE;
+  return launch_rwkv7_chunked_fwd(r, w_pre, k, v, kk_pre, a_pre, n_state ? h0 : nullptr, n_state, o, ht, workspace,
+                                  B, T, H, 0, keep != 0, (cudaStream_t)stream, nullptr, nullptr, 0, true);
+}
+
+int rwkvb200_rwkv7_fused_bwd(const void* r, const void* w_pre, const void* k, const void* v,
+                             const void* kk_pre, const void* a_pre,
+                             const float* h0, int n_state, const void* d_o, const float* d_ht,
+                             void* dr, void* dw_pre, void* dk, void* dv, void* dkk_pre, void* da_pre, float* d_h0,
+                             void* workspace, size_t workspace_bytes,
+                             int B, int T, int H, int head_size, int dtype, int kept, void* stream) {
+  int e = check_common(B, T, H, head_size, dtype);
+  if (e) return e;
+  if (dtype != RWKVB200_BF16) return RWKVB200_E_UNSUPPORTED;
+  if (!r || !w_pre || !k || !v || !kk_pre || !a_pre || !d_o || !dr || !dw_pre || !dk || !dv || !dkk_pre || !da_pre)
+    return RWKVB200_E_NULL;
+  if (n_state != 0 && n_state != 1 && n_state != B) return RWKVB200_E_SHAPE;
+  if (n_state != 0 && !h0) return RWKVB200_E_NULL;
+  const void* ps[] = {r, w_pre, k, v, kk_pre, a_pre, h0, d_o, d_ht, dr, dw_pre, dk, dv, dkk_pre, da_pre, d_h0, workspace};
+  for (const void* p : ps) if (p && !aligned16(p)) return RWKVB200_E_ALIGN;
+  const size_t need = r7c::fwd_workspace_bytes(B, T, H, r7c::ALL_TILES);
+  if (workspace_bytes < need || !workspace) return RWKVB200_E_WORKSPACE;
+  return launch_rwkv7_chunked_bwd(r, w_pre, k, v, kk_pre, a_pre, n_state ? h0 : nullptr, n_state, d_o, d_ht,
+                                  dr, dw_pre, dk, dv, dkk_pre, da_pre, d_h0, workspace, B, T, H, 0, kept != 0,
+                                  (cudaStream_t)stream, nullptr, nullptr, 0, true);
+}
+
 int rwkvb200_wkv6_fwd(const void* r, const void* k, const void* v, const void* w, const float* u,
                       const float* s0, int n_state, const int32_t* state_map,
                       void* y, float* sT, void* workspace, size_t workspace_bytes,

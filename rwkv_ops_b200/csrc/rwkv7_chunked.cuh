@@ -75,6 +75,16 @@ struct SeqView {
   }
 };
 
+// Fused producers (template parameter FUSED of the intra and final kernels).  The three inputs w, a, b of
+// the delta rule are then computed on the fly from pre-activations p, u, q of the same shape,
+//   w = -e^{-1/2} sigmoid(p),   kk = u / max(|u|_2, 1e-12) over the 64 channels of a head,
+//   a = -kk,   b = kk sigmoid(q),
+// the elementwise tail of an RWKV7 time-mix block; each is rounded to bfloat16 exactly as if it had been
+// materialised as a bfloat16 tensor, so the fused and the unfused operator return the same bits.
+constexpr float W_SCALE = -0.60653065971263342f;
+__device__ __forceinline__ float sigmoidf_(float x) { return 1.f / (1.f + __expf(-x)); }
+__device__ __forceinline__ float round_bf16(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+
 // Rows 0 .. n_rows-1 of a swizzled bf16 tile to token rows `dst`, `dst + st`, ... (st in elements), by all
 // NTHREADS threads of the CTA: the store of a chunk whose last rows belong to the next packed sequence,
 // which a TMA store of the whole box would overwrite.
@@ -116,15 +126,22 @@ inline Workspace carve(void* ws, int B, int T, int H, int tiles_per_chunk) {
 // Backward of the chunked path; `workspace` must hold fwd_workspace_bytes(B, T, H, ALL_TILES).
 // Packed variable-length batches: seq_start / seq_len are device arrays of B entries, Tn the longest length
 // and T_total the number of tokens in the one batch row; dense batches pass nullptr, nullptr, 0.
+// `fused`: w, a, b are the pre-activations p, u, q (dense batches only).
 int launch_rwkv7_chunked_bwd(const void* r, const void* w, const void* k, const void* v, const void* a, const void* b,
                              const float* h0, int n_state, const void* d_o, const float* d_ht,
                              void* dr, void* dw, void* dk, void* dv, void* da, void* db, float* d_h0,
                              void* workspace, int B, int Tn, int H, int head_first, bool kept, cudaStream_t st,
-                             const int* seq_start = nullptr, const int* seq_len = nullptr, int T_total = 0);
+                             const int* seq_start = nullptr, const int* seq_len = nullptr, int T_total = 0,
+                             bool fused = false);
 
 int launch_rwkv7_chunked_fwd(const void* r, const void* w, const void* k, const void* v, const void* a, const void* b,
                              const float* h0, int n_state, void* o, float* ht, void* workspace,
                              int B, int Tn, int H, int head_first, bool keep_for_bwd, cudaStream_t st,
-                             const int* seq_start = nullptr, const int* seq_len = nullptr, int T_total = 0);
+                             const int* seq_start = nullptr, const int* seq_len = nullptr, int T_total = 0,
+                             bool fused = false);
+
+// Fused producers, backward: dw, da, db (in place in the three buffers) -> dp, du, dq.
+int launch_rwkv7_producer_bwd(const void* p, const void* u, const void* q, void* dw_dp, void* da_du, void* db_dq,
+                              long long n_rows, cudaStream_t st);
 
 }  // namespace rwkvb200

@@ -299,7 +299,7 @@ struct FinalSmem {
 // rows wait in registers, so only the first chunk-head of a CTA pays the load latency.
 // 256 threads: warp w reads TMEM lanes 32*(w&3).. (its row), and the two warps that share a lane
 // window split the columns (hsel = w>>2), so every elementwise phase is spread over 8 warps.
-template <bool PACKED>
+template <bool PACKED, bool FUSED>
 __global__ void __launch_bounds__(256)
 r7c_bwd_final_kernel(const bf16* __restrict__ w, const __grid_constant__ CUtensorMap tmap_do,
                      const __grid_constant__ CUtensorMap tmap_v, const unsigned char* __restrict__ ws_tiles,
@@ -427,8 +427,13 @@ r7c_bwd_final_kernel(const bf16* __restrict__ w, const __grid_constant__ CUtenso
       float g[8];
 #pragma unroll
       for (int m = 0; m < 4; ++m) {
-        g[2 * m] = valid ? -__expf(bf16_lo(u[m])) : 0.f;
-        g[2 * m + 1] = valid ? -__expf(bf16_hi(u[m])) : 0.f;
+        float w0 = bf16_lo(u[m]), w1 = bf16_hi(u[m]);
+        if constexpr (FUSED) {      // the rows hold p: w = -e^{-1/2} sigmoid(p), as a bfloat16 value
+          w0 = round_bf16(W_SCALE * sigmoidf_(w0));
+          w1 = round_bf16(W_SCALE * sigmoidf_(w1));
+        }
+        g[2 * m] = valid ? -__expf(w0) : 0.f;
+        g[2 * m + 1] = valid ? -__expf(w1) : 0.f;
       }
       *reinterpret_cast<float4*>(&sm.gg[row * NROW + 8 * cc]) = make_float4(g[0], g[1], g[2], g[3]);
       *reinterpret_cast<float4*>(&sm.gg[row * NROW + 8 * cc + 4]) = make_float4(g[4], g[5], g[6], g[7]);
@@ -652,19 +657,80 @@ r7c_bwd_final_kernel(const bf16* __restrict__ w, const __grid_constant__ CUtenso
 #undef R7C_STAMP
 }
 
+// ---------------------------------------------------------------------------------------------
+// 6. fused producers, backward: one 64-channel row per 8 threads (16 bytes each), in place
+//      dp = dw W_SCALE s_p (1 - s_p),  s_p = sigmoid(p)
+//      dkk = -da + db s_q,  s_q = sigmoid(q);   dq = db kk s_q (1 - s_q)
+//      du = (dkk - kk (kk . dkk)) / |u|,  kk = u / |u|
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+r7c_producer_bwd_kernel(const bf16* __restrict__ p, const bf16* __restrict__ u, const bf16* __restrict__ q,
+                        bf16* dw_dp, bf16* da_du, bf16* db_dq, long long n_rows) {
+  const long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long row = t >> 3;
+  const bool live = row < n_rows;
+  const long long off = (live ? row : 0) * 64 + 8 * (t & 7);
+  float pv[8], uv[8], qv[8], dw[8], da[8], db[8];
+  auto load8 = [&](const bf16* src, float* x) {
+    const uint4 w4 = *reinterpret_cast<const uint4*>(src + off);
+    const uint32_t w[4] = {w4.x, w4.y, w4.z, w4.w};
+#pragma unroll
+    for (int m = 0; m < 4; ++m) { x[2 * m] = bf16_lo(w[m]); x[2 * m + 1] = bf16_hi(w[m]); }
+  };
+  auto store8 = [&](bf16* dst, const float* x) {
+    *reinterpret_cast<uint4*>(dst + off) = make_uint4(pack_bf16(x[0], x[1]), pack_bf16(x[2], x[3]),
+                                                      pack_bf16(x[4], x[5]), pack_bf16(x[6], x[7]));
+  };
+  load8(p, pv); load8(u, uv); load8(q, qv); load8(dw_dp, dw); load8(da_du, da); load8(db_dq, db);
+  float ss = 0.f;
+#pragma unroll
+  for (int x = 0; x < 8; ++x) ss += uv[x] * uv[x];
+  ss += __shfl_xor_sync(0xffffffffu, ss, 1);
+  ss += __shfl_xor_sync(0xffffffffu, ss, 2);
+  ss += __shfl_xor_sync(0xffffffffu, ss, 4);
+  const float inv = 1.f / fmaxf(sqrtf(ss), 1e-12f);
+  float kk[8], dkk[8], dot = 0.f, dp[8], dq[8], du[8];
+#pragma unroll
+  for (int x = 0; x < 8; ++x) {
+    const float sp = sigmoidf_(pv[x]), sq = sigmoidf_(qv[x]);
+    kk[x] = uv[x] * inv;
+    dp[x] = dw[x] * W_SCALE * sp * (1.f - sp);
+    dkk[x] = -da[x] + db[x] * sq;
+    dq[x] = db[x] * kk[x] * sq * (1.f - sq);
+    dot += kk[x] * dkk[x];
+  }
+  dot += __shfl_xor_sync(0xffffffffu, dot, 1);
+  dot += __shfl_xor_sync(0xffffffffu, dot, 2);
+  dot += __shfl_xor_sync(0xffffffffu, dot, 4);
+#pragma unroll
+  for (int x = 0; x < 8; ++x) du[x] = (dkk[x] - kk[x] * dot) * inv;
+  if (live) { store8(dw_dp, dp); store8(da_du, du); store8(db_dq, dq); }
+}
+
 }  // namespace r7c
+
+int launch_rwkv7_producer_bwd(const void* p, const void* u, const void* q, void* dw_dp, void* da_du, void* db_dq,
+                              long long n_rows, cudaStream_t st) {
+  typedef __nv_bfloat16 bf16;
+  ProfScope prof("r7c_producer_bwd_kernel", st);
+  const long long threads = n_rows * 8;
+  r7c::r7c_producer_bwd_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, st>>>(
+      (const bf16*)p, (const bf16*)u, (const bf16*)q, (bf16*)dw_dp, (bf16*)da_du, (bf16*)db_dq, n_rows);
+  return check_launch();
+}
 
 int launch_rwkv7_chunked_bwd(const void* r, const void* w, const void* k, const void* v, const void* a, const void* b,
                              const float* h0, int n_state, const void* d_o, const float* d_ht,
                              void* dr, void* dw, void* dk, void* dv, void* da, void* db, float* d_h0,
                              void* workspace, int B, int Tn, int H, int head_first, bool kept, cudaStream_t st,
-                             const int* seq_start, const int* seq_len, int T_total) {
+                             const int* seq_start, const int* seq_len, int T_total, bool fused) {
   using namespace r7c;
+  if (fused && (seq_start || head_first)) return RWKVB200_E_UNSUPPORTED;
   typedef __nv_bfloat16 bf16;
   int e = RWKVB200_OK;
   if (!kept) {   // the workspace does not hold a forward pass yet: recompute it from the inputs
     e = launch_rwkv7_chunked_fwd(r, w, k, v, a, b, h0, n_state, nullptr, nullptr, workspace, B, Tn, H, head_first,
-                                 true, st, seq_start, seq_len, T_total);
+                                 true, st, seq_start, seq_len, T_total, fused);
     if (e) return e;
   }
   int* status = device_status_ptr();
@@ -715,16 +781,25 @@ int launch_rwkv7_chunked_bwd(const void* r, const void* w, const void* k, const 
     if (cuda_ok(cudaGetDevice(&dev)) || cuda_ok(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)))
       return RWKVB200_E_CUDA;
     const int grid = n_ch < sms ? n_ch : sms;     // persistent: one CTA per SM
-    R7C_DISPATCH_PACKED(
-      if (cuda_ok(cudaFuncSetAttribute(r7c_bwd_final_kernel<P>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)))
-        return RWKVB200_E_CUDA;
-      r7c_bwd_final_kernel<P><<<grid, 256, smem, st>>>((const bf16*)w, tmap_do, tmap_v, ws.tiles, ALL_TILES,
-                                                       tmap_out[0], tmap_out[1], tmap_out[2], tmap_out[3],
-                                                       tmap_out[4], tmap_out[5], (bf16*)dr, (bf16*)dw, (bf16*)dk,
-                                                       (bf16*)dv, (bf16*)da, (bf16*)db, sv, H, NT, n_ch, lay, status,
-                                                       debug_stamp_buffer()));
+#define R7C_LAUNCH_FINAL(P, F)                                                                                    \
+    do {                                                                                                          \
+      if (cuda_ok(cudaFuncSetAttribute(r7c_bwd_final_kernel<P, F>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem))) \
+        return RWKVB200_E_CUDA;                                                                                   \
+      r7c_bwd_final_kernel<P, F><<<grid, 256, smem, st>>>((const bf16*)w, tmap_do, tmap_v, ws.tiles, ALL_TILES,   \
+          tmap_out[0], tmap_out[1], tmap_out[2], tmap_out[3], tmap_out[4], tmap_out[5], (bf16*)dr, (bf16*)dw,     \
+          (bf16*)dk, (bf16*)dv, (bf16*)da, (bf16*)db, sv, H, NT, n_ch, lay, status, debug_stamp_buffer());        \
+    } while (0)
+    if (seq_start) R7C_LAUNCH_FINAL(true, false);
+    else if (fused) R7C_LAUNCH_FINAL(false, true);
+    else R7C_LAUNCH_FINAL(false, false);
+#undef R7C_LAUNCH_FINAL
   }
 #undef R7C_DISPATCH_PACKED
+  if (fused) {      // dw, da, db -> gradients of the pre-activations, in place
+    e = check_launch();
+    if (e) return e;
+    return launch_rwkv7_producer_bwd(w, a, b, dw, da, db, (long long)B * Tn * H, st);
+  }
   return check_launch();
 }
 

@@ -37,7 +37,7 @@ struct IntraSmem {
 // MMA 2 has read the current one, and the rows of the one after that are asked into L2.
 // 256 threads: warp w reads TMEM lanes 32*(w&3).. and the two warps that share a lane window split
 // the columns (hsel = w>>2); the triangular solve runs on warps 0-1 while the other warps drain MMA 2.
-template <bool PACKED>
+template <bool PACKED, bool FUSED>
 __global__ void __launch_bounds__(256, 2)
 r7c_intra_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ w, const bf16* __restrict__ k,
                      const bf16* __restrict__ a, const bf16* __restrict__ b,
@@ -157,8 +157,13 @@ r7c_intra_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ w, con
         const uint32_t u[4] = {rw[n].x, rw[n].y, rw[n].z, rw[n].w};
 #pragma unroll
         for (int m = 0; m < 4; ++m) {
-          gown[n][2 * m] = valid ? -__expf(bf16_lo(u[m])) : 0.f;
-          gown[n][2 * m + 1] = valid ? -__expf(bf16_hi(u[m])) : 0.f;
+          float w0 = bf16_lo(u[m]), w1 = bf16_hi(u[m]);
+          if constexpr (FUSED) {      // the tile holds p: w = -e^{-1/2} sigmoid(p), as a bfloat16 value
+            w0 = round_bf16(W_SCALE * sigmoidf_(w0));
+            w1 = round_bf16(W_SCALE * sigmoidf_(w1));
+          }
+          gown[n][2 * m] = valid ? -__expf(w0) : 0.f;
+          gown[n][2 * m + 1] = valid ? -__expf(w1) : 0.f;
         }
         *reinterpret_cast<float4*>(&gs[row * NROW + 8 * cc]) = make_float4(gown[n][0], gown[n][1], gown[n][2], gown[n][3]);
         *reinterpret_cast<float4*>(&gs[row * NROW + 8 * cc + 4]) = make_float4(gown[n][4], gown[n][5], gown[n][6], gown[n][7]);
@@ -199,6 +204,27 @@ r7c_intra_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ w, con
         rb[n] = *reinterpret_cast<const uint4*>(sm.bt + off);
         if (PACKED && t0 + (e >> 3) >= Tn) {      // in a packed batch these rows belong to the next sequence
           rq[n] = make_uint4(0u, 0u, 0u, 0u); rk[n] = rq[n]; ra[n] = rq[n]; rb[n] = rq[n];
+        }
+        if constexpr (FUSED) {      // the a / b tiles hold u and q: a = -kk, b = kk sigmoid(q), kk = u / |u|
+          const uint32_t uu[4] = {ra[n].x, ra[n].y, ra[n].z, ra[n].w}, qq[4] = {rb[n].x, rb[n].y, rb[n].z, rb[n].w};
+          float uv[8], ss = 0.f;
+#pragma unroll
+          for (int m = 0; m < 4; ++m) { uv[2 * m] = bf16_lo(uu[m]); uv[2 * m + 1] = bf16_hi(uu[m]); }
+#pragma unroll
+          for (int x = 0; x < 8; ++x) ss += uv[x] * uv[x];
+          ss += __shfl_xor_sync(0xffffffffu, ss, 1);      // the 8 threads of a token row are neighbouring lanes
+          ss += __shfl_xor_sync(0xffffffffu, ss, 2);
+          ss += __shfl_xor_sync(0xffffffffu, ss, 4);
+          const float inv = 1.f / fmaxf(sqrtf(ss), 1e-12f);
+          uint32_t na[4], nb[4];
+#pragma unroll
+          for (int m = 0; m < 4; ++m) {
+            const float k0 = uv[2 * m] * inv, k1 = uv[2 * m + 1] * inv;
+            na[m] = pack_bf16(-k0, -k1);
+            nb[m] = pack_bf16(k0 * sigmoidf_(bf16_lo(qq[m])), k1 * sigmoidf_(bf16_hi(qq[m])));
+          }
+          ra[n] = make_uint4(na[0], na[1], na[2], na[3]);
+          rb[n] = make_uint4(nb[0], nb[1], nb[2], nb[3]);
         }
       }
 #pragma unroll
@@ -774,9 +800,10 @@ r7c_scan_fwd_kernel(const __grid_constant__ CUtensorMap tmap_v, const unsigned c
 int launch_rwkv7_chunked_fwd(const void* r, const void* w, const void* k, const void* v, const void* a, const void* b,
                              const float* h0, int n_state, void* o, float* ht, void* workspace,
                              int B, int Tn, int H, int head_first, bool keep_for_bwd, cudaStream_t st,
-                             const int* seq_start, const int* seq_len, int T_total) {
+                             const int* seq_start, const int* seq_len, int T_total, bool fused) {
   using namespace r7c;
   typedef __nv_bfloat16 bf16;
+  if (fused && seq_start) return RWKVB200_E_UNSUPPORTED;
   const SeqView sv{seq_start, seq_len, Tn};
   const int mapB = seq_start ? 1 : B, mapT = seq_start ? T_total : Tn;   // shape of the token tensors
   int* status = device_status_ptr();
@@ -804,15 +831,17 @@ int launch_rwkv7_chunked_fwd(const void* r, const void* w, const void* k, const 
     if (cuda_ok(cudaGetDevice(&dev)) || cuda_ok(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)))
       return RWKVB200_E_CUDA;
     const int grid = n_ch < 2 * sms ? n_ch : 2 * sms;     // persistent: two CTAs per SM
-#define R7C_LAUNCH_INTRA(P)                                                                                        \
+#define R7C_LAUNCH_INTRA(P, F)                                                                                     \
     do {                                                                                                           \
-      if (cuda_ok(cudaFuncSetAttribute(r7c_intra_fwd_kernel<P>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem))) \
+      if (cuda_ok(cudaFuncSetAttribute(r7c_intra_fwd_kernel<P, F>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem))) \
         return RWKVB200_E_CUDA;                                                                                    \
-      r7c_intra_fwd_kernel<P><<<grid, 256, smem, st>>>((const bf16*)r, (const bf16*)w, (const bf16*)k,            \
+      r7c_intra_fwd_kernel<P, F><<<grid, 256, smem, st>>>((const bf16*)r, (const bf16*)w, (const bf16*)k,         \
           (const bf16*)a, (const bf16*)b, tmap_in[0], tmap_in[1], tmap_in[2], tmap_in[3], tmap_in[4], tmap_v,      \
           ws.tiles, ws.aux, tpc, keep_for_bwd ? 1 : 0, sv, H, NT, n_ch, lay, status, debug_stamp_buffer());        \
     } while (0)
-    if (seq_start) R7C_LAUNCH_INTRA(true); else R7C_LAUNCH_INTRA(false);
+    if (seq_start) R7C_LAUNCH_INTRA(true, false);
+    else if (fused) R7C_LAUNCH_INTRA(false, true);
+    else R7C_LAUNCH_INTRA(false, false);
 #undef R7C_LAUNCH_INTRA
   }
   e = check_launch();

@@ -5,6 +5,7 @@
     python -m rwkv_ops_b200.microbench wkv6  [--B 16 --T 4096 --H 32 --steps 5]
     python -m rwkv_ops_b200.microbench rwkv7 [--B 8 --T 4096 --H 32 --steps 5 --dtype bf16 --algo auto]
     python -m rwkv_ops_b200.microbench varlen [--B 8 --T 4096 --H 32]     (packed sequences vs padded)
+    python -m rwkv_ops_b200.microbench fused  [--B 8 --T 4096 --H 32]     (producers of w, a, b fused in vs torch)
     python -m torch.distributed.run --nproc-per-node 2 --master-addr 127.0.0.1 -m rwkv_ops_b200.microbench sp
 
 Each prints one JSON line with the time per call and the achieved algorithmic bandwidth.  These
@@ -130,6 +131,32 @@ def bench_varlen(a):
             "kernel_ms": kern}
 
 
+def bench_fused(a):
+    """Forward + backward with the producers of w, a, b inside the operator, against the same producers as
+    torch elementwise ops (with autograd) in front of the plain operator; bf16."""
+    from rwkv_ops_b200.fused import producers
+    gen = torch.Generator(device="cuda").manual_seed(1001)
+    names = ("r", "w_pre", "k", "v", "kk_pre", "a_pre")
+    x = {n: torch.randn(a.B, a.T, a.H, 64, generator=gen, device="cuda").bfloat16().requires_grad_(True) for n in names}
+    d_out = torch.randn(a.B, a.T, a.H, 64, generator=gen, device="cuda").bfloat16()
+    d_state = 0.1 * torch.randn(a.B, a.H, 64, 64, generator=gen, device="cuda")
+
+    def fused():
+        o, s = ro.generalized_delta_rule_fused(*[x[n] for n in names])
+        torch.autograd.backward([o, s], [d_out, d_state])
+
+    def unfused():
+        w, aa, bb = producers(x["w_pre"], x["kk_pre"], x["a_pre"])
+        o, s = ro.generalized_delta_rule(x["r"], w, x["k"], x["v"], aa, bb)
+        torch.autograd.backward([o, s], [d_out, d_state])
+
+    ms_fused, kern = _time(fused, a.steps)
+    ms_unfused, _ = _time(unfused, a.steps)
+    return {"op": "rwkv7_fwd_bwd_fused_producers", "B": a.B, "T": a.T, "H": a.H, "ms_fused": ms_fused,
+            "ms_unfused_torch_producers": ms_unfused, "tokens_per_s_fused": a.B * a.T / (ms_fused / 1e3),
+            "tokens_per_s_unfused": a.B * a.T / (ms_unfused / 1e3), "kernel_ms": kern}
+
+
 def bench_sp(a):
     """Sequence-parallel forward + backward: every rank holds T tokens of each of B sequences (the whole
     sequence is world x T long); run under torchrun, one rank per GPU.  Time = max over ranks."""
@@ -209,7 +236,7 @@ def bench_rwkv7(a):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("op", choices=["step", "wkv6", "rwkv7", "varlen", "sp"])
+    ap.add_argument("op", choices=["step", "wkv6", "rwkv7", "varlen", "sp", "fused"])
     ap.add_argument("--groups", type=int, default=4, help="sp: batch groups pipelined along the chain of ranks")
     ap.add_argument("--B", type=int)
     ap.add_argument("--T", type=int, default=4096)
@@ -221,13 +248,13 @@ def main():
                     help="step: decode in place on one state buffer of this type (rwkvb200_rwkv7_decode_step)")
     ap.add_argument("--fwd-only", action="store_true")
     a = ap.parse_args()
-    defaults = {"step": (256, 64, "bf16"), "wkv6": (16, 32, "f32"), "rwkv7": (8, 32, "bf16"), "varlen": (8, 32, "bf16"), "sp": (8, 32, "bf16")}[a.op]
+    defaults = {"step": (256, 64, "bf16"), "wkv6": (16, 32, "f32"), "rwkv7": (8, 32, "bf16"), "varlen": (8, 32, "bf16"), "sp": (8, 32, "bf16"), "fused": (8, 32, "bf16")}[a.op]
     a.B = a.B or defaults[0]
     a.H = a.H or defaults[1]
     a.dtype = a.dtype or defaults[2]
     if a.op != "sp":
         torch.cuda.set_device(0)
-    res = {"step": bench_step, "wkv6": bench_wkv6, "rwkv7": bench_rwkv7, "varlen": bench_varlen, "sp": bench_sp}[a.op](a)
+    res = {"step": bench_step, "wkv6": bench_wkv6, "rwkv7": bench_rwkv7, "varlen": bench_varlen, "sp": bench_sp, "fused": bench_fused}[a.op](a)
     if res is not None:
         print(json.dumps(res), flush=True)
 
