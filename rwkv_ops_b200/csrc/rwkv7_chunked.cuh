@@ -82,7 +82,7 @@ struct SeqView {
 // the elementwise tail of an RWKV7 time-mix block; each is rounded to bfloat16 exactly as if it had been
 // materialised as a bfloat16 tensor, so the fused and the unfused operator return the same bits.
 constexpr float W_SCALE = -0.60653065971263342f;
-__device__ __forceinline__ float sigmoidf_(float x) { return 1.f / (1.f + __expf(-x)); }
+__device__ __forceinline__ float sigmoidf_(float x) { return __fdividef(1.f, 1.f + __expf(-x)); }
 __device__ __forceinline__ float round_bf16(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
 
 // Rows 0 .. n_rows-1 of a swizzled bf16 tile to token rows `dst`, `dst + st`, ... (st in elements), by all

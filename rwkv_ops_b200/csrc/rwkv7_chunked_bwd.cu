@@ -688,7 +688,7 @@ r7c_producer_bwd_kernel(const bf16* __restrict__ p, const bf16* __restrict__ u, 
   ss += __shfl_xor_sync(0xffffffffu, ss, 1);
   ss += __shfl_xor_sync(0xffffffffu, ss, 2);
   ss += __shfl_xor_sync(0xffffffffu, ss, 4);
-  const float inv = 1.f / fmaxf(sqrtf(ss), 1e-12f);
+  const float inv = rsqrtf(fmaxf(ss, 1e-24f));      // 1 / max(|u|, 1e-12)
   float kk[8], dkk[8], dot = 0.f, dp[8], dq[8], du[8];
 #pragma unroll
   for (int x = 0; x < 8; ++x) {

@@ -215,7 +215,7 @@ r7c_intra_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ w, con
           ss += __shfl_xor_sync(0xffffffffu, ss, 1);      // the 8 threads of a token row are neighbouring lanes
           ss += __shfl_xor_sync(0xffffffffu, ss, 2);
           ss += __shfl_xor_sync(0xffffffffu, ss, 4);
-          const float inv = 1.f / fmaxf(sqrtf(ss), 1e-12f);
+          const float inv = rsqrtf(fmaxf(ss, 1e-24f));      // 1 / max(|u|, 1e-12)
           uint32_t na[4], nb[4];
 #pragma unroll
           for (int m = 0; m < 4; ++m) {
