@@ -97,7 +97,10 @@ def bench_varlen(a):
     from rwkv_ops_b200 import generalized_delta_rule_varlen
     gen = torch.Generator().manual_seed(1001)
     n_seq = a.B
-    lens = torch.randint(a.T // 16, a.T + 1, (n_seq,), generator=gen).tolist()
+    if a.tail:      # the padding pattern of benchmark configuration 2: T minus up to `tail` tokens
+        lens = (a.T - torch.randint(0, a.tail + 1, (n_seq,), generator=gen)).tolist()
+    else:
+        lens = torch.randint(a.T // 16, a.T + 1, (n_seq,), generator=gen).tolist()
     cu = [0]
     for n in lens:
         cu.append(cu[-1] + n)
@@ -237,6 +240,8 @@ def bench_rwkv7(a):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("op", choices=["step", "wkv6", "rwkv7", "varlen", "sp", "fused"])
+    ap.add_argument("--tail", type=int, default=0,
+                    help="varlen: lengths are T minus a random 0..tail tokens instead of uniform in [T/16, T]")
     ap.add_argument("--groups", type=int, default=4, help="sp: batch groups pipelined along the chain of ranks")
     ap.add_argument("--B", type=int)
     ap.add_argument("--T", type=int, default=4096)
