@@ -88,8 +88,9 @@ __device__ __forceinline__ float round_bf16(float x) { return __bfloat162float(_
 // Rows 0 .. n_rows-1 of a swizzled bf16 tile to token rows `dst`, `dst + st`, ... (st in elements), by all
 // NTHREADS threads of the CTA: the store of a chunk whose last rows belong to the next packed sequence,
 // which a TMA store of the whole box would overwrite.
+// (Kept out of line: it runs for one chunk per sequence and would only lengthen the persistent loops.)
 template <int NTHREADS>
-__device__ __forceinline__ void store_tile_rows(__nv_bfloat16* dst, long long st, const unsigned char* tile,
+__device__ __noinline__ void store_tile_rows(__nv_bfloat16* dst, long long st, const unsigned char* tile,
                                                 int n_rows, int tid) {
   for (int e = tid; e < 512; e += NTHREADS) {
     const int row = e >> 3, cc = e & 7;
