@@ -75,6 +75,24 @@ struct SeqView {
   }
 };
 
+// Position of a persistent CTA in the list of chunk slots: slot index, sequence, head, chunk within the
+// sequence.  Stepping by the grid size updates it without the divisions of the direct formula.
+struct ChunkPos { int ch, bi, hi, c; };
+__device__ __forceinline__ ChunkPos chunk_pos(int ch, int NT, int H) {
+  ChunkPos p;
+  const int unit = ch / NT;
+  p.ch = ch; p.c = ch % NT; p.bi = unit / H; p.hi = unit % H;
+  return p;
+}
+__device__ __forceinline__ void chunk_step(ChunkPos& p, int stride, int NT, int H) {
+  p.ch += stride;
+  p.c += stride;
+  while (p.c >= NT) {
+    p.c -= NT;
+    if (++p.hi == H) { p.hi = 0; ++p.bi; }
+  }
+}
+
 // Fused producers (template parameter FUSED of the intra and final kernels).  The three inputs w, a, b of
 // the delta rule are then computed on the fly from pre-activations p, u, q of the same shape,
 //   w = -e^{-1/2} sigmoid(p),   kk = u / max(|u|_2, 1e-12) over the 64 channels of a head,

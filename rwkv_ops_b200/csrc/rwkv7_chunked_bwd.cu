@@ -326,13 +326,10 @@ r7c_bwd_final_kernel(const bf16* __restrict__ w, const __grid_constant__ CUtenso
   tc_fence_after();
   const uint32_t tm = sm.tmem_base;
 
-  auto coords = [&](int ch, int& bi, int& hi, int& t0) {
-    const int unit = ch / NT;
-    bi = unit / H; hi = unit % H; t0 = (ch % NT) * L;
-  };
-  auto load_group_a = [&](int ch) {     // tid 0
-    int bi, hi, t0; coords(ch, bi, hi, t0);
-    const unsigned char* tiles = ws_tiles + (size_t)ch * tiles_per_chunk * TILE_BYTES;
+  auto coords = [&](const ChunkPos& p, int& bi, int& hi, int& t0) { bi = p.bi; hi = p.hi; t0 = p.c * L; };
+  auto load_group_a = [&](const ChunkPos& p) {     // tid 0
+    int bi, hi, t0; coords(p, bi, hi, t0);
+    const unsigned char* tiles = ws_tiles + (size_t)p.ch * tiles_per_chunk * TILE_BYTES;
     mbar_expect_tx(&sm.bar_lda, 8 * TILE_BYTES);
     tma_load_4d(sm.dout, &tmap_do, &sm.bar_lda, 0, sv.first<PACKED>(bi) + t0, hi, sv.row<PACKED>(bi));
     tma_load_4d(sm.v, &tmap_v, &sm.bar_lda, 0, sv.first<PACKED>(bi) + t0, hi, sv.row<PACKED>(bi));
@@ -342,8 +339,8 @@ r7c_bwd_final_kernel(const bf16* __restrict__ w, const __grid_constant__ CUtenso
     bulk_load(sm.h0, tiles + S_H0 * TILE_BYTES, TILE_BYTES, &sm.bar_lda);
     bulk_load(sm.dhh, tiles + S_DHH * TILE_BYTES, TILE_BYTES, &sm.bar_lda);
   };
-  auto load_group_b = [&](int ch) {     // tid 0
-    const unsigned char* tiles = ws_tiles + (size_t)ch * tiles_per_chunk * TILE_BYTES;
+  auto load_group_b = [&](const ChunkPos& p) {     // tid 0
+    const unsigned char* tiles = ws_tiles + (size_t)p.ch * tiles_per_chunk * TILE_BYTES;
     mbar_expect_tx(&sm.bar_ldb, 4 * TILE_BYTES);
     bulk_load(sm.qt, tiles + S_QT * TILE_BYTES, TILE_BYTES, &sm.bar_ldb);
     bulk_load(sm.at, tiles + S_AT * TILE_BYTES, TILE_BYTES, &sm.bar_ldb);
@@ -352,9 +349,9 @@ r7c_bwd_final_kernel(const bf16* __restrict__ w, const __grid_constant__ CUtenso
   };
   // Ask for everything a chunk-head will load to be brought into L2 (issued one chunk-head ahead of the
   // loads themselves, which then take an L2 round trip instead of a DRAM one).
-  auto prefetch_l2 = [&](int ch) {      // one warp
-    int bi, hi, t0; coords(ch, bi, hi, t0);
-    const unsigned char* tiles = ws_tiles + (size_t)ch * tiles_per_chunk * TILE_BYTES;
+  auto prefetch_l2 = [&](const ChunkPos& p) {      // one warp
+    int bi, hi, t0; coords(p, bi, hi, t0);
+    const unsigned char* tiles = ws_tiles + (size_t)p.ch * tiles_per_chunk * TILE_BYTES;
     if (lane == 0) {
       tma_prefetch_4d(&tmap_do, 0, sv.first<PACKED>(bi) + t0, hi, sv.row<PACKED>(bi));
       tma_prefetch_4d(&tmap_v, 0, sv.first<PACKED>(bi) + t0, hi, sv.row<PACKED>(bi));
@@ -371,8 +368,8 @@ r7c_bwd_final_kernel(const bf16* __restrict__ w, const __grid_constant__ CUtenso
       if (tok < Tn) asm volatile("prefetch.global.L2 [%0];" ::"l"(w + base + (long long)tok * lay.st));
     }
   };
-  auto load_w = [&](int ch, uint4 (&rw)[2]) {   // all threads: 2 x 8 channels of the chunk's w rows
-    int bi, hi, t0; coords(ch, bi, hi, t0);
+  auto load_w = [&](const ChunkPos& p, uint4 (&rw)[2]) {   // all threads: 2 x 8 channels of the chunk's w rows
+    int bi, hi, t0; coords(p, bi, hi, t0);
     const int Tn = sv.length<PACKED>(bi);
     const long long base = sv.row<PACKED>(bi) * lay.sb + hi * lay.sh + sv.first<PACKED>(bi) * lay.st;
 #pragma unroll
@@ -384,30 +381,31 @@ r7c_bwd_final_kernel(const bf16* __restrict__ w, const __grid_constant__ CUtenso
   };
 
   // chunk slots past the end of a (packed) sequence are skipped
-  auto empty = [&](int ch) {
+  auto empty = [&](const ChunkPos& p) {
     if constexpr (!PACKED) return false;      // a dense batch has no empty slots
-    int bi, hi, t0; coords(ch, bi, hi, t0);
-    return t0 >= sv.length<PACKED>(bi);
+    return p.c * L >= sv.length<PACKED>(p.bi);
   };
-  auto advance = [&](int ch) {
-    do { ch += gridDim.x; } while (ch < n_ch && empty(ch));
-    return ch;
+  auto advance = [&](ChunkPos p) {
+    do { chunk_step(p, gridDim.x, NT, H); } while (p.ch < n_ch && empty(p));
+    return p;
   };
-  int ch_first = blockIdx.x;
-  if (ch_first < n_ch && empty(ch_first)) ch_first = advance(ch_first);
+  ChunkPos cur = chunk_pos(blockIdx.x, NT, H);
+  if (cur.ch < n_ch && empty(cur)) cur = advance(cur);
+  ChunkPos nxt = cur;     // the chunk-head after `cur`, and the one after that (found once per iteration)
+  if (cur.ch < n_ch) nxt = advance(cur);
 
   uint4 rw[2];
-  if (ch_first < n_ch) {
-    if (tid == 0) { load_group_a(ch_first); load_group_b(ch_first); }
-    load_w(ch_first, rw);
-    const int second = advance(ch_first);
-    if (warp == 1 && second < n_ch) prefetch_l2(second);
+  if (cur.ch < n_ch) {
+    if (tid == 0) { load_group_a(cur); load_group_b(cur); }
+    load_w(cur, rw);
+    if (warp == 1 && nxt.ch < n_ch) prefetch_l2(nxt);
   }
 
   bool ok = true;
   int it = 0;
-  for (int ch = ch_first, next; ch < n_ch && ok; ch = next, ++it) {
-    int bi, hi, t0; coords(ch, bi, hi, t0);
+  for (ChunkPos aft = nxt; cur.ch < n_ch && ok; cur = nxt, nxt = aft, ++it) {
+    const int ch = cur.ch, next = nxt.ch;
+    int bi, hi, t0; coords(cur, bi, hi, t0);
     const int Tn = sv.length<PACKED>(bi);
     // in a packed batch the last rows of a sequence's last chunk belong to the next sequence: such a chunk
     // is stored row by row instead of by TMA boxes
@@ -415,7 +413,6 @@ r7c_bwd_final_kernel(const bf16* __restrict__ w, const __grid_constant__ CUtenso
     const long long out_base = sv.row<PACKED>(bi) * lay.sb + hi * lay.sh + (long long)(sv.first<PACKED>(bi) + t0) * lay.st;
     const unsigned char* tiles = ws_tiles + (size_t)ch * tiles_per_chunk * TILE_BYTES;
     const uint32_t par = it & 1;
-    next = advance(ch);
     R7C_STAMP(16);
 
     // ---- g of every (token, channel), from the w rows already in registers
@@ -548,10 +545,10 @@ r7c_bwd_final_kernel(const bf16* __restrict__ w, const __grid_constant__ CUtenso
     R7C_STAMP(21);
     // group A tiles are free: request the next chunk-head's, and fetch its w rows
     if (next < n_ch) {
-      if (tid == 0 && ok) { bulk_wait_read(); load_group_a(next); }
-      load_w(next, rw);
-      const int after = advance(next);
-      if (warp == 1 && after < n_ch) prefetch_l2(after);
+      if (tid == 0 && ok) { bulk_wait_read(); load_group_a(nxt); }
+      load_w(nxt, rw);
+      aft = advance(nxt);
+      if (warp == 1 && aft.ch < n_ch) prefetch_l2(aft);
     }
 
     // ---- epilogue.  Row r < 64 holds dq~_i and dk~_i (token i = r), row r >= 64 holds da~_i, db~_i; the
@@ -616,7 +613,7 @@ r7c_bwd_final_kernel(const bf16* __restrict__ w, const __grid_constant__ CUtenso
         tma_store_4d(&tmap_db, sm.stage[3], 0, tt, hi, br);
         bulk_commit();
       }
-      if (next < n_ch) load_group_b(next);      // q~, a~, k~, b~ were last read by the epilogue above
+      if (next < n_ch) load_group_b(nxt);       // q~, a~, k~, b~ were last read by the epilogue above
     }
     // reverse inclusive prefix over tokens, per channel; thread = (channel, quarter)
     {

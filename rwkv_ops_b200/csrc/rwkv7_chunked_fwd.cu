@@ -63,21 +63,18 @@ r7c_intra_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ w, con
   tc_fence_after();
   const uint32_t tm = sm.tmem_base;
 
-  auto coords = [&](int ch, int& bi, int& hi, int& t0) {
-    const int unit = ch / NT;
-    bi = unit / H; hi = unit % H; t0 = (ch % NT) * L;
-  };
+  auto coords = [&](const ChunkPos& p, int& bi, int& hi, int& t0) { bi = p.bi; hi = p.hi; t0 = p.c * L; };
   // The raw tiles of a chunk-head (rows past the end of the sequence arrive as zeros).  w, needed first,
   // lands in the A_qk tile, free from the end of the triangular inverse to the first epilogue of the next
   // chunk-head; q, k, a, b, needed only after the prefix sums, land in the tiles that will hold their
   // scaled versions once those have been copied out.
-  auto load_w = [&](int ch) {       // tid 0
-    int bi, hi, t0; coords(ch, bi, hi, t0);
+  auto load_w = [&](const ChunkPos& p) {       // tid 0
+    int bi, hi, t0; coords(p, bi, hi, t0);
     mbar_expect_tx(&sm.bar_w, TILE_BYTES);
     tma_load_4d(sm.aqk, &tmap_w, &sm.bar_w, 0, sv.first<PACKED>(bi) + t0, hi, sv.row<PACKED>(bi));
   };
-  auto load_in = [&](int ch) {      // tid 0
-    int bi, hi, t0; coords(ch, bi, hi, t0);
+  auto load_in = [&](const ChunkPos& p) {      // tid 0
+    int bi, hi, t0; coords(p, bi, hi, t0);
     const int tt = sv.first<PACKED>(bi) + t0, br = sv.row<PACKED>(bi);
     mbar_expect_tx(&sm.bar_in, 4 * TILE_BYTES);
     tma_load_4d(sm.qt, &tmap_q, &sm.bar_in, 0, tt, hi, br);
@@ -86,18 +83,17 @@ r7c_intra_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ w, con
     tma_load_4d(sm.bt, &tmap_b, &sm.bar_in, 0, tt, hi, br);
   };
   // chunk slots past the end of a (packed) sequence are skipped
-  auto empty = [&](int ch) {
+  auto empty = [&](const ChunkPos& p) {
     if constexpr (!PACKED) return false;      // a dense batch has no empty slots
-    int bi, hi, t0; coords(ch, bi, hi, t0);
-    return t0 >= sv.length<PACKED>(bi);
+    return p.c * L >= sv.length<PACKED>(p.bi);
   };
-  auto advance = [&](int ch) {
-    do { ch += gridDim.x; } while (ch < n_ch && empty(ch));
-    return ch;
+  auto advance = [&](ChunkPos p) {
+    do { chunk_step(p, gridDim.x, NT, H); } while (p.ch < n_ch && empty(p));
+    return p;
   };
   // Ask for a chunk-head's token rows to be brought into L2, ahead of the TMA loads above.
-  auto prefetch_rows = [&](int ch) {
-    int bi, hi, t0; coords(ch, bi, hi, t0);
+  auto prefetch_rows = [&](const ChunkPos& p) {
+    int bi, hi, t0; coords(p, bi, hi, t0);
     const int Tn = sv.length<PACKED>(bi);
     const long long base = sv.row<PACKED>(bi) * lay.sb + hi * lay.sh + sv.first<PACKED>(bi) * lay.st;
 #pragma unroll
@@ -113,14 +109,14 @@ r7c_intra_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ w, con
       }
     }
   };
-  auto load_v = [&](int ch) {   // tid 0
-    int bi, hi, t0; coords(ch, bi, hi, t0);
+  auto load_v = [&](const ChunkPos& p) {   // tid 0
+    int bi, hi, t0; coords(p, bi, hi, t0);
     mbar_expect_tx(&sm.bar_v, TILE_BYTES);
     tma_load_4d(sm.v, &tmap_v, &sm.bar_v, 0, sv.first<PACKED>(bi) + t0, hi, sv.row<PACKED>(bi));
   };
-  int ch_first = blockIdx.x;
-  if (ch_first < n_ch && empty(ch_first)) ch_first = advance(ch_first);
-  if (ch_first < n_ch && tid == 0) { load_w(ch_first); load_in(ch_first); load_v(ch_first); }
+  ChunkPos cur = chunk_pos(blockIdx.x, NT, H);
+  if (cur.ch < n_ch && empty(cur)) cur = advance(cur);
+  if (cur.ch < n_ch && tid == 0) { load_w(cur); load_in(cur); load_v(cur); }
   // The two CTAs that share an SM would otherwise run their phases in lockstep and compete for the
   // same unit (shared-memory pipe during the triangular solve); start every other CTA half a
   // chunk-head late.
@@ -128,15 +124,17 @@ r7c_intra_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ w, con
 
   bool ok = true;
   int it = 0;
-  for (int ch = ch_first, next; ch < n_ch && ok; ch = next, ++it) {
-    int bi, hi, t0; coords(ch, bi, hi, t0);
+  for (ChunkPos nxt; cur.ch < n_ch && ok; cur = nxt, ++it) {
+    const int ch = cur.ch;
+    int bi, hi, t0; coords(cur, bi, hi, t0);
     const int Tn = sv.length<PACKED>(bi);
     unsigned char* out_tiles = ws_tiles + (size_t)ch * tiles_per_chunk * TILE_BYTES;
     const uint32_t par = it & 1;
-    next = advance(ch);
+    nxt = advance(cur);
+    const int next = nxt.ch;
 
     R7C_STAMP(0);
-    if (next < n_ch) prefetch_rows(next);
+    if (next < n_ch) prefetch_rows(nxt);
     // this thread's 2 x 16 bytes (8 channels of one token) of the raw w tile
     uint4 rw[2];
     ok = mbar_wait(&sm.bar_w, par, status, 206) && ok;
@@ -385,7 +383,7 @@ r7c_intra_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ w, con
       ok = mbar_wait(&sm.bar_m2, par, status, 205) && ok;
       if (tid == 0) {
         if (keep_for_bwd) bulk_wait_read();
-        if (next < n_ch) load_v(next);      // MMA 2 has read the v tile: request the next one
+        if (next < n_ch) load_v(nxt);      // MMA 2 has read the v tile: request the next one
       }
       __syncthreads();
       R7C_STAMP(10);
@@ -488,7 +486,7 @@ r7c_intra_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ w, con
     R7C_STAMP(6);
     // ---- MMA 3: W = Ainv a~ (lower lane halves), U = Ainv Y (upper lane halves) -> TMEM columns 0..63
     if (tid == 0) {
-      if (ok && next < n_ch) load_w(next);      // the scratch area in the A_qk tile is free again
+      if (ok && next < n_ch) load_w(nxt);      // the scratch area in the A_qk tile is free again
       tc_fence_after();
       umma_tile<64, 64, 0, 1>(tmem_addr(tm, 0, 0), smem_u32(sm.ainv), smem_u32(sm.at), false);
       umma_tile<64, 64, 0, 1>(tmem_addr(tm, 16, 0), smem_u32(sm.ainv), smem_u32(sm.y), false);
@@ -527,7 +525,7 @@ r7c_intra_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ w, con
       bulk_commit();
       // every copy but the two just committed has left shared memory (q~, k~, a~, b~ among them), and MMA 3
       // has read a~: the next raw tiles may land
-      if (next < n_ch) { bulk_wait_read_1(); load_in(next); }
+      if (next < n_ch) { bulk_wait_read_1(); load_in(nxt); }
     }
     R7C_STAMP(9);
   }
