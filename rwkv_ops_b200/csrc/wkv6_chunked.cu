@@ -17,9 +17,11 @@
 // operand X is split as X = hi + lo (two bf16 tiles) and every product is the three tensor-core
 // products hi*hi + hi*lo + lo*hi accumulated in fp32 TMEM (relative error ~2^-16 per term).
 //
-// One CTA of 256 threads per (batch, head) walks the chunks in order; the state lives in TMEM (fp32)
-// and nothing but the inputs and outputs touches HBM in the forward pass (plus, for the backward, the
-// fp32 state at every chunk boundary).  Tile and TMEM conventions are those of tc.cuh.
+// One CTA of 256 threads per (batch, head) walks the chunks in order; the fp32 state (its gradient in the
+// backward) lives in the registers of the threads that own its rows, the products in TMEM, and nothing but
+// the inputs and outputs touches HBM in the forward pass (plus, for the backward, the fp32 state at every
+// chunk boundary).  The raw rows of the next chunk arrive by TMA while the current chunk is worked on.
+// Tile and TMEM conventions are those of tc.cuh.
 #include "common.cuh"
 #include "tc.cuh"
 
