@@ -131,7 +131,7 @@ wkv6c_fwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
   __syncthreads();
   tc_fence_after();
   const uint32_t tm = sm.tmem_base;
-  // TMEM: columns 0..63 lower halves = r~ k~^T; columns 64..127 lower halves = y, upper halves = state
+  // TMEM: columns 0..63 lower halves = r~ k~^T; columns 64..127 lower halves = y, upper halves = k~^T v
   const uint32_t tm_a = tmem_addr(tm, 32 * wq, 32 * hsel);
   const uint32_t tm_ys = tmem_addr(tm, 32 * wq, 64 + 32 * hsel);
 
