@@ -85,6 +85,10 @@ __device__ __forceinline__ ChunkPos chunk_pos(int ch, int NT, int H) {
   return p;
 }
 __device__ __forceinline__ void chunk_step(ChunkPos& p, int stride, int NT, int H) {
+  if (stride >= 4 * NT) {      // short sequences: a step crosses many of them, divide after all
+    p = chunk_pos(p.ch + stride, NT, H);
+    return;
+  }
   p.ch += stride;
   p.c += stride;
   while (p.c >= NT) {
