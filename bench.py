@@ -48,8 +48,8 @@ FLOP_PER_TOKEN_HEAD = 434176
 # DRAM traffic (dram__bytes_read + dram__bytes_write, ncu) per chunk-head (64 tokens of one head) of each
 # chunked kernel, captured on a small case (profiles/r7c_chunked_kernels_B2_T4096_H16.md); traffic grows
 # in proportion to the number of chunk-heads, so a full launch is this figure times B*H*ceil(T/64).
-TRAFFIC_PER_CHUNK_HEAD = {"r7c_intra_fwd_kernel": 112.8e3, "r7c_scan_fwd_kernel": 86.0e3,
-                          "r7c_bwd_pre_kernel": 36.6e3, "r7c_bwd_scan_kernel": 48.3e3,
+TRAFFIC_PER_CHUNK_HEAD = {"r7c_intra_fwd_kernel": 112.8e3, "r7c_scan_fwd_kernel": 85.4e3,
+                          "r7c_bwd_pre_kernel": 35.9e3, "r7c_bwd_scan_kernel": 48.7e3,
                           "r7c_bwd_final_kernel": 149.8e3}
 CPU_SAMPLE_T = 256     # tokens per sequence of the cpu_baseline sample
 REF_STEP_T = 128       # tokens per sequence of one --impl reference step
