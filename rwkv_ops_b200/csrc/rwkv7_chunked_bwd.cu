@@ -285,7 +285,7 @@ struct FinalSmem {
   unsigned char red_pad[2048];    // the two fp32 scratch arrays that later overlay the dA tiles need 34 KB
   unsigned char dge[TILE_BYTES];  // da~ a~ as bf16
   unsigned char stage[5][TILE_BYTES];   // dq, dk, da, db, dw rows staged for TMA stores
-  float gs[L * NROW];       // gi - (start of the half): inclusive prefix of g inside each half of the chunk
+  float gs[L * NROW];       // gi - gref: inclusive prefix of g inside the chunk, relative to the reference point
   float gg[L * NROW];       // g
   float qtot[4][64];        // sums of g over the four quarters of the chunk
   float rqtot[4][64];       // sums of the decay-gradient terms over the four quarters
@@ -461,7 +461,8 @@ r7c_bwd_final_kernel(const bf16* __restrict__ w, const __grid_constant__ CUtenso
       for (int j = 0; j < 16; ++j) { run += gv[j]; gv[j] = run; }
       sm.qtot[quarter][c] = run;
       __syncthreads();
-      const float add = (quarter & 1) ? sm.qtot[quarter - 1][c] : 0.f;    // start of the half
+      // gi - gref: the prefix inside the half; the first half lies before the reference point, the end of that half
+      const float add = quarter == 0 ? -(run + sm.qtot[1][c]) : quarter == 1 ? -run : quarter == 3 ? sm.qtot[2][c] : 0.f;
 #pragma unroll
       for (int j = 0; j < 16; ++j) sm.gs[(16 * quarter + j) * NROW + c] = gv[j] + add;
     }
@@ -574,15 +575,12 @@ r7c_bwd_final_kernel(const bf16* __restrict__ w, const __grid_constant__ CUtenso
         const int c = c0 + j4;
         const float4 gs4 = *reinterpret_cast<const float4*>(&sm.gs[i * NROW + c]);
         const float4 gg4 = *reinterpret_cast<const float4*>(&sm.gg[i * NROW + c]);
-        const float4 ta4 = *reinterpret_cast<const float4*>(&sm.qtot[0][c]);
-        const float4 tb4 = *reinterpret_cast<const float4*>(&sm.qtot[1][c]);
         const float gsv[4] = {gs4.x, gs4.y, gs4.z, gs4.w}, ggv[4] = {gg4.x, gg4.y, gg4.z, gg4.w};
-        const float ttv[4] = {ta4.x + tb4.x, ta4.y + tb4.y, ta4.z + tb4.z, ta4.w + tb4.w};   // gref - (start of chunk)
         float rd[4];
 #pragma unroll
         for (int m = 0; m < 4; ++m) {
           const int j = j4 + m;
-          const float d1 = gsv[m] - (i < 32 ? ttv[m] : 0.f);            // gi - gref
+          const float d1 = gsv[m];                                       // gi - gref
           const float x1 = __uint_as_float(r1[j]), x2 = __uint_as_float(r2[j]);
           o2[j] = x2 * cexp(-d1);                                        // dk / db
           o1[j] = x1 * (second ? cexp(d1 - ggv[m]) : cexp(d1));          // da / dq
