@@ -178,9 +178,10 @@ r7c_intra_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ w, con
         for (int j = 0; j < 16; ++j) { run += gv[j]; gv[j] = run; }
         sm.qtot[quarter][c] = run;
         __syncthreads();
-        const float add = (quarter & 1) ? sm.qtot[quarter - 1][c] : 0.f;
+        // gi - gref: the prefix inside the half; the reference point is the end of the first half
+        const float add = quarter == 0 ? -(run + sm.qtot[1][c]) : quarter == 1 ? -run : quarter == 3 ? sm.qtot[2][c] : 0.f;
 #pragma unroll
-        for (int j = 0; j < 16; ++j) gs[(16 * quarter + j) * NROW + c] = gv[j] + add;   // prefix inside each half
+        for (int j = 0; j < 16; ++j) gs[(16 * quarter + j) * NROW + c] = gv[j] + add;
       }
       __syncthreads();
       if (tid < 64) {
@@ -228,14 +229,9 @@ r7c_intra_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ w, con
 #pragma unroll
       for (int n = 0; n < 2; ++n) {
         const int e = tid + 256 * n, row = e >> 3, cc = e & 7;
-        const bool first_half = row < 32;
-        float gl[8], sh[8], sh2[8];
+        float gl[8];
         *reinterpret_cast<float4*>(gl) = *reinterpret_cast<const float4*>(&gs[row * NROW + 8 * cc]);
         *reinterpret_cast<float4*>(gl + 4) = *reinterpret_cast<const float4*>(&gs[row * NROW + 8 * cc + 4]);
-        *reinterpret_cast<float4*>(sh) = *reinterpret_cast<const float4*>(&sm.qtot[0][8 * cc]);
-        *reinterpret_cast<float4*>(sh + 4) = *reinterpret_cast<const float4*>(&sm.qtot[0][8 * cc + 4]);
-        *reinterpret_cast<float4*>(sh2) = *reinterpret_cast<const float4*>(&sm.qtot[1][8 * cc]);
-        *reinterpret_cast<float4*>(sh2 + 4) = *reinterpret_cast<const float4*>(&sm.qtot[1][8 * cc + 4]);
         const uint32_t uq[4] = {rq[n].x, rq[n].y, rq[n].z, rq[n].w};
         const uint32_t uk[4] = {rk[n].x, rk[n].y, rk[n].z, rk[n].w};
         const uint32_t ua[4] = {ra[n].x, ra[n].y, ra[n].z, ra[n].w};
@@ -247,7 +243,7 @@ r7c_intra_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ w, con
 #pragma unroll
           for (int hh = 0; hh < 2; ++hh) {
             const int x = 2 * m + hh;
-            const float d1 = gl[x] - (first_half ? sh[x] + sh2[x] : 0.f);   // gi - gref
+            const float d1 = gl[x];                                         // gi - gref
             eq[hh] = cexp(d1); ek[hh] = cexp(-d1); ea[hh] = cexp(d1 - gown[n][x]);
           }
           oq[m] = pack_bf16(bf16_lo(uq[m]) * eq[0], bf16_hi(uq[m]) * eq[1]);
