@@ -90,7 +90,7 @@ struct FwdSmem {
   unsigned char vt[2][TILE_BYTES];    // v hi, lo       [token][v]
   unsigned char at[2][TILE_BYTES];    // A hi, lo       [token i][token j]
   unsigned char st[2][TILE_BYTES];    // S~0 hi, lo     [k][v]
-  float gs[L * NROW];                 // prefix of g inside each half; later the staged y rows
+  float gs[L * NROW];                 // gi - gref (prefix of g relative to the reference point); later the staged y rows
   float qtot[4][64];
   float dgs[64];                      // sum_k r u k per token
   uint64_t bar_1, bar_2, bar_in;
@@ -210,9 +210,10 @@ wkv6c_fwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
       for (int j = 0; j < 16; ++j) { run += gv[j]; gv[j] = run; }
       sm.qtot[quarter][ch] = run;
       __syncthreads();
-      const float add = (quarter & 1) ? sm.qtot[quarter - 1][ch] : 0.f;
+      // gi - gref: the prefix inside the half; the reference point is the end of the first half
+      const float add = quarter == 0 ? -(run + sm.qtot[1][ch]) : quarter == 1 ? -run : quarter == 3 ? sm.qtot[2][ch] : 0.f;
 #pragma unroll
-      for (int j = 0; j < 16; ++j) sm.gs[(16 * quarter + j) * NROW + ch] = gv[j] + add;   // prefix inside each half
+      for (int j = 0; j < 16; ++j) sm.gs[(16 * quarter + j) * NROW + ch] = gv[j] + add;
     }
     __syncthreads();
     W6C_STAMP(2);
@@ -249,11 +250,7 @@ wkv6c_fwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
       const int e = tid + 256 * n, row = e >> 4;
       const float4 r4 = rr4[n], k4 = kk4[n];
       const float4 gp = *reinterpret_cast<const float4*>(&sm.gs[row * NROW + 4 * c4]);
-      const float4 ta = *reinterpret_cast<const float4*>(&sm.qtot[0][4 * c4]);
-      const float4 tb = *reinterpret_cast<const float4*>(&sm.qtot[1][4 * c4]);
-      const bool fh = row < 32;
-      const float d1x = gp.x - (fh ? ta.x + tb.x : 0.f), d1y = gp.y - (fh ? ta.y + tb.y : 0.f);
-      const float d1z = gp.z - (fh ? ta.z + tb.z : 0.f), d1w = gp.w - (fh ? ta.w + tb.w : 0.f);   // gi - gref
+      const float d1x = gp.x, d1y = gp.y, d1z = gp.z, d1w = gp.w;   // gi - gref
       const float4 rs = make_float4(r4.x * cexp(d1x - gw[n].x), r4.y * cexp(d1y - gw[n].y),
                                     r4.z * cexp(d1z - gw[n].z), r4.w * cexp(d1w - gw[n].w));
       const float4 ks = make_float4(k4.x * cexp(-d1x), k4.y * cexp(-d1y), k4.z * cexp(-d1z), k4.w * cexp(-d1w));
@@ -400,7 +397,7 @@ struct BwdSmem {
   unsigned char dat[2][TILE_BYTES];   // stril(dA)     [i][j]
   unsigned char st[2][TILE_BYTES];    // S~0           [k][v]
   unsigned char dst[2][TILE_BYTES];   // dS^           [k][v]
-  float gs[L * NROW];                 // prefix of g inside each half
+  float gs[L * NROW];                 // gi - gref (prefix of g relative to the reference point)
   float gg[L * NROW];                 // g
   float red_e[L * NROW];              // dr~ r~
   float qtot[4][64];
@@ -532,7 +529,8 @@ wkv6c_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
       for (int j = 0; j < 16; ++j) { run += gv[j]; gv[j] = run; }
       sm.qtot[quarter][ch] = run;
       __syncthreads();
-      const float add = (quarter & 1) ? sm.qtot[quarter - 1][ch] : 0.f;
+      // gi - gref: the prefix inside the half; the reference point is the end of the first half
+      const float add = quarter == 0 ? -(run + sm.qtot[1][ch]) : quarter == 1 ? -run : quarter == 3 ? sm.qtot[2][ch] : 0.f;
 #pragma unroll
       for (int j = 0; j < 16; ++j) sm.gs[(16 * quarter + j) * NROW + ch] = gv[j] + add;
     }
@@ -563,11 +561,7 @@ wkv6c_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
       const int e = tid + 256 * n, row = e >> 4;
       const float4 r4 = rr4[n], k4 = kk4[n];
       const float4 gp = *reinterpret_cast<const float4*>(&sm.gs[row * NROW + 4 * c4]);
-      const float4 ta = *reinterpret_cast<const float4*>(&sm.qtot[0][4 * c4]);
-      const float4 tb = *reinterpret_cast<const float4*>(&sm.qtot[1][4 * c4]);
-      const bool fh = row < 32;
-      const float d1x = gp.x - (fh ? ta.x + tb.x : 0.f), d1y = gp.y - (fh ? ta.y + tb.y : 0.f);
-      const float d1z = gp.z - (fh ? ta.z + tb.z : 0.f), d1w = gp.w - (fh ? ta.w + tb.w : 0.f);
+      const float d1x = gp.x, d1y = gp.y, d1z = gp.z, d1w = gp.w;   // gi - gref
       const float4 rs = make_float4(r4.x * cexp(d1x - gw[n].x), r4.y * cexp(d1y - gw[n].y),
                                     r4.z * cexp(d1z - gw[n].z), r4.w * cexp(d1w - gw[n].w));
       const float4 ks = make_float4(k4.x * cexp(-d1x), k4.y * cexp(-d1y), k4.z * cexp(-d1z), k4.w * cexp(-d1w));
@@ -712,15 +706,12 @@ wkv6c_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
         const int cc = c0 + j4;
         const float4 gs4 = *reinterpret_cast<const float4*>(&sm.gs[srow * NROW + cc]);
         const float4 gg4 = *reinterpret_cast<const float4*>(&sm.gg[srow * NROW + cc]);
-        const float4 ta4 = *reinterpret_cast<const float4*>(&sm.qtot[0][cc]);
-        const float4 tb4 = *reinterpret_cast<const float4*>(&sm.qtot[1][cc]);
         const float gsv[4] = {gs4.x, gs4.y, gs4.z, gs4.w}, ggv[4] = {gg4.x, gg4.y, gg4.z, gg4.w};
-        const float ttv[4] = {ta4.x + tb4.x, ta4.y + tb4.y, ta4.z + tb4.z, ta4.w + tb4.w};
         float o[4], rd[4];
 #pragma unroll
         for (int m = 0; m < 4; ++m) {
           const int j = j4 + m;
-          const float d1 = gsv[m] - (srow < 32 ? ttv[m] : 0.f);     // gi - gref
+          const float d1 = gsv[m];                                   // gi - gref
           const float tt = th[j] + tl[j];                            // k~ (lower) / r~ (upper)
           const float x = __uint_as_float(r1[j]);                    // dk~ (lower) / dr~ (upper)
           o[m] = x * cexp(lower ? -d1 : d1 - ggv[m]);                // dk = dk~ e^{gref-gi},  dr = dr~ e^{ge-gref}
