@@ -12,10 +12,15 @@ so scaling is weak and ``value`` is the sum over ranks.
 
 Prints ONE JSON line (rank 0).  ``value``: inputs resident in HBM, device-timed with CUDA events,
 max over ranks.  ``e2e``: the same metric through the public API with HOST buffers, host->device
-and device->host copies of every input and output inside the timed region.  ``roofline``: the
-dominant kernel's achieved algorithmic bytes/s, timed with CUDA events around its launches inside
-the timed region.  ``cpu_baseline``: the CPU oracle (a port of the reference's native operator)
-timed on this host on a bounded sample.
+and device->host copies of every input and output inside the timed region (``copy_ceiling`` is the
+same copies with no compute between them).  ``roofline``: the pass (forward or backward) that holds
+the dominant kernel, its algorithmic bytes over the summed CUDA-event time of ALL kernels of that
+pass, plus the whole step's fractions of the HBM and tensor peaks.  ``decode`` and ``wkv6``: the other
+two measured paths of the metric (T=1 decode of configuration 3, RWKV6 wkv forward + backward of
+configuration 4), each with its own roofline.  ``strong_scaling``: configuration 2 with its batch of
+16 sequences SHARDED over the ranks (total work fixed).  ``recompute``: the step with the backward
+recomputing the forward instead of reading kept tiles.  ``cpu_baseline``: the CPU oracle (a port of
+the reference's native operator) timed on this host on a bounded sample.
 
 ``--impl reference`` times the reference's own CPU implementation of the path (the oracle port of
 ``rwkv_ops/rwkv7_kernel/native_keras_op.py``; the reference checkout itself does not travel to the
@@ -46,11 +51,13 @@ WORKLOADS = {
 BYTES_PER_TOKEN_HEAD = 2560
 FLOP_PER_TOKEN_HEAD = 434176
 # DRAM traffic (dram__bytes_read + dram__bytes_write, ncu) per chunk-head (64 tokens of one head) of each
-# chunked kernel, captured on a small case (profiles/r7c_chunked_kernels_B2_T4096_H16.md); traffic grows
-# in proportion to the number of chunk-heads, so a full launch is this figure times B*H*ceil(T/64).
+# chunked kernel, captured on a small case (B=2, T=4096, H=16); traffic grows in proportion to the number of
+# chunk-heads, so a full launch is this figure times B*H*ceil(T/64).
 TRAFFIC_PER_CHUNK_HEAD = {"r7c_intra_fwd_kernel": 112.8e3, "r7c_scan_fwd_kernel": 85.4e3,
                           "r7c_bwd_pre_kernel": 35.9e3, "r7c_bwd_scan_kernel": 48.7e3,
                           "r7c_bwd_final_kernel": 149.8e3}
+TRAFFIC_SOURCE = ("ncu dram__bytes_read.sum + dram__bytes_write.sum per chunk-head on B=2 T=4096 H=16 "
+                  "(a full-size launch is too large to capture), scaled by the chunk-heads of this launch")
 CPU_SAMPLE_T = 256     # tokens per sequence of the cpu_baseline sample
 REF_STEP_T = 128       # tokens per sequence of one --impl reference step
 
@@ -174,6 +181,115 @@ def run_reference(args, wl):
     print(json.dumps(line), flush=True)
 
 
+def _timed(fn, steps, warmup, barrier, max_over_ranks):
+    for _ in range(warmup):
+        fn()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    barrier()
+    return max_over_ranks(e0.elapsed_time(e1)) / steps
+
+
+def sub_decode(dev, world, max_over_ranks, barrier, pk):
+    """Configuration 3: T=1 decode, B=256, H=64, bf16 tokens, float32 state fed back over 1024 consecutive
+    steps (ping-pong state buffers of 268 MB each, larger than L2; 8 rotating sets of token vectors)."""
+    from rwkv_ops_b200 import _lib
+    from rwkv_ops_b200.workloads import rwkv7_inputs
+    B, H, STEPS = 256, 64, 1024
+    lib = _lib.load()
+    ds = [rwkv7_inputs(B, 1, H, dtype=torch.bfloat16, seed=1003 + i, device=dev) for i in range(8)]
+    bufs = [0.1 * torch.randn(B, H, 64, 64, device=dev), torch.empty(B, H, 64, 64, device=dev)]
+    o = torch.empty(B, H, 64, dtype=torch.bfloat16, device=dev)
+    st = torch.cuda.current_stream().cuda_stream
+    i = [0]
+
+    def fn():
+        d = ds[i[0] & 7]
+        rc = lib.rwkvb200_rwkv7_step(*[d[n].data_ptr() for n in "rwkvab"], bufs[i[0] & 1].data_ptr(), B,
+                                     bufs[(i[0] + 1) & 1].data_ptr(), o.data_ptr(), B, H, 64, _lib.BF16, st)
+        assert rc == 0
+        i[0] += 1
+
+    ms = _timed(fn, STEPS, 8, barrier, max_over_ranks)
+    nbytes = B * H * (2 * 64 * 64 * 4 + 7 * 64 * 2)
+    gbs = nbytes / (ms / 1e3) / 1e9
+    return {"workload": "rwkv7_decode_T1_bf16_B256_H64_f32_state", "steps": STEPS, "us_per_step": 1e3 * ms,
+            "value": gbs, "unit": "GB/s per GPU", "tokens_per_s": world * B / (ms / 1e3),
+            "roofline": {"bound": "hbm", "algorithmic_bytes": nbytes, "achieved": gbs, "peak": pk["hbm_gbs"],
+                         "frac": gbs / pk["hbm_gbs"], "kernel": "rwkv7_step_kernel"}}
+
+
+def sub_wkv6(dev, world, max_over_ranks, barrier, pk):
+    """Configuration 4: RWKV6 wkv forward + backward, fp32, B=16, T=4096, 32 heads, 4 initial states
+    selected through state_map; algorithmic bytes 14 fp32 vectors of 256 B per token*head."""
+    import rwkv_ops_b200 as ro
+    from rwkv_ops_b200 import _lib
+    from rwkv_ops_b200.workloads import wkv6_inputs
+    B, T, H = 16, 4096, 32
+    d = wkv6_inputs(B, T, H, seed=1004, device=dev, n_state=4, with_grads=True)
+    g = {n: d[n].requires_grad_(True) for n in "rkvwu"}
+    s0 = d["init_state"].requires_grad_(True)
+    op = ro.RWKV6_OP(64, T)
+
+    def fn():
+        y, s = op(g["r"], g["k"], g["v"], g["w"], g["u"], with_state=True, init_state=s0, state_map=d["state_map"])
+        torch.autograd.backward([y, s], [d["d_y"], d["d_state"]])
+        for t in list(g.values()) + [s0]:
+            t.grad = None
+
+    for _ in range(3):
+        fn()
+    _lib.profile(True)
+    ms = _timed(fn, 5, 0, barrier, max_over_ranks)
+    prof = _lib.profile_results()
+    _lib.profile(False)
+    nbytes = B * T * H * 3584
+    gbs = nbytes / (ms / 1e3) / 1e9
+    return {"workload": "wkv6_fwd_bwd_f32_B16_T4096_C2048_4states", "ms_per_step": ms,
+            "value": world * B * T / (ms / 1e3), "unit": "tokens/s",
+            "kernels": {k_: v[0] / 5 for k_, v in prof.items()},
+            "roofline": {"bound": "hbm", "algorithmic_bytes": nbytes, "achieved": gbs, "peak": pk["hbm_gbs"],
+                         "frac": gbs / pk["hbm_gbs"], "kernel": "wkv6c_bwd_kernel"}}
+
+
+def sub_cfg2_sharded(dev, world, rank, max_over_ranks, barrier):
+    """Configuration 2 (bf16, B=16, T=8192, H=64, per-sequence initial state, trailing 0..512 tokens padded
+    through w): the 16 sequences are sharded over the ranks (B/N per rank, no collective), so the total work
+    is the same at every N.  value = tokens of all 16 sequences / max over ranks of the step time."""
+    import rwkv_ops_b200 as ro
+    from rwkv_ops_b200.workloads import rwkv7_inputs, rwkv7_pad_lengths, apply_w_padding
+    Bg, T, H = 16, 8192, 64
+    if Bg % world:
+        return {"skipped": f"{Bg} sequences do not divide over {world} ranks"}
+    Bl = Bg // world
+    d = rwkv7_inputs(Bl, T, H, dtype=torch.bfloat16, seed=1002 + 17 * rank, device=dev, with_state=True,
+                     with_grads=True)
+    lengths = rwkv7_pad_lengths(Bg, T, seed=1002)[rank * Bl:(rank + 1) * Bl]
+    d["w"] = apply_w_padding(d["w"], lengths)
+    leaves = {n: d[n].requires_grad_(True) for n in "rwkvab"}
+    h0 = d["initial_state"].requires_grad_(True)
+
+    def fn():
+        o, s = ro.generalized_delta_rule(*[leaves[n] for n in "rwkvab"], initial_state=h0)
+        torch.autograd.backward([o, s], [d["d_out"], d["d_state"]])
+        for n in "rwkvab":
+            leaves[n].grad = None
+        h0.grad = None
+
+    ms = _timed(fn, 5, 3, barrier, max_over_ranks)
+    out = {"workload": "rwkv7_fwd_bwd_bf16_B16_T8192_H64_K64_h0_padded", "scaling": "strong",
+           "sharding": f"{Bl} of 16 sequences per rank, {world} rank(s), no collective",
+           "ms_per_step": ms, "value": Bg * T / (ms / 1e3), "unit": "tokens/s",
+           "units_per_gpu": Bl * H}
+    del d, leaves, h0
+    torch.cuda.empty_cache()
+    return out
+
+
 def run_ours(args, wl):
     import torch.distributed as dist
     import rwkv_ops_b200 as ro
@@ -244,27 +360,55 @@ def run_ours(args, wl):
     value = world * B * T / (ms_step / 1e3)
     launches = sum(n for _, n in prof.values())
 
-    # ---- roofline of the dominant kernel (by summed event time inside the timed region)
+    # ---- roofline.  The dominant kernel (by summed event time inside the timed region) names the pass;
+    # the pass's algorithmic bytes (forward: 6 vectors of 128 B read + 1 written per token*head = 896 B;
+    # backward: 7 read + 6 written = 1664 B) are divided by the summed time of ALL kernels of that pass.
     pk = peaks()
     roof = None
+    units = B * T * H
     if prof:
-        top = max(prof, key=lambda k_: prof[k_][0])
-        top_ms, top_n = prof[top]
-        per_launch_s = top_ms / top_n / 1e3
-        units = B * T * H
-        # bytes the kernel must move per launch: the backward kernels read 7 and write 6 token
-        # vectors per token*head, the forward kernels read 6 and write 1
-        bytes_per_unit = 1664 if "bwd" in top else 896
-        achieved = units * bytes_per_unit / per_launch_s / 1e9
-        roof = {"kernel": top, "bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
-                "frac": achieved / pk["hbm_gbs"],
-                "traffic": (TRAFFIC_PER_CHUNK_HEAD[top] * B * H * ((T + 63) // 64)
-                            if top in TRAFFIC_PER_CHUNK_HEAD else None),
+        per_step = {k_: v[0] / args.steps for k_, v in prof.items()}
+        top = max(per_step, key=per_step.get)
+        is_bwd = "bwd" in top
+        members = [k_ for k_ in per_step if ("bwd" in k_) == is_bwd]
+        pass_ms = sum(per_step[k_] for k_ in members)
+        bytes_per_unit = 1664 if is_bwd else 896
+        achieved = units * bytes_per_unit / (pass_ms / 1e3) / 1e9
+        n_ch = B * H * ((T + 63) // 64)
+        traffic = sum(TRAFFIC_PER_CHUNK_HEAD.get(k_, 0.0) for k_ in members) * n_ch
+        step_gbs = units * BYTES_PER_TOKEN_HEAD / (ms_step / 1e3) / 1e9
+        step_tf = units * FLOP_PER_TOKEN_HEAD / (ms_step / 1e3) / 1e12
+        roof = {"kernel": top, "pass": "backward" if is_bwd else "forward", "pass_kernels": sorted(members),
+                "bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
+                "frac": achieved / pk["hbm_gbs"], "traffic": traffic or None,
+                "traffic_source": TRAFFIC_SOURCE,
                 "algorithmic_bytes": units * bytes_per_unit, "peak_source": pk["source"],
-                "launch_ms": top_ms / top_n,
-                "tensor_tflops_whole_step": units * FLOP_PER_TOKEN_HEAD / (ms_step / 1e3) / 1e12,
+                "pass_ms": pass_ms, "launch_ms": per_step[top],
+                "step": {"algorithmic_bytes": units * BYTES_PER_TOKEN_HEAD, "hbm_gbs": step_gbs,
+                         "hbm_frac": step_gbs / pk["hbm_gbs"], "flop": units * FLOP_PER_TOKEN_HEAD,
+                         "tensor_tflops": step_tf, "tensor_frac": step_tf / pk["bf16_tflops"]},
                 "kernels": {k_: {"ms_per_step": v[0] / args.steps, "launches_per_step": v[1] / args.steps}
                             for k_, v in prof.items()}}
+
+    # ---- the same step with the backward recomputing the forward (nothing kept between the passes)
+    kept_bytes = _lib.load().rwkvb200_rwkv7_fwd_workspace_bytes(B, T, H, 64, _lib.BF16, _lib.ALGO_KEEP)
+    os.environ["RWKV_OPS_B200_KEEP_LIMIT_MB"] = "0"
+    for _ in range(2):
+        step()
+    barrier()
+    ev0.record()
+    for _ in range(max(3, args.steps // 2)):
+        step()
+    ev1.record()
+    barrier()
+    recompute_ms = max_over_ranks(ev0.elapsed_time(ev1)) / max(3, args.steps // 2)
+    del os.environ["RWKV_OPS_B200_KEEP_LIMIT_MB"]
+
+    extra = {}
+    if not args.only_main:
+        extra["decode"] = sub_decode(dev, world, max_over_ranks, barrier, pk)
+        extra["wkv6"] = sub_wkv6(dev, world, max_over_ranks, barrier, pk)
+        extra["strong_scaling"] = sub_cfg2_sharded(dev, world, rank, max_over_ranks, barrier)
 
     # ---- end to end: host buffers in, host buffers out, through the public API.
     # Every step copies all of its inputs from pinned host memory and all of its results back to
@@ -340,6 +484,29 @@ def run_ours(args, wl):
     e2e_ms = max_over_ranks(max(ev0.elapsed_time(ev1), 1e3 * (time.perf_counter() - t0))) / e2e_steps
     e2e_val = world * B * T / (e2e_ms / 1e3)
 
+    # copy-only ceiling of the same host path: the same pinned buffers up and down on the two copy
+    # streams, no compute between them
+    dev_out = {n: torch.empty_like(t, device=dev) for n, t in host_out[0].items()}
+
+    def copy_only(nsteps):
+        for i in range(nsteps):
+            sl = i & 1
+            with torch.cuda.stream(s_up):
+                for n, t in host_in.items():
+                    dev_in[sl][n].copy_(t, non_blocking=True)
+            with torch.cuda.stream(s_down):
+                for n in out_names:
+                    host_out[sl][n].copy_(dev_out[n], non_blocking=True)
+        s_up.synchronize()
+        s_down.synchronize()
+
+    copy_only(2)
+    barrier()
+    t0 = time.perf_counter()
+    copy_only(e2e_steps)
+    barrier()
+    copy_ms = max_over_ranks(1e3 * (time.perf_counter() - t0)) / e2e_steps
+
     if rank == 0:
         line = {
             "metric": "rwkv7_fwd_bwd_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
@@ -352,10 +519,17 @@ def run_ours(args, wl):
             "clocks": clocks.summary(),
             "e2e": {"value": e2e_val, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": e2e_ms, "steps": e2e_steps,
-                    "pipeline": "upload / compute / download of consecutive steps overlap on three streams"},
+                    "pipeline": "upload / compute / download of consecutive steps overlap on three streams",
+                    "copy_ceiling": {"ms_per_step": copy_ms, "value": world * B * T / (copy_ms / 1e3),
+                                     "frac_of_ceiling": copy_ms / e2e_ms,
+                                     "what": "the same pinned host buffers copied up and down, no compute"}},
             "gpu_launches": launches,
             "roofline": roof,
+            "recompute": {"ms_per_step": recompute_ms, "value": world * B * T / (recompute_ms / 1e3),
+                          "kept_bytes_per_step": int(kept_bytes),
+                          "what": "backward recomputes the forward from the inputs (nothing saved but inputs)"},
         }
+        line.update(extra)
         if world == 1 and not args.no_cpu_baseline:
             cores = os.cpu_count() or 1
             torch.set_num_threads(cores)
@@ -375,6 +549,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="cfg1", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--only-main", action="store_true", help="skip the decode / wkv6 / strong-scaling sub-records")
     args = ap.parse_args()
     wl = WORKLOADS[args.workload]
     if args.impl == "reference":

@@ -52,9 +52,14 @@ enum {
 
 /* algo argument of the RWKV7 entry points */
 enum {
-  RWKVB200_ALGO_AUTO = 0,       /* chunked tensor-core path for bf16/f16 tokens, recurrent for f32 */
+  RWKVB200_ALGO_AUTO = 0,       /* chunked tensor-core path for bf16 tokens, recurrent for f32 and f16 */
   RWKVB200_ALGO_RECURRENT = 1,  /* token-by-token float32 recurrence (float32-exact) */
-  RWKVB200_ALGO_CHUNKED = 2,    /* chunked tcgen05 path */
+  /* Chunked tcgen05 path (bf16 tokens).  Its scaled operands are exact while the sum of exp(w) over any 32
+   * consecutive tokens of a channel stays below 60 (always true for w <= 0.62; RWKV7's own
+   * parametrisation keeps exp(w) below 0.61).  A (batch, head) unit beyond that is detected on the device
+   * and recomputed, forward and backward, by the float32 recurrence inside the same call: results hold
+   * for any w, such units just run at the recurrent path's speed. */
+  RWKVB200_ALGO_CHUNKED = 2,
   /* Flag, OR-ed into algo (chunked path only).  Forward: also leave the per-chunk tiles the backward
    * needs in the workspace (size it with the flag set).  Backward: the workspace still holds what that
    * forward call left there, so skip the recomputation.  Without the flag the backward recomputes the
@@ -211,10 +216,18 @@ int rwkvb200_rwkv7_bwd_static(const void* r, const void* w, const void* k, const
  *   algo           RWKVB200_ALGO_AUTO / _RECURRENT (token-by-token float32) / _CHUNKED (tcgen05 with
  *                  split-precision bf16 operands, float32-grade accuracy for every dtype); AUTO = chunked.
  *                  With RWKVB200_ALGO_KEEP (chunked only) the forward also writes the state at every chunk
- *                  boundary into `workspace` (rwkvb200_wkv6_bwd_workspace_bytes of it), and a backward
- *                  called with the same flag and workspace skips its recomputation of the forward;
- *                  without the flag the forward needs no workspace (NULL, 0).
+ *                  boundary into `workspace`, and a backward called with the same flag and workspace
+ *                  skips its recomputation of the forward.
+ *   workspace      rwkvb200_wkv6_fwd_workspace_bytes(...) bytes: with KEEP the backward's workspace
+ *                  (rwkvb200_wkv6_bwd_workspace_bytes, the two are equal), without it a few bytes per
+ *                  (batch, head) for the chunked path and none for the recurrent one.
+ * Decay range of the chunked path: its scaled operands are exact while the sum of exp(w) over any 32
+ * consecutive tokens of a channel stays below 60 (always true for w <= 0.62).  A (batch, head) unit that
+ * exceeds this is detected on the device and recomputed, forward and backward, by the float32 recurrence
+ * inside the same call: results are exact for any w, such units just run at the recurrent path's speed.
  * ---------------------------------------------------------------------------------------- */
+size_t rwkvb200_wkv6_fwd_workspace_bytes(int B, int T, int H, int head_size, int dtype, int algo);
+
 int rwkvb200_wkv6_fwd(const void* r, const void* k, const void* v, const void* w, const float* u,
                       const float* s0, int n_state, const int32_t* state_map,
                       void* y, float* sT, void* workspace, size_t workspace_bytes,

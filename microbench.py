@@ -1,15 +1,15 @@
 """Device-timed micro-benchmarks of the individual operators (CUDA events, inputs resident in HBM).
 
-    python -m rwkv_ops_b200.microbench step  [--B 256 --H 64 --steps 50 --dtype bf16]
-    python -m rwkv_ops_b200.microbench step  --state-dtype bf16      (in place, bfloat16 state)
-    python -m rwkv_ops_b200.microbench wkv6  [--B 16 --T 4096 --H 32 --steps 5]
-    python -m rwkv_ops_b200.microbench rwkv7 [--B 8 --T 4096 --H 32 --steps 5 --dtype bf16 --algo auto]
-    python -m rwkv_ops_b200.microbench varlen [--B 8 --T 4096 --H 32]     (packed sequences vs padded)
-    python -m rwkv_ops_b200.microbench fused  [--B 8 --T 4096 --H 32]     (producers of w, a, b fused in vs torch)
-    python -m torch.distributed.run --nproc-per-node 2 --master-addr 127.0.0.1 -m rwkv_ops_b200.microbench sp
+    python microbench.py step  [--B 256 --H 64 --steps 50 --dtype bf16]
+    python microbench.py step  --state-dtype bf16      (in place, bfloat16 state)
+    python microbench.py wkv6  [--B 16 --T 4096 --H 32 --steps 5]
+    python microbench.py rwkv7 [--B 8 --T 4096 --H 32 --steps 5 --dtype bf16 --algo auto]
+    python microbench.py varlen [--B 8 --T 4096 --H 32]     (packed sequences vs padded)
+    python microbench.py fused  [--B 8 --T 4096 --H 32]     (producers of w, a, b fused in vs torch)
+    python -m torch.distributed.run --nproc-per-node 2 --master-addr 127.0.0.1 microbench.py sp
 
-Each prints one JSON line with the time per call and the achieved algorithmic bandwidth.  These
-are the commands the profiler captures in ``profiles/`` were taken from.
+Each prints one JSON line with the time per call and the achieved algorithmic bandwidth; small cases of
+these commands are what the profiler captures.
 """
 from __future__ import annotations
 
@@ -17,7 +17,11 @@ import argparse
 import json
 import os
 
+import sys
+
 import torch
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 
 import rwkv_ops_b200 as ro
 from rwkv_ops_b200 import _lib

@@ -41,6 +41,7 @@ SIGNATURES = {
     "rwkvb200_rwkv7_bwd": (c_int, [_P] * 6 + [_P, _I, _P, _P] + [_P] * 7 + [_P, _Z] + [_I] * 7 + [_P]),
     "rwkvb200_rwkv7_bwd_static_capacity_bytes": (c_size_t, []),
     "rwkvb200_rwkv7_bwd_static": (c_int, [_P] * 6 + [_P, _I, _P, _P] + [_P] * 7 + [_I] * 6 + [_P]),
+    "rwkvb200_wkv6_fwd_workspace_bytes": (c_size_t, [_I] * 6),
     "rwkvb200_wkv6_fwd": (c_int, [_P] * 5 + [_P, _I, _P, _P, _P, _P, _Z] + [_I] * 6 + [_P]),
     "rwkvb200_wkv6_bwd_workspace_bytes": (c_size_t, [_I] * 6),
     "rwkvb200_wkv6_bwd": (c_int, [_P] * 5 + [_P, _I, _P, _P, _P] + [_P] * 6 + [_P, _Z] + [_I] * 6 + [_P]),

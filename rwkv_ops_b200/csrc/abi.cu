@@ -264,6 +264,12 @@ int rwkvb200_rwkv7_fused_bwd(const void* r, const void* w_pre, const void* k, co
                                   (cudaStream_t)stream, nullptr, nullptr, 0, true);
 }
 
+size_t rwkvb200_wkv6_fwd_workspace_bytes(int B, int T, int H, int head_size, int dtype, int algo) {
+  if (check_common(B, T, H, head_size, dtype)) return 0;
+  if (resolve_w6_algo(algo) != RWKVB200_ALGO_CHUNKED) return 0;
+  return (algo & RWKVB200_ALGO_KEEP) ? wkv6_chunked_bwd_workspace_bytes(B, T, H) : wkv6_chunked_flags_bytes(B, H);
+}
+
 int rwkvb200_wkv6_fwd(const void* r, const void* k, const void* v, const void* w, const float* u,
                       const float* s0, int n_state, const int32_t* state_map,
                       void* y, float* sT, void* workspace, size_t workspace_bytes,
@@ -277,13 +283,16 @@ int rwkvb200_wkv6_fwd(const void* r, const void* k, const void* v, const void* w
   const void* ps[] = {r, k, v, w, u, s0, y, sT};
   for (const void* p : ps) if (p && !aligned16(p)) return RWKVB200_E_ALIGN;
   if (resolve_w6_algo(algo) == RWKVB200_ALGO_CHUNKED) {
+    if (!workspace || !aligned16(workspace) ||
+        workspace_bytes < rwkvb200_wkv6_fwd_workspace_bytes(B, T, H, head_size, dtype, algo))
+      return RWKVB200_E_WORKSPACE;
     float* states = nullptr;
+    int* flags = reinterpret_cast<int*>(workspace);
     if (algo & RWKVB200_ALGO_KEEP) {
-      if (!workspace || !aligned16(workspace) || workspace_bytes < wkv6_chunked_bwd_workspace_bytes(B, T, H))
-        return RWKVB200_E_WORKSPACE;
       states = reinterpret_cast<float*>(workspace);
+      flags = wkv6_chunked_workspace_flags(workspace, B, T, H);
     }
-    return launch_wkv6_chunked_fwd(r, k, v, w, u, n_state ? s0 : nullptr, n_state, state_map, y, sT, states,
+    return launch_wkv6_chunked_fwd(r, k, v, w, u, n_state ? s0 : nullptr, n_state, state_map, y, sT, states, flags,
                                    B, T, H, dtype, (cudaStream_t)stream);
   }
   return launch_wkv6_fwd(r, k, v, w, u, n_state ? s0 : nullptr, n_state, state_map, y, sT, nullptr,

@@ -125,6 +125,17 @@ struct ProfScope {
     default: return RWKVB200_E_DTYPE;                                        \
   }
 
+// Which (batch, head) units a recurrent kernel works on, and where their tokens and checkpoints lie.  The
+// recurrent kernels double as the exact fallback of the chunked tensor-core paths: a chunked kernel marks
+// the units whose decay leaves the range its scaled operands can represent, and the recurrent kernel is
+// then launched over all units with `flags` set, so that only the marked ones run.
+struct UnitSel {
+  const int* flags;             // one entry per unit, nonzero = run it; nullptr = run every unit
+  const int* seq_start;         // packed variable-length batch: first token and length of every sequence
+  const int* seq_len;           //   (all in batch row 0); nullptr = dense batch
+  long long ckpt_unit_stride;   // floats between the checkpoint regions of consecutive units; 0 = dense
+};
+
 // Kernel launchers implemented in the .cu files (internal linkage across the library only).
 int launch_rwkv7_decode_step(const void* r, const void* w, const void* k, const void* v, const void* a, const void* b,
                              void* state, int state_dtype, void* o, int B, int H, int dtype, cudaStream_t st);
@@ -136,16 +147,25 @@ int launch_rwkv7_step(const void* r, const void* w, const void* k, const void* v
 // ckpt_every-th token as [B,H,ceil(T/ckpt_every),64,64]; o and ht may be NULL.
 int launch_rwkv7_rec_fwd(const void* r, const void* w, const void* k, const void* v, const void* a, const void* b,
                          const float* h0, int n_state, void* o, float* ht, float* ckpt, int ckpt_every,
-                         int B, int Tn, int H, int dtype, int head_first, cudaStream_t st);
+                         int B, int Tn, int H, int dtype, int head_first, cudaStream_t st,
+                         const UnitSel* sel = nullptr, int T_total = 0);
 int launch_rwkv7_rec_bwd(const void* r, const void* w, const void* k, const void* v, const void* a, const void* b,
                          const void* d_o, const float* d_ht, const float* ckpt,
                          void* dr, void* dw, void* dk, void* dv, void* da, void* db, float* d_h0,
-                         int B, int Tn, int H, int dtype, int head_first, cudaStream_t st);
+                         int B, int Tn, int H, int dtype, int head_first, cudaStream_t st,
+                         const UnitSel* sel = nullptr, int T_total = 0);
 constexpr int R7_CKPT = 8;   // tokens between state checkpoints of the recurrent backward
 
 int launch_wkv6_fwd(const void* r, const void* k, const void* v, const void* w, const float* u,
                     const float* s0, int n_state, const int32_t* smap, void* y, float* sT,
-                    float* ckpt, int B, int Tn, int H, int dtype, cudaStream_t st);
+                    float* ckpt, int B, int Tn, int H, int dtype, cudaStream_t st, const UnitSel* sel = nullptr,
+                    int ckpt_every = 0);
+int launch_wkv6_bwd_coarse(const void* r, const void* k, const void* v, const void* w, const float* u,
+                           const void* d_y, const float* d_sT, const float* ckpt,
+                           void* dr, void* dk, void* dv, void* dw, float* du_partial, float* d_s0,
+                           int B, int Tn, int H, int dtype, cudaStream_t st, const UnitSel* sel);
+int launch_wkv6_du_reduce_mixed(const float* part_chunked, const float* part_rec, const int* flags, float* du,
+                                int B, int H, cudaStream_t st);
 int launch_wkv6_bwd(const void* r, const void* k, const void* v, const void* w, const float* u,
                     const void* d_y, const float* d_sT, const float* ckpt,
                     void* dr, void* dk, void* dv, void* dw, float* du_partial, float* du, float* d_s0,
@@ -156,8 +176,10 @@ constexpr int W6_CKPT = 8;
 // boundary, [B*H][ceil(T/64)+1][64][64].
 int launch_wkv6_chunked_fwd(const void* r, const void* k, const void* v, const void* w, const float* u,
                             const float* s0, int n_state, const int32_t* smap, void* y, float* sT,
-                            float* states, int B, int Tn, int H, int dtype, cudaStream_t st);
+                            float* states, int* flags, int B, int Tn, int H, int dtype, cudaStream_t st);
 size_t wkv6_chunked_bwd_workspace_bytes(int B, int Tn, int H);
+size_t wkv6_chunked_flags_bytes(int B, int H);
+int* wkv6_chunked_workspace_flags(void* workspace, int B, int Tn, int H);
 int launch_wkv6_chunked_bwd(const void* r, const void* k, const void* v, const void* w, const float* u,
                             const float* s0, int n_state, const int32_t* smap, const void* d_y, const float* d_sT,
                             void* dr, void* dk, void* dv, void* dw, float* du, float* d_s0, void* workspace,

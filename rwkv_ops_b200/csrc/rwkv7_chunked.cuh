@@ -124,14 +124,25 @@ __device__ __noinline__ void store_tile_rows(__nv_bfloat16* dst, long long st, c
 struct Workspace {
   unsigned char* tiles;   // [n_chunks_total][tiles_per_chunk][8192]
   float* aux;             // [n_chunks_total][128]
+  int* flags;             // [B*H] nonzero: the unit's decay left the range of the scaled operands (DECAY_LIMIT)
   int tiles_per_chunk;
 };
+
+// The scaled operands carry e^{+-(gi - gref)}: with the reference point in the middle of the chunk the
+// exponent of a channel reaches the sum of |g| over half a chunk.  Up to DECAY_LIMIT every factor and every
+// scaled state entry stays a normal bfloat16 / float32 number and the chunk equations are exact; a
+// (batch, head) unit with a larger half-chunk sum in any channel is marked in Workspace::flags by the intra
+// kernel and recomputed afterwards by the float32 recurrence (rwkv7_recurrent.cu), so the operator never
+// returns values computed from clamped exponents.  |g| <= 1.875 per token never reaches the limit; RWKV7's
+// own parametrisation keeps |g| below 0.61.
+constexpr float DECAY_LIMIT = 60.f;
 
 inline size_t align256(size_t x) { return (x + 255) & ~size_t(255); }
 
 inline size_t fwd_workspace_bytes(int B, int T, int H, int tiles_per_chunk) {
   const size_t n = (size_t)B * H * num_chunks(T);
-  return align256(n * tiles_per_chunk * tc::TILE_BYTES) + align256(n * AUX_FLOATS * sizeof(float)) + 1024;
+  return align256(n * tiles_per_chunk * tc::TILE_BYTES) + align256(n * AUX_FLOATS * sizeof(float)) +
+         align256((size_t)B * H * sizeof(int)) + 1024;
 }
 
 inline Workspace carve(void* ws, int B, int T, int H, int tiles_per_chunk) {
@@ -140,6 +151,7 @@ inline Workspace carve(void* ws, int B, int T, int H, int tiles_per_chunk) {
   uintptr_t p = (reinterpret_cast<uintptr_t>(ws) + 1023) & ~uintptr_t(1023);
   w.tiles = reinterpret_cast<unsigned char*>(p);
   w.aux = reinterpret_cast<float*>(p + align256(n * tiles_per_chunk * tc::TILE_BYTES));
+  w.flags = reinterpret_cast<int*>(reinterpret_cast<unsigned char*>(w.aux) + align256(n * AUX_FLOATS * sizeof(float)));
   w.tiles_per_chunk = tiles_per_chunk;
   return w;
 }

@@ -310,7 +310,7 @@ r7c_bwd_final_kernel(const bf16* __restrict__ w, const __grid_constant__ CUtenso
                      bf16* __restrict__ dq_rows, bf16* __restrict__ dw_rows, bf16* __restrict__ dk_rows,
                      bf16* __restrict__ dv_rows, bf16* __restrict__ da_rows, bf16* __restrict__ db_rows,
                      SeqView sv, int H, int NT, int n_ch, TokLayout lay, int* status, long long* dbg) {
-#define R7C_STAMP(n) do { if (dbg && tid == 0 && blockIdx.x == gridDim.x / 2 && it == 1) dbg[n] = clock64(); } while (0)
+#define R7C_STAMP(n) do { if (dbg && tid == 0 && blockIdx.x == gridDim.x / 2 && it == 30) dbg[n] = clock64(); } while (0)
   extern __shared__ unsigned char smem_raw[];
   FinalSmem& sm = *reinterpret_cast<FinalSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -795,7 +795,23 @@ int launch_rwkv7_chunked_bwd(const void* r, const void* w, const void* k, const 
     if (e) return e;
     return launch_rwkv7_producer_bwd(w, a, b, dw, da, db, (long long)B * Tn * H, st);
   }
-  return check_launch();
+  e = check_launch();
+  if (e) return e;
+  // Units the forward marked (decay beyond the range of the scaled operands): their gradients come from the
+  // float32 recurrence instead.  Its state checkpoints (16 KB per 8 tokens = 128 KB per chunk) go into the
+  // unit's own tile region of the workspace (144 KB per chunk), whose contents are void for such a unit.
+  {
+    const long long unit_floats = (long long)NT * ALL_TILES * TILE_BYTES / (long long)sizeof(float);
+    float* ckpt = reinterpret_cast<float*>(ws.tiles);
+    const UnitSel sel{ws.flags, seq_start, seq_len, unit_floats};
+    const int tt = seq_start ? T_total : 0;
+    e = launch_rwkv7_rec_fwd(r, w, k, v, a, b, h0, n_state, nullptr, nullptr, ckpt, R7_CKPT, B, Tn, H, RWKVB200_BF16,
+                             head_first, st, &sel, tt);
+    if (e) return e;
+    e = launch_rwkv7_rec_bwd(r, w, k, v, a, b, d_o, d_ht, ckpt, dr, dw, dk, dv, da, db, d_h0, B, Tn, H,
+                             RWKVB200_BF16, head_first, st, &sel, tt);
+  }
+  return e;
 }
 
 }  // namespace rwkvb200

@@ -45,9 +45,9 @@ r7c_intra_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ w, con
                      const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_a,
                      const __grid_constant__ CUtensorMap tmap_b,
                      const __grid_constant__ CUtensorMap tmap_v, unsigned char* __restrict__ ws_tiles,
-                     float* __restrict__ ws_aux, int tiles_per_chunk, int keep_for_bwd,
-                     SeqView sv, int H, int NT, int n_ch, TokLayout lay, int* status, long long* dbg) {
-#define R7C_STAMP(n) do { if (dbg && tid == 0 && blockIdx.x == gridDim.x / 2 && it == 1) dbg[n] = clock64(); } while (0)
+                     float* __restrict__ ws_aux, int* __restrict__ ws_flags, int tiles_per_chunk,
+                     int keep_for_bwd, SeqView sv, int H, int NT, int n_ch, TokLayout lay, int* status, long long* dbg) {
+#define R7C_STAMP(n) do { if (dbg && tid == 0 && blockIdx.x == gridDim.x / 2 && it == 30) dbg[n] = clock64(); } while (0)
   extern __shared__ unsigned char smem_raw[];
   IntraSmem& sm = *reinterpret_cast<IntraSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -188,6 +188,8 @@ r7c_intra_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ w, con
         const float tot0 = sm.qtot[0][tid] + sm.qtot[1][tid], tot1 = sm.qtot[2][tid] + sm.qtot[3][tid];
         ws_aux[(size_t)ch * AUX_FLOATS + tid] = __expf(fmaxf(tot0, -EXP_CLAMP));        // e^{gref}
         ws_aux[(size_t)ch * AUX_FLOATS + 64 + tid] = __expf(fmaxf(tot1, -EXP_CLAMP));   // e^{glast-gref}
+        // a half-chunk decay sum beyond the limit: the unit is recomputed by the float32 recurrence
+        if (fminf(tot0, tot1) < -DECAY_LIMIT) ws_flags[bi * H + hi] = 1;
       }
       // the raw q, k, a, b: each thread scales its own 2 x 16 bytes in place (the previous chunk-head's W, U
       // copies, committed last, may still be reading their tiles: those are rewritten only after MMA 1)
@@ -655,10 +657,11 @@ r7c_scan_fwd_kernel(const __grid_constant__ CUtensorMap tmap_v, const unsigned c
       if (c + 1 < NT && hsel == 0) asm volatile("prefetch.global.L2 [%0];" ::"l"(tile + (size_t)tiles_per_chunk * TILE_BYTES + row * 128));
     }
     // decay factors needed at the end of this chunk, fetched early
-    float scale = 1.f;
+    // (applied one after the other: their product can underflow float32 where neither factor does)
+    float scale = 1.f, scale_next = 1.f;
     if (state_lane) {
       scale = ws_aux[(ch0 + c) * AUX_FLOATS + 64 + row];                       // e^{glast-gref} of this chunk
-      if (c + 1 < NT) scale *= ws_aux[(ch0 + c + 1) * AUX_FLOATS + row];        // e^{gref} of the next chunk
+      if (c + 1 < NT) scale_next = ws_aux[(ch0 + c + 1) * AUX_FLOATS + row];    // e^{gref} of the next chunk
     }
     // (a) SA = W h~0, QH = q~ h~0 (P1);  H += k~^T v (P2 lower)
     if (tid == 0) {
@@ -747,7 +750,7 @@ r7c_scan_fwd_kernel(const __grid_constant__ CUtensorMap tmap_v, const unsigned c
           tile_store_row32(sm.xt, row, c0, x);
         }
 #pragma unroll
-        for (int j = 0; j < 32; ++j) { x[j] = __uint_as_float(r[j]) * scale; r[j] = __float_as_uint(x[j]); }
+        for (int j = 0; j < 32; ++j) { x[j] = (__uint_as_float(r[j]) * scale) * scale_next; r[j] = __float_as_uint(x[j]); }
         if (!last) {
           tile_store_row32(sm.ht, row, c0, x);
         } else if (ht) {
@@ -817,6 +820,7 @@ int launch_rwkv7_chunked_fwd(const void* r, const void* w, const void* k, const 
   const int tpc = keep_for_bwd ? (int)ALL_TILES : (int)FWD_TILES;
   Workspace ws = carve(workspace, B, Tn, H, tpc);
   TokLayout lay(mapT, H, head_first);
+  if (cuda_ok(cudaMemsetAsync(ws.flags, 0, (size_t)B * H * sizeof(int), st))) return RWKVB200_E_CUDA;
   {
     const int smem = (int)sizeof(IntraSmem) + 1024;
     ProfScope prof("r7c_intra_fwd_kernel", st);
@@ -831,7 +835,8 @@ int launch_rwkv7_chunked_fwd(const void* r, const void* w, const void* k, const 
         return RWKVB200_E_CUDA;                                                                                    \
       r7c_intra_fwd_kernel<P, F><<<grid, 256, smem, st>>>((const bf16*)r, (const bf16*)w, (const bf16*)k,         \
           (const bf16*)a, (const bf16*)b, tmap_in[0], tmap_in[1], tmap_in[2], tmap_in[3], tmap_in[4], tmap_v,      \
-          ws.tiles, ws.aux, tpc, keep_for_bwd ? 1 : 0, sv, H, NT, n_ch, lay, status, debug_stamp_buffer());        \
+          ws.tiles, ws.aux, ws.flags, tpc, keep_for_bwd ? 1 : 0, sv, H, NT, n_ch, lay, status,                    \
+          debug_stamp_buffer());                                                                                   \
     } while (0)
     if (seq_start) R7C_LAUNCH_INTRA(true, false);
     else if (fused) R7C_LAUNCH_INTRA(false, true);
@@ -859,7 +864,16 @@ int launch_rwkv7_chunked_fwd(const void* r, const void* w, const void* k, const 
     else             { if (seq_start) R7C_LAUNCH_SCAN(2, true); else R7C_LAUNCH_SCAN(2, false); }
 #undef R7C_LAUNCH_SCAN
   }
-  return check_launch();
+  e = check_launch();
+  if (e || fused) return e;      // fused producers bound |g| by e^{-1/2}: no unit can be marked
+  // units whose decay left the range of the scaled operands: exact float32 recurrence over them (the
+  // kernel's other CTAs leave at once)
+  if (o || ht) {
+    const UnitSel sel{ws.flags, seq_start, seq_len, 0};
+    e = launch_rwkv7_rec_fwd(r, w, k, v, a, b, h0, n_state, o, ht, nullptr, R7_CKPT, B, Tn, H, RWKVB200_BF16,
+                             head_first, st, &sel, seq_start ? T_total : 0);
+  }
+  return e;
 }
 
 }  // namespace rwkvb200

@@ -45,16 +45,20 @@ __global__ void __launch_bounds__(64)
 rwkv7_rec_fwd_kernel(const T* __restrict__ r, const T* __restrict__ w, const T* __restrict__ k,
                      const T* __restrict__ v, const T* __restrict__ a, const T* __restrict__ b,
                      const float* __restrict__ h0, int n_state, T* __restrict__ o, float* __restrict__ ht,
-                     float* __restrict__ ckpt, int ckpt_every, int Tn, int H, TokLayout lay) {
+                     float* __restrict__ ckpt, int ckpt_every, int Tn_dense, int H, TokLayout lay, UnitSel sel) {
   __shared__ __align__(16) float tile[TL][5][HS];   // r, d, k, a, b
   __shared__ __align__(16) float vt[TL][VS];
   __shared__ __align__(16) float ot[TL][VS];
 
   const int unit = blockIdx.x, y = blockIdx.y, tid = threadIdx.x;
+  if (sel.flags && sel.flags[unit] == 0) return;      // only the selected units run
   const int bi = unit / H, hi = unit % H;
   const int vl = tid >> 2, kq = tid & 3;
-  const long long base = bi * lay.sb + hi * lay.sh;
-  const int NC = ckpt ? (Tn + ckpt_every - 1) / ckpt_every : 0;
+  // a packed batch keeps its sequences end to end in batch row 0
+  const int Tn = sel.seq_len ? sel.seq_len[bi] : Tn_dense;
+  const long long base = sel.seq_start ? hi * lay.sh + sel.seq_start[bi] * lay.st : bi * lay.sb + hi * lay.sh;
+  const long long ckpt_unit = sel.ckpt_unit_stride ? sel.ckpt_unit_stride
+                                                   : (long long)((Tn_dense + ckpt_every - 1) / ckpt_every) * HS * HS;
 
   float S[16];
   if (h0 && n_state > 0) {
@@ -89,7 +93,7 @@ rwkv7_rec_fwd_kernel(const T* __restrict__ r, const T* __restrict__ w, const T* 
     for (int tl = 0; tl < nt; ++tl) {
       const int t = t0 + tl;
       if (ckpt && (t % ckpt_every) == 0) {
-        float* p = ckpt + ((((long long)unit * NC + t / ckpt_every) * HS) + (y * VS + vl)) * HS + 16 * kq;
+        float* p = ckpt + unit * ckpt_unit + (((long long)(t / ckpt_every) * HS) + (y * VS + vl)) * HS + 16 * kq;
 #pragma unroll
         for (int j = 0; j < 16; j += 4)
           *reinterpret_cast<float4*>(p + j) = make_float4(S[j], S[j + 1], S[j + 2], S[j + 3]);
@@ -160,17 +164,21 @@ rwkv7_rec_bwd_kernel(const T* __restrict__ r, const T* __restrict__ w, const T* 
                      const T* __restrict__ d_o, const float* __restrict__ d_ht, const float* __restrict__ ckpt,
                      T* __restrict__ dr, T* __restrict__ dw, T* __restrict__ dk, T* __restrict__ dv,
                      T* __restrict__ da, T* __restrict__ db, float* __restrict__ d_h0,
-                     int Tn, int H, TokLayout lay) {
+                     int Tn_dense, int H, TokLayout lay, UnitSel sel) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   BwdSmem& sm = *reinterpret_cast<BwdSmem*>(smem_raw);
   cg::cluster_group cluster = cg::this_cluster();
 
   const int unit = blockIdx.x, y = blockIdx.y, tid = threadIdx.x;
+  if (sel.flags && sel.flags[unit] == 0) return;      // the four CTAs of a cluster share the unit: all leave
   const int bi = unit / H, hi = unit % H;
   const int vl = tid >> 2, kq = tid & 3;   // row role
   const int kc = tid;                      // column role
-  const long long base = bi * lay.sb + hi * lay.sh;
+  const int Tn = sel.seq_len ? sel.seq_len[bi] : Tn_dense;
+  const long long base = sel.seq_start ? hi * lay.sh + sel.seq_start[bi] * lay.st : bi * lay.sb + hi * lay.sh;
   const int NC = (Tn + CK - 1) / CK;
+  const long long ckpt_unit = sel.ckpt_unit_stride ? sel.ckpt_unit_stride
+                                                   : (long long)((Tn_dense + CK - 1) / CK) * HS * HS;
 
   float dSr[16], dSc[VS];
   if (d_ht) {
@@ -206,7 +214,7 @@ rwkv7_rec_bwd_kernel(const T* __restrict__ r, const T* __restrict__ w, const T* 
     // ---- re-run the chunk forward from its checkpoint (row role)
     float S[16];
     {
-      const float* p = ckpt + ((((long long)unit * NC + c) * HS) + (y * VS + vl)) * HS + 16 * kq;
+      const float* p = ckpt + unit * ckpt_unit + (((long long)c * HS) + (y * VS + vl)) * HS + 16 * kq;
 #pragma unroll
       for (int j = 0; j < 16; j += 4) {
         float4 f = *reinterpret_cast<const float4*>(p + j);
@@ -334,21 +342,25 @@ rwkv7_rec_bwd_kernel(const T* __restrict__ r, const T* __restrict__ w, const T* 
 
 int launch_rwkv7_rec_fwd(const void* r, const void* w, const void* k, const void* v, const void* a, const void* b,
                          const float* h0, int n_state, void* o, float* ht, float* ckpt, int ckpt_every,
-                         int B, int Tn, int H, int dtype, int head_first, cudaStream_t st) {
-  TokLayout lay(Tn, H, head_first);
+                         int B, int Tn, int H, int dtype, int head_first, cudaStream_t st, const UnitSel* sel_,
+                         int T_total) {
+  TokLayout lay(T_total ? T_total : Tn, H, head_first);
+  const UnitSel sel = sel_ ? *sel_ : UnitSel{nullptr, nullptr, nullptr, 0};
   dim3 grid(B * H, NQ);
   ProfScope prof("rwkv7_rec_fwd_kernel", st);
   RWKVB200_DISPATCH_DTYPE(dtype,
     rwkv7_rec_fwd_kernel<T><<<grid, 64, 0, st>>>((const T*)r, (const T*)w, (const T*)k, (const T*)v, (const T*)a,
-                                                 (const T*)b, h0, n_state, (T*)o, ht, ckpt, ckpt_every, Tn, H, lay));
+                                                 (const T*)b, h0, n_state, (T*)o, ht, ckpt, ckpt_every, Tn, H, lay, sel));
   return check_launch();
 }
 
 int launch_rwkv7_rec_bwd(const void* r, const void* w, const void* k, const void* v, const void* a, const void* b,
                          const void* d_o, const float* d_ht, const float* ckpt,
                          void* dr, void* dw, void* dk, void* dv, void* da, void* db, float* d_h0,
-                         int B, int Tn, int H, int dtype, int head_first, cudaStream_t st) {
-  TokLayout lay(Tn, H, head_first);
+                         int B, int Tn, int H, int dtype, int head_first, cudaStream_t st, const UnitSel* sel_,
+                         int T_total) {
+  TokLayout lay(T_total ? T_total : Tn, H, head_first);
+  const UnitSel sel = sel_ ? *sel_ : UnitSel{nullptr, nullptr, nullptr, 0};
   dim3 grid(B * H, NQ);
   const int smem = (int)sizeof(BwdSmem);
   ProfScope prof("rwkv7_rec_bwd_kernel", st);
@@ -356,7 +368,7 @@ int launch_rwkv7_rec_bwd(const void* r, const void* w, const void* k, const void
     if (cuda_ok(cudaFuncSetAttribute(rwkv7_rec_bwd_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem))) return RWKVB200_E_CUDA;
     rwkv7_rec_bwd_kernel<T><<<grid, 64, smem, st>>>((const T*)r, (const T*)w, (const T*)k, (const T*)v, (const T*)a,
                                                     (const T*)b, (const T*)d_o, d_ht, ckpt, (T*)dr, (T*)dw, (T*)dk,
-                                                    (T*)dv, (T*)da, (T*)db, d_h0, Tn, H, lay));
+                                                    (T*)dv, (T*)da, (T*)db, d_h0, Tn, H, lay, sel));
   return check_launch();
 }
 

@@ -229,6 +229,19 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
         "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
       : "memory");
 }
+// 16 consecutive columns of the thread's lane
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr) : "memory");
+}
+// N = 16 or 32 consecutive columns
+template <int N> __device__ __forceinline__ void tmem_ld(uint32_t taddr, uint32_t (&r)[N]);
+template <> __device__ __forceinline__ void tmem_ld<32>(uint32_t taddr, uint32_t (&r)[32]) { tmem_ld32(taddr, r); }
+template <> __device__ __forceinline__ void tmem_ld<16>(uint32_t taddr, uint32_t (&r)[16]) { tmem_ld16(taddr, r); }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
@@ -263,6 +276,31 @@ __device__ __forceinline__ void tile_store_row32(unsigned char* tile, int row, i
 __device__ __forceinline__ void tile_load_row32(const unsigned char* tile, int row, int col0, float* x) {
 #pragma unroll
   for (int c = 0; c < 4; ++c) {
+    const uint4 u = *reinterpret_cast<const uint4*>(tile + tile_chunk_off(row, (col0 >> 3) + c));
+    x[8 * c + 0] = bf16_lo(u.x); x[8 * c + 1] = bf16_hi(u.x);
+    x[8 * c + 2] = bf16_lo(u.y); x[8 * c + 3] = bf16_hi(u.y);
+    x[8 * c + 4] = bf16_lo(u.z); x[8 * c + 5] = bf16_hi(u.z);
+    x[8 * c + 6] = bf16_lo(u.w); x[8 * c + 7] = bf16_hi(u.w);
+  }
+}
+
+// the same for N = 16 or 32 consecutive values (col0 a multiple of 8)
+template <int N>
+__device__ __forceinline__ void tile_store_row(unsigned char* tile, int row, int col0, const float* x) {
+#pragma unroll
+  for (int c = 0; c < N / 8; ++c) {
+    uint4 u;
+    u.x = pack_bf16(x[8 * c + 0], x[8 * c + 1]);
+    u.y = pack_bf16(x[8 * c + 2], x[8 * c + 3]);
+    u.z = pack_bf16(x[8 * c + 4], x[8 * c + 5]);
+    u.w = pack_bf16(x[8 * c + 6], x[8 * c + 7]);
+    *reinterpret_cast<uint4*>(tile + tile_chunk_off(row, (col0 >> 3) + c)) = u;
+  }
+}
+template <int N>
+__device__ __forceinline__ void tile_load_row(const unsigned char* tile, int row, int col0, float* x) {
+#pragma unroll
+  for (int c = 0; c < N / 8; ++c) {
     const uint4 u = *reinterpret_cast<const uint4*>(tile + tile_chunk_off(row, (col0 >> 3) + c));
     x[8 * c + 0] = bf16_lo(u.x); x[8 * c + 1] = bf16_hi(u.x);
     x[8 * c + 2] = bf16_lo(u.y); x[8 * c + 3] = bf16_hi(u.y);

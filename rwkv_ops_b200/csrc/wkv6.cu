@@ -19,6 +19,8 @@
 // per-chunk partial sums through distributed shared memory in a fixed order (deterministic).
 #include <cooperative_groups.h>
 
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace cg = cooperative_groups;
@@ -45,17 +47,20 @@ __global__ void __launch_bounds__(64)
 wkv6_fwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __restrict__ v,
                 const T* __restrict__ w, const float* __restrict__ u,
                 const float* __restrict__ s0, int n_state, const int32_t* __restrict__ smap,
-                T* __restrict__ yout, float* __restrict__ sT, float* __restrict__ ckpt, int Tn, int H) {
+                T* __restrict__ yout, float* __restrict__ sT, float* __restrict__ ckpt, int ckpt_every,
+                int Tn, int H, UnitSel sel) {
   __shared__ __align__(16) float tile[TL][4][HS];   // r, d, k, r*u*k
   __shared__ __align__(16) float vt[TL][VS];
   __shared__ __align__(16) float yt[TL][VS];
 
   const int unit = blockIdx.x, y = blockIdx.y, tid = threadIdx.x;
+  if (sel.flags && sel.flags[unit] == 0) return;      // only the selected units run
   const int bi = unit / H, hi = unit % H;
   const int vl = tid >> 2, kq = tid & 3;
   const long long base = ((long long)bi * Tn * H + hi) * HS;   // + t*H*HS
   const long long tstride = (long long)H * HS;
-  const int NC = ckpt ? (Tn + CK - 1) / CK : 0;
+  const long long ckpt_unit = sel.ckpt_unit_stride ? sel.ckpt_unit_stride
+                                                   : (long long)((Tn + ckpt_every - 1) / ckpt_every) * HS * HS;
   const float4 u4 = *reinterpret_cast<const float4*>(u + hi * HS + 4 * (tid & 15));
 
   float S[16];
@@ -89,8 +94,8 @@ wkv6_fwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __res
     __syncthreads();
     for (int tl = 0; tl < nt; ++tl) {
       const int t = t0 + tl;
-      if (ckpt && (t % CK) == 0) {
-        float* p = ckpt + ((((long long)unit * NC + t / CK) * HS) + 16 * kq) * HS + y * VS + vl;
+      if (ckpt && (t % ckpt_every) == 0) {
+        float* p = ckpt + unit * ckpt_unit + (((long long)(t / ckpt_every) * HS) + 16 * kq) * HS + y * VS + vl;
 #pragma unroll
         for (int j = 0; j < 16; ++j) p[j * HS] = S[j];
       }
@@ -136,25 +141,33 @@ struct BwdSmem {
   float part[2][CK][3][HS];       // partial dr, dk, dd over this CTA's 16 value columns
   float pdyv[2][CK];              // partial sum_v dy v
 };
+// COARSE variant: the checkpoints lie 64 tokens apart (the chunk-boundary states of the chunked path); the
+// states at the start of the eight 8-token groups of a 64-token stretch are recomputed into `sub`.
+struct BwdSmemCoarse : BwdSmem {
+  float sub[8][HS][VS];
+};
 
-template <typename T>
+template <typename T, bool COARSE>
 __global__ void __cluster_dims__(1, NQ, 1) __launch_bounds__(64)
 wkv6_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __restrict__ v,
                 const T* __restrict__ w, const float* __restrict__ u,
                 const T* __restrict__ d_y, const float* __restrict__ d_sT, const float* __restrict__ ckpt,
                 T* __restrict__ dr, T* __restrict__ dk, T* __restrict__ dv, T* __restrict__ dw,
-                float* __restrict__ du_partial, float* __restrict__ d_s0, int Tn, int H) {
+                float* __restrict__ du_partial, float* __restrict__ d_s0, int Tn, int H, UnitSel sel) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  BwdSmem& sm = *reinterpret_cast<BwdSmem*>(smem_raw);
+  typedef typename std::conditional<COARSE, BwdSmemCoarse, BwdSmem>::type Smem;
+  Smem& sm = *reinterpret_cast<Smem*>(smem_raw);
   cg::cluster_group cluster = cg::this_cluster();
 
   const int unit = blockIdx.x, y = blockIdx.y, tid = threadIdx.x;
+  if (sel.flags && sel.flags[unit] == 0) return;      // the four CTAs of a cluster share the unit: all leave
   const int bi = unit / H, hi = unit % H;
   const int vl = tid >> 2, kq = tid & 3;   // value role
   const int kc = tid;                      // key role
   const long long base = ((long long)bi * Tn * H + hi) * HS;
   const long long tstride = (long long)H * HS;
   const int NC = (Tn + CK - 1) / CK;
+  const long long ckpt_unit = sel.ckpt_unit_stride ? sel.ckpt_unit_stride : (long long)NC * HS * HS;
   const float4 u4 = *reinterpret_cast<const float4*>(u + hi * HS + 4 * (tid & 15));
 
   float Gv[16], Gk[VS];   // value-role copy G[16kq+j][vl], key-role copy G[kc][i]
@@ -173,6 +186,46 @@ wkv6_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __res
 
   for (int c = NC - 1; c >= 0; --c) {
     const int t0 = c * CK, nt = min(CK, Tn - t0), pb = c & 1;
+    if constexpr (COARSE) {
+      // entering a 64-token stretch (from its end): re-run it forward from its checkpoint, keeping the
+      // state at the start of each of its 8-token groups
+      if (c == NC - 1 || (c & 7) == 7) {
+        const int c64 = c >> 3;
+        float S0[16];
+        {
+          const float* p = ckpt + unit * ckpt_unit + (((long long)c64 * HS) + 16 * kq) * HS + y * VS + vl;
+#pragma unroll
+          for (int j = 0; j < 16; ++j) S0[j] = p[j * HS];
+        }
+        for (int g = 8 * c64; g <= c; ++g) {
+          const int tg0 = g * CK, ntg = min(CK, Tn - tg0);
+          for (int i = tid; i < ntg * 16; i += 64) {
+            const int quad = i & 15, tl = i >> 4;
+            const long long off = base + (long long)(tg0 + tl) * tstride + 4 * quad;
+            const float4 k4 = load4(k + off), w4 = load4(w + off);
+            *reinterpret_cast<float4*>(&sm.tile[tl][1][4 * quad]) =
+                make_float4(decay_of(w4.x), decay_of(w4.y), decay_of(w4.z), decay_of(w4.w));
+            *reinterpret_cast<float4*>(&sm.tile[tl][3][4 * quad]) = k4;
+          }
+          if (tid < ntg * 4) {
+            const int tl = tid >> 2, quad = tid & 3;
+            *reinterpret_cast<float4*>(&sm.vt[tl][4 * quad]) =
+                load4(v + base + (long long)(tg0 + tl) * tstride + y * VS + 4 * quad);
+          }
+          __syncthreads();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) sm.sub[g & 7][16 * kq + j][vl] = S0[j];
+          for (int tl = 0; tl < ntg; ++tl) {
+            const float* td = &sm.tile[tl][1][16 * kq];
+            const float* tk = &sm.tile[tl][3][16 * kq];
+            const float vv = sm.vt[tl][vl];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) S0[j] = td[j] * S0[j] + tk[j] * vv;
+          }
+          __syncthreads();      // the tile is staged again for the next group
+        }
+      }
+    }
     for (int i = tid; i < nt * 16; i += 64) {
       const int quad = i & 15, tl = i >> 4;
       const long long off = base + (long long)(t0 + tl) * tstride + 4 * quad;
@@ -192,8 +245,11 @@ wkv6_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __res
       *reinterpret_cast<float4*>(&sm.dyt[tl][4 * quad]) = load4(d_y + off);
     }
     float S[16];
-    {
-      const float* p = ckpt + ((((long long)unit * NC + c) * HS) + 16 * kq) * HS + y * VS + vl;
+    if constexpr (COARSE) {
+#pragma unroll
+      for (int j = 0; j < 16; ++j) S[j] = sm.sub[c & 7][16 * kq + j][vl];
+    } else {
+      const float* p = ckpt + unit * ckpt_unit + (((long long)c * HS) + 16 * kq) * HS + y * VS + vl;
 #pragma unroll
       for (int j = 0; j < 16; ++j) S[j] = p[j * HS];
     }
@@ -294,16 +350,60 @@ wkv6_du_reduce_kernel(const float* __restrict__ du_partial, float* __restrict__ 
   du[hi * HS + kc] = s;
 }
 
+// The same for the chunked path with its recurrent fallback: a unit contributes one row of `part_chunked`
+// [B*H][64], or, when the forward marked it (flags), its four rows of `part_rec` [B*H][4][64].
+__global__ void __launch_bounds__(64)
+wkv6_du_reduce_mixed_kernel(const float* __restrict__ part_chunked, const float* __restrict__ part_rec,
+                            const int* __restrict__ flags, float* __restrict__ du, int B, int H) {
+  const int hi = blockIdx.x, kc = threadIdx.x;
+  float s = 0.f;
+  for (int bi = 0; bi < B; ++bi) {
+    const long long unit = (long long)bi * H + hi;
+    if (flags[unit]) {
+      for (int q = 0; q < NQ; ++q) s += part_rec[(unit * NQ + q) * HS + kc];
+    } else {
+      s += part_chunked[unit * HS + kc];
+    }
+  }
+  du[hi * HS + kc] = s;
+}
+
 }  // namespace
 
 int launch_wkv6_fwd(const void* r, const void* k, const void* v, const void* w, const float* u,
                     const float* s0, int n_state, const int32_t* smap, void* y, float* sT,
-                    float* ckpt, int B, int Tn, int H, int dtype, cudaStream_t st) {
+                    float* ckpt, int B, int Tn, int H, int dtype, cudaStream_t st, const UnitSel* sel_,
+                    int ckpt_every) {
   dim3 grid(B * H, NQ);
+  const UnitSel sel = sel_ ? *sel_ : UnitSel{nullptr, nullptr, nullptr, 0};
   ProfScope prof("wkv6_fwd_kernel", st);
   RWKVB200_DISPATCH_DTYPE(dtype,
     wkv6_fwd_kernel<T><<<grid, 64, 0, st>>>((const T*)r, (const T*)k, (const T*)v, (const T*)w, u, s0, n_state, smap,
-                                            (T*)y, sT, ckpt, Tn, H));
+                                            (T*)y, sT, ckpt, ckpt_every ? ckpt_every : CK, Tn, H, sel));
+  return check_launch();
+}
+
+// The backward over the units marked in sel->flags, from checkpoints 64 tokens apart (sel->ckpt_unit_stride
+// floats between units); du_partial receives four rows per unit.  No reduction of du.
+int launch_wkv6_bwd_coarse(const void* r, const void* k, const void* v, const void* w, const float* u,
+                           const void* d_y, const float* d_sT, const float* ckpt,
+                           void* dr, void* dk, void* dv, void* dw, float* du_partial, float* d_s0,
+                           int B, int Tn, int H, int dtype, cudaStream_t st, const UnitSel* sel) {
+  dim3 grid(B * H, NQ);
+  const int smem = (int)sizeof(BwdSmemCoarse);
+  ProfScope prof("wkv6_bwd_kernel", st);
+  RWKVB200_DISPATCH_DTYPE(dtype,
+    if (cuda_ok(cudaFuncSetAttribute(wkv6_bwd_kernel<T, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem))) return RWKVB200_E_CUDA;
+    wkv6_bwd_kernel<T, true><<<grid, 64, smem, st>>>((const T*)r, (const T*)k, (const T*)v, (const T*)w, u,
+                                                     (const T*)d_y, d_sT, ckpt, (T*)dr, (T*)dk, (T*)dv, (T*)dw,
+                                                     du_partial, d_s0, Tn, H, *sel));
+  return check_launch();
+}
+
+int launch_wkv6_du_reduce_mixed(const float* part_chunked, const float* part_rec, const int* flags, float* du,
+                                int B, int H, cudaStream_t st) {
+  ProfScope prof("wkv6_du_reduce_kernel", st);
+  wkv6_du_reduce_mixed_kernel<<<H, 64, 0, st>>>(part_chunked, part_rec, flags, du, B, H);
   return check_launch();
 }
 
@@ -316,9 +416,10 @@ int launch_wkv6_bwd(const void* r, const void* k, const void* v, const void* w, 
   {
     ProfScope prof("wkv6_bwd_kernel", st);
     RWKVB200_DISPATCH_DTYPE(dtype,
-      if (cuda_ok(cudaFuncSetAttribute(wkv6_bwd_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem))) return RWKVB200_E_CUDA;
-      wkv6_bwd_kernel<T><<<grid, 64, smem, st>>>((const T*)r, (const T*)k, (const T*)v, (const T*)w, u, (const T*)d_y,
-                                                 d_sT, ckpt, (T*)dr, (T*)dk, (T*)dv, (T*)dw, du_partial, d_s0, Tn, H));
+      if (cuda_ok(cudaFuncSetAttribute(wkv6_bwd_kernel<T, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem))) return RWKVB200_E_CUDA;
+      wkv6_bwd_kernel<T, false><<<grid, 64, smem, st>>>((const T*)r, (const T*)k, (const T*)v, (const T*)w, u,
+                                                        (const T*)d_y, d_sT, ckpt, (T*)dr, (T*)dk, (T*)dv, (T*)dw,
+                                                        du_partial, d_s0, Tn, H, UnitSel{nullptr, nullptr, nullptr, 0}));
   }
   int e = check_launch();
   if (e) return e;

@@ -35,6 +35,12 @@ constexpr int L = 64;
 constexpr int NROW = 68;
 constexpr float EXP_CLAMP = 80.f;
 __device__ __forceinline__ float cexp(float x) { return __expf(fminf(fmaxf(x, -EXP_CLAMP), EXP_CLAMP)); }
+// The scaled operands carry e^{+-(gi - gref)}, whose exponent reaches the sum of |g| over half a chunk.  Up to
+// DECAY_LIMIT every factor (and the low half of every split operand) stays a normal number and the chunk
+// equations are exact.  A (batch, head) unit that exceeds it in any channel of any chunk is marked by the
+// forward kernel and recomputed by the float32 recurrence (wkv6.cu), forward and backward, so that no value
+// computed from a clamped exponent is ever returned.  |g| <= 1.875 per token (w <= 0.62) never reaches it.
+constexpr float DECAY_LIMIT = 60.f;
 
 // two values as packed bf16 pairs hi and lo with x = hi + lo (+ an error of about 2^-17 |x|)
 __device__ __forceinline__ void split_pair(float x0, float x1, uint32_t& hi, uint32_t& lo) {
@@ -107,7 +113,7 @@ __global__ void __launch_bounds__(256, 2)
 wkv6c_fwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __restrict__ v, const T* __restrict__ w,
                  const float* __restrict__ u, const float* __restrict__ s0, int n_state,
                  const int32_t* __restrict__ smap, T* __restrict__ y, float* __restrict__ sT,
-                 float* __restrict__ states, const __grid_constant__ CUtensorMap tmap_r,
+                 float* __restrict__ states, int* __restrict__ flags, const __grid_constant__ CUtensorMap tmap_r,
                  const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
                  const __grid_constant__ CUtensorMap tmap_w, int Tn, int H, int* status, long long* dbg) {
 #define W6C_STAMP(n) do { if (dbg && tid == 0 && blockIdx.x == gridDim.x / 2 && c == 2) dbg[n] = clock64(); } while (0)
@@ -220,8 +226,11 @@ wkv6c_fwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
     // decay factors of the state rows: e^{gref} of this chunk scales the incoming state, e^{glast-gref} the outgoing
     float e0 = 1.f, dlast = 1.f;
     if (!tok_lane) {
-      e0 = __expf(fmaxf(sm.qtot[0][srow] + sm.qtot[1][srow], -EXP_CLAMP));
-      dlast = __expf(fmaxf(sm.qtot[2][srow] + sm.qtot[3][srow], -EXP_CLAMP));
+      const float tot0 = sm.qtot[0][srow] + sm.qtot[1][srow], tot1 = sm.qtot[2][srow] + sm.qtot[3][srow];
+      e0 = __expf(fmaxf(tot0, -EXP_CLAMP));
+      dlast = __expf(fmaxf(tot1, -EXP_CLAMP));
+      // a half-chunk decay sum beyond the limit: the unit is recomputed by the float32 recurrence
+      if (hsel == 0 && fminf(tot0, tot1) < -DECAY_LIMIT) flags[unit] = 1;
     }
     // ---- S~0 = e^{gref} S0 stays in registers (fp32); hi/lo bf16 tiles for the r~ S~0 product
     if (!tok_lane) {
@@ -797,21 +806,13 @@ wkv6c_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
   if (warp == 0) tmem_dealloc(tm, 256);
 }
 
-// du[h][k] = sum over batch rows, fixed order
-__global__ void __launch_bounds__(64)
-wkv6c_du_reduce_kernel(const float* __restrict__ du_partial, float* __restrict__ du, int B, int H) {
-  const int hi = blockIdx.x, kc = threadIdx.x;
-  float s = 0.f;
-  for (int bi = 0; bi < B; ++bi) s += du_partial[((size_t)bi * H + hi) * HS + kc];
-  du[hi * HS + kc] = s;
-}
-
 }  // namespace w6c
 
 int launch_wkv6_chunked_fwd(const void* r, const void* k, const void* v, const void* w, const float* u,
                             const float* s0, int n_state, const int32_t* smap, void* y, float* sT,
-                            float* states, int B, int Tn, int H, int dtype, cudaStream_t st) {
+                            float* states, int* flags, int B, int Tn, int H, int dtype, cudaStream_t st) {
   using namespace w6c;
+  if (cuda_ok(cudaMemsetAsync(flags, 0, (size_t)B * H * sizeof(int), st))) return RWKVB200_E_CUDA;
   int* status = device_status_ptr();
   if (!status) { last_cuda_error_slot() = 99999; return RWKVB200_E_CUDA; }
   const int smem = (int)sizeof(FwdSmem) + 1024;
@@ -822,38 +823,71 @@ int launch_wkv6_chunked_fwd(const void* r, const void* k, const void* v, const v
   if (!e) e = make_row_tensor_map(&tm_v, v, B, Tn, H, esz);
   if (!e) e = make_row_tensor_map(&tm_w, w, B, Tn, H, esz);
   if (e) return e;
-  ProfScope prof("wkv6c_fwd_kernel", st);
-  RWKVB200_DISPATCH_DTYPE(dtype,
-    if (cuda_ok(cudaFuncSetAttribute(wkv6c_fwd_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)))
-      return RWKVB200_E_CUDA;
-    wkv6c_fwd_kernel<T><<<B * H, 256, smem, st>>>((const T*)r, (const T*)k, (const T*)v, (const T*)w, u, s0, n_state,
-                                                   smap, (T*)y, sT, states, tm_r, tm_k, tm_v, tm_w, Tn, H, status,
-                                                   debug_stamp_buffer()));
-  return check_launch();
+  {
+    ProfScope prof("wkv6c_fwd_kernel", st);
+    RWKVB200_DISPATCH_DTYPE(dtype,
+      if (cuda_ok(cudaFuncSetAttribute(wkv6c_fwd_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)))
+        return RWKVB200_E_CUDA;
+      wkv6c_fwd_kernel<T><<<B * H, 256, smem, st>>>((const T*)r, (const T*)k, (const T*)v, (const T*)w, u, s0, n_state,
+                                                     smap, (T*)y, sT, states, flags, tm_r, tm_k, tm_v, tm_w, Tn, H,
+                                                     status, debug_stamp_buffer()));
+  }
+  e = check_launch();
+  if (e) return e;
+  // the marked units again, exactly: outputs, final state and (for the backward) the chunk-boundary states
+  const long long unit_floats = (long long)((Tn + L - 1) / L + 1) * HS * HS;
+  const UnitSel sel{flags, nullptr, nullptr, states ? unit_floats : 0};
+  return launch_wkv6_fwd(r, k, v, w, u, s0, n_state, smap, y, sT, states, B, Tn, H, dtype, st, &sel, L);
 }
 
 }  // namespace rwkvb200
 
 namespace rwkvb200 {
 
-size_t wkv6_chunked_bwd_workspace_bytes(int B, int Tn, int H) {
+// workspace of the backward: [chunk-boundary states | du rows, one per unit | du rows of the recurrent
+// fallback, four per unit | unit flags]; the forward fills the states and the flags
+namespace {
+struct W6Workspace { float* states; float* du_partial; float* du_partial_rec; int* flags; };
+inline size_t a256(size_t x) { return (x + 255) & ~size_t(255); }
+inline size_t w6_states_bytes(int B, int Tn, int H) {
   const size_t nt = (size_t)(Tn + w6c::L - 1) / w6c::L;
-  return (((size_t)B * H * (nt + 1) * HS * HS * sizeof(float) + 255) & ~size_t(255)) +
-         (((size_t)B * H * HS * sizeof(float) + 255) & ~size_t(255));
+  return a256((size_t)B * H * (nt + 1) * HS * HS * sizeof(float));
 }
+inline W6Workspace w6_carve(void* workspace, int B, int Tn, int H) {
+  char* p = reinterpret_cast<char*>(workspace);
+  W6Workspace w;
+  w.states = reinterpret_cast<float*>(p);
+  p += w6_states_bytes(B, Tn, H);
+  w.du_partial = reinterpret_cast<float*>(p);
+  p += a256((size_t)B * H * HS * sizeof(float));
+  w.du_partial_rec = reinterpret_cast<float*>(p);
+  p += a256((size_t)B * H * 4 * HS * sizeof(float));
+  w.flags = reinterpret_cast<int*>(p);
+  return w;
+}
+}  // namespace
+
+size_t wkv6_chunked_flags_bytes(int B, int H) { return a256((size_t)B * H * sizeof(int)); }
+
+size_t wkv6_chunked_bwd_workspace_bytes(int B, int Tn, int H) {
+  return w6_states_bytes(B, Tn, H) + a256((size_t)B * H * HS * sizeof(float)) +
+         a256((size_t)B * H * 4 * HS * sizeof(float)) + wkv6_chunked_flags_bytes(B, H);
+}
+
+int* wkv6_chunked_workspace_flags(void* workspace, int B, int Tn, int H) { return w6_carve(workspace, B, Tn, H).flags; }
 
 int launch_wkv6_chunked_bwd(const void* r, const void* k, const void* v, const void* w, const float* u,
                             const float* s0, int n_state, const int32_t* smap, const void* d_y, const float* d_sT,
                             void* dr, void* dk, void* dv, void* dw, float* du, float* d_s0, void* workspace,
                             int B, int Tn, int H, int dtype, bool kept, cudaStream_t st) {
   using namespace w6c;
-  const size_t nt = (size_t)(Tn + L - 1) / L;
-  float* states = reinterpret_cast<float*>(workspace);
-  float* du_partial = reinterpret_cast<float*>(
-      reinterpret_cast<char*>(workspace) + (((size_t)B * H * (nt + 1) * HS * HS * sizeof(float) + 255) & ~size_t(255)));
+  const W6Workspace ws = w6_carve(workspace, B, Tn, H);
+  float* states = ws.states;
+  float* du_partial = ws.du_partial;
   int e = RWKVB200_OK;
   if (!kept) {   // the workspace does not hold the chunk-boundary states yet: run the forward for them
-    e = launch_wkv6_chunked_fwd(r, k, v, w, u, s0, n_state, smap, nullptr, nullptr, states, B, Tn, H, dtype, st);
+    e = launch_wkv6_chunked_fwd(r, k, v, w, u, s0, n_state, smap, nullptr, nullptr, states, ws.flags, B, Tn, H, dtype,
+                                st);
     if (e) return e;
   }
   int* status = device_status_ptr();
@@ -879,9 +913,15 @@ int launch_wkv6_chunked_bwd(const void* r, const void* k, const void* v, const v
   }
   e = check_launch();
   if (e) return e;
-  ProfScope prof("wkv6c_du_reduce_kernel", st);
-  wkv6c_du_reduce_kernel<<<H, 64, 0, st>>>(du_partial, du, B, H);
-  return check_launch();
+  // the units the forward marked: gradients from the float32 recurrence, which restarts from the (exact)
+  // chunk-boundary states the fallback forward left in the workspace
+  {
+    const UnitSel sel{ws.flags, nullptr, nullptr, (long long)((Tn + L - 1) / L + 1) * HS * HS};
+    e = launch_wkv6_bwd_coarse(r, k, v, w, u, d_y, d_sT, states, dr, dk, dv, dw, ws.du_partial_rec, d_s0, B, Tn, H,
+                               dtype, st, &sel);
+    if (e) return e;
+  }
+  return launch_wkv6_du_reduce_mixed(du_partial, ws.du_partial_rec, ws.flags, du, B, H, st);
 }
 
 }  // namespace rwkvb200

@@ -38,15 +38,18 @@ def _wkv6_fwd(r: torch.Tensor, k: torch.Tensor, v: torch.Tensor, w: torch.Tensor
     sT = torch.empty(B, H, HEAD_SIZE, HEAD_SIZE, dtype=torch.float32, device=dev)
     n_state = 0 if s0 is None else s0.shape[0]
     with torch.cuda.device(dev):
-        # a training forward of the chunked path leaves the chunk-boundary states for the backward
+        # a training forward of the chunked path leaves the chunk-boundary states for the backward; an
+        # inference forward needs a few bytes per (batch, head) for the decay-range marks
         flags = algo | (_lib.ALGO_KEEP if keep else 0)
-        nws = lib.rwkvb200_wkv6_bwd_workspace_bytes(B, T, H, HEAD_SIZE, code, algo) if keep else 0
+        nws = lib.rwkvb200_wkv6_fwd_workspace_bytes(B, T, H, HEAD_SIZE, code, flags)
         kept = torch.empty(nws, dtype=torch.uint8, device=dev)
         rc = lib.rwkvb200_wkv6_fwd(r.data_ptr(), k.data_ptr(), v.data_ptr(), w.data_ptr(), u.data_ptr(),
                                    _lib.ptr(s0), n_state, _lib.ptr(state_map), y.data_ptr(), sT.data_ptr(),
-                                   kept.data_ptr() if keep else None, nws,
+                                   kept.data_ptr() if nws else None, nws,
                                    B, T, H, HEAD_SIZE, code, flags, _lib.stream_ptr(dev))
         _lib.check(rc, "wkv6_fwd")
+    if not keep:
+        kept = kept.new_empty(0)
     return y, sT, kept
 
 
@@ -57,6 +60,8 @@ def _(r, k, v, w, u, s0, state_map, algo, keep):
             r.new_empty((0,), dtype=torch.uint8))
 
 
+# `kept` (the forward's chunk-boundary states) also holds the backward's scratch rows; what the forward
+# left there is not changed, so the op declares no mutation (a second backward through the graph stays legal).
 @torch.library.custom_op("rwkv_ops_b200::wkv6_bwd", mutates_args=())
 def _wkv6_bwd(r: torch.Tensor, k: torch.Tensor, v: torch.Tensor, w: torch.Tensor, u: torch.Tensor,
               s0: Optional[torch.Tensor], state_map: Optional[torch.Tensor],
@@ -170,9 +175,13 @@ class RWKVKernelOperator:
                     state_map = torch.tensor(state_map, dtype=torch.int32)
                 assert state_map.dtype in (torch.int32, torch.int64), "state_map must be int32 or int64"
                 assert state_map.numel() == B, "state_map must have one entry per batch row"
-                host = state_map.detach().cpu()
-                assert bool((host >= 0).all()) and bool((host < n_state).all()), (
-                    f"state_map values must lie in [0, {n_state})")
+                if not state_map.is_cuda:
+                    # a host-side map (list, CPU tensor) is range-checked here, where the reference
+                    # device-asserts (rwkv6_kernel/torch_kernel/wkv6_cuda.cu:81); a map that already lives
+                    # on the device is not read back (that would stall the stream on every call): the
+                    # kernels clamp its entries to the table instead of trapping
+                    assert bool((state_map >= 0).all()) and bool((state_map < n_state).all()), (
+                        f"state_map values must lie in [0, {n_state})")
                 smap = state_map.to(device=dev, dtype=torch.int32).contiguous().view(B)
             s0 = init_state.to(torch.float32).contiguous()
         else:

@@ -121,6 +121,8 @@ def _(r, w, k, v, a, b, h0, head_first, algo):
 
 
 # `kept` also serves as scratch for the backward kernels; the tiles the forward left in it are not changed.
+# (Not declared in mutates_args: autograd would then refuse a second backward through the same graph, and
+# nothing that anyone reads from `kept` ever changes.)
 @torch.library.custom_op("rwkv_ops_b200::rwkv7_bwd_kept", mutates_args=())
 def _rwkv7_bwd_kept(r: torch.Tensor, w: torch.Tensor, k: torch.Tensor, v: torch.Tensor, a: torch.Tensor,
                     b: torch.Tensor, h0: Optional[torch.Tensor], d_o: torch.Tensor, d_ht: Optional[torch.Tensor],

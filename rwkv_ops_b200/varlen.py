@@ -134,6 +134,12 @@ def _backward(ctx, d_o, d_ht, d_kept):
 torch.library.register_autograd("rwkv_ops_b200::rwkv7_fwd_varlen", _backward, setup_context=_setup_ctx)
 
 
+def _token_args(r, w, k, v, a, b):
+    """The six token tensors in ``r``'s dtype, contiguous: the kernels read all of them as one element type
+    (``generalized_delta_rule`` casts in the same way; under mixed precision ``w`` often arrives as float32)."""
+    return [x.to(r.dtype).contiguous() for x in (r, w, k, v, a, b)]
+
+
 def generalized_delta_rule_varlen(r, w, k, v, a, b, cu_seqlens, initial_state=None, output_final_state=True):
     """``generalized_delta_rule`` over sequences packed end to end (see the module docstring).
 
@@ -174,7 +180,7 @@ def generalized_delta_rule_varlen(r, w, k, v, a, b, cu_seqlens, initial_state=No
             states.append(si)
         o, ht = torch.cat(outs, dim=1), torch.cat(states, dim=0)
     else:
-        args = [x.contiguous() for x in (r, w, k, v, a, b)]
+        args = _token_args(r, w, k, v, a, b)
         needs_grad = torch.is_grad_enabled() and (
             any(x.requires_grad for x in args) or (h0 is not None and h0.requires_grad))
         o, ht, _ = _fwd_varlen(*args, start, lens, max_len, h0, needs_grad)

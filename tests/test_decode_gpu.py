@@ -97,3 +97,45 @@ def test_decode_rejects_bad_arguments():
     x = torch.zeros(2, 2, 2, 64, device="cuda")
     with pytest.raises(ValueError):
         dec.step(x, x, x, x, x, x)
+
+
+@pytest.mark.parametrize("state_dtype,tol_o,tol_s", [(torch.float32, 2e-2, 1e-4), (torch.bfloat16, 2e-2, 2e-2)])
+def test_cfg3_full_shape_1024_chained_steps(state_dtype, tol_o, tol_s):
+    """Benchmark configuration 3 at its own shape: B=256, H=64, bf16 tokens, 1024 consecutive steps with the
+    state fed back (fresh token vectors every step).  Sampled (batch, head) units are checked against the
+    oracle run over the unit's 1024-token sequence; the error after 1024 steps is the drift of the chain.
+    The float32 state also goes through the T == 1 operator (rwkvb200_rwkv7_step) on a ping-pong pair."""
+    import rwkv_ops_b200 as ro
+    from oracle import generalized_delta_rule as oracle_gdr
+    B, H, STEPS = 256, 64, 1024
+    units = [(0, 0), (100, 37), (255, 63)]
+    gen = torch.Generator(device="cuda").manual_seed(1003)
+    s0 = 0.1 * torch.randn(B, H, 64, 64, device="cuda", generator=gen)
+    dec = ro.Rwkv7DecodeState(B, H, state_dtype=state_dtype, initial_state=s0)
+    s_op = s0.clone() if state_dtype == torch.float32 else None
+    kept_in = {u: [] for u in units}
+    kept_out = {u: [] for u in units}
+    for t in range(STEPS):
+        d = rwkv7_inputs(B, 1, H, dtype=torch.bfloat16, seed=5000 + t, device="cuda")
+        x = [d[n] for n in "rwkvab"]
+        o = dec.step(*x)
+        if s_op is not None and t < 64:      # the operator path, bit for bit, over the first steps
+            o2, s_op = ro.generalized_delta_rule(*x, initial_state=s_op)
+            assert torch.equal(o, o2)
+        for (b, h) in units:
+            kept_in[(b, h)].append(torch.stack([t_[b, 0, h] for t_ in x]).cpu())
+            kept_out[(b, h)].append(o[b, 0, h].cpu())
+    if s_op is not None:
+        pass
+    final = dec.final_state()
+    drift = {}
+    for (b, h) in units:
+        seq = torch.stack(kept_in[(b, h)], dim=1)            # [6, STEPS, 64]
+        sub = [seq[i][None, :, None, :] for i in range(6)]
+        o_ref, s_ref = oracle_gdr(*sub, initial_state=s0[b:b + 1, h:h + 1].cpu())
+        o_got = torch.stack(kept_out[(b, h)])[None, :, None, :]
+        drift[(b, h)] = (rel_l2(o_got, o_ref), rel_l2(o_got[:, -64:], o_ref[:, -64:]),
+                         rel_l2(final[b:b + 1, h:h + 1], s_ref))
+    print("cfg3 drift (o all steps, o last 64 steps, final state):", state_dtype, drift)
+    for e_all, e_tail, e_s in drift.values():
+        assert e_all < tol_o and e_tail < tol_o and e_s < tol_s

@@ -2,7 +2,7 @@
 import pytest
 import torch
 
-from rwkv_ops_b200.varlen import _seq_arrays, generalized_delta_rule_varlen
+from rwkv_ops_b200.varlen import _seq_arrays, _token_args, generalized_delta_rule_varlen
 from rwkv_ops_b200 import _lib
 
 
@@ -31,3 +31,12 @@ def test_varlen_needs_cuda_tensors():
     x = torch.zeros(1, 4, 2, 64, dtype=torch.bfloat16)
     with pytest.raises(_lib.RwkvB200Error):
         generalized_delta_rule_varlen(x, x, x, x, x, x, [0, 4])
+
+
+def test_token_tensors_are_cast_to_the_dtype_of_r():
+    """Mixed dtypes (w in float32 beside bfloat16 r) must not reach the kernels, which read one element type."""
+    r = torch.zeros(1, 4, 2, 64, dtype=torch.bfloat16)
+    w = torch.full((1, 4, 2, 64), -0.5, dtype=torch.float32)
+    out = _token_args(r, w, r, r, r.transpose(1, 2).contiguous().transpose(1, 2), r)
+    assert all(t.dtype == torch.bfloat16 and t.is_contiguous() for t in out)
+    assert torch.equal(out[1], w.to(torch.bfloat16))

@@ -134,3 +134,26 @@ def test_full_size_sampled_units():
         gr = wkv6_manual_backward(*sub, s0b, d["d_y"][b:b + 1, :, sl].cpu(), d["d_state"][b:b + 1, h:h + 1].cpu(), 64)
         for n, gn in zip("rkvw", gr[:4]):
             assert rel_l2(g[n].grad[b:b + 1, :, sl], gn) < 1e-4, n
+
+
+def test_full_size_du_and_init_state_gradient():
+    """Configuration 4 at full size: the two gradients that sum over batch rows.  du of one head (all 16
+    batch rows and 4096 tokens) and the gradient of the initial-state table for that head (every table row is
+    the start of several batch rows through state_map) against the float64 reverse recurrence."""
+    B, T, H = 16, 4096, 32
+    d = wkv6_inputs(B, T, H, seed=1004, device="cuda", n_state=4, with_grads=True)
+    g = {n: d[n].requires_grad_(True) for n in "rkvwu"}
+    s0 = d["init_state"].requires_grad_(True)
+    y, s = ro.RWKV6_OP(64, T)(g["r"], g["k"], g["v"], g["w"], g["u"], with_state=True, init_state=s0,
+                              state_map=d["state_map"])
+    ((y * d["d_y"]).sum() + (s * d["d_state"]).sum()).backward()
+    smap = d["state_map"].cpu().long()
+    assert len(set(smap.tolist())) < B      # table rows are shared
+    for h in (0, 19):
+        sl = slice(h * 64, (h + 1) * 64)
+        sub = [g[n].detach()[:, :, sl].cpu() for n in "rkvw"] + [g["u"].detach()[h:h + 1].cpu()]
+        s0b = s0.detach()[:, h:h + 1].cpu()[smap]                      # [B,1,64,64]
+        gr = wkv6_manual_backward(*sub, s0b, d["d_y"][:, :, sl].cpu(), d["d_state"][:, h:h + 1].cpu(), 64)
+        assert rel_l2(g["u"].grad[h:h + 1], gr[4]) < 1e-4
+        ds0_ref = torch.zeros(4, 1, 64, 64, dtype=gr[5].dtype).index_add_(0, smap, gr[5])
+        assert rel_l2(s0.grad[:, h:h + 1], ds0_ref) < 1e-4
