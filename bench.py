@@ -290,6 +290,44 @@ def sub_cfg2_sharded(dev, world, rank, max_over_ranks, barrier):
     return out
 
 
+def sub_cfg2_sequence_parallel(dev, world, rank, max_over_ranks, barrier):
+    """Configuration 2 with every sequence's 8192 tokens split over the ranks (rank g holds tokens
+    [g*T/N, (g+1)*T/N) of all 16 sequences); the boundary states and their gradients travel between
+    neighbours by NCCL point-to-point.  value = tokens of all 16 sequences / max over ranks of the step."""
+    import torch.distributed as dist
+    from rwkv_ops_b200.sequence_parallel import generalized_delta_rule_sp
+    from rwkv_ops_b200.workloads import rwkv7_inputs
+    B, T, H = 16, 8192, 64
+    if T % (64 * world):
+        return {"skipped": f"{T} tokens do not split into whole chunks over {world} ranks"}
+    Tl = T // world
+    d = rwkv7_inputs(B, Tl, H, dtype=torch.bfloat16, seed=1002 + 31 * rank, device=dev, with_state=True,
+                     with_grads=True)
+    leaves = {n: d[n].requires_grad_(True) for n in "rwkvab"}
+    h0 = d["initial_state"].requires_grad_(True) if rank == 0 else None
+    d_state = d["d_state"] if rank == world - 1 else None
+
+    def fn():
+        o, s = generalized_delta_rule_sp(*[leaves[n] for n in "rwkvab"], initial_state=h0)
+        if d_state is not None:
+            torch.autograd.backward([o, s], [d["d_out"], d_state])
+        else:
+            torch.autograd.backward([o], [d["d_out"]])
+        for n in "rwkvab":
+            leaves[n].grad = None
+        if h0 is not None:
+            h0.grad = None
+
+    ms = _timed(fn, 5, 3, barrier, max_over_ranks)
+    out = {"workload": "rwkv7_fwd_bwd_bf16_B16_T8192_H64_K64_h0_sequence_parallel", "scaling": "strong",
+           "sharding": f"{Tl} of 8192 tokens of every sequence per rank, {world} rank(s), boundary states by "
+                       "NCCL send/recv into the receiver's own memory",
+           "ms_per_step": ms, "value": B * T / (ms / 1e3), "unit": "tokens/s"}
+    del d, leaves
+    torch.cuda.empty_cache()
+    return out
+
+
 def run_ours(args, wl):
     import torch.distributed as dist
     import rwkv_ops_b200 as ro
@@ -409,6 +447,8 @@ def run_ours(args, wl):
         extra["decode"] = sub_decode(dev, world, max_over_ranks, barrier, pk)
         extra["wkv6"] = sub_wkv6(dev, world, max_over_ranks, barrier, pk)
         extra["strong_scaling"] = sub_cfg2_sharded(dev, world, rank, max_over_ranks, barrier)
+        if world > 1:
+            extra["sequence_parallel"] = sub_cfg2_sequence_parallel(dev, world, rank, max_over_ranks, barrier)
 
     # ---- end to end: host buffers in, host buffers out, through the public API.
     # Every step copies all of its inputs from pinned host memory and all of its results back to

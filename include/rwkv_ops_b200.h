@@ -64,7 +64,19 @@ enum {
    * needs in the workspace (size it with the flag set).  Backward: the workspace still holds what that
    * forward call left there, so skip the recomputation.  Without the flag the backward recomputes the
    * forward from the inputs, as the reference does (rwkv_ops/rwkv7_kernel/torch_op.py:163-183). */
-  RWKVB200_ALGO_KEEP = 0x100
+  RWKVB200_ALGO_KEEP = 0x100,
+  /* Flags, OR-ed into algo (chunked path of rwkvb200_rwkv7_fwd / _bwd only): run part of the call.  None set
+   * = the whole call.  The parts of one call must run in order on the same workspace with the same
+   * arguments.  Forward: PREPARE does everything that does not depend on the initial state (h0, o and ht
+   * are not touched and o may be NULL), SCAN walks the state through the chunks and writes o and ht.
+   * Backward: PREPARE does what does not depend on d_ht, SCAN carries the state gradient back through the
+   * chunks and writes d_h0, FINISH writes the six token gradients.  A caller that splits one sequence over
+   * several GPUs runs PREPARE / FINISH on all of them at once and only the SCAN parts one GPU after the
+   * other, passing ht (forward) and d_h0 (backward) to the neighbour.  No counterpart in the reference,
+   * which has no multi-device mode (README.md:179). */
+  RWKVB200_ALGO_PHASE_PREPARE = 0x1000,
+  RWKVB200_ALGO_PHASE_SCAN = 0x2000,
+  RWKVB200_ALGO_PHASE_FINISH = 0x4000
 };
 
 int rwkvb200_abi_version(void);
@@ -221,8 +233,8 @@ int rwkvb200_rwkv7_bwd_static(const void* r, const void* w, const void* k, const
  *   workspace      rwkvb200_wkv6_fwd_workspace_bytes(...) bytes: with KEEP the backward's workspace
  *                  (rwkvb200_wkv6_bwd_workspace_bytes, the two are equal), without it a few bytes per
  *                  (batch, head) for the chunked path and none for the recurrent one.
- * Decay range of the chunked path: its scaled operands are exact while the sum of exp(w) over any 32
- * consecutive tokens of a channel stays below 60 (always true for w <= 0.62).  A (batch, head) unit that
+ * Decay range of the chunked path: it holds the 1e-4 parity bar while the sum of exp(w) over the 32 tokens
+ * of a half chunk stays below 45 in every channel (always true for w <= 0.34).  A (batch, head) unit that
  * exceeds this is detected on the device and recomputed, forward and backward, by the float32 recurrence
  * inside the same call: results are exact for any w, such units just run at the recurrent path's speed.
  * ---------------------------------------------------------------------------------------- */

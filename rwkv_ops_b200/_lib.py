@@ -17,6 +17,7 @@ LIB_PATH = os.path.join(_PKG, "librwkv_ops_b200.so")
 F32, BF16, F16 = 0, 1, 2
 ALGO_AUTO, ALGO_RECURRENT, ALGO_CHUNKED = 0, 1, 2
 ALGO_KEEP = 0x100
+PHASE_PREPARE, PHASE_SCAN, PHASE_FINISH = 0x1000, 0x2000, 0x4000
 _DTYPE_CODE = {torch.float32: F32, torch.bfloat16: BF16, torch.float16: F16}
 
 # name -> (restype, argtypes); mirrors include/rwkv_ops_b200.h one to one

@@ -25,6 +25,15 @@ inline int resolve_r7_algo(int algo, int dtype) {
   return algo;
 }
 
+// phase bits of the algo argument (chunked path); none set = the whole call
+inline int phases_of(int algo) {
+  int p = 0;
+  if (algo & RWKVB200_ALGO_PHASE_PREPARE) p |= PHASE_PREPARE;
+  if (algo & RWKVB200_ALGO_PHASE_SCAN) p |= PHASE_SCAN;
+  if (algo & RWKVB200_ALGO_PHASE_FINISH) p |= PHASE_FINISH;
+  return p ? p : (int)PHASE_ALL;
+}
+
 // wkv6: AUTO = chunked tensor-core path (its split-precision operands keep float32-grade accuracy).
 inline int resolve_w6_algo(int algo) {
   algo &= 0xff;
@@ -105,13 +114,15 @@ int rwkvb200_rwkv7_fwd(const void* r, const void* w, const void* k, const void* 
                        void* stream) {
   int e = check_common(B, T, H, head_size, dtype);
   if (e) return e;
-  if (!r || !w || !k || !v || !a || !b || !o) return RWKVB200_E_NULL;
+  const int phases = phases_of(algo);
+  if (!r || !w || !k || !v || !a || !b || (!o && (phases & PHASE_SCAN))) return RWKVB200_E_NULL;
   if (n_state != 0 && n_state != 1 && n_state != B) return RWKVB200_E_SHAPE;
   if (n_state != 0 && !h0) return RWKVB200_E_NULL;
   const void* ps[] = {r, w, k, v, a, b, h0, o, ht, workspace};
   for (const void* p : ps) if (p && !aligned16(p)) return RWKVB200_E_ALIGN;
   const size_t need = rwkvb200_rwkv7_fwd_workspace_bytes(B, T, H, head_size, dtype, algo);
   if (workspace_bytes < need || (need && !workspace)) return RWKVB200_E_WORKSPACE;
+  if (phases != PHASE_ALL && resolve_r7_algo(algo, dtype) != RWKVB200_ALGO_CHUNKED) return RWKVB200_E_UNSUPPORTED;
   switch (resolve_r7_algo(algo, dtype)) {
     case RWKVB200_ALGO_RECURRENT:
       return launch_rwkv7_rec_fwd(r, w, k, v, a, b, n_state ? h0 : nullptr, n_state, o, ht, nullptr, R7_CKPT,
@@ -119,7 +130,8 @@ int rwkvb200_rwkv7_fwd(const void* r, const void* w, const void* k, const void* 
     case RWKVB200_ALGO_CHUNKED:
       if (dtype != RWKVB200_BF16) return RWKVB200_E_UNSUPPORTED;
       return launch_rwkv7_chunked_fwd(r, w, k, v, a, b, n_state ? h0 : nullptr, n_state, o, ht, workspace,
-                                      B, T, H, head_first, (algo & RWKVB200_ALGO_KEEP) != 0, (cudaStream_t)stream);
+                                      B, T, H, head_first, (algo & RWKVB200_ALGO_KEEP) != 0, (cudaStream_t)stream,
+                                      nullptr, nullptr, 0, false, phases);
     default:
       return RWKVB200_E_UNSUPPORTED;
   }
@@ -152,6 +164,8 @@ int rwkvb200_rwkv7_bwd(const void* r, const void* w, const void* k, const void* 
   const size_t need = rwkvb200_rwkv7_bwd_workspace_bytes(B, T, H, head_size, dtype, algo);
   if (workspace_bytes < need || (need && !workspace)) return RWKVB200_E_WORKSPACE;
   cudaStream_t st = (cudaStream_t)stream;
+  if (phases_of(algo) != PHASE_ALL && resolve_r7_algo(algo, dtype) != RWKVB200_ALGO_CHUNKED)
+    return RWKVB200_E_UNSUPPORTED;
   switch (resolve_r7_algo(algo, dtype)) {
     case RWKVB200_ALGO_RECURRENT: {
       float* ckpt = reinterpret_cast<float*>(workspace);
@@ -165,7 +179,8 @@ int rwkvb200_rwkv7_bwd(const void* r, const void* w, const void* k, const void* 
       if (dtype != RWKVB200_BF16) return RWKVB200_E_UNSUPPORTED;
       return launch_rwkv7_chunked_bwd(r, w, k, v, a, b, n_state ? h0 : nullptr, n_state, d_o, d_ht,
                                       dr, dw, dk, dv, da, db, d_h0, workspace, B, T, H, head_first,
-                                      (algo & RWKVB200_ALGO_KEEP) != 0, st);
+                                      (algo & RWKVB200_ALGO_KEEP) != 0, st, nullptr, nullptr, 0, false,
+                                      phases_of(algo));
     default:
       return RWKVB200_E_UNSUPPORTED;
   }

@@ -158,6 +158,14 @@ inline Workspace carve(void* ws, int B, int T, int H, int tiles_per_chunk) {
 
 }  // namespace r7c
 
+// Phases of a forward / backward call (bit mask).  A whole call runs all of them in order; a caller that splits
+// a sequence over several GPUs runs the state-independent phase on every GPU at once and only the scans one GPU
+// after the other (the workspace carries everything from one phase to the next).
+//   forward:  PREPARE = intra-chunk kernel;            SCAN = state scan over the chunks (+ exact fallback)
+//   backward: PREPARE = (forward recomputation and) the state-independent products of the reverse scan;
+//             SCAN = reverse scan (gradient of the state);   FINISH = token gradients (+ exact fallback)
+enum Phase { PHASE_PREPARE = 1, PHASE_SCAN = 2, PHASE_FINISH = 4, PHASE_ALL = 7 };
+
 // Backward of the chunked path; `workspace` must hold fwd_workspace_bytes(B, T, H, ALL_TILES).
 // Packed variable-length batches: seq_start / seq_len are device arrays of B entries, Tn the longest length
 // and T_total the number of tokens in the one batch row; dense batches pass nullptr, nullptr, 0.
@@ -167,13 +175,13 @@ int launch_rwkv7_chunked_bwd(const void* r, const void* w, const void* k, const 
                              void* dr, void* dw, void* dk, void* dv, void* da, void* db, float* d_h0,
                              void* workspace, int B, int Tn, int H, int head_first, bool kept, cudaStream_t st,
                              const int* seq_start = nullptr, const int* seq_len = nullptr, int T_total = 0,
-                             bool fused = false);
+                             bool fused = false, int phases = PHASE_ALL);
 
 int launch_rwkv7_chunked_fwd(const void* r, const void* w, const void* k, const void* v, const void* a, const void* b,
                              const float* h0, int n_state, void* o, float* ht, void* workspace,
                              int B, int Tn, int H, int head_first, bool keep_for_bwd, cudaStream_t st,
                              const int* seq_start = nullptr, const int* seq_len = nullptr, int T_total = 0,
-                             bool fused = false);
+                             bool fused = false, int phases = PHASE_ALL);
 
 // Fused producers, backward: dw, da, db (in place in the three buffers) -> dp, du, dq.
 int launch_rwkv7_producer_bwd(const void* p, const void* u, const void* q, void* dw_dp, void* da_du, void* db_dq,

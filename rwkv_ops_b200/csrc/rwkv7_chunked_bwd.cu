@@ -718,12 +718,12 @@ int launch_rwkv7_chunked_bwd(const void* r, const void* w, const void* k, const 
                              const float* h0, int n_state, const void* d_o, const float* d_ht,
                              void* dr, void* dw, void* dk, void* dv, void* da, void* db, float* d_h0,
                              void* workspace, int B, int Tn, int H, int head_first, bool kept, cudaStream_t st,
-                             const int* seq_start, const int* seq_len, int T_total, bool fused) {
+                             const int* seq_start, const int* seq_len, int T_total, bool fused, int phases) {
   using namespace r7c;
   if (fused && (seq_start || head_first)) return RWKVB200_E_UNSUPPORTED;
   typedef __nv_bfloat16 bf16;
   int e = RWKVB200_OK;
-  if (!kept) {   // the workspace does not hold a forward pass yet: recompute it from the inputs
+  if (!kept && (phases & PHASE_PREPARE)) {   // the workspace does not hold a forward pass yet: recompute it from the inputs
     e = launch_rwkv7_chunked_fwd(r, w, k, v, a, b, h0, n_state, nullptr, nullptr, workspace, B, Tn, H, head_first,
                                  true, st, seq_start, seq_len, T_total, fused);
     if (e) return e;
@@ -747,7 +747,7 @@ int launch_rwkv7_chunked_bwd(const void* r, const void* w, const void* k, const 
   TokLayout lay(mapT, H, head_first);
   // every kernel exists for dense batches and for packed variable-length ones
 #define R7C_DISPATCH_PACKED(...) do { if (seq_start) { constexpr bool P = true; __VA_ARGS__; } else { constexpr bool P = false; __VA_ARGS__; } } while (0)
-  {
+  if (phases & PHASE_PREPARE) {
     const int smem = (int)sizeof(PreSmem) + 1024;
     ProfScope prof("r7c_bwd_pre_kernel", st);
     R7C_DISPATCH_PACKED(
@@ -757,7 +757,7 @@ int launch_rwkv7_chunked_bwd(const void* r, const void* w, const void* k, const 
   }
   e = check_launch();
   if (e) return e;
-  {
+  if (phases & PHASE_SCAN) {
     const int smem = (int)sizeof(BScanSmem) + 1024;
     ProfScope prof("r7c_bwd_scan_kernel", st);
     R7C_DISPATCH_PACKED(
@@ -767,7 +767,7 @@ int launch_rwkv7_chunked_bwd(const void* r, const void* w, const void* k, const 
                                                        status));
   }
   e = check_launch();
-  if (e) return e;
+  if (e || !(phases & PHASE_FINISH)) return e;
   {
     const int smem = (int)sizeof(FinalSmem) + 1024;
     ProfScope prof("r7c_bwd_final_kernel", st);

@@ -797,7 +797,7 @@ r7c_scan_fwd_kernel(const __grid_constant__ CUtensorMap tmap_v, const unsigned c
 int launch_rwkv7_chunked_fwd(const void* r, const void* w, const void* k, const void* v, const void* a, const void* b,
                              const float* h0, int n_state, void* o, float* ht, void* workspace,
                              int B, int Tn, int H, int head_first, bool keep_for_bwd, cudaStream_t st,
-                             const int* seq_start, const int* seq_len, int T_total, bool fused) {
+                             const int* seq_start, const int* seq_len, int T_total, bool fused, int phases) {
   using namespace r7c;
   typedef __nv_bfloat16 bf16;
   if (fused && seq_start) return RWKVB200_E_UNSUPPORTED;
@@ -820,8 +820,8 @@ int launch_rwkv7_chunked_fwd(const void* r, const void* w, const void* k, const 
   const int tpc = keep_for_bwd ? (int)ALL_TILES : (int)FWD_TILES;
   Workspace ws = carve(workspace, B, Tn, H, tpc);
   TokLayout lay(mapT, H, head_first);
-  if (cuda_ok(cudaMemsetAsync(ws.flags, 0, (size_t)B * H * sizeof(int), st))) return RWKVB200_E_CUDA;
-  {
+  if (phases & PHASE_PREPARE) {
+    if (cuda_ok(cudaMemsetAsync(ws.flags, 0, (size_t)B * H * sizeof(int), st))) return RWKVB200_E_CUDA;
     const int smem = (int)sizeof(IntraSmem) + 1024;
     ProfScope prof("r7c_intra_fwd_kernel", st);
     const int n_ch = B * H * NT;
@@ -844,7 +844,7 @@ int launch_rwkv7_chunked_fwd(const void* r, const void* w, const void* k, const 
 #undef R7C_LAUNCH_INTRA
   }
   e = check_launch();
-  if (e) return e;
+  if (e || !(phases & PHASE_SCAN)) return e;
   {
     int dev = 0, sms = 0;
     if (cuda_ok(cudaGetDevice(&dev)) || cuda_ok(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)))

@@ -100,12 +100,14 @@ def _w_wkv6(kind, shape, gen):
         w = -torch.exp(-0.5 + 0.5 * n)
         w[1] = 1.0 + 0.3 * n[1]
         return w
-    if kind == "edge":
+    if kind == "edge":                # every channel just inside the limit of the chunked path (32 x 1.35 < 45)
+        return torch.log(1.3 + 0.05 * torch.rand(shape, generator=gen))
+    if kind == "beyond_edge":         # and just outside it
         return torch.log(1.75 + 0.05 * torch.rand(shape, generator=gen))
     raise ValueError(kind)
 
 
-@pytest.mark.parametrize("kind", ["normal", "fast", "one_row_fast", "edge"])
+@pytest.mark.parametrize("kind", ["normal", "fast", "one_row_fast", "edge", "beyond_edge"])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("T", [100, 193])
 def test_wkv6_decay_range(kind, dtype, T):

@@ -22,7 +22,7 @@ def _free_port():
     return p
 
 
-def _worker(rank, world, port, groups, with_state, out):
+def _worker(rank, world, port, groups, with_state, out, mid_loss=False):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
@@ -37,6 +37,8 @@ def _worker(rank, world, port, groups, with_state, out):
     loss = (o * d["d_out"][:, sl]).sum()
     if rank == world - 1:
         loss = loss + (s * d["d_state"]).sum()
+    elif mid_loss:      # a loss on the boundary state of a rank that is not the last one
+        loss = loss + (s * (0.5 + rank) * d["d_state"]).sum()
     loss.backward()
     res = {"o": o.detach(), "s": s.detach(), **{f"d{n}": loc[n].grad for n in "rwkvab"}}
     if with_state and rank == 0:
@@ -65,3 +67,28 @@ def test_chain_matches_single_process(tmp_path, world, groups, with_state):
             assert rel_l2(res["s"], s) < 1e-5
         if with_state and rank == 0:
             assert rel_l2(res["dh0"], h0.grad) < 1e-4
+
+
+def test_loss_on_an_inner_boundary_state_is_differentiated(tmp_path):
+    """The state a rank returns is the state at the end of its slice; a loss on it (on a rank that is not the
+    last) must reach every token before that boundary, on this rank and on the ranks to its left."""
+    world = 3
+    port = _free_port()
+    mp.spawn(_worker, args=(world, port, 1, True, str(tmp_path), True), nprocs=world, join=True)
+    B, T, H = 3, 12 * world, 2
+    d = rwkv7_inputs(B, T, H, seed=42, with_state=True, with_grads=True)
+    full = {n: d[n].clone().requires_grad_(True) for n in "rwkvab"}
+    h0 = d["initial_state"].clone().requires_grad_(True)
+    o, s = oracle_gdr(*[full[n] for n in "rwkvab"], initial_state=h0)
+    loss = (o * d["d_out"]).sum() + (s * d["d_state"]).sum()
+    for rank in range(world - 1):
+        end = (rank + 1) * T // world
+        _, s_mid = oracle_gdr(*[full[n][:, :end] for n in "rwkvab"], initial_state=h0)
+        loss = loss + (s_mid * (0.5 + rank) * d["d_state"]).sum()
+    loss.backward()
+    for rank in range(world):
+        res = torch.load(os.path.join(str(tmp_path), f"rank{rank}.pt"))
+        sl = slice(rank * T // world, (rank + 1) * T // world)
+        for n in "rwkvab":
+            assert rel_l2(res[f"d{n}"], full[n].grad[:, sl]) < 1e-4, (rank, n)
+    assert rel_l2(torch.load(os.path.join(str(tmp_path), "rank0.pt"))["dh0"], h0.grad) < 1e-4

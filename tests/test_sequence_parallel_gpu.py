@@ -1,5 +1,7 @@
-"""Sequence-parallel mode on real GPUs (NCCL point-to-point): two ranks, each with half of every
-sequence, against one GPU running the whole sequence.  Skipped on a single-GPU box."""
+"""Sequence-parallel mode on real GPUs.  The phases of the local operator (state-independent work, scans,
+token gradients) are checked on one GPU against the whole call and the oracle; the two-rank run (NCCL
+point-to-point, each rank with half of every sequence) is checked against the CPU oracle run over the whole
+sequence, and is skipped on a single-GPU box."""
 import os
 import socket
 
@@ -37,18 +39,23 @@ def _worker(rank, world, port, out):
     dist.destroy_process_group()
 
 
-def test_two_gpu_chain_matches_one_gpu(tmp_path):
+def _oracle_full(B, T, H):
+    from oracle import generalized_delta_rule as oracle_gdr
+    d = rwkv7_inputs(B, T, H, dtype=torch.bfloat16, seed=43, with_state=True, with_grads=True)
+    full = {n: d[n].float().clone().requires_grad_(True) for n in "rwkvab"}
+    h0 = d["initial_state"].clone().requires_grad_(True)
+    o, s = oracle_gdr(*[full[n] for n in "rwkvab"], initial_state=h0)
+    ((o * d["d_out"].float()).sum() + (s * d["d_state"]).sum()).backward()
+    return d, full, h0, o, s
+
+
+def test_two_gpu_chain_matches_the_oracle(tmp_path):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
-    import rwkv_ops_b200 as ro
     s_ = socket.socket(); s_.bind(("127.0.0.1", 0)); port = s_.getsockname()[1]; s_.close()
     mp.spawn(_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
     B, T, H = 4, 512, 4
-    d = rwkv7_inputs(B, T, H, dtype=torch.bfloat16, seed=43, with_state=True, with_grads=True)
-    full = {n: d[n].cuda().requires_grad_(True) for n in "rwkvab"}
-    h0 = d["initial_state"].cuda().requires_grad_(True)
-    o, s = ro.generalized_delta_rule(*[full[n] for n in "rwkvab"], initial_state=h0)
-    torch.autograd.backward([o, s], [d["d_out"].cuda(), d["d_state"].cuda()])
+    d, full, h0, o, s = _oracle_full(B, T, H)
     for rank in range(2):
         res = torch.load(os.path.join(str(tmp_path), f"rank{rank}.pt"))
         sl = slice(rank * T // 2, (rank + 1) * T // 2)
@@ -57,3 +64,42 @@ def test_two_gpu_chain_matches_one_gpu(tmp_path):
             assert rel_l2(res[f"d{n}"], full[n].grad[:, sl]) < 2e-2, (rank, n)
     assert rel_l2(res["s"], s) < 2e-2
     assert rel_l2(torch.load(os.path.join(str(tmp_path), "rank0.pt"))["dh0"], h0.grad) < 2e-2
+
+
+def test_phases_on_one_gpu_chain_two_halves():
+    """The phased operator on one GPU, playing both ranks of a two-way split in the order a real run
+    interleaves them (both `prepare` phases first, then the scans left to right; backward: both `prepare`
+    phases, the reverse scans right to left, then both `finish` phases), against the oracle run over the
+    whole sequence; and the phases of one slice against the unsplit call, bit for bit."""
+    import rwkv_ops_b200 as ro
+    from rwkv_ops_b200.sequence_parallel import ChunkedPhasedOp
+    B, T, H = 4, 512, 4
+    d, full, h0, o_ref, s_ref = _oracle_full(B, T, H)
+    op = ChunkedPhasedOp()
+    half = T // 2
+    tok = [[d[n][:, i * half:(i + 1) * half].cuda().contiguous() for n in "rwkvab"] for i in range(2)]
+    st = [op.prepare_fwd(*tok[i], False) for i in range(2)]
+    o0, h_mid = op.scan_fwd(st[0], d["initial_state"].cuda())
+    o1, h_end = op.scan_fwd(st[1], h_mid)
+    assert rel_l2(torch.cat([o0, o1], 1), o_ref) < 2e-2 and rel_l2(h_end, s_ref) < 2e-2
+    for i in range(2):
+        op.prepare_bwd(st[i], d["d_out"][:, i * half:(i + 1) * half].cuda())
+    d_mid = op.scan_bwd(st[1], d["d_state"].cuda()).clone()
+    d_h0 = op.scan_bwd(st[0], d_mid).clone()
+    grads = [op.finish_bwd(st[i]) for i in range(2)]
+    for j, n in enumerate("rwkvab"):
+        got = torch.cat([grads[0][j], grads[1][j]], 1)
+        assert rel_l2(got, full[n].grad) < 2e-2, n
+    assert rel_l2(d_h0, h0.grad) < 2e-2
+    # one slice, phase by phase, equals the unsplit operator call on that slice
+    g = {n: t.clone().requires_grad_(True) for n, t in zip("rwkvab", tok[1])}
+    hm = h_mid.clone().requires_grad_(True)
+    o_w, s_w = ro.generalized_delta_rule(*[g[n] for n in "rwkvab"], initial_state=hm)
+    torch.autograd.backward([o_w, s_w], [d["d_out"][:, half:].cuda(), d["d_state"].cuda()])
+    assert torch.equal(o_w, o1) and torch.equal(s_w, h_end)
+    for j, n in enumerate("rwkvab"):
+        assert torch.equal(g[n].grad, grads[1][j]), n
+    assert torch.equal(hm.grad, d_mid)
+    torch.cuda.synchronize()
+    from rwkv_ops_b200 import _lib
+    assert _lib.load().rwkvb200_device_status(1) == 0
