@@ -264,22 +264,10 @@ int rwkvb200_wkv6_bwd(const void* r, const void* k, const void* v, const void* w
  * rwkvb200_device_status: every wait inside a tensor-core kernel (on an mbarrier that a TMA copy or
  *   an MMA completes) gives up after a fixed number of polls, records a non-zero code in a status word
  *   on the device and lets the kernel finish; this call synchronises the device, returns the word
- *   (0 = no wait ever ran out) and clears it when reset != 0.
- * rwkvb200_tc_selftest: runs one building block on caller data so a test can compare with a plain
- *   matrix product.  mode 0: out[128][128] = [X;Y] [Z;W]^T (X..W are 64x64 bf16, row-major);
- *   mode 1: dumps the 128-lane x 64-column accumulator block holding X*Z (lower lane halves) and
- *   X^T*W (upper lane halves) to out[128][64]; mode 2: TMA-loads the 64-token tile (b,t0,h) of the
- *   [B,T,H,64] bf16 tensor tok, and writes its shared-memory image twice to img (2 x 4096 bf16), the
- *   second copy after a bulk load of the first; mode 3: out[128][64] = [X^T; Y^T] Z (128-wide
- *   transposed A operand); mode 4: lanes' lower halves of out[128][64] = X^T Z + Y^T W (contraction
- *   length 128 over two adjacent tiles).
+ *   (0 = no wait ever ran out) and clears it when reset != 0.  The Python layer reads it after every
+ *   operator call when RWKV_OPS_B200_CHECK_STATUS=1 is set (a debugging aid: it synchronises).
  * ---------------------------------------------------------------------------------------- */
 int rwkvb200_device_status(int reset);
-/* Developer aid: while device_buffer (>= 64 int64, caller-owned) is installed, one CTA of each
- * tensor-core kernel writes clock64() stamps at its phase boundaries into it; NULL switches it off. */
-void rwkvb200_debug_stamps(void* device_buffer);
-int rwkvb200_tc_selftest(int mode, const void* X, const void* Y, const void* Z, const void* W, float* out,
-                         const void* tok, int B, int T, int H, int b, int t0, int h, void* img, void* stream);
 
 /* ------------------------------------------------------------------------------------------
  * Per-kernel timing for benchmarks (no counterpart in the reference, which ships no timing code).

@@ -12,7 +12,10 @@ from ctypes import c_int, c_size_t, c_void_p, c_char_p
 import torch
 
 _PKG = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_PKG, "librwkv_ops_b200.so")
+# RWKV_OPS_B200_LIBRARY selects another build of the library (e.g. the developer build, to profile with its
+# phase stamps); default: the library built in-tree next to this file
+LIB_PATH = os.environ.get("RWKV_OPS_B200_LIBRARY") or os.path.join(_PKG, "librwkv_ops_b200.so")
+DEV_LIB_PATH = os.path.join(_PKG, "librwkv_ops_b200_dev.so")
 
 F32, BF16, F16 = 0, 1, 2
 ALGO_AUTO, ALGO_RECURRENT, ALGO_CHUNKED = 0, 1, 2
@@ -47,15 +50,20 @@ SIGNATURES = {
     "rwkvb200_wkv6_bwd_workspace_bytes": (c_size_t, [_I] * 6),
     "rwkvb200_wkv6_bwd": (c_int, [_P] * 5 + [_P, _I, _P, _P, _P] + [_P] * 6 + [_P, _Z] + [_I] * 6 + [_P]),
     "rwkvb200_device_status": (c_int, [_I]),
-    "rwkvb200_debug_stamps": (None, [_P]),
-    "rwkvb200_tc_selftest": (c_int, [_I] + [_P] * 6 + [_I] * 6 + [_P, _P]),
     "rwkvb200_profile_enable": (None, [_I]),
     "rwkvb200_profile_reset": (None, []),
     "rwkvb200_profile_count": (c_int, []),
     "rwkvb200_profile_get": (c_int, [_I, c_char_p, _I, ctypes.POINTER(ctypes.c_float), ctypes.POINTER(c_int)]),
 }
 
+# the developer build adds these (include/rwkv_ops_b200_devtools.h)
+DEV_SIGNATURES = {
+    "rwkvb200_debug_stamps": (None, [_P]),
+    "rwkvb200_tc_selftest": (c_int, [_I] + [_P] * 6 + [_I] * 6 + [_P, _P]),
+}
+
 _lib = None
+_dev_lib = None
 
 
 class RwkvB200Error(RuntimeError):
@@ -82,6 +90,35 @@ def load() -> ctypes.CDLL:
         raise RwkvB200Error(f"ABI version mismatch: library {got}, binding 1")
     _lib = lib
     return lib
+
+
+def load_dev() -> ctypes.CDLL:
+    """The developer build of the library (``python -m rwkv_ops_b200.build --dev``): every product entry point
+    plus the self-test and phase-stamp entry points.  Used by the unit tests of the tensor-core building blocks
+    only; it is a separate library with its own device state."""
+    global _dev_lib
+    if _dev_lib is not None:
+        return _dev_lib
+    if not os.path.exists(DEV_LIB_PATH):
+        raise RwkvB200Error(f"{DEV_LIB_PATH} not found. Build it with `python -m rwkv_ops_b200.build --dev`.")
+    lib = ctypes.CDLL(DEV_LIB_PATH)
+    for name, (res, args) in {**SIGNATURES, **DEV_SIGNATURES}.items():
+        fn = getattr(lib, name)
+        fn.restype = res
+        fn.argtypes = args
+    _dev_lib = lib
+    return lib
+
+
+def check_status(what: str) -> None:
+    """With ``RWKV_OPS_B200_CHECK_STATUS=1``: synchronise and raise if a bounded wait inside a tensor-core
+    kernel ran out during ``what`` (the kernel then wound down and its results are not valid).  Off by
+    default, because it synchronises the device after every operator call."""
+    if os.environ.get("RWKV_OPS_B200_CHECK_STATUS", "0") not in ("", "0"):
+        code = load().rwkvb200_device_status(1)
+        if code != 0:
+            raise RwkvB200Error(f"{what}: a bounded wait inside a tensor-core kernel ran out (code {code}); "
+                                "the results of this call are not valid")
 
 
 def strerror(code: int) -> str:

@@ -5,6 +5,10 @@
 The library is a plain C-ABI shared object (no torch, no pybind): one nvcc
 invocation per ``csrc/*.cu`` into ``csrc/_build/*.o`` and a link step.  A source is
 recompiled only when it or a header is newer than its object.
+
+A second library, ``librwkv_ops_b200_dev.so``, is the same sources with ``-DRWKVB200_DEVTOOLS``: it adds the
+building-block self-test and the phase-stamp instrumentation that the unit tests of the tensor-core
+primitives use (``include/rwkv_ops_b200_devtools.h``).  The product never loads it.
 """
 from __future__ import annotations
 
@@ -20,6 +24,7 @@ PKG = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG, "csrc")
 BUILD = os.path.join(CSRC, "_build")
 LIB = os.path.join(PKG, "librwkv_ops_b200.so")
+DEV_LIB = os.path.join(PKG, "librwkv_ops_b200_dev.so")
 INCLUDE = os.path.join(os.path.dirname(PKG), "include")
 
 NVCC_FLAGS = [
@@ -43,22 +48,26 @@ def _newest_header() -> float:
     return max(os.path.getmtime(h) for h in hs)
 
 
-def build(force: bool = False, verbose: bool = False) -> str:
-    os.makedirs(BUILD, exist_ok=True)
+def build(force: bool = False, verbose: bool = False, dev: bool = False) -> str:
+    """Build the product library, or with ``dev`` the developer build."""
+    build_dir = os.path.join(BUILD, "dev") if dev else BUILD
+    lib = DEV_LIB if dev else LIB
+    flags = NVCC_FLAGS + (["-DRWKVB200_DEVTOOLS"] if dev else [])
+    os.makedirs(build_dir, exist_ok=True)
     nvcc = _nvcc()
     srcs = sorted(glob.glob(os.path.join(CSRC, "*.cu")))
     hdr_m = _newest_header()
     jobs = []
     objs = []
     for s in srcs:
-        o = os.path.join(BUILD, os.path.basename(s)[:-3] + ".o")
+        o = os.path.join(build_dir, os.path.basename(s)[:-3] + ".o")
         objs.append(o)
         if force or not os.path.exists(o) or os.path.getmtime(o) < max(os.path.getmtime(s), hdr_m):
             jobs.append((s, o))
 
     def compile_one(job):
         s, o = job
-        cmd = [nvcc, *NVCC_FLAGS, "-I", INCLUDE, "-c", s, "-o", o]
+        cmd = [nvcc, *flags, "-I", INCLUDE, "-c", s, "-o", o]
         p = subprocess.run(cmd, capture_output=True, text=True)
         log = p.stdout + p.stderr
         with open(o[:-2] + ".ptxas.log", "w") as f:
@@ -71,18 +80,19 @@ def build(force: bool = False, verbose: bool = False) -> str:
 
     with ThreadPoolExecutor(max_workers=min(8, max(1, len(jobs)))) as ex:
         list(ex.map(compile_one, jobs))
-    if jobs or force or not os.path.exists(LIB):
-        cmd = [nvcc, "-shared", "-o", LIB, *objs, "-lcudart"]
+    if jobs or force or not os.path.exists(lib):
+        cmd = [nvcc, "-shared", "-o", lib, *objs, "-lcudart"]
         p = subprocess.run(cmd, capture_output=True, text=True)
         if p.returncode != 0:
             raise RuntimeError("link failed:\n" + p.stdout + p.stderr)
-    return LIB
+    return lib
 
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--force", action="store_true")
     ap.add_argument("--verbose", action="store_true")
+    ap.add_argument("--dev", action="store_true", help="build the developer library instead")
     a = ap.parse_args()
-    print(build(a.force, a.verbose))
+    print(build(a.force, a.verbose, a.dev))
     sys.exit(0)

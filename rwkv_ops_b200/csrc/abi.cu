@@ -9,9 +9,10 @@ namespace {
 
 inline size_t align256(size_t x) { return (x + 255) & ~size_t(255); }
 
-inline int check_common(int B, int T, int H, int head_size, int dtype) {
+// head sizes: 64 everywhere; 128 for the RWKV7 operator through the float32 recurrence (big_heads)
+inline int check_common(int B, int T, int H, int head_size, int dtype, bool big_heads = false) {
   if (B <= 0 || T <= 0 || H <= 0) return RWKVB200_E_SHAPE;
-  if (head_size != HS) return RWKVB200_E_UNSUPPORTED;
+  if (head_size != HS && !(big_heads && head_size == 128)) return RWKVB200_E_UNSUPPORTED;
   if (dtype != RWKVB200_F32 && dtype != RWKVB200_BF16 && dtype != RWKVB200_F16) return RWKVB200_E_DTYPE;
   return RWKVB200_OK;
 }
@@ -19,9 +20,10 @@ inline int check_common(int B, int T, int H, int head_size, int dtype) {
 // AUTO: bf16 token tensors take the chunked tensor-core path; float32 (whose parity bar of 1e-4 a
 // bf16-operand path cannot meet) and float16 (whose range the scaled operands exceed) take the
 // float32 recurrence.
-inline int resolve_r7_algo(int algo, int dtype) {
+inline int resolve_r7_algo(int algo, int dtype, int head_size = HS) {
   algo &= 0xff;
-  if (algo == RWKVB200_ALGO_AUTO) return dtype == RWKVB200_BF16 ? RWKVB200_ALGO_CHUNKED : RWKVB200_ALGO_RECURRENT;
+  if (algo == RWKVB200_ALGO_AUTO)
+    return dtype == RWKVB200_BF16 && head_size == HS ? RWKVB200_ALGO_CHUNKED : RWKVB200_ALGO_RECURRENT;
   return algo;
 }
 
@@ -40,9 +42,9 @@ inline int resolve_w6_algo(int algo) {
   return algo == RWKVB200_ALGO_RECURRENT ? RWKVB200_ALGO_RECURRENT : RWKVB200_ALGO_CHUNKED;
 }
 
-inline size_t r7_ckpt_bytes(int B, int T, int H) {
+inline size_t r7_ckpt_bytes(int B, int T, int H, int head_size = HS) {
   const size_t nc = (size_t)(T + R7_CKPT - 1) / R7_CKPT;
-  return align256((size_t)B * H * nc * HS * HS * sizeof(float));
+  return align256((size_t)B * H * nc * head_size * head_size * sizeof(float));
 }
 
 inline size_t w6_ckpt_bytes(int B, int T, int H) {
@@ -76,13 +78,16 @@ int rwkvb200_rwkv7_step(const void* r, const void* w, const void* k, const void*
                         const void* a, const void* b,
                         const float* state_in, int n_state, float* state_out, void* o,
                         int B, int H, int head_size, int dtype, void* stream) {
-  int e = check_common(B, 1, H, head_size, dtype);
+  int e = check_common(B, 1, H, head_size, dtype, true);
   if (e) return e;
   if (!r || !w || !k || !v || !a || !b || !state_out || !o) return RWKVB200_E_NULL;
   if (n_state != 0 && n_state != 1 && n_state != B) return RWKVB200_E_SHAPE;
   if (n_state != 0 && !state_in) return RWKVB200_E_NULL;
   const void* ps[] = {r, w, k, v, a, b, state_in, state_out, o};
   for (const void* p : ps) if (p && !aligned16(p)) return RWKVB200_E_ALIGN;
+  if (head_size != HS)      // one token of the float32 recurrence
+    return launch_rwkv7_rec_fwd(r, w, k, v, a, b, n_state ? state_in : nullptr, n_state, o, state_out, nullptr,
+                                R7_CKPT, B, 1, H, dtype, 0, (cudaStream_t)stream, nullptr, 0, head_size);
   return launch_rwkv7_step(r, w, k, v, a, b, n_state ? state_in : nullptr, n_state, state_out, o, B, H, dtype,
                            (cudaStream_t)stream);
 }
@@ -100,8 +105,8 @@ int rwkvb200_rwkv7_decode_step(const void* r, const void* w, const void* k, cons
 }
 
 size_t rwkvb200_rwkv7_fwd_workspace_bytes(int B, int T, int H, int head_size, int dtype, int algo) {
-  if (check_common(B, T, H, head_size, dtype)) return 0;
-  if (resolve_r7_algo(algo, dtype) == RWKVB200_ALGO_CHUNKED)
+  if (check_common(B, T, H, head_size, dtype, true)) return 0;
+  if (head_size == HS && resolve_r7_algo(algo, dtype, head_size) == RWKVB200_ALGO_CHUNKED)
     return r7c::fwd_workspace_bytes(B, T, H, (algo & RWKVB200_ALGO_KEEP) ? r7c::ALL_TILES : r7c::FWD_TILES);
   return 0;
 }
@@ -112,8 +117,10 @@ int rwkvb200_rwkv7_fwd(const void* r, const void* w, const void* k, const void* 
                        void* workspace, size_t workspace_bytes,
                        int B, int T, int H, int head_size, int dtype, int head_first, int algo,
                        void* stream) {
-  int e = check_common(B, T, H, head_size, dtype);
+  int e = check_common(B, T, H, head_size, dtype, true);
   if (e) return e;
+  if (head_size != HS && resolve_r7_algo(algo, dtype, head_size) != RWKVB200_ALGO_RECURRENT)
+    return RWKVB200_E_UNSUPPORTED;      // the tensor-core path is built for head size 64
   const int phases = phases_of(algo);
   if (!r || !w || !k || !v || !a || !b || (!o && (phases & PHASE_SCAN))) return RWKVB200_E_NULL;
   if (n_state != 0 && n_state != 1 && n_state != B) return RWKVB200_E_SHAPE;
@@ -122,11 +129,12 @@ int rwkvb200_rwkv7_fwd(const void* r, const void* w, const void* k, const void* 
   for (const void* p : ps) if (p && !aligned16(p)) return RWKVB200_E_ALIGN;
   const size_t need = rwkvb200_rwkv7_fwd_workspace_bytes(B, T, H, head_size, dtype, algo);
   if (workspace_bytes < need || (need && !workspace)) return RWKVB200_E_WORKSPACE;
-  if (phases != PHASE_ALL && resolve_r7_algo(algo, dtype) != RWKVB200_ALGO_CHUNKED) return RWKVB200_E_UNSUPPORTED;
-  switch (resolve_r7_algo(algo, dtype)) {
+  if (phases != PHASE_ALL && resolve_r7_algo(algo, dtype, head_size) != RWKVB200_ALGO_CHUNKED)
+    return RWKVB200_E_UNSUPPORTED;
+  switch (resolve_r7_algo(algo, dtype, head_size)) {
     case RWKVB200_ALGO_RECURRENT:
       return launch_rwkv7_rec_fwd(r, w, k, v, a, b, n_state ? h0 : nullptr, n_state, o, ht, nullptr, R7_CKPT,
-                                  B, T, H, dtype, head_first, (cudaStream_t)stream);
+                                  B, T, H, dtype, head_first, (cudaStream_t)stream, nullptr, 0, head_size);
     case RWKVB200_ALGO_CHUNKED:
       if (dtype != RWKVB200_BF16) return RWKVB200_E_UNSUPPORTED;
       return launch_rwkv7_chunked_fwd(r, w, k, v, a, b, n_state ? h0 : nullptr, n_state, o, ht, workspace,
@@ -138,10 +146,10 @@ int rwkvb200_rwkv7_fwd(const void* r, const void* w, const void* k, const void* 
 }
 
 size_t rwkvb200_rwkv7_bwd_workspace_bytes(int B, int T, int H, int head_size, int dtype, int algo) {
-  if (check_common(B, T, H, head_size, dtype)) return 0;
-  switch (resolve_r7_algo(algo, dtype)) {
-    case RWKVB200_ALGO_RECURRENT: return r7_ckpt_bytes(B, T, H);
-    case RWKVB200_ALGO_CHUNKED: return r7c::fwd_workspace_bytes(B, T, H, r7c::ALL_TILES);
+  if (check_common(B, T, H, head_size, dtype, true)) return 0;
+  switch (resolve_r7_algo(algo, dtype, head_size)) {
+    case RWKVB200_ALGO_RECURRENT: return r7_ckpt_bytes(B, T, H, head_size);
+    case RWKVB200_ALGO_CHUNKED: return head_size == HS ? r7c::fwd_workspace_bytes(B, T, H, r7c::ALL_TILES) : 0;
     default: return 0;
   }
 }
@@ -154,8 +162,10 @@ int rwkvb200_rwkv7_bwd(const void* r, const void* w, const void* k, const void* 
                        void* workspace, size_t workspace_bytes,
                        int B, int T, int H, int head_size, int dtype, int head_first, int algo,
                        void* stream) {
-  int e = check_common(B, T, H, head_size, dtype);
+  int e = check_common(B, T, H, head_size, dtype, true);
   if (e) return e;
+  if (head_size != HS && resolve_r7_algo(algo, dtype, head_size) != RWKVB200_ALGO_RECURRENT)
+    return RWKVB200_E_UNSUPPORTED;
   if (!r || !w || !k || !v || !a || !b || !d_o || !dr || !dw || !dk || !dv || !da || !db) return RWKVB200_E_NULL;
   if (n_state != 0 && n_state != 1 && n_state != B) return RWKVB200_E_SHAPE;
   if (n_state != 0 && !h0) return RWKVB200_E_NULL;
@@ -164,16 +174,16 @@ int rwkvb200_rwkv7_bwd(const void* r, const void* w, const void* k, const void* 
   const size_t need = rwkvb200_rwkv7_bwd_workspace_bytes(B, T, H, head_size, dtype, algo);
   if (workspace_bytes < need || (need && !workspace)) return RWKVB200_E_WORKSPACE;
   cudaStream_t st = (cudaStream_t)stream;
-  if (phases_of(algo) != PHASE_ALL && resolve_r7_algo(algo, dtype) != RWKVB200_ALGO_CHUNKED)
+  if (phases_of(algo) != PHASE_ALL && resolve_r7_algo(algo, dtype, head_size) != RWKVB200_ALGO_CHUNKED)
     return RWKVB200_E_UNSUPPORTED;
-  switch (resolve_r7_algo(algo, dtype)) {
+  switch (resolve_r7_algo(algo, dtype, head_size)) {
     case RWKVB200_ALGO_RECURRENT: {
       float* ckpt = reinterpret_cast<float*>(workspace);
       e = launch_rwkv7_rec_fwd(r, w, k, v, a, b, n_state ? h0 : nullptr, n_state, nullptr, nullptr, ckpt, R7_CKPT,
-                               B, T, H, dtype, head_first, st);
+                               B, T, H, dtype, head_first, st, nullptr, 0, head_size);
       if (e) return e;
       return launch_rwkv7_rec_bwd(r, w, k, v, a, b, d_o, d_ht, ckpt, dr, dw, dk, dv, da, db, d_h0,
-                                  B, T, H, dtype, head_first, st);
+                                  B, T, H, dtype, head_first, st, nullptr, 0, head_size);
     }
     case RWKVB200_ALGO_CHUNKED:
       if (dtype != RWKVB200_BF16) return RWKVB200_E_UNSUPPORTED;

@@ -88,10 +88,10 @@ __device__ __forceinline__ float decay_of(float w) { return expf(-expf(w)); }
 // Strides (in elements) of a [B,T,H,64] or [B,H,T,64] token tensor.
 struct TokLayout {
   long long sb, st, sh;
-  __host__ __device__ TokLayout(int T, int H, int head_first) {
-    sb = (long long)T * H * HS;
-    if (head_first) { sh = (long long)T * HS; st = HS; }
-    else            { sh = HS;                st = (long long)H * HS; }
+  __host__ __device__ TokLayout(int T, int H, int head_first, int hs = HS) {
+    sb = (long long)T * H * hs;
+    if (head_first) { sh = (long long)T * hs; st = hs; }
+    else            { sh = hs;                st = (long long)H * hs; }
   }
 };
 
@@ -148,12 +148,12 @@ int launch_rwkv7_step(const void* r, const void* w, const void* k, const void* v
 int launch_rwkv7_rec_fwd(const void* r, const void* w, const void* k, const void* v, const void* a, const void* b,
                          const float* h0, int n_state, void* o, float* ht, float* ckpt, int ckpt_every,
                          int B, int Tn, int H, int dtype, int head_first, cudaStream_t st,
-                         const UnitSel* sel = nullptr, int T_total = 0);
+                         const UnitSel* sel = nullptr, int T_total = 0, int head_size = HS);
 int launch_rwkv7_rec_bwd(const void* r, const void* w, const void* k, const void* v, const void* a, const void* b,
                          const void* d_o, const float* d_ht, const float* ckpt,
                          void* dr, void* dw, void* dk, void* dv, void* da, void* db, float* d_h0,
                          int B, int Tn, int H, int dtype, int head_first, cudaStream_t st,
-                         const UnitSel* sel = nullptr, int T_total = 0);
+                         const UnitSel* sel = nullptr, int T_total = 0, int head_size = HS);
 constexpr int R7_CKPT = 8;   // tokens between state checkpoints of the recurrent backward
 
 int launch_wkv6_fwd(const void* r, const void* k, const void* v, const void* w, const float* u,

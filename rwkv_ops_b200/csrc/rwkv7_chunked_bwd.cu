@@ -310,7 +310,11 @@ r7c_bwd_final_kernel(const bf16* __restrict__ w, const __grid_constant__ CUtenso
                      bf16* __restrict__ dq_rows, bf16* __restrict__ dw_rows, bf16* __restrict__ dk_rows,
                      bf16* __restrict__ dv_rows, bf16* __restrict__ da_rows, bf16* __restrict__ db_rows,
                      SeqView sv, int H, int NT, int n_ch, TokLayout lay, int* status, long long* dbg) {
+#ifdef RWKVB200_DEVTOOLS
 #define R7C_STAMP(n) do { if (dbg && tid == 0 && blockIdx.x == gridDim.x / 2 && it == 30) dbg[n] = clock64(); } while (0)
+#else
+#define R7C_STAMP(n) do {} while (0)
+#endif
   extern __shared__ unsigned char smem_raw[];
   FinalSmem& sm = *reinterpret_cast<FinalSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;

@@ -47,7 +47,11 @@ r7c_intra_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ w, con
                      const __grid_constant__ CUtensorMap tmap_v, unsigned char* __restrict__ ws_tiles,
                      float* __restrict__ ws_aux, int* __restrict__ ws_flags, int tiles_per_chunk,
                      int keep_for_bwd, SeqView sv, int H, int NT, int n_ch, TokLayout lay, int* status, long long* dbg) {
+#ifdef RWKVB200_DEVTOOLS
 #define R7C_STAMP(n) do { if (dbg && tid == 0 && blockIdx.x == gridDim.x / 2 && it == 30) dbg[n] = clock64(); } while (0)
+#else
+#define R7C_STAMP(n) do {} while (0)
+#endif
   extern __shared__ unsigned char smem_raw[];
   IntraSmem& sm = *reinterpret_cast<IntraSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -575,7 +579,11 @@ r7c_scan_fwd_kernel(const __grid_constant__ CUtensorMap tmap_v, const unsigned c
                     const float* __restrict__ h0, int n_state, const __grid_constant__ CUtensorMap tmap_o,
                     int write_o, float* __restrict__ ht, bf16* __restrict__ o_rows, SeqView sv, int H, int NT_slots,
                     TokLayout lay, int* status, long long* dbg) {
+#ifdef RWKVB200_DEVTOOLS
 #define R7C_STAMP(n) do { if (dbg && tid == 0 && blockIdx.x == gridDim.x / 2 && c == 2) dbg[n] = clock64(); } while (0)
+#else
+#define R7C_STAMP(n) do {} while (0)
+#endif
   extern __shared__ unsigned char smem_raw[];
   ScanSmem<STAGES>& sm =
       *reinterpret_cast<ScanSmem<STAGES>*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));

@@ -32,37 +32,38 @@ namespace rwkvb200 {
 namespace {
 
 constexpr int VS = 16;        // value rows per CTA
-constexpr int NQ = HS / VS;   // CTAs per (batch, head)
 constexpr int TL = 16;        // tokens staged per tile in the forward kernel
 constexpr int CK = R7_CKPT;   // chunk of the backward = checkpoint interval
-constexpr int SROW = HS + 1;  // padded row of a state slab in shared memory
+// The kernels are templates over the head size N (64 or 128): N / 16 CTAs per (batch, head), N threads per
+// CTA, N / 16 lanes share a state row (16 key columns each).
 
 // ---------------------------------------------------------------------------------------------
 // forward
 // ---------------------------------------------------------------------------------------------
-template <typename T>
-__global__ void __launch_bounds__(64)
+template <typename T, int N>
+__global__ void __launch_bounds__(N)
 rwkv7_rec_fwd_kernel(const T* __restrict__ r, const T* __restrict__ w, const T* __restrict__ k,
                      const T* __restrict__ v, const T* __restrict__ a, const T* __restrict__ b,
                      const float* __restrict__ h0, int n_state, T* __restrict__ o, float* __restrict__ ht,
                      float* __restrict__ ckpt, int ckpt_every, int Tn_dense, int H, TokLayout lay, UnitSel sel) {
-  __shared__ __align__(16) float tile[TL][5][HS];   // r, d, k, a, b
+  __shared__ __align__(16) float tile[TL][5][N];   // r, d, k, a, b
   __shared__ __align__(16) float vt[TL][VS];
   __shared__ __align__(16) float ot[TL][VS];
 
   const int unit = blockIdx.x, y = blockIdx.y, tid = threadIdx.x;
   if (sel.flags && sel.flags[unit] == 0) return;      // only the selected units run
   const int bi = unit / H, hi = unit % H;
-  const int vl = tid >> 2, kq = tid & 3;
+  constexpr int KSEG = N / 16;      // lanes per state row
+  const int vl = tid / KSEG, kq = tid % KSEG;
   // a packed batch keeps its sequences end to end in batch row 0
   const int Tn = sel.seq_len ? sel.seq_len[bi] : Tn_dense;
   const long long base = sel.seq_start ? hi * lay.sh + sel.seq_start[bi] * lay.st : bi * lay.sb + hi * lay.sh;
   const long long ckpt_unit = sel.ckpt_unit_stride ? sel.ckpt_unit_stride
-                                                   : (long long)((Tn_dense + ckpt_every - 1) / ckpt_every) * HS * HS;
+                                                   : (long long)((Tn_dense + ckpt_every - 1) / ckpt_every) * N * N;
 
   float S[16];
   if (h0 && n_state > 0) {
-    const float* p = h0 + ((long long)(n_state == 1 ? hi : unit) * HS + (y * VS + vl)) * HS + 16 * kq;
+    const float* p = h0 + ((long long)(n_state == 1 ? hi : unit) * N + (y * VS + vl)) * N + 16 * kq;
 #pragma unroll
     for (int j = 0; j < 16; j += 4) {
       float4 f = *reinterpret_cast<const float4*>(p + j);
@@ -76,8 +77,8 @@ rwkv7_rec_fwd_kernel(const T* __restrict__ r, const T* __restrict__ w, const T* 
   for (int t0 = 0; t0 < Tn; t0 += TL) {
     const int nt = min(TL, Tn - t0);
     // stage the tile: 5 vectors x nt tokens, one float4 per thread per pass
-    for (int i = tid; i < nt * 5 * 16; i += 64) {
-      const int quad = i & 15, row = i >> 4, tl = row / 5, which = row % 5;
+    for (int i = tid; i < nt * 5 * (N / 4); i += N) {
+      const int quad = i % (N / 4), row = i / (N / 4), tl = row / 5, which = row % 5;
       const T* src = which == 0 ? r : which == 1 ? w : which == 2 ? k : which == 3 ? a : b;
       float4 f = load4(src + base + (long long)(t0 + tl) * lay.st + 4 * quad);
       if (which == 1) f = make_float4(decay_of(f.x), decay_of(f.y), decay_of(f.z), decay_of(f.w));
@@ -93,7 +94,7 @@ rwkv7_rec_fwd_kernel(const T* __restrict__ r, const T* __restrict__ w, const T* 
     for (int tl = 0; tl < nt; ++tl) {
       const int t = t0 + tl;
       if (ckpt && (t % ckpt_every) == 0) {
-        float* p = ckpt + unit * ckpt_unit + (((long long)(t / ckpt_every) * HS) + (y * VS + vl)) * HS + 16 * kq;
+        float* p = ckpt + unit * ckpt_unit + (((long long)(t / ckpt_every) * N) + (y * VS + vl)) * N + 16 * kq;
 #pragma unroll
         for (int j = 0; j < 16; j += 4)
           *reinterpret_cast<float4*>(p + j) = make_float4(S[j], S[j + 1], S[j + 2], S[j + 3]);
@@ -109,8 +110,8 @@ rwkv7_rec_fwd_kernel(const T* __restrict__ r, const T* __restrict__ w, const T* 
         s0 += S[j] * ta[j]; s1 += S[j + 1] * ta[j + 1]; s2 += S[j + 2] * ta[j + 2]; s3 += S[j + 3] * ta[j + 3];
       }
       float sa = (s0 + s1) + (s2 + s3);
-      sa += __shfl_xor_sync(0xffffffffu, sa, 1);
-      sa += __shfl_xor_sync(0xffffffffu, sa, 2);
+#pragma unroll
+      for (int m = 1; m < KSEG; m <<= 1) sa += __shfl_xor_sync(0xffffffffu, sa, m);
       const float vv = vt[tl][vl];
       float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
 #pragma unroll
@@ -122,8 +123,8 @@ rwkv7_rec_fwd_kernel(const T* __restrict__ r, const T* __restrict__ w, const T* 
         o0 += S[j] * tr[j]; o1 += S[j + 1] * tr[j + 1]; o2 += S[j + 2] * tr[j + 2]; o3 += S[j + 3] * tr[j + 3];
       }
       float oo = (o0 + o1) + (o2 + o3);
-      oo += __shfl_xor_sync(0xffffffffu, oo, 1);
-      oo += __shfl_xor_sync(0xffffffffu, oo, 2);
+#pragma unroll
+      for (int m = 1; m < KSEG; m <<= 1) oo += __shfl_xor_sync(0xffffffffu, oo, m);
       if (kq == 0) ot[tl][vl] = oo;
     }
     __syncthreads();
@@ -136,7 +137,7 @@ rwkv7_rec_fwd_kernel(const T* __restrict__ r, const T* __restrict__ w, const T* 
     // above; ot is rewritten only after the next barrier pair
   }
   if (ht) {
-    float* p = ht + ((long long)unit * HS + (y * VS + vl)) * HS + 16 * kq;
+    float* p = ht + ((long long)unit * N + (y * VS + vl)) * N + 16 * kq;
 #pragma unroll
     for (int j = 0; j < 16; j += 4)
       *reinterpret_cast<float4*>(p + j) = make_float4(S[j], S[j + 1], S[j + 2], S[j + 3]);
@@ -146,19 +147,21 @@ rwkv7_rec_fwd_kernel(const T* __restrict__ r, const T* __restrict__ w, const T* 
 // ---------------------------------------------------------------------------------------------
 // backward
 // ---------------------------------------------------------------------------------------------
+template <int N>
 struct BwdSmem {
-  float tile[CK][6][HS];        // r, d, exp(w), k, a, b
+  float tile[CK][6][N];         // r, d, exp(w), k, a, b
   float vt[CK][VS];
   float dot[CK][VS];
   float sa[CK][VS];
   float dvt[CK][VS];
   float dsa[2][VS];
-  float Sbuf[CK + 1][VS][SROW]; // state before token i of the chunk (i = nt: after the last)
-  float part[2][CK][5][HS];     // per-chunk partial dr, dk, db, da, dd of this CTA's 16 rows
+  float Sbuf[CK + 1][VS][N + 1]; // state before token i of the chunk (i = nt: after the last), padded rows
+  float part[2][CK][5][N];      // per-chunk partial dr, dk, db, da, dd of this CTA's 16 rows
 };
 
-template <typename T>
-__global__ void __cluster_dims__(1, NQ, 1) __launch_bounds__(64)
+// launched as clusters of N / 16 CTAs along y (one per 16 value rows of a unit)
+template <typename T, int N>
+__global__ void __launch_bounds__(N)
 rwkv7_rec_bwd_kernel(const T* __restrict__ r, const T* __restrict__ w, const T* __restrict__ k,
                      const T* __restrict__ v, const T* __restrict__ a, const T* __restrict__ b,
                      const T* __restrict__ d_o, const float* __restrict__ d_ht, const float* __restrict__ ckpt,
@@ -166,27 +169,28 @@ rwkv7_rec_bwd_kernel(const T* __restrict__ r, const T* __restrict__ w, const T* 
                      T* __restrict__ da, T* __restrict__ db, float* __restrict__ d_h0,
                      int Tn_dense, int H, TokLayout lay, UnitSel sel) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  BwdSmem& sm = *reinterpret_cast<BwdSmem*>(smem_raw);
+  BwdSmem<N>& sm = *reinterpret_cast<BwdSmem<N>*>(smem_raw);
+  constexpr int KSEG = N / 16, NQ = N / VS;
   cg::cluster_group cluster = cg::this_cluster();
 
   const int unit = blockIdx.x, y = blockIdx.y, tid = threadIdx.x;
   if (sel.flags && sel.flags[unit] == 0) return;      // the four CTAs of a cluster share the unit: all leave
   const int bi = unit / H, hi = unit % H;
-  const int vl = tid >> 2, kq = tid & 3;   // row role
+  const int vl = tid / KSEG, kq = tid % KSEG;   // row role
   const int kc = tid;                      // column role
   const int Tn = sel.seq_len ? sel.seq_len[bi] : Tn_dense;
   const long long base = sel.seq_start ? hi * lay.sh + sel.seq_start[bi] * lay.st : bi * lay.sb + hi * lay.sh;
   const int NC = (Tn + CK - 1) / CK;
   const long long ckpt_unit = sel.ckpt_unit_stride ? sel.ckpt_unit_stride
-                                                   : (long long)((Tn_dense + CK - 1) / CK) * HS * HS;
+                                                   : (long long)((Tn_dense + CK - 1) / CK) * N * N;
 
   float dSr[16], dSc[VS];
   if (d_ht) {
-    const float* p = d_ht + ((long long)unit * HS + (y * VS + vl)) * HS + 16 * kq;
+    const float* p = d_ht + ((long long)unit * N + (y * VS + vl)) * N + 16 * kq;
 #pragma unroll
     for (int j = 0; j < 16; ++j) dSr[j] = p[j];
 #pragma unroll
-    for (int i = 0; i < VS; ++i) dSc[i] = d_ht[((long long)unit * HS + (y * VS + i)) * HS + kc];
+    for (int i = 0; i < VS; ++i) dSc[i] = d_ht[((long long)unit * N + (y * VS + i)) * N + kc];
   } else {
 #pragma unroll
     for (int j = 0; j < 16; ++j) dSr[j] = 0.f;
@@ -197,8 +201,8 @@ rwkv7_rec_bwd_kernel(const T* __restrict__ r, const T* __restrict__ w, const T* 
   for (int c = NC - 1; c >= 0; --c) {
     const int t0 = c * CK, nt = min(CK, Tn - t0), pb = c & 1;
     // ---- stage the chunk's inputs
-    for (int i = tid; i < nt * 6 * 16; i += 64) {
-      const int quad = i & 15, row = i >> 4, tl = row / 6, which = row % 6;
+    for (int i = tid; i < nt * 6 * (N / 4); i += N) {
+      const int quad = i % (N / 4), row = i / (N / 4), tl = row / 6, which = row % 6;
       const T* src = which == 0 ? r : (which == 1 || which == 2) ? w : which == 3 ? k : which == 4 ? a : b;
       float4 f = load4(src + base + (long long)(t0 + tl) * lay.st + 4 * quad);
       if (which == 1) f = make_float4(decay_of(f.x), decay_of(f.y), decay_of(f.z), decay_of(f.w));
@@ -214,7 +218,7 @@ rwkv7_rec_bwd_kernel(const T* __restrict__ r, const T* __restrict__ w, const T* 
     // ---- re-run the chunk forward from its checkpoint (row role)
     float S[16];
     {
-      const float* p = ckpt + unit * ckpt_unit + (((long long)c * HS) + (y * VS + vl)) * HS + 16 * kq;
+      const float* p = ckpt + unit * ckpt_unit + (((long long)c * N) + (y * VS + vl)) * N + 16 * kq;
 #pragma unroll
       for (int j = 0; j < 16; j += 4) {
         float4 f = *reinterpret_cast<const float4*>(p + j);
@@ -235,8 +239,8 @@ rwkv7_rec_bwd_kernel(const T* __restrict__ r, const T* __restrict__ w, const T* 
         s0 += S[j] * ta[j]; s1 += S[j + 1] * ta[j + 1];
       }
       float sa = s0 + s1;
-      sa += __shfl_xor_sync(0xffffffffu, sa, 1);
-      sa += __shfl_xor_sync(0xffffffffu, sa, 2);
+#pragma unroll
+      for (int m = 1; m < KSEG; m <<= 1) sa += __shfl_xor_sync(0xffffffffu, sa, m);
       if (kq == 0) sm.sa[tl][vl] = sa;
       const float vv = sm.vt[tl][vl];
 #pragma unroll
@@ -268,10 +272,11 @@ rwkv7_rec_bwd_kernel(const T* __restrict__ r, const T* __restrict__ w, const T* 
         b0 += dSr[j] * tb[j]; b1 += dSr[j + 1] * tb[j + 1];
       }
       float dvv = a0 + a1, dsa = b0 + b1;
-      dvv += __shfl_xor_sync(0xffffffffu, dvv, 1);
-      dsa += __shfl_xor_sync(0xffffffffu, dsa, 1);
-      dvv += __shfl_xor_sync(0xffffffffu, dvv, 2);
-      dsa += __shfl_xor_sync(0xffffffffu, dsa, 2);
+#pragma unroll
+      for (int m = 1; m < KSEG; m <<= 1) {
+        dvv += __shfl_xor_sync(0xffffffffu, dvv, m);
+        dsa += __shfl_xor_sync(0xffffffffu, dsa, m);
+      }
       if (kq == 0) { sm.dvt[tl][vl] = dvv; sm.dsa[buf][vl] = dsa; }
       // column role, part 1 (does not need dsa)
       float p_dr = 0.f, p_dk = 0.f, p_db = 0.f, p_dd = 0.f;
@@ -305,7 +310,7 @@ rwkv7_rec_bwd_kernel(const T* __restrict__ r, const T* __restrict__ w, const T* 
     }
     // ---- dv rows of this CTA
     __syncthreads();
-    for (int i = tid; i < nt * VS; i += 64) {
+    for (int i = tid; i < nt * VS; i += N) {
       const int tl = i >> 4, vi = i & 15;
       dv[base + (long long)(t0 + tl) * lay.st + y * VS + vi] = from_f32<T>(sm.dvt[tl][vi]);
     }
@@ -317,7 +322,7 @@ rwkv7_rec_bwd_kernel(const T* __restrict__ r, const T* __restrict__ w, const T* 
       for (int rk_ = 0; rk_ < NQ; ++rk_) {
         const float* rp = cluster.map_shared_rank(&sm.part[pb][tl][0][0], rk_);
 #pragma unroll
-        for (int qn = 0; qn < 5; ++qn) acc[qn] += rp[qn * HS + kc];
+        for (int qn = 0; qn < 5; ++qn) acc[qn] += rp[qn * N + kc];
       }
       const long long off = base + (long long)(t0 + tl) * lay.st + kc;
       dr[off] = from_f32<T>(acc[0]);
@@ -331,7 +336,7 @@ rwkv7_rec_bwd_kernel(const T* __restrict__ r, const T* __restrict__ w, const T* 
     __syncthreads();
   }
   if (d_h0) {
-    float* p = d_h0 + ((long long)unit * HS + (y * VS + vl)) * HS + 16 * kq;
+    float* p = d_h0 + ((long long)unit * N + (y * VS + vl)) * N + 16 * kq;
 #pragma unroll
     for (int j = 0; j < 16; ++j) p[j] = dSr[j];
   }
@@ -340,17 +345,27 @@ rwkv7_rec_bwd_kernel(const T* __restrict__ r, const T* __restrict__ w, const T* 
 
 }  // namespace
 
+// head size 64 or 128
+#define RWKVB200_DISPATCH_HEAD(hs, ...)                           \
+  switch (hs) {                                                   \
+    case 64:  { constexpr int N = 64;  __VA_ARGS__; break; }      \
+    case 128: { constexpr int N = 128; __VA_ARGS__; break; }      \
+    default: return RWKVB200_E_UNSUPPORTED;                       \
+  }
+
 int launch_rwkv7_rec_fwd(const void* r, const void* w, const void* k, const void* v, const void* a, const void* b,
                          const float* h0, int n_state, void* o, float* ht, float* ckpt, int ckpt_every,
                          int B, int Tn, int H, int dtype, int head_first, cudaStream_t st, const UnitSel* sel_,
-                         int T_total) {
-  TokLayout lay(T_total ? T_total : Tn, H, head_first);
+                         int T_total, int head_size) {
+  TokLayout lay(T_total ? T_total : Tn, H, head_first, head_size);
   const UnitSel sel = sel_ ? *sel_ : UnitSel{nullptr, nullptr, nullptr, 0};
-  dim3 grid(B * H, NQ);
   ProfScope prof("rwkv7_rec_fwd_kernel", st);
-  RWKVB200_DISPATCH_DTYPE(dtype,
-    rwkv7_rec_fwd_kernel<T><<<grid, 64, 0, st>>>((const T*)r, (const T*)w, (const T*)k, (const T*)v, (const T*)a,
-                                                 (const T*)b, h0, n_state, (T*)o, ht, ckpt, ckpt_every, Tn, H, lay, sel));
+  RWKVB200_DISPATCH_HEAD(head_size,
+    dim3 grid(B * H, N / VS);
+    RWKVB200_DISPATCH_DTYPE(dtype,
+      rwkv7_rec_fwd_kernel<T, N><<<grid, N, 0, st>>>((const T*)r, (const T*)w, (const T*)k, (const T*)v, (const T*)a,
+                                                     (const T*)b, h0, n_state, (T*)o, ht, ckpt, ckpt_every, Tn, H,
+                                                     lay, sel)));
   return check_launch();
 }
 
@@ -358,17 +373,29 @@ int launch_rwkv7_rec_bwd(const void* r, const void* w, const void* k, const void
                          const void* d_o, const float* d_ht, const float* ckpt,
                          void* dr, void* dw, void* dk, void* dv, void* da, void* db, float* d_h0,
                          int B, int Tn, int H, int dtype, int head_first, cudaStream_t st, const UnitSel* sel_,
-                         int T_total) {
-  TokLayout lay(T_total ? T_total : Tn, H, head_first);
+                         int T_total, int head_size) {
+  TokLayout lay(T_total ? T_total : Tn, H, head_first, head_size);
   const UnitSel sel = sel_ ? *sel_ : UnitSel{nullptr, nullptr, nullptr, 0};
-  dim3 grid(B * H, NQ);
-  const int smem = (int)sizeof(BwdSmem);
   ProfScope prof("rwkv7_rec_bwd_kernel", st);
-  RWKVB200_DISPATCH_DTYPE(dtype,
-    if (cuda_ok(cudaFuncSetAttribute(rwkv7_rec_bwd_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem))) return RWKVB200_E_CUDA;
-    rwkv7_rec_bwd_kernel<T><<<grid, 64, smem, st>>>((const T*)r, (const T*)w, (const T*)k, (const T*)v, (const T*)a,
-                                                    (const T*)b, (const T*)d_o, d_ht, ckpt, (T*)dr, (T*)dw, (T*)dk,
-                                                    (T*)dv, (T*)da, (T*)db, d_h0, Tn, H, lay, sel));
+  RWKVB200_DISPATCH_HEAD(head_size,
+    const int smem = (int)sizeof(BwdSmem<N>);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(B * H, N / VS);
+    cfg.blockDim = dim3(N);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;      // the CTAs of a unit exchange partial sums
+    attr[0].val.clusterDim.x = 1; attr[0].val.clusterDim.y = N / VS; attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    RWKVB200_DISPATCH_DTYPE(dtype,
+      if (cuda_ok(cudaFuncSetAttribute(rwkv7_rec_bwd_kernel<T, N>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)))
+        return RWKVB200_E_CUDA;
+      if (cuda_ok(cudaLaunchKernelEx(&cfg, rwkv7_rec_bwd_kernel<T, N>, (const T*)r, (const T*)w, (const T*)k,
+                                     (const T*)v, (const T*)a, (const T*)b, (const T*)d_o, d_ht, ckpt, (T*)dr, (T*)dw,
+                                     (T*)dk, (T*)dv, (T*)da, (T*)db, d_h0, Tn, H, lay, sel)))
+        return RWKVB200_E_CUDA));
   return check_launch();
 }
 

@@ -68,9 +68,10 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // `status` is the library's device status word (0 = fine), see device_status_ptr().
 // The result is made uniform over the threads of the warp that wait together, so that the
 // warp-collective TMEM instructions that follow are never executed by part of a warp.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int code) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int code,
+                                          uint32_t limit = WAIT_LIMIT) {
   bool done = false;
-  for (uint32_t i = 0; i < WAIT_LIMIT && !done; ++i) done = mbar_try_wait(bar, parity);
+  for (uint32_t i = 0; i < limit && !done; ++i) done = mbar_try_wait(bar, parity);
   if (!done) atomicCAS(status, 0, code);
   return __all_sync(__activemask(), done) != 0;
 }
@@ -319,9 +320,11 @@ int make_token_tensor_map(CUtensorMap* out, const void* base, int B, int T, int 
 // ran out; nullptr if the lookup failed.  Read and cleared by rwkvb200_device_status().
 int* device_status_ptr();
 
-// Optional device buffer (>= 64 long long) that kernels fill with clock64() stamps at their phase
-// boundaries (one designated CTA); nullptr unless a developer installed one.
 int make_row_tensor_map(CUtensorMap* out, const void* base, int B, int T, int H, int elem_bytes);
+
+// Device buffer (>= 64 long long) that kernels fill with clock64() stamps at their phase boundaries (one
+// designated CTA).  Only the developer build (-DRWKVB200_DEVTOOLS) can install one and only its kernels
+// contain the stamping code; in the shipped library this is always nullptr.
 long long* debug_stamp_buffer();
 
 }  // namespace rwkvb200

@@ -119,7 +119,11 @@ wkv6c_fwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
                  float* __restrict__ states, int* __restrict__ flags, const __grid_constant__ CUtensorMap tmap_r,
                  const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
                  const __grid_constant__ CUtensorMap tmap_w, int Tn, int H, int* status, long long* dbg) {
+#ifdef RWKVB200_DEVTOOLS
 #define W6C_STAMP(n) do { if (dbg && tid == 0 && blockIdx.x == gridDim.x / 2 && c == 2) dbg[n] = clock64(); } while (0)
+#else
+#define W6C_STAMP(n) do {} while (0)
+#endif
   extern __shared__ unsigned char smem_raw[];
   FwdSmem& sm = *reinterpret_cast<FwdSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -436,7 +440,11 @@ wkv6c_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
                  const __grid_constant__ CUtensorMap tmap_r, const __grid_constant__ CUtensorMap tmap_k,
                  const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_w,
                  const __grid_constant__ CUtensorMap tmap_dy, int Tn, int H, int* status, long long* dbg) {
+#ifdef RWKVB200_DEVTOOLS
 #define W6C_STAMP(n) do { if (dbg && tid == 0 && blockIdx.x == gridDim.x / 2 && c == NT - 2) dbg[n] = clock64(); } while (0)
+#else
+#define W6C_STAMP(n) do {} while (0)
+#endif
   extern __shared__ unsigned char smem_raw[];
   BwdSmem& sm = *reinterpret_cast<BwdSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;

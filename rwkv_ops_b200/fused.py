@@ -53,6 +53,7 @@ def _fused_fwd(r: torch.Tensor, w_pre: torch.Tensor, k: torch.Tensor, v: torch.T
                                           o.data_ptr(), ht.data_ptr(), ws.data_ptr(), nws, B, T, H, K,
                                           _lib.BF16, int(keep), _lib.stream_ptr(dev))
         _lib.check(rc, "rwkv7_fused_fwd")
+        _lib.check_status("rwkv7_fused_fwd")
     return o, ht, (ws if keep else ws.new_empty((1,)))
 
 
@@ -86,6 +87,7 @@ def _fused_bwd(r: torch.Tensor, w_pre: torch.Tensor, k: torch.Tensor, v: torch.T
                                           dh0.data_ptr(), ws.data_ptr(), nws, B, T, H, K, _lib.BF16, int(have),
                                           _lib.stream_ptr(dev))
         _lib.check(rc, "rwkv7_fused_bwd")
+        _lib.check_status("rwkv7_fused_bwd")
     return dr, dw, dk, dv, du, dq, dh0
 
 

@@ -48,6 +48,7 @@ def _wkv6_fwd(r: torch.Tensor, k: torch.Tensor, v: torch.Tensor, w: torch.Tensor
                                    kept.data_ptr() if nws else None, nws,
                                    B, T, H, HEAD_SIZE, code, flags, _lib.stream_ptr(dev))
         _lib.check(rc, "wkv6_fwd")
+        _lib.check_status("wkv6_fwd")
     if not keep:
         kept = kept.new_empty(0)
     return y, sT, kept
@@ -87,6 +88,7 @@ def _wkv6_bwd(r: torch.Tensor, k: torch.Tensor, v: torch.Tensor, w: torch.Tensor
                                    ds0.data_ptr(), ws.data_ptr(), nws, B, T, H, HEAD_SIZE, code, algo,
                                    _lib.stream_ptr(dev))
         _lib.check(rc, "wkv6_bwd")
+        _lib.check_status("wkv6_bwd")
     return dr, dk, dv, dw, du, ds0
 
 

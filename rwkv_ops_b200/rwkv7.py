@@ -17,7 +17,8 @@ import torch
 
 from . import _lib
 
-HEAD_SIZE = 64
+HEAD_SIZE = 64               # the head size of the tensor-core path
+HEAD_SIZES = (64, 128)       # head sizes the operator accepts (128: float32 recurrence for every dtype)
 _ALGO_NAMES = {"auto": _lib.ALGO_AUTO, "recurrent": _lib.ALGO_RECURRENT, "chunked": _lib.ALGO_CHUNKED}
 
 
@@ -62,6 +63,7 @@ def _rwkv7_fwd(r: torch.Tensor, w: torch.Tensor, k: torch.Tensor, v: torch.Tenso
                                          b.data_ptr(), _lib.ptr(h0), n_state, ht.data_ptr(), o.data_ptr(),
                                          B, H, K, code, _lib.stream_ptr(dev))
             _lib.check(rc, "rwkv7_step")
+            _lib.check_status("rwkv7_step")
         else:
             nws = lib.rwkvb200_rwkv7_fwd_workspace_bytes(B, T, H, K, code, algo)
             ws = _workspace(nws, dev)
@@ -70,6 +72,7 @@ def _rwkv7_fwd(r: torch.Tensor, w: torch.Tensor, k: torch.Tensor, v: torch.Tenso
                                         _lib.ptr(ws), nws, B, T, H, K, code, int(head_first), algo,
                                         _lib.stream_ptr(dev))
             _lib.check(rc, "rwkv7_fwd")
+            _lib.check_status("rwkv7_fwd")
     return o, ht
 
 
@@ -107,6 +110,7 @@ def _rwkv7_fwd_keep(r: torch.Tensor, w: torch.Tensor, k: torch.Tensor, v: torch.
                                     kept.data_ptr(), nws, B, T, H, K, code, int(head_first), flags,
                                     _lib.stream_ptr(dev))
         _lib.check(rc, "rwkv7_fwd")
+        _lib.check_status("rwkv7_fwd")
     return o, ht, kept
 
 
@@ -146,6 +150,7 @@ def _rwkv7_bwd_kept(r: torch.Tensor, w: torch.Tensor, k: torch.Tensor, v: torch.
                                     db.data_ptr(), dh0.data_ptr(), kept.data_ptr(), kept.numel(),
                                     B, T, H, K, code, int(head_first), algo | _lib.ALGO_KEEP, _lib.stream_ptr(dev))
         _lib.check(rc, "rwkv7_bwd")
+        _lib.check_status("rwkv7_bwd")
     return dr, dw, dk, dv, da, db, dh0
 
 
@@ -210,6 +215,7 @@ def _rwkv7_bwd(r: torch.Tensor, w: torch.Tensor, k: torch.Tensor, v: torch.Tenso
                                     db.data_ptr(), dh0.data_ptr(), _lib.ptr(ws), nws,
                                     B, T, H, K, code, int(head_first), algo, _lib.stream_ptr(dev))
         _lib.check(rc, "rwkv7_bwd")
+        _lib.check_status("rwkv7_bwd")
     return dr, dw, dk, dv, da, db, dh0
 
 
@@ -265,14 +271,17 @@ def generalized_delta_rule(
 ):
     """Drop-in for the reference's ``generalized_delta_rule``.
 
-    ``r, w, k, v, a, b``: ``[B, T, H, 64]`` (``[B, H, T, 64]`` when ``head_first``), any of
-    float32 / bfloat16 / float16; ``w`` is the raw decay input (the operator applies
-    ``exp(-exp(w))``).  ``initial_state``: float32 ``[N, H, 64, 64]`` with ``N == B`` or ``N == 1``
+    ``r, w, k, v, a, b``: ``[B, T, H, K]`` (``[B, H, T, K]`` when ``head_first``) with head size
+    ``K`` 64 or 128 (the reference's value test runs 128, ``test_script/test_rwkv7_value.py:46-51``), any
+    of float32 / bfloat16 / float16; ``w`` is the raw decay input (the operator applies
+    ``exp(-exp(w))``).  ``initial_state``: float32 ``[N, H, K, K]`` with ``N == B`` or ``N == 1``
     (broadcast), value index before key index.  Returns ``(o, final_state)`` or just ``o``.
+    Head size 64 with bfloat16 tokens takes the tensor-core path, everything else the float32 recurrence.
     """
     _lib.require_cuda(r, w, k, v, a, b, initial_state)
-    if r.dim() != 4 or r.shape[-1] != HEAD_SIZE:
-        raise ValueError(f"expected 4-D token tensors with head size {HEAD_SIZE}, got {tuple(r.shape)}")
+    if r.dim() != 4 or r.shape[-1] not in HEAD_SIZES:
+        raise ValueError(f"expected 4-D token tensors with head size in {HEAD_SIZES}, got {tuple(r.shape)}")
+    HEAD_SIZE = r.shape[-1]
     for name, x in (("w", w), ("k", k), ("v", v), ("a", a), ("b", b)):
         if x.shape != r.shape:
             raise ValueError(f"{name} has shape {tuple(x.shape)}, expected {tuple(r.shape)}")
@@ -293,7 +302,7 @@ def generalized_delta_rule(
     needs_grad = torch.is_grad_enabled() and (
         any(x.requires_grad for x in (r_, w_, k_, v_, a_, b_)) or (h0 is not None and h0.requires_grad))
     keep = False
-    if needs_grad and T > 1 and cdt == torch.bfloat16 and algo in (_lib.ALGO_AUTO, _lib.ALGO_CHUNKED):
+    if needs_grad and T > 1 and cdt == torch.bfloat16 and HEAD_SIZE == 64 and algo in (_lib.ALGO_AUTO, _lib.ALGO_CHUNKED):
         nws = _lib.load().rwkvb200_rwkv7_fwd_workspace_bytes(B, T, H, HEAD_SIZE, _lib.BF16, algo | _lib.ALGO_KEEP)
         keep = nws <= _keep_limit_bytes(r_.device)
     if keep:
@@ -313,6 +322,6 @@ def get_generalized_delta_rule(HEAD_SIZE: int = 64, KERNEL_TYPE: str = "cuda"):
     ``USE_KERNEL`` is always True (callers use it to choose the padding recipe of the kernel
     path).  ``KERNEL_TYPE`` is accepted for compatibility and ignored: there is one implementation.
     """
-    if HEAD_SIZE != 64:
-        raise ValueError("rwkv_ops_b200 is built for head size 64")
+    if HEAD_SIZE not in HEAD_SIZES:
+        raise ValueError(f"rwkv_ops_b200 is built for head sizes {HEAD_SIZES}")
     return generalized_delta_rule, True

@@ -64,6 +64,7 @@ def _fwd_varlen(r: torch.Tensor, w: torch.Tensor, k: torch.Tensor, v: torch.Tens
                                            T, _lib.ptr(h0), n_state, o.data_ptr(), ht.data_ptr(), ws.data_ptr(),
                                            nws, H, K, _lib.dtype_code(r.dtype), int(keep), _lib.stream_ptr(dev))
         _lib.check(rc, "rwkv7_fwd_varlen")
+        _lib.check_status("rwkv7_fwd_varlen")
     return o, ht, (ws if keep else ws.new_empty((1,)))
 
 
@@ -99,6 +100,7 @@ def _bwd_varlen(r: torch.Tensor, w: torch.Tensor, k: torch.Tensor, v: torch.Tens
                                            da.data_ptr(), db.data_ptr(), dh0.data_ptr(), ws.data_ptr(), nws,
                                            H, K, _lib.dtype_code(r.dtype), int(have), _lib.stream_ptr(dev))
         _lib.check(rc, "rwkv7_bwd_varlen")
+        _lib.check_status("rwkv7_bwd_varlen")
     return dr, dw, dk, dv, da, db, dh0
 
 

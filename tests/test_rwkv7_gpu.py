@@ -204,3 +204,31 @@ def test_full_size_sampled_units(cfg, algo):
     assert rel_l2(s[bi.cuda(), hi.cuda()].unsqueeze(1), s_ref) < 2e-2
     for n, gr in zip("rwkvab", grads[:6]):
         assert rel_l2(pick(g[n].grad), gr) < 2e-2, n
+
+
+@pytest.mark.parametrize("T", [1, 37, 130])
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-4), (torch.bfloat16, 2e-2)])
+def test_head_size_128_forward_backward(T, dtype, tol):
+    """Head size 128, the size of the reference's own value test (test_script/test_rwkv7_value.py:46-51):
+    outputs, final state and all gradients against the oracle."""
+    B, H, K = 2, 3, 128
+    fn, use_kernel = ro.get_generalized_delta_rule(HEAD_SIZE=K)
+    assert use_kernel
+    d = rwkv7_inputs(B, T, H, K, dtype=dtype, seed=900 + T, with_state=True, with_grads=True)
+    ref = {n: d[n].float().clone().requires_grad_(True) for n in "rwkvab"}
+    h0r = d["initial_state"].clone().requires_grad_(True)
+    o_ref, s_ref = oracle_gdr(*[ref[n] for n in "rwkvab"], initial_state=h0r)
+    ((o_ref * d["d_out"].float()).sum() + (s_ref * d["d_state"]).sum()).backward()
+    g = {n: d[n].cuda().requires_grad_(True) for n in "rwkvab"}
+    h0 = d["initial_state"].cuda().requires_grad_(True)
+    o, s = fn(*[g[n] for n in "rwkvab"], initial_state=h0)
+    assert o.shape == (B, T, H, K) and o.dtype == dtype and s.shape == (B, H, K, K)
+    torch.autograd.backward([o, s], [d["d_out"].cuda(), d["d_state"].cuda()])
+    errs = {"o": rel_l2(o, o_ref), "s": rel_l2(s, s_ref), "dh0": rel_l2(h0.grad, h0r.grad)}
+    errs.update({f"d{n}": rel_l2(g[n].grad, ref[n].grad) for n in "rwkvab"})
+    assert all(e < tol for e in errs.values()), errs
+    # [B, H, T, K] in and out
+    with torch.no_grad():
+        o_hf = fn(*[g[n].detach().permute(0, 2, 1, 3).contiguous() for n in "rwkvab"], initial_state=h0.detach(),
+                  output_final_state=False, head_first=True)
+    assert torch.equal(o_hf.permute(0, 2, 1, 3), o)

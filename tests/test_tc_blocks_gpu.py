@@ -1,5 +1,5 @@
 """The tcgen05 / TMA building blocks of the chunked path, one at a time on known data, through the
-C ABI (``rwkvb200_tc_selftest``): 128-row MMA, paired 64-row MMAs with transposed (MN-major) operands,
+C ABI of the developer build of the library (``rwkvb200_tc_selftest``, ``include/rwkv_ops_b200_devtools.h``): 128-row MMA, paired 64-row MMAs with transposed (MN-major) operands,
 TMA tiled load with zero fill past the end of the sequence, bulk store and bulk load."""
 import pytest
 import torch
@@ -19,7 +19,7 @@ def _status_clear(lib):
 
 
 def test_mma_128x128_kmajor():
-    lib = _lib.load()
+    lib = _lib.load_dev()
     X, Y, Z, W = _mats(1)
     out = torch.zeros(128, 128, device="cuda")
     rc = lib.rwkvb200_tc_selftest(0, X.data_ptr(), Y.data_ptr(), Z.data_ptr(), W.data_ptr(), out.data_ptr(),
@@ -32,7 +32,7 @@ def test_mma_128x128_kmajor():
 
 
 def test_mma_64_pairs_with_transposed_operands():
-    lib = _lib.load()
+    lib = _lib.load_dev()
     X, Y, Z, W = _mats(2)
     out = torch.zeros(128, 64, device="cuda")
     rc = lib.rwkvb200_tc_selftest(1, X.data_ptr(), Y.data_ptr(), Z.data_ptr(), W.data_ptr(), out.data_ptr(),
@@ -51,7 +51,7 @@ def test_mma_64_pairs_with_transposed_operands():
 
 
 def test_mma_wide_and_long_transposed_operands():
-    lib = _lib.load()
+    lib = _lib.load_dev()
     X, Y, Z, W = _mats(4)
     out = torch.zeros(128, 64, device="cuda")
     args = (X.data_ptr(), Y.data_ptr(), Z.data_ptr(), W.data_ptr(), out.data_ptr(), None, 0, 0, 0, 0, 0, 0, None)
@@ -72,7 +72,7 @@ def test_mma_wide_and_long_transposed_operands():
 
 @pytest.mark.parametrize("t0,T", [(64, 192), (128, 150)])
 def test_tma_tile_load_and_bulk_copies(t0, T):
-    lib = _lib.load()
+    lib = _lib.load_dev()
     B, H, b, h = 2, 3, 1, 2
     g = torch.Generator().manual_seed(3)
     tok = torch.randn(B, T, H, 64, generator=g).to(torch.bfloat16).cuda()
@@ -93,3 +93,26 @@ def test_tma_tile_load_and_bulk_copies(t0, T):
     exp = exp.reshape(-1)
     assert torch.equal(img[:4096].cpu(), exp)
     assert torch.equal(img[4096:].cpu(), exp)
+
+
+def test_a_wait_that_runs_out_is_reported_and_the_kernel_returns():
+    """A bounded wait on a barrier that nothing ever completes (a thousand polls): the kernel gives up, winds
+    down normally and the status word carries the code of the wait; the context stays usable."""
+    lib = _lib.load_dev()
+    _status_clear(lib)
+    out = torch.zeros(4, device="cuda")
+    rc = lib.rwkvb200_tc_selftest(5, None, None, None, None, out.data_ptr(), None, 0, 0, 0, 0, 0, 0, None,
+                                  torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert lib.rwkvb200_device_status(1) == 105
+    assert lib.rwkvb200_device_status(0) == 0      # cleared by the read above
+    assert out[0].item() == 0.0
+    X, Y, Z, W = _mats(9)                          # and the next kernel runs as usual
+    o2 = torch.zeros(128, 128, device="cuda")
+    assert lib.rwkvb200_tc_selftest(0, X.data_ptr(), Y.data_ptr(), Z.data_ptr(), W.data_ptr(), o2.data_ptr(),
+                                    None, 0, 0, 0, 0, 0, 0, None, torch.cuda.current_stream().cuda_stream) == 0
+    torch.cuda.synchronize()
+    _status_clear(lib)
+    ref = torch.cat([X, Y]).float() @ torch.cat([Z, W]).float().T
+    assert torch.allclose(o2, ref, rtol=1e-4, atol=1e-3)
