@@ -14,8 +14,7 @@ namespace r7c {
 using namespace tc;
 typedef __nv_bfloat16 bf16;
 
-constexpr float EXP_CLAMP = 80.f;
-__device__ __forceinline__ float cexp(float x) { return __expf(fminf(fmaxf(x, -EXP_CLAMP), EXP_CLAMP)); }
+// decay sums are kept in units of log 2 (tc::ex2), as in the forward kernels; nothing is clamped
 constexpr int NROW = 68;
 
 __device__ __forceinline__ void store_row32_global(bf16* dst, const float* x) {
@@ -285,8 +284,8 @@ struct FinalSmem {
   unsigned char red_pad[2048];    // the two fp32 scratch arrays that later overlay the dA tiles need 34 KB
   unsigned char dge[TILE_BYTES];  // da~ a~ as bf16
   unsigned char stage[5][TILE_BYTES];   // dq, dk, da, db, dw rows staged for TMA stores
-  float gs[L * NROW];       // gi - gref: inclusive prefix of g inside the chunk, relative to the reference point
-  float gg[L * NROW];       // g
+  float gs[L * NROW];       // (gi - gref) log2(e): inclusive prefix of g inside the chunk, relative to the reference point
+  float gg[L * NROW];       // g log2(e)
   float qtot[4][64];        // sums of g over the four quarters of the chunk
   float rqtot[4][64];       // sums of the decay-gradient terms over the four quarters
   float dgl[64];            // dglast
@@ -433,8 +432,8 @@ r7c_bwd_final_kernel(const bf16* __restrict__ w, const __grid_constant__ CUtenso
           w0 = round_bf16(W_SCALE * sigmoidf_(w0));
           w1 = round_bf16(W_SCALE * sigmoidf_(w1));
         }
-        g[2 * m] = valid ? -__expf(w0) : 0.f;
-        g[2 * m + 1] = valid ? -__expf(w1) : 0.f;
+        g[2 * m] = valid ? -LOG2E * ex2(LOG2E * w0) : 0.f;
+        g[2 * m + 1] = valid ? -LOG2E * ex2(LOG2E * w1) : 0.f;
       }
       *reinterpret_cast<float4*>(&sm.gg[row * NROW + 8 * cc]) = make_float4(g[0], g[1], g[2], g[3]);
       *reinterpret_cast<float4*>(&sm.gg[row * NROW + 8 * cc + 4]) = make_float4(g[4], g[5], g[6], g[7]);
@@ -586,8 +585,8 @@ r7c_bwd_final_kernel(const bf16* __restrict__ w, const __grid_constant__ CUtenso
           const int j = j4 + m;
           const float d1 = gsv[m];                                       // gi - gref
           const float x1 = __uint_as_float(r1[j]), x2 = __uint_as_float(r2[j]);
-          o2[j] = x2 * cexp(-d1);                                        // dk / db
-          o1[j] = x1 * (second ? cexp(d1 - ggv[m]) : cexp(d1));          // da / dq
+          o2[j] = x2 * ex2(-d1);                                         // dk / db
+          o1[j] = x1 * ex2(second ? d1 - ggv[m] : d1);                   // da / dq
           ge[j] = x1 * t1[j];
           rd[m] = ge[j] - x2 * t2[j];
         }
@@ -635,7 +634,8 @@ r7c_bwd_final_kernel(const bf16* __restrict__ w, const __grid_constant__ CUtenso
         const int ii = 16 * quarter + j;
         const float e_ = __bfloat162float(*reinterpret_cast<const bf16*>(sm.dge + tile_off(ii, c)));
         const float dg = rv[j] + add - e_;
-        *reinterpret_cast<bf16*>(sm.stage[4] + tile_off(ii, c)) = __float2bfloat16_rn(dg * sm.gg[ii * NROW + c]);
+        // dw = dg g, with g = gg ln 2 (gg is in units of log 2)
+        *reinterpret_cast<bf16*>(sm.stage[4] + tile_off(ii, c)) = __float2bfloat16_rn(dg * (LN2 * sm.gg[ii * NROW + c]));
       }
     }
     fence_async_smem();

@@ -8,8 +8,10 @@ namespace r7c {
 using namespace tc;
 typedef __nv_bfloat16 bf16;
 
-constexpr float EXP_CLAMP = 80.f;
-__device__ __forceinline__ float cexp(float x) { return __expf(fminf(fmaxf(x, -EXP_CLAMP), EXP_CLAMP)); }
+// All decay sums of this file are in units of log 2 (tc::ex2).  No exponent is clamped: inside DECAY_LIMIT every
+// factor is a normal number, and a unit beyond it is recomputed by the float32 recurrence whatever the
+// tensor-core kernels wrote for it.
+constexpr float EXP2_FLOOR = -126.f;      // 2^x below this is flushed to zero anyway
 
 // ---------------------------------------------------------------------------------------------
 // intra-chunk kernel: persistent CTAs of 256 threads over the B*H*NT chunk-heads
@@ -147,7 +149,7 @@ r7c_intra_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ w, con
       const int e = tid + 256 * n;
       rw[n] = *reinterpret_cast<const uint4*>(sm.aqk + tile_chunk_off(e >> 3, e & 7));
     }
-    // ---- phase A: decay prefix sums and the four scaled operands; the prefix sum over tokens goes
+    // ---- phase A: decay prefix sums (in units of log 2) and the four scaled operands; the prefix sum over tokens goes
     // through shared memory (the fp32 area that later holds A_ab).
     {
       float* gs = sm.nmat;
@@ -164,8 +166,8 @@ r7c_intra_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ w, con
             w0 = round_bf16(W_SCALE * sigmoidf_(w0));
             w1 = round_bf16(W_SCALE * sigmoidf_(w1));
           }
-          gown[n][2 * m] = valid ? -__expf(w0) : 0.f;
-          gown[n][2 * m + 1] = valid ? -__expf(w1) : 0.f;
+          gown[n][2 * m] = valid ? -LOG2E * ex2(LOG2E * w0) : 0.f;
+          gown[n][2 * m + 1] = valid ? -LOG2E * ex2(LOG2E * w1) : 0.f;
         }
         *reinterpret_cast<float4*>(&gs[row * NROW + 8 * cc]) = make_float4(gown[n][0], gown[n][1], gown[n][2], gown[n][3]);
         *reinterpret_cast<float4*>(&gs[row * NROW + 8 * cc + 4]) = make_float4(gown[n][4], gown[n][5], gown[n][6], gown[n][7]);
@@ -190,10 +192,10 @@ r7c_intra_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ w, con
       __syncthreads();
       if (tid < 64) {
         const float tot0 = sm.qtot[0][tid] + sm.qtot[1][tid], tot1 = sm.qtot[2][tid] + sm.qtot[3][tid];
-        ws_aux[(size_t)ch * AUX_FLOATS + tid] = __expf(fmaxf(tot0, -EXP_CLAMP));        // e^{gref}
-        ws_aux[(size_t)ch * AUX_FLOATS + 64 + tid] = __expf(fmaxf(tot1, -EXP_CLAMP));   // e^{glast-gref}
+        ws_aux[(size_t)ch * AUX_FLOATS + tid] = ex2(fmaxf(tot0, EXP2_FLOOR));        // e^{gref}
+        ws_aux[(size_t)ch * AUX_FLOATS + 64 + tid] = ex2(fmaxf(tot1, EXP2_FLOOR));   // e^{glast-gref}
         // a half-chunk decay sum beyond the limit: the unit is recomputed by the float32 recurrence
-        if (fminf(tot0, tot1) < -DECAY_LIMIT) ws_flags[bi * H + hi] = 1;
+        if (fminf(tot0, tot1) < -DECAY_LIMIT * LOG2E) ws_flags[bi * H + hi] = 1;
       }
       // the raw q, k, a, b: each thread scales its own 2 x 16 bytes in place (the previous chunk-head's W, U
       // copies, committed last, may still be reading their tiles: those are rewritten only after MMA 1)
@@ -250,7 +252,7 @@ r7c_intra_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ w, con
           for (int hh = 0; hh < 2; ++hh) {
             const int x = 2 * m + hh;
             const float d1 = gl[x];                                         // gi - gref
-            eq[hh] = cexp(d1); ek[hh] = cexp(-d1); ea[hh] = cexp(d1 - gown[n][x]);
+            eq[hh] = ex2(d1); ek[hh] = ex2(-d1); ea[hh] = ex2(d1 - gown[n][x]);
           }
           oq[m] = pack_bf16(bf16_lo(uq[m]) * eq[0], bf16_hi(uq[m]) * eq[1]);
           ok_[m] = pack_bf16(bf16_lo(uk[m]) * ek[0], bf16_hi(uk[m]) * ek[1]);

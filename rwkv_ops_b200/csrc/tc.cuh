@@ -251,6 +251,16 @@ __device__ __forceinline__ uint32_t tmem_addr(uint32_t base, uint32_t lane, uint
   return base + (lane << 16) + col;
 }
 
+// 2^x in one instruction.  The chunked kernels keep every decay sum in units of log 2 (g log2(e)), so that a
+// scale factor e^{sum} costs this one instruction and no multiplication.
+constexpr float LOG2E = 1.4426950408889634f;
+constexpr float LN2 = 0.6931471805599453f;
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 // ---------------------------------------------------------------------------------------------
 // small helpers for moving rows between registers and swizzled tiles
 // ---------------------------------------------------------------------------------------------

@@ -33,8 +33,8 @@ typedef __nv_bfloat16 bf16;
 
 constexpr int L = 64;
 constexpr int NROW = 68;
-constexpr float EXP_CLAMP = 80.f;
-__device__ __forceinline__ float cexp(float x) { return __expf(fminf(fmaxf(x, -EXP_CLAMP), EXP_CLAMP)); }
+// All decay sums are kept in units of log 2 (tc::ex2: a scale factor is one instruction); nothing is clamped.
+constexpr float EXP2_FLOOR = -126.f;      // 2^x below this is flushed to zero anyway
 // The scaled operands carry e^{+-(gi - gref)}, whose exponent reaches the sum of |g| over half a chunk.  Range
 // alone would allow about 60 (every factor, and the low half of every split operand, stays a normal number),
 // but the decay gradient is a difference of prefix sums that cancel the more the faster the state decays:
@@ -206,7 +206,9 @@ wkv6c_fwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
     for (int n = 0; n < 4; ++n) {
       const int e = tid + 256 * n, row = e >> 4, tok = t0 + row;
       float4 f = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (tok < Tn) f = make_float4(-__expf(gw[n].x), -__expf(gw[n].y), -__expf(gw[n].z), -__expf(gw[n].w));
+      if (tok < Tn)
+        f = make_float4(-LOG2E * ex2(LOG2E * gw[n].x), -LOG2E * ex2(LOG2E * gw[n].y), -LOG2E * ex2(LOG2E * gw[n].z),
+                        -LOG2E * ex2(LOG2E * gw[n].w));
       gw[n] = f;
       *reinterpret_cast<float4*>(&sm.gs[row * NROW + 4 * c4]) = f;
       store_split4(sm.vt[0], sm.vt[1], row, 4 * c4, vv4[n]);
@@ -234,10 +236,10 @@ wkv6c_fwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
     float e0 = 1.f, dlast = 1.f;
     if (!tok_lane) {
       const float tot0 = sm.qtot[0][srow] + sm.qtot[1][srow], tot1 = sm.qtot[2][srow] + sm.qtot[3][srow];
-      e0 = __expf(fmaxf(tot0, -EXP_CLAMP));
-      dlast = __expf(fmaxf(tot1, -EXP_CLAMP));
+      e0 = ex2(fmaxf(tot0, EXP2_FLOOR));
+      dlast = ex2(fmaxf(tot1, EXP2_FLOOR));
       // a half-chunk decay sum beyond the limit: the unit is recomputed by the float32 recurrence
-      if (hsel == 0 && fminf(tot0, tot1) < -DECAY_LIMIT) flags[unit] = 1;
+      if (hsel == 0 && fminf(tot0, tot1) < -DECAY_LIMIT * LOG2E) flags[unit] = 1;
     }
     // ---- S~0 = e^{gref} S0 stays in registers (fp32); hi/lo bf16 tiles for the r~ S~0 product
     if (!tok_lane) {
@@ -267,9 +269,9 @@ wkv6c_fwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
       const float4 r4 = rr4[n], k4 = kk4[n];
       const float4 gp = *reinterpret_cast<const float4*>(&sm.gs[row * NROW + 4 * c4]);
       const float d1x = gp.x, d1y = gp.y, d1z = gp.z, d1w = gp.w;   // gi - gref
-      const float4 rs = make_float4(r4.x * cexp(d1x - gw[n].x), r4.y * cexp(d1y - gw[n].y),
-                                    r4.z * cexp(d1z - gw[n].z), r4.w * cexp(d1w - gw[n].w));
-      const float4 ks = make_float4(k4.x * cexp(-d1x), k4.y * cexp(-d1y), k4.z * cexp(-d1z), k4.w * cexp(-d1w));
+      const float4 rs = make_float4(r4.x * ex2(d1x - gw[n].x), r4.y * ex2(d1y - gw[n].y),
+                                    r4.z * ex2(d1z - gw[n].z), r4.w * ex2(d1w - gw[n].w));
+      const float4 ks = make_float4(k4.x * ex2(-d1x), k4.y * ex2(-d1y), k4.z * ex2(-d1z), k4.w * ex2(-d1w));
       store_split4(sm.rt[0], sm.rt[1], row, 4 * c4, rs);
       store_split4(sm.kt[0], sm.kt[1], row, 4 * c4, ks);
       float dg = r4.x * u4.x * k4.x + r4.y * u4.y * k4.y + r4.z * u4.z * k4.z + r4.w * u4.w * k4.w;
@@ -414,7 +416,7 @@ struct BwdSmem {
   unsigned char st[2][TILE_BYTES];    // S~0           [k][v]
   unsigned char dst[2][TILE_BYTES];   // dS^           [k][v]
   float gs[L * NROW];                 // gi - gref (prefix of g relative to the reference point)
-  float gg[L * NROW];                 // g
+  float gg[L * NROW];                 // g log2(e)
   float red_e[L * NROW];              // dr~ r~
   float qtot[4][64];
   float rqtot[4][64];
@@ -530,7 +532,9 @@ wkv6c_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
         const int e = tid + 256 * n, row = e >> 4, tok = t0 + row;
         const float4 w4 = load4_shared(raw_w + row * 64 + 4 * c4);
         float4 f = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (tok < Tn) f = make_float4(-__expf(w4.x), -__expf(w4.y), -__expf(w4.z), -__expf(w4.w));
+        if (tok < Tn)
+          f = make_float4(-LOG2E * ex2(LOG2E * w4.x), -LOG2E * ex2(LOG2E * w4.y), -LOG2E * ex2(LOG2E * w4.z),
+                          -LOG2E * ex2(LOG2E * w4.w));
         gw[n] = f;
         *reinterpret_cast<float4*>(&sm.gg[row * NROW + 4 * c4]) = f;
         store_split4(sm.dyt[0], sm.dyt[1], row, 4 * c4, load4_shared(raw_dy + row * 64 + 4 * c4));
@@ -582,9 +586,9 @@ wkv6c_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
       const float4 r4 = rr4[n], k4 = kk4[n];
       const float4 gp = *reinterpret_cast<const float4*>(&sm.gs[row * NROW + 4 * c4]);
       const float d1x = gp.x, d1y = gp.y, d1z = gp.z, d1w = gp.w;   // gi - gref
-      const float4 rs = make_float4(r4.x * cexp(d1x - gw[n].x), r4.y * cexp(d1y - gw[n].y),
-                                    r4.z * cexp(d1z - gw[n].z), r4.w * cexp(d1w - gw[n].w));
-      const float4 ks = make_float4(k4.x * cexp(-d1x), k4.y * cexp(-d1y), k4.z * cexp(-d1z), k4.w * cexp(-d1w));
+      const float4 rs = make_float4(r4.x * ex2(d1x - gw[n].x), r4.y * ex2(d1y - gw[n].y),
+                                    r4.z * ex2(d1z - gw[n].z), r4.w * ex2(d1w - gw[n].w));
+      const float4 ks = make_float4(k4.x * ex2(-d1x), k4.y * ex2(-d1y), k4.z * ex2(-d1z), k4.w * ex2(-d1w));
       store_split4(sm.rt[0], sm.rt[1], row, 4 * c4, rs);
       store_split4(sm.kt[0], sm.kt[1], row, 4 * c4, ks);
       float dg = r4.x * u4.x * k4.x + r4.y * u4.y * k4.y + r4.z * u4.z * k4.z + r4.w * u4.w * k4.w;
@@ -655,8 +659,8 @@ wkv6c_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
       store_split_row32(hi_t, hi_t + TILE_BYTES, srow, 32 * hsel, x);
     }
     // decay factors of state row k = srow (both lanes of a pair work on that row below)
-    const float e0 = __expf(fmaxf(sm.qtot[0][srow] + sm.qtot[1][srow], -EXP_CLAMP));
-    const float dlast = __expf(fmaxf(sm.qtot[2][srow] + sm.qtot[3][srow], -EXP_CLAMP));
+    const float e0 = ex2(fmaxf(sm.qtot[0][srow] + sm.qtot[1][srow], EXP2_FLOOR));
+    const float dlast = ex2(fmaxf(sm.qtot[2][srow] + sm.qtot[3][srow], EXP2_FLOOR));
     // ---- state rows: the upper lane of a pair holds dS and takes dglast and dS^ = e^{glast-gref} dS_L,
     // the lower lane takes S~0 = e^{gref} S0; one split-and-store call serves both
     {
@@ -734,7 +738,7 @@ wkv6c_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
           const float d1 = gsv[m];                                   // gi - gref
           const float tt = th[j] + tl[j];                            // k~ (lower) / r~ (upper)
           const float x = __uint_as_float(r1[j]);                    // dk~ (lower) / dr~ (upper)
-          o[m] = x * cexp(lower ? -d1 : d1 - ggv[m]);                // dk = dk~ e^{gref-gi},  dr = dr~ e^{ge-gref}
+          o[m] = x * ex2(lower ? -d1 : d1 - ggv[m]);                 // dk = dk~ e^{gref-gi},  dr = dr~ e^{ge-gref}
           rd[m] = lower ? -x * tt : x * tt;                          // dgi = -dk~ k~,  dge = dr~ r~
         }
         if (lower) {
@@ -771,7 +775,7 @@ wkv6c_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
       for (int j = 0; j < 16; ++j) {
         const int ii = 16 * quarter + j;
         const float dg = rv[j] + add - sm.red_e[ii * NROW + ch];
-        stage_dw[ii * NROW + ch] = dg * sm.gg[ii * NROW + ch];
+        stage_dw[ii * NROW + ch] = dg * (LN2 * sm.gg[ii * NROW + ch]);      // dw = dg g, g = gg ln 2
       }
     }
     __syncthreads();
