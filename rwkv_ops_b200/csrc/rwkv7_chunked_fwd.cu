@@ -29,7 +29,7 @@ struct IntraSmem {
   unsigned char y[TILE_BYTES];                      // A_ak v
   float nmat[L * NROW];                             // stril(A_ab) in fp32
   float qtot[4][64];                                // sums of g over the four quarters of the chunk
-  uint64_t bar_v, bar_w, bar_in, bar_m1, bar_m2, bar_m3;
+  uint64_t bar_v, bar_w, bar_in, bar_ia, bar_m1, bar_m2, bar_m3;
   uint32_t tmem_base;
 };
 
@@ -60,7 +60,7 @@ r7c_intra_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ w, con
   const int wq = warp & 3, hsel = warp >> 2;
 
   if (tid == 0) {
-    mbar_init(&sm.bar_v, 1); mbar_init(&sm.bar_w, 1); mbar_init(&sm.bar_in, 1); mbar_init(&sm.bar_m1, 1); mbar_init(&sm.bar_m2, 1); mbar_init(&sm.bar_m3, 1);
+    mbar_init(&sm.bar_v, 1); mbar_init(&sm.bar_w, 1); mbar_init(&sm.bar_in, 1); mbar_init(&sm.bar_ia, 1); mbar_init(&sm.bar_m1, 1); mbar_init(&sm.bar_m2, 1); mbar_init(&sm.bar_m3, 1);
     fence_mbar_init();
   }
   if (warp == 0) tmem_alloc(&sm.tmem_base, 256);
@@ -79,14 +79,21 @@ r7c_intra_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ w, con
     mbar_expect_tx(&sm.bar_w, TILE_BYTES);
     tma_load_4d(sm.aqk, &tmap_w, &sm.bar_w, 0, sv.first<PACKED>(bi) + t0, hi, sv.row<PACKED>(bi));
   };
-  auto load_in = [&](const ChunkPos& p) {      // tid 0
+  // q, k, b land in tiles that only MMA 1 reads and are requested as soon as MMA 2 has completed (their
+  // copies to the workspace have left shared memory by then); a lands in the tile MMA 3 reads and is requested
+  // after it: both are on their way most of a chunk-head before the next one needs them.
+  auto load_qkb = [&](const ChunkPos& p) {     // tid 0
     int bi, hi, t0; coords(p, bi, hi, t0);
     const int tt = sv.first<PACKED>(bi) + t0, br = sv.row<PACKED>(bi);
-    mbar_expect_tx(&sm.bar_in, 4 * TILE_BYTES);
+    mbar_expect_tx(&sm.bar_in, 3 * TILE_BYTES);
     tma_load_4d(sm.qt, &tmap_q, &sm.bar_in, 0, tt, hi, br);
     tma_load_4d(sm.kt, &tmap_k, &sm.bar_in, 0, tt, hi, br);
-    tma_load_4d(sm.at, &tmap_a, &sm.bar_in, 0, tt, hi, br);
     tma_load_4d(sm.bt, &tmap_b, &sm.bar_in, 0, tt, hi, br);
+  };
+  auto load_a = [&](const ChunkPos& p) {       // tid 0
+    int bi, hi, t0; coords(p, bi, hi, t0);
+    mbar_expect_tx(&sm.bar_ia, TILE_BYTES);
+    tma_load_4d(sm.at, &tmap_a, &sm.bar_ia, 0, sv.first<PACKED>(bi) + t0, hi, sv.row<PACKED>(bi));
   };
   // chunk slots past the end of a (packed) sequence are skipped
   auto empty = [&](const ChunkPos& p) {
@@ -122,7 +129,7 @@ r7c_intra_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ w, con
   };
   ChunkPos cur = chunk_pos(blockIdx.x, NT, H);
   if (cur.ch < n_ch && empty(cur)) cur = advance(cur);
-  if (cur.ch < n_ch && tid == 0) { load_w(cur); load_in(cur); load_v(cur); }
+  if (cur.ch < n_ch && tid == 0) { load_w(cur); load_qkb(cur); load_a(cur); load_v(cur); }
   // The two CTAs that share an SM would otherwise run their phases in lockstep and compete for the
   // same unit (shared-memory pipe during the triangular solve); start every other CTA half a
   // chunk-head late.
@@ -197,10 +204,11 @@ r7c_intra_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ w, con
         // a half-chunk decay sum beyond the limit: the unit is recomputed by the float32 recurrence
         if (fminf(tot0, tot1) < -DECAY_LIMIT * LOG2E) ws_flags[bi * H + hi] = 1;
       }
-      // the raw q, k, a, b: each thread scales its own 2 x 16 bytes in place (the previous chunk-head's W, U
-      // copies, committed last, may still be reading their tiles: those are rewritten only after MMA 1)
+      // the raw q, k, a, b: each thread scales its own 2 x 16 bytes in place (the previous chunk-head's W, U,
+      // A_qb, O1 copies may still be reading their tiles: those are rewritten only after MMA 1)
       uint4 rq[2], rk[2], ra[2], rb[2];
       ok = mbar_wait(&sm.bar_in, par, status, 207) && ok;
+      ok = mbar_wait(&sm.bar_ia, par, status, 208) && ok;
 #pragma unroll
       for (int n = 0; n < 2; ++n) {
         const int e = tid + 256 * n;
@@ -280,6 +288,12 @@ r7c_intra_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ w, con
     ok = mbar_wait(&sm.bar_m1, par, status, 201) && ok;
     tc_fence_after();
     R7C_STAMP(3);
+    if (tid == 0 && ok) {      // MMA 1 was the last reader of q~, k~, b~ in shared memory: copy them out now
+      bulk_store(out_tiles + S_QT * TILE_BYTES, sm.qt, TILE_BYTES);
+      bulk_store(out_tiles + S_KT * TILE_BYTES, sm.kt, TILE_BYTES);
+      bulk_store(out_tiles + S_BT * TILE_BYTES, sm.bt, TILE_BYTES);
+      bulk_commit();
+    }
     if (ok) {
       const int r = 32 * wq + lane, i = r & 63;
       const bool lower = r >= 64;       // rows of a~: strictly lower triangle; rows of q~: lower incl. diagonal
@@ -386,8 +400,8 @@ r7c_intra_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ w, con
       // the scratch area: MMA 2 (and the copies of A_qk / A_ak kept for the backward) must be done with it
       ok = mbar_wait(&sm.bar_m2, par, status, 205) && ok;
       if (tid == 0) {
-        if (keep_for_bwd) bulk_wait_read();
-        if (next < n_ch) load_v(nxt);      // MMA 2 has read the v tile: request the next one
+        bulk_wait_read();                  // q~, k~, b~ (and the tiles kept for the backward) have left shared memory
+        if (next < n_ch) { load_v(nxt); load_qkb(nxt); }      // MMA 2 has read the v tile; nothing reads q~, k~, b~ any more
       }
       __syncthreads();
       R7C_STAMP(10);
@@ -495,9 +509,6 @@ r7c_intra_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ w, con
       umma_tile<64, 64, 0, 1>(tmem_addr(tm, 0, 0), smem_u32(sm.ainv), smem_u32(sm.at), false);
       umma_tile<64, 64, 0, 1>(tmem_addr(tm, 16, 0), smem_u32(sm.ainv), smem_u32(sm.y), false);
       umma_commit(&sm.bar_m3);
-      bulk_store(out_tiles + S_QT * TILE_BYTES, sm.qt, TILE_BYTES);
-      bulk_store(out_tiles + S_KT * TILE_BYTES, sm.kt, TILE_BYTES);
-      bulk_store(out_tiles + S_BT * TILE_BYTES, sm.bt, TILE_BYTES);
       bulk_store(out_tiles + S_AQB * TILE_BYTES, sm.aqb, TILE_BYTES);
       bulk_store(out_tiles + S_O1 * TILE_BYTES, sm.o1, TILE_BYTES);
       if (keep_for_bwd) bulk_store(out_tiles + S_AINV * TILE_BYTES, sm.ainv, TILE_BYTES);
@@ -527,9 +538,8 @@ r7c_intra_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ w, con
       bulk_store(out_tiles + S_W * TILE_BYTES, sm.aak, TILE_BYTES);
       bulk_store(out_tiles + S_U * TILE_BYTES, sm.y, TILE_BYTES);
       bulk_commit();
-      // every copy but the two just committed has left shared memory (q~, k~, a~, b~ among them), and MMA 3
-      // has read a~: the next raw tiles may land
-      if (next < n_ch) { bulk_wait_read_1(); load_in(nxt); }
+      // MMA 3 has read a~ (and its copy for the backward left shared memory long ago): the next raw a may land
+      if (next < n_ch) load_a(nxt);
     }
     R7C_STAMP(9);
   }
