@@ -121,6 +121,25 @@ def check_status(what: str) -> None:
                                 "the results of this call are not valid")
 
 
+def _a256(x: int) -> int:
+    return (x + 255) & ~255
+
+
+def rwkv7_kept_bytes(n_seq: int, max_len: int, H: int) -> int:
+    """Size of the tile store a training forward of the chunked RWKV7 path hands to its backward: the value of
+    ``rwkvb200_rwkv7_fwd_workspace_bytes(..., ALGO_KEEP)`` without calling into the library (the shape
+    functions of the custom ops must run without a device)."""
+    n = n_seq * H * ((max_len + 63) // 64)
+    return _a256(n * 18 * 8192) + _a256(n * 128 * 4) + _a256(n_seq * H * 4) + 1024
+
+
+def wkv6_kept_bytes(B: int, T: int, H: int) -> int:
+    """Likewise for ``rwkvb200_wkv6_fwd_workspace_bytes(..., ALGO_KEEP)``."""
+    nt = (T + 63) // 64
+    return (_a256(B * H * (nt + 1) * 64 * 64 * 4) + _a256(B * H * 64 * 4) + _a256(B * H * 4 * 64 * 4)
+            + _a256(B * H * 4))
+
+
 def strerror(code: int) -> str:
     return load().rwkvb200_strerror(code).decode()
 

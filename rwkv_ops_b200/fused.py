@@ -60,7 +60,8 @@ def _fused_fwd(r: torch.Tensor, w_pre: torch.Tensor, k: torch.Tensor, v: torch.T
 @_fused_fwd.register_fake
 def _(r, w_pre, k, v, kk_pre, a_pre, h0, keep):
     B, T, H, K = r.shape
-    return torch.empty_like(r), r.new_empty((B, H, K, K), dtype=torch.float32), r.new_empty((1,), dtype=torch.uint8)
+    return (torch.empty_like(r), r.new_empty((B, H, K, K), dtype=torch.float32),
+            r.new_empty((_lib.rwkv7_kept_bytes(B, T, H) if keep else 1,), dtype=torch.uint8))
 
 
 # `kept` also serves as scratch for the backward kernels; the tiles the forward left in it are not changed.

@@ -57,8 +57,10 @@ def _wkv6_fwd(r: torch.Tensor, k: torch.Tensor, v: torch.Tensor, w: torch.Tensor
 @_wkv6_fwd.register_fake
 def _(r, k, v, w, u, s0, state_map, algo, keep):
     B, T, C = r.shape
-    return (torch.empty_like(r), r.new_empty((B, C // HEAD_SIZE, HEAD_SIZE, HEAD_SIZE), dtype=torch.float32),
-            r.new_empty((0,), dtype=torch.uint8))
+    H = C // HEAD_SIZE
+    chunked = (algo & 0xff) != _lib.ALGO_RECURRENT
+    return (torch.empty_like(r), r.new_empty((B, H, HEAD_SIZE, HEAD_SIZE), dtype=torch.float32),
+            r.new_empty((_lib.wkv6_kept_bytes(B, T, H) if keep and chunked else 0,), dtype=torch.uint8))
 
 
 # `kept` (the forward's chunk-boundary states) also holds the backward's scratch rows; what the forward

@@ -121,7 +121,7 @@ def _(r, w, k, v, a, b, h0, head_first, algo):
     else:
         B, T, H, K = r.shape
     return (torch.empty_like(r), r.new_empty((B, H, K, K), dtype=torch.float32),
-            r.new_empty((1,), dtype=torch.uint8))
+            r.new_empty((_lib.rwkv7_kept_bytes(B, T, H),), dtype=torch.uint8))
 
 
 # `kept` also serves as scratch for the backward kernels; the tiles the forward left in it are not changed.

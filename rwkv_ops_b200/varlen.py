@@ -71,8 +71,9 @@ def _fwd_varlen(r: torch.Tensor, w: torch.Tensor, k: torch.Tensor, v: torch.Tens
 @_fwd_varlen.register_fake
 def _(r, w, k, v, a, b, seq_start, seq_len, max_len, h0, keep):
     _, T, H, K = r.shape
-    return (torch.empty_like(r), r.new_empty((seq_start.numel(), H, K, K), dtype=torch.float32),
-            r.new_empty((1,), dtype=torch.uint8))
+    n_seq = seq_start.numel()
+    return (torch.empty_like(r), r.new_empty((n_seq, H, K, K), dtype=torch.float32),
+            r.new_empty((_lib.rwkv7_kept_bytes(n_seq, max_len, H) if keep else 1,), dtype=torch.uint8))
 
 
 # `kept` also serves as scratch for the backward kernels; the tiles the forward left in it are not changed.

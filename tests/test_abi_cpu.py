@@ -95,3 +95,14 @@ def test_reference_api_surface():
     assert list(sig6.parameters) == ["self", "r", "k", "v", "w", "u", "with_state", "init_state", "state_map"]
     assert list(inspect.signature(ro.RWKV6_OP.__init__).parameters) == ["self", "head_size", "max_sequence_length", "ops_loop"]
     assert ro.get_rwkv6_kernel("cuda") is ro.RWKV6_OP
+
+
+def test_python_mirrors_of_the_kept_sizes_match_the_library(lib):
+    """The shape functions of the custom ops (register_fake) size the tile store a training forward returns
+    without calling the library; they must agree with it."""
+    keep = _lib.ALGO_KEEP
+    for (B, T, H) in [(1, 1, 1), (2, 64, 3), (3, 65, 2), (8, 4096, 32), (5, 1000, 7)]:
+        assert _lib.rwkv7_kept_bytes(B, T, H) == lib.rwkvb200_rwkv7_fwd_workspace_bytes(B, T, H, 64, _lib.BF16, keep)
+        assert _lib.rwkv7_kept_bytes(B, T, H) == lib.rwkvb200_rwkv7_varlen_workspace_bytes(B, T, H, 64, 1)
+        assert _lib.wkv6_kept_bytes(B, T, H) == lib.rwkvb200_wkv6_fwd_workspace_bytes(B, T, H, 64, _lib.F32, keep)
+        assert _lib.wkv6_kept_bytes(B, T, H) == lib.rwkvb200_wkv6_bwd_workspace_bytes(B, T, H, 64, _lib.F32, 0)
