@@ -29,7 +29,7 @@ struct IntraSmem {
   unsigned char y[TILE_BYTES];                      // A_ak v
   float nmat[L * NROW];                             // stril(A_ab) in fp32
   float qtot[4][64];                                // sums of g over the four quarters of the chunk
-  uint64_t bar_v, bar_w, bar_in, bar_ia, bar_m1, bar_m2, bar_m3;
+  uint64_t bar_v, bar_w, bar_in, bar_ia, bar_m1, bar_m2, bar_m3, bar_m4, bar_m5;
   uint32_t tmem_base;
 };
 
@@ -61,6 +61,7 @@ r7c_intra_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ w, con
 
   if (tid == 0) {
     mbar_init(&sm.bar_v, 1); mbar_init(&sm.bar_w, 1); mbar_init(&sm.bar_in, 1); mbar_init(&sm.bar_ia, 1); mbar_init(&sm.bar_m1, 1); mbar_init(&sm.bar_m2, 1); mbar_init(&sm.bar_m3, 1);
+    mbar_init(&sm.bar_m4, 1); mbar_init(&sm.bar_m5, 1);
     fence_mbar_init();
   }
   if (warp == 0) tmem_alloc(&sm.tmem_base, 256);
@@ -338,14 +339,13 @@ r7c_intra_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ w, con
         bulk_commit();
       }
     }
-    // ---- rows of MMA 2 (warps 2-7), then Ainv = X = (I - N)^-1, N = stril(A_ab), in fp32 on all eight warps,
-    // by two levels of block inversion (everything below happens in place in nmat):
-    //   D. the four 16 x 16 diagonal blocks D_I = (I - N_II)^-1, one column per thread, row by row -- the
-    //      only substitutions, all four side by side;
-    //   1. the two 32 x 32 diagonal blocks: X_10 = D_1 (N_10 D_0) and X_32 = D_3 (N_32 D_2), 64 threads each;
-    //   2. T = N_BA X_A (A = rows 0..31, B = rows 32..63), four entries per thread on all 256 threads;
-    //   3. X_BA = X_B T, likewise.
-    // P = N_IJ D_J and T pass through the A_qk / A_ak tiles, free once MMA 2 has read them.
+    // ---- rows of MMA 2 (warps 2-7), then Ainv = X = (I - N)^-1, N = stril(A_ab), by two levels of block
+    // inversion:
+    //   D. the four 16 x 16 diagonal blocks D_I = (I - N_II)^-1 in fp32, one column per thread, row by row --
+    //      the only substitutions, all four side by side (in place in nmat);
+    //   1. the two 32 x 32 diagonal blocks in fp32: X_10 = D_1 (N_10 D_0) and X_32 = D_3 (N_32 D_2), 64 threads
+    //      each (in place; P = N_IJ D_J passes through the A_qk tile, free once MMA 2 has read it);
+    //   2., 3. the last block X_BA = X_B N_BA X_A (A = rows 0..31, B = rows 32..63) as two tensor-core products.
     {
       const int c = tid & 63, I = tid >> 6;
       float* scratch = reinterpret_cast<float*>(sm.aqk);
@@ -445,53 +445,63 @@ r7c_intra_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ w, con
       }
       __syncthreads();
       R7C_STAMP(11);
-      float* Tm = scratch;       // T[32][33]
-      {                          // step 2, and the three finished quadrants of Ainv as bf16
-        const int r0 = 4 * warp;
-        float col[32], acc[4];
+      // steps 2 and 3 on the tensor cores.  With P = diag(X_A, X_B) (the two finished 32 x 32 blocks) and
+      // Q = [0 0; N_BA 0], the missing block is X_BA = (P Q P)_BA: T = Q P, then P T, two 64x64x64 products
+      // of bf16 operands (N_BA is a small correction: rounding it, X_A, X_B and T to bf16 changes the rounded
+      // inverse by less than the rounding of the inverse itself).  P is the Ainv tile with a zero BA
+      // quadrant; Q and T pass through the A_qk / A_ak tiles, free since MMA 2.
 #pragma unroll
-        for (int kk = 0; kk < 32; ++kk) col[kk] = sm.nmat[kk * NROW + lane];                 // X_A[:, lane]
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const float* nrow = &sm.nmat[(32 + r0 + q) * NROW];
-          float s_ = 0.f;
-#pragma unroll
-          for (int jj = 0; jj < 8; ++jj) {
-            const float4 n = *reinterpret_cast<const float4*>(nrow + 4 * jj);
-            s_ += n.x * col[4 * jj] + n.y * col[4 * jj + 1] + n.z * col[4 * jj + 2] + n.w * col[4 * jj + 3];
-          }
-          acc[q] = s_;
-        }
-#pragma unroll
-        for (int q = 0; q < 4; ++q) Tm[(r0 + q) * 33 + lane] = acc[q];
-#pragma unroll
-        for (int n = 0; n < 2; ++n) {
-          const int e = tid + 256 * n, row = e >> 3, cc = e & 7;
-          if (row < 32 || cc >= 4) {
-            const float4 f0 = *reinterpret_cast<const float4*>(&sm.nmat[row * NROW + 8 * cc]);
-            const float4 f1 = *reinterpret_cast<const float4*>(&sm.nmat[row * NROW + 8 * cc + 4]);
-            *reinterpret_cast<uint4*>(sm.ainv + tile_chunk_off(row, cc)) =
-                make_uint4(pack_bf16(f0.x, f0.y), pack_bf16(f0.z, f0.w), pack_bf16(f1.x, f1.y), pack_bf16(f1.z, f1.w));
-          }
-        }
+      for (int n = 0; n < 2; ++n) {
+        const int e = tid + 256 * n, row = e >> 3, cc = e & 7;
+        const float4 f0 = *reinterpret_cast<const float4*>(&sm.nmat[row * NROW + 8 * cc]);
+        const float4 f1 = *reinterpret_cast<const float4*>(&sm.nmat[row * NROW + 8 * cc + 4]);
+        const uint4 val = make_uint4(pack_bf16(f0.x, f0.y), pack_bf16(f0.z, f0.w), pack_bf16(f1.x, f1.y), pack_bf16(f1.z, f1.w));
+        const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+        const bool ba = row >= 32 && cc < 4;
+        *reinterpret_cast<uint4*>(sm.ainv + tile_chunk_off(row, cc)) = ba ? zero : val;
+        *reinterpret_cast<uint4*>(sm.aqk + tile_chunk_off(row, cc)) = ba ? val : zero;
       }
+      fence_async_smem();
+      tc_fence_before();
       __syncthreads();
       R7C_STAMP(12);
-      {                          // step 3
-        const int r0 = 4 * warp;
-        float col[32];
+      if (tid == 0) {
+        tc_fence_after();
+        umma_tile<64, 64, 0, 1>(tmem_addr(tm, 0, 128), smem_u32(sm.aqk), smem_u32(sm.ainv), false);     // T = Q P
+        umma_commit(&sm.bar_m4);
+      }
+      ok = mbar_wait(&sm.bar_m4, par, status, 209) && ok;
+      tc_fence_after();
+      if (ok) {
+        uint32_t rr[32];
+        tmem_ld32(tmem_addr(tm, 32 * wq, 128 + 32 * hsel), rr);
+        tmem_ld_wait();
+        if (lane < 16) {        // an M = 64 accumulator lives on the lower 16 lanes of every warp's window
+          float x[32];
 #pragma unroll
-        for (int kk = 0; kk < 32; ++kk) col[kk] = Tm[kk * 33 + lane];
+          for (int j = 0; j < 32; ++j) x[j] = __uint_as_float(rr[j]);
+          tile_store_row32(sm.aak, 16 * wq + lane, 32 * hsel, x);
+        }
+      }
+      fence_async_smem();
+      tc_fence_before();
+      ok = __syncthreads_and(ok);
+      if (tid == 0 && ok) {
+        tc_fence_after();
+        umma_tile<64, 64, 0, 1>(tmem_addr(tm, 0, 128), smem_u32(sm.ainv), smem_u32(sm.aak), false);     // P T
+        umma_commit(&sm.bar_m5);
+      }
+      ok = mbar_wait(&sm.bar_m5, par, status, 210) && ok;
+      tc_fence_after();
+      if (ok && hsel == 0) {      // rows 32..63, columns 0..31: the BA quadrant of Ainv
+        uint32_t rr[32];
+        tmem_ld32(tmem_addr(tm, 32 * wq, 128), rr);
+        tmem_ld_wait();
+        if (lane < 16 && wq >= 2) {
+          float x[32];
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const float* xrow = &sm.nmat[(32 + r0 + q) * NROW + 32];        // X_B row (zeros above the diagonal)
-          float s_ = 0.f;
-#pragma unroll
-          for (int jj = 0; jj < 8; ++jj) {
-            const float4 n = *reinterpret_cast<const float4*>(xrow + 4 * jj);
-            s_ += n.x * col[4 * jj] + n.y * col[4 * jj + 1] + n.z * col[4 * jj + 2] + n.w * col[4 * jj + 3];
-          }
-          *reinterpret_cast<bf16*>(sm.ainv + tile_off(32 + r0 + q, lane)) = __float2bfloat16_rn(s_);
+          for (int j = 0; j < 32; ++j) x[j] = __uint_as_float(rr[j]);
+          tile_store_row32(sm.ainv, 16 * wq + lane, 0, x);
         }
       }
       R7C_STAMP(13);
