@@ -28,30 +28,33 @@ __device__ __forceinline__ void store_row32_global(bf16* dst, const float* x) {
 }
 
 // ---------------------------------------------------------------------------------------------
-// 3. B2 = Ainv^T b~ and P2 = Ainv^T (A_qb^T do): grid = B*H*NT, 128 threads
+// 3. B2 = Ainv^T b~ and P2 = Ainv^T (A_qb^T do): persistent CTAs of 128 threads over the chunk-heads
 // ---------------------------------------------------------------------------------------------
-struct PreSmem {
+struct PreStage {
   unsigned char ainv[TILE_BYTES], bt[TILE_BYTES], aqb[TILE_BYTES], dout[TILE_BYTES];
+};
+struct PreSmem {
+  PreStage st[2];             // the operand tiles of this chunk-head and of the next one
   unsigned char p1[TILE_BYTES], b2[TILE_BYTES], p2[TILE_BYTES];
-  uint64_t bar_ld, bar_m1, bar_m2;
+  uint64_t bar_ld[2], bar_m1, bar_m2;
   uint32_t tmem_base;
 };
 
+// Two CTAs per SM walk over chunk-heads ch = blockIdx.x, blockIdx.x + gridDim.x, ...; the four operand tiles
+// of the next chunk-head are requested before the current one is worked on, so that loads, the two dependent
+// MMAs and the copies of the results overlap.
 template <bool PACKED>
 __global__ void __launch_bounds__(128)
 r7c_bwd_pre_kernel(const __grid_constant__ CUtensorMap tmap_do, unsigned char* __restrict__ ws_tiles,
-                   int tiles_per_chunk, SeqView sv, int H, int NT, int* status) {
+                   int tiles_per_chunk, SeqView sv, int H, int NT, int n_ch, int* status) {
   extern __shared__ unsigned char smem_raw[];
   PreSmem& sm = *reinterpret_cast<PreSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int ch = blockIdx.x, unit = ch / NT, cidx = ch % NT, bi = unit / H, hi = unit % H;
-  if (cidx * L >= sv.length<PACKED>(bi)) return;      // a chunk slot past the end of a packed sequence
-  unsigned char* tiles = ws_tiles + (size_t)ch * tiles_per_chunk * TILE_BYTES;
   const int row = 16 * warp + (lane & 15);
   const bool lo = lane < 16;
 
   if (tid == 0) {
-    mbar_init(&sm.bar_ld, 1); mbar_init(&sm.bar_m1, 1); mbar_init(&sm.bar_m2, 1);
+    mbar_init(&sm.bar_ld[0], 1); mbar_init(&sm.bar_ld[1], 1); mbar_init(&sm.bar_m1, 1); mbar_init(&sm.bar_m2, 1);
     fence_mbar_init();
   }
   if (warp == 0) tmem_alloc(&sm.tmem_base, 128);
@@ -59,67 +62,96 @@ r7c_bwd_pre_kernel(const __grid_constant__ CUtensorMap tmap_do, unsigned char* _
   __syncthreads();
   tc_fence_after();
   const uint32_t tm = sm.tmem_base;
-  if (tid == 0) {
-    mbar_expect_tx(&sm.bar_ld, 4 * TILE_BYTES);
-    bulk_load(sm.ainv, tiles + S_AINV * TILE_BYTES, TILE_BYTES, &sm.bar_ld);
-    bulk_load(sm.bt, tiles + S_BT * TILE_BYTES, TILE_BYTES, &sm.bar_ld);
-    bulk_load(sm.aqb, tiles + S_AQB * TILE_BYTES, TILE_BYTES, &sm.bar_ld);
-    tma_load_4d(sm.dout, &tmap_do, &sm.bar_ld, 0, sv.first<PACKED>(bi) + cidx * L, hi, sv.row<PACKED>(bi));
-  }
-  bool ok = mbar_wait(&sm.bar_ld, 0, status, 301);
-  if (tid == 0 && ok) {
-    tc_fence_after();
-    umma_tile<64, 64, 1, 1>(tmem_addr(tm, 0, 0), smem_u32(sm.aqb), smem_u32(sm.dout), false);   // A_qb^T do
-    umma_tile<64, 64, 1, 1>(tmem_addr(tm, 16, 0), smem_u32(sm.ainv), smem_u32(sm.bt), false);   // Ainv^T b~
-    umma_commit(&sm.bar_m1);
-  }
-  ok = mbar_wait(&sm.bar_m1, 0, status, 302) && ok;
-  tc_fence_after();
-  if (ok) {
-#pragma unroll
-    for (int part = 0; part < 2; ++part) {
-      uint32_t r[32];
-      tmem_ld32(tmem_addr(tm, 32 * warp, 32 * part), r);
-      tmem_ld_wait();
-      float x[32];
-#pragma unroll
-      for (int j = 0; j < 32; ++j) x[j] = __uint_as_float(r[j]);
-      tile_store_row32(lo ? sm.p1 : sm.b2, row, 32 * part, x);
+
+  auto empty = [&](const ChunkPos& p) {
+    if constexpr (!PACKED) return false;
+    return p.c * L >= sv.length<PACKED>(p.bi);      // a chunk slot past the end of a packed sequence
+  };
+  auto advance = [&](ChunkPos p) {
+    do { chunk_step(p, gridDim.x, NT, H); } while (p.ch < n_ch && empty(p));
+    return p;
+  };
+  auto issue_loads = [&](const ChunkPos& p, int s) {      // tid 0
+    const unsigned char* tiles = ws_tiles + (size_t)p.ch * tiles_per_chunk * TILE_BYTES;
+    PreStage& g = sm.st[s];
+    mbar_expect_tx(&sm.bar_ld[s], 4 * TILE_BYTES);
+    bulk_load(g.ainv, tiles + S_AINV * TILE_BYTES, TILE_BYTES, &sm.bar_ld[s]);
+    bulk_load(g.bt, tiles + S_BT * TILE_BYTES, TILE_BYTES, &sm.bar_ld[s]);
+    bulk_load(g.aqb, tiles + S_AQB * TILE_BYTES, TILE_BYTES, &sm.bar_ld[s]);
+    tma_load_4d(g.dout, &tmap_do, &sm.bar_ld[s], 0, sv.first<PACKED>(p.bi) + p.c * L, p.hi, sv.row<PACKED>(p.bi));
+  };
+  ChunkPos cur = chunk_pos(blockIdx.x, NT, H);
+  if (cur.ch < n_ch && empty(cur)) cur = advance(cur);
+  if (cur.ch < n_ch && tid == 0) issue_loads(cur, 0);
+
+  bool ok = true;
+  int it = 0;
+  for (ChunkPos nxt; cur.ch < n_ch && ok; cur = nxt, ++it) {
+    const int s = it & 1;
+    const uint32_t par = it & 1;
+    PreStage& g = sm.st[s];
+    unsigned char* tiles = ws_tiles + (size_t)cur.ch * tiles_per_chunk * TILE_BYTES;
+    nxt = advance(cur);
+    // the other stage was last read by the MMAs of the previous chunk-head, which have completed
+    if (tid == 0 && nxt.ch < n_ch) issue_loads(nxt, s ^ 1);
+    ok = mbar_wait(&sm.bar_ld[s], (it >> 1) & 1, status, 301);
+    if (tid == 0 && ok) {
+      bulk_wait_read();      // the copies of the previous B2 / P2 have left their tiles, which are rewritten below
+      tc_fence_after();
+      umma_tile<64, 64, 1, 1>(tmem_addr(tm, 0, 0), smem_u32(g.aqb), smem_u32(g.dout), false);   // A_qb^T do
+      umma_tile<64, 64, 1, 1>(tmem_addr(tm, 16, 0), smem_u32(g.ainv), smem_u32(g.bt), false);   // Ainv^T b~
+      umma_commit(&sm.bar_m1);
     }
-  }
-  fence_async_smem();
-  tc_fence_before();
-  __syncthreads();
-  if (tid == 0 && ok) {
+    ok = mbar_wait(&sm.bar_m1, par, status, 302) && ok;
     tc_fence_after();
-    umma_tile<64, 64, 1, 1>(tmem_addr(tm, 0, 64), smem_u32(sm.ainv), smem_u32(sm.p1), false);   // Ainv^T P1
-    umma_commit(&sm.bar_m2);
-    bulk_store(tiles + S_B2 * TILE_BYTES, sm.b2, TILE_BYTES);
-    bulk_commit();
-  }
-  ok = mbar_wait(&sm.bar_m2, 0, status, 303) && ok;
-  tc_fence_after();
-  if (ok) {
+    if (ok) {
 #pragma unroll
-    for (int part = 0; part < 2; ++part) {
-      uint32_t r[32];
-      tmem_ld32(tmem_addr(tm, 32 * warp, 64 + 32 * part), r);
-      tmem_ld_wait();
-      if (lo) {
+      for (int part = 0; part < 2; ++part) {
+        uint32_t r[32];
+        tmem_ld32(tmem_addr(tm, 32 * warp, 32 * part), r);
+        tmem_ld_wait();
         float x[32];
 #pragma unroll
         for (int j = 0; j < 32; ++j) x[j] = __uint_as_float(r[j]);
-        tile_store_row32(sm.p2, row, 32 * part, x);
+        tile_store_row32(lo ? sm.p1 : sm.b2, row, 32 * part, x);
       }
     }
+    fence_async_smem();
+    tc_fence_before();
+    ok = __syncthreads_and(ok);
+    if (tid == 0 && ok) {
+      tc_fence_after();
+      umma_tile<64, 64, 1, 1>(tmem_addr(tm, 0, 64), smem_u32(g.ainv), smem_u32(sm.p1), false);   // Ainv^T P1
+      umma_commit(&sm.bar_m2);
+      bulk_store(tiles + S_B2 * TILE_BYTES, sm.b2, TILE_BYTES);
+      bulk_commit();
+    }
+    ok = mbar_wait(&sm.bar_m2, par, status, 303) && ok;
+    tc_fence_after();
+    if (ok) {
+#pragma unroll
+      for (int part = 0; part < 2; ++part) {
+        uint32_t r[32];
+        tmem_ld32(tmem_addr(tm, 32 * warp, 64 + 32 * part), r);
+        tmem_ld_wait();
+        if (lo) {
+          float x[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) x[j] = __uint_as_float(r[j]);
+          tile_store_row32(sm.p2, row, 32 * part, x);
+        }
+      }
+    }
+    fence_async_smem();
+    tc_fence_before();
+    ok = __syncthreads_and(ok);
+    if (tid == 0 && ok) {
+      bulk_store(tiles + S_P2 * TILE_BYTES, sm.p2, TILE_BYTES);
+      bulk_commit();
+    }
   }
-  fence_async_smem();
+  if (tid == 0) bulk_wait_all();
   tc_fence_before();
-  __syncthreads();
-  if (tid == 0) {
-    if (ok) { bulk_store(tiles + S_P2 * TILE_BYTES, sm.p2, TILE_BYTES); bulk_commit(); }
-    bulk_wait_all();
-  }
   __syncthreads();
   if (warp == 0) tmem_dealloc(tm, 128);
 }
@@ -753,11 +785,15 @@ int launch_rwkv7_chunked_bwd(const void* r, const void* w, const void* k, const 
 #define R7C_DISPATCH_PACKED(...) do { if (seq_start) { constexpr bool P = true; __VA_ARGS__; } else { constexpr bool P = false; __VA_ARGS__; } } while (0)
   if (phases & PHASE_PREPARE) {
     const int smem = (int)sizeof(PreSmem) + 1024;
+    int dev = 0, sms = 0;
+    if (cuda_ok(cudaGetDevice(&dev)) || cuda_ok(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)))
+      return RWKVB200_E_CUDA;
+    const int pre_grid = B * H * NT < 2 * sms ? B * H * NT : 2 * sms;     // persistent: two CTAs per SM
     ProfScope prof("r7c_bwd_pre_kernel", st);
     R7C_DISPATCH_PACKED(
       if (cuda_ok(cudaFuncSetAttribute(r7c_bwd_pre_kernel<P>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)))
         return RWKVB200_E_CUDA;
-      r7c_bwd_pre_kernel<P><<<B * H * NT, 128, smem, st>>>(tmap_do, ws.tiles, ALL_TILES, sv, H, NT, status));
+      r7c_bwd_pre_kernel<P><<<pre_grid, 128, smem, st>>>(tmap_do, ws.tiles, ALL_TILES, sv, H, NT, B * H * NT, status));
   }
   e = check_launch();
   if (e) return e;
