@@ -142,3 +142,28 @@ def test_wkv6_inference_forward_out_of_range():
     with torch.no_grad():
         y, s = ro.RWKV6_OP(64, T)(*[d[n].cuda() for n in "rkvwu"], with_state=True)
     assert rel_l2(y, y_ref) < 1e-4 and rel_l2(s, s_ref) < 1e-4
+
+
+def test_rwkv7_out_of_range_units_with_head_first_layout_and_broadcast_state():
+    """The recomputation of out-of-range units reads [B, H, T, 64] tensors and a broadcast initial state as
+    the tensor-core kernels do: same results as the [B, T, H, 64] call on permuted tensors."""
+    B, T, H = 2, 150, 3
+    d = rwkv7_inputs(B, T, H, dtype=torch.bfloat16, seed=4500, with_state=True, n_state=1, with_grads=True)
+    d["w"] = _w_rwkv7("one_unit_fast", d["w"].shape, torch.Generator().manual_seed(6)).to(torch.bfloat16)
+
+    def run(head_first):
+        perm = (lambda t: t.permute(0, 2, 1, 3).contiguous()) if head_first else (lambda t: t)
+        g = {n: perm(d[n].cuda()).requires_grad_(True) for n in "rwkvab"}
+        h0 = d["initial_state"].cuda().requires_grad_(True)
+        o, s = ro.generalized_delta_rule(*[g[n] for n in "rwkvab"], initial_state=h0, head_first=head_first)
+        torch.autograd.backward([o, s], [perm(d["d_out"].cuda()), d["d_state"].cuda()])
+        return perm(o), s, {n: perm(g[n].grad) for n in "rwkvab"}, h0.grad
+
+    o0, s0, g0, dh0 = run(False)
+    o1, s1, g1, dh1 = run(True)
+    assert torch.equal(o0, o1) and torch.equal(s0, s1) and torch.equal(dh0, dh1)
+    for n in "rwkvab":
+        assert torch.equal(g0[n], g1[n]), n
+    ref = {n: d[n].float().clone().requires_grad_(True) for n in "rwkvab"}
+    o_ref, s_ref = oracle_gdr(*[ref[n] for n in "rwkvab"], initial_state=d["initial_state"])
+    assert rel_l2(o0, o_ref) < 2e-2 and rel_l2(s0, s_ref) < 2e-2

@@ -133,3 +133,41 @@ def test_varlen_rejects_bad_arguments():
         generalized_delta_rule_varlen(*x, [0, 10, 10, 20])     # an empty sequence
     with pytest.raises(ValueError):
         generalized_delta_rule_varlen(*[t.expand(2, -1, -1, -1) for t in x], [0, 20])
+
+
+@pytest.mark.parametrize("bcast", [False, True])
+def test_varlen_with_decays_beyond_the_range_of_the_chunked_kernels(bcast):
+    """Packed sequences of which some decay too fast for the tensor-core kernels (w ~ 1 + 0.3 N(0,1) in one
+    sequence for all heads, and in one head of another): those (sequence, head) units are recomputed by the
+    float32 recurrence inside the call, reading their tokens at the sequence's offset in the packed row."""
+    from rwkv_ops_b200 import generalized_delta_rule_varlen
+    H, lens = 3, [70, 131, 64, 200]
+    T = sum(lens)
+    cu = [0]
+    for n in lens:
+        cu.append(cu[-1] + n)
+    d = rwkv7_inputs(1, T, H, dtype=torch.bfloat16, seed=4343)
+    gen = torch.Generator().manual_seed(11)
+    fast = (1.0 + 0.3 * torch.randn(1, T, H, 64, generator=gen)).bfloat16()
+    d["w"][:, cu[1]:cu[2]] = fast[:, cu[1]:cu[2]]              # sequence 1, every head
+    d["w"][:, cu[3]:cu[4], 2] = fast[:, cu[3]:cu[4], 2]        # sequence 3, head 2
+    n_state = 1 if bcast else len(lens)
+    h0 = 0.1 * torch.randn(n_state, H, 64, 64, generator=gen)
+    d_out = torch.randn(1, T, H, 64, generator=gen).bfloat16()
+    d_state = 0.1 * torch.randn(len(lens), H, 64, 64, generator=gen)
+    o_ref, s_ref, g_ref, dh_ref = _oracle_per_sequence(d, cu, h0, d_out, d_state)
+
+    g = {n: d[n].cuda().requires_grad_(True) for n in NAMES}
+    h = h0.cuda().requires_grad_(True)
+    o, st = generalized_delta_rule_varlen(*[g[n] for n in NAMES], torch.tensor(cu), initial_state=h)
+    torch.autograd.backward([o, st], [d_out.cuda(), d_state.cuda()])
+    assert rel_l2(o, o_ref) <= 2e-2 and rel_l2(st, s_ref) <= 2e-2
+    for n in NAMES:
+        assert rel_l2(g[n].grad, g_ref[n]) <= 2e-2, n
+    assert rel_l2(h.grad, dh_ref) <= 2e-2
+    # sequence by sequence as well: a wrong token offset in one unit would hide in the norm of the whole row
+    for i in range(len(lens)):
+        sl = slice(cu[i], cu[i + 1])
+        assert rel_l2(o[:, sl], o_ref[:, sl]) <= 2e-2, i
+        for n in NAMES:
+            assert rel_l2(g[n].grad[:, sl], g_ref[n][:, sl]) <= 2e-2, (i, n)
