@@ -444,11 +444,18 @@ def run_ours(args, wl):
 
     extra = {}
     if not args.only_main:
-        extra["decode"] = sub_decode(dev, world, max_over_ranks, barrier, pk)
-        extra["wkv6"] = sub_wkv6(dev, world, max_over_ranks, barrier, pk)
-        extra["strong_scaling"] = sub_cfg2_sharded(dev, world, rank, max_over_ranks, barrier)
+        subs = [("decode", lambda: sub_decode(dev, world, max_over_ranks, barrier, pk)),
+                ("wkv6", lambda: sub_wkv6(dev, world, max_over_ranks, barrier, pk)),
+                ("strong_scaling", lambda: sub_cfg2_sharded(dev, world, rank, max_over_ranks, barrier))]
         if world > 1:
-            extra["sequence_parallel"] = sub_cfg2_sequence_parallel(dev, world, rank, max_over_ranks, barrier)
+            subs.append(("sequence_parallel",
+                         lambda: sub_cfg2_sequence_parallel(dev, world, rank, max_over_ranks, barrier)))
+        for name, fn in subs:
+            try:      # a sub-record that cannot run (e.g. out of memory) must not cost the main line
+                extra[name] = fn()
+            except Exception as exc:      # noqa: BLE001
+                extra[name] = {"error": f"{type(exc).__name__}: {exc}"[:300]}
+                torch.cuda.empty_cache()
 
     # ---- end to end: host buffers in, host buffers out, through the public API.
     # Every step copies all of its inputs from pinned host memory and all of its results back to
