@@ -523,21 +523,37 @@ r7c_bwd_final_kernel(const bf16* __restrict__ w, const __grid_constant__ CUtenso
     if (ok) {
       const int r = 32 * wq + lane, i = r & 63;
       const bool lower = r >= 64;       // rows of dz: strictly lower; rows of do: lower incl. diagonal
+      // The warp's 32 rows are i = 32*ihalf + lane, so which side of the diagonal a block of 32 columns lies on is
+      // the same for the whole warp: left of the diagonal block every element is kept, right of it every element
+      // is zero (TMEM is not read), and only the diagonal block takes a per-element choice.
+      const int ihalf = wq & 1;
+      unsigned char* dst = lower ? (hsel ? sm.daab : sm.daak) : (hsel ? sm.daqb : sm.daqk);
 #pragma unroll
       for (int pp = 0; pp < 2; ++pp) {
         const int part = 2 * hsel + pp;   // hsel 0: products with v (dA_qk / dA_ak); hsel 1: with sa (dA_qb / dA_ab)
+        const int j0 = 32 * pp;
+        float x[32];
+        if (pp > ihalf) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) x[j] = 0.f;
+          tile_store_row32(dst, i, j0, x);
+          continue;
+        }
         uint32_t rr[32];
         tmem_ld32(tmem_addr(tm, 32 * wq, 32 * part), rr);
         tmem_ld_wait();
-        float x[32];
-        const int j0 = 32 * pp;
+        if (pp < ihalf) {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const bool keep = lower ? (j0 + j < i) : (j0 + j <= i);
-          x[j] = keep ? __uint_as_float(rr[j]) : 0.f;
+          for (int j = 0; j < 32; ++j) x[j] = __uint_as_float(rr[j]);
+          tile_store_row32(dst, i, j0, x);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const bool keep = lower ? (j < lane) : (j <= lane);
+            x[j] = keep ? __uint_as_float(rr[j]) : 0.f;
+          }
+          tile_store_row32(dst, i, j0, x);
         }
-        unsigned char* dst = lower ? (hsel ? sm.daab : sm.daak) : (hsel ? sm.daqb : sm.daqk);
-        tile_store_row32(dst, i, j0, x);
       }
       // dv rows sit on the lower lane halves of columns 128..191; each warp of a pair takes 32 columns.
       // Staged in the A_qk tile (dead: MMA group 1 has completed), stored by TMA below.

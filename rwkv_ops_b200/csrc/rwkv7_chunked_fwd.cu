@@ -298,18 +298,11 @@ r7c_intra_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ w, con
     if (ok) {
       const int r = 32 * wq + lane, i = r & 63;
       const bool lower = r >= 64;       // rows of a~: strictly lower triangle; rows of q~: lower incl. diagonal
-#pragma unroll
-      for (int pp = 0; pp < 2; ++pp) {
-        uint32_t rr[32];
-        tmem_ld32(tmem_addr(tm, 32 * wq, 64 * hsel + 32 * pp), rr);   // hsel 0: products with k~, 1: with b~
-        tmem_ld_wait();
-        float x[32];
-        const int j0 = 32 * pp;
-#pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const bool keep = lower ? (j0 + j < i) : (j0 + j <= i);
-          x[j] = keep ? __uint_as_float(rr[j]) : 0.f;
-        }
+      // The warp's 32 rows are i = 32*ihalf + lane, so which side of the diagonal a block of 32 columns lies on is
+      // the same for the whole warp: left of the diagonal block every element is kept, right of it every element
+      // is zero (TMEM is not read), and only the diagonal block takes a per-element choice.
+      const int ihalf = wq & 1;
+      auto emit = [&](const float (&x)[32], int j0) {
         if (!lower) {
           tile_store_row32(hsel ? sm.aqb : sm.aqk, i, j0, x);
         } else if (!hsel) {
@@ -318,6 +311,32 @@ r7c_intra_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ w, con
 #pragma unroll
           for (int j = 0; j < 32; j += 4)
             *reinterpret_cast<float4*>(&sm.nmat[i * NROW + j0 + j]) = make_float4(x[j], x[j + 1], x[j + 2], x[j + 3]);
+        }
+      };
+#pragma unroll
+      for (int pp = 0; pp < 2; ++pp) {
+        const int j0 = 32 * pp;
+        float x[32];
+        if (pp > ihalf) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) x[j] = 0.f;
+          emit(x, j0);
+          continue;
+        }
+        uint32_t rr[32];
+        tmem_ld32(tmem_addr(tm, 32 * wq, 64 * hsel + 32 * pp), rr);   // hsel 0: products with k~, 1: with b~
+        tmem_ld_wait();
+        if (pp < ihalf) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) x[j] = __uint_as_float(rr[j]);
+          emit(x, j0);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const bool keep = lower ? (j < lane) : (j <= lane);
+            x[j] = keep ? __uint_as_float(rr[j]) : 0.f;
+          }
+          emit(x, j0);
         }
       }
     }

@@ -83,6 +83,40 @@ __device__ __forceinline__ void umma_split(uint32_t tmem_d, uint32_t a_hi, uint3
   umma_tile<M, N, A_MN, B_MN>(tmem_d, a_hi + TILE_BYTES, b_hi, true);
 }
 
+// Row `lr` (0..15) of a warp's 16 x 32 block of a 64 x 64 product that is kept strictly below the diagonal, the
+// diagonal itself set to `diag`, split and stored.  Where the diagonal crosses the block depends on the warp alone:
+// left of column JLO (of the block's 32) every element is kept, from JLO + 16 on every element is zero, and only
+// the 16 columns between take a per-element choice.  JLO = 32: the whole block is kept; JLO = -16: all zero
+// (`rr` is not read).
+template <int JLO>
+__device__ __forceinline__ void store_masked_row(const uint32_t (&rr)[32], int lr, float diag, unsigned char* hi_t,
+                                                 int row, int col0) {
+  float x[32];
+#pragma unroll
+  for (int j = 0; j < 32; ++j) {
+    if (j < JLO) x[j] = __uint_as_float(rr[j]);
+    else if (j >= JLO + 16) x[j] = 0.f;
+    else x[j] = (j - JLO) < lr ? __uint_as_float(rr[j]) : ((j - JLO) == lr ? diag : 0.f);
+  }
+  store_split_row32(hi_t, hi_t + TILE_BYTES, row, col0, x);
+}
+// the same for a warp whose rows are 16*wq .. and whose columns are 32*hsel ..; all lanes of the warp call it
+__device__ __forceinline__ void load_store_masked_row(uint32_t taddr, int wq, int hsel, int lr, float diag,
+                                                      unsigned char* hi_t, int row, bool active) {
+  const int jlo = 16 * wq - 32 * hsel;
+  uint32_t rr[32];
+  if (jlo < 0) {
+    if (active) store_masked_row<-16>(rr, lr, diag, hi_t, row, 32 * hsel);
+    return;
+  }
+  tmem_ld32(taddr, rr);
+  tmem_ld_wait();
+  if (!active) return;
+  if (jlo >= 32) store_masked_row<32>(rr, lr, diag, hi_t, row, 32 * hsel);
+  else if (jlo == 16) store_masked_row<16>(rr, lr, diag, hi_t, row, 32 * hsel);
+  else store_masked_row<0>(rr, lr, diag, hi_t, row, 32 * hsel);
+}
+
 __device__ __forceinline__ long long state_row(const int32_t* smap, int n_state, int bi) {
   if (n_state == 1) return 0;
   if (!smap) return bi;
@@ -280,24 +314,11 @@ wkv6c_fwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
       if (c4 == 0) sm.dgs[row] = dg;
     }
     // ask for the next chunk's rows to be brought into L2 while this chunk is in its MMA phases
-    if (t0 + L < Tn && c4 == 0) {
-#pragma unroll
-      for (int n = 0; n < 4; ++n) {
-        const int tok = t0 + L + ((tid + 256 * n) >> 4);
-        if (tok < Tn) {
-          const long long off = base + (long long)tok * tstride;
-          asm volatile("prefetch.global.L2 [%0];" ::"l"(w + off));
-          asm volatile("prefetch.global.L2 [%0];" ::"l"(r + off));
-          asm volatile("prefetch.global.L2 [%0];" ::"l"(k + off));
-          asm volatile("prefetch.global.L2 [%0];" ::"l"(v + off));
-          if (sizeof(T) == 4) {
-            asm volatile("prefetch.global.L2 [%0];" ::"l"(w + off + 32));
-            asm volatile("prefetch.global.L2 [%0];" ::"l"(r + off + 32));
-            asm volatile("prefetch.global.L2 [%0];" ::"l"(k + off + 32));
-            asm volatile("prefetch.global.L2 [%0];" ::"l"(v + off + 32));
-          }
-        }
-      }
+    if (tid == 0 && t0 + L < Tn) {
+      tma_prefetch_4d(&tmap_w, 0, t0 + L, hi, bi);
+      tma_prefetch_4d(&tmap_v, 0, t0 + L, hi, bi);
+      tma_prefetch_4d(&tmap_r, 0, t0 + L, hi, bi);
+      tma_prefetch_4d(&tmap_k, 0, t0 + L, hi, bi);
     }
     fence_async_smem();
     tc_fence_before();
@@ -318,18 +339,7 @@ wkv6c_fwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
     if (ok) {
       // A rows (lower halves of columns 0..63): strictly lower part plus the diagonal term, split hi/lo
       uint32_t rr[32];
-      tmem_ld32(tm_a, rr);
-      tmem_ld_wait();
-      if (tok_lane) {
-        float x[32];
-        const float dgi = sm.dgs[srow];
-#pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const int jj = 32 * hsel + j;
-          x[j] = jj < srow ? __uint_as_float(rr[j]) : (jj == srow ? dgi : 0.f);
-        }
-        store_split_row32(sm.at[0], sm.at[1], srow, 32 * hsel, x);
-      }
+      load_store_masked_row(tm_a, wq, hsel, lane & 15, tok_lane ? sm.dgs[srow] : 0.f, sm.at[0], srow, tok_lane);
       // state rows (k~^T v on the upper halves of columns 64..127): S_L = e^{glast-gref} (S~0 + k~^T v)
       tmem_ld32(tm_ys, rr);
       tmem_ld_wait();
@@ -604,30 +614,14 @@ wkv6c_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
 #pragma unroll
       for (int j = 0; j < 8; ++j) srow4[j] = *reinterpret_cast<const float4*>(Srow + 4 * j);
     }
-    if (c > 0 && c4 == 0) {   // bring the previous chunk's rows into L2 while this chunk is in its MMA phases
-#pragma unroll
-      for (int n = 0; n < 4; ++n) {
-        const int tok = t0 - L + ((tid + 256 * n) >> 4);
-        const long long off = base + (long long)tok * tstride;
-        asm volatile("prefetch.global.L2 [%0];" ::"l"(w + off));
-        asm volatile("prefetch.global.L2 [%0];" ::"l"(r + off));
-        asm volatile("prefetch.global.L2 [%0];" ::"l"(k + off));
-        asm volatile("prefetch.global.L2 [%0];" ::"l"(v + off));
-        asm volatile("prefetch.global.L2 [%0];" ::"l"(d_y + off));
-        {   // the chunk-boundary state the previous chunk starts from, one 256-byte row per request pair
-          const int row = (tid + 256 * n) >> 4;
-          const float* S0p = states + (((size_t)unit * (NT + 1) + c - 1) * HS + row) * HS;
-          asm volatile("prefetch.global.L2 [%0];" ::"l"(S0p));
-          asm volatile("prefetch.global.L2 [%0];" ::"l"(S0p + 32));
-        }
-        if (sizeof(T) == 4) {
-          asm volatile("prefetch.global.L2 [%0];" ::"l"(w + off + 32));
-          asm volatile("prefetch.global.L2 [%0];" ::"l"(r + off + 32));
-          asm volatile("prefetch.global.L2 [%0];" ::"l"(k + off + 32));
-          asm volatile("prefetch.global.L2 [%0];" ::"l"(v + off + 32));
-          asm volatile("prefetch.global.L2 [%0];" ::"l"(d_y + off + 32));
-        }
-      }
+    if (tid == 0 && c > 0) {   // bring the previous chunk's rows into L2 while this chunk is in its MMA phases
+      tma_prefetch_4d(&tmap_w, 0, t0 - L, hi, bi);
+      tma_prefetch_4d(&tmap_dy, 0, t0 - L, hi, bi);
+      tma_prefetch_4d(&tmap_v, 0, t0 - L, hi, bi);
+      tma_prefetch_4d(&tmap_r, 0, t0 - L, hi, bi);
+      tma_prefetch_4d(&tmap_k, 0, t0 - L, hi, bi);
+      // and the chunk-boundary state the previous chunk starts from
+      bulk_prefetch_l2(states + ((size_t)unit * (NT + 1) + c - 1) * HS * HS, HS * HS * (uint32_t)sizeof(float));
     }
     fence_async_smem();
     tc_fence_before();
@@ -645,18 +639,9 @@ wkv6c_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
     tc_fence_after();
     W6C_STAMP(37);
     if (ok) {
-      uint32_t rr[32];
-      tmem_ld32(tm_c0, rr);
-      tmem_ld_wait();
-      float x[32];
       const float dgi = lower ? sm.dgs[srow] : 0.f;     // the diagonal of A carries the u term; dA's does not
-#pragma unroll
-      for (int j = 0; j < 32; ++j) {
-        const int jj = 32 * hsel + j;
-        x[j] = jj < srow ? __uint_as_float(rr[j]) : (jj == srow ? dgi : 0.f);
-      }
-      unsigned char* hi_t = lower ? sm.at[0] : sm.dat[0];      // one call: both lane halves run the same code
-      store_split_row32(hi_t, hi_t + TILE_BYTES, srow, 32 * hsel, x);
+      // one call: both lane halves run the same code
+      load_store_masked_row(tm_c0, wq, hsel, lane & 15, dgi, lower ? sm.at[0] : sm.dat[0], srow, true);
     }
     // decay factors of state row k = srow (both lanes of a pair work on that row below)
     const float e0 = ex2(fmaxf(sm.qtot[0][srow] + sm.qtot[1][srow], EXP2_FLOOR));
@@ -757,7 +742,7 @@ wkv6c_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
     ok = __syncthreads_and(ok);
     if (tid == 0 && ok && c > 0) load_in_b(c - 1);      // the epilogue above was the last reader of rt / kt
     W6C_STAMP(40);
-    // ---- decay gradient: dg_j = sum_{i>=j} (dgi_i + dge_i) - dge_j + dglast;  dw = dg g
+    // ---- decay gradient: dg_j = sum_{i>j} (dgi_i + dge_i) + dgi_j + dglast;  dw = dg g
     {
       const int ch = tid & 63, quarter = tid >> 6;
       float rv[16];
@@ -766,7 +751,7 @@ wkv6c_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
         rv[j] = red_i[(16 * quarter + j) * NROW + ch] + sm.red_e[(16 * quarter + j) * NROW + ch];
       float run = 0.f;
 #pragma unroll
-      for (int j = 15; j >= 0; --j) { run += rv[j]; rv[j] = run; }
+      for (int j = 15; j >= 0; --j) { const float t = rv[j]; rv[j] = run; run += t; }      // sums over i > j
       sm.rqtot[quarter][ch] = run;
       __syncthreads();
       float add = sm.dgl[0][ch] + sm.dgl[1][ch];
@@ -774,7 +759,7 @@ wkv6c_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
 #pragma unroll
       for (int j = 0; j < 16; ++j) {
         const int ii = 16 * quarter + j;
-        const float dg = rv[j] + add - sm.red_e[ii * NROW + ch];
+        const float dg = rv[j] + add + red_i[ii * NROW + ch];
         stage_dw[ii * NROW + ch] = dg * (LN2 * sm.gg[ii * NROW + ch]);      // dw = dg g, g = gg ln 2
       }
     }
