@@ -13,7 +13,9 @@
  *   dtype        RWKVB200_F32 / RWKVB200_BF16 / RWKVB200_F16: element type of the
  *                token tensors (inputs, outputs and their gradients).  Arithmetic
  *                and all states are float32.
- *   head size    64 (key and value); other sizes return RWKVB200_E_UNSUPPORTED.
+ *   head size    64 (key and value) on every entry point; the dense RWKV7 forward / backward / step also
+ *                take 128 and the wkv6 forward / backward 32 and 128, through the float32 recurrence
+ *                (RWKVB200_ALGO_AUTO or _RECURRENT).  Other sizes return RWKVB200_E_UNSUPPORTED.
  *   decay        every operator applies exp(-exp(w)) to its w input, as the
  *                reference does (rwkv_ops/rwkv7_kernel/native_keras_op.py:58,
  *                rwkv_ops/rwkv6_kernel/ops_rwkv_kernel.py:63).
@@ -233,6 +235,9 @@ int rwkvb200_rwkv7_bwd_static(const void* r, const void* w, const void* k, const
  *   workspace      rwkvb200_wkv6_fwd_workspace_bytes(...) bytes: with KEEP the backward's workspace
  *                  (rwkvb200_wkv6_bwd_workspace_bytes, the two are equal), without it a few bytes per
  *                  (batch, head) for the chunked path and none for the recurrent one.
+ * Head sizes 32 and 128 (the reference's operator takes the head size in its constructor,
+ * rwkv_ops/rwkv6_kernel/__init__.py:37-50) run the recurrent path whatever `algo` says, except that an
+ * explicit RWKVB200_ALGO_CHUNKED returns RWKVB200_E_UNSUPPORTED; states are [head_size][head_size].
  * Decay range of the chunked path: it holds the 1e-4 parity bar while the sum of exp(w) over the 32 tokens
  * of a half chunk stays below 45 in every channel (always true for w <= 0.34).  A (batch, head) unit that
  * exceeds this is detected on the device and recomputed, forward and backward, by the float32 recurrence

@@ -37,9 +37,18 @@ inline int phases_of(int algo) {
 }
 
 // wkv6: AUTO = chunked tensor-core path (its split-precision operands keep float32-grade accuracy).
-inline int resolve_w6_algo(int algo) {
+// head sizes 32 and 128 run the float32 recurrence (the tensor-core path is built for head size 64)
+inline int resolve_w6_algo(int algo, int head_size = HS) {
   algo &= 0xff;
+  if (head_size != HS) return RWKVB200_ALGO_RECURRENT;
   return algo == RWKVB200_ALGO_RECURRENT ? RWKVB200_ALGO_RECURRENT : RWKVB200_ALGO_CHUNKED;
+}
+inline int check_w6(int B, int T, int H, int head_size, int dtype, int algo) {
+  if (B <= 0 || T <= 0 || H <= 0) return RWKVB200_E_SHAPE;
+  if (head_size != 32 && head_size != HS && head_size != 128) return RWKVB200_E_UNSUPPORTED;
+  if (head_size != HS && (algo & 0xff) == RWKVB200_ALGO_CHUNKED) return RWKVB200_E_UNSUPPORTED;
+  if (dtype != RWKVB200_F32 && dtype != RWKVB200_BF16 && dtype != RWKVB200_F16) return RWKVB200_E_DTYPE;
+  return RWKVB200_OK;
 }
 
 inline size_t r7_ckpt_bytes(int B, int T, int H, int head_size = HS) {
@@ -47,9 +56,9 @@ inline size_t r7_ckpt_bytes(int B, int T, int H, int head_size = HS) {
   return align256((size_t)B * H * nc * head_size * head_size * sizeof(float));
 }
 
-inline size_t w6_ckpt_bytes(int B, int T, int H) {
+inline size_t w6_ckpt_bytes(int B, int T, int H, int head_size = HS) {
   const size_t nc = (size_t)(T + W6_CKPT - 1) / W6_CKPT;
-  return align256((size_t)B * H * nc * HS * HS * sizeof(float));
+  return align256((size_t)B * H * nc * head_size * head_size * sizeof(float));
 }
 
 }  // namespace
@@ -290,8 +299,8 @@ int rwkvb200_rwkv7_fused_bwd(const void* r, const void* w_pre, const void* k, co
 }
 
 size_t rwkvb200_wkv6_fwd_workspace_bytes(int B, int T, int H, int head_size, int dtype, int algo) {
-  if (check_common(B, T, H, head_size, dtype)) return 0;
-  if (resolve_w6_algo(algo) != RWKVB200_ALGO_CHUNKED) return 0;
+  if (check_w6(B, T, H, head_size, dtype, algo)) return 0;
+  if (resolve_w6_algo(algo, head_size) != RWKVB200_ALGO_CHUNKED) return 0;
   return (algo & RWKVB200_ALGO_KEEP) ? wkv6_chunked_bwd_workspace_bytes(B, T, H) : wkv6_chunked_flags_bytes(B, H);
 }
 
@@ -299,7 +308,7 @@ int rwkvb200_wkv6_fwd(const void* r, const void* k, const void* v, const void* w
                       const float* s0, int n_state, const int32_t* state_map,
                       void* y, float* sT, void* workspace, size_t workspace_bytes,
                       int B, int T, int H, int head_size, int dtype, int algo, void* stream) {
-  int e = check_common(B, T, H, head_size, dtype);
+  int e = check_w6(B, T, H, head_size, dtype, algo);
   if (e) return e;
   if (!r || !k || !v || !w || !u || !y) return RWKVB200_E_NULL;
   if (n_state < 0) return RWKVB200_E_SHAPE;
@@ -307,7 +316,7 @@ int rwkvb200_wkv6_fwd(const void* r, const void* k, const void* v, const void* w
   if (n_state > 1 && !state_map && n_state != B) return RWKVB200_E_STATE_MAP;
   const void* ps[] = {r, k, v, w, u, s0, y, sT};
   for (const void* p : ps) if (p && !aligned16(p)) return RWKVB200_E_ALIGN;
-  if (resolve_w6_algo(algo) == RWKVB200_ALGO_CHUNKED) {
+  if (resolve_w6_algo(algo, head_size) == RWKVB200_ALGO_CHUNKED) {
     if (!workspace || !aligned16(workspace) ||
         workspace_bytes < rwkvb200_wkv6_fwd_workspace_bytes(B, T, H, head_size, dtype, algo))
       return RWKVB200_E_WORKSPACE;
@@ -321,13 +330,14 @@ int rwkvb200_wkv6_fwd(const void* r, const void* k, const void* v, const void* w
                                    B, T, H, dtype, (cudaStream_t)stream);
   }
   return launch_wkv6_fwd(r, k, v, w, u, n_state ? s0 : nullptr, n_state, state_map, y, sT, nullptr,
-                         B, T, H, dtype, (cudaStream_t)stream);
+                         B, T, H, dtype, (cudaStream_t)stream, nullptr, 0, head_size);
 }
 
 size_t rwkvb200_wkv6_bwd_workspace_bytes(int B, int T, int H, int head_size, int dtype, int algo) {
-  if (check_common(B, T, H, head_size, dtype)) return 0;
-  if (resolve_w6_algo(algo) == RWKVB200_ALGO_CHUNKED) return wkv6_chunked_bwd_workspace_bytes(B, T, H);
-  return w6_ckpt_bytes(B, T, H) + align256((size_t)B * H * 4 * HS * sizeof(float));
+  if (check_w6(B, T, H, head_size, dtype, algo)) return 0;
+  if (resolve_w6_algo(algo, head_size) == RWKVB200_ALGO_CHUNKED) return wkv6_chunked_bwd_workspace_bytes(B, T, H);
+  // checkpoints, and one row of du per CTA (head_size / 16 of them per unit)
+  return w6_ckpt_bytes(B, T, H, head_size) + align256((size_t)B * H * (head_size / 16) * head_size * sizeof(float));
 }
 
 int rwkvb200_wkv6_bwd(const void* r, const void* k, const void* v, const void* w, const float* u,
@@ -336,7 +346,7 @@ int rwkvb200_wkv6_bwd(const void* r, const void* k, const void* v, const void* w
                       void* dr, void* dk, void* dv, void* dw, float* du, float* d_s0,
                       void* workspace, size_t workspace_bytes,
                       int B, int T, int H, int head_size, int dtype, int algo, void* stream) {
-  int e = check_common(B, T, H, head_size, dtype);
+  int e = check_w6(B, T, H, head_size, dtype, algo);
   if (e) return e;
   if (!r || !k || !v || !w || !u || !d_y || !dr || !dk || !dv || !dw || !du) return RWKVB200_E_NULL;
   if (n_state < 0) return RWKVB200_E_SHAPE;
@@ -347,16 +357,17 @@ int rwkvb200_wkv6_bwd(const void* r, const void* k, const void* v, const void* w
   if (!workspace || workspace_bytes < rwkvb200_wkv6_bwd_workspace_bytes(B, T, H, head_size, dtype, algo))
     return RWKVB200_E_WORKSPACE;
   cudaStream_t st = (cudaStream_t)stream;
-  if (resolve_w6_algo(algo) == RWKVB200_ALGO_CHUNKED)
+  if (resolve_w6_algo(algo, head_size) == RWKVB200_ALGO_CHUNKED)
     return launch_wkv6_chunked_bwd(r, k, v, w, u, n_state ? s0 : nullptr, n_state, state_map, d_y, d_sT,
                                    dr, dk, dv, dw, du, d_s0, workspace, B, T, H, dtype,
                                    (algo & RWKVB200_ALGO_KEEP) != 0, st);
   float* ckpt = reinterpret_cast<float*>(workspace);
-  float* du_partial = reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + w6_ckpt_bytes(B, T, H));
+  float* du_partial = reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + w6_ckpt_bytes(B, T, H, head_size));
   e = launch_wkv6_fwd(r, k, v, w, u, n_state ? s0 : nullptr, n_state, state_map, nullptr, nullptr, ckpt,
-                      B, T, H, dtype, st);
+                      B, T, H, dtype, st, nullptr, 0, head_size);
   if (e) return e;
-  return launch_wkv6_bwd(r, k, v, w, u, d_y, d_sT, ckpt, dr, dk, dv, dw, du_partial, du, d_s0, B, T, H, dtype, st);
+  return launch_wkv6_bwd(r, k, v, w, u, d_y, d_sT, ckpt, dr, dk, dv, dw, du_partial, du, d_s0, B, T, H, dtype, st,
+                         head_size);
 }
 
 }  // extern "C"

@@ -159,7 +159,7 @@ constexpr int R7_CKPT = 8;   // tokens between state checkpoints of the recurren
 int launch_wkv6_fwd(const void* r, const void* k, const void* v, const void* w, const float* u,
                     const float* s0, int n_state, const int32_t* smap, void* y, float* sT,
                     float* ckpt, int B, int Tn, int H, int dtype, cudaStream_t st, const UnitSel* sel = nullptr,
-                    int ckpt_every = 0);
+                    int ckpt_every = 0, int head_size = HS);
 int launch_wkv6_bwd_coarse(const void* r, const void* k, const void* v, const void* w, const float* u,
                            const void* d_y, const float* d_sT, const float* ckpt,
                            void* dr, void* dk, void* dv, void* dw, float* du_partial, float* d_s0,
@@ -169,7 +169,7 @@ int launch_wkv6_du_reduce_mixed(const float* part_chunked, const float* part_rec
 int launch_wkv6_bwd(const void* r, const void* k, const void* v, const void* w, const float* u,
                     const void* d_y, const float* d_sT, const float* ckpt,
                     void* dr, void* dk, void* dv, void* dw, float* du_partial, float* du, float* d_s0,
-                    int B, int Tn, int H, int dtype, cudaStream_t st);
+                    int B, int Tn, int H, int dtype, cudaStream_t st, int head_size = HS);
 constexpr int W6_CKPT = 8;
 
 // Chunked tcgen05 wkv6 (wkv6_chunked.cu).  `states` (may be NULL) receives the fp32 state at every chunk

@@ -4,9 +4,10 @@
 //   d_t = exp(-exp(w_t));  y_t[v] = sum_k r_t[k] (u[k] k_t[k] v_t[v] + S_{t-1}[k][v]);  S_t = diag(d_t) S_{t-1} + k_t v_t^T
 // with S[k][v] and S_0 = s0[state_map[b]] or zero.
 //
-// Column v of S never mixes with another column, so the 64 value columns are split over four CTAs
-// (16 columns each): grid (B*H, 4), 64 threads.  In the "value role" thread (vl = tid>>2, kq = tid&3)
-// holds S[16*kq .. 16*kq+15][vl] in registers; the reduction over k takes two shuffles.
+// Column v of S never mixes with another column, so the N value columns (N = head size: 32, 64 or 128) are
+// split over N/16 CTAs of 16 columns each: grid (B*H, N/16), N threads.  In the "value role" thread
+// (vl = tid / NKQ, kq = tid % NKQ, NKQ = N/16) holds S[16*kq .. 16*kq+15][vl] in registers; the reduction
+// over k takes log2(NKQ) shuffles.  In the "key role" thread kc = tid owns key channel kc.
 //
 // Backward, with G the gradient of the state flowing from the future and dyv = sum_v dy_t[v] v_t[v]:
 //   dr_t[k] = u[k] k_t[k] dyv + sum_v S_{t-1}[k][v] dy_t[v]      dk_t[k] = r_t[k] u[k] dyv + sum_v G[k][v] v_t[v]
@@ -15,7 +16,7 @@
 //   dw_t = dd_t * d_t * (-exp(w_t))
 // S_{t-1} is needed per token: the forward sweep stores the state every W6_CKPT tokens (the workspace)
 // and the backward kernel re-runs each chunk forward into shared memory before sweeping it backward.
-// Sums over v need all four CTAs of a (batch, head): they form a thread-block cluster and exchange
+// Sums over v need all CTAs of a (batch, head): they form a thread-block cluster and exchange
 // per-chunk partial sums through distributed shared memory in a fixed order (deterministic).
 #include <cooperative_groups.h>
 
@@ -30,7 +31,6 @@ namespace rwkvb200 {
 namespace {
 
 constexpr int VS = 16;
-constexpr int NQ = HS / VS;
 constexpr int TL = 16;
 constexpr int CK = W6_CKPT;
 constexpr int SCOL = VS + 1;   // padded row (one key, 16 values) of a state slab in shared memory
@@ -42,32 +42,41 @@ __device__ __forceinline__ long long state_row(const int32_t* smap, int n_state,
   return m < 0 ? 0 : (m >= n_state ? n_state - 1 : m);
 }
 
-template <typename T>
-__global__ void __launch_bounds__(64)
+// sum over the NKQ lanes that share a value column
+template <int NKQ>
+__device__ __forceinline__ float sum_kq(float x) {
+#pragma unroll
+  for (int m = 1; m < NKQ; m <<= 1) x += __shfl_xor_sync(0xffffffffu, x, m);
+  return x;
+}
+
+template <typename T, int N>
+__global__ void __launch_bounds__(N)
 wkv6_fwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __restrict__ v,
                 const T* __restrict__ w, const float* __restrict__ u,
                 const float* __restrict__ s0, int n_state, const int32_t* __restrict__ smap,
                 T* __restrict__ yout, float* __restrict__ sT, float* __restrict__ ckpt, int ckpt_every,
                 int Tn, int H, UnitSel sel) {
-  __shared__ __align__(16) float tile[TL][4][HS];   // r, d, k, r*u*k
+  constexpr int NKQ = N / VS, QUADS = N / 4;
+  __shared__ __align__(16) float tile[TL][4][N];   // r, d, k, r*u*k
   __shared__ __align__(16) float vt[TL][VS];
   __shared__ __align__(16) float yt[TL][VS];
 
   const int unit = blockIdx.x, y = blockIdx.y, tid = threadIdx.x;
   if (sel.flags && sel.flags[unit] == 0) return;      // only the selected units run
   const int bi = unit / H, hi = unit % H;
-  const int vl = tid >> 2, kq = tid & 3;
-  const long long base = ((long long)bi * Tn * H + hi) * HS;   // + t*H*HS
-  const long long tstride = (long long)H * HS;
+  const int vl = tid / NKQ, kq = tid % NKQ;
+  const long long base = ((long long)bi * Tn * H + hi) * N;   // + t*H*N
+  const long long tstride = (long long)H * N;
   const long long ckpt_unit = sel.ckpt_unit_stride ? sel.ckpt_unit_stride
-                                                   : (long long)((Tn + ckpt_every - 1) / ckpt_every) * HS * HS;
-  const float4 u4 = *reinterpret_cast<const float4*>(u + hi * HS + 4 * (tid & 15));
+                                                   : (long long)((Tn + ckpt_every - 1) / ckpt_every) * N * N;
+  const float4 u4 = *reinterpret_cast<const float4*>(u + hi * N + 4 * (tid % QUADS));
 
   float S[16];
   if (s0 && n_state > 0) {
-    const float* p = s0 + ((state_row(smap, n_state, bi) * H + hi) * HS + 16 * kq) * HS + y * VS + vl;
+    const float* p = s0 + ((state_row(smap, n_state, bi) * H + hi) * N + 16 * kq) * N + y * VS + vl;
 #pragma unroll
-    for (int j = 0; j < 16; ++j) S[j] = p[j * HS];
+    for (int j = 0; j < 16; ++j) S[j] = p[j * N];
   } else {
 #pragma unroll
     for (int j = 0; j < 16; ++j) S[j] = 0.f;
@@ -75,8 +84,8 @@ wkv6_fwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __res
 
   for (int t0 = 0; t0 < Tn; t0 += TL) {
     const int nt = min(TL, Tn - t0);
-    for (int i = tid; i < nt * 16; i += 64) {
-      const int quad = i & 15, tl = i >> 4;   // quad == tid & 15
+    for (int i = tid; i < nt * QUADS; i += N) {
+      const int quad = i % QUADS, tl = i / QUADS;   // quad == tid % QUADS
       const long long off = base + (long long)(t0 + tl) * tstride + 4 * quad;
       const float4 r4 = load4(r + off), k4 = load4(k + off), w4 = load4(w + off);
       *reinterpret_cast<float4*>(&tile[tl][0][4 * quad]) = r4;
@@ -86,8 +95,8 @@ wkv6_fwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __res
       *reinterpret_cast<float4*>(&tile[tl][3][4 * quad]) =
           make_float4(r4.x * u4.x * k4.x, r4.y * u4.y * k4.y, r4.z * u4.z * k4.z, r4.w * u4.w * k4.w);
     }
-    if (tid < nt * 4) {
-      const int tl = tid >> 2, quad = tid & 3;
+    for (int i = tid; i < nt * 4; i += N) {
+      const int tl = i >> 2, quad = i & 3;
       *reinterpret_cast<float4*>(&vt[tl][4 * quad]) =
           load4(v + base + (long long)(t0 + tl) * tstride + y * VS + 4 * quad);
     }
@@ -95,9 +104,9 @@ wkv6_fwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __res
     for (int tl = 0; tl < nt; ++tl) {
       const int t = t0 + tl;
       if (ckpt && (t % ckpt_every) == 0) {
-        float* p = ckpt + unit * ckpt_unit + (((long long)(t / ckpt_every) * HS) + 16 * kq) * HS + y * VS + vl;
+        float* p = ckpt + unit * ckpt_unit + (((long long)(t / ckpt_every) * N) + 16 * kq) * N + y * VS + vl;
 #pragma unroll
-        for (int j = 0; j < 16; ++j) p[j * HS] = S[j];
+        for (int j = 0; j < 16; ++j) p[j * N] = S[j];
       }
       const float* tr = &tile[tl][0][16 * kq];
       const float* td = &tile[tl][1][16 * kq];
@@ -112,70 +121,72 @@ wkv6_fwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __res
         S[j] = td[j] * S[j] + tk[j] * vv;
         S[j + 1] = td[j + 1] * S[j + 1] + tk[j + 1] * vv;
       }
-      float yy = (y0 + y1) + vv * (q0 + q1);
-      yy += __shfl_xor_sync(0xffffffffu, yy, 1);
-      yy += __shfl_xor_sync(0xffffffffu, yy, 2);
+      const float yy = sum_kq<NKQ>((y0 + y1) + vv * (q0 + q1));
       if (kq == 0) yt[tl][vl] = yy;
     }
     __syncthreads();
-    if (yout && tid < nt * 4) {
-      const int tl = tid >> 2, quad = tid & 3;
-      store4(yout + base + (long long)(t0 + tl) * tstride + y * VS + 4 * quad,
-             *reinterpret_cast<const float4*>(&yt[tl][4 * quad]));
+    if (yout) {
+      for (int i = tid; i < nt * 4; i += N) {
+        const int tl = i >> 2, quad = i & 3;
+        store4(yout + base + (long long)(t0 + tl) * tstride + y * VS + 4 * quad,
+               *reinterpret_cast<const float4*>(&yt[tl][4 * quad]));
+      }
     }
   }
   if (sT) {
-    float* p = sT + (((long long)unit * HS) + 16 * kq) * HS + y * VS + vl;
+    float* p = sT + (((long long)unit * N) + 16 * kq) * N + y * VS + vl;
 #pragma unroll
-    for (int j = 0; j < 16; ++j) p[j * HS] = S[j];
+    for (int j = 0; j < 16; ++j) p[j * N] = S[j];
   }
 }
 
-struct BwdSmem {
-  float tile[CK][6][HS];          // r, d, exp(w), k, r*u, u*k
+template <int N> struct BwdSmem {
+  float tile[CK][6][N];           // r, d, exp(w), k, r*u, u*k
   float ruk[CK];                  // sum_k r u k
   float vt[CK][VS];
   float dyt[CK][VS];
   float dvt[CK][VS];
-  float Sbuf[CK][HS][SCOL];       // state before token i of the chunk
-  float part[2][CK][3][HS];       // partial dr, dk, dd over this CTA's 16 value columns
+  float Sbuf[CK][N][SCOL];        // state before token i of the chunk
+  float part[2][CK][3][N];        // partial dr, dk, dd over this CTA's 16 value columns
   float pdyv[2][CK];              // partial sum_v dy v
 };
 // COARSE variant: the checkpoints lie 64 tokens apart (the chunk-boundary states of the chunked path); the
 // states at the start of the eight 8-token groups of a 64-token stretch are recomputed into `sub`.
-struct BwdSmemCoarse : BwdSmem {
-  float sub[8][HS][VS];
+template <int N> struct BwdSmemCoarse : BwdSmem<N> {
+  float sub[8][N][VS];
 };
 
-template <typename T, bool COARSE>
-__global__ void __cluster_dims__(1, NQ, 1) __launch_bounds__(64)
+// launched with a cluster of (1, N/16, 1): the CTAs of one unit
+template <typename T, int N, bool COARSE>
+__global__ void __launch_bounds__(N)
 wkv6_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __restrict__ v,
                 const T* __restrict__ w, const float* __restrict__ u,
                 const T* __restrict__ d_y, const float* __restrict__ d_sT, const float* __restrict__ ckpt,
                 T* __restrict__ dr, T* __restrict__ dk, T* __restrict__ dv, T* __restrict__ dw,
                 float* __restrict__ du_partial, float* __restrict__ d_s0, int Tn, int H, UnitSel sel) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  typedef typename std::conditional<COARSE, BwdSmemCoarse, BwdSmem>::type Smem;
+  constexpr int NKQ = N / VS, NQ = N / VS, QUADS = N / 4;
+  typedef typename std::conditional<COARSE, BwdSmemCoarse<N>, BwdSmem<N>>::type Smem;
   Smem& sm = *reinterpret_cast<Smem*>(smem_raw);
   cg::cluster_group cluster = cg::this_cluster();
 
   const int unit = blockIdx.x, y = blockIdx.y, tid = threadIdx.x;
-  if (sel.flags && sel.flags[unit] == 0) return;      // the four CTAs of a cluster share the unit: all leave
+  if (sel.flags && sel.flags[unit] == 0) return;      // the CTAs of a cluster share the unit: all leave
   const int bi = unit / H, hi = unit % H;
-  const int vl = tid >> 2, kq = tid & 3;   // value role
+  const int vl = tid / NKQ, kq = tid % NKQ;   // value role
   const int kc = tid;                      // key role
-  const long long base = ((long long)bi * Tn * H + hi) * HS;
-  const long long tstride = (long long)H * HS;
+  const long long base = ((long long)bi * Tn * H + hi) * N;
+  const long long tstride = (long long)H * N;
   const int NC = (Tn + CK - 1) / CK;
-  const long long ckpt_unit = sel.ckpt_unit_stride ? sel.ckpt_unit_stride : (long long)NC * HS * HS;
-  const float4 u4 = *reinterpret_cast<const float4*>(u + hi * HS + 4 * (tid & 15));
+  const long long ckpt_unit = sel.ckpt_unit_stride ? sel.ckpt_unit_stride : (long long)NC * N * N;
+  const float4 u4 = *reinterpret_cast<const float4*>(u + hi * N + 4 * (tid % QUADS));
 
   float Gv[16], Gk[VS];   // value-role copy G[16kq+j][vl], key-role copy G[kc][i]
   if (d_sT) {
 #pragma unroll
-    for (int j = 0; j < 16; ++j) Gv[j] = d_sT[(((long long)unit * HS) + 16 * kq + j) * HS + y * VS + vl];
+    for (int j = 0; j < 16; ++j) Gv[j] = d_sT[(((long long)unit * N) + 16 * kq + j) * N + y * VS + vl];
 #pragma unroll
-    for (int i = 0; i < VS; ++i) Gk[i] = d_sT[(((long long)unit * HS) + kc) * HS + y * VS + i];
+    for (int i = 0; i < VS; ++i) Gk[i] = d_sT[(((long long)unit * N) + kc) * N + y * VS + i];
   } else {
 #pragma unroll
     for (int j = 0; j < 16; ++j) Gv[j] = 0.f;
@@ -193,22 +204,22 @@ wkv6_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __res
         const int c64 = c >> 3;
         float S0[16];
         {
-          const float* p = ckpt + unit * ckpt_unit + (((long long)c64 * HS) + 16 * kq) * HS + y * VS + vl;
+          const float* p = ckpt + unit * ckpt_unit + (((long long)c64 * N) + 16 * kq) * N + y * VS + vl;
 #pragma unroll
-          for (int j = 0; j < 16; ++j) S0[j] = p[j * HS];
+          for (int j = 0; j < 16; ++j) S0[j] = p[j * N];
         }
         for (int g = 8 * c64; g <= c; ++g) {
           const int tg0 = g * CK, ntg = min(CK, Tn - tg0);
-          for (int i = tid; i < ntg * 16; i += 64) {
-            const int quad = i & 15, tl = i >> 4;
+          for (int i = tid; i < ntg * QUADS; i += N) {
+            const int quad = i % QUADS, tl = i / QUADS;
             const long long off = base + (long long)(tg0 + tl) * tstride + 4 * quad;
             const float4 k4 = load4(k + off), w4 = load4(w + off);
             *reinterpret_cast<float4*>(&sm.tile[tl][1][4 * quad]) =
                 make_float4(decay_of(w4.x), decay_of(w4.y), decay_of(w4.z), decay_of(w4.w));
             *reinterpret_cast<float4*>(&sm.tile[tl][3][4 * quad]) = k4;
           }
-          if (tid < ntg * 4) {
-            const int tl = tid >> 2, quad = tid & 3;
+          for (int i = tid; i < ntg * 4; i += N) {
+            const int tl = i >> 2, quad = i & 3;
             *reinterpret_cast<float4*>(&sm.vt[tl][4 * quad]) =
                 load4(v + base + (long long)(tg0 + tl) * tstride + y * VS + 4 * quad);
           }
@@ -226,8 +237,8 @@ wkv6_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __res
         }
       }
     }
-    for (int i = tid; i < nt * 16; i += 64) {
-      const int quad = i & 15, tl = i >> 4;
+    for (int i = tid; i < nt * QUADS; i += N) {
+      const int quad = i % QUADS, tl = i / QUADS;
       const long long off = base + (long long)(t0 + tl) * tstride + 4 * quad;
       const float4 r4 = load4(r + off), k4 = load4(k + off), w4 = load4(w + off);
       *reinterpret_cast<float4*>(&sm.tile[tl][0][4 * quad]) = r4;
@@ -238,8 +249,8 @@ wkv6_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __res
       *reinterpret_cast<float4*>(&sm.tile[tl][4][4 * quad]) = make_float4(r4.x * u4.x, r4.y * u4.y, r4.z * u4.z, r4.w * u4.w);
       *reinterpret_cast<float4*>(&sm.tile[tl][5][4 * quad]) = make_float4(u4.x * k4.x, u4.y * k4.y, u4.z * k4.z, u4.w * k4.w);
     }
-    if (tid < nt * 4) {
-      const int tl = tid >> 2, quad = tid & 3;
+    for (int i = tid; i < nt * 4; i += N) {
+      const int tl = i >> 2, quad = i & 3;
       const long long off = base + (long long)(t0 + tl) * tstride + y * VS + 4 * quad;
       *reinterpret_cast<float4*>(&sm.vt[tl][4 * quad]) = load4(v + off);
       *reinterpret_cast<float4*>(&sm.dyt[tl][4 * quad]) = load4(d_y + off);
@@ -249,15 +260,15 @@ wkv6_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __res
 #pragma unroll
       for (int j = 0; j < 16; ++j) S[j] = sm.sub[c & 7][16 * kq + j][vl];
     } else {
-      const float* p = ckpt + unit * ckpt_unit + (((long long)c * HS) + 16 * kq) * HS + y * VS + vl;
+      const float* p = ckpt + unit * ckpt_unit + (((long long)c * N) + 16 * kq) * N + y * VS + vl;
 #pragma unroll
-      for (int j = 0; j < 16; ++j) S[j] = p[j * HS];
+      for (int j = 0; j < 16; ++j) S[j] = p[j * N];
     }
     __syncthreads();
     // sum_k r u k per token (threads 0..nt-1, one token each)
     if (tid < nt) {
       float s = 0.f;
-      for (int j = 0; j < HS; ++j) s += sm.tile[tid][4][j] * sm.tile[tid][3][j];
+      for (int j = 0; j < N; ++j) s += sm.tile[tid][4][j] * sm.tile[tid][3][j];
       sm.ruk[tid] = s;
     }
     // re-run the chunk forward (value role), keeping the state before every token
@@ -286,9 +297,7 @@ wkv6_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __res
         Gv[j] = td[j] * Gv[j] + tr[j] * dyr;
         Gv[j + 1] = td[j + 1] * Gv[j + 1] + tr[j + 1] * dyr;
       }
-      float dvv = a0 + a1;
-      dvv += __shfl_xor_sync(0xffffffffu, dvv, 1);
-      dvv += __shfl_xor_sync(0xffffffffu, dvv, 2);
+      const float dvv = sum_kq<NKQ>(a0 + a1);
       if (kq == 0) sm.dvt[tl][vl] = dvv + dyr * sm.ruk[tl];
       // key role
       const float rk = sm.tile[tl][0][kc], dk_ = sm.tile[tl][1][kc];
@@ -309,7 +318,7 @@ wkv6_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __res
       if (kc == 0) sm.pdyv[pb][tl] = p_dyv;
     }
     __syncthreads();
-    for (int i = tid; i < nt * VS; i += 64) {
+    for (int i = tid; i < nt * VS; i += N) {
       const int tl = i >> 4, vi = i & 15;
       dv[base + (long long)(t0 + tl) * tstride + y * VS + vi] = from_f32<T>(sm.dvt[tl][vi]);
     }
@@ -321,7 +330,7 @@ wkv6_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __res
         const float* rp = cluster.map_shared_rank(&sm.part[pb][tl][0][0], rk_);
         const float* rd = cluster.map_shared_rank(&sm.pdyv[pb][0], rk_);
 #pragma unroll
-        for (int qn = 0; qn < 3; ++qn) acc[qn] += rp[qn * HS + kc];
+        for (int qn = 0; qn < 3; ++qn) acc[qn] += rp[qn * N + kc];
         dyv += rd[tl];
       }
       const long long off = base + (long long)(t0 + tl) * tstride + kc;
@@ -332,22 +341,22 @@ wkv6_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __res
     }
     __syncthreads();
   }
-  du_partial[((long long)unit * NQ + y) * HS + kc] = du_acc;
+  du_partial[((long long)unit * NQ + y) * N + kc] = du_acc;
   if (d_s0) {
 #pragma unroll
-    for (int j = 0; j < 16; ++j) d_s0[(((long long)unit * HS) + 16 * kq + j) * HS + y * VS + vl] = Gv[j];
+    for (int j = 0; j < 16; ++j) d_s0[(((long long)unit * N) + 16 * kq + j) * N + y * VS + vl] = Gv[j];
   }
   cluster.sync();
 }
 
-// du[h][k] = sum over batch rows and the four CTAs of a unit, in a fixed order.
-__global__ void __launch_bounds__(64)
+// du[h][k] = sum over batch rows and the CTAs of a unit, in a fixed order (one thread per key channel).
+__global__ void __launch_bounds__(128)
 wkv6_du_reduce_kernel(const float* __restrict__ du_partial, float* __restrict__ du, int B, int H) {
-  const int hi = blockIdx.x, kc = threadIdx.x;
+  const int hi = blockIdx.x, kc = threadIdx.x, n = blockDim.x, nq = n / VS;
   float s = 0.f;
   for (int bi = 0; bi < B; ++bi)
-    for (int q = 0; q < NQ; ++q) s += du_partial[(((long long)bi * H + hi) * NQ + q) * HS + kc];
-  du[hi * HS + kc] = s;
+    for (int q = 0; q < nq; ++q) s += du_partial[(((long long)bi * H + hi) * nq + q) * n + kc];
+  du[hi * n + kc] = s;
 }
 
 // The same for the chunked path with its recurrent fallback: a unit contributes one row of `part_chunked`
@@ -355,6 +364,7 @@ wkv6_du_reduce_kernel(const float* __restrict__ du_partial, float* __restrict__ 
 __global__ void __launch_bounds__(64)
 wkv6_du_reduce_mixed_kernel(const float* __restrict__ part_chunked, const float* __restrict__ part_rec,
                             const int* __restrict__ flags, float* __restrict__ du, int B, int H) {
+  constexpr int NQ = HS / VS;
   const int hi = blockIdx.x, kc = threadIdx.x;
   float s = 0.f;
   for (int bi = 0; bi < B; ++bi) {
@@ -370,33 +380,68 @@ wkv6_du_reduce_mixed_kernel(const float* __restrict__ part_chunked, const float*
 
 }  // namespace
 
+// head size 32, 64 or 128
+#define RWKVB200_DISPATCH_HEAD6(hs, ...)                          \
+  switch (hs) {                                                   \
+    case 32:  { constexpr int N = 32;  __VA_ARGS__; break; }      \
+    case 64:  { constexpr int N = 64;  __VA_ARGS__; break; }      \
+    case 128: { constexpr int N = 128; __VA_ARGS__; break; }      \
+    default: return RWKVB200_E_UNSUPPORTED;                       \
+  }
+
 int launch_wkv6_fwd(const void* r, const void* k, const void* v, const void* w, const float* u,
                     const float* s0, int n_state, const int32_t* smap, void* y, float* sT,
                     float* ckpt, int B, int Tn, int H, int dtype, cudaStream_t st, const UnitSel* sel_,
-                    int ckpt_every) {
-  dim3 grid(B * H, NQ);
+                    int ckpt_every, int head_size) {
   const UnitSel sel = sel_ ? *sel_ : UnitSel{nullptr, nullptr, nullptr, 0};
   ProfScope prof("wkv6_fwd_kernel", st);
-  RWKVB200_DISPATCH_DTYPE(dtype,
-    wkv6_fwd_kernel<T><<<grid, 64, 0, st>>>((const T*)r, (const T*)k, (const T*)v, (const T*)w, u, s0, n_state, smap,
-                                            (T*)y, sT, ckpt, ckpt_every ? ckpt_every : CK, Tn, H, sel));
+  RWKVB200_DISPATCH_HEAD6(head_size,
+    dim3 grid(B * H, N / VS);
+    RWKVB200_DISPATCH_DTYPE(dtype,
+      wkv6_fwd_kernel<T, N><<<grid, N, 0, st>>>((const T*)r, (const T*)k, (const T*)v, (const T*)w, u, s0, n_state,
+                                                smap, (T*)y, sT, ckpt, ckpt_every ? ckpt_every : CK, Tn, H, sel)));
   return check_launch();
 }
 
+namespace {
+// the backward kernel over a cluster of the N/16 CTAs of a unit
+template <typename T, int N, bool COARSE>
+int launch_bwd_cluster(const void* r, const void* k, const void* v, const void* w, const float* u, const void* d_y,
+                       const float* d_sT, const float* ckpt, void* dr, void* dk, void* dv, void* dw,
+                       float* du_partial, float* d_s0, int B, int Tn, int H, cudaStream_t st, const UnitSel& sel) {
+  typedef typename std::conditional<COARSE, BwdSmemCoarse<N>, BwdSmem<N>>::type Smem;
+  const int smem = (int)sizeof(Smem);
+  if (cuda_ok(cudaFuncSetAttribute(wkv6_bwd_kernel<T, N, COARSE>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)))
+    return RWKVB200_E_CUDA;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(B * H, N / VS);
+  cfg.blockDim = dim3(N);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;      // the CTAs of a unit exchange partial sums
+  attr[0].val.clusterDim.x = 1; attr[0].val.clusterDim.y = N / VS; attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (cuda_ok(cudaLaunchKernelEx(&cfg, wkv6_bwd_kernel<T, N, COARSE>, (const T*)r, (const T*)k, (const T*)v,
+                                 (const T*)w, u, (const T*)d_y, d_sT, ckpt, (T*)dr, (T*)dk, (T*)dv, (T*)dw,
+                                 du_partial, d_s0, Tn, H, sel)))
+    return RWKVB200_E_CUDA;
+  return RWKVB200_OK;
+}
+}  // namespace
+
 // The backward over the units marked in sel->flags, from checkpoints 64 tokens apart (sel->ckpt_unit_stride
-// floats between units); du_partial receives four rows per unit.  No reduction of du.
+// floats between units); du_partial receives four rows per unit.  No reduction of du.  Head size 64.
 int launch_wkv6_bwd_coarse(const void* r, const void* k, const void* v, const void* w, const float* u,
                            const void* d_y, const float* d_sT, const float* ckpt,
                            void* dr, void* dk, void* dv, void* dw, float* du_partial, float* d_s0,
                            int B, int Tn, int H, int dtype, cudaStream_t st, const UnitSel* sel) {
-  dim3 grid(B * H, NQ);
-  const int smem = (int)sizeof(BwdSmemCoarse);
   ProfScope prof("wkv6_bwd_kernel", st);
   RWKVB200_DISPATCH_DTYPE(dtype,
-    if (cuda_ok(cudaFuncSetAttribute(wkv6_bwd_kernel<T, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem))) return RWKVB200_E_CUDA;
-    wkv6_bwd_kernel<T, true><<<grid, 64, smem, st>>>((const T*)r, (const T*)k, (const T*)v, (const T*)w, u,
-                                                     (const T*)d_y, d_sT, ckpt, (T*)dr, (T*)dk, (T*)dv, (T*)dw,
-                                                     du_partial, d_s0, Tn, H, *sel));
+    const int e = launch_bwd_cluster<T, HS, true>(r, k, v, w, u, d_y, d_sT, ckpt, dr, dk, dv, dw, du_partial, d_s0,
+                                                  B, Tn, H, st, *sel);
+    if (e) return e);
   return check_launch();
 }
 
@@ -410,21 +455,20 @@ int launch_wkv6_du_reduce_mixed(const float* part_chunked, const float* part_rec
 int launch_wkv6_bwd(const void* r, const void* k, const void* v, const void* w, const float* u,
                     const void* d_y, const float* d_sT, const float* ckpt,
                     void* dr, void* dk, void* dv, void* dw, float* du_partial, float* du, float* d_s0,
-                    int B, int Tn, int H, int dtype, cudaStream_t st) {
-  dim3 grid(B * H, NQ);
-  const int smem = (int)sizeof(BwdSmem);
+                    int B, int Tn, int H, int dtype, cudaStream_t st, int head_size) {
   {
     ProfScope prof("wkv6_bwd_kernel", st);
-    RWKVB200_DISPATCH_DTYPE(dtype,
-      if (cuda_ok(cudaFuncSetAttribute(wkv6_bwd_kernel<T, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem))) return RWKVB200_E_CUDA;
-      wkv6_bwd_kernel<T, false><<<grid, 64, smem, st>>>((const T*)r, (const T*)k, (const T*)v, (const T*)w, u,
-                                                        (const T*)d_y, d_sT, ckpt, (T*)dr, (T*)dk, (T*)dv, (T*)dw,
-                                                        du_partial, d_s0, Tn, H, UnitSel{nullptr, nullptr, nullptr, 0}));
+    const UnitSel none{nullptr, nullptr, nullptr, 0};
+    RWKVB200_DISPATCH_HEAD6(head_size,
+      RWKVB200_DISPATCH_DTYPE(dtype,
+        const int e = launch_bwd_cluster<T, N, false>(r, k, v, w, u, d_y, d_sT, ckpt, dr, dk, dv, dw, du_partial,
+                                                      d_s0, B, Tn, H, st, none);
+        if (e) return e));
   }
   int e = check_launch();
   if (e) return e;
   ProfScope prof("wkv6_du_reduce_kernel", st);
-  wkv6_du_reduce_kernel<<<H, 64, 0, st>>>(du_partial, du, B, H);
+  wkv6_du_reduce_kernel<<<H, head_size, 0, st>>>(du_partial, du, B, H);
   return check_launch();
 }
 

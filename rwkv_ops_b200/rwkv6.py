@@ -17,7 +17,8 @@ import torch
 
 from . import _lib
 
-HEAD_SIZE = 64
+HEAD_SIZE = 64                  # the head size of the chunked tensor-core path
+HEAD_SIZES = (32, 64, 128)      # 32 and 128 run the float32 recurrence
 _ALGO_NAMES = {"auto": _lib.ALGO_AUTO, "recurrent": _lib.ALGO_RECURRENT, "chunked": _lib.ALGO_CHUNKED}
 
 
@@ -32,21 +33,21 @@ def _wkv6_fwd(r: torch.Tensor, k: torch.Tensor, v: torch.Tensor, w: torch.Tensor
     lib = _lib.load()
     dev = _lib.require_cuda(r, k, v, w, u, s0, state_map)
     B, T, C = r.shape
-    H = C // HEAD_SIZE
+    H, N = u.shape                      # u arrives as [H, head_size]
     code = _lib.dtype_code(r.dtype)
     y = torch.empty_like(r)
-    sT = torch.empty(B, H, HEAD_SIZE, HEAD_SIZE, dtype=torch.float32, device=dev)
+    sT = torch.empty(B, H, N, N, dtype=torch.float32, device=dev)
     n_state = 0 if s0 is None else s0.shape[0]
     with torch.cuda.device(dev):
         # a training forward of the chunked path leaves the chunk-boundary states for the backward; an
         # inference forward needs a few bytes per (batch, head) for the decay-range marks
         flags = algo | (_lib.ALGO_KEEP if keep else 0)
-        nws = lib.rwkvb200_wkv6_fwd_workspace_bytes(B, T, H, HEAD_SIZE, code, flags)
+        nws = lib.rwkvb200_wkv6_fwd_workspace_bytes(B, T, H, N, code, flags)
         kept = torch.empty(nws, dtype=torch.uint8, device=dev)
         rc = lib.rwkvb200_wkv6_fwd(r.data_ptr(), k.data_ptr(), v.data_ptr(), w.data_ptr(), u.data_ptr(),
                                    _lib.ptr(s0), n_state, _lib.ptr(state_map), y.data_ptr(), sT.data_ptr(),
                                    kept.data_ptr() if nws else None, nws,
-                                   B, T, H, HEAD_SIZE, code, flags, _lib.stream_ptr(dev))
+                                   B, T, H, N, code, flags, _lib.stream_ptr(dev))
         _lib.check(rc, "wkv6_fwd")
         _lib.check_status("wkv6_fwd")
     if not keep:
@@ -57,9 +58,9 @@ def _wkv6_fwd(r: torch.Tensor, k: torch.Tensor, v: torch.Tensor, w: torch.Tensor
 @_wkv6_fwd.register_fake
 def _(r, k, v, w, u, s0, state_map, algo, keep):
     B, T, C = r.shape
-    H = C // HEAD_SIZE
-    chunked = (algo & 0xff) != _lib.ALGO_RECURRENT
-    return (torch.empty_like(r), r.new_empty((B, H, HEAD_SIZE, HEAD_SIZE), dtype=torch.float32),
+    H, N = u.shape
+    chunked = (algo & 0xff) != _lib.ALGO_RECURRENT and N == HEAD_SIZE
+    return (torch.empty_like(r), r.new_empty((B, H, N, N), dtype=torch.float32),
             r.new_empty((_lib.wkv6_kept_bytes(B, T, H) if keep and chunked else 0,), dtype=torch.uint8))
 
 
@@ -73,21 +74,21 @@ def _wkv6_bwd(r: torch.Tensor, k: torch.Tensor, v: torch.Tensor, w: torch.Tensor
     lib = _lib.load()
     dev = _lib.require_cuda(r, k, v, w, u, s0, state_map, d_y, d_sT)
     B, T, C = r.shape
-    H = C // HEAD_SIZE
+    H, N = u.shape
     code = _lib.dtype_code(r.dtype)
     dr, dk, dv, dw = (torch.empty_like(r) for _ in range(4))
-    du = torch.empty(H, HEAD_SIZE, dtype=torch.float32, device=dev)
-    ds0 = torch.empty(B, H, HEAD_SIZE, HEAD_SIZE, dtype=torch.float32, device=dev)
+    du = torch.empty(H, N, dtype=torch.float32, device=dev)
+    ds0 = torch.empty(B, H, N, N, dtype=torch.float32, device=dev)
     n_state = 0 if s0 is None else s0.shape[0]
     with torch.cuda.device(dev):
-        nws = lib.rwkvb200_wkv6_bwd_workspace_bytes(B, T, H, HEAD_SIZE, code, algo)
+        nws = lib.rwkvb200_wkv6_bwd_workspace_bytes(B, T, H, N, code, algo)
         have = kept.numel() >= nws and kept.numel() > 0      # the forward left its chunk-boundary states
         ws = kept if have else torch.empty(nws, dtype=torch.uint8, device=dev)
         algo = algo | (_lib.ALGO_KEEP if have else 0)
         rc = lib.rwkvb200_wkv6_bwd(r.data_ptr(), k.data_ptr(), v.data_ptr(), w.data_ptr(), u.data_ptr(),
                                    _lib.ptr(s0), n_state, _lib.ptr(state_map), d_y.data_ptr(), _lib.ptr(d_sT),
                                    dr.data_ptr(), dk.data_ptr(), dv.data_ptr(), dw.data_ptr(), du.data_ptr(),
-                                   ds0.data_ptr(), ws.data_ptr(), nws, B, T, H, HEAD_SIZE, code, algo,
+                                   ds0.data_ptr(), ws.data_ptr(), nws, B, T, H, N, code, algo,
                                    _lib.stream_ptr(dev))
         _lib.check(rc, "wkv6_bwd")
         _lib.check_status("wkv6_bwd")
@@ -97,10 +98,10 @@ def _wkv6_bwd(r: torch.Tensor, k: torch.Tensor, v: torch.Tensor, w: torch.Tensor
 @_wkv6_bwd.register_fake
 def _(r, k, v, w, u, s0, state_map, d_y, d_sT, kept, algo):
     B, T, C = r.shape
-    H = C // HEAD_SIZE
+    H, N = u.shape
     e = torch.empty_like
-    return (e(r), e(r), e(r), e(r), r.new_empty((H, HEAD_SIZE), dtype=torch.float32),
-            r.new_empty((B, H, HEAD_SIZE, HEAD_SIZE), dtype=torch.float32))
+    return (e(r), e(r), e(r), e(r), r.new_empty((H, N), dtype=torch.float32),
+            r.new_empty((B, H, N, N), dtype=torch.float32))
 
 
 def _setup_ctx(ctx, inputs, output):
@@ -139,8 +140,8 @@ class RWKVKernelOperator:
     """Drop-in for the class returned by the reference's ``get_rwkv6_kernel``."""
 
     def __init__(self, head_size, max_sequence_length, ops_loop=False):
-        if head_size != HEAD_SIZE:
-            raise ValueError("rwkv_ops_b200 is built for head size 64")
+        if head_size not in HEAD_SIZES:
+            raise ValueError(f"rwkv_ops_b200 wkv6 supports head sizes {HEAD_SIZES}, got {head_size}")
         self.head_size = head_size
         self.max_sequence_length = max_sequence_length   # kept for compatibility; no limit applies
         self.ops_loop = ops_loop
@@ -192,6 +193,10 @@ class RWKVKernelOperator:
             assert state_map is None, "state_map needs init_state"
 
         algo = _default_algo()
+        if N != HEAD_SIZE:
+            if algo == _lib.ALGO_CHUNKED:
+                raise ValueError("the chunked wkv6 path is built for head size 64")
+            algo = _lib.ALGO_RECURRENT
         needs_grad = torch.is_grad_enabled() and (
             any(x.requires_grad for x in (r, k, v, w, u)) or (init_state is not None and init_state.requires_grad))
         keep = needs_grad and algo != _lib.ALGO_RECURRENT and T > 1

@@ -65,7 +65,14 @@ def test_argument_validation_without_launch(lib):
     # wkv6: several initial states and no state_map, n_state != B
     assert lib.rwkvb200_wkv6_fwd(*([A] * 5), A, 3, None, A, None, None, 0, 2, 8, 4, 64, 0, 0, None) == -8
     assert lib.rwkvb200_wkv6_bwd_workspace_bytes(2, 8, 4, 64, 0, 1) > 0
-    assert lib.rwkvb200_wkv6_bwd_workspace_bytes(2, 8, 4, 32, 0, 1) == 0
+    # wkv6 head sizes: 32 and 128 through the recurrence (checkpoints every 8 tokens + one du row per CTA),
+    # anything else and the chunked path at a head size other than 64 are unsupported
+    assert lib.rwkvb200_wkv6_bwd_workspace_bytes(2, 8, 4, 32, 0, 1) == 2 * 4 * 32 * 32 * 4 + 2 * 4 * 2 * 32 * 4
+    assert lib.rwkvb200_wkv6_bwd_workspace_bytes(2, 8, 4, 128, 0, 0) == 2 * 4 * 128 * 128 * 4 + 2 * 4 * 8 * 128 * 4
+    assert lib.rwkvb200_wkv6_bwd_workspace_bytes(2, 8, 4, 48, 0, 1) == 0
+    assert lib.rwkvb200_wkv6_bwd_workspace_bytes(2, 8, 4, 128, 0, 2) == 0
+    assert lib.rwkvb200_wkv6_fwd(*([A] * 5), None, 0, None, A, None, None, 0, 2, 8, 4, 48, 0, 0, None) == -6
+    assert lib.rwkvb200_wkv6_fwd(*([A] * 5), None, 0, None, A, None, None, 0, 2, 8, 4, 128, 0, 2, None) == -6
 
 
 def test_python_layer_refuses_cpu_tensors():

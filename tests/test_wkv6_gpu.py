@@ -76,6 +76,37 @@ def test_ragged_lengths_vs_oracle(T, dtype):
     assert rel_l2(s0.grad, s0r.grad) < tol
 
 
+@pytest.mark.parametrize("N", [32, 128])
+@pytest.mark.parametrize("T", [1, 9, 70])
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-4), (torch.bfloat16, 2e-2)])
+def test_head_sizes_32_and_128(N, T, dtype, tol):
+    """The operator's constructor takes the head size (rwkv6_kernel/__init__.py:37-50): 32 and 128 against the
+    oracle, outputs, final state and every gradient, with a repeated state_map row."""
+    B, H = 3, 2
+    d = wkv6_inputs(B, T, H, N, dtype=dtype, seed=640 + T + N, n_state=2, with_grads=True)
+    d["state_map"] = torch.tensor([1, 0, 1], dtype=torch.int32)
+    ref = {n: d[n].float().clone().requires_grad_(True) for n in "rkvwu"}
+    s0r = d["init_state"].float().clone().requires_grad_(True)
+    y_ref, s_ref = OracleOp(N, T)(ref["r"], ref["k"], ref["v"], ref["w"], ref["u"], with_state=True,
+                                  init_state=s0r, state_map=d["state_map"])
+    ((y_ref * d["d_y"].float()).sum() + (s_ref * d["d_state"].float()).sum()).backward()
+    g = {n: d[n].cuda().requires_grad_(True) for n in "rkvwu"}
+    s0 = d["init_state"].cuda().requires_grad_(True)
+    y, s = ro.RWKV6_OP(N, T)(g["r"], g["k"], g["v"], g["w"], g["u"], with_state=True, init_state=s0,
+                             state_map=d["state_map"].cuda())
+    assert y.shape == (B, T, H * N) and s.shape == (B, H, N, N) and y.dtype == dtype
+    ((y.float() * d["d_y"].cuda().float()).sum() + (s.float() * d["d_state"].cuda().float()).sum()).backward()
+    errs = {"y": rel_l2(y, y_ref), "s": rel_l2(s, s_ref), "ds0": rel_l2(s0.grad, s0r.grad)}
+    errs.update({f"d{n}": rel_l2(g[n].grad, ref[n].grad) for n in "rkvwu"})
+    assert all(e < tol for e in errs.values()), errs
+    assert g["u"].grad.shape == d["u"].shape
+
+
+def test_unsupported_head_size_raises():
+    with pytest.raises(ValueError):
+        ro.RWKV6_OP(48, 16)
+
+
 def test_u_shapes_list_state_map_and_errors():
     B, T, H = 2, 12, 2
     d = wkv6_inputs(B, T, H, seed=61, n_state=3)
