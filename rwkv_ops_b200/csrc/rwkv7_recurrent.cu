@@ -32,7 +32,10 @@ namespace rwkvb200 {
 namespace {
 
 constexpr int VS = 16;        // value rows per CTA
-constexpr int TL = 16;        // tokens staged per tile in the forward kernel
+// A staged vector of N key channels is kept as segments of 16 with 4 floats of padding between them: the lanes
+// of a quarter warp read the same 16 bytes of N/16 different segments, which 64 bytes apart would share banks.
+__host__ __device__ constexpr int padk(int k) { return k + ((k >> 4) << 2); }
+template <int N> __host__ __device__ constexpr int NP() { return N + N / 4; }
 constexpr int CK = R7_CKPT;   // chunk of the backward = checkpoint interval
 // The kernels are templates over the head size N (64 or 128): N / 16 CTAs per (batch, head), N threads per
 // CTA, N / 16 lanes share a state row (16 key columns each).
@@ -46,7 +49,8 @@ rwkv7_rec_fwd_kernel(const T* __restrict__ r, const T* __restrict__ w, const T* 
                      const T* __restrict__ v, const T* __restrict__ a, const T* __restrict__ b,
                      const float* __restrict__ h0, int n_state, T* __restrict__ o, float* __restrict__ ht,
                      float* __restrict__ ckpt, int ckpt_every, int Tn_dense, int H, TokLayout lay, UnitSel sel) {
-  __shared__ __align__(16) float tile[TL][5][N];   // r, d, k, a, b
+  constexpr int TL = N > 64 ? 8 : 16;   // tokens staged per tile (the static shared memory holds 16 only up to N = 64)
+  __shared__ __align__(16) float tile[TL][5][NP<N>()];   // r, d, k, a, b
   __shared__ __align__(16) float vt[TL][VS];
   __shared__ __align__(16) float ot[TL][VS];
 
@@ -74,22 +78,39 @@ rwkv7_rec_fwd_kernel(const T* __restrict__ r, const T* __restrict__ w, const T* 
     for (int j = 0; j < 16; ++j) S[j] = 0.f;
   }
 
+  // The inputs of a tile travel global memory -> registers -> shared memory, and the loads of tile i + 1 are
+  // issued before the tokens of tile i are worked on: few warps share an SM here (the grid is B*H*N/16 CTAs of N
+  // threads), so a load that is waited for where it is issued costs its full latency every time.
+  constexpr int PER = TL * 5 / 4;      // float4 per thread per tile: TL tokens x 5 vectors x N/4 quads over N threads
+  float4 buf[PER], vbuf = make_float4(0.f, 0.f, 0.f, 0.f);
+  const int quad = tid % (N / 4), rq = tid / (N / 4);      // this thread's quad of channels; its rows are rq + 4 m
+  auto fetch = [&](int t0) {
+    const int nt = min(TL, Tn - t0);
+#pragma unroll
+    for (int m = 0; m < PER; ++m) {
+      const int row = rq + 4 * m, tl = row / 5, which = row % 5;
+      const T* src = which == 0 ? r : which == 1 ? w : which == 2 ? k : which == 3 ? a : b;
+      buf[m] = tl < nt ? load4(src + base + (long long)(t0 + tl) * lay.st + 4 * quad) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    if (tid < nt * 4)
+      vbuf = load4(v + base + (long long)(t0 + (tid >> 2)) * lay.st + y * VS + 4 * (tid & 3));
+  };
+  auto stash = [&]() {
+#pragma unroll
+    for (int m = 0; m < PER; ++m) {
+      const int row = rq + 4 * m, tl = row / 5, which = row % 5;
+      float4 f = buf[m];
+      if (which == 1) f = make_float4(decay_of(f.x), decay_of(f.y), decay_of(f.z), decay_of(f.w));
+      *reinterpret_cast<float4*>(&tile[tl][which][padk(4 * quad)]) = f;
+    }
+    if (tid < TL * 4) *reinterpret_cast<float4*>(&vt[tid >> 2][4 * (tid & 3)]) = vbuf;
+  };
+  if (Tn > 0) fetch(0);
   for (int t0 = 0; t0 < Tn; t0 += TL) {
     const int nt = min(TL, Tn - t0);
-    // stage the tile: 5 vectors x nt tokens, one float4 per thread per pass
-    for (int i = tid; i < nt * 5 * (N / 4); i += N) {
-      const int quad = i % (N / 4), row = i / (N / 4), tl = row / 5, which = row % 5;
-      const T* src = which == 0 ? r : which == 1 ? w : which == 2 ? k : which == 3 ? a : b;
-      float4 f = load4(src + base + (long long)(t0 + tl) * lay.st + 4 * quad);
-      if (which == 1) f = make_float4(decay_of(f.x), decay_of(f.y), decay_of(f.z), decay_of(f.w));
-      *reinterpret_cast<float4*>(&tile[tl][which][4 * quad]) = f;
-    }
-    if (tid < nt * 4) {
-      const int tl = tid >> 2, quad = tid & 3;
-      *reinterpret_cast<float4*>(&vt[tl][4 * quad]) =
-          load4(v + base + (long long)(t0 + tl) * lay.st + y * VS + 4 * quad);
-    }
+    stash();
     __syncthreads();
+    if (t0 + TL < Tn) fetch(t0 + TL);
 
     for (int tl = 0; tl < nt; ++tl) {
       const int t = t0 + tl;
@@ -99,11 +120,11 @@ rwkv7_rec_fwd_kernel(const T* __restrict__ r, const T* __restrict__ w, const T* 
         for (int j = 0; j < 16; j += 4)
           *reinterpret_cast<float4*>(p + j) = make_float4(S[j], S[j + 1], S[j + 2], S[j + 3]);
       }
-      const float* tr = &tile[tl][0][16 * kq];
-      const float* td = &tile[tl][1][16 * kq];
-      const float* tk = &tile[tl][2][16 * kq];
-      const float* ta = &tile[tl][3][16 * kq];
-      const float* tb = &tile[tl][4][16 * kq];
+      const float* tr = &tile[tl][0][20 * kq];
+      const float* td = &tile[tl][1][20 * kq];
+      const float* tk = &tile[tl][2][20 * kq];
+      const float* ta = &tile[tl][3][20 * kq];
+      const float* tb = &tile[tl][4][20 * kq];
       float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
 #pragma unroll
       for (int j = 0; j < 16; j += 4) {
@@ -149,7 +170,7 @@ rwkv7_rec_fwd_kernel(const T* __restrict__ r, const T* __restrict__ w, const T* 
 // ---------------------------------------------------------------------------------------------
 template <int N>
 struct BwdSmem {
-  float tile[CK][6][N];         // r, d, exp(w), k, a, b
+  float tile[CK][6][NP<N>()];         // r, d, exp(w), k, a, b
   float vt[CK][VS];
   float dot[CK][VS];
   float sa[CK][VS];
@@ -198,39 +219,62 @@ rwkv7_rec_bwd_kernel(const T* __restrict__ r, const T* __restrict__ w, const T* 
     for (int i = 0; i < VS; ++i) dSc[i] = 0.f;
   }
 
-  for (int c = NC - 1; c >= 0; --c) {
-    const int t0 = c * CK, nt = min(CK, Tn - t0), pb = c & 1;
-    // ---- stage the chunk's inputs
-    for (int i = tid; i < nt * 6 * (N / 4); i += N) {
-      const int quad = i % (N / 4), row = i / (N / 4), tl = row / 6, which = row % 6;
-      const T* src = which == 0 ? r : (which == 1 || which == 2) ? w : which == 3 ? k : which == 4 ? a : b;
-      float4 f = load4(src + base + (long long)(t0 + tl) * lay.st + 4 * quad);
-      if (which == 1) f = make_float4(decay_of(f.x), decay_of(f.y), decay_of(f.z), decay_of(f.w));
-      if (which == 2) f = make_float4(expf(f.x), expf(f.y), expf(f.z), expf(f.w));
-      *reinterpret_cast<float4*>(&sm.tile[tl][which][4 * quad]) = f;
+  // The inputs and the checkpoint of chunk c - 1 are requested (into registers) before chunk c is worked on,
+  // and written to shared memory when chunk c is done: see the forward kernel.
+  constexpr int PER = CK * 5 / 4;      // float4 per thread per chunk: CK tokens x (r, w, k, a, b) x N/4 quads
+  float4 buf[PER], vbuf = make_float4(0.f, 0.f, 0.f, 0.f), dobuf = vbuf, Snext[4];
+  const int quad = tid % (N / 4), rq = tid / (N / 4);
+  auto fetch = [&](int c) {
+    const int t0 = c * CK, nt = min(CK, Tn - t0);
+#pragma unroll
+    for (int m = 0; m < PER; ++m) {
+      const int row = rq + 4 * m, tl = row / 5, which = row % 5;
+      const T* src = which == 0 ? r : which == 1 ? w : which == 2 ? k : which == 3 ? a : b;
+      buf[m] = tl < nt ? load4(src + base + (long long)(t0 + tl) * lay.st + 4 * quad) : make_float4(0.f, 0.f, 0.f, 0.f);
     }
     if (tid < nt * 4) {
-      const int tl = tid >> 2, quad = tid & 3;
-      const long long off = base + (long long)(t0 + tl) * lay.st + y * VS + 4 * quad;
-      *reinterpret_cast<float4*>(&sm.vt[tl][4 * quad]) = load4(v + off);
-      *reinterpret_cast<float4*>(&sm.dot[tl][4 * quad]) = load4(d_o + off);
+      const long long off = base + (long long)(t0 + (tid >> 2)) * lay.st + y * VS + 4 * (tid & 3);
+      vbuf = load4(v + off);
+      dobuf = load4(d_o + off);
     }
-    // ---- re-run the chunk forward from its checkpoint (row role)
-    float S[16];
-    {
-      const float* p = ckpt + unit * ckpt_unit + (((long long)c * N) + (y * VS + vl)) * N + 16 * kq;
+    const float* p = ckpt + unit * ckpt_unit + (((long long)c * N) + (y * VS + vl)) * N + 16 * kq;
 #pragma unroll
-      for (int j = 0; j < 16; j += 4) {
-        float4 f = *reinterpret_cast<const float4*>(p + j);
-        S[j] = f.x; S[j + 1] = f.y; S[j + 2] = f.z; S[j + 3] = f.w;
+    for (int j = 0; j < 4; ++j) Snext[j] = *reinterpret_cast<const float4*>(p + 4 * j);
+  };
+  // tile rows: 0 r, 1 d, 2 exp(w), 3 k, 4 a, 5 b
+  auto stash = [&]() {
+#pragma unroll
+    for (int m = 0; m < PER; ++m) {
+      const int row = rq + 4 * m, tl = row / 5, which = row % 5;
+      const float4 f = buf[m];
+      if (which == 1) {
+        *reinterpret_cast<float4*>(&sm.tile[tl][1][padk(4 * quad)]) =
+            make_float4(decay_of(f.x), decay_of(f.y), decay_of(f.z), decay_of(f.w));
+        *reinterpret_cast<float4*>(&sm.tile[tl][2][padk(4 * quad)]) = make_float4(expf(f.x), expf(f.y), expf(f.z), expf(f.w));
+      } else {
+        *reinterpret_cast<float4*>(&sm.tile[tl][which == 0 ? 0 : which + 1][padk(4 * quad)]) = f;
       }
     }
+    if (tid < CK * 4) {
+      *reinterpret_cast<float4*>(&sm.vt[tid >> 2][4 * (tid & 3)]) = vbuf;
+      *reinterpret_cast<float4*>(&sm.dot[tid >> 2][4 * (tid & 3)]) = dobuf;
+    }
+  };
+  if (NC > 0) fetch(NC - 1);
+  for (int c = NC - 1; c >= 0; --c) {
+    const int t0 = c * CK, nt = min(CK, Tn - t0), pb = c & 1;
+    // ---- the chunk's inputs, and its checkpoint (row role) for the forward re-run
+    stash();
+    float S[16];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) { S[4 * j] = Snext[j].x; S[4 * j + 1] = Snext[j].y; S[4 * j + 2] = Snext[j].z; S[4 * j + 3] = Snext[j].w; }
     __syncthreads();
+    if (c > 0) fetch(c - 1);
     for (int tl = 0; tl < nt; ++tl) {
-      const float* td = &sm.tile[tl][1][16 * kq];
-      const float* tk = &sm.tile[tl][3][16 * kq];
-      const float* ta = &sm.tile[tl][4][16 * kq];
-      const float* tb = &sm.tile[tl][5][16 * kq];
+      const float* td = &sm.tile[tl][1][20 * kq];
+      const float* tk = &sm.tile[tl][3][20 * kq];
+      const float* ta = &sm.tile[tl][4][20 * kq];
+      const float* tb = &sm.tile[tl][5][20 * kq];
       float s0 = 0.f, s1 = 0.f;
 #pragma unroll
       for (int j = 0; j < 16; j += 2) {
@@ -256,12 +300,12 @@ rwkv7_rec_bwd_kernel(const T* __restrict__ r, const T* __restrict__ w, const T* 
     for (int i = 0; i < VS; ++i) St[i] = sm.Sbuf[nt][i][kc];
     for (int tl = nt - 1; tl >= 0; --tl) {
       const int buf = tl & 1;
-      const float rk = sm.tile[tl][0][kc], dk_ = sm.tile[tl][1][kc], ak = sm.tile[tl][4][kc];
-      const float* tr = &sm.tile[tl][0][16 * kq];
-      const float* td = &sm.tile[tl][1][16 * kq];
-      const float* tk = &sm.tile[tl][3][16 * kq];
-      const float* ta = &sm.tile[tl][4][16 * kq];
-      const float* tb = &sm.tile[tl][5][16 * kq];
+      const float rk = sm.tile[tl][0][padk(kc)], dk_ = sm.tile[tl][1][padk(kc)], ak = sm.tile[tl][4][padk(kc)];
+      const float* tr = &sm.tile[tl][0][20 * kq];
+      const float* td = &sm.tile[tl][1][20 * kq];
+      const float* tk = &sm.tile[tl][3][20 * kq];
+      const float* ta = &sm.tile[tl][4][20 * kq];
+      const float* tb = &sm.tile[tl][5][20 * kq];
       // row role: dS += do r^T ; dv = dS k ; dsa = dS b
       const float dor = sm.dot[tl][vl];
       float a0 = 0.f, a1 = 0.f, b0 = 0.f, b1 = 0.f;
@@ -329,7 +373,7 @@ rwkv7_rec_bwd_kernel(const T* __restrict__ r, const T* __restrict__ w, const T* 
       dk[off] = from_f32<T>(acc[1]);
       db[off] = from_f32<T>(acc[2]);
       da[off] = from_f32<T>(acc[3]);
-      dw[off] = from_f32<T>(acc[4] * sm.tile[tl][1][kc] * (-sm.tile[tl][2][kc]));
+      dw[off] = from_f32<T>(acc[4] * sm.tile[tl][1][padk(kc)] * (-sm.tile[tl][2][padk(kc)]));
     }
     // part[pb] is rewritten two chunks later, after the next chunk's cluster.sync(); the tile is
     // rewritten by the next chunk's staging, which only this CTA reads

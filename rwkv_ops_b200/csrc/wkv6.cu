@@ -31,6 +31,10 @@ namespace rwkvb200 {
 namespace {
 
 constexpr int VS = 16;
+// A staged vector of N key channels is kept as segments of 16 with 4 floats of padding between them: the lanes
+// of a quarter warp read the same 16 bytes of N/16 different segments, which 64 bytes apart would share banks.
+__host__ __device__ constexpr int padk(int k) { return k + ((k >> 4) << 2); }
+template <int N> __host__ __device__ constexpr int NP() { return N + N / 4; }
 constexpr int TL = 16;
 constexpr int CK = W6_CKPT;
 constexpr int SCOL = VS + 1;   // padded row (one key, 16 values) of a state slab in shared memory
@@ -58,7 +62,7 @@ wkv6_fwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __res
                 T* __restrict__ yout, float* __restrict__ sT, float* __restrict__ ckpt, int ckpt_every,
                 int Tn, int H, UnitSel sel) {
   constexpr int NKQ = N / VS, QUADS = N / 4;
-  __shared__ __align__(16) float tile[TL][4][N];   // r, d, k, r*u*k
+  __shared__ __align__(16) float tile[TL][4][NP<N>()];   // r, d, k, r*u*k
   __shared__ __align__(16) float vt[TL][VS];
   __shared__ __align__(16) float yt[TL][VS];
 
@@ -82,25 +86,55 @@ wkv6_fwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __res
     for (int j = 0; j < 16; ++j) S[j] = 0.f;
   }
 
-  for (int t0 = 0; t0 < Tn; t0 += TL) {
+  // The inputs of a tile travel global memory -> registers -> shared memory, and the loads of tile i + 1 are
+  // issued before the tokens of tile i are worked on: few warps share an SM here, so a load that is waited for
+  // where it is issued costs its full latency every time.
+  constexpr int PER = TL / 4;                      // (token, quad) pairs per thread per tile: TL x N/4 over N threads
+  constexpr int VPER = (TL * 4 + N - 1) / N;       // float4 of v per thread per tile (16 values per token)
+  float4 rbuf[PER], kbuf[PER], wbuf[PER], vbuf[VPER];
+  const int quad = tid % QUADS, rq = tid / QUADS;      // this thread's quad of channels; its tokens are rq + 4 m
+  auto fetch = [&](int t0) {
     const int nt = min(TL, Tn - t0);
-    for (int i = tid; i < nt * QUADS; i += N) {
-      const int quad = i % QUADS, tl = i / QUADS;   // quad == tid % QUADS
+#pragma unroll
+    for (int m = 0; m < PER; ++m) {
+      const int tl = rq + 4 * m;
       const long long off = base + (long long)(t0 + tl) * tstride + 4 * quad;
-      const float4 r4 = load4(r + off), k4 = load4(k + off), w4 = load4(w + off);
-      *reinterpret_cast<float4*>(&tile[tl][0][4 * quad]) = r4;
-      *reinterpret_cast<float4*>(&tile[tl][1][4 * quad]) =
+      const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
+      rbuf[m] = tl < nt ? load4(r + off) : z;
+      kbuf[m] = tl < nt ? load4(k + off) : z;
+      wbuf[m] = tl < nt ? load4(w + off) : z;
+    }
+#pragma unroll
+    for (int m = 0; m < VPER; ++m) {
+      const int i = tid + m * N;
+      vbuf[m] = i < nt * 4 ? load4(v + base + (long long)(t0 + (i >> 2)) * tstride + y * VS + 4 * (i & 3))
+                           : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+  };
+  auto stash = [&]() {
+#pragma unroll
+    for (int m = 0; m < PER; ++m) {
+      const int tl = rq + 4 * m;
+      const float4 r4 = rbuf[m], k4 = kbuf[m], w4 = wbuf[m];
+      *reinterpret_cast<float4*>(&tile[tl][0][padk(4 * quad)]) = r4;
+      *reinterpret_cast<float4*>(&tile[tl][1][padk(4 * quad)]) =
           make_float4(decay_of(w4.x), decay_of(w4.y), decay_of(w4.z), decay_of(w4.w));
-      *reinterpret_cast<float4*>(&tile[tl][2][4 * quad]) = k4;
-      *reinterpret_cast<float4*>(&tile[tl][3][4 * quad]) =
+      *reinterpret_cast<float4*>(&tile[tl][2][padk(4 * quad)]) = k4;
+      *reinterpret_cast<float4*>(&tile[tl][3][padk(4 * quad)]) =
           make_float4(r4.x * u4.x * k4.x, r4.y * u4.y * k4.y, r4.z * u4.z * k4.z, r4.w * u4.w * k4.w);
     }
-    for (int i = tid; i < nt * 4; i += N) {
-      const int tl = i >> 2, quad = i & 3;
-      *reinterpret_cast<float4*>(&vt[tl][4 * quad]) =
-          load4(v + base + (long long)(t0 + tl) * tstride + y * VS + 4 * quad);
+#pragma unroll
+    for (int m = 0; m < VPER; ++m) {
+      const int i = tid + m * N;
+      if (i < TL * 4) *reinterpret_cast<float4*>(&vt[i >> 2][4 * (i & 3)]) = vbuf[m];
     }
+  };
+  if (Tn > 0) fetch(0);
+  for (int t0 = 0; t0 < Tn; t0 += TL) {
+    const int nt = min(TL, Tn - t0);
+    stash();
     __syncthreads();
+    if (t0 + TL < Tn) fetch(t0 + TL);
     for (int tl = 0; tl < nt; ++tl) {
       const int t = t0 + tl;
       if (ckpt && (t % ckpt_every) == 0) {
@@ -108,10 +142,10 @@ wkv6_fwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __res
 #pragma unroll
         for (int j = 0; j < 16; ++j) p[j * N] = S[j];
       }
-      const float* tr = &tile[tl][0][16 * kq];
-      const float* td = &tile[tl][1][16 * kq];
-      const float* tk = &tile[tl][2][16 * kq];
-      const float* tq = &tile[tl][3][16 * kq];
+      const float* tr = &tile[tl][0][20 * kq];
+      const float* td = &tile[tl][1][20 * kq];
+      const float* tk = &tile[tl][2][20 * kq];
+      const float* tq = &tile[tl][3][20 * kq];
       const float vv = vt[tl][vl];
       float y0 = 0.f, y1 = 0.f, q0 = 0.f, q1 = 0.f;
 #pragma unroll
@@ -141,7 +175,7 @@ wkv6_fwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __res
 }
 
 template <int N> struct BwdSmem {
-  float tile[CK][6][N];           // r, d, exp(w), k, r*u, u*k
+  float tile[CK][6][NP<N>()];           // r, d, exp(w), k, r*u, u*k
   float ruk[CK];                  // sum_k r u k
   float vt[CK][VS];
   float dyt[CK][VS];
@@ -195,6 +229,62 @@ wkv6_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __res
   }
   float du_acc = 0.f;
 
+  // The inputs of chunk c - 1 (and, from checkpoints one chunk apart, its starting state) are requested into
+  // registers before chunk c is worked on, and written to shared memory when chunk c is done: see the forward
+  // kernel.
+  constexpr int PER = CK / 4;                      // (token, quad) pairs per thread per chunk
+  constexpr int VPER = (CK * 4 + N - 1) / N;       // float4 of v (and of dy) per thread per chunk
+  float4 rbuf[PER], kbuf[PER], wbuf[PER], vbuf[VPER], dybuf[VPER];
+  float Snext[16];
+  const int quad = tid % QUADS, rq = tid / QUADS;
+  auto fetch = [&](int c) {
+    const int t0 = c * CK, nt = min(CK, Tn - t0);
+#pragma unroll
+    for (int m = 0; m < PER; ++m) {
+      const int tl = rq + 4 * m;
+      const long long off = base + (long long)(t0 + tl) * tstride + 4 * quad;
+      const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
+      rbuf[m] = tl < nt ? load4(r + off) : z;
+      kbuf[m] = tl < nt ? load4(k + off) : z;
+      wbuf[m] = tl < nt ? load4(w + off) : z;
+    }
+#pragma unroll
+    for (int m = 0; m < VPER; ++m) {
+      const int i = tid + m * N;
+      const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
+      const long long off = base + (long long)(t0 + (i >> 2)) * tstride + y * VS + 4 * (i & 3);
+      vbuf[m] = i < nt * 4 ? load4(v + off) : z;
+      dybuf[m] = i < nt * 4 ? load4(d_y + off) : z;
+    }
+    if constexpr (!COARSE) {
+      const float* p = ckpt + unit * ckpt_unit + (((long long)c * N) + 16 * kq) * N + y * VS + vl;
+#pragma unroll
+      for (int j = 0; j < 16; ++j) Snext[j] = p[j * N];
+    }
+  };
+  auto stash = [&]() {
+#pragma unroll
+    for (int m = 0; m < PER; ++m) {
+      const int tl = rq + 4 * m;
+      const float4 r4 = rbuf[m], k4 = kbuf[m], w4 = wbuf[m];
+      *reinterpret_cast<float4*>(&sm.tile[tl][0][padk(4 * quad)]) = r4;
+      *reinterpret_cast<float4*>(&sm.tile[tl][1][padk(4 * quad)]) =
+          make_float4(decay_of(w4.x), decay_of(w4.y), decay_of(w4.z), decay_of(w4.w));
+      *reinterpret_cast<float4*>(&sm.tile[tl][2][padk(4 * quad)]) = make_float4(expf(w4.x), expf(w4.y), expf(w4.z), expf(w4.w));
+      *reinterpret_cast<float4*>(&sm.tile[tl][3][padk(4 * quad)]) = k4;
+      *reinterpret_cast<float4*>(&sm.tile[tl][4][padk(4 * quad)]) = make_float4(r4.x * u4.x, r4.y * u4.y, r4.z * u4.z, r4.w * u4.w);
+      *reinterpret_cast<float4*>(&sm.tile[tl][5][padk(4 * quad)]) = make_float4(u4.x * k4.x, u4.y * k4.y, u4.z * k4.z, u4.w * k4.w);
+    }
+#pragma unroll
+    for (int m = 0; m < VPER; ++m) {
+      const int i = tid + m * N;
+      if (i < CK * 4) {
+        *reinterpret_cast<float4*>(&sm.vt[i >> 2][4 * (i & 3)]) = vbuf[m];
+        *reinterpret_cast<float4*>(&sm.dyt[i >> 2][4 * (i & 3)]) = dybuf[m];
+      }
+    }
+  };
+  if (NC > 0) fetch(NC - 1);
   for (int c = NC - 1; c >= 0; --c) {
     const int t0 = c * CK, nt = min(CK, Tn - t0), pb = c & 1;
     if constexpr (COARSE) {
@@ -214,9 +304,9 @@ wkv6_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __res
             const int quad = i % QUADS, tl = i / QUADS;
             const long long off = base + (long long)(tg0 + tl) * tstride + 4 * quad;
             const float4 k4 = load4(k + off), w4 = load4(w + off);
-            *reinterpret_cast<float4*>(&sm.tile[tl][1][4 * quad]) =
+            *reinterpret_cast<float4*>(&sm.tile[tl][1][padk(4 * quad)]) =
                 make_float4(decay_of(w4.x), decay_of(w4.y), decay_of(w4.z), decay_of(w4.w));
-            *reinterpret_cast<float4*>(&sm.tile[tl][3][4 * quad]) = k4;
+            *reinterpret_cast<float4*>(&sm.tile[tl][3][padk(4 * quad)]) = k4;
           }
           for (int i = tid; i < ntg * 4; i += N) {
             const int tl = i >> 2, quad = i & 3;
@@ -227,8 +317,8 @@ wkv6_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __res
 #pragma unroll
           for (int j = 0; j < 16; ++j) sm.sub[g & 7][16 * kq + j][vl] = S0[j];
           for (int tl = 0; tl < ntg; ++tl) {
-            const float* td = &sm.tile[tl][1][16 * kq];
-            const float* tk = &sm.tile[tl][3][16 * kq];
+            const float* td = &sm.tile[tl][1][20 * kq];
+            const float* tk = &sm.tile[tl][3][20 * kq];
             const float vv = sm.vt[tl][vl];
 #pragma unroll
             for (int j = 0; j < 16; ++j) S0[j] = td[j] * S0[j] + tk[j] * vv;
@@ -237,44 +327,28 @@ wkv6_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __res
         }
       }
     }
-    for (int i = tid; i < nt * QUADS; i += N) {
-      const int quad = i % QUADS, tl = i / QUADS;
-      const long long off = base + (long long)(t0 + tl) * tstride + 4 * quad;
-      const float4 r4 = load4(r + off), k4 = load4(k + off), w4 = load4(w + off);
-      *reinterpret_cast<float4*>(&sm.tile[tl][0][4 * quad]) = r4;
-      *reinterpret_cast<float4*>(&sm.tile[tl][1][4 * quad]) =
-          make_float4(decay_of(w4.x), decay_of(w4.y), decay_of(w4.z), decay_of(w4.w));
-      *reinterpret_cast<float4*>(&sm.tile[tl][2][4 * quad]) = make_float4(expf(w4.x), expf(w4.y), expf(w4.z), expf(w4.w));
-      *reinterpret_cast<float4*>(&sm.tile[tl][3][4 * quad]) = k4;
-      *reinterpret_cast<float4*>(&sm.tile[tl][4][4 * quad]) = make_float4(r4.x * u4.x, r4.y * u4.y, r4.z * u4.z, r4.w * u4.w);
-      *reinterpret_cast<float4*>(&sm.tile[tl][5][4 * quad]) = make_float4(u4.x * k4.x, u4.y * k4.y, u4.z * k4.z, u4.w * k4.w);
-    }
-    for (int i = tid; i < nt * 4; i += N) {
-      const int tl = i >> 2, quad = i & 3;
-      const long long off = base + (long long)(t0 + tl) * tstride + y * VS + 4 * quad;
-      *reinterpret_cast<float4*>(&sm.vt[tl][4 * quad]) = load4(v + off);
-      *reinterpret_cast<float4*>(&sm.dyt[tl][4 * quad]) = load4(d_y + off);
-    }
+    // ---- the chunk's inputs, and the state at its start (value role) for the forward re-run
+    stash();
     float S[16];
     if constexpr (COARSE) {
 #pragma unroll
       for (int j = 0; j < 16; ++j) S[j] = sm.sub[c & 7][16 * kq + j][vl];
     } else {
-      const float* p = ckpt + unit * ckpt_unit + (((long long)c * N) + 16 * kq) * N + y * VS + vl;
 #pragma unroll
-      for (int j = 0; j < 16; ++j) S[j] = p[j * N];
+      for (int j = 0; j < 16; ++j) S[j] = Snext[j];
     }
     __syncthreads();
+    if (c > 0) fetch(c - 1);
     // sum_k r u k per token (threads 0..nt-1, one token each)
     if (tid < nt) {
       float s = 0.f;
-      for (int j = 0; j < N; ++j) s += sm.tile[tid][4][j] * sm.tile[tid][3][j];
+      for (int j = 0; j < N; ++j) s += sm.tile[tid][4][padk(j)] * sm.tile[tid][3][padk(j)];
       sm.ruk[tid] = s;
     }
     // re-run the chunk forward (value role), keeping the state before every token
     for (int tl = 0; tl < nt; ++tl) {
-      const float* td = &sm.tile[tl][1][16 * kq];
-      const float* tk = &sm.tile[tl][3][16 * kq];
+      const float* td = &sm.tile[tl][1][20 * kq];
+      const float* tk = &sm.tile[tl][3][20 * kq];
       const float vv = sm.vt[tl][vl];
 #pragma unroll
       for (int j = 0; j < 16; ++j) {
@@ -286,9 +360,9 @@ wkv6_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __res
 
     for (int tl = nt - 1; tl >= 0; --tl) {
       // value role: dv = dy * sum(ruk) + sum_k G[k][v] k[k]
-      const float* tr = &sm.tile[tl][0][16 * kq];
-      const float* td = &sm.tile[tl][1][16 * kq];
-      const float* tk = &sm.tile[tl][3][16 * kq];
+      const float* tr = &sm.tile[tl][0][20 * kq];
+      const float* td = &sm.tile[tl][1][20 * kq];
+      const float* tk = &sm.tile[tl][3][20 * kq];
       const float dyr = sm.dyt[tl][vl];
       float a0 = 0.f, a1 = 0.f;
 #pragma unroll
@@ -300,7 +374,7 @@ wkv6_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __res
       const float dvv = sum_kq<NKQ>(a0 + a1);
       if (kq == 0) sm.dvt[tl][vl] = dvv + dyr * sm.ruk[tl];
       // key role
-      const float rk = sm.tile[tl][0][kc], dk_ = sm.tile[tl][1][kc];
+      const float rk = sm.tile[tl][0][padk(kc)], dk_ = sm.tile[tl][1][padk(kc)];
       float p_dr = 0.f, p_dk = 0.f, p_dd = 0.f, p_dyv = 0.f;
 #pragma unroll
       for (int i = 0; i < VS; ++i) {
@@ -334,10 +408,10 @@ wkv6_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __res
         dyv += rd[tl];
       }
       const long long off = base + (long long)(t0 + tl) * tstride + kc;
-      dr[off] = from_f32<T>(acc[0] + sm.tile[tl][5][kc] * dyv);
-      dk[off] = from_f32<T>(acc[1] + sm.tile[tl][4][kc] * dyv);
-      dw[off] = from_f32<T>(acc[2] * sm.tile[tl][1][kc] * (-sm.tile[tl][2][kc]));
-      du_acc += sm.tile[tl][0][kc] * sm.tile[tl][3][kc] * dyv;
+      dr[off] = from_f32<T>(acc[0] + sm.tile[tl][5][padk(kc)] * dyv);
+      dk[off] = from_f32<T>(acc[1] + sm.tile[tl][4][padk(kc)] * dyv);
+      dw[off] = from_f32<T>(acc[2] * sm.tile[tl][1][padk(kc)] * (-sm.tile[tl][2][padk(kc)]));
+      du_acc += sm.tile[tl][0][padk(kc)] * sm.tile[tl][3][padk(kc)] * dyv;
     }
     __syncthreads();
   }
