@@ -264,6 +264,32 @@ int rwkvb200_wkv6_bwd(const void* r, const void* k, const void* v, const void* w
                       void* workspace, size_t workspace_bytes,
                       int B, int T, int H, int head_size, int dtype, int algo, void* stream);
 
+/* wkv6 on packed variable-length batches (head size 64, every dtype; the chunked tensor-core path with its
+ * recurrent fallback).  The n_seq sequences lie end to end in token tensors of shape [1, total_len, H*64];
+ * sequence i is tokens seq_start[i] .. seq_start[i] + seq_len[i] - 1 (device arrays of n_seq int32, every
+ * length >= 1, no overlap), max_len is the longest length.  Initial states as in the dense entry points with
+ * the sequence in the place of the batch row (s0 [n_state, H, 64, 64], state_map [n_seq] or NULL); sT and
+ * d_s0 are [n_seq, H, 64, 64].  keep / kept as RWKVB200_ALGO_KEEP in the dense entry points; the workspace
+ * is sized by rwkvb200_wkv6_varlen_workspace_bytes (the backward always needs the keep = 1 size).
+ * No counterpart in the reference: its wkv6 operator takes dense [B, T, C] batches only
+ * (rwkv_ops/rwkv6_kernel/ops_rwkv_kernel.py:10-21); the result equals running each sequence on its own. */
+size_t rwkvb200_wkv6_varlen_workspace_bytes(int n_seq, int max_len, int H, int head_size, int dtype, int keep);
+
+int rwkvb200_wkv6_fwd_varlen(const void* r, const void* k, const void* v, const void* w, const float* u,
+                             const int32_t* seq_start, const int32_t* seq_len, int n_seq, int max_len, int total_len,
+                             const float* s0, int n_state, const int32_t* state_map,
+                             void* y, float* sT, void* workspace, size_t workspace_bytes,
+                             int H, int head_size, int dtype, int keep, void* stream);
+
+int rwkvb200_wkv6_bwd_varlen(const void* r, const void* k, const void* v, const void* w, const float* u,
+                             const int32_t* seq_start, const int32_t* seq_len, int n_seq, int max_len, int total_len,
+                             const float* s0, int n_state, const int32_t* state_map,
+                             const void* d_y, const float* d_sT,
+                             void* dr, void* dk, void* dv, void* dw, float* du, float* d_s0,
+                             void* workspace, size_t workspace_bytes,
+                             int H, int head_size, int dtype, int kept, void* stream);
+
+
 /* ------------------------------------------------------------------------------------------
  * Diagnostics of the tensor-core path (no counterpart in the reference).
  * rwkvb200_device_status: every wait inside a tensor-core kernel (on an mbarrier that a TMA copy or

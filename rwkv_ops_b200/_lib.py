@@ -49,6 +49,10 @@ SIGNATURES = {
     "rwkvb200_wkv6_fwd": (c_int, [_P] * 5 + [_P, _I, _P, _P, _P, _P, _Z] + [_I] * 6 + [_P]),
     "rwkvb200_wkv6_bwd_workspace_bytes": (c_size_t, [_I] * 6),
     "rwkvb200_wkv6_bwd": (c_int, [_P] * 5 + [_P, _I, _P, _P, _P] + [_P] * 6 + [_P, _Z] + [_I] * 6 + [_P]),
+    "rwkvb200_wkv6_varlen_workspace_bytes": (c_size_t, [_I] * 6),
+    "rwkvb200_wkv6_fwd_varlen": (c_int, [_P] * 5 + [_P, _P, _I, _I, _I, _P, _I, _P, _P, _P, _P, _Z] + [_I] * 4 + [_P]),
+    "rwkvb200_wkv6_bwd_varlen": (c_int, [_P] * 5 + [_P, _P, _I, _I, _I, _P, _I, _P, _P, _P] + [_P] * 6 + [_P, _Z] +
+                                 [_I] * 4 + [_P]),
     "rwkvb200_device_status": (c_int, [_I]),
     "rwkvb200_profile_enable": (None, [_I]),
     "rwkvb200_profile_reset": (None, []),

@@ -370,4 +370,59 @@ int rwkvb200_wkv6_bwd(const void* r, const void* k, const void* v, const void* w
                          head_size);
 }
 
+size_t rwkvb200_wkv6_varlen_workspace_bytes(int n_seq, int max_len, int H, int head_size, int dtype, int keep) {
+  if (check_common(n_seq, max_len, H, head_size, dtype)) return 0;
+  return keep ? wkv6_chunked_bwd_workspace_bytes(n_seq, max_len, H) : wkv6_chunked_flags_bytes(n_seq, H);
+}
+
+int rwkvb200_wkv6_fwd_varlen(const void* r, const void* k, const void* v, const void* w, const float* u,
+                             const int32_t* seq_start, const int32_t* seq_len, int n_seq, int max_len, int total_len,
+                             const float* s0, int n_state, const int32_t* state_map,
+                             void* y, float* sT, void* workspace, size_t workspace_bytes,
+                             int H, int head_size, int dtype, int keep, void* stream) {
+  int e = check_common(n_seq, max_len, H, head_size, dtype);
+  if (e) return e;
+  if (total_len < max_len) return RWKVB200_E_SHAPE;
+  if (!r || !k || !v || !w || !u || !y || !seq_start || !seq_len) return RWKVB200_E_NULL;
+  if (n_state < 0) return RWKVB200_E_SHAPE;
+  if (n_state > 0 && !s0) return RWKVB200_E_NULL;
+  if (n_state > 1 && !state_map && n_state != n_seq) return RWKVB200_E_STATE_MAP;
+  const void* ps[] = {r, k, v, w, u, s0, y, sT, workspace};
+  for (const void* p : ps) if (p && !aligned16(p)) return RWKVB200_E_ALIGN;
+  if (!workspace || workspace_bytes < rwkvb200_wkv6_varlen_workspace_bytes(n_seq, max_len, H, head_size, dtype, keep))
+    return RWKVB200_E_WORKSPACE;
+  float* states = nullptr;
+  int* flags = reinterpret_cast<int*>(workspace);
+  if (keep) {
+    states = reinterpret_cast<float*>(workspace);
+    flags = wkv6_chunked_workspace_flags(workspace, n_seq, max_len, H);
+  }
+  return launch_wkv6_chunked_fwd(r, k, v, w, u, n_state ? s0 : nullptr, n_state, state_map, y, sT, states, flags,
+                                 n_seq, max_len, H, dtype, (cudaStream_t)stream, seq_start, seq_len, total_len);
+}
+
+int rwkvb200_wkv6_bwd_varlen(const void* r, const void* k, const void* v, const void* w, const float* u,
+                             const int32_t* seq_start, const int32_t* seq_len, int n_seq, int max_len, int total_len,
+                             const float* s0, int n_state, const int32_t* state_map,
+                             const void* d_y, const float* d_sT,
+                             void* dr, void* dk, void* dv, void* dw, float* du, float* d_s0,
+                             void* workspace, size_t workspace_bytes,
+                             int H, int head_size, int dtype, int kept, void* stream) {
+  int e = check_common(n_seq, max_len, H, head_size, dtype);
+  if (e) return e;
+  if (total_len < max_len) return RWKVB200_E_SHAPE;
+  if (!r || !k || !v || !w || !u || !d_y || !dr || !dk || !dv || !dw || !du || !seq_start || !seq_len)
+    return RWKVB200_E_NULL;
+  if (n_state < 0) return RWKVB200_E_SHAPE;
+  if (n_state > 0 && !s0) return RWKVB200_E_NULL;
+  if (n_state > 1 && !state_map && n_state != n_seq) return RWKVB200_E_STATE_MAP;
+  const void* ps[] = {r, k, v, w, u, s0, d_y, d_sT, dr, dk, dv, dw, du, d_s0, workspace};
+  for (const void* p : ps) if (p && !aligned16(p)) return RWKVB200_E_ALIGN;
+  if (!workspace || workspace_bytes < rwkvb200_wkv6_varlen_workspace_bytes(n_seq, max_len, H, head_size, dtype, 1))
+    return RWKVB200_E_WORKSPACE;
+  return launch_wkv6_chunked_bwd(r, k, v, w, u, n_state ? s0 : nullptr, n_state, state_map, d_y, d_sT,
+                                 dr, dk, dv, dw, du, d_s0, workspace, n_seq, max_len, H, dtype, kept != 0,
+                                 (cudaStream_t)stream, seq_start, seq_len, total_len);
+}
+
 }  // extern "C"

@@ -60,7 +60,7 @@ wkv6_fwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __res
                 const T* __restrict__ w, const float* __restrict__ u,
                 const float* __restrict__ s0, int n_state, const int32_t* __restrict__ smap,
                 T* __restrict__ yout, float* __restrict__ sT, float* __restrict__ ckpt, int ckpt_every,
-                int Tn, int H, UnitSel sel) {
+                int Tn_dense, int H, UnitSel sel) {
   constexpr int NKQ = N / VS, QUADS = N / 4;
   __shared__ __align__(16) float tile[TL][4][NP<N>()];   // r, d, k, r*u*k
   __shared__ __align__(16) float vt[TL][VS];
@@ -70,10 +70,13 @@ wkv6_fwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __res
   if (sel.flags && sel.flags[unit] == 0) return;      // only the selected units run
   const int bi = unit / H, hi = unit % H;
   const int vl = tid / NKQ, kq = tid % NKQ;
-  const long long base = ((long long)bi * Tn * H + hi) * N;   // + t*H*N
+  // a packed batch keeps its sequences end to end in batch row 0
+  const int Tn = sel.seq_len ? sel.seq_len[bi] : Tn_dense;
+  const long long base = sel.seq_start ? ((long long)sel.seq_start[bi] * H + hi) * N
+                                       : ((long long)bi * Tn_dense * H + hi) * N;   // + t*H*N
   const long long tstride = (long long)H * N;
   const long long ckpt_unit = sel.ckpt_unit_stride ? sel.ckpt_unit_stride
-                                                   : (long long)((Tn + ckpt_every - 1) / ckpt_every) * N * N;
+                                                   : (long long)((Tn_dense + ckpt_every - 1) / ckpt_every) * N * N;
   const float4 u4 = *reinterpret_cast<const float4*>(u + hi * N + 4 * (tid % QUADS));
 
   float S[16];
@@ -197,7 +200,7 @@ wkv6_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __res
                 const T* __restrict__ w, const float* __restrict__ u,
                 const T* __restrict__ d_y, const float* __restrict__ d_sT, const float* __restrict__ ckpt,
                 T* __restrict__ dr, T* __restrict__ dk, T* __restrict__ dv, T* __restrict__ dw,
-                float* __restrict__ du_partial, float* __restrict__ d_s0, int Tn, int H, UnitSel sel) {
+                float* __restrict__ du_partial, float* __restrict__ d_s0, int Tn_dense, int H, UnitSel sel) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   constexpr int NKQ = N / VS, NQ = N / VS, QUADS = N / 4;
   typedef typename std::conditional<COARSE, BwdSmemCoarse<N>, BwdSmem<N>>::type Smem;
@@ -209,10 +212,13 @@ wkv6_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __res
   const int bi = unit / H, hi = unit % H;
   const int vl = tid / NKQ, kq = tid % NKQ;   // value role
   const int kc = tid;                      // key role
-  const long long base = ((long long)bi * Tn * H + hi) * N;
+  const int Tn = sel.seq_len ? sel.seq_len[bi] : Tn_dense;
+  const long long base = sel.seq_start ? ((long long)sel.seq_start[bi] * H + hi) * N
+                                       : ((long long)bi * Tn_dense * H + hi) * N;
   const long long tstride = (long long)H * N;
   const int NC = (Tn + CK - 1) / CK;
-  const long long ckpt_unit = sel.ckpt_unit_stride ? sel.ckpt_unit_stride : (long long)NC * N * N;
+  const long long ckpt_unit = sel.ckpt_unit_stride ? sel.ckpt_unit_stride
+                                                   : (long long)((Tn_dense + CK - 1) / CK) * N * N;
   const float4 u4 = *reinterpret_cast<const float4*>(u + hi * N + 4 * (tid % QUADS));
 
   float Gv[16], Gk[VS];   // value-role copy G[16kq+j][vl], key-role copy G[kc][i]

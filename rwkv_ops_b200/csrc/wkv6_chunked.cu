@@ -124,6 +124,16 @@ __device__ __forceinline__ long long state_row(const int32_t* smap, int n_state,
   return m < 0 ? 0 : (m >= n_state ? n_state - 1 : m);
 }
 
+// Where the tokens of a unit's sequence lie.  Dense batches: row bi of [B][T][H][64], Tn tokens.  Packed batches
+// (PACKED): the sequences lie end to end in one row [1][total][H][64]; sequence bi is tokens start[bi] ..
+// start[bi] + len[bi] - 1, and the rows of a chunk past the end of the sequence belong to the next one: they are
+// read as zeros and never stored.
+struct Seqs {
+  const int32_t* start;
+  const int32_t* len;
+  int nts;      // chunk-boundary state slots per unit in `states` (chunks of the longest sequence + 1)
+};
+
 // ---------------------------------------------------------------------------------------------
 // forward
 // ---------------------------------------------------------------------------------------------
@@ -145,14 +155,15 @@ struct FwdSmem {
 // the last MMA of the current one has read those tiles; a thread reads its elements, all threads meet at a
 // barrier, and then the split tiles are written over the raw rows.
 // S0 of every chunk (and the final state) goes to `states` [B*H][NT+1][64][64] when it is not NULL.
-template <typename T>
+template <typename T, bool PACKED>
 __global__ void __launch_bounds__(256, 2)
 wkv6c_fwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __restrict__ v, const T* __restrict__ w,
                  const float* __restrict__ u, const float* __restrict__ s0, int n_state,
                  const int32_t* __restrict__ smap, T* __restrict__ y, float* __restrict__ sT,
                  float* __restrict__ states, int* __restrict__ flags, const __grid_constant__ CUtensorMap tmap_r,
                  const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
-                 const __grid_constant__ CUtensorMap tmap_w, int Tn, int H, int* status, long long* dbg) {
+                 const __grid_constant__ CUtensorMap tmap_w, int Tn_dense, int H, Seqs seqs, int* status,
+                 long long* dbg) {
 #ifdef RWKVB200_DEVTOOLS
 #define W6C_STAMP(n) do { if (dbg && tid == 0 && blockIdx.x == gridDim.x / 2 && c == 2) dbg[n] = clock64(); } while (0)
 #else
@@ -164,8 +175,12 @@ wkv6c_fwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
   const int wq = warp & 3, hsel = warp >> 2;
   const int unit = blockIdx.x, bi = unit / H, hi = unit % H;
   const long long tstride = (long long)H * HS;
-  const long long base = ((long long)bi * Tn * H + hi) * HS;
+  const int Tn = PACKED ? seqs.len[bi] : Tn_dense;
+  const int tok0 = PACKED ? seqs.start[bi] : 0;       // first token row of the sequence in its batch row
+  const int brow = PACKED ? 0 : bi;
+  const long long base = (((long long)brow * Tn_dense + tok0) * H + hi) * HS;   // Tn_dense: rows per batch row
   const int NT = (Tn + L - 1) / L;
+  const size_t nts = PACKED ? (size_t)seqs.nts : (size_t)(NT + 1);
   const int srow = 16 * wq + (lane & 15);     // state row k (upper lane halves) / token row (lower lane halves)
   const bool tok_lane = lane < 16;            // lower lane halves hold token rows, upper halves state rows
 
@@ -213,10 +228,10 @@ wkv6c_fwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
   const T* raw_w = reinterpret_cast<const T*>(sm.at[0]);
   auto load_in = [&](int c) {      // tid 0; rows past the end of the sequence arrive as zeros
     mbar_expect_tx(&sm.bar_in, 4 * 64 * 64 * (uint32_t)sizeof(T));
-    tma_load_4d(sm.at[0], &tmap_w, &sm.bar_in, 0, c * L, hi, bi);
-    tma_load_4d(sm.vt[0], &tmap_v, &sm.bar_in, 0, c * L, hi, bi);
-    tma_load_4d(sm.rt[0], &tmap_r, &sm.bar_in, 0, c * L, hi, bi);
-    tma_load_4d(sm.kt[0], &tmap_k, &sm.bar_in, 0, c * L, hi, bi);
+    tma_load_4d(sm.at[0], &tmap_w, &sm.bar_in, 0, tok0 + c * L, hi, brow);
+    tma_load_4d(sm.vt[0], &tmap_v, &sm.bar_in, 0, tok0 + c * L, hi, brow);
+    tma_load_4d(sm.rt[0], &tmap_r, &sm.bar_in, 0, tok0 + c * L, hi, brow);
+    tma_load_4d(sm.kt[0], &tmap_k, &sm.bar_in, 0, tok0 + c * L, hi, brow);
   };
   if (tid == 0 && NT > 0) load_in(0);
 
@@ -233,6 +248,7 @@ wkv6c_fwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
       const int e = tid + 256 * n, row = e >> 4;
       gw[n] = load4_shared(raw_w + row * 64 + 4 * c4);
       vv4[n] = load4_shared(raw_v + row * 64 + 4 * c4);
+      if (PACKED && t0 + row >= Tn) vv4[n] = make_float4(0.f, 0.f, 0.f, 0.f);      // the next sequence's row
     }
     __syncthreads();      // every raw v element is in registers: the split v tiles may overwrite the rows
     // ---- pass W: g and its prefix sums; pass V
@@ -278,7 +294,7 @@ wkv6c_fwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
     // ---- S~0 = e^{gref} S0 stays in registers (fp32); hi/lo bf16 tiles for the r~ S~0 product
     if (!tok_lane) {
       if (states) {
-        float* dst = states + (((size_t)unit * (NT + 1) + c) * HS + srow) * HS + 32 * hsel;
+        float* dst = states + (((size_t)unit * nts + c) * HS + srow) * HS + 32 * hsel;
 #pragma unroll
         for (int j = 0; j < 32; j += 4)
           *reinterpret_cast<float4*>(dst + j) = make_float4(sreg[j], sreg[j + 1], sreg[j + 2], sreg[j + 3]);
@@ -295,6 +311,7 @@ wkv6c_fwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
       const int row = (tid + 256 * n) >> 4;
       rr4[n] = load4_shared(raw_r + row * 64 + 4 * c4);
       kk4[n] = load4_shared(raw_k + row * 64 + 4 * c4);
+      if (PACKED && t0 + row >= Tn) { rr4[n] = make_float4(0.f, 0.f, 0.f, 0.f); kk4[n] = rr4[n]; }
     }
     __syncthreads();      // every raw r, k element is in registers
 #pragma unroll
@@ -315,10 +332,10 @@ wkv6c_fwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
     }
     // ask for the next chunk's rows to be brought into L2 while this chunk is in its MMA phases
     if (tid == 0 && t0 + L < Tn) {
-      tma_prefetch_4d(&tmap_w, 0, t0 + L, hi, bi);
-      tma_prefetch_4d(&tmap_v, 0, t0 + L, hi, bi);
-      tma_prefetch_4d(&tmap_r, 0, t0 + L, hi, bi);
-      tma_prefetch_4d(&tmap_k, 0, t0 + L, hi, bi);
+      tma_prefetch_4d(&tmap_w, 0, tok0 + t0 + L, hi, brow);
+      tma_prefetch_4d(&tmap_v, 0, tok0 + t0 + L, hi, brow);
+      tma_prefetch_4d(&tmap_r, 0, tok0 + t0 + L, hi, brow);
+      tma_prefetch_4d(&tmap_k, 0, tok0 + t0 + L, hi, brow);
     }
     fence_async_smem();
     tc_fence_before();
@@ -400,7 +417,7 @@ wkv6c_fwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
         *reinterpret_cast<float4*>(dst + j) = make_float4(sreg[j], sreg[j + 1], sreg[j + 2], sreg[j + 3]);
     }
     if (states) {
-      float* dst = states + (((size_t)unit * (NT + 1) + NT) * HS + srow) * HS + 32 * hsel;
+      float* dst = states + (((size_t)unit * nts + NT) * HS + srow) * HS + 32 * hsel;
 #pragma unroll
       for (int j = 0; j < 32; j += 4)
         *reinterpret_cast<float4*>(dst + j) = make_float4(sreg[j], sreg[j + 1], sreg[j + 2], sreg[j + 3]);
@@ -443,7 +460,7 @@ struct BwdSmem {
 };
 static_assert(sizeof(BwdSmem) + 1024 <= 227 * 1024, "backward shared memory");
 
-template <typename T>
+template <typename T, bool PACKED>
 __global__ void __launch_bounds__(256)
 wkv6c_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __restrict__ v, const T* __restrict__ w,
                  const float* __restrict__ u, const T* __restrict__ d_y, const float* __restrict__ d_sT,
@@ -451,7 +468,8 @@ wkv6c_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
                  T* __restrict__ dw, float* __restrict__ du_partial, float* __restrict__ d_s0,
                  const __grid_constant__ CUtensorMap tmap_r, const __grid_constant__ CUtensorMap tmap_k,
                  const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_w,
-                 const __grid_constant__ CUtensorMap tmap_dy, int Tn, int H, int* status, long long* dbg) {
+                 const __grid_constant__ CUtensorMap tmap_dy, int Tn_dense, int H, Seqs seqs, int* status,
+                 long long* dbg) {
 #ifdef RWKVB200_DEVTOOLS
 #define W6C_STAMP(n) do { if (dbg && tid == 0 && blockIdx.x == gridDim.x / 2 && c == NT - 2) dbg[n] = clock64(); } while (0)
 #else
@@ -463,8 +481,12 @@ wkv6c_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
   const int wq = warp & 3, hsel = warp >> 2;
   const int unit = blockIdx.x, bi = unit / H, hi = unit % H;
   const long long tstride = (long long)H * HS;
-  const long long base = ((long long)bi * Tn * H + hi) * HS;
+  const int Tn = PACKED ? seqs.len[bi] : Tn_dense;
+  const int tok0 = PACKED ? seqs.start[bi] : 0;
+  const int brow = PACKED ? 0 : bi;
+  const long long base = (((long long)brow * Tn_dense + tok0) * H + hi) * HS;
   const int NT = (Tn + L - 1) / L;
+  const size_t nts = PACKED ? (size_t)seqs.nts : (size_t)(NT + 1);
   const int srow = 16 * wq + (lane & 15);
   const bool lower = lane < 16;
   const int c4 = tid & 15;
@@ -513,17 +535,17 @@ wkv6c_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
   const T* raw_k = reinterpret_cast<const T*>(sm.kt[0]);
   auto load_in_a = [&](int c) {      // tid 0; rows past the end of the sequence arrive as zeros
     mbar_expect_tx(&sm.bar_in_a, 2 * RAW_BYTES);
-    tma_load_4d(sm.raw_w, &tmap_w, &sm.bar_in_a, 0, c * L, hi, bi);
-    tma_load_4d(sm.raw_dy, &tmap_dy, &sm.bar_in_a, 0, c * L, hi, bi);
+    tma_load_4d(sm.raw_w, &tmap_w, &sm.bar_in_a, 0, tok0 + c * L, hi, brow);
+    tma_load_4d(sm.raw_dy, &tmap_dy, &sm.bar_in_a, 0, tok0 + c * L, hi, brow);
   };
   auto load_in_b = [&](int c) {
     mbar_expect_tx(&sm.bar_in_b, 2 * RAW_BYTES);
-    tma_load_4d(sm.rt[0], &tmap_r, &sm.bar_in_b, 0, c * L, hi, bi);
-    tma_load_4d(sm.kt[0], &tmap_k, &sm.bar_in_b, 0, c * L, hi, bi);
+    tma_load_4d(sm.rt[0], &tmap_r, &sm.bar_in_b, 0, tok0 + c * L, hi, brow);
+    tma_load_4d(sm.kt[0], &tmap_k, &sm.bar_in_b, 0, tok0 + c * L, hi, brow);
   };
   auto load_in_c = [&](int c) {
     mbar_expect_tx(&sm.bar_in_c, RAW_BYTES);
-    tma_load_4d(sm.red_e, &tmap_v, &sm.bar_in_c, 0, c * L, hi, bi);
+    tma_load_4d(sm.red_e, &tmap_v, &sm.bar_in_c, 0, tok0 + c * L, hi, brow);
   };
   if (tid == 0 && NT > 0) { load_in_a(NT - 1); load_in_c(NT - 1); load_in_b(NT - 1); }
 
@@ -547,7 +569,9 @@ wkv6c_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
                           -LOG2E * ex2(LOG2E * w4.w));
         gw[n] = f;
         *reinterpret_cast<float4*>(&sm.gg[row * NROW + 4 * c4]) = f;
-        store_split4(sm.dyt[0], sm.dyt[1], row, 4 * c4, load4_shared(raw_dy + row * 64 + 4 * c4));
+        float4 y4 = load4_shared(raw_dy + row * 64 + 4 * c4);
+        if (PACKED && tok >= Tn) y4 = make_float4(0.f, 0.f, 0.f, 0.f);      // the next sequence's row
+        store_split4(sm.dyt[0], sm.dyt[1], row, 4 * c4, y4);
       }
     }
     __syncthreads();
@@ -581,7 +605,10 @@ wkv6c_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
       rr4[n] = load4_shared(raw_r + row * 64 + 4 * c4);
       kk4[n] = load4_shared(raw_k + row * 64 + 4 * c4);
       // pass V: split tiles and dd_i = dy_i . v_i
-      const float4 v4 = load4_shared(raw_v + row * 64 + 4 * c4), y4 = load4_shared(raw_dy + row * 64 + 4 * c4);
+      float4 v4 = load4_shared(raw_v + row * 64 + 4 * c4), y4 = load4_shared(raw_dy + row * 64 + 4 * c4);
+      if (PACKED && t0 + row >= Tn) {
+        v4 = make_float4(0.f, 0.f, 0.f, 0.f); y4 = v4; rr4[n] = v4; kk4[n] = v4;
+      }
       store_split4(sm.vt[0], sm.vt[1], row, 4 * c4, v4);
       float dd = v4.x * y4.x + v4.y * y4.y + v4.z * y4.z + v4.w * y4.w;
 #pragma unroll
@@ -610,18 +637,18 @@ wkv6c_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
     // after the first epilogue: MMA batch 1 and that epilogue cover its latency
     float4 srow4[8];
     {
-      const float* Srow = states + (((size_t)unit * (NT + 1) + c + (lower ? 0 : 1)) * HS + srow) * HS + 32 * hsel;
+      const float* Srow = states + (((size_t)unit * nts + c + (lower ? 0 : 1)) * HS + srow) * HS + 32 * hsel;
 #pragma unroll
       for (int j = 0; j < 8; ++j) srow4[j] = *reinterpret_cast<const float4*>(Srow + 4 * j);
     }
     if (tid == 0 && c > 0) {   // bring the previous chunk's rows into L2 while this chunk is in its MMA phases
-      tma_prefetch_4d(&tmap_w, 0, t0 - L, hi, bi);
-      tma_prefetch_4d(&tmap_dy, 0, t0 - L, hi, bi);
-      tma_prefetch_4d(&tmap_v, 0, t0 - L, hi, bi);
-      tma_prefetch_4d(&tmap_r, 0, t0 - L, hi, bi);
-      tma_prefetch_4d(&tmap_k, 0, t0 - L, hi, bi);
+      tma_prefetch_4d(&tmap_w, 0, tok0 + t0 - L, hi, brow);
+      tma_prefetch_4d(&tmap_dy, 0, tok0 + t0 - L, hi, brow);
+      tma_prefetch_4d(&tmap_v, 0, tok0 + t0 - L, hi, brow);
+      tma_prefetch_4d(&tmap_r, 0, tok0 + t0 - L, hi, brow);
+      tma_prefetch_4d(&tmap_k, 0, tok0 + t0 - L, hi, brow);
       // and the chunk-boundary state the previous chunk starts from
-      bulk_prefetch_l2(states + ((size_t)unit * (NT + 1) + c - 1) * HS * HS, HS * HS * (uint32_t)sizeof(float));
+      bulk_prefetch_l2(states + ((size_t)unit * nts + c - 1) * HS * HS, HS * HS * (uint32_t)sizeof(float));
     }
     fence_async_smem();
     tc_fence_before();
@@ -810,33 +837,39 @@ wkv6c_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
 
 int launch_wkv6_chunked_fwd(const void* r, const void* k, const void* v, const void* w, const float* u,
                             const float* s0, int n_state, const int32_t* smap, void* y, float* sT,
-                            float* states, int* flags, int B, int Tn, int H, int dtype, cudaStream_t st) {
+                            float* states, int* flags, int B, int Tn, int H, int dtype, cudaStream_t st,
+                            const int32_t* seq_start, const int32_t* seq_len, int T_total) {
   using namespace w6c;
+  // a packed batch: B sequences (the longest of Tn tokens) end to end in one row of T_total tokens
+  const bool packed = seq_start != nullptr;
+  const int mapB = packed ? 1 : B, mapT = packed ? T_total : Tn;
+  const Seqs seqs{seq_start, seq_len, (Tn + L - 1) / L + 1};
   if (cuda_ok(cudaMemsetAsync(flags, 0, (size_t)B * H * sizeof(int), st))) return RWKVB200_E_CUDA;
   int* status = device_status_ptr();
   if (!status) { last_cuda_error_slot() = 99999; return RWKVB200_E_CUDA; }
   const int smem = (int)sizeof(FwdSmem) + 1024;
   const int esz = dtype == RWKVB200_F32 ? 4 : 2;
   CUtensorMap tm_r, tm_k, tm_v, tm_w;
-  int e = make_row_tensor_map(&tm_r, r, B, Tn, H, esz);
-  if (!e) e = make_row_tensor_map(&tm_k, k, B, Tn, H, esz);
-  if (!e) e = make_row_tensor_map(&tm_v, v, B, Tn, H, esz);
-  if (!e) e = make_row_tensor_map(&tm_w, w, B, Tn, H, esz);
+  int e = make_row_tensor_map(&tm_r, r, mapB, mapT, H, esz);
+  if (!e) e = make_row_tensor_map(&tm_k, k, mapB, mapT, H, esz);
+  if (!e) e = make_row_tensor_map(&tm_v, v, mapB, mapT, H, esz);
+  if (!e) e = make_row_tensor_map(&tm_w, w, mapB, mapT, H, esz);
   if (e) return e;
+#define W6C_DISPATCH_PACKED(...) do { if (packed) { constexpr bool P = true; __VA_ARGS__; } else { constexpr bool P = false; __VA_ARGS__; } } while (0)
   {
     ProfScope prof("wkv6c_fwd_kernel", st);
-    RWKVB200_DISPATCH_DTYPE(dtype,
-      if (cuda_ok(cudaFuncSetAttribute(wkv6c_fwd_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)))
+    RWKVB200_DISPATCH_DTYPE(dtype, W6C_DISPATCH_PACKED(
+      if (cuda_ok(cudaFuncSetAttribute(wkv6c_fwd_kernel<T, P>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)))
         return RWKVB200_E_CUDA;
-      wkv6c_fwd_kernel<T><<<B * H, 256, smem, st>>>((const T*)r, (const T*)k, (const T*)v, (const T*)w, u, s0, n_state,
-                                                     smap, (T*)y, sT, states, flags, tm_r, tm_k, tm_v, tm_w, Tn, H,
-                                                     status, debug_stamp_buffer()));
+      wkv6c_fwd_kernel<T, P><<<B * H, 256, smem, st>>>((const T*)r, (const T*)k, (const T*)v, (const T*)w, u, s0,
+                                                        n_state, smap, (T*)y, sT, states, flags, tm_r, tm_k, tm_v, tm_w,
+                                                        mapT, H, seqs, status, debug_stamp_buffer())));
   }
   e = check_launch();
   if (e) return e;
   // the marked units again, exactly: outputs, final state and (for the backward) the chunk-boundary states
-  const long long unit_floats = (long long)((Tn + L - 1) / L + 1) * HS * HS;
-  const UnitSel sel{flags, nullptr, nullptr, states ? unit_floats : 0};
+  const long long unit_floats = (long long)seqs.nts * HS * HS;
+  const UnitSel sel{flags, seq_start, seq_len, states ? unit_floats : 0};
   return launch_wkv6_fwd(r, k, v, w, u, s0, n_state, smap, y, sT, states, B, Tn, H, dtype, st, &sel, L);
 }
 
@@ -879,15 +912,19 @@ int* wkv6_chunked_workspace_flags(void* workspace, int B, int Tn, int H) { retur
 int launch_wkv6_chunked_bwd(const void* r, const void* k, const void* v, const void* w, const float* u,
                             const float* s0, int n_state, const int32_t* smap, const void* d_y, const float* d_sT,
                             void* dr, void* dk, void* dv, void* dw, float* du, float* d_s0, void* workspace,
-                            int B, int Tn, int H, int dtype, bool kept, cudaStream_t st) {
+                            int B, int Tn, int H, int dtype, bool kept, cudaStream_t st,
+                            const int32_t* seq_start, const int32_t* seq_len, int T_total) {
   using namespace w6c;
+  const bool packed = seq_start != nullptr;
+  const int mapB = packed ? 1 : B, mapT = packed ? T_total : Tn;
+  const Seqs seqs{seq_start, seq_len, (Tn + L - 1) / L + 1};
   const W6Workspace ws = w6_carve(workspace, B, Tn, H);
   float* states = ws.states;
   float* du_partial = ws.du_partial;
   int e = RWKVB200_OK;
   if (!kept) {   // the workspace does not hold the chunk-boundary states yet: run the forward for them
     e = launch_wkv6_chunked_fwd(r, k, v, w, u, s0, n_state, smap, nullptr, nullptr, states, ws.flags, B, Tn, H, dtype,
-                                st);
+                                st, seq_start, seq_len, T_total);
     if (e) return e;
   }
   int* status = device_status_ptr();
@@ -896,27 +933,27 @@ int launch_wkv6_chunked_bwd(const void* r, const void* k, const void* v, const v
   {
     const int esz = dtype == RWKVB200_F32 ? 4 : 2;
     CUtensorMap tm_r, tm_k, tm_v, tm_w, tm_dy;
-    e = make_row_tensor_map(&tm_r, r, B, Tn, H, esz);
-    if (!e) e = make_row_tensor_map(&tm_k, k, B, Tn, H, esz);
-    if (!e) e = make_row_tensor_map(&tm_v, v, B, Tn, H, esz);
-    if (!e) e = make_row_tensor_map(&tm_w, w, B, Tn, H, esz);
-    if (!e) e = make_row_tensor_map(&tm_dy, d_y, B, Tn, H, esz);
+    e = make_row_tensor_map(&tm_r, r, mapB, mapT, H, esz);
+    if (!e) e = make_row_tensor_map(&tm_k, k, mapB, mapT, H, esz);
+    if (!e) e = make_row_tensor_map(&tm_v, v, mapB, mapT, H, esz);
+    if (!e) e = make_row_tensor_map(&tm_w, w, mapB, mapT, H, esz);
+    if (!e) e = make_row_tensor_map(&tm_dy, d_y, mapB, mapT, H, esz);
     if (e) return e;
     ProfScope prof("wkv6c_bwd_kernel", st);
-    RWKVB200_DISPATCH_DTYPE(dtype,
-      if (cuda_ok(cudaFuncSetAttribute(wkv6c_bwd_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)))
+    RWKVB200_DISPATCH_DTYPE(dtype, W6C_DISPATCH_PACKED(
+      if (cuda_ok(cudaFuncSetAttribute(wkv6c_bwd_kernel<T, P>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)))
         return RWKVB200_E_CUDA;
-      wkv6c_bwd_kernel<T><<<B * H, 256, smem, st>>>((const T*)r, (const T*)k, (const T*)v, (const T*)w, u,
-                                                     (const T*)d_y, d_sT, states, (T*)dr, (T*)dk, (T*)dv, (T*)dw,
-                                                     du_partial, d_s0, tm_r, tm_k, tm_v, tm_w, tm_dy, Tn, H, status,
-                                                     debug_stamp_buffer()));
+      wkv6c_bwd_kernel<T, P><<<B * H, 256, smem, st>>>((const T*)r, (const T*)k, (const T*)v, (const T*)w, u,
+                                                        (const T*)d_y, d_sT, states, (T*)dr, (T*)dk, (T*)dv, (T*)dw,
+                                                        du_partial, d_s0, tm_r, tm_k, tm_v, tm_w, tm_dy, mapT, H, seqs,
+                                                        status, debug_stamp_buffer())));
   }
   e = check_launch();
   if (e) return e;
   // the units the forward marked: gradients from the float32 recurrence, which restarts from the (exact)
   // chunk-boundary states the fallback forward left in the workspace
   {
-    const UnitSel sel{ws.flags, nullptr, nullptr, (long long)((Tn + L - 1) / L + 1) * HS * HS};
+    const UnitSel sel{ws.flags, seq_start, seq_len, (long long)seqs.nts * HS * HS};
     e = launch_wkv6_bwd_coarse(r, k, v, w, u, d_y, d_sT, states, dr, dk, dv, dw, ws.du_partial_rec, d_s0, B, Tn, H,
                                dtype, st, &sel);
     if (e) return e;

@@ -188,3 +188,182 @@ def generalized_delta_rule_varlen(r, w, k, v, a, b, cu_seqlens, initial_state=No
             any(x.requires_grad for x in args) or (h0 is not None and h0.requires_grad))
         o, ht, _ = _fwd_varlen(*args, start, lens, max_len, h0, needs_grad)
     return (o, ht) if output_final_state else o
+
+
+# ---------------------------------------------------------------------------------------------------------
+# RWKV6 wkv on packed batches
+# ---------------------------------------------------------------------------------------------------------
+@torch.library.custom_op("rwkv_ops_b200::wkv6_fwd_varlen", mutates_args=())
+def _wkv6_fwd_varlen(r: torch.Tensor, k: torch.Tensor, v: torch.Tensor, w: torch.Tensor, u: torch.Tensor,
+                     seq_start: torch.Tensor, seq_len: torch.Tensor, max_len: int, s0: Optional[torch.Tensor],
+                     state_map: Optional[torch.Tensor], keep: bool
+                     ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    lib = _lib.load()
+    dev = _lib.require_cuda(r, k, v, w, u, seq_start, seq_len, s0, state_map)
+    T = r.shape[1]
+    H, N = u.shape
+    n_seq = seq_start.numel()
+    code = _lib.dtype_code(r.dtype)
+    y = torch.empty_like(r)
+    sT = torch.empty(n_seq, H, N, N, dtype=torch.float32, device=dev)
+    n_state = 0 if s0 is None else s0.shape[0]
+    with torch.cuda.device(dev):
+        nws = lib.rwkvb200_wkv6_varlen_workspace_bytes(n_seq, max_len, H, N, code, int(keep))
+        ws = torch.empty(nws, dtype=torch.uint8, device=dev)
+        rc = lib.rwkvb200_wkv6_fwd_varlen(r.data_ptr(), k.data_ptr(), v.data_ptr(), w.data_ptr(), u.data_ptr(),
+                                          seq_start.data_ptr(), seq_len.data_ptr(), n_seq, max_len, T,
+                                          _lib.ptr(s0), n_state, _lib.ptr(state_map), y.data_ptr(), sT.data_ptr(),
+                                          ws.data_ptr(), nws, H, N, code, int(keep), _lib.stream_ptr(dev))
+        _lib.check(rc, "wkv6_fwd_varlen")
+        _lib.check_status("wkv6_fwd_varlen")
+    return y, sT, (ws if keep else ws.new_empty((1,)))
+
+
+@_wkv6_fwd_varlen.register_fake
+def _(r, k, v, w, u, seq_start, seq_len, max_len, s0, state_map, keep):
+    H, N = u.shape
+    n_seq = seq_start.numel()
+    return (torch.empty_like(r), r.new_empty((n_seq, H, N, N), dtype=torch.float32),
+            r.new_empty((_lib.wkv6_kept_bytes(n_seq, max_len, H) if keep else 1,), dtype=torch.uint8))
+
+
+# `kept` also serves as scratch for the backward kernel; the states the forward left in it are not changed.
+@torch.library.custom_op("rwkv_ops_b200::wkv6_bwd_varlen", mutates_args=())
+def _wkv6_bwd_varlen(r: torch.Tensor, k: torch.Tensor, v: torch.Tensor, w: torch.Tensor, u: torch.Tensor,
+                     seq_start: torch.Tensor, seq_len: torch.Tensor, max_len: int, s0: Optional[torch.Tensor],
+                     state_map: Optional[torch.Tensor], d_y: torch.Tensor, d_sT: Optional[torch.Tensor],
+                     kept: torch.Tensor
+                     ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
+    lib = _lib.load()
+    dev = _lib.require_cuda(r, k, v, w, u, seq_start, seq_len, s0, state_map, d_y, d_sT, kept)
+    T = r.shape[1]
+    H, N = u.shape
+    n_seq = seq_start.numel()
+    code = _lib.dtype_code(r.dtype)
+    dr, dk, dv, dw = (torch.empty_like(r) for _ in range(4))
+    du = torch.empty(H, N, dtype=torch.float32, device=dev)
+    ds0 = torch.empty(n_seq, H, N, N, dtype=torch.float32, device=dev)
+    n_state = 0 if s0 is None else s0.shape[0]
+    with torch.cuda.device(dev):
+        nws = lib.rwkvb200_wkv6_varlen_workspace_bytes(n_seq, max_len, H, N, code, 1)
+        have = kept.numel() >= nws
+        ws = kept if have else torch.empty(nws, dtype=torch.uint8, device=dev)
+        rc = lib.rwkvb200_wkv6_bwd_varlen(r.data_ptr(), k.data_ptr(), v.data_ptr(), w.data_ptr(), u.data_ptr(),
+                                          seq_start.data_ptr(), seq_len.data_ptr(), n_seq, max_len, T,
+                                          _lib.ptr(s0), n_state, _lib.ptr(state_map), d_y.data_ptr(),
+                                          _lib.ptr(d_sT), dr.data_ptr(), dk.data_ptr(), dv.data_ptr(),
+                                          dw.data_ptr(), du.data_ptr(), ds0.data_ptr(), ws.data_ptr(), nws,
+                                          H, N, code, int(have), _lib.stream_ptr(dev))
+        _lib.check(rc, "wkv6_bwd_varlen")
+        _lib.check_status("wkv6_bwd_varlen")
+    return dr, dk, dv, dw, du, ds0
+
+
+@_wkv6_bwd_varlen.register_fake
+def _(r, k, v, w, u, seq_start, seq_len, max_len, s0, state_map, d_y, d_sT, kept):
+    H, N = u.shape
+    e = torch.empty_like
+    return (e(r), e(r), e(r), e(r), r.new_empty((H, N), dtype=torch.float32),
+            r.new_empty((seq_start.numel(), H, N, N), dtype=torch.float32))
+
+
+def _wkv6_setup_ctx(ctx, inputs, output):
+    r, k, v, w, u, seq_start, seq_len, max_len, s0, state_map, keep = inputs
+    ctx.save_for_backward(r, k, v, w, u, seq_start, seq_len, s0, state_map, output[2])
+    ctx.set_materialize_grads(False)
+    ctx.max_len = max_len
+
+
+def _wkv6_backward(ctx, d_y, d_sT, d_kept):
+    r, k, v, w, u, seq_start, seq_len, s0, state_map, kept = ctx.saved_tensors
+    if d_y is None:
+        d_y = torch.zeros_like(r)
+    d_y = d_y.to(r.dtype).contiguous()
+    if d_sT is not None:
+        d_sT = d_sT.to(torch.float32).contiguous()
+    dr, dk, dv, dw, du, ds0_rows = _wkv6_bwd_varlen(r, k, v, w, u, seq_start, seq_len, ctx.max_len, s0, state_map,
+                                                    d_y, d_sT, kept)
+    ds0 = None
+    if s0 is not None and ctx.needs_input_grad[8]:
+        n_state, n_seq = s0.shape[0], seq_start.numel()
+        if state_map is not None:
+            idx = state_map.to(torch.int64)
+        elif n_state == 1:
+            idx = torch.zeros(n_seq, dtype=torch.int64, device=r.device)
+        else:
+            idx = torch.arange(n_seq, device=r.device)
+        ds0 = torch.zeros_like(s0).index_add_(0, idx, ds0_rows)      # sequences that share a table row add up
+    return dr, dk, dv, dw, du, None, None, None, ds0, None, None
+
+
+torch.library.register_autograd("rwkv_ops_b200::wkv6_fwd_varlen", _wkv6_backward, setup_context=_wkv6_setup_ctx)
+
+
+def wkv6_varlen(r, k, v, w, u, cu_seqlens, init_state=None, state_map=None, head_size: int = 64):
+    """The RWKV6 wkv operator over sequences packed end to end.
+
+    The reference's operator takes dense ``[B, T, C]`` batches only (``rwkv_ops/rwkv6_kernel/
+    ops_rwkv_kernel.py:10-21``); this is the same recurrence per sequence without a padded token ever loaded,
+    computed or stored.  ``r, k, v, w``: ``[1, total_len, C]`` (or ``[total_len, C]``), ``C = H * 64``;
+    ``u``: ``C`` elements; ``cu_seqlens``: ``n_seq + 1`` increasing integers from 0 to ``total_len`` (tensor,
+    list or ``PackedSequences``); ``init_state``: ``[n_state, H, 64, 64]`` or ``[H, 64, 64]`` and ``state_map``
+    ``[n_seq]`` as in the dense operator, with the sequence in the place of the batch row.  Returns
+    ``(y, state)``: ``y`` shaped like ``r``, ``state`` ``[n_seq, H, 64, 64]`` in the operator's state dtype.
+    Differentiable with respect to ``r, k, v, w, u`` and ``init_state``.
+    """
+    dev = _lib.require_cuda(r, k, v, w, u, init_state)
+    if head_size != 64:
+        raise ValueError("the packed wkv6 operator is built for head size 64")
+    squeeze = r.dim() == 2
+    if squeeze:
+        r, k, v, w = (x[None] for x in (r, k, v, w))
+    if r.dim() != 3 or r.shape[0] != 1 or r.shape[-1] % 64:
+        raise ValueError(f"expected packed token tensors [1, total_len, H*64], got {tuple(r.shape)}")
+    for name, x in (("k", k), ("v", v), ("w", w)):
+        if x.shape != r.shape or x.dtype != r.dtype:
+            raise ValueError(f"{name} must match r in shape and dtype")
+    T, C = r.shape[1], r.shape[2]
+    H, N = C // 64, 64
+    if u.numel() != C:
+        raise ValueError(f"u must have {C} elements")
+    if isinstance(cu_seqlens, PackedSequences):
+        if cu_seqlens.total_len != T or cu_seqlens.start.device != dev:
+            raise ValueError("the PackedSequences object was made for another token count or device")
+        start, lens, max_len = cu_seqlens.start, cu_seqlens.lens, cu_seqlens.max_len
+    else:
+        _, start, lens, max_len = _seq_arrays(cu_seqlens, T, dev)
+    n_seq = start.numel()
+    dt = r.dtype
+    cdt = dt if dt in (torch.float32, torch.bfloat16, torch.float16) else torch.float32
+    state_dtype = torch.float32 if dt == torch.float16 else dt
+    s0 = smap = None
+    if init_state is not None:
+        if init_state.dim() == 3:
+            init_state = init_state[None]
+        if init_state.dim() != 4 or tuple(init_state.shape[1:]) != (H, N, N):
+            raise ValueError(f"init_state must be [n_state, {H}, {N}, {N}] or [{H}, {N}, {N}]")
+        n_state = init_state.shape[0]
+        if state_map is None:
+            if n_state not in (1, n_seq):
+                raise ValueError("state_map cannot be inferred from init_state; pass it explicitly")
+        else:
+            if isinstance(state_map, (list, tuple)):
+                state_map = torch.tensor(state_map, dtype=torch.int32)
+            if state_map.numel() != n_seq:
+                raise ValueError("state_map must have one entry per sequence")
+            if not state_map.is_cuda and not (bool((state_map >= 0).all()) and bool((state_map < n_state).all())):
+                raise ValueError(f"state_map values must lie in [0, {n_state})")
+            smap = state_map.to(device=dev, dtype=torch.int32).contiguous().view(n_seq)
+        s0 = init_state.to(torch.float32).contiguous()
+    elif state_map is not None:
+        raise ValueError("state_map needs init_state")
+    args = [x.to(cdt).contiguous() for x in (r, k, v, w)]
+    uu = u.reshape(H, N).to(torch.float32).contiguous()
+    needs_grad = torch.is_grad_enabled() and (
+        any(x.requires_grad for x in (r, k, v, w, u)) or (init_state is not None and init_state.requires_grad))
+    y, sT, _ = _wkv6_fwd_varlen(*args, uu, start, lens, max_len, s0, smap, needs_grad)
+    if y.dtype != dt:
+        y = y.to(dt)
+    if squeeze:
+        y = y[0]
+    return y, sT.to(state_dtype)

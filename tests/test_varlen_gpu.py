@@ -2,6 +2,7 @@
 import pytest
 import torch
 
+import rwkv_ops_b200 as ro
 from rwkv_ops_b200.workloads import rel_l2, rwkv7_inputs
 
 pytestmark = pytest.mark.gpu
@@ -171,3 +172,73 @@ def test_varlen_with_decays_beyond_the_range_of_the_chunked_kernels(bcast):
         assert rel_l2(o[:, sl], o_ref[:, sl]) <= 2e-2, i
         for n in NAMES:
             assert rel_l2(g[n].grad[:, sl], g_ref[n][:, sl]) <= 2e-2, (i, n)
+
+
+# ---------------------------------------------------------------------------------------------------------
+# RWKV6 wkv on packed batches
+# ---------------------------------------------------------------------------------------------------------
+def _wkv6_packed_case(lens, H, dtype, seed, w_scale=None):
+    from rwkv_ops_b200.workloads import wkv6_inputs
+    total = sum(lens)
+    d = wkv6_inputs(1, total, H, dtype=dtype, seed=seed, with_grads=True)
+    g = torch.Generator().manual_seed(seed + 1)
+    d["init_state"] = (0.1 * torch.randn(2, H, 64, 64, generator=g)).to(dtype)
+    d["d_state"] = (0.1 * torch.randn(len(lens), H, 64, 64, generator=g)).to(dtype)
+    if w_scale is not None:      # one head of one sequence decays faster than the tensor-core kernels' range
+        w = d["w"].float().view(1, total, H, 64)
+        s0 = sum(lens[:1])
+        w[:, s0:s0 + lens[1], 0] = w_scale
+        d["w"] = w.view(1, total, H * 64).to(dtype)
+    return d
+
+
+@pytest.mark.parametrize("lens,dtype,tol,w_scale", [
+    ((70, 1, 64, 129, 5), torch.float32, 1e-4, None),
+    ((70, 1, 64, 129, 5), torch.bfloat16, 2e-2, None),
+    ((33, 200, 64), torch.float32, 1e-4, 1.2),      # exp(1.2) = 3.3 per token: far beyond the chunked range
+])
+def test_wkv6_packed_equals_per_sequence_oracle(lens, dtype, tol, w_scale):
+    """``wkv6_varlen`` on sequences packed end to end against the CPU oracle run on every sequence alone:
+    outputs, final states, and the gradients of r, k, v, w, u and of an initial-state table whose rows are
+    shared between sequences."""
+    from oracle import RWKVKernelOperator as OracleOp
+    H = 2
+    d = _wkv6_packed_case(lens, H, dtype, seed=8100 + len(lens), w_scale=w_scale)
+    smap = [i % 2 for i in range(len(lens))]
+    cu = [0]
+    for n in lens:
+        cu.append(cu[-1] + n)
+    # oracle, sequence by sequence
+    ref = {n: d[n].float().clone().requires_grad_(True) for n in "rkvwu"}
+    s0r = d["init_state"].float().clone().requires_grad_(True)
+    ys, ss = [], []
+    for i, n in enumerate(lens):
+        sl = slice(cu[i], cu[i + 1])
+        yi, si = OracleOp(64, n)(ref["r"][:, sl], ref["k"][:, sl], ref["v"][:, sl], ref["w"][:, sl], ref["u"],
+                                 with_state=True, init_state=s0r, state_map=torch.tensor([smap[i]], dtype=torch.int32))
+        ys.append(yi)
+        ss.append(si)
+    y_ref, s_ref = torch.cat(ys, dim=1), torch.cat(ss, dim=0)
+    ((y_ref * d["d_y"].float()).sum() + (s_ref * d["d_state"].float()).sum()).backward()
+    # the packed operator
+    g = {n: d[n].cuda().requires_grad_(True) for n in "rkvwu"}
+    s0 = d["init_state"].cuda().requires_grad_(True)
+    y, s = ro.wkv6_varlen(g["r"], g["k"], g["v"], g["w"], g["u"], cu, init_state=s0, state_map=smap)
+    assert y.shape == d["r"].shape and y.dtype == dtype and s.shape == (len(lens), H, 64, 64)
+    ((y.float() * d["d_y"].cuda().float()).sum() + (s.float() * d["d_state"].cuda().float()).sum()).backward()
+    errs = {"y": rel_l2(y, y_ref), "s": rel_l2(s, s_ref), "ds0": rel_l2(s0.grad, s0r.grad)}
+    errs.update({f"d{n}": rel_l2(g[n].grad, ref[n].grad) for n in "rkvwu"})
+    assert all(e < tol for e in errs.values()), errs
+
+
+def test_wkv6_packed_matches_dense_when_lengths_are_equal():
+    """Two sequences of 128 tokens, packed and as a dense [2, 128, C] batch: the same kernels on the same data."""
+    from rwkv_ops_b200.workloads import wkv6_inputs
+    H, T = 2, 128
+    d = wkv6_inputs(2, T, H, dtype=torch.float32, seed=8200)
+    x = {n: d[n].cuda() for n in "rkvw"}
+    u = d["u"].cuda()
+    y_d, s_d = ro.RWKV6_OP(64, T)(x["r"], x["k"], x["v"], x["w"], u, with_state=True)
+    p = {n: x[n].reshape(1, 2 * T, -1) for n in "rkvw"}
+    y_p, s_p = ro.wkv6_varlen(p["r"], p["k"], p["v"], p["w"], u, [0, T, 2 * T])
+    assert torch.equal(y_p.reshape(2, T, -1), y_d) and torch.equal(s_p, s_d)
