@@ -38,8 +38,11 @@ def _default_local_op():
 class PhasedLocalOp:
     """Interface of a local operator whose state-independent work can run ahead of the chain.
 
-    ``prepare_fwd(r, w, k, v, a, b, head_first) -> st``; ``scan_fwd(st, h_in) -> (o, ht)``;
-    ``prepare_bwd(st, d_o)``; ``scan_bwd(st, d_ht) -> d_h_in``; ``finish_bwd(st) -> six token gradients``.
+    ``prepare_fwd(r, w, k, v, a, b, head_first) -> st``; ``scan_fwd(st, h_in, o_out, ht_out) -> (o, ht)``;
+    ``prepare_bwd(st, d_o, grads_out)``; ``scan_bwd(st, d_ht) -> d_h_in``; ``finish_bwd(st) -> six token
+    gradients``.  ``o_out``, ``ht_out`` and the six ``grads_out`` are views (one group of batch rows) of the
+    caller's full-size results: an operator that can write its results in place does, so that nothing is
+    copied afterwards.
     """
 
 
@@ -73,12 +76,19 @@ class ChunkedPhasedOp(PhasedLocalOp):
             _lib.check(rc, "rwkv7_fwd (prepare)")
         return st
 
-    def scan_fwd(self, st, h_in):
+    @staticmethod
+    def _usable(x, like):
+        return (x is not None and x.is_contiguous() and x.dtype == like.dtype and x.shape == like.shape
+                and x.device == like.device)
+
+    def scan_fwd(self, st, h_in, o_out=None, ht_out=None):
         from . import _lib
         lib = _lib.load()
         st.h_in = None if h_in is None else h_in.to(torch.float32).contiguous()
-        o = torch.empty_like(st.tok[0])
+        o = o_out if self._usable(o_out, st.tok[0]) else torch.empty_like(st.tok[0])
         ht = torch.empty(st.B, st.H, 64, 64, dtype=torch.float32, device=st.dev)
+        if ht_out is not None and ht_out.is_contiguous() and ht_out.dtype == ht.dtype and ht_out.shape == ht.shape:
+            ht = ht_out
         with torch.cuda.device(st.dev):
             rc = lib.rwkvb200_rwkv7_fwd(*[t.data_ptr() for t in st.tok], _lib.ptr(st.h_in),
                                         0 if st.h_in is None else st.h_in.shape[0], o.data_ptr(), ht.data_ptr(),
@@ -98,11 +108,14 @@ class ChunkedPhasedOp(PhasedLocalOp):
                                         int(st.head_first), st.algo | phase, _lib.stream_ptr(st.dev))
             _lib.check(rc, f"rwkv7_bwd ({what})")
 
-    def prepare_bwd(self, st, d_o):
+    def prepare_bwd(self, st, d_o, grads_out=None):
         from . import _lib
         st.d_o = d_o.to(torch.bfloat16).contiguous()
         st.d_ht = None
-        st.grads = [torch.empty_like(st.tok[0]) for _ in range(6)]
+        if grads_out is not None and all(self._usable(g, st.tok[0]) for g in grads_out):
+            st.grads = list(grads_out)
+        else:
+            st.grads = [torch.empty_like(st.tok[0]) for _ in range(6)]
         st.d_h0 = torch.empty(st.B, st.H, 64, 64, dtype=torch.float32, device=st.dev)
         self._bwd(st, _lib.PHASE_PREPARE, "prepare")
 
@@ -134,7 +147,7 @@ class ChainPhasedOp(PhasedLocalOp):
         st.leaves = [x.detach().requires_grad_(True) for x in (r, w, k, v, a, b)]
         return st
 
-    def scan_fwd(self, st, h_in):
+    def scan_fwd(self, st, h_in, o_out=None, ht_out=None):
         B = st.leaves[0].shape[0]
         H = st.leaves[0].shape[1] if st.head_first else st.leaves[0].shape[2]
         if h_in is None:
@@ -145,7 +158,7 @@ class ChainPhasedOp(PhasedLocalOp):
                                         head_first=st.head_first)
         return st.o.detach(), st.ht.detach()
 
-    def prepare_bwd(self, st, d_o):
+    def prepare_bwd(self, st, d_o, grads_out=None):
         st.d_o = d_o
 
     def scan_bwd(self, st, d_ht):
@@ -173,7 +186,9 @@ class _Chain(torch.autograd.Function):
         spans = [(bounds[j], bounds[j + 1]) for j in range(groups) if bounds[j] < bounds[j + 1]]
         # everything that does not wait for a neighbour first: it runs while the left ranks scan
         states = [op.prepare_fwd(*(x[lo:hi] for x in (r, w, k, v, a, b)), head_first) for lo, hi in spans]
-        outs, finals = [], []
+        # full-size results; every group writes its rows in place where the operator can
+        o_full = torch.empty_like(r)
+        ht_full = torch.empty(B, H, 64, 64, dtype=torch.float32, device=r.device)
         for (lo, hi), st in zip(spans, states):
             if prev_rank is not None:
                 h_in = torch.empty(hi - lo, H, 64, 64, dtype=torch.float32, device=r.device)
@@ -182,18 +197,20 @@ class _Chain(torch.autograd.Function):
                 h_in = (h0 if h0.shape[0] != 1 else h0.expand(B, -1, -1, -1))[lo:hi].contiguous()
             else:
                 h_in = None
-            o, ht = op.scan_fwd(st, h_in)
+            o, ht = op.scan_fwd(st, h_in, o_full[lo:hi], ht_full[lo:hi])
             if next_rank is not None:
                 dist.send(ht.contiguous(), dst=next_rank, group=group)
-            outs.append(o)
-            finals.append(ht)
+            if o.data_ptr() != o_full[lo:hi].data_ptr():
+                o_full[lo:hi] = o
+            if ht.data_ptr() != ht_full[lo:hi].data_ptr():
+                ht_full[lo:hi] = ht
         ctx.op, ctx.states, ctx.spans, ctx.group = op, states, spans, group
         ctx.prev_rank, ctx.next_rank = prev_rank, next_rank
         ctx.h0_shape = None if h0 is None else tuple(h0.shape)
         ctx.shape, ctx.dtype, ctx.device = tuple(r.shape), r.dtype, r.device
         ctx.state_tail = (H, 64, 64)
         ctx.set_materialize_grads(False)
-        return torch.cat(outs, 0), torch.cat(finals, 0)
+        return o_full, ht_full
 
     @staticmethod
     def backward(ctx, d_o, d_ht):
@@ -205,7 +222,7 @@ class _Chain(torch.autograd.Function):
         for (lo, hi), st in zip(ctx.spans, ctx.states):
             g_o = d_o[lo:hi] if d_o is not None else torch.zeros((hi - lo,) + ctx.shape[1:], dtype=ctx.dtype,
                                                                  device=ctx.device)
-            op.prepare_bwd(st, g_o)
+            op.prepare_bwd(st, g_o, [g[lo:hi] for g in grads])
         # same group order as the forward, so that neighbouring ranks overlap in the reverse chain too
         for (lo, hi), st in zip(ctx.spans, ctx.states):
             # the gradient of this rank's boundary state: what the right neighbour sends, plus whatever the
@@ -223,7 +240,8 @@ class _Chain(torch.autograd.Function):
         for (lo, hi), st in zip(ctx.spans, ctx.states):
             res = op.finish_bwd(st)
             for i in range(6):
-                grads[i][lo:hi] = res[i]
+                if res[i].data_ptr() != grads[i][lo:hi].data_ptr():
+                    grads[i][lo:hi] = res[i]
         if d_h0 is not None and ctx.h0_shape[0] == 1:
             d_h0 = d_h0.sum(0, keepdim=True)
         ctx.states = None
@@ -232,12 +250,17 @@ class _Chain(torch.autograd.Function):
 
 def generalized_delta_rule_sp(r, w, k, v, a, b, initial_state: Optional[torch.Tensor] = None,
                               output_final_state: bool = True, head_first: bool = False,
-                              group=None, pipeline_groups: int = 1, local_op=None):
+                              group=None, pipeline_groups: Optional[int] = None, local_op=None):
     """``generalized_delta_rule`` on a sequence split across the ranks of ``group`` (rank order =
     sequence order).  Every rank passes its own slice of the token tensors; ``initial_state`` is used on
     the first rank only.  Returns the local slice of ``o`` and, when ``output_final_state``, the state at
     the end of the local slice (the true final state on the last rank; a loss on the state of another rank
     is differentiated too).
+
+    ``pipeline_groups``: the batch rows are cut into this many groups whose scans follow one another, so that
+    a rank scans group j + 1 while its right neighbour scans group j (the chain then costs about
+    ``(ranks + groups - 1) / (ranks * groups)`` of the unsplit scans).  Default: up to 4 groups of at least 256
+    (batch, head) units each, enough to fill the scan kernels' grid.
 
     ``local_op``: a ``PhasedLocalOp``, or a ``generalized_delta_rule``-like callable (run as a plain chain);
     default: the phased tensor-core operator for bfloat16 CUDA tensors, else the plain chain over
@@ -246,6 +269,9 @@ def generalized_delta_rule_sp(r, w, k, v, a, b, initial_state: Optional[torch.Te
     if not dist.is_initialized():
         raise RuntimeError("torch.distributed is not initialised")
     B = r.shape[0]
+    if pipeline_groups is None:
+        H = r.shape[1] if head_first else r.shape[2]
+        pipeline_groups = min(4, (B * H) // 256)
     groups = max(1, min(int(pipeline_groups), B))
     if local_op is None:
         op = ChunkedPhasedOp() if (r.is_cuda and r.dtype == torch.bfloat16) else ChainPhasedOp(_default_local_op())
