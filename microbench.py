@@ -115,6 +115,8 @@ def bench_varlen(a):
     d_state = 0.1 * torch.randn(n_seq, a.H, 64, 64, device="cuda")
 
     def packed():
+        for t in g.values():      # no accumulation into .grad of an earlier step
+            t.grad = None
         o, s = generalized_delta_rule_varlen(*[g[n] for n in "rwkvab"], cu_t)
         torch.autograd.backward([o, s], [d["d_out"], d_state])
 
@@ -127,6 +129,8 @@ def bench_varlen(a):
     d_out_pad = torch.randn(n_seq, a.T, a.H, 64, device="cuda").bfloat16()
 
     def padded():
+        for t in gp.values():
+            t.grad = None
         o, s = ro.generalized_delta_rule(*[gp[n] for n in "rwkvab"])
         torch.autograd.backward([o, s], [d_out_pad, d_state])
 
@@ -148,11 +152,17 @@ def bench_fused(a):
     d_out = torch.randn(a.B, a.T, a.H, 64, generator=gen, device="cuda").bfloat16()
     d_state = 0.1 * torch.randn(a.B, a.H, 64, 64, generator=gen, device="cuda")
 
+    def clear():      # no accumulation into .grad of an earlier step (six more passes over the tensors)
+        for t in x.values():
+            t.grad = None
+
     def fused():
+        clear()
         o, s = ro.generalized_delta_rule_fused(*[x[n] for n in names])
         torch.autograd.backward([o, s], [d_out, d_state])
 
     def unfused():
+        clear()
         w, aa, bb = producers(x["w_pre"], x["kk_pre"], x["a_pre"])
         o, s = ro.generalized_delta_rule(x["r"], w, x["k"], x["v"], aa, bb)
         torch.autograd.backward([o, s], [d_out, d_state])
@@ -176,6 +186,8 @@ def bench_sp(a):
     g = {n: d[n].requires_grad_(True) for n in "rwkvab"}
 
     def step():
+        for t in g.values():      # no accumulation into .grad of an earlier step
+            t.grad = None
         o, s = generalized_delta_rule_sp(*[g[n] for n in "rwkvab"], pipeline_groups=a.groups)
         torch.autograd.backward([o, s], [d["d_out"], d["d_state"]])
 
