@@ -11,6 +11,8 @@
 //   dv = A^T dy + k~ dS^        dA = dy v^T (strictly lower part -> r~, k~; diagonal -> the u term)
 //   dr~ = dy S~0^T + stril(dA) k~      dk~ = stril(dA)^T r~ + v dS^^T      dS0 = diag(e^{gref}) (r~^T dy + dS^)
 //   dge = dr~ r~,  dgi = -dk~ k~,  dglast = sum_v dS_L S_L,  dg_j = sum_{i>j} dge_i + sum_{i>=j} dgi_i + dglast
+//   (computed without the cancellation between dglast and the state part of dgi: with X = v dS^^T,
+//    dg_j = sum_{i>j} dge_i - sum_{i>=j} (stril(dA)^T r~)_i k~_i + sum_v dS^ S~0 + sum_{i<j} X_i k~_i)
 //   dw = dg g;   with dd_i = dy_i . v_i:  dr += dd u k,  dk += dd r u,  du += sum_i dd r k
 //
 // Precision.  The parity bar for float32 inputs is 1e-4, which bf16 operands cannot meet, so every
@@ -447,9 +449,10 @@ struct BwdSmem {
   float red_e[L * NROW];              // dr~ r~
   float qtot[4][64];
   float rqtot[4][64];
+  float pqtot[4][64];
   float dgs[64];                      // sum_k r u k per token
   float dds[64];                      // dy_i . v_i per token
-  float dgl[2][64];                   // dglast, one partial per column half
+  float dgl[2][64];                   // sum_v dS^ S~0, one partial per column half
   float du_s[64];
   // raw rows of the next chunk, requested by TMA a chunk ahead: w and dy (needed first) here; r and k land
   // in the space of rt / kt once the last epilogue has read those, v in red_e once the decay gradient has
@@ -497,6 +500,7 @@ wkv6c_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
   float* stage_dv = stage_dk + L * NROW;
   float* stage_dw = stage_dv + L * NROW;
   float* red_i = stage_dw + L * NROW;          // 5 x 17408 B = 87040 B <= 12 tiles
+  float* red_x = stage_dw;                     // X k~ per (token, channel), read before dw is staged over it
 
   if (tid == 0) {
     mbar_init(&sm.bar_1, 1); mbar_init(&sm.bar_2, 1);
@@ -512,6 +516,7 @@ wkv6c_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
   const uint32_t tm_c0 = tmem_addr(tm, 32 * wq, 32 * hsel);          // A (lower), dA (upper)
   const uint32_t tm_c1 = tmem_addr(tm, 32 * wq, 64 + 32 * hsel);     // dk~ (lower), dr~ (upper)
   const uint32_t tm_c2 = tmem_addr(tm, 32 * wq, 128 + 32 * hsel);    // dv (lower), dS~0 (upper)
+  const uint32_t tm_c3 = tmem_addr(tm, 32 * wq, 192 + 32 * hsel);    // X = v dS^^T (lower): the state part of dk~
 
   // gradient of the state after the current chunk: row k = srow (upper lane halves), 32 columns
   float dsreg[32];
@@ -633,11 +638,11 @@ wkv6c_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
       for (int m = 8; m >= 1; m >>= 1) dg += __shfl_xor_sync(0xffffffffu, dg, m);
       if (c4 == 0) sm.dgs[row] = dg;
     }
-    // the state row of this lane (upper lane: S_L for dglast, lower lane: S0) is requested here and used
-    // after the first epilogue: MMA batch 1 and that epilogue cover its latency
+    // the row of S0 (both lanes of a pair: the lower one for S~0, the upper one for sum_v dS^ S~0) is requested
+    // here and used after the first epilogue: MMA batch 1 and that epilogue cover its latency
     float4 srow4[8];
     {
-      const float* Srow = states + (((size_t)unit * nts + c + (lower ? 0 : 1)) * HS + srow) * HS + 32 * hsel;
+      const float* Srow = states + (((size_t)unit * nts + c) * HS + srow) * HS + 32 * hsel;
 #pragma unroll
       for (int j = 0; j < 8; ++j) srow4[j] = *reinterpret_cast<const float4*>(Srow + 4 * j);
     }
@@ -673,8 +678,9 @@ wkv6c_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
     // decay factors of state row k = srow (both lanes of a pair work on that row below)
     const float e0 = ex2(fmaxf(sm.qtot[0][srow] + sm.qtot[1][srow], EXP2_FLOOR));
     const float dlast = ex2(fmaxf(sm.qtot[2][srow] + sm.qtot[3][srow], EXP2_FLOOR));
-    // ---- state rows: the upper lane of a pair holds dS and takes dglast and dS^ = e^{glast-gref} dS_L,
-    // the lower lane takes S~0 = e^{gref} S0; one split-and-store call serves both
+    // ---- state rows: the upper lane of a pair holds dS and takes sum_v dS^ S~0 (the part of dglast that nothing
+    // cancels) and dS^ = e^{glast-gref} dS_L, the lower lane takes S~0 = e^{gref} S0; one split-and-store call
+    // serves both
     {
       float x[32];
       if (!lower) {
@@ -684,7 +690,7 @@ wkv6c_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
           const float4 f = srow4[j >> 2];
           acc += dsreg[j] * f.x + dsreg[j + 1] * f.y + dsreg[j + 2] * f.z + dsreg[j + 3] * f.w;
         }
-        sm.dgl[hsel][srow] = acc;
+        sm.dgl[hsel][srow] = acc * (e0 * dlast);      // sum_v dS^ S~0 = e^{gref} e^{glast-gref} sum_v dS_L S0
 #pragma unroll
         for (int j = 0; j < 32; ++j) { dsreg[j] *= dlast; x[j] = dsreg[j]; }     // dsreg now holds dS^
       } else {
@@ -714,7 +720,9 @@ wkv6c_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
       // dk~ = stril(dA)^T r~ + v dS^^T              (lower halves, columns 64..127: beside dr~, so that one
       // piece of code scales both in the epilogue)
       umma_split<64, 64, 1, 1>(tmem_addr(tm, 0, 64), smem_u32(sm.dat[0]), smem_u32(sm.rt[0]), false);
-      umma_split<64, 64, 0, 0>(tmem_addr(tm, 0, 64), smem_u32(sm.vt[0]), smem_u32(sm.dst[0]), true);
+      // its state part X = v dS^^T apart (lower halves, columns 192..255): the decay gradient takes the two
+      // parts of dk~ k~ in different sums
+      umma_split<64, 64, 0, 0>(tmem_addr(tm, 0, 192), smem_u32(sm.vt[0]), smem_u32(sm.dst[0]), false);
       // dS~0 = r~^T dy                              (upper halves, columns 128..191)
       umma_split<64, 64, 1, 1>(tmem_addr(tm, 16, 128), smem_u32(sm.rt[0]), smem_u32(sm.dyt[0]), false);
       umma_commit(&sm.bar_2);
@@ -723,42 +731,54 @@ wkv6c_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
     tc_fence_after();
     W6C_STAMP(39);
     if (ok) {
-      uint32_t r1[32], r2[32];
-      tmem_ld32(tm_c1, r1);
-      tmem_ld32(tm_c2, r2);
-      tmem_ld_wait();
       const int c0 = 32 * hsel;
+      {
+        // dv row of token srow (lower halves) / dS~0 row k = srow (upper halves)
+        uint32_t r2[32];
+        tmem_ld32(tm_c2, r2);
+        tmem_ld_wait();
+        if (!lower) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) dsreg[j] = e0 * (__uint_as_float(r2[j]) + dsreg[j]);   // dS0 = e^{gref}(r~^T dy + dS^)
+        } else {
+#pragma unroll
+          for (int j4 = 0; j4 < 32; j4 += 4)
+            *reinterpret_cast<float4*>(&stage_dv[srow * NROW + c0 + j4]) =
+                make_float4(__uint_as_float(r2[j4]), __uint_as_float(r2[j4 + 1]), __uint_as_float(r2[j4 + 2]),
+                            __uint_as_float(r2[j4 + 3]));
+        }
+      }
+      // r1: the part of dk~ from inside the chunk, stril(dA)^T r~ (lower halves) / dr~ (upper halves), row of token
+      // srow; rx: the state part of dk~, X = v dS^^T (lower halves only)
+      uint32_t r1[32], rx[32];
+      tmem_ld32(tm_c1, r1);
+      tmem_ld32(tm_c3, rx);
+      tmem_ld_wait();
       float th[32], tl[32];
-      // r1: dk~ (lower halves) / dr~ (upper halves) row of token srow; r2: dv row of token srow (lower) /
-      // dS~0 row k = srow (upper)
       tile_load_row32(lower ? sm.kt[0] : sm.rt[0], srow, c0, th);
       tile_load_row32(lower ? sm.kt[1] : sm.rt[1], srow, c0, tl);
-      if (!lower) {
-#pragma unroll
-        for (int j = 0; j < 32; ++j) dsreg[j] = e0 * (__uint_as_float(r2[j]) + dsreg[j]);   // dS0 = e^{gref}(r~^T dy + dS^)
-      }
 #pragma unroll
       for (int j4 = 0; j4 < 32; j4 += 4) {
         const int cc = c0 + j4;
         const float4 gs4 = *reinterpret_cast<const float4*>(&sm.gs[srow * NROW + cc]);
         const float4 gg4 = *reinterpret_cast<const float4*>(&sm.gg[srow * NROW + cc]);
         const float gsv[4] = {gs4.x, gs4.y, gs4.z, gs4.w}, ggv[4] = {gg4.x, gg4.y, gg4.z, gg4.w};
-        float o[4], rd[4];
+        float o[4], rd[4], rs[4];
 #pragma unroll
         for (int m = 0; m < 4; ++m) {
           const int j = j4 + m;
           const float d1 = gsv[m];                                   // gi - gref
           const float tt = th[j] + tl[j];                            // k~ (lower) / r~ (upper)
-          const float x = __uint_as_float(r1[j]);                    // dk~ (lower) / dr~ (upper)
-          o[m] = x * ex2(lower ? -d1 : d1 - ggv[m]);                 // dk = dk~ e^{gref-gi},  dr = dr~ e^{ge-gref}
-          rd[m] = lower ? -x * tt : x * tt;                          // dgi = -dk~ k~,  dge = dr~ r~
+          const float x = __uint_as_float(r1[j]);
+          const float xs = lower ? __uint_as_float(rx[j]) : 0.f;
+          o[m] = (x + xs) * ex2(lower ? -d1 : d1 - ggv[m]);          // dk = dk~ e^{gref-gi},  dr = dr~ e^{ge-gref}
+          rd[m] = lower ? -x * tt : x * tt;                          // -(stril(dA)^T r~) k~,  dge = dr~ r~
+          rs[m] = xs * tt;                                           // X k~
         }
         if (lower) {
           *reinterpret_cast<float4*>(&stage_dk[srow * NROW + cc]) = make_float4(o[0], o[1], o[2], o[3]);
           *reinterpret_cast<float4*>(&red_i[srow * NROW + cc]) = make_float4(rd[0], rd[1], rd[2], rd[3]);
-          *reinterpret_cast<float4*>(&stage_dv[srow * NROW + cc]) =
-              make_float4(__uint_as_float(r2[j4]), __uint_as_float(r2[j4 + 1]), __uint_as_float(r2[j4 + 2]),
-                          __uint_as_float(r2[j4 + 3]));
+          *reinterpret_cast<float4*>(&red_x[srow * NROW + cc]) = make_float4(rs[0], rs[1], rs[2], rs[3]);
         } else {
           *reinterpret_cast<float4*>(&stage_dr[srow * NROW + cc]) = make_float4(o[0], o[1], o[2], o[3]);
           *reinterpret_cast<float4*>(&sm.red_e[srow * NROW + cc]) = make_float4(rd[0], rd[1], rd[2], rd[3]);
@@ -769,24 +789,34 @@ wkv6c_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
     ok = __syncthreads_and(ok);
     if (tid == 0 && ok && c > 0) load_in_b(c - 1);      // the epilogue above was the last reader of rt / kt
     W6C_STAMP(40);
-    // ---- decay gradient: dg_j = sum_{i>j} (dgi_i + dge_i) + dgi_j + dglast;  dw = dg g
+    // ---- decay gradient, with I_i = -(stril(dA)^T r~)_i k~_i and X_i k~_i the two parts of dgi_i = -dk~_i k~_i:
+    // dg_j = sum_{i>j} (dge_i + I_i) + I_j + sum_v dS^ S~0 + sum_{i<j} X_i k~_i;   dw = dg g.
+    // (dglast = sum_v dS_L S_L contains sum_i X_i k~_i; taking the sum over i < j instead of dglast minus the
+    // sum over i >= j keeps the two large, nearly equal terms from cancelling.)
     {
       const int ch = tid & 63, quarter = tid >> 6;
-      float rv[16];
+      float rv[16], px[16];
 #pragma unroll
-      for (int j = 0; j < 16; ++j)
+      for (int j = 0; j < 16; ++j) {
         rv[j] = red_i[(16 * quarter + j) * NROW + ch] + sm.red_e[(16 * quarter + j) * NROW + ch];
-      float run = 0.f;
+        px[j] = red_x[(16 * quarter + j) * NROW + ch];
+      }
+      float run = 0.f, prun = 0.f;
 #pragma unroll
       for (int j = 15; j >= 0; --j) { const float t = rv[j]; rv[j] = run; run += t; }      // sums over i > j
+#pragma unroll
+      for (int j = 0; j < 16; ++j) { const float t = px[j]; px[j] = prun; prun += t; }      // sums over i < j
       sm.rqtot[quarter][ch] = run;
+      sm.pqtot[quarter][ch] = prun;
       __syncthreads();
       float add = sm.dgl[0][ch] + sm.dgl[1][ch];
       for (int q2 = quarter + 1; q2 < 4; ++q2) add += sm.rqtot[q2][ch];
+      for (int q2 = 0; q2 < quarter; ++q2) add += sm.pqtot[q2][ch];
 #pragma unroll
       for (int j = 0; j < 16; ++j) {
         const int ii = 16 * quarter + j;
-        const float dg = rv[j] + add + red_i[ii * NROW + ch];
+        const float dg = (rv[j] + px[j]) + add + red_i[ii * NROW + ch];
+        // stage_dw lies over red_x: this thread has read its 16 entries above and writes the same 16
         stage_dw[ii * NROW + ch] = dg * (LN2 * sm.gg[ii * NROW + ch]);      // dw = dg g, g = gg ln 2
       }
     }
