@@ -238,6 +238,7 @@ int rwkvb200_rwkv7_bwd_static(const void* r, const void* w, const void* k, const
  * Head sizes 32 and 128 (the reference's operator takes the head size in its constructor,
  * rwkv_ops/rwkv6_kernel/__init__.py:37-50) run the recurrent path whatever `algo` says, except that an
  * explicit RWKVB200_ALGO_CHUNKED returns RWKVB200_E_UNSUPPORTED; states are [head_size][head_size].
+ * Sequences shorter than 8 tokens are computed by the float32 recurrence as well (same mechanism as below).
  * Decay range of the chunked path: it holds the 1e-4 parity bar while the sum of exp(w) over the 32 tokens
  * of a half chunk stays below 45 in every channel (always true for w <= 0.34).  A (batch, head) unit that
  * exceeds this is detected on the device and recomputed, forward and backward, by the float32 recurrence

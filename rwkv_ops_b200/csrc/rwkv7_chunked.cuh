@@ -136,6 +136,11 @@ struct Workspace {
 // returns values computed from clamped exponents.  |g| <= 1.875 per token never reaches the limit; RWKV7's
 // own parametrisation keeps |g| below 0.61.
 constexpr float DECAY_LIMIT = 60.f;
+// Sequences shorter than this are recomputed by the recurrence as well (marked in the same flags): with one or
+// two tokens the decay gradient is what is left of sums over the whole chunk that cancel almost completely
+// (exactly zero for one token and no initial state), so the bfloat16 roundings of the chunk products would be all
+// there is in dw; the recurrence costs nothing at that length.
+constexpr int SHORT_SEQ = 8;
 
 inline size_t align256(size_t x) { return (x + 255) & ~size_t(255); }
 

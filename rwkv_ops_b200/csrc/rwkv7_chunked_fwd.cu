@@ -203,7 +203,7 @@ r7c_intra_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ w, con
         ws_aux[(size_t)ch * AUX_FLOATS + tid] = ex2(fmaxf(tot0, EXP2_FLOOR));        // e^{gref}
         ws_aux[(size_t)ch * AUX_FLOATS + 64 + tid] = ex2(fmaxf(tot1, EXP2_FLOOR));   // e^{glast-gref}
         // a half-chunk decay sum beyond the limit: the unit is recomputed by the float32 recurrence
-        if (fminf(tot0, tot1) < -DECAY_LIMIT * LOG2E) ws_flags[bi * H + hi] = 1;
+        if (fminf(tot0, tot1) < -DECAY_LIMIT * LOG2E || Tn < SHORT_SEQ) ws_flags[bi * H + hi] = 1;
       }
       // the raw q, k, a, b: each thread scales its own 2 x 16 bytes in place (the previous chunk-head's W, U,
       // A_qb, O1 copies may still be reading their tiles: those are rewritten only after MMA 1)

@@ -46,6 +46,12 @@ constexpr float EXP2_FLOOR = -126.f;      // 2^x below this is flushed to zero a
 // chunk is marked by the forward kernel and recomputed by the float32 recurrence (wkv6.cu), forward and
 // backward, so that no value computed from a clamped exponent is ever returned.
 constexpr float DECAY_LIMIT = 45.f;
+// Sequences shorter than this take the recurrence as well (marked in the same flags): with two or three tokens and
+// fast decays the decay gradient is the small remainder of pair sums that cancel (every pair of tokens enters the
+// row sums of dr~ r~ and the column sums of dk~ k~ with opposite signs, computed by different tensor-core
+// products), and the 2^-17 roundings of the split operands reached 5e-4 of dw there; the recurrence costs nothing
+// at that length.
+constexpr int SHORT_SEQ = 8;
 
 // two values as packed bf16 pairs hi and lo with x = hi + lo (+ an error of about 2^-17 |x|)
 __device__ __forceinline__ void split_pair(float x0, float x1, uint32_t& hi, uint32_t& lo) {
@@ -291,7 +297,7 @@ wkv6c_fwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
       e0 = ex2(fmaxf(tot0, EXP2_FLOOR));
       dlast = ex2(fmaxf(tot1, EXP2_FLOOR));
       // a half-chunk decay sum beyond the limit: the unit is recomputed by the float32 recurrence
-      if (hsel == 0 && fminf(tot0, tot1) < -DECAY_LIMIT * LOG2E) flags[unit] = 1;
+      if (hsel == 0 && (fminf(tot0, tot1) < -DECAY_LIMIT * LOG2E || Tn < SHORT_SEQ)) flags[unit] = 1;
     }
     // ---- S~0 = e^{gref} S0 stays in registers (fp32); hi/lo bf16 tiles for the r~ S~0 product
     if (!tok_lane) {

@@ -232,3 +232,16 @@ def test_head_size_128_forward_backward(T, dtype, tol):
         o_hf = fn(*[g[n].detach().permute(0, 2, 1, 3).contiguous() for n in "rwkvab"], initial_state=h0.detach(),
                   output_final_state=False, head_first=True)
     assert torch.equal(o_hf.permute(0, 2, 1, 3), o)
+
+
+def test_one_token_without_state_has_no_decay_gradient():
+    """One token and no initial state: the output does not depend on the decay, so dw is exactly zero (on the
+    tensor-core path it would be the rounding residue of two chunk sums that cancel; sequences this short take
+    the recurrence)."""
+    B, T, H = 3, 1, 5
+    d = rwkv7_inputs(B, T, H, dtype=torch.bfloat16, seed=4242, with_grads=True)
+    g = {n: d[n].cuda().requires_grad_(True) for n in "rwkvab"}
+    o, s = ro.generalized_delta_rule(*[g[n] for n in "rwkvab"])
+    torch.autograd.backward([o, s], [d["d_out"].cuda(), d["d_state"].cuda()])
+    assert torch.count_nonzero(g["w"].grad) == 0
+    assert torch.isfinite(g["r"].grad.float()).all() and torch.count_nonzero(g["k"].grad) > 0

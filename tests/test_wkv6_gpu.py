@@ -188,3 +188,27 @@ def test_full_size_du_and_init_state_gradient():
         assert rel_l2(g["u"].grad[h:h + 1], gr[4]) < 1e-4
         ds0_ref = torch.zeros(4, 1, 64, 64, dtype=gr[5].dtype).index_add_(0, smap, gr[5])
         assert rel_l2(s0.grad[:, h:h + 1], ds0_ref) < 1e-4
+
+
+@pytest.mark.parametrize("T", [2, 3])
+def test_very_short_sequences_with_fast_decays(T):
+    """Two- and three-token sequences whose decays are fast (w ~ N(-0.3, 0.8^2)): the decay gradient is then a
+    small remainder of sums that cancel, the case in which the tensor-core path's roundings would show most;
+    such sequences take the recurrence.  Twelve seeds against the float64 oracle."""
+    B, H = 2, 7
+    for seed in range(12):
+        d = wkv6_inputs(B, T, H, dtype=torch.float32, seed=7700 + seed, n_state=1, with_grads=True)
+        g0 = torch.Generator().manual_seed(seed)
+        d["w"] = -0.3 + 0.8 * torch.randn(d["w"].shape, generator=g0)
+        ref = {n: d[n].double().clone().requires_grad_(True) for n in "rkvwu"}
+        s0r = d["init_state"].double().clone().requires_grad_(True)
+        y_ref, s_ref = OracleOp(64, T, compute_dtype=torch.float64)(ref["r"], ref["k"], ref["v"], ref["w"], ref["u"],
+                                                                    with_state=True, init_state=s0r)
+        ((y_ref * d["d_y"].double()).sum() + (s_ref * d["d_state"].double()).sum()).backward()
+        g = {n: d[n].cuda().requires_grad_(True) for n in "rkvwu"}
+        s0 = d["init_state"].cuda().requires_grad_(True)
+        y, s = ro.RWKV6_OP(64, T)(g["r"], g["k"], g["v"], g["w"], g["u"], with_state=True, init_state=s0)
+        ((y * d["d_y"].cuda()).sum() + (s * d["d_state"].cuda()).sum()).backward()
+        errs = {"y": rel_l2(y, y_ref), "s": rel_l2(s, s_ref), "ds0": rel_l2(s0.grad, s0r.grad)}
+        errs.update({f"d{n}": rel_l2(g[n].grad, ref[n].grad) for n in "rkvwu"})
+        assert all(e < 1e-4 for e in errs.values()), (seed, errs)
