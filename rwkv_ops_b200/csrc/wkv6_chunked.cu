@@ -645,7 +645,7 @@ wkv6c_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
       if (c4 == 0) sm.dgs[row] = dg;
     }
     // the row of S0 (both lanes of a pair: the lower one for S~0, the upper one for sum_v dS^ S~0) is requested
-    // here and used after the first epilogue: MMA batch 1 and that epilogue cover its latency
+    // here and used under MMA batch 1 (requested a phase earlier, the loads held the pass above up instead)
     float4 srow4[8];
     {
       const float* Srow = states + (((size_t)unit * nts + c) * HS + srow) * HS + 32 * hsel;
@@ -673,18 +673,11 @@ wkv6c_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
       umma_split<64, 64, 0, 0>(tmem_addr(tm, 16, 0), smem_u32(sm.dyt[0]), smem_u32(sm.vt[0]), false);
       umma_commit(&sm.bar_1);
     }
-    ok = mbar_wait(&sm.bar_1, par, status, 411) && ok;
-    tc_fence_after();
-    W6C_STAMP(37);
-    if (ok) {
-      const float dgi = lower ? sm.dgs[srow] : 0.f;     // the diagonal of A carries the u term; dA's does not
-      // one call: both lane halves run the same code
-      load_store_masked_row(tm_c0, wq, hsel, lane & 15, dgi, lower ? sm.at[0] : sm.dat[0], srow, true);
-    }
     // decay factors of state row k = srow (both lanes of a pair work on that row below)
     const float e0 = ex2(fmaxf(sm.qtot[0][srow] + sm.qtot[1][srow], EXP2_FLOOR));
     const float dlast = ex2(fmaxf(sm.qtot[2][srow] + sm.qtot[3][srow], EXP2_FLOOR));
-    // ---- state rows: the upper lane of a pair holds dS and takes sum_v dS^ S~0 (the part of dglast that nothing
+    // ---- state rows, while MMA batch 1 runs (it reads neither of the two tiles written here): the upper lane of a
+    // pair holds dS and takes sum_v dS^ S~0 (the part of dglast that nothing
     // cancels) and dS^ = e^{glast-gref} dS_L, the lower lane takes S~0 = e^{gref} S0; one split-and-store call
     // serves both
     {
@@ -708,6 +701,14 @@ wkv6c_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
       }
       unsigned char* hi_t = lower ? sm.st[0] : sm.dst[0];
       store_split_row32(hi_t, hi_t + TILE_BYTES, srow, 32 * hsel, x);
+    }
+    ok = mbar_wait(&sm.bar_1, par, status, 411) && ok;
+    tc_fence_after();
+    W6C_STAMP(37);
+    if (ok) {
+      const float dgi = lower ? sm.dgs[srow] : 0.f;     // the diagonal of A carries the u term; dA's does not
+      // one call: both lane halves run the same code
+      load_store_masked_row(tm_c0, wq, hsel, lane & 15, dgi, lower ? sm.at[0] : sm.dat[0], srow, true);
     }
     fence_async_smem();
     tc_fence_before();
