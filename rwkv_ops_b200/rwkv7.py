@@ -276,7 +276,9 @@ def generalized_delta_rule(
     of float32 / bfloat16 / float16; ``w`` is the raw decay input (the operator applies
     ``exp(-exp(w))``).  ``initial_state``: float32 ``[N, H, K, K]`` with ``N == B`` or ``N == 1``
     (broadcast), value index before key index.  Returns ``(o, final_state)`` or just ``o``.
-    Head size 64 with bfloat16 tokens takes the tensor-core path, everything else the float32 recurrence.
+    Head size 64 with bfloat16 tokens takes the tensor-core path, everything else the float32 recurrence
+    (``RWKV_OPS_B200_RWKV7_ALGO=chunked`` sends float32 / float16 tokens of head size 64 through the tensor-core
+    path as well, rounded to bfloat16).
     """
     _lib.require_cuda(r, w, k, v, a, b, initial_state)
     if r.dim() != 4 or r.shape[-1] not in HEAD_SIZES:
@@ -287,6 +289,11 @@ def generalized_delta_rule(
             raise ValueError(f"{name} has shape {tuple(x.shape)}, expected {tuple(r.shape)}")
     out_dtype = r.dtype
     cdt = r.dtype if r.dtype in (torch.float32, torch.bfloat16, torch.float16) else torch.float32
+    if cdt != torch.bfloat16 and HEAD_SIZE == 64 and _default_algo() == _lib.ALGO_CHUNKED:
+        # RWKV_OPS_B200_RWKV7_ALGO=chunked asked for the tensor-core path by name: float32 / float16 tokens are
+        # rounded to bfloat16 for it (about 15 times the speed of the float32 recurrence at bfloat16-operand
+        # accuracy, 2e-2 against the oracle instead of 1e-4); gradients come back in the inputs' dtypes
+        cdt = torch.bfloat16
     r_, w_, k_, v_, a_, b_ = (x.to(cdt).contiguous() for x in (r, w, k, v, a, b))
     B = r.shape[0]
     H = r.shape[1] if head_first else r.shape[2]

@@ -245,3 +245,25 @@ def test_one_token_without_state_has_no_decay_gradient():
     torch.autograd.backward([o, s], [d["d_out"].cuda(), d["d_state"].cuda()])
     assert torch.count_nonzero(g["w"].grad) == 0
     assert torch.isfinite(g["r"].grad.float()).all() and torch.count_nonzero(g["k"].grad) > 0
+
+
+def test_float32_tokens_on_the_tensor_core_path_by_request(monkeypatch):
+    """RWKV_OPS_B200_RWKV7_ALGO=chunked with float32 tokens: rounded to bfloat16 for the tensor-core kernels,
+    outputs and gradients back in float32, bfloat16-grade agreement with the oracle."""
+    monkeypatch.setenv("RWKV_OPS_B200_RWKV7_ALGO", "chunked")
+    B, T, H = 2, 150, 3
+    d = rwkv7_inputs(B, T, H, dtype=torch.float32, seed=4343, with_state=True, with_grads=True)
+    ref = {n: d[n].clone().requires_grad_(True) for n in "rwkvab"}
+    h0r = d["initial_state"].clone().requires_grad_(True)
+    o_ref, s_ref = oracle_gdr(*[ref[n] for n in "rwkvab"], initial_state=h0r)
+    ((o_ref * d["d_out"]).sum() + (s_ref * d["d_state"]).sum()).backward()
+    g = {n: d[n].cuda().requires_grad_(True) for n in "rwkvab"}
+    h0 = d["initial_state"].cuda().requires_grad_(True)
+    o, s = ro.generalized_delta_rule(*[g[n] for n in "rwkvab"], initial_state=h0)
+    assert o.dtype == torch.float32
+    torch.autograd.backward([o, s], [d["d_out"].cuda(), d["d_state"].cuda()])
+    errs = {"o": rel_l2(o, o_ref), "s": rel_l2(s, s_ref), "dh0": rel_l2(h0.grad, h0r.grad)}
+    errs.update({f"d{n}": rel_l2(g[n].grad, ref[n].grad) for n in "rwkvab"})
+    assert all(g[n].grad.dtype == torch.float32 for n in "rwkvab")
+    assert all(e < 2e-2 for e in errs.values()), errs
+    assert errs["o"] > 1e-5      # the bfloat16 path did run (the recurrence is float32-exact)
