@@ -464,7 +464,7 @@ struct BwdSmem {
   // in the space of rt / kt once the last epilogue has read those, v in red_e once the decay gradient has
   alignas(128) unsigned char raw_w[L * 64 * 4];
   alignas(128) unsigned char raw_dy[L * 64 * 4];
-  uint64_t bar_1, bar_2, bar_in_a, bar_in_b, bar_in_c;
+  uint64_t bar_1, bar_2, bar_2a, bar_in_a, bar_in_b, bar_in_c;
   uint32_t tmem_base;
 };
 static_assert(sizeof(BwdSmem) + 1024 <= 227 * 1024, "backward shared memory");
@@ -509,7 +509,7 @@ wkv6c_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
   float* red_x = stage_dw;                     // X k~ per (token, channel), read before dw is staged over it
 
   if (tid == 0) {
-    mbar_init(&sm.bar_1, 1); mbar_init(&sm.bar_2, 1);
+    mbar_init(&sm.bar_1, 1); mbar_init(&sm.bar_2, 1); mbar_init(&sm.bar_2a, 1);
     mbar_init(&sm.bar_in_a, 1); mbar_init(&sm.bar_in_b, 1); mbar_init(&sm.bar_in_c, 1);
     fence_mbar_init();
   }
@@ -715,48 +715,35 @@ wkv6c_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
     ok = __syncthreads_and(ok);
 
     W6C_STAMP(38);
-    // ---- batch 2
+    // ---- batch 2, committed in two parts: the products the heavier part of the read-out needs first, so that its
+    // arithmetic runs while the tensor pipe works on the rest (its results stay in registers until then: the
+    // staging arrays lie over operand tiles of the products still running)
     if (tid == 0 && ok) {
       tc_fence_after();
-      // dv = A^T dy + k~ dS^                        (lower halves, columns 128..191)
-      umma_split<64, 64, 1, 1>(tmem_addr(tm, 0, 128), smem_u32(sm.at[0]), smem_u32(sm.dyt[0]), false);
-      umma_split<64, 64, 0, 1>(tmem_addr(tm, 0, 128), smem_u32(sm.kt[0]), smem_u32(sm.dst[0]), true);
       // dr~ = dy S~0^T + stril(dA) k~               (upper halves, columns 64..127)
       umma_split<64, 64, 0, 0>(tmem_addr(tm, 16, 64), smem_u32(sm.dyt[0]), smem_u32(sm.st[0]), false);
       umma_split<64, 64, 0, 1>(tmem_addr(tm, 16, 64), smem_u32(sm.dat[0]), smem_u32(sm.kt[0]), true);
-      // dk~ = stril(dA)^T r~ + v dS^^T              (lower halves, columns 64..127: beside dr~, so that one
-      // piece of code scales both in the epilogue)
+      // the part of dk~ from inside the chunk, stril(dA)^T r~   (lower halves, columns 64..127: beside dr~, so
+      // that one piece of code scales both in the epilogue)
       umma_split<64, 64, 1, 1>(tmem_addr(tm, 0, 64), smem_u32(sm.dat[0]), smem_u32(sm.rt[0]), false);
       // its state part X = v dS^^T apart (lower halves, columns 192..255): the decay gradient takes the two
       // parts of dk~ k~ in different sums
       umma_split<64, 64, 0, 0>(tmem_addr(tm, 0, 192), smem_u32(sm.vt[0]), smem_u32(sm.dst[0]), false);
+      umma_commit(&sm.bar_2a);
+      // dv = A^T dy + k~ dS^                        (lower halves, columns 128..191)
+      umma_split<64, 64, 1, 1>(tmem_addr(tm, 0, 128), smem_u32(sm.at[0]), smem_u32(sm.dyt[0]), false);
+      umma_split<64, 64, 0, 1>(tmem_addr(tm, 0, 128), smem_u32(sm.kt[0]), smem_u32(sm.dst[0]), true);
       // dS~0 = r~^T dy                              (upper halves, columns 128..191)
       umma_split<64, 64, 1, 1>(tmem_addr(tm, 16, 128), smem_u32(sm.rt[0]), smem_u32(sm.dyt[0]), false);
       umma_commit(&sm.bar_2);
     }
-    ok = mbar_wait(&sm.bar_2, par, status, 412) && ok;
+    ok = mbar_wait(&sm.bar_2a, par, status, 416) && ok;
     tc_fence_after();
-    W6C_STAMP(39);
+    const int c0 = 32 * hsel;
+    float o[32], rd[32], rs[32];
     if (ok) {
-      const int c0 = 32 * hsel;
-      {
-        // dv row of token srow (lower halves) / dS~0 row k = srow (upper halves)
-        uint32_t r2[32];
-        tmem_ld32(tm_c2, r2);
-        tmem_ld_wait();
-        if (!lower) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) dsreg[j] = e0 * (__uint_as_float(r2[j]) + dsreg[j]);   // dS0 = e^{gref}(r~^T dy + dS^)
-        } else {
-#pragma unroll
-          for (int j4 = 0; j4 < 32; j4 += 4)
-            *reinterpret_cast<float4*>(&stage_dv[srow * NROW + c0 + j4]) =
-                make_float4(__uint_as_float(r2[j4]), __uint_as_float(r2[j4 + 1]), __uint_as_float(r2[j4 + 2]),
-                            __uint_as_float(r2[j4 + 3]));
-        }
-      }
-      // r1: the part of dk~ from inside the chunk, stril(dA)^T r~ (lower halves) / dr~ (upper halves), row of token
-      // srow; rx: the state part of dk~, X = v dS^^T (lower halves only)
+      // r1: the part of dk~ from inside the chunk (lower halves) / dr~ (upper halves), row of token srow; rx: the
+      // state part of dk~ (lower halves only)
       uint32_t r1[32], rx[32];
       tmem_ld32(tm_c1, r1);
       tmem_ld32(tm_c3, rx);
@@ -770,7 +757,6 @@ wkv6c_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
         const float4 gs4 = *reinterpret_cast<const float4*>(&sm.gs[srow * NROW + cc]);
         const float4 gg4 = *reinterpret_cast<const float4*>(&sm.gg[srow * NROW + cc]);
         const float gsv[4] = {gs4.x, gs4.y, gs4.z, gs4.w}, ggv[4] = {gg4.x, gg4.y, gg4.z, gg4.w};
-        float o[4], rd[4], rs[4];
 #pragma unroll
         for (int m = 0; m < 4; ++m) {
           const int j = j4 + m;
@@ -778,18 +764,39 @@ wkv6c_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
           const float tt = th[j] + tl[j];                            // k~ (lower) / r~ (upper)
           const float x = __uint_as_float(r1[j]);
           const float xs = lower ? __uint_as_float(rx[j]) : 0.f;
-          o[m] = (x + xs) * ex2(lower ? -d1 : d1 - ggv[m]);          // dk = dk~ e^{gref-gi},  dr = dr~ e^{ge-gref}
-          rd[m] = lower ? -x * tt : x * tt;                          // -(stril(dA)^T r~) k~,  dge = dr~ r~
-          rs[m] = xs * tt;                                           // X k~
+          o[j] = (x + xs) * ex2(lower ? -d1 : d1 - ggv[m]);          // dk = dk~ e^{gref-gi},  dr = dr~ e^{ge-gref}
+          rd[j] = lower ? -x * tt : x * tt;                          // -(stril(dA)^T r~) k~,  dge = dr~ r~
+          rs[j] = xs * tt;                                           // X k~
         }
-        if (lower) {
-          *reinterpret_cast<float4*>(&stage_dk[srow * NROW + cc]) = make_float4(o[0], o[1], o[2], o[3]);
-          *reinterpret_cast<float4*>(&red_i[srow * NROW + cc]) = make_float4(rd[0], rd[1], rd[2], rd[3]);
-          *reinterpret_cast<float4*>(&red_x[srow * NROW + cc]) = make_float4(rs[0], rs[1], rs[2], rs[3]);
-        } else {
-          *reinterpret_cast<float4*>(&stage_dr[srow * NROW + cc]) = make_float4(o[0], o[1], o[2], o[3]);
-          *reinterpret_cast<float4*>(&sm.red_e[srow * NROW + cc]) = make_float4(rd[0], rd[1], rd[2], rd[3]);
-        }
+      }
+    }
+    ok = mbar_wait(&sm.bar_2, par, status, 412) && ok;
+    tc_fence_after();
+    W6C_STAMP(39);
+    if (ok) {
+      float* so = lower ? stage_dk : stage_dr;
+      float* sd = lower ? red_i : sm.red_e;
+#pragma unroll
+      for (int j4 = 0; j4 < 32; j4 += 4) {
+        const int cc = c0 + j4;
+        *reinterpret_cast<float4*>(&so[srow * NROW + cc]) = make_float4(o[j4], o[j4 + 1], o[j4 + 2], o[j4 + 3]);
+        *reinterpret_cast<float4*>(&sd[srow * NROW + cc]) = make_float4(rd[j4], rd[j4 + 1], rd[j4 + 2], rd[j4 + 3]);
+        if (lower)
+          *reinterpret_cast<float4*>(&red_x[srow * NROW + cc]) = make_float4(rs[j4], rs[j4 + 1], rs[j4 + 2], rs[j4 + 3]);
+      }
+      // dv row of token srow (lower halves) / dS~0 row k = srow (upper halves)
+      uint32_t r2[32];
+      tmem_ld32(tm_c2, r2);
+      tmem_ld_wait();
+      if (!lower) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) dsreg[j] = e0 * (__uint_as_float(r2[j]) + dsreg[j]);   // dS0 = e^{gref}(r~^T dy + dS^)
+      } else {
+#pragma unroll
+        for (int j4 = 0; j4 < 32; j4 += 4)
+          *reinterpret_cast<float4*>(&stage_dv[srow * NROW + c0 + j4]) =
+              make_float4(__uint_as_float(r2[j4]), __uint_as_float(r2[j4 + 1]), __uint_as_float(r2[j4 + 2]),
+                          __uint_as_float(r2[j4 + 3]));
       }
     }
     tc_fence_before();
