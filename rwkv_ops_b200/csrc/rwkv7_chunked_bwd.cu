@@ -823,7 +823,28 @@ int launch_rwkv7_chunked_bwd(const void* r, const void* w, const void* k, const 
                                                        status));
   }
   e = check_launch();
-  if (e || !(phases & PHASE_FINISH)) return e;
+  if (e) return e;
+  // Units the forward marked (decay beyond the range of the scaled operands, or a very short sequence): their
+  // gradients come from the float32 recurrence instead.  Its state checkpoints (16 KB per 8 tokens = 128 KB per
+  // chunk) go into the unit's own tile region of the workspace (144 KB per chunk), whose contents are void for
+  // such a unit.
+  auto exact_units = [&]() -> int {
+    const long long unit_floats = (long long)NT * ALL_TILES * TILE_BYTES / (long long)sizeof(float);
+    float* ckpt = reinterpret_cast<float*>(ws.tiles);
+    const UnitSel sel{ws.flags, seq_start, seq_len, unit_floats};
+    const int tt = seq_start ? T_total : 0;
+    int e2 = launch_rwkv7_rec_fwd(r, w, k, v, a, b, h0, n_state, nullptr, nullptr, ckpt, R7_CKPT, B, Tn, H,
+                                  RWKVB200_BF16, head_first, st, &sel, tt);
+    if (e2) return e2;
+    return launch_rwkv7_rec_bwd(r, w, k, v, a, b, d_o, d_ht, ckpt, dr, dw, dk, dv, da, db, d_h0, B, Tn, H,
+                                RWKVB200_BF16, head_first, st, &sel, tt);
+  };
+  if (!(phases & PHASE_FINISH)) {
+    // a scan-only call hands the gradient of the initial state to its caller (who passes it to the rank on the
+    // left) before the token gradients exist: the marked units' share of it has to be exact already
+    if ((phases & PHASE_SCAN) && !fused) return exact_units();
+    return e;
+  }
   {
     const int smem = (int)sizeof(FinalSmem) + 1024;
     ProfScope prof("r7c_bwd_final_kernel", st);
@@ -853,21 +874,8 @@ int launch_rwkv7_chunked_bwd(const void* r, const void* w, const void* k, const 
   }
   e = check_launch();
   if (e) return e;
-  // Units the forward marked (decay beyond the range of the scaled operands): their gradients come from the
-  // float32 recurrence instead.  Its state checkpoints (16 KB per 8 tokens = 128 KB per chunk) go into the
-  // unit's own tile region of the workspace (144 KB per chunk), whose contents are void for such a unit.
-  {
-    const long long unit_floats = (long long)NT * ALL_TILES * TILE_BYTES / (long long)sizeof(float);
-    float* ckpt = reinterpret_cast<float*>(ws.tiles);
-    const UnitSel sel{ws.flags, seq_start, seq_len, unit_floats};
-    const int tt = seq_start ? T_total : 0;
-    e = launch_rwkv7_rec_fwd(r, w, k, v, a, b, h0, n_state, nullptr, nullptr, ckpt, R7_CKPT, B, Tn, H, RWKVB200_BF16,
-                             head_first, st, &sel, tt);
-    if (e) return e;
-    e = launch_rwkv7_rec_bwd(r, w, k, v, a, b, d_o, d_ht, ckpt, dr, dw, dk, dv, da, db, d_h0, B, Tn, H,
-                             RWKVB200_BF16, head_first, st, &sel, tt);
-  }
-  return e;
+  return exact_units();
 }
+
 
 }  // namespace rwkvb200

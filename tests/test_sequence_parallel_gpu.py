@@ -103,3 +103,39 @@ def test_phases_on_one_gpu_chain_two_halves():
     torch.cuda.synchronize()
     from rwkv_ops_b200 import _lib
     assert _lib.load().rwkvb200_device_status(1) == 0
+
+
+def test_phases_with_a_unit_beyond_the_decay_range():
+    """One head of the right half decays faster than the tensor-core kernels' range: its outputs and gradients
+    come from the recurrence, and so must its share of the state gradient that the right rank hands to the left
+    one after its scan phase (before its token gradients exist)."""
+    from oracle import generalized_delta_rule as oracle_gdr
+    from rwkv_ops_b200.sequence_parallel import ChunkedPhasedOp
+    B, T, H = 2, 256, 3
+    d = rwkv7_inputs(B, T, H, dtype=torch.bfloat16, seed=47, with_state=True, with_grads=True)
+    w = d["w"].float()
+    w[1, T // 2:, 2] = 1.0      # exp(1) = 2.7 per token: 87 over half a chunk, beyond the limit of 60
+    d["w"] = w.bfloat16()
+    full = {n: d[n].float().clone().requires_grad_(True) for n in "rwkvab"}
+    h0 = d["initial_state"].clone().requires_grad_(True)
+    o_ref, s_ref = oracle_gdr(*[full[n] for n in "rwkvab"], initial_state=h0)
+    ((o_ref * d["d_out"].float()).sum() + (s_ref * d["d_state"]).sum()).backward()
+    op = ChunkedPhasedOp()
+    half = T // 2
+    tok = [[d[n][:, i * half:(i + 1) * half].cuda().contiguous() for n in "rwkvab"] for i in range(2)]
+    st = [op.prepare_fwd(*tok[i], False) for i in range(2)]
+    o0, h_mid = op.scan_fwd(st[0], d["initial_state"].cuda())
+    o1, h_end = op.scan_fwd(st[1], h_mid)
+    assert rel_l2(torch.cat([o0, o1], 1), o_ref) < 2e-2 and rel_l2(h_end, s_ref) < 2e-2
+    for i in range(2):
+        op.prepare_bwd(st[i], d["d_out"][:, i * half:(i + 1) * half].cuda())
+    d_mid = op.scan_bwd(st[1], d["d_state"].cuda()).clone()
+    d_h0 = op.scan_bwd(st[0], d_mid).clone()
+    grads = [op.finish_bwd(st[i]) for i in range(2)]
+    for j, n in enumerate("rwkvab"):
+        got = torch.cat([grads[0][j], grads[1][j]], 1)
+        assert torch.isfinite(got.float()).all(), n
+        assert rel_l2(got, full[n].grad) < 2e-2, n
+        # the left half alone: it sees the marked unit only through d_mid
+        assert rel_l2(grads[0][j][1, :, 2], full[n].grad[1, :half, 2]) < 2e-2, n
+    assert rel_l2(d_h0, h0.grad) < 2e-2
