@@ -72,7 +72,9 @@ enum {
    * arguments.  Forward: PREPARE does everything that does not depend on the initial state (h0, o and ht
    * are not touched and o may be NULL), SCAN walks the state through the chunks and writes o and ht.
    * Backward: PREPARE does what does not depend on d_ht, SCAN carries the state gradient back through the
-   * chunks and writes d_h0, FINISH writes the six token gradients.  A caller that splits one sequence over
+   * chunks and writes d_h0, FINISH writes the six token gradients (pass the same gradient buffers to every
+   * part: for units beyond the decay range SCAN already runs the recurrence, which writes into them, so that
+   * their share of d_h0 is exact when SCAN returns).  A caller that splits one sequence over
    * several GPUs runs PREPARE / FINISH on all of them at once and only the SCAN parts one GPU after the
    * other, passing ht (forward) and d_h0 (backward) to the neighbour.  No counterpart in the reference,
    * which has no multi-device mode (README.md:179). */
