@@ -58,6 +58,25 @@ TRAFFIC_PER_CHUNK_HEAD = {"r7c_intra_fwd_kernel": 112.1e3, "r7c_scan_fwd_kernel"
                           "r7c_bwd_final_kernel": 150.9e3}
 TRAFFIC_SOURCE = ("ncu dram__bytes_read.sum + dram__bytes_write.sum per chunk-head on B=2 T=4096 H=16 "
                   "(a full-size launch is too large to capture), scaled by the chunk-heads of this launch")
+
+
+def cores_near_gpu(dev):
+    """The CPU cores NVML reports as local to CUDA device `dev` (its NUMA node), restricted to the cores this
+    process may run on; None when that cannot be found out.  Reads only."""
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        p = torch.cuda.get_device_properties(dev)
+        bus = f"{p.pci_domain_id:08x}:{p.pci_bus_id:02x}:{p.pci_device_id:02x}.0"
+        h = pynvml.nvmlDeviceGetHandleByPciBusId(bus.encode())
+        words = pynvml.nvmlDeviceGetCpuAffinity(h, (os.cpu_count() + 63) // 64)
+        cpus = {64 * i + b for i, wd in enumerate(words) for b in range(64) if (int(wd) >> b) & 1}
+        cpus &= os.sched_getaffinity(0)
+        return cpus if len(cpus) >= 2 else None
+    except Exception:      # noqa: BLE001  (no NVML, no such call, a container that hides the topology)
+        return None
+
+
 CPU_SAMPLE_T = 256     # tokens per sequence of the cpu_baseline sample
 REF_STEP_T = 128       # tokens per sequence of one --impl reference step
 
@@ -342,7 +361,17 @@ def run_ours(args, wl):
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+        # the NCCL backend announces its version on stdout when its first communicator is made; stdout is for the
+        # one JSON line, so that goes to stderr
+        sys.stdout.flush()
+        saved_stdout = os.dup(1)
+        os.dup2(2, 1)
+        try:
+            dist.init_process_group("nccl", device_id=dev)
+            dist.barrier()
+        finally:
+            os.dup2(saved_stdout, 1)
+            os.close(saved_stdout)
     _lib.load()
 
     B, T, H = wl["B"], wl["T"], wl["H"]
@@ -462,6 +491,12 @@ def run_ours(args, wl):
     # pinned host memory.  Steps are independent, so they are software-pipelined over three streams:
     # the upload of step i+1 and the download of step i-1 overlap the compute of step i (PCIe is
     # full duplex); two sets of device and host buffers alternate.
+    # The pinned buffers are allocated (and first touched) while the process is bound to the cores of the GPU's
+    # own NUMA node, so that with several ranks on a multi-socket host no rank copies across sockets.
+    near = cores_near_gpu(dev)
+    before = os.sched_getaffinity(0)
+    if near:
+        os.sched_setaffinity(0, near)
     host_in = {n: d[n].detach().to("cpu").pin_memory() for n in names}
     host_in["d_out"] = d_out.to("cpu").pin_memory()
     host_in["d_state"] = d_state.to("cpu").pin_memory()
@@ -478,6 +513,8 @@ def run_ours(args, wl):
         return ho
 
     host_out = [host_out_set(), host_out_set()]
+    if near:
+        os.sched_setaffinity(0, before)
     dev_in = [{n: torch.empty_like(t, device=dev) for n, t in host_in.items()} for _ in range(2)]
     h2d = sum(t.numel() * t.element_size() for t in host_in.values())
     d2h = sum(t.numel() * t.element_size() for t in host_out[0].values())
@@ -569,6 +606,8 @@ def run_ours(args, wl):
             "e2e": {"value": e2e_val, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": e2e_ms, "steps": e2e_steps,
                     "pipeline": "upload / compute / download of consecutive steps overlap on three streams",
+                    "host_buffers": (f"pinned while bound to the {len(near)} cores NVML reports as local to the GPU"
+                                     if near else "pinned where the process ran (no NVML core affinity found)"),
                     "copy_ceiling": {"ms_per_step": copy_ms, "value": world * B * T / (copy_ms / 1e3),
                                      "frac_of_ceiling": copy_ms / e2e_ms,
                                      "what": "the same pinned host buffers copied up and down, no compute"}},
