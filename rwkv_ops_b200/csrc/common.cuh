@@ -165,7 +165,7 @@ int launch_wkv6_bwd_coarse(const void* r, const void* k, const void* v, const vo
                            void* dr, void* dk, void* dv, void* dw, float* du_partial, float* d_s0,
                            int B, int Tn, int H, int dtype, cudaStream_t st, const UnitSel* sel);
 int launch_wkv6_du_reduce_mixed(const float* part_chunked, const float* part_rec, const int* flags, float* du,
-                                int B, int H, cudaStream_t st);
+                                int B, int H, cudaStream_t st, int rows = 1);
 int launch_wkv6_bwd(const void* r, const void* k, const void* v, const void* w, const float* u,
                     const void* d_y, const float* d_sT, const float* ckpt,
                     void* dr, void* dk, void* dv, void* dw, float* du_partial, float* du, float* d_s0,

@@ -439,11 +439,12 @@ wkv6_du_reduce_kernel(const float* __restrict__ du_partial, float* __restrict__ 
   du[hi * n + kc] = s;
 }
 
-// The same for the chunked path with its recurrent fallback: a unit contributes one row of `part_chunked`
-// [B*H][64], or, when the forward marked it (flags), its four rows of `part_rec` [B*H][4][64].
+// The same for the chunked path with its recurrent fallback: a unit contributes `rows` rows of `part_chunked`
+// [rows][B*H][64] (two when its chunks were worked on as two halves), or, when the forward marked it (flags),
+// its four rows of `part_rec` [B*H][4][64].
 __global__ void __launch_bounds__(64)
 wkv6_du_reduce_mixed_kernel(const float* __restrict__ part_chunked, const float* __restrict__ part_rec,
-                            const int* __restrict__ flags, float* __restrict__ du, int B, int H) {
+                            const int* __restrict__ flags, float* __restrict__ du, int B, int H, int rows) {
   constexpr int NQ = HS / VS;
   const int hi = blockIdx.x, kc = threadIdx.x;
   float s = 0.f;
@@ -452,7 +453,7 @@ wkv6_du_reduce_mixed_kernel(const float* __restrict__ part_chunked, const float*
     if (flags[unit]) {
       for (int q = 0; q < NQ; ++q) s += part_rec[(unit * NQ + q) * HS + kc];
     } else {
-      s += part_chunked[unit * HS + kc];
+      for (int q = 0; q < rows; ++q) s += part_chunked[((long long)q * B * H + unit) * HS + kc];
     }
   }
   du[hi * HS + kc] = s;
@@ -526,9 +527,9 @@ int launch_wkv6_bwd_coarse(const void* r, const void* k, const void* v, const vo
 }
 
 int launch_wkv6_du_reduce_mixed(const float* part_chunked, const float* part_rec, const int* flags, float* du,
-                                int B, int H, cudaStream_t st) {
+                                int B, int H, cudaStream_t st, int rows) {
   ProfScope prof("wkv6_du_reduce_kernel", st);
-  wkv6_du_reduce_mixed_kernel<<<H, 64, 0, st>>>(part_chunked, part_rec, flags, du, B, H);
+  wkv6_du_reduce_mixed_kernel<<<H, 64, 0, st>>>(part_chunked, part_rec, flags, du, B, H, rows);
   return check_launch();
 }
 

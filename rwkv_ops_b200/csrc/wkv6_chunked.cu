@@ -466,6 +466,7 @@ struct BwdSmem {
   alignas(128) unsigned char raw_dy[L * 64 * 4];
   uint64_t bar_1, bar_2, bar_2a, bar_in_a, bar_in_b, bar_in_c;
   uint32_t tmem_base;
+  int handoff_ok;
 };
 static_assert(sizeof(BwdSmem) + 1024 <= 227 * 1024, "backward shared memory");
 
@@ -477,10 +478,11 @@ wkv6c_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
                  T* __restrict__ dw, float* __restrict__ du_partial, float* __restrict__ d_s0,
                  const __grid_constant__ CUtensorMap tmap_r, const __grid_constant__ CUtensorMap tmap_k,
                  const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_w,
-                 const __grid_constant__ CUtensorMap tmap_dy, int Tn_dense, int H, Seqs seqs, int* status,
+                 const __grid_constant__ CUtensorMap tmap_dy, int Tn_dense, int H, Seqs seqs, int n_units,
+                 int split, float* __restrict__ handoff, int* __restrict__ handoff_flags, int* status,
                  long long* dbg) {
 #ifdef RWKVB200_DEVTOOLS
-#define W6C_STAMP(n) do { if (dbg && tid == 0 && blockIdx.x == gridDim.x / 2 && c == NT - 2) dbg[n] = clock64(); } while (0)
+#define W6C_STAMP(n) do { if (dbg && tid == 0 && item == gridDim.x / 2 && c == NT - 2) dbg[n] = clock64(); } while (0)
 #else
 #define W6C_STAMP(n) do {} while (0)
 #endif
@@ -488,18 +490,10 @@ wkv6c_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
   BwdSmem& sm = *reinterpret_cast<BwdSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int wq = warp & 3, hsel = warp >> 2;
-  const int unit = blockIdx.x, bi = unit / H, hi = unit % H;
   const long long tstride = (long long)H * HS;
-  const int Tn = PACKED ? seqs.len[bi] : Tn_dense;
-  const int tok0 = PACKED ? seqs.start[bi] : 0;
-  const int brow = PACKED ? 0 : bi;
-  const long long base = (((long long)brow * Tn_dense + tok0) * H + hi) * HS;
-  const int NT = (Tn + L - 1) / L;
-  const size_t nts = PACKED ? (size_t)seqs.nts : (size_t)(NT + 1);
   const int srow = 16 * wq + (lane & 15);
   const bool lower = lane < 16;
   const int c4 = tid & 15;
-  const float4 u4 = *reinterpret_cast<const float4*>(u + hi * HS + 4 * c4);
   // fp32 arrays that overlay the dead tiles after MMA batch 2
   float* stage_dr = reinterpret_cast<float*>(sm.vt[0]);
   float* stage_dk = stage_dr + L * NROW;
@@ -513,7 +507,6 @@ wkv6c_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
     mbar_init(&sm.bar_in_a, 1); mbar_init(&sm.bar_in_b, 1); mbar_init(&sm.bar_in_c, 1);
     fence_mbar_init();
   }
-  if (tid < 64) sm.du_s[tid] = 0.f;
   if (warp == 0) tmem_alloc(&sm.tmem_base, 256);
   tc_fence_before();
   __syncthreads();
@@ -524,11 +517,70 @@ wkv6c_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
   const uint32_t tm_c2 = tmem_addr(tm, 32 * wq, 128 + 32 * hsel);    // dv (lower), dS~0 (upper)
   const uint32_t tm_c3 = tmem_addr(tm, 32 * wq, 192 + 32 * hsel);    // X = v dS^^T (lower): the state part of dk~
 
+  constexpr uint32_t RAW_BYTES = 64 * 64 * (uint32_t)sizeof(T);
+  const T* raw_w = reinterpret_cast<const T*>(sm.raw_w);
+  const T* raw_dy = reinterpret_cast<const T*>(sm.raw_dy);
+  const T* raw_v = reinterpret_cast<const T*>(sm.red_e);
+  const T* raw_r = reinterpret_cast<const T*>(sm.rt[0]);
+  const T* raw_k = reinterpret_cast<const T*>(sm.kt[0]);
+
+  // Work items.  Without `split` an item is a (batch, head) unit and the grid has one CTA per unit.  With it
+  // (more units than SMs) every unit is two items, the later half of its chunks and the earlier half, and the
+  // grid is one persistent CTA per SM that takes items blockIdx.x, blockIdx.x + gridDim.x, ...: all later halves
+  // come first in that order, so a unit's earlier half is taken at least three items after its later half, and
+  // the state gradient travels between them through `handoff` (a flag per unit says it is there).  Halves of
+  // units instead of whole units even out the last round of CTAs (512 units on 148 SMs: 3.5 unit times instead
+  // of 4).
+  const int n_items = split ? 2 * n_units : n_units;
+  bool ok = true;
+  uint32_t n_done = 0;      // chunks this CTA has worked on: every barrier completes once per chunk
+  for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+  const int unit = split ? item % n_units : item;
+  const bool early_half = split && item >= n_units;
+  const int bi = unit / H, hi = unit % H;
+  const int Tn = PACKED ? seqs.len[bi] : Tn_dense;
+  const int tok0 = PACKED ? seqs.start[bi] : 0;
+  const int brow = PACKED ? 0 : bi;
+  const long long base = (((long long)brow * Tn_dense + tok0) * H + hi) * HS;
+  const int NT = (Tn + L - 1) / L;
+  const size_t nts = PACKED ? (size_t)seqs.nts : (size_t)(NT + 1);
+  const int mid = split ? NT / 2 : 0;                 // the later half is chunks mid .. NT-1, the earlier 0 .. mid-1
+  const int c_hi = early_half ? mid - 1 : NT - 1;     // first chunk of this item (chunks go in reverse)
+  const int c_lo = early_half ? 0 : mid;              // last chunk of this item
+  if (c_hi < c_lo) {                                  // an earlier half with nothing in it (a one-chunk sequence)
+    if (tid < 64) du_partial[(size_t)item * HS + tid] = 0.f;
+    continue;
+  }
+  const float4 u4 = *reinterpret_cast<const float4*>(u + hi * HS + 4 * c4);
+  if (tid < 64) sm.du_s[tid] = 0.f;
+
   // gradient of the state after the current chunk: row k = srow (upper lane halves), 32 columns
   float dsreg[32];
 #pragma unroll
   for (int j = 0; j < 32; ++j) dsreg[j] = 0.f;
-  if (!lower && d_sT) {
+  if (early_half) {
+    // wait for the later half of this unit (taken at least three items ago by a CTA that is resident): bounded
+    if (tid == 0) {
+      uint32_t polls = 0;
+      int seen = 0;
+      while (true) {
+        asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(seen) : "l"(handoff_flags + unit) : "memory");
+        if (seen || ++polls > (WAIT_LIMIT << 2)) break;
+        __nanosleep(200);
+      }
+      if (!seen) { atomicExch(status, 417); sm.handoff_ok = 0; } else { sm.handoff_ok = 1; }
+    }
+    __syncthreads();
+    ok = sm.handoff_ok != 0;
+    if (!lower && ok) {
+      const float* S = handoff + (((size_t)unit * HS) + srow) * HS + 32 * hsel;
+#pragma unroll
+      for (int j = 0; j < 32; j += 4) {
+        const float4 f = __ldcg(reinterpret_cast<const float4*>(S + j));
+        dsreg[j] = f.x; dsreg[j + 1] = f.y; dsreg[j + 2] = f.z; dsreg[j + 3] = f.w;
+      }
+    }
+  } else if (!lower && d_sT) {
     const float* S = d_sT + (((size_t)unit * HS) + srow) * HS + 32 * hsel;
 #pragma unroll
     for (int j = 0; j < 32; j += 4) {
@@ -538,12 +590,6 @@ wkv6c_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
   }
   float4 du_acc = make_float4(0.f, 0.f, 0.f, 0.f);
 
-  constexpr uint32_t RAW_BYTES = 64 * 64 * (uint32_t)sizeof(T);
-  const T* raw_w = reinterpret_cast<const T*>(sm.raw_w);
-  const T* raw_dy = reinterpret_cast<const T*>(sm.raw_dy);
-  const T* raw_v = reinterpret_cast<const T*>(sm.red_e);
-  const T* raw_r = reinterpret_cast<const T*>(sm.rt[0]);
-  const T* raw_k = reinterpret_cast<const T*>(sm.kt[0]);
   auto load_in_a = [&](int c) {      // tid 0; rows past the end of the sequence arrive as zeros
     mbar_expect_tx(&sm.bar_in_a, 2 * RAW_BYTES);
     tma_load_4d(sm.raw_w, &tmap_w, &sm.bar_in_a, 0, tok0 + c * L, hi, brow);
@@ -558,12 +604,11 @@ wkv6c_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
     mbar_expect_tx(&sm.bar_in_c, RAW_BYTES);
     tma_load_4d(sm.red_e, &tmap_v, &sm.bar_in_c, 0, tok0 + c * L, hi, brow);
   };
-  if (tid == 0 && NT > 0) { load_in_a(NT - 1); load_in_c(NT - 1); load_in_b(NT - 1); }
+  if (tid == 0 && ok) { load_in_a(c_hi); load_in_c(c_hi); load_in_b(c_hi); }
 
-  bool ok = true;
-  for (int c = NT - 1; c >= 0 && ok; --c) {
+  for (int c = c_hi; c >= c_lo && ok; --c, ++n_done) {
     const int t0 = c * L;
-    const uint32_t par = (NT - 1 - c) & 1;
+    const uint32_t par = n_done & 1;
     W6C_STAMP(32);
     // ---- r and k are read at pass RK and stay in registers until the u-term gradients at the end of the chunk
     float4 gw[4], rr4[4], kk4[4];
@@ -627,7 +672,7 @@ wkv6c_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
       if (c4 == 0) sm.dds[row] = dd;
     }
     __syncthreads();
-    if (tid == 0 && ok && c > 0) load_in_a(c - 1);      // every thread has taken its w and dy elements
+    if (tid == 0 && ok && c > c_lo) load_in_a(c - 1);      // every thread has taken its w and dy elements
 #pragma unroll
     for (int n = 0; n < 4; ++n) {
       const int e = tid + 256 * n, row = e >> 4;
@@ -652,7 +697,7 @@ wkv6c_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
 #pragma unroll
       for (int j = 0; j < 8; ++j) srow4[j] = *reinterpret_cast<const float4*>(Srow + 4 * j);
     }
-    if (tid == 0 && c > 0) {   // bring the previous chunk's rows into L2 while this chunk is in its MMA phases
+    if (tid == 0 && c > c_lo) {   // bring the previous chunk's rows into L2 while this chunk is in its MMA phases
       tma_prefetch_4d(&tmap_w, 0, tok0 + t0 - L, hi, brow);
       tma_prefetch_4d(&tmap_dy, 0, tok0 + t0 - L, hi, brow);
       tma_prefetch_4d(&tmap_v, 0, tok0 + t0 - L, hi, brow);
@@ -801,7 +846,7 @@ wkv6c_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
     }
     tc_fence_before();
     ok = __syncthreads_and(ok);
-    if (tid == 0 && ok && c > 0) load_in_b(c - 1);      // the epilogue above was the last reader of rt / kt
+    if (tid == 0 && ok && c > c_lo) load_in_b(c - 1);      // the epilogue above was the last reader of rt / kt
     W6C_STAMP(40);
     // ---- decay gradient, with I_i = -(stril(dA)^T r~)_i k~_i and X_i k~_i the two parts of dgi_i = -dk~_i k~_i:
     // dg_j = sum_{i>j} (dge_i + I_i) + I_j + sum_v dS^ S~0 + sum_{i<j} X_i k~_i;   dw = dg g.
@@ -835,7 +880,7 @@ wkv6c_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
       }
     }
     __syncthreads();
-    if (tid == 0 && ok && c > 0) load_in_c(c - 1);      // red_e has been read for the last time
+    if (tid == 0 && ok && c > c_lo) load_in_c(c - 1);      // red_e has been read for the last time
     W6C_STAMP(41);
     // ---- outputs, coalesced, plus the u-term parts of dr, dk and du
 #pragma unroll
@@ -861,17 +906,27 @@ wkv6c_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
     W6C_STAMP(42);
   }
 #undef W6C_STAMP
-  // ---- du of this (batch, head) and the gradient of its initial state
+  // ---- du of this item and the gradient of the state at its first token: the initial state's, or what the
+  // earlier half of the unit starts from
   atomicAdd(&sm.du_s[4 * c4], du_acc.x); atomicAdd(&sm.du_s[4 * c4 + 1], du_acc.y);
   atomicAdd(&sm.du_s[4 * c4 + 2], du_acc.z); atomicAdd(&sm.du_s[4 * c4 + 3], du_acc.w);
   __syncthreads();
-  if (tid < 64) du_partial[(size_t)unit * HS + tid] = sm.du_s[tid];
-  if (!lower && d_s0 && ok) {
-    float* dst = d_s0 + (((size_t)unit * HS) + srow) * HS + 32 * hsel;
+  if (tid < 64) du_partial[(size_t)item * HS + tid] = sm.du_s[tid];
+  const bool hand_on = split && !early_half && mid > 0;
+  float* dS_out = hand_on ? handoff : d_s0;
+  if (!lower && dS_out && ok) {
+    float* dst = dS_out + (((size_t)unit * HS) + srow) * HS + 32 * hsel;
 #pragma unroll
     for (int j = 0; j < 32; j += 4)
       *reinterpret_cast<float4*>(dst + j) = make_float4(dsreg[j], dsreg[j + 1], dsreg[j + 2], dsreg[j + 3]);
   }
+  if (hand_on) {
+    __threadfence();
+    __syncthreads();
+    if (tid == 0 && ok) asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(handoff_flags + unit), "r"(1) : "memory");
+  }
+  __syncthreads();      // du_s and the tiles are the next item's
+  }   // items
   tc_fence_before();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tm, 256);
@@ -921,10 +976,11 @@ int launch_wkv6_chunked_fwd(const void* r, const void* k, const void* v, const v
 
 namespace rwkvb200 {
 
-// workspace of the backward: [chunk-boundary states | du rows, one per unit | du rows of the recurrent
-// fallback, four per unit | unit flags]; the forward fills the states and the flags
+// workspace of the backward: [chunk-boundary states | du rows, two per unit | du rows of the recurrent
+// fallback, four per unit | unit flags | state gradients handed from the later to the earlier half of a unit |
+// their flags]; the forward fills the states and the unit flags
 namespace {
-struct W6Workspace { float* states; float* du_partial; float* du_partial_rec; int* flags; };
+struct W6Workspace { float* states; float* du_partial; float* du_partial_rec; int* flags; float* handoff; int* hflags; };
 inline size_t a256(size_t x) { return (x + 255) & ~size_t(255); }
 inline size_t w6_states_bytes(int B, int Tn, int H) {
   const size_t nt = (size_t)(Tn + w6c::L - 1) / w6c::L;
@@ -936,10 +992,14 @@ inline W6Workspace w6_carve(void* workspace, int B, int Tn, int H) {
   w.states = reinterpret_cast<float*>(p);
   p += w6_states_bytes(B, Tn, H);
   w.du_partial = reinterpret_cast<float*>(p);
-  p += a256((size_t)B * H * HS * sizeof(float));
+  p += a256((size_t)B * H * 2 * HS * sizeof(float));
   w.du_partial_rec = reinterpret_cast<float*>(p);
   p += a256((size_t)B * H * 4 * HS * sizeof(float));
   w.flags = reinterpret_cast<int*>(p);
+  p += a256((size_t)B * H * sizeof(int));
+  w.handoff = reinterpret_cast<float*>(p);
+  p += a256((size_t)B * H * HS * HS * sizeof(float));
+  w.hflags = reinterpret_cast<int*>(p);
   return w;
 }
 }  // namespace
@@ -947,8 +1007,9 @@ inline W6Workspace w6_carve(void* workspace, int B, int Tn, int H) {
 size_t wkv6_chunked_flags_bytes(int B, int H) { return a256((size_t)B * H * sizeof(int)); }
 
 size_t wkv6_chunked_bwd_workspace_bytes(int B, int Tn, int H) {
-  return w6_states_bytes(B, Tn, H) + a256((size_t)B * H * HS * sizeof(float)) +
-         a256((size_t)B * H * 4 * HS * sizeof(float)) + wkv6_chunked_flags_bytes(B, H);
+  return w6_states_bytes(B, Tn, H) + a256((size_t)B * H * 2 * HS * sizeof(float)) +
+         a256((size_t)B * H * 4 * HS * sizeof(float)) + wkv6_chunked_flags_bytes(B, H) +
+         a256((size_t)B * H * HS * HS * sizeof(float)) + wkv6_chunked_flags_bytes(B, H);
 }
 
 int* wkv6_chunked_workspace_flags(void* workspace, int B, int Tn, int H) { return w6_carve(workspace, B, Tn, H).flags; }
@@ -974,6 +1035,7 @@ int launch_wkv6_chunked_bwd(const void* r, const void* k, const void* v, const v
   int* status = device_status_ptr();
   if (!status) { last_cuda_error_slot() = 99999; return RWKVB200_E_CUDA; }
   const int smem = (int)sizeof(BwdSmem) + 1024;
+  bool split = false;
   {
     const int esz = dtype == RWKVB200_F32 ? 4 : 2;
     CUtensorMap tm_r, tm_k, tm_v, tm_w, tm_dy;
@@ -983,14 +1045,24 @@ int launch_wkv6_chunked_bwd(const void* r, const void* k, const void* v, const v
     if (!e) e = make_row_tensor_map(&tm_w, w, mapB, mapT, H, esz);
     if (!e) e = make_row_tensor_map(&tm_dy, d_y, mapB, mapT, H, esz);
     if (e) return e;
+    // more units than SMs: every unit as two half-length items on one persistent CTA per SM, which evens out
+    // the last round (see the kernel); else one CTA per unit
+    int dev = 0, sms = 0;
+    if (cuda_ok(cudaGetDevice(&dev)) || cuda_ok(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)))
+      return RWKVB200_E_CUDA;
+    const int n_units = B * H;
+    split = n_units > sms && (Tn + L - 1) / L >= 4;
+    const int grid = split ? sms : n_units;
+    if (split && cuda_ok(cudaMemsetAsync(ws.hflags, 0, (size_t)n_units * sizeof(int), st))) return RWKVB200_E_CUDA;
     ProfScope prof("wkv6c_bwd_kernel", st);
     RWKVB200_DISPATCH_DTYPE(dtype, W6C_DISPATCH_PACKED(
       if (cuda_ok(cudaFuncSetAttribute(wkv6c_bwd_kernel<T, P>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)))
         return RWKVB200_E_CUDA;
-      wkv6c_bwd_kernel<T, P><<<B * H, 256, smem, st>>>((const T*)r, (const T*)k, (const T*)v, (const T*)w, u,
-                                                        (const T*)d_y, d_sT, states, (T*)dr, (T*)dk, (T*)dv, (T*)dw,
-                                                        du_partial, d_s0, tm_r, tm_k, tm_v, tm_w, tm_dy, mapT, H, seqs,
-                                                        status, debug_stamp_buffer())));
+      wkv6c_bwd_kernel<T, P><<<grid, 256, smem, st>>>((const T*)r, (const T*)k, (const T*)v, (const T*)w, u,
+                                                       (const T*)d_y, d_sT, states, (T*)dr, (T*)dk, (T*)dv, (T*)dw,
+                                                       du_partial, d_s0, tm_r, tm_k, tm_v, tm_w, tm_dy, mapT, H, seqs,
+                                                       n_units, split ? 1 : 0, ws.handoff, ws.hflags, status,
+                                                       debug_stamp_buffer())));
   }
   e = check_launch();
   if (e) return e;
@@ -1002,7 +1074,7 @@ int launch_wkv6_chunked_bwd(const void* r, const void* k, const void* v, const v
                                dtype, st, &sel);
     if (e) return e;
   }
-  return launch_wkv6_du_reduce_mixed(du_partial, ws.du_partial_rec, ws.flags, du, B, H, st);
+  return launch_wkv6_du_reduce_mixed(du_partial, ws.du_partial_rec, ws.flags, du, B, H, st, split ? 2 : 1);
 }
 
 }  // namespace rwkvb200

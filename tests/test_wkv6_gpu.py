@@ -212,3 +212,22 @@ def test_very_short_sequences_with_fast_decays(T):
         errs = {"y": rel_l2(y, y_ref), "s": rel_l2(s, s_ref), "ds0": rel_l2(s0.grad, s0r.grad)}
         errs.update({f"d{n}": rel_l2(g[n].grad, ref[n].grad) for n in "rkvwu"})
         assert all(e < 1e-4 for e in errs.values()), (seed, errs)
+
+
+@pytest.mark.parametrize("B,H,T", [(10, 20, 300), (150, 1, 512), (3, 50, 257)])
+def test_more_units_than_sms_backward_in_half_unit_items(B, H, T, monkeypatch):
+    """With more (batch, head) units than SMs the chunked backward works on every unit as two items (the later
+    and the earlier half of its chunks) and hands the state gradient from one to the other: gradients, du over
+    all batch rows and the gradient of a shared initial-state table against the float32 recurrence."""
+    d = wkv6_inputs(B, T, H, dtype=torch.float32, seed=31 + T, device="cuda", n_state=3, with_grads=True)
+    res = {}
+    for algo in ("chunked", "recurrent"):
+        monkeypatch.setenv("RWKV_OPS_B200_WKV6_ALGO", algo)
+        g = {n: d[n].clone().requires_grad_(True) for n in "rkvwu"}
+        s0 = d["init_state"].clone().requires_grad_(True)
+        y, s = ro.RWKV6_OP(64, T)(g["r"], g["k"], g["v"], g["w"], g["u"], with_state=True, init_state=s0,
+                                  state_map=d["state_map"])
+        torch.autograd.backward([y, s], [d["d_y"], d["d_state"]])
+        res[algo] = {"y": y, "s": s, "ds0": s0.grad, **{n: g[n].grad for n in "rkvwu"}}
+    errs = {k_: rel_l2(res["chunked"][k_], res["recurrent"][k_]) for k_ in res["chunked"]}
+    assert max(errs.values()) < 1e-4, errs
