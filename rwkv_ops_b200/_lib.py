@@ -141,7 +141,7 @@ def wkv6_kept_bytes(B: int, T: int, H: int) -> int:
     """Likewise for ``rwkvb200_wkv6_fwd_workspace_bytes(..., ALGO_KEEP)``."""
     nt = (T + 63) // 64
     return (_a256(B * H * (nt + 1) * 64 * 64 * 4) + _a256(B * H * 2 * 64 * 4) + _a256(B * H * 4 * 64 * 4)
-            + _a256(B * H * 4) + _a256(B * H * 64 * 64 * 4) + _a256(B * H * 4))
+            + _a256(B * H * 4) + _a256(B * H * 64 * 64 * 4) + _a256((B * H + 1) * 4))
 
 
 def strerror(code: int) -> str:

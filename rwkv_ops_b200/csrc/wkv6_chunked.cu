@@ -466,7 +466,7 @@ struct BwdSmem {
   alignas(128) unsigned char raw_dy[L * 64 * 4];
   uint64_t bar_1, bar_2, bar_2a, bar_in_a, bar_in_b, bar_in_c;
   uint32_t tmem_base;
-  int handoff_ok;
+  int handoff_ok, next_item;
 };
 static_assert(sizeof(BwdSmem) + 1024 <= 227 * 1024, "backward shared memory");
 
@@ -526,15 +526,23 @@ wkv6c_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
 
   // Work items.  Without `split` an item is a (batch, head) unit and the grid has one CTA per unit.  With it
   // (more units than SMs) every unit is two items, the later half of its chunks and the earlier half, and the
-  // grid is one persistent CTA per SM that takes items blockIdx.x, blockIdx.x + gridDim.x, ...: all later halves
-  // come first in that order, so a unit's earlier half is taken at least three items after its later half, and
-  // the state gradient travels between them through `handoff` (a flag per unit says it is there).  Halves of
-  // units instead of whole units even out the last round of CTAs (512 units on 148 SMs: 3.5 unit times instead
-  // of 4).
+  // grid is one persistent CTA per SM; a CTA that is free takes the next item from a counter (handoff_flags
+  // [n_units]).  All later halves come first in that order, so when an earlier half is taken its later half has
+  // been taken before, by a CTA that is running, and the state gradient travels between them through `handoff` (a
+  // flag per unit says it is there).  Halves of units instead of whole units even out the last round of CTAs
+  // (512 units on 148 SMs: 3.5 unit times instead of 4).
   const int n_items = split ? 2 * n_units : n_units;
   bool ok = true;
   uint32_t n_done = 0;      // chunks this CTA has worked on: every barrier completes once per chunk
-  for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+  for (bool first = true; ok; first = false) {
+  if (split) {
+    if (tid == 0) sm.next_item = atomicAdd(handoff_flags + n_units, 1);
+    __syncthreads();
+  } else if (!first) {
+    break;
+  }
+  const int item = split ? sm.next_item : (int)blockIdx.x;
+  if (item >= n_items) break;
   const int unit = split ? item % n_units : item;
   const bool early_half = split && item >= n_units;
   const int bi = unit / H, hi = unit % H;
@@ -549,6 +557,7 @@ wkv6c_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
   const int c_lo = early_half ? 0 : mid;              // last chunk of this item
   if (c_hi < c_lo) {                                  // an earlier half with nothing in it (a one-chunk sequence)
     if (tid < 64) du_partial[(size_t)item * HS + tid] = 0.f;
+    __syncthreads();      // next_item is rewritten at the top
     continue;
   }
   const float4 u4 = *reinterpret_cast<const float4*>(u + hi * HS + 4 * c4);
@@ -559,7 +568,7 @@ wkv6c_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
 #pragma unroll
   for (int j = 0; j < 32; ++j) dsreg[j] = 0.f;
   if (early_half) {
-    // wait for the later half of this unit (taken at least three items ago by a CTA that is resident): bounded
+    // wait for the later half of this unit (taken before this item, by a CTA that is running): bounded
     if (tid == 0) {
       uint32_t polls = 0;
       int seen = 0;
@@ -999,7 +1008,7 @@ inline W6Workspace w6_carve(void* workspace, int B, int Tn, int H) {
   p += a256((size_t)B * H * sizeof(int));
   w.handoff = reinterpret_cast<float*>(p);
   p += a256((size_t)B * H * HS * HS * sizeof(float));
-  w.hflags = reinterpret_cast<int*>(p);
+  w.hflags = reinterpret_cast<int*>(p);      // one flag per unit, then the item counter
   return w;
 }
 }  // namespace
@@ -1009,7 +1018,7 @@ size_t wkv6_chunked_flags_bytes(int B, int H) { return a256((size_t)B * H * size
 size_t wkv6_chunked_bwd_workspace_bytes(int B, int Tn, int H) {
   return w6_states_bytes(B, Tn, H) + a256((size_t)B * H * 2 * HS * sizeof(float)) +
          a256((size_t)B * H * 4 * HS * sizeof(float)) + wkv6_chunked_flags_bytes(B, H) +
-         a256((size_t)B * H * HS * HS * sizeof(float)) + wkv6_chunked_flags_bytes(B, H);
+         a256((size_t)B * H * HS * HS * sizeof(float)) + a256(((size_t)B * H + 1) * sizeof(int));
 }
 
 int* wkv6_chunked_workspace_flags(void* workspace, int B, int Tn, int H) { return w6_carve(workspace, B, Tn, H).flags; }
@@ -1053,7 +1062,7 @@ int launch_wkv6_chunked_bwd(const void* r, const void* k, const void* v, const v
     const int n_units = B * H;
     split = n_units > sms && (Tn + L - 1) / L >= 4;
     const int grid = split ? sms : n_units;
-    if (split && cuda_ok(cudaMemsetAsync(ws.hflags, 0, (size_t)n_units * sizeof(int), st))) return RWKVB200_E_CUDA;
+    if (split && cuda_ok(cudaMemsetAsync(ws.hflags, 0, ((size_t)n_units + 1) * sizeof(int), st))) return RWKVB200_E_CUDA;
     ProfScope prof("wkv6c_bwd_kernel", st);
     RWKVB200_DISPATCH_DTYPE(dtype, W6C_DISPATCH_PACKED(
       if (cuda_ok(cudaFuncSetAttribute(wkv6c_bwd_kernel<T, P>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)))
