@@ -301,7 +301,7 @@ int rwkvb200_rwkv7_fused_bwd(const void* r, const void* w_pre, const void* k, co
 size_t rwkvb200_wkv6_fwd_workspace_bytes(int B, int T, int H, int head_size, int dtype, int algo) {
   if (check_w6(B, T, H, head_size, dtype, algo)) return 0;
   if (resolve_w6_algo(algo, head_size) != RWKVB200_ALGO_CHUNKED) return 0;
-  return (algo & RWKVB200_ALGO_KEEP) ? wkv6_chunked_bwd_workspace_bytes(B, T, H) : wkv6_chunked_flags_bytes(B, H);
+  return (algo & RWKVB200_ALGO_KEEP) ? wkv6_chunked_bwd_workspace_bytes(B, T, H) : wkv6_chunked_fwd_scratch_bytes(B, H);
 }
 
 int rwkvb200_wkv6_fwd(const void* r, const void* k, const void* v, const void* w, const float* u,
@@ -321,13 +321,17 @@ int rwkvb200_wkv6_fwd(const void* r, const void* k, const void* v, const void* w
         workspace_bytes < rwkvb200_wkv6_fwd_workspace_bytes(B, T, H, head_size, dtype, algo))
       return RWKVB200_E_WORKSPACE;
     float* states = nullptr;
-    int* flags = reinterpret_cast<int*>(workspace);
+    float* handoff = nullptr;
+    int* flags = nullptr;
+    int* hflags = nullptr;
     if (algo & RWKVB200_ALGO_KEEP) {
       states = reinterpret_cast<float*>(workspace);
-      flags = wkv6_chunked_workspace_flags(workspace, B, T, H);
+      wkv6_chunked_workspace_parts(workspace, B, T, H, &flags, &handoff, &hflags);
+    } else {
+      wkv6_chunked_fwd_scratch(workspace, B, H, &flags, &handoff, &hflags);
     }
     return launch_wkv6_chunked_fwd(r, k, v, w, u, n_state ? s0 : nullptr, n_state, state_map, y, sT, states, flags,
-                                   B, T, H, dtype, (cudaStream_t)stream);
+                                   handoff, hflags, B, T, H, dtype, (cudaStream_t)stream);
   }
   return launch_wkv6_fwd(r, k, v, w, u, n_state ? s0 : nullptr, n_state, state_map, y, sT, nullptr,
                          B, T, H, dtype, (cudaStream_t)stream, nullptr, 0, head_size);
@@ -372,7 +376,7 @@ int rwkvb200_wkv6_bwd(const void* r, const void* k, const void* v, const void* w
 
 size_t rwkvb200_wkv6_varlen_workspace_bytes(int n_seq, int max_len, int H, int head_size, int dtype, int keep) {
   if (check_common(n_seq, max_len, H, head_size, dtype)) return 0;
-  return keep ? wkv6_chunked_bwd_workspace_bytes(n_seq, max_len, H) : wkv6_chunked_flags_bytes(n_seq, H);
+  return keep ? wkv6_chunked_bwd_workspace_bytes(n_seq, max_len, H) : wkv6_chunked_fwd_scratch_bytes(n_seq, H);
 }
 
 int rwkvb200_wkv6_fwd_varlen(const void* r, const void* k, const void* v, const void* w, const float* u,
@@ -392,13 +396,18 @@ int rwkvb200_wkv6_fwd_varlen(const void* r, const void* k, const void* v, const 
   if (!workspace || workspace_bytes < rwkvb200_wkv6_varlen_workspace_bytes(n_seq, max_len, H, head_size, dtype, keep))
     return RWKVB200_E_WORKSPACE;
   float* states = nullptr;
-  int* flags = reinterpret_cast<int*>(workspace);
+  float* handoff = nullptr;
+  int* flags = nullptr;
+  int* hflags = nullptr;
   if (keep) {
     states = reinterpret_cast<float*>(workspace);
-    flags = wkv6_chunked_workspace_flags(workspace, n_seq, max_len, H);
+    wkv6_chunked_workspace_parts(workspace, n_seq, max_len, H, &flags, &handoff, &hflags);
+  } else {
+    wkv6_chunked_fwd_scratch(workspace, n_seq, H, &flags, &handoff, &hflags);
   }
   return launch_wkv6_chunked_fwd(r, k, v, w, u, n_state ? s0 : nullptr, n_state, state_map, y, sT, states, flags,
-                                 n_seq, max_len, H, dtype, (cudaStream_t)stream, seq_start, seq_len, total_len);
+                                 handoff, hflags, n_seq, max_len, H, dtype, (cudaStream_t)stream, seq_start, seq_len,
+                                 total_len);
 }
 
 int rwkvb200_wkv6_bwd_varlen(const void* r, const void* k, const void* v, const void* w, const float* u,

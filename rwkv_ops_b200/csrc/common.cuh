@@ -176,11 +176,14 @@ constexpr int W6_CKPT = 8;
 // boundary, [B*H][ceil(T/64)+1][64][64].
 int launch_wkv6_chunked_fwd(const void* r, const void* k, const void* v, const void* w, const float* u,
                             const float* s0, int n_state, const int32_t* smap, void* y, float* sT,
-                            float* states, int* flags, int B, int Tn, int H, int dtype, cudaStream_t st,
-                            const int32_t* seq_start = nullptr, const int32_t* seq_len = nullptr, int T_total = 0);
+                            float* states, int* flags, float* handoff, int* hflags, int B, int Tn, int H, int dtype,
+                            cudaStream_t st, const int32_t* seq_start = nullptr, const int32_t* seq_len = nullptr,
+                            int T_total = 0);
+size_t wkv6_chunked_fwd_scratch_bytes(int B, int H);
+void wkv6_chunked_fwd_scratch(void* workspace, int B, int H, int** flags, float** handoff, int** hflags);
+void wkv6_chunked_workspace_parts(void* workspace, int B, int Tn, int H, int** flags, float** handoff, int** hflags);
 size_t wkv6_chunked_bwd_workspace_bytes(int B, int Tn, int H);
 size_t wkv6_chunked_flags_bytes(int B, int H);
-int* wkv6_chunked_workspace_flags(void* workspace, int B, int Tn, int H);
 int launch_wkv6_chunked_bwd(const void* r, const void* k, const void* v, const void* w, const float* u,
                             const float* s0, int n_state, const int32_t* smap, const void* d_y, const float* d_sT,
                             void* dr, void* dk, void* dv, void* dw, float* du, float* d_s0, void* workspace,

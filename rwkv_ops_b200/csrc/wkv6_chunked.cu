@@ -156,6 +156,7 @@ struct FwdSmem {
   float dgs[64];                      // sum_k r u k per token
   uint64_t bar_1, bar_2, bar_in;
   uint32_t tmem_base;
+  int handoff_ok, next_item;
 };
 
 // The raw r, k, v, w rows of a chunk (64 rows of 64 elements each) arrive by TMA in the space of the tile
@@ -170,10 +171,10 @@ wkv6c_fwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
                  const int32_t* __restrict__ smap, T* __restrict__ y, float* __restrict__ sT,
                  float* __restrict__ states, int* __restrict__ flags, const __grid_constant__ CUtensorMap tmap_r,
                  const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
-                 const __grid_constant__ CUtensorMap tmap_w, int Tn_dense, int H, Seqs seqs, int* status,
-                 long long* dbg) {
+                 const __grid_constant__ CUtensorMap tmap_w, int Tn_dense, int H, Seqs seqs, int n_units, int parts,
+                 float* __restrict__ handoff, int* __restrict__ handoff_flags, int* status, long long* dbg) {
 #ifdef RWKVB200_DEVTOOLS
-#define W6C_STAMP(n) do { if (dbg && tid == 0 && blockIdx.x == gridDim.x / 2 && c == 2) dbg[n] = clock64(); } while (0)
+#define W6C_STAMP(n) do { if (dbg && tid == 0 && item == gridDim.x / 2 && c == 2) dbg[n] = clock64(); } while (0)
 #else
 #define W6C_STAMP(n) do {} while (0)
 #endif
@@ -181,14 +182,7 @@ wkv6c_fwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
   FwdSmem& sm = *reinterpret_cast<FwdSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int wq = warp & 3, hsel = warp >> 2;
-  const int unit = blockIdx.x, bi = unit / H, hi = unit % H;
   const long long tstride = (long long)H * HS;
-  const int Tn = PACKED ? seqs.len[bi] : Tn_dense;
-  const int tok0 = PACKED ? seqs.start[bi] : 0;       // first token row of the sequence in its batch row
-  const int brow = PACKED ? 0 : bi;
-  const long long base = (((long long)brow * Tn_dense + tok0) * H + hi) * HS;   // Tn_dense: rows per batch row
-  const int NT = (Tn + L - 1) / L;
-  const size_t nts = PACKED ? (size_t)seqs.nts : (size_t)(NT + 1);
   const int srow = 16 * wq + (lane & 15);     // state row k (upper lane halves) / token row (lower lane halves)
   const bool tok_lane = lane < 16;            // lower lane halves hold token rows, upper halves state rows
 
@@ -205,35 +199,81 @@ wkv6c_fwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
   const uint32_t tm_a = tmem_addr(tm, 32 * wq, 32 * hsel);
   const uint32_t tm_ys = tmem_addr(tm, 32 * wq, 64 + 32 * hsel);
 
-  // per-thread slice of u (4 channels) for the diagonal term
   const int c4 = tid & 15;
-  const float4 u4 = *reinterpret_cast<const float4*>(u + hi * HS + 4 * c4);
-
-  // ---- initial state: rows k on the upper lane halves, this warp's 32 columns
-  float sreg[32];
-  {
-    if (!tok_lane) {
-      if (s0 && n_state > 0) {
-        const float* S = s0 + ((state_row(smap, n_state, bi) * H + hi) * HS + srow) * HS + 32 * hsel;
-#pragma unroll
-        for (int j = 0; j < 32; j += 4) {
-          const float4 f = *reinterpret_cast<const float4*>(S + j);
-          sreg[j] = f.x; sreg[j + 1] = f.y; sreg[j + 2] = f.z; sreg[j + 3] = f.w;
-        }
-      } else {
-#pragma unroll
-        for (int j = 0; j < 32; ++j) sreg[j] = 0.f;
-      }
-    } else {
-#pragma unroll
-      for (int j = 0; j < 32; ++j) sreg[j] = 0.f;
-    }
-  }
-
   const T* raw_r = reinterpret_cast<const T*>(sm.rt[0]);
   const T* raw_k = reinterpret_cast<const T*>(sm.kt[0]);
   const T* raw_v = reinterpret_cast<const T*>(sm.vt[0]);
   const T* raw_w = reinterpret_cast<const T*>(sm.at[0]);
+
+  // Work items.  parts == 1: an item is a (batch, head) unit and the grid has one CTA per unit.  parts > 1 (more
+  // units than the two CTAs per SM can hold at once): every unit is `parts` items, consecutive stretches of its
+  // chunks, on a persistent grid whose free CTAs take the next item from a counter (handoff_flags[n_units]); all
+  // first stretches come first in that order, so when a stretch is taken the one before it has been taken
+  // already, by a CTA that is running, and the state travels between them through `handoff` (handoff_flags[unit]
+  // counts the stretches of the unit that are done).  Shorter items even out the last round of CTAs (512 units
+  // on 296 slots: 1.75 unit times instead of 2).
+  const int n_items = parts * n_units;
+  bool ok = true;
+  uint32_t n_done = 0;      // chunks this CTA has worked on: every barrier completes once per chunk
+  for (bool first = true; ok; first = false) {
+  if (parts > 1) {
+    if (tid == 0) sm.next_item = atomicAdd(handoff_flags + n_units, 1);
+    __syncthreads();
+  } else if (!first) {
+    break;
+  }
+  const int item = parts > 1 ? sm.next_item : (int)blockIdx.x;
+  if (item >= n_items) break;
+  const int unit = item % n_units, part = item / n_units;
+  const int bi = unit / H, hi = unit % H;
+  const int Tn = PACKED ? seqs.len[bi] : Tn_dense;
+  const int tok0 = PACKED ? seqs.start[bi] : 0;       // first token row of the sequence in its batch row
+  const int brow = PACKED ? 0 : bi;
+  const long long base = (((long long)brow * Tn_dense + tok0) * H + hi) * HS;   // Tn_dense: rows per batch row
+  const int NT = (Tn + L - 1) / L;
+  const size_t nts = PACKED ? (size_t)seqs.nts : (size_t)(NT + 1);
+  // this item's chunks: c_lo .. c_hi - 1; the unit's last item is the one that reaches NT
+  const int c_lo = (int)((long long)NT * part / parts), c_hi = (int)((long long)NT * (part + 1) / parts);
+  const bool last_part = part == parts - 1;
+  // (a stretch without a chunk, in a sequence shorter than `parts` chunks, just passes the state on)
+  // per-thread slice of u (4 channels) for the diagonal term
+  const float4 u4 = *reinterpret_cast<const float4*>(u + hi * HS + 4 * c4);
+
+  // ---- state at the item's first chunk: rows k on the upper lane halves, this warp's 32 columns
+  float sreg[32];
+#pragma unroll
+  for (int j = 0; j < 32; ++j) sreg[j] = 0.f;
+  if (part > 0) {
+    // wait for the stretch before this one (taken before this item, by a CTA that is running): bounded
+    if (tid == 0) {
+      uint32_t polls = 0;
+      int seen = 0;
+      while (true) {
+        asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(seen) : "l"(handoff_flags + unit) : "memory");
+        if (seen >= part || ++polls > (WAIT_LIMIT << 2)) break;
+        __nanosleep(200);
+      }
+      if (seen < part) { atomicExch(status, 405); sm.handoff_ok = 0; } else { sm.handoff_ok = 1; }
+    }
+    __syncthreads();
+    ok = sm.handoff_ok != 0;
+    if (!tok_lane && ok) {
+      const float* S = handoff + (((size_t)unit * HS) + srow) * HS + 32 * hsel;
+#pragma unroll
+      for (int j = 0; j < 32; j += 4) {
+        const float4 fv = __ldcg(reinterpret_cast<const float4*>(S + j));
+        sreg[j] = fv.x; sreg[j + 1] = fv.y; sreg[j + 2] = fv.z; sreg[j + 3] = fv.w;
+      }
+    }
+  } else if (!tok_lane && s0 && n_state > 0) {
+    const float* S = s0 + ((state_row(smap, n_state, bi) * H + hi) * HS + srow) * HS + 32 * hsel;
+#pragma unroll
+    for (int j = 0; j < 32; j += 4) {
+      const float4 fv = *reinterpret_cast<const float4*>(S + j);
+      sreg[j] = fv.x; sreg[j + 1] = fv.y; sreg[j + 2] = fv.z; sreg[j + 3] = fv.w;
+    }
+  }
+
   auto load_in = [&](int c) {      // tid 0; rows past the end of the sequence arrive as zeros
     mbar_expect_tx(&sm.bar_in, 4 * 64 * 64 * (uint32_t)sizeof(T));
     tma_load_4d(sm.at[0], &tmap_w, &sm.bar_in, 0, tok0 + c * L, hi, brow);
@@ -241,12 +281,11 @@ wkv6c_fwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
     tma_load_4d(sm.rt[0], &tmap_r, &sm.bar_in, 0, tok0 + c * L, hi, brow);
     tma_load_4d(sm.kt[0], &tmap_k, &sm.bar_in, 0, tok0 + c * L, hi, brow);
   };
-  if (tid == 0 && NT > 0) load_in(0);
+  if (tid == 0 && ok && c_lo < c_hi) load_in(c_lo);
 
-  bool ok = true;
-  for (int c = 0; c < NT && ok; ++c) {
+  for (int c = c_lo; c < c_hi && ok; ++c, ++n_done) {
     const int t0 = c * L;
-    const uint32_t par = c & 1;
+    const uint32_t par = n_done & 1;
     W6C_STAMP(0);
     // ---- the raw rows of the chunk have landed: this thread's w and v elements
     ok = mbar_wait(&sm.bar_in, par, status, 403) && ok;
@@ -339,7 +378,7 @@ wkv6c_fwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
       if (c4 == 0) sm.dgs[row] = dg;
     }
     // ask for the next chunk's rows to be brought into L2 while this chunk is in its MMA phases
-    if (tid == 0 && t0 + L < Tn) {
+    if (tid == 0 && c + 1 < c_hi) {
       tma_prefetch_4d(&tmap_w, 0, tok0 + t0 + L, hi, brow);
       tma_prefetch_4d(&tmap_v, 0, tok0 + t0 + L, hi, brow);
       tma_prefetch_4d(&tmap_r, 0, tok0 + t0 + L, hi, brow);
@@ -387,7 +426,7 @@ wkv6c_fwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
     ok = mbar_wait(&sm.bar_2, par, status, 402) && ok;
     tc_fence_after();
     W6C_STAMP(7);
-    if (tid == 0 && ok && c + 1 < NT) load_in(c + 1);      // the tiles of this chunk have been read for the last time
+    if (tid == 0 && ok && c + 1 < c_hi) load_in(c + 1);      // the tiles of this chunk have been read for the last time
     if (ok) {
       uint32_t rr[32];
       tmem_ld32(tm_ys, rr);
@@ -416,21 +455,36 @@ wkv6c_fwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
     W6C_STAMP(9);
   }
 #undef W6C_STAMP
-  // ---- final state
+  // ---- the state after the item's last chunk: the unit's final state, or what its next stretch starts from
   if (!tok_lane && ok) {
-    if (sT) {
-      float* dst = sT + (((size_t)unit * HS) + srow) * HS + 32 * hsel;
+    if (last_part) {
+      if (sT) {
+        float* dst = sT + (((size_t)unit * HS) + srow) * HS + 32 * hsel;
 #pragma unroll
-      for (int j = 0; j < 32; j += 4)
-        *reinterpret_cast<float4*>(dst + j) = make_float4(sreg[j], sreg[j + 1], sreg[j + 2], sreg[j + 3]);
-    }
-    if (states) {
-      float* dst = states + (((size_t)unit * nts + NT) * HS + srow) * HS + 32 * hsel;
+        for (int j = 0; j < 32; j += 4)
+          *reinterpret_cast<float4*>(dst + j) = make_float4(sreg[j], sreg[j + 1], sreg[j + 2], sreg[j + 3]);
+      }
+      if (states) {
+        float* dst = states + (((size_t)unit * nts + NT) * HS + srow) * HS + 32 * hsel;
+#pragma unroll
+        for (int j = 0; j < 32; j += 4)
+          *reinterpret_cast<float4*>(dst + j) = make_float4(sreg[j], sreg[j + 1], sreg[j + 2], sreg[j + 3]);
+      }
+    } else {
+      float* dst = handoff + (((size_t)unit * HS) + srow) * HS + 32 * hsel;
 #pragma unroll
       for (int j = 0; j < 32; j += 4)
         *reinterpret_cast<float4*>(dst + j) = make_float4(sreg[j], sreg[j + 1], sreg[j + 2], sreg[j + 3]);
     }
   }
+  if (!last_part) {
+    __threadfence();
+    __syncthreads();
+    if (tid == 0 && ok)
+      asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(handoff_flags + unit), "r"(part + 1) : "memory");
+  }
+  __syncthreads();      // the tiles and next_item are the next item's
+  }   // items
   tc_fence_before();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tm, 128);
@@ -945,8 +999,9 @@ wkv6c_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
 
 int launch_wkv6_chunked_fwd(const void* r, const void* k, const void* v, const void* w, const float* u,
                             const float* s0, int n_state, const int32_t* smap, void* y, float* sT,
-                            float* states, int* flags, int B, int Tn, int H, int dtype, cudaStream_t st,
-                            const int32_t* seq_start, const int32_t* seq_len, int T_total) {
+                            float* states, int* flags, float* handoff, int* hflags, int B, int Tn, int H,
+                            int dtype, cudaStream_t st, const int32_t* seq_start, const int32_t* seq_len,
+                            int T_total) {
   using namespace w6c;
   // a packed batch: B sequences (the longest of Tn tokens) end to end in one row of T_total tokens
   const bool packed = seq_start != nullptr;
@@ -965,13 +1020,30 @@ int launch_wkv6_chunked_fwd(const void* r, const void* k, const void* v, const v
   if (e) return e;
 #define W6C_DISPATCH_PACKED(...) do { if (packed) { constexpr bool P = true; __VA_ARGS__; } else { constexpr bool P = false; __VA_ARGS__; } } while (0)
   {
+    // more units than the two CTAs per SM hold at once: every unit as 2 or 4 stretches of its chunks on a
+    // persistent grid, whichever evens out the last round best (see the kernel); else one CTA per unit
+    int dev = 0, sms = 0;
+    if (cuda_ok(cudaGetDevice(&dev)) || cuda_ok(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)))
+      return RWKVB200_E_CUDA;
+    const int n_units = B * H, slots = 2 * sms, NTmax = (Tn + L - 1) / L;
+    int parts = 1;
+    if (n_units > slots) {
+      double best = (double)((n_units + slots - 1) / slots);      // rounds, in unit times
+      for (int p2 = 2; p2 <= 4 && NTmax >= 4 * p2; p2 *= 2) {
+        const double rounds = (double)(((long long)n_units * p2 + slots - 1) / slots) / p2;
+        if (rounds < best - 1e-9) { best = rounds; parts = p2; }
+      }
+    }
+    const int grid = parts > 1 ? slots : n_units;
+    if (parts > 1 && cuda_ok(cudaMemsetAsync(hflags, 0, ((size_t)n_units + 1) * sizeof(int), st))) return RWKVB200_E_CUDA;
     ProfScope prof("wkv6c_fwd_kernel", st);
     RWKVB200_DISPATCH_DTYPE(dtype, W6C_DISPATCH_PACKED(
       if (cuda_ok(cudaFuncSetAttribute(wkv6c_fwd_kernel<T, P>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)))
         return RWKVB200_E_CUDA;
-      wkv6c_fwd_kernel<T, P><<<B * H, 256, smem, st>>>((const T*)r, (const T*)k, (const T*)v, (const T*)w, u, s0,
-                                                        n_state, smap, (T*)y, sT, states, flags, tm_r, tm_k, tm_v, tm_w,
-                                                        mapT, H, seqs, status, debug_stamp_buffer())));
+      wkv6c_fwd_kernel<T, P><<<grid, 256, smem, st>>>((const T*)r, (const T*)k, (const T*)v, (const T*)w, u, s0,
+                                                       n_state, smap, (T*)y, sT, states, flags, tm_r, tm_k, tm_v, tm_w,
+                                                       mapT, H, seqs, n_units, parts, handoff, hflags, status,
+                                                       debug_stamp_buffer())));
   }
   e = check_launch();
   if (e) return e;
@@ -1015,13 +1087,31 @@ inline W6Workspace w6_carve(void* workspace, int B, int Tn, int H) {
 
 size_t wkv6_chunked_flags_bytes(int B, int H) { return a256((size_t)B * H * sizeof(int)); }
 
+// scratch of a forward that keeps nothing for a backward: [unit flags | state hand-off | its flags and counter]
+size_t wkv6_chunked_fwd_scratch_bytes(int B, int H) {
+  return wkv6_chunked_flags_bytes(B, H) + a256((size_t)B * H * HS * HS * sizeof(float)) +
+         a256(((size_t)B * H + 1) * sizeof(int));
+}
+void wkv6_chunked_fwd_scratch(void* workspace, int B, int H, int** flags, float** handoff, int** hflags) {
+  char* p = reinterpret_cast<char*>(workspace);
+  *flags = reinterpret_cast<int*>(p);
+  p += wkv6_chunked_flags_bytes(B, H);
+  *handoff = reinterpret_cast<float*>(p);
+  p += a256((size_t)B * H * HS * HS * sizeof(float));
+  *hflags = reinterpret_cast<int*>(p);
+}
+// the same three parts inside the backward's workspace (a forward that keeps its chunk-boundary states)
+void wkv6_chunked_workspace_parts(void* workspace, int B, int Tn, int H, int** flags, float** handoff, int** hflags) {
+  const W6Workspace w = w6_carve(workspace, B, Tn, H);
+  *flags = w.flags; *handoff = w.handoff; *hflags = w.hflags;
+}
+
 size_t wkv6_chunked_bwd_workspace_bytes(int B, int Tn, int H) {
   return w6_states_bytes(B, Tn, H) + a256((size_t)B * H * 2 * HS * sizeof(float)) +
          a256((size_t)B * H * 4 * HS * sizeof(float)) + wkv6_chunked_flags_bytes(B, H) +
          a256((size_t)B * H * HS * HS * sizeof(float)) + a256(((size_t)B * H + 1) * sizeof(int));
 }
 
-int* wkv6_chunked_workspace_flags(void* workspace, int B, int Tn, int H) { return w6_carve(workspace, B, Tn, H).flags; }
 
 int launch_wkv6_chunked_bwd(const void* r, const void* k, const void* v, const void* w, const float* u,
                             const float* s0, int n_state, const int32_t* smap, const void* d_y, const float* d_sT,
@@ -1037,8 +1127,8 @@ int launch_wkv6_chunked_bwd(const void* r, const void* k, const void* v, const v
   float* du_partial = ws.du_partial;
   int e = RWKVB200_OK;
   if (!kept) {   // the workspace does not hold the chunk-boundary states yet: run the forward for them
-    e = launch_wkv6_chunked_fwd(r, k, v, w, u, s0, n_state, smap, nullptr, nullptr, states, ws.flags, B, Tn, H, dtype,
-                                st, seq_start, seq_len, T_total);
+    e = launch_wkv6_chunked_fwd(r, k, v, w, u, s0, n_state, smap, nullptr, nullptr, states, ws.flags, ws.handoff,
+                                ws.hflags, B, Tn, H, dtype, st, seq_start, seq_len, T_total);
     if (e) return e;
   }
   int* status = device_status_ptr();

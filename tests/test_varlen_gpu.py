@@ -242,3 +242,43 @@ def test_wkv6_packed_matches_dense_when_lengths_are_equal():
     p = {n: x[n].reshape(1, 2 * T, -1) for n in "rkvw"}
     y_p, s_p = ro.wkv6_varlen(p["r"], p["k"], p["v"], p["w"], u, [0, T, 2 * T])
     assert torch.equal(y_p.reshape(2, T, -1), y_d) and torch.equal(s_p, s_d)
+
+
+def test_wkv6_packed_with_more_sequences_than_cta_slots():
+    """400 sequences of one head, 1 .. 1100 tokens: the chunked kernels run them as work items on persistent CTAs
+    (stretches of chunks with the state handed on; sequences shorter than the number of stretches have empty
+    ones), against the recurrence run on every sequence alone."""
+    import random
+    from rwkv_ops_b200.workloads import wkv6_inputs
+    rng = random.Random(4)
+    n_seq = 400
+    lens = [rng.choice([1, 5, 64, 100, 256, 300, 513, 1100]) for _ in range(n_seq)]
+    cu = [0]
+    for n in lens:
+        cu.append(cu[-1] + n)
+    d = wkv6_inputs(1, cu[-1], 1, dtype=torch.float32, seed=78, device="cuda", with_grads=True)
+    d_state = 0.1 * torch.randn(n_seq, 1, 64, 64, device="cuda")
+    g = {n: d[n].clone().requires_grad_(True) for n in "rkvwu"}
+    y, s = ro.wkv6_varlen(g["r"], g["k"], g["v"], g["w"], g["u"], cu)
+    torch.autograd.backward([y, s], [d["d_y"], d_state])
+    g2 = {n: d[n].clone().requires_grad_(True) for n in "rkvwu"}
+    import os
+    old = os.environ.get("RWKV_OPS_B200_WKV6_ALGO")
+    os.environ["RWKV_OPS_B200_WKV6_ALGO"] = "recurrent"
+    try:
+        ys, ss = [], []
+        for i in range(n_seq):
+            sl = slice(cu[i], cu[i + 1])
+            yi, si = ro.RWKV6_OP(64, lens[i])(g2["r"][:, sl], g2["k"][:, sl], g2["v"][:, sl], g2["w"][:, sl], g2["u"],
+                                              with_state=True)
+            ys.append(yi)
+            ss.append(si)
+        torch.autograd.backward([torch.cat(ys, 1), torch.cat(ss, 0)], [d["d_y"], d_state])
+    finally:
+        if old is None:
+            os.environ.pop("RWKV_OPS_B200_WKV6_ALGO")
+        else:
+            os.environ["RWKV_OPS_B200_WKV6_ALGO"] = old
+    errs = {"y": rel_l2(y, torch.cat(ys, 1)), "s": rel_l2(s, torch.cat(ss, 0))}
+    errs.update({n: rel_l2(g[n].grad, g2[n].grad) for n in "rkvwu"})
+    assert max(errs.values()) < 1e-4, errs

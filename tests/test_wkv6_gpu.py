@@ -214,11 +214,12 @@ def test_very_short_sequences_with_fast_decays(T):
         assert all(e < 1e-4 for e in errs.values()), (seed, errs)
 
 
-@pytest.mark.parametrize("B,H,T", [(10, 20, 300), (150, 1, 512), (3, 50, 257)])
-def test_more_units_than_sms_backward_in_half_unit_items(B, H, T, monkeypatch):
-    """With more (batch, head) units than SMs the chunked backward works on every unit as two items (the later
-    and the earlier half of its chunks) and hands the state gradient from one to the other: gradients, du over
-    all batch rows and the gradient of a shared initial-state table against the float32 recurrence."""
+@pytest.mark.parametrize("B,H,T", [(10, 20, 300), (150, 1, 512), (3, 50, 257), (9, 40, 1100), (20, 16, 520)])
+def test_more_units_than_sms_work_items(B, H, T, monkeypatch):
+    """With more (batch, head) units than CTA slots the chunked kernels work on every unit as several items
+    (stretches of its chunks: two in the backward above 148 units, two or four in the forward above 296) and hand
+    the state, or its gradient, from one to the next: outputs, gradients, du over all batch rows and the gradient
+    of a shared initial-state table against the float32 recurrence."""
     d = wkv6_inputs(B, T, H, dtype=torch.float32, seed=31 + T, device="cuda", n_state=3, with_grads=True)
     res = {}
     for algo in ("chunked", "recurrent"):
