@@ -235,8 +235,10 @@ int rwkvb200_rwkv7_bwd_static(const void* r, const void* w, const void* k, const
  *                  boundary into `workspace`, and a backward called with the same flag and workspace
  *                  skips its recomputation of the forward.
  *   workspace      rwkvb200_wkv6_fwd_workspace_bytes(...) bytes: with KEEP the backward's workspace
- *                  (rwkvb200_wkv6_bwd_workspace_bytes, the two are equal), without it a few bytes per
- *                  (batch, head) for the chunked path and none for the recurrent one.
+ *                  (rwkvb200_wkv6_bwd_workspace_bytes, the two are equal), without it 16 KiB and a few
+ *                  bytes per (batch, head) for the chunked path (decay-range marks, and the state handed
+ *                  between the stretches a unit is worked on in when the units outnumber the SMs' CTA
+ *                  slots) and none for the recurrent one.
  * Head sizes 32 and 128 (the reference's operator takes the head size in its constructor,
  * rwkv_ops/rwkv6_kernel/__init__.py:37-50) run the recurrent path whatever `algo` says, except that an
  * explicit RWKVB200_ALGO_CHUNKED returns RWKVB200_E_UNSUPPORTED; states are [head_size][head_size].
