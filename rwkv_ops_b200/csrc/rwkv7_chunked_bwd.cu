@@ -175,7 +175,7 @@ template <bool PACKED>
 __global__ void __launch_bounds__(256, 2)
 r7c_bwd_scan_kernel(const __grid_constant__ CUtensorMap tmap_do, unsigned char* __restrict__ ws_tiles,
                     const float* __restrict__ ws_aux, int tiles_per_chunk, const float* __restrict__ d_ht,
-                    float* __restrict__ d_h0, SeqView sv, int H, int NT_slots, int* status) {
+                    float* __restrict__ d_h0, SeqView sv, int H, int NT_slots, int spread, int* status) {
   extern __shared__ unsigned char smem_raw[];
   BScanSmem& sm = *reinterpret_cast<BScanSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -186,6 +186,10 @@ r7c_bwd_scan_kernel(const __grid_constant__ CUtensorMap tmap_do, unsigned char* 
   const int wq = warp & 3, hsel = warp >> 2, c0 = 32 * hsel;
   const int row = 16 * wq + (lane & 15);
   const bool state_lane = lane < 16;
+  // single-thread jobs side by side: thread 0 issues the MMAs, st_thread copies dh^ and dz out (and waits for
+  // its own bulk-copy groups), ld_thread requests the operand tiles of the chunk after the next
+  // (they share the SM with a second CTA when there are more sequences than SMs, and then stay with thread 0)
+  const bool st_thread = tid == (spread ? 32 : 0), ld_thread = tid == (spread ? 64 : 0);
 
   if (tid == 0) {
     mbar_init(&sm.bar_full[0], 1); mbar_init(&sm.bar_full[1], 1);
@@ -225,20 +229,30 @@ r7c_bwd_scan_kernel(const __grid_constant__ CUtensorMap tmap_do, unsigned char* 
     for (int vv = 0; vv < 32; ++vv) dh[vv] = 0.f;
   }
 
-  bool ok = true;
+  // the two decay factors of a chunk are fetched one chunk ahead: they head the chain of a chunk
+  float dc_next = 1.f, e0_next = 1.f;
+  if (state_lane) {
+    dc_next = ws_aux[(ch0 + NT - 1) * AUX_FLOATS + 64 + row];
+    e0_next = ws_aux[(ch0 + NT - 1) * AUX_FLOATS + row];
+  }
+  bool ok = true;          // the same in every thread at the loop's head: the result of the last barrier
+  bool tail_ok = true;     // this thread's wait at the end of the previous chunk
   for (int n = 0; n < NT && ok; ++n) {
     const int c = NT - 1 - n;
     BScanStage& s = sm.st[n & 1];
     unsigned char* tiles = ws_tiles + (ch0 + c) * (size_t)tiles_per_chunk * TILE_BYTES;
-    float e0 = 1.f;
+    const float dc = dc_next, e0 = e0_next;
     if (state_lane) {
-      const float dc = ws_aux[(ch0 + c) * AUX_FLOATS + 64 + row];
-      e0 = ws_aux[(ch0 + c) * AUX_FLOATS + row];
 #pragma unroll
       for (int vv = 0; vv < 32; ++vv) dh[vv] *= dc;      // dh^ = e^{glast-gref} dh_L
       tile_store_row32(sm.dhh, row, c0, dh);
+      if (c > 0) {
+        dc_next = ws_aux[(ch0 + c - 1) * AUX_FLOATS + 64 + row];
+        e0_next = ws_aux[(ch0 + c - 1) * AUX_FLOATS + row];
+      }
     }
-    ok = mbar_wait(&sm.bar_full[n & 1], (n >> 1) & 1, status, 311);
+    ok = tail_ok && mbar_wait(&sm.bar_full[n & 1], (n >> 1) & 1, status, 311);
+    if (st_thread) bulk_wait_read();    // the copy of the previous chunk's dz has left its tile, rewritten below
     fence_async_smem();
     tc_fence_before();
     ok = __syncthreads_and(ok);
@@ -247,6 +261,8 @@ r7c_bwd_scan_kernel(const __grid_constant__ CUtensorMap tmap_do, unsigned char* 
       umma_tile<64, 64, 0, 1>(tmem_addr(tm, 16, 0), smem_u32(s.b2), smem_u32(sm.dhh), false);   // B2 dh^
       umma_tile<64, 64, 1, 1>(tmem_addr(tm, 0, 0), smem_u32(s.qt), smem_u32(s.dout), false);    // q~^T do
       umma_commit(&sm.bar_m1);
+    }
+    if (st_thread && ok) {
       bulk_store(tiles + S_DHH * TILE_BYTES, sm.dhh, TILE_BYTES);
       bulk_commit();
     }
@@ -264,6 +280,7 @@ r7c_bwd_scan_kernel(const __grid_constant__ CUtensorMap tmap_do, unsigned char* 
         tile_store_row32(sm.dz, row, c0, x);
       }
     }
+    if (st_thread) bulk_wait_read();    // the copy of dh^ has left its tile, rewritten at the top of the next chunk
     fence_async_smem();
     tc_fence_before();
     ok = __syncthreads_and(ok);
@@ -271,12 +288,16 @@ r7c_bwd_scan_kernel(const __grid_constant__ CUtensorMap tmap_do, unsigned char* 
       tc_fence_after();
       umma_tile<64, 64, 1, 1>(tmem_addr(tm, 0, 0), smem_u32(s.at), smem_u32(sm.dz), true);      // += a~^T dz
       umma_commit(&sm.bar_m2);
+    }
+    if (st_thread && ok) {
       bulk_store(tiles + S_DZ * TILE_BYTES, sm.dz, TILE_BYTES);
       bulk_commit();
     }
-    ok = ok && mbar_wait(&sm.bar_m2, n & 1, status, 313);
+    tail_ok = ok && mbar_wait(&sm.bar_m2, n & 1, status, 313);
     tc_fence_after();
-    if (ok) {
+    // this stage has been read: p2 by every thread before the last barrier, the rest by the two MMA groups
+    if (ld_thread && tail_ok && n + 2 < NT) issue_loads(n + 2);
+    if (tail_ok) {
       uint32_t r[32];
       tmem_ld32(tm_w, r);
       tmem_ld_wait();
@@ -285,17 +306,15 @@ r7c_bwd_scan_kernel(const __grid_constant__ CUtensorMap tmap_do, unsigned char* 
         for (int j = 0; j < 32; ++j) dh[j] = e0 * (__uint_as_float(r[j]) + dh[j]);
       }
     }
-    if (tid == 0) bulk_wait_read();     // dhh and dz tiles are rewritten in the next iteration
-    tc_fence_before();
-    ok = __syncthreads_and(ok);
-    if (tid == 0 && ok && n + 2 < NT) issue_loads(n + 2);
+    // no barrier here: the next one (after dh^ of the next chunk is in its tile) orders these TMEM reads
+    // before the MMAs that overwrite the accumulators
   }
-  if (state_lane && d_h0 && ok) {
+  if (state_lane && d_h0 && ok && tail_ok) {
     float* S = d_h0 + (size_t)unit * 4096;
 #pragma unroll
     for (int vv = 0; vv < 32; ++vv) S[(c0 + vv) * 64 + row] = dh[vv];
   }
-  if (tid == 0) bulk_wait_all();
+  if (st_thread) bulk_wait_all();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tm, 64);
 }
@@ -815,12 +834,15 @@ int launch_rwkv7_chunked_bwd(const void* r, const void* w, const void* k, const 
   if (e) return e;
   if (phases & PHASE_SCAN) {
     const int smem = (int)sizeof(BScanSmem) + 1024;
+    int dev = 0, sms = 0;
+    if (cuda_ok(cudaGetDevice(&dev)) || cuda_ok(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)))
+      return RWKVB200_E_CUDA;
     ProfScope prof("r7c_bwd_scan_kernel", st);
     R7C_DISPATCH_PACKED(
       if (cuda_ok(cudaFuncSetAttribute(r7c_bwd_scan_kernel<P>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)))
         return RWKVB200_E_CUDA;
       r7c_bwd_scan_kernel<P><<<B * H, 256, smem, st>>>(tmap_do, ws.tiles, ws.aux, ALL_TILES, d_ht, d_h0, sv, H, NT,
-                                                       status));
+                                                       B * H <= sms ? 1 : 0, status));
   }
   e = check_launch();
   if (e) return e;

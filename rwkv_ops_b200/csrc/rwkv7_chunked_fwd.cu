@@ -636,6 +636,15 @@ r7c_scan_fwd_kernel(const __grid_constant__ CUtensorMap tmap_v, const unsigned c
   const int NT = (Tn + L - 1) / L;           // chunks of this sequence (at least one)
   const int row = 16 * wq + (lane & 15);     // state row k (lanes 0-15) or token row i (lanes 16-31)
   const bool state_lane = lane < 16;
+  // With one CTA per SM the single-thread jobs of a chunk lie on the chain from chunk to chunk, and each
+  // bulk copy costs its issuing thread about a hundred cycles: they go to the first threads of four warps and
+  // run side by side (-12 % per chunk).  Thread 0 issues the MMAs, ld_thread requests operand tiles,
+  // st_thread copies sa and h~0 out for the backward, out_thread copies X and the output rows out.  Bulk-copy
+  // groups belong to the thread that committed them, so each storing thread waits for its own copies.  With
+  // two CTAs per SM the other CTA fills such gaps and thread 0 keeps all four jobs.
+  constexpr bool SPREAD = STAGES == 2;
+  const bool ld_thread = tid == (SPREAD ? 32 : 0), st_thread = tid == (SPREAD ? 64 : 0),
+             out_thread = tid == (SPREAD ? 96 : 0);
 
   if (tid == 0) {
     for (int i = 0; i < STAGES; ++i) { mbar_init(&sm.bar_g1[i], 1); mbar_init(&sm.bar_g2[i], 1); }
@@ -729,7 +738,7 @@ r7c_scan_fwd_kernel(const __grid_constant__ CUtensorMap tmap_v, const unsigned c
     tc_fence_after();
     R7C_STAMP(50);
     // group 1 has been read by the MMAs: request the next (the staged O1 / U rows are still to be read)
-    if (STAGES == 1 && tid == 0 && ok && c + STAGES < NT) issue_g1(c + STAGES);
+    if (STAGES == 1 && ld_thread && ok && c + STAGES < NT) issue_g1(c + STAGES);
     float keep[32];     // token lanes: q~ h~0 + O1
     if constexpr (STAGES == 2) {      // the staged O1 / U rows: observe the arrival of group 1 before reading them
       ok = ok && mbar_wait(&sm.bar_g1[c % STAGES], (c / STAGES) & 1, status, 215);
@@ -757,8 +766,8 @@ r7c_scan_fwd_kernel(const __grid_constant__ CUtensorMap tmap_v, const unsigned c
     fence_async_smem();
     tc_fence_before();
     ok = __syncthreads_and(ok);
-    if (STAGES == 2 && tid == 0 && ok && c + STAGES < NT) issue_g1(c + STAGES);
-    if (bwd_tiles && tid == 0 && ok) {   // the backward needs sa and h~0 of every chunk
+    if (STAGES == 2 && ld_thread && ok && c + STAGES < NT) issue_g1(c + STAGES);
+    if (bwd_tiles && st_thread && ok) {   // the backward needs sa and h~0 of every chunk
       unsigned char* dst = bwd_tiles + (ch0 + c) * (size_t)tiles_per_chunk * TILE_BYTES;
       bulk_store(dst + S_SA * TILE_BYTES, sm.sa, TILE_BYTES);
       bulk_store(dst + S_H0 * TILE_BYTES, sm.ht, TILE_BYTES);
@@ -780,9 +789,9 @@ r7c_scan_fwd_kernel(const __grid_constant__ CUtensorMap tmap_v, const unsigned c
     ok = ok && mbar_wait(&sm.bar_c, c & 1, status, 213);
     tc_fence_after();
     R7C_STAMP(53);
-    if (tid == 0 && ok && c + STAGES < NT) issue_g2(c + STAGES);     // group 2 has been read
+    if (ld_thread && ok && c + STAGES < NT) issue_g2(c + STAGES);     // group 2 has been read
     if (bwd_tiles) {                                  // ht / sa are rewritten below and in the next chunk
-      if (tid == 0) bulk_wait_read();
+      if (st_thread) bulk_wait_read();
       __syncthreads();
     }
     R7C_STAMP(54);
@@ -819,7 +828,7 @@ r7c_scan_fwd_kernel(const __grid_constant__ CUtensorMap tmap_v, const unsigned c
     tc_fence_before();
     ok = __syncthreads_and(ok);
     R7C_STAMP(55);
-    if (bwd_tiles && tid == 0 && ok) {
+    if (bwd_tiles && out_thread && ok) {
       bulk_store(bwd_tiles + ((ch0 + c) * (size_t)tiles_per_chunk + S_X) * TILE_BYTES, sm.xt, TILE_BYTES);
       bulk_commit();
     }
@@ -827,7 +836,7 @@ r7c_scan_fwd_kernel(const __grid_constant__ CUtensorMap tmap_v, const unsigned c
       if (PACKED && t0 + L > Tn) {  // the last rows of the box belong to the next sequence: row by row
         store_tile_rows<256>(o_rows + brow * lay.sb + hi * lay.sh + (long long)(tb + t0) * lay.st, lay.st,
                              sm.ot[c & 1], Tn - t0, tid);
-      } else if (tid == 0) {             // rows past the end of the tensor are clipped by the TMA store
+      } else if (out_thread) {           // rows past the end of the tensor are clipped by the TMA store
         tma_store_4d(&tmap_o, sm.ot[c & 1], 0, tb + t0, hi, brow);
         bulk_commit();
         bulk_wait_read_1();              // the buffer of the previous chunk is free again
@@ -836,7 +845,7 @@ r7c_scan_fwd_kernel(const __grid_constant__ CUtensorMap tmap_v, const unsigned c
     R7C_STAMP(56);
   }
 #undef R7C_STAMP
-  if (tid == 0) bulk_wait_all();
+  if (st_thread || out_thread) bulk_wait_all();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tm, 128);
 }
