@@ -53,9 +53,9 @@ FLOP_PER_TOKEN_HEAD = 434176
 # DRAM traffic (dram__bytes_read + dram__bytes_write, ncu) per chunk-head (64 tokens of one head) of each
 # chunked kernel, captured on a small case (B=2, T=4096, H=16); traffic grows in proportion to the number of
 # chunk-heads, so a full launch is this figure times B*H*ceil(T/64).
-TRAFFIC_PER_CHUNK_HEAD = {"r7c_intra_fwd_kernel": 112.1e3, "r7c_scan_fwd_kernel": 85.6e3,
-                          "r7c_bwd_pre_kernel": 35.7e3, "r7c_bwd_scan_kernel": 47.5e3,
-                          "r7c_bwd_final_kernel": 150.9e3}
+TRAFFIC_PER_CHUNK_HEAD = {"r7c_intra_fwd_kernel": 112.1e3, "r7c_scan_fwd_kernel": 85.2e3,
+                          "r7c_bwd_pre_kernel": 35.5e3, "r7c_bwd_scan_kernel": 47.9e3,
+                          "r7c_bwd_final_kernel": 149.8e3}
 TRAFFIC_SOURCE = ("ncu dram__bytes_read.sum + dram__bytes_write.sum per chunk-head on B=2 T=4096 H=16 "
                   "(a full-size launch is too large to capture), scaled by the chunk-heads of this launch")
 
