@@ -180,6 +180,32 @@ __device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t adesc, uint64_t b
       "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
       ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc) : "memory");
 }
+// The same from the two halves of each descriptor.  The issuing thread runs alone in its warp, one dependent
+// instruction every few cycles, so what it computes per MMA is what a group of MMAs costs: here two additions
+// (the lower words, by the caller) and the instruction itself; the upper word is the same for every operand
+// (SBO 1024 B, version 1, 128-byte swizzle), and a literal accumulate flag folds into the predicate.
+constexpr uint32_t UMMA_DESC_HI = ((1024u >> 4) & 0x3FFFu) | (1u << 14) | (2u << 29);
+__device__ __forceinline__ uint32_t umma_desc_lo(uint32_t addr, uint32_t lbo_bytes) {
+  return ((addr & 0x3FFFF) >> 4) | (((lbo_bytes >> 4) & 0x3FFF) << 16);
+}
+template <bool ACC>
+__device__ __forceinline__ void umma_lo(uint32_t tmem_d, uint32_t a_lo, uint32_t b_lo, uint32_t idesc) {
+  if constexpr (ACC) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+        "mov.b64 da, {%1, %4};\n\tmov.b64 db, {%2, %4};\n\t"
+        "setp.ne.b32 p, 1, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, p;\n\t}"
+        ::"r"(tmem_d), "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(UMMA_DESC_HI) : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+        "mov.b64 da, {%1, %4};\n\tmov.b64 db, {%2, %4};\n\t"
+        "setp.ne.b32 p, 0, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, p;\n\t}"
+        ::"r"(tmem_d), "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(UMMA_DESC_HI) : "memory");
+  }
+}
 // Make `bar` complete (one arrival) when all MMAs issued so far by this thread have finished.
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
@@ -195,12 +221,13 @@ __device__ __forceinline__ void umma_tile(uint32_t tmem_d, uint32_t a_addr, uint
                                           uint32_t a_lbo = TILE_BYTES, uint32_t b_lbo = TILE_BYTES) {
   static_assert(KSTEPS == 4 || (A_MN && B_MN), "a K-major operand holds 64 contraction elements");
   constexpr uint32_t id = idesc_bf16(M, N, A_MN, B_MN);
+  // lower descriptor words of step 0; a K=16 step advances the start address by 32 B (K-major) or 2048 B
+  // (MN-major), i.e. the word by 2 or 128 (no carry out of the 14-bit field: shared addresses stay below 256 KB)
+  const uint32_t a0 = umma_desc_lo(a_addr, A_MN ? a_lbo : 16u), b0 = umma_desc_lo(b_addr, B_MN ? b_lbo : 16u);
+  constexpr uint32_t a_step = A_MN ? 128u : 2u, b_step = B_MN ? 128u : 2u;
+  if (accumulate) umma_lo<true>(tmem_d, a0, b0, id); else umma_lo<false>(tmem_d, a0, b0, id);
 #pragma unroll
-  for (int ks = 0; ks < KSTEPS; ++ks) {
-    const uint64_t ad = A_MN ? desc_mnmajor(a_addr, ks, a_lbo) : desc_kmajor(a_addr, ks);
-    const uint64_t bd = B_MN ? desc_mnmajor(b_addr, ks, b_lbo) : desc_kmajor(b_addr, ks);
-    umma(tmem_d, ad, bd, id, accumulate || ks > 0);
-  }
+  for (int ks = 1; ks < KSTEPS; ++ks) umma_lo<true>(tmem_d, a0 + a_step * ks, b0 + b_step * ks, id);
 }
 
 // ---------------------------------------------------------------------------------------------
