@@ -371,7 +371,9 @@ r7c_bwd_final_kernel(const bf16* __restrict__ w, const __grid_constant__ CUtenso
   const int wq = warp & 3, hsel = warp >> 2;
 
   if (tid == 0) {
-    mbar_init(&sm.bar_lda, 1); mbar_init(&sm.bar_ldb, 1); mbar_init(&sm.bar_m1, 1); mbar_init(&sm.bar_m2, 1);
+    // each MMA group is issued by two threads (threads 0 and 32), one accumulator each, and completes with
+    // the arrival of both: one thread issues an MMA about every 80 cycles, the tensor pipe takes them faster
+    mbar_init(&sm.bar_lda, 1); mbar_init(&sm.bar_ldb, 1); mbar_init(&sm.bar_m1, 2); mbar_init(&sm.bar_m2, 2);
     fence_mbar_init();
   }
   if (warp == 0) tmem_alloc(&sm.tmem_base, 256);
@@ -500,6 +502,10 @@ r7c_bwd_final_kernel(const bf16* __restrict__ w, const __grid_constant__ CUtenso
     if (tid == 0 && ok) {
       tc_fence_after();
       umma_tile<128, 128, 0, 0>(tmem_addr(tm, 0, 0), smem_u32(sm.dout), smem_u32(sm.v), false);        // [do;dz] [v;sa]^T
+      umma_commit(&sm.bar_m1);
+    }
+    if (tid == 32 && ok) {
+      tc_fence_after();
       umma_tile<64, 64, 1, 1, 8>(tmem_addr(tm, 0, 128), smem_u32(sm.aqk), smem_u32(sm.dout), false);   // A_qk^T do + A_ak^T dz
       umma_tile<64, 64, 0, 1>(tmem_addr(tm, 0, 128), smem_u32(sm.kt), smem_u32(sm.dhh), true);         // + k~ dh^
       umma_commit(&sm.bar_m1);
@@ -593,14 +599,18 @@ r7c_bwd_final_kernel(const bf16* __restrict__ w, const __grid_constant__ CUtenso
     R7C_STAMP(20);
 
     // ---- MMA group 2: [dq~; da~] (columns 0..63) and [dk~; db~] (columns 64..127)
+    if (tid == 32 && ok) {
+      tc_fence_after();
+      umma_tile<128, 64, 1, 1>(tmem_addr(tm, 0, 64), smem_u32(sm.daqk), smem_u32(sm.qt), false, 2 * TILE_BYTES);  // [dA_qk|dA_qb]^T q~
+      umma_tile<128, 64, 1, 1>(tmem_addr(tm, 0, 64), smem_u32(sm.daak), smem_u32(sm.at), true, 2 * TILE_BYTES);   // + [dA_ak|dA_ab]^T a~
+      umma_tile<128, 64, 0, 0>(tmem_addr(tm, 0, 64), smem_u32(sm.v), smem_u32(sm.dhh), true);          // + [v;sa] dh^^T
+      umma_commit(&sm.bar_m2);
+    }
     if (tid == 0 && ok) {
       tc_fence_after();
       umma_tile<128, 64, 0, 0>(tmem_addr(tm, 0, 0), smem_u32(sm.dout), smem_u32(sm.h0), false);        // [do;dz] h~0^T
       umma_tile<128, 64, 0, 1>(tmem_addr(tm, 0, 0), smem_u32(sm.daqk), smem_u32(sm.kt), true);         // + [dA_qk;dA_ak] k~
       umma_tile<128, 64, 0, 1>(tmem_addr(tm, 0, 0), smem_u32(sm.daqb), smem_u32(sm.bt), true);         // + [dA_qb;dA_ab] b~
-      umma_tile<128, 64, 1, 1>(tmem_addr(tm, 0, 64), smem_u32(sm.daqk), smem_u32(sm.qt), false, 2 * TILE_BYTES);  // [dA_qk|dA_qb]^T q~
-      umma_tile<128, 64, 1, 1>(tmem_addr(tm, 0, 64), smem_u32(sm.daak), smem_u32(sm.at), true, 2 * TILE_BYTES);   // + [dA_ak|dA_ab]^T a~
-      umma_tile<128, 64, 0, 0>(tmem_addr(tm, 0, 64), smem_u32(sm.v), smem_u32(sm.dhh), true);          // + [v;sa] dh^^T
       umma_commit(&sm.bar_m2);
       if (!row_stores) {
         tma_store_4d(&tmap_dv, sm.aqk, 0, sv.first<PACKED>(bi) + t0, hi, sv.row<PACKED>(bi));

@@ -648,7 +648,9 @@ r7c_scan_fwd_kernel(const __grid_constant__ CUtensorMap tmap_v, const unsigned c
 
   if (tid == 0) {
     for (int i = 0; i < STAGES; ++i) { mbar_init(&sm.bar_g1[i], 1); mbar_init(&sm.bar_g2[i], 1); }
-    mbar_init(&sm.bar_a, 1); mbar_init(&sm.bar_c, 1);
+    // with one CTA per SM each accumulator of an MMA group has its own issuing thread (one thread issues an
+    // MMA about every 80 cycles, the tensor pipe takes them faster), and a group completes with all arrivals
+    mbar_init(&sm.bar_a, SPREAD ? 3 : 1); mbar_init(&sm.bar_c, SPREAD ? 2 : 1);
     fence_mbar_init();
   }
   if (warp == 0) tmem_alloc(&sm.tmem_base, 128);
@@ -722,15 +724,15 @@ r7c_scan_fwd_kernel(const __grid_constant__ CUtensorMap tmap_v, const unsigned c
       if (c + 1 < NT) scale_next = ws_aux[(ch0 + c + 1) * AUX_FLOATS + row];    // e^{gref} of the next chunk
     }
     // (a) SA = W h~0, QH = q~ h~0 (P1);  H += k~^T v (P2 lower)
-    if (tid == 0) {
+    if (lane == 0 && warp < (SPREAD ? 3 : 1)) {
       ScanGroup1<STAGES>& g = sm.g1[c % STAGES];
       ok = mbar_wait(&sm.bar_g1[c % STAGES], (c / STAGES) & 1, status, 211);
       R7C_STAMP(49);
       if (ok) {
         tc_fence_after();
-        umma_tile<64, 64, 0, 1>(tmem_addr(tm, 0, 0), smem_u32(g.w), smem_u32(sm.ht), false);
-        umma_tile<64, 64, 0, 1>(tmem_addr(tm, 16, 0), smem_u32(g.qt), smem_u32(sm.ht), false);
-        umma_tile<64, 64, 1, 1>(tmem_addr(tm, 0, 64), smem_u32(g.kt), smem_u32(g.v), true);
+        if (!SPREAD || warp == 0) umma_tile<64, 64, 0, 1>(tmem_addr(tm, 0, 0), smem_u32(g.w), smem_u32(sm.ht), false);
+        if (!SPREAD || warp == 1) umma_tile<64, 64, 0, 1>(tmem_addr(tm, 16, 0), smem_u32(g.qt), smem_u32(sm.ht), false);
+        if (!SPREAD || warp == 2) umma_tile<64, 64, 1, 1>(tmem_addr(tm, 0, 64), smem_u32(g.kt), smem_u32(g.v), true);
         umma_commit(&sm.bar_a);
       }
     }
@@ -775,14 +777,14 @@ r7c_scan_fwd_kernel(const __grid_constant__ CUtensorMap tmap_v, const unsigned c
     }
     // (c) H += b~^T sa (P2 lower);  OQ = A_qb sa (P2 upper)
     R7C_STAMP(51);
-    if (tid == 0 && ok) {
+    if (lane == 0 && warp < (SPREAD ? 2 : 1) && ok) {
       ScanGroup2& g = sm.g2[c % STAGES];
       ok = mbar_wait(&sm.bar_g2[c % STAGES], (c / STAGES) & 1, status, 214);
       R7C_STAMP(52);
       if (ok) {
         tc_fence_after();
-        umma_tile<64, 64, 1, 1>(tmem_addr(tm, 0, 64), smem_u32(g.bt), smem_u32(sm.sa), true);
-        umma_tile<64, 64, 0, 1>(tmem_addr(tm, 16, 64), smem_u32(g.aqb), smem_u32(sm.sa), false);
+        if (!SPREAD || warp == 0) umma_tile<64, 64, 1, 1>(tmem_addr(tm, 0, 64), smem_u32(g.bt), smem_u32(sm.sa), true);
+        if (!SPREAD || warp == 1) umma_tile<64, 64, 0, 1>(tmem_addr(tm, 16, 64), smem_u32(g.aqb), smem_u32(sm.sa), false);
         umma_commit(&sm.bar_c);
       }
     }

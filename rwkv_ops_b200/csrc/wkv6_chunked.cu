@@ -557,7 +557,9 @@ wkv6c_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
   float* red_x = stage_dw;                     // X k~ per (token, channel), read before dw is staged over it
 
   if (tid == 0) {
-    mbar_init(&sm.bar_1, 1); mbar_init(&sm.bar_2, 1); mbar_init(&sm.bar_2a, 1);
+    // every MMA batch is issued by two threads (threads 0 and 32, each with accumulators of its own) and completes
+    // with the arrival of both: one thread issues an MMA about every 55 cycles, the tensor pipe takes them faster
+    mbar_init(&sm.bar_1, 2); mbar_init(&sm.bar_2, 2); mbar_init(&sm.bar_2a, 2);
     mbar_init(&sm.bar_in_a, 1); mbar_init(&sm.bar_in_b, 1); mbar_init(&sm.bar_in_c, 1);
     fence_mbar_init();
   }
@@ -778,6 +780,10 @@ wkv6c_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
     if (tid == 0) {
       tc_fence_after();
       umma_split<64, 64, 0, 0>(tmem_addr(tm, 0, 0), smem_u32(sm.rt[0]), smem_u32(sm.kt[0]), false);
+      umma_commit(&sm.bar_1);
+    }
+    if (tid == 32) {
+      tc_fence_after();
       umma_split<64, 64, 0, 0>(tmem_addr(tm, 16, 0), smem_u32(sm.dyt[0]), smem_u32(sm.vt[0]), false);
       umma_commit(&sm.bar_1);
     }
@@ -831,6 +837,14 @@ wkv6c_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
       // dr~ = dy S~0^T + stril(dA) k~               (upper halves, columns 64..127)
       umma_split<64, 64, 0, 0>(tmem_addr(tm, 16, 64), smem_u32(sm.dyt[0]), smem_u32(sm.st[0]), false);
       umma_split<64, 64, 0, 1>(tmem_addr(tm, 16, 64), smem_u32(sm.dat[0]), smem_u32(sm.kt[0]), true);
+      umma_commit(&sm.bar_2a);
+      // dv = A^T dy + k~ dS^                        (lower halves, columns 128..191)
+      umma_split<64, 64, 1, 1>(tmem_addr(tm, 0, 128), smem_u32(sm.at[0]), smem_u32(sm.dyt[0]), false);
+      umma_split<64, 64, 0, 1>(tmem_addr(tm, 0, 128), smem_u32(sm.kt[0]), smem_u32(sm.dst[0]), true);
+      umma_commit(&sm.bar_2);
+    }
+    if (tid == 32 && ok) {
+      tc_fence_after();
       // the part of dk~ from inside the chunk, stril(dA)^T r~   (lower halves, columns 64..127: beside dr~, so
       // that one piece of code scales both in the epilogue)
       umma_split<64, 64, 1, 1>(tmem_addr(tm, 0, 64), smem_u32(sm.dat[0]), smem_u32(sm.rt[0]), false);
@@ -838,9 +852,6 @@ wkv6c_bwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
       // parts of dk~ k~ in different sums
       umma_split<64, 64, 0, 0>(tmem_addr(tm, 0, 192), smem_u32(sm.vt[0]), smem_u32(sm.dst[0]), false);
       umma_commit(&sm.bar_2a);
-      // dv = A^T dy + k~ dS^                        (lower halves, columns 128..191)
-      umma_split<64, 64, 1, 1>(tmem_addr(tm, 0, 128), smem_u32(sm.at[0]), smem_u32(sm.dyt[0]), false);
-      umma_split<64, 64, 0, 1>(tmem_addr(tm, 0, 128), smem_u32(sm.kt[0]), smem_u32(sm.dst[0]), true);
       // dS~0 = r~^T dy                              (upper halves, columns 128..191)
       umma_split<64, 64, 1, 1>(tmem_addr(tm, 16, 128), smem_u32(sm.rt[0]), smem_u32(sm.dyt[0]), false);
       umma_commit(&sm.bar_2);
