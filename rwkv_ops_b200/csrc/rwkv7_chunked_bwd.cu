@@ -193,7 +193,8 @@ r7c_bwd_scan_kernel(const __grid_constant__ CUtensorMap tmap_do, unsigned char* 
 
   if (tid == 0) {
     mbar_init(&sm.bar_full[0], 1); mbar_init(&sm.bar_full[1], 1);
-    mbar_init(&sm.bar_m1, 1); mbar_init(&sm.bar_m2, 1);
+    // with one CTA per SM the two products of the first MMA group have an issuing thread each
+    mbar_init(&sm.bar_m1, spread ? 2 : 1); mbar_init(&sm.bar_m2, 1);
     fence_mbar_init();
   }
   if (warp == 0) tmem_alloc(&sm.tmem_base, 64);
@@ -259,6 +260,11 @@ r7c_bwd_scan_kernel(const __grid_constant__ CUtensorMap tmap_do, unsigned char* 
     if (tid == 0 && ok) {
       tc_fence_after();
       umma_tile<64, 64, 0, 1>(tmem_addr(tm, 16, 0), smem_u32(s.b2), smem_u32(sm.dhh), false);   // B2 dh^
+      if (!spread) umma_tile<64, 64, 1, 1>(tmem_addr(tm, 0, 0), smem_u32(s.qt), smem_u32(s.dout), false);    // q~^T do
+      umma_commit(&sm.bar_m1);
+    }
+    if (spread && tid == 96 && ok) {
+      tc_fence_after();
       umma_tile<64, 64, 1, 1>(tmem_addr(tm, 0, 0), smem_u32(s.qt), smem_u32(s.dout), false);    // q~^T do
       umma_commit(&sm.bar_m1);
     }

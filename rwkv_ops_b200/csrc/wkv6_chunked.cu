@@ -187,7 +187,8 @@ wkv6c_fwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
   const bool tok_lane = lane < 16;            // lower lane halves hold token rows, upper halves state rows
 
   if (tid == 0) {
-    mbar_init(&sm.bar_1, 1); mbar_init(&sm.bar_2, 1); mbar_init(&sm.bar_in, 1);
+    // MMA batch 1 has three accumulators and three issuing threads (0, 32, 64) and completes with all arrivals
+    mbar_init(&sm.bar_1, 3); mbar_init(&sm.bar_2, 1); mbar_init(&sm.bar_in, 1);
     fence_mbar_init();
   }
   if (warp == 0) tmem_alloc(&sm.tmem_base, 128);
@@ -390,11 +391,11 @@ wkv6c_fwd_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __re
 
     W6C_STAMP(4);
     // ---- batch 1: r~ k~^T (columns 0..63), y = r~ S~0 (columns 64.., lower), k~^T v (upper)
-    if (tid == 0) {
+    if (lane == 0 && warp < 3) {
       tc_fence_after();
-      umma_split<64, 64, 0, 0>(tmem_addr(tm, 0, 0), smem_u32(sm.rt[0]), smem_u32(sm.kt[0]), false);
-      umma_split<64, 64, 0, 1>(tmem_addr(tm, 0, 64), smem_u32(sm.rt[0]), smem_u32(sm.st[0]), false);
-      umma_split<64, 64, 1, 1>(tmem_addr(tm, 16, 64), smem_u32(sm.kt[0]), smem_u32(sm.vt[0]), false);
+      if (warp == 0)      umma_split<64, 64, 0, 0>(tmem_addr(tm, 0, 0), smem_u32(sm.rt[0]), smem_u32(sm.kt[0]), false);
+      else if (warp == 1) umma_split<64, 64, 0, 1>(tmem_addr(tm, 0, 64), smem_u32(sm.rt[0]), smem_u32(sm.st[0]), false);
+      else                umma_split<64, 64, 1, 1>(tmem_addr(tm, 16, 64), smem_u32(sm.kt[0]), smem_u32(sm.vt[0]), false);
       umma_commit(&sm.bar_1);
     }
     ok = mbar_wait(&sm.bar_1, par, status, 401) && ok;
