@@ -146,22 +146,8 @@ __device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
 // K-major : rows 128 B apart, 8-row groups SBO = 1024 B apart; a K=16 step advances the start by 32 B.
 // MN-major: 64 M/N elements per 128-byte row; 8-row contraction groups SBO = 1024 B apart; the next
 //           64 M/N elements (a second tile) are LBO = 8192 B further; a K=16 step advances by 2048 B.
-__device__ __forceinline__ uint64_t umma_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
-  uint64_t d = 0;
-  d |= (uint64_t)((addr & 0x3FFFF) >> 4);
-  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
-  d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
-  d |= (uint64_t)1 << 46;
-  d |= (uint64_t)2 << 61;
-  return d;
-}
-__device__ __forceinline__ uint64_t desc_kmajor(uint32_t tile_addr, int kstep) {
-  return umma_desc(tile_addr + 32u * kstep, 16, 1024);
-}
-// `lbo` is the byte distance to the tile holding M/N elements 64..127 of a 128-wide MN-major operand.
-__device__ __forceinline__ uint64_t desc_mnmajor(uint32_t tile_addr, int kstep, uint32_t lbo = TILE_BYTES) {
-  return umma_desc(tile_addr + 2048u * kstep, lbo, 1024);
-}
+// The descriptor is built from its two 32-bit halves (umma_desc_lo, UMMA_DESC_HI below).  For an MN-major operand
+// `lbo` is the byte distance to the tile holding M/N elements 64..127 of a 128-wide operand.
 
 // Instruction descriptor, kind::f16 with bf16 inputs and fp32 accumulation.
 //   [4,6) D format 1 = f32; [7,10) A format 1 = bf16; [10,13) B format 1 = bf16;
@@ -171,17 +157,9 @@ __host__ __device__ constexpr uint32_t idesc_bf16(int M, int N, int a_mn, int b_
          ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
 }
 
-// D[tmem] (+)= A[smem] * B[smem]; issued by ONE thread.
-__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, bool accumulate) {
-  uint32_t acc = accumulate ? 1u : 0u;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc) : "memory");
-}
-// The same from the two halves of each descriptor.  The issuing thread runs alone in its warp, one dependent
-// instruction every few cycles, so what it computes per MMA is what a group of MMAs costs: here two additions
+// D[tmem] (+)= A[smem] * B[smem]; issued by ONE thread, from the two halves of each descriptor.  The issuing
+// thread runs alone in its warp, one dependent instruction every few cycles, so what it computes per MMA is
+// part of what a group of MMAs costs: here two additions
 // (the lower words, by the caller) and the instruction itself; the upper word is the same for every operand
 // (SBO 1024 B, version 1, 128-byte swizzle), and a literal accumulate flag folds into the predicate.
 constexpr uint32_t UMMA_DESC_HI = ((1024u >> 4) & 0x3FFFu) | (1u << 14) | (2u << 29);
