@@ -186,7 +186,8 @@ r7c_bwd_scan_kernel(const __grid_constant__ CUtensorMap tmap_do, unsigned char* 
   const int wq = warp & 3, hsel = warp >> 2, c0 = 32 * hsel;
   const int row = 16 * wq + (lane & 15);
   const bool state_lane = lane < 16;
-  // single-thread jobs side by side: thread 0 issues the MMAs, st_thread copies dh^ and dz out (and waits for
+  // single-thread jobs side by side: thread 0 issues the MMAs (thread 96 one product of the first group, when
+  // the CTA has the SM to itself), st_thread copies dh^ and dz out (and waits for
   // its own bulk-copy groups), ld_thread requests the operand tiles of the chunk after the next
   // (they share the SM with a second CTA when there are more sequences than SMs, and then stay with thread 0)
   const bool st_thread = tid == (spread ? 32 : 0), ld_thread = tid == (spread ? 64 : 0);

@@ -638,7 +638,8 @@ r7c_scan_fwd_kernel(const __grid_constant__ CUtensorMap tmap_v, const unsigned c
   const bool state_lane = lane < 16;
   // With one CTA per SM the single-thread jobs of a chunk lie on the chain from chunk to chunk, and each
   // bulk copy costs its issuing thread about a hundred cycles: they go to the first threads of four warps and
-  // run side by side (-12 % per chunk).  Thread 0 issues the MMAs, ld_thread requests operand tiles,
+  // run side by side (-12 % per chunk).  Thread 0 issues the MMAs (with the first threads of warps 1 and 2, one
+  // accumulator each), ld_thread requests operand tiles,
   // st_thread copies sa and h~0 out for the backward, out_thread copies X and the output rows out.  Bulk-copy
   // groups belong to the thread that committed them, so each storing thread waits for its own copies.  With
   // two CTAs per SM the other CTA fills such gaps and thread 0 keeps all four jobs.
@@ -660,7 +661,7 @@ r7c_scan_fwd_kernel(const __grid_constant__ CUtensorMap tmap_v, const unsigned c
   const uint32_t tm = sm.tmem_base;
   const uint32_t tm_p1 = tmem_addr(tm, 32 * wq, c0), tm_p2 = tmem_addr(tm, 32 * wq, 64 + c0);
 
-  auto issue_g1 = [&](int c) {      // tid 0
+  auto issue_g1 = [&](int c) {      // ld_thread (thread 0 for the first chunks)
     const unsigned char* tiles = ws_tiles + (ch0 + c) * (size_t)tiles_per_chunk * TILE_BYTES;
     ScanGroup1<STAGES>& g = sm.g1[c % STAGES];
     uint64_t* bar = &sm.bar_g1[c % STAGES];
@@ -670,7 +671,7 @@ r7c_scan_fwd_kernel(const __grid_constant__ CUtensorMap tmap_v, const unsigned c
     else                       bulk_load(g.w, tiles + S_W * TILE_BYTES, TILE_BYTES, bar);
     tma_load_4d(g.v, &tmap_v, bar, 0, tb + c * L, hi, brow);
   };
-  auto issue_g2 = [&](int c) {      // tid 0
+  auto issue_g2 = [&](int c) {      // ld_thread (thread 0 for the first chunks)
     const unsigned char* tiles = ws_tiles + (ch0 + c) * (size_t)tiles_per_chunk * TILE_BYTES;
     uint64_t* bar = &sm.bar_g2[c % STAGES];
     mbar_expect_tx(bar, 2 * TILE_BYTES);
